@@ -1,0 +1,106 @@
+/* spinf_b200: C ABI of the B200 (sm_100a) packed-prefill scoring kernels.
+ *
+ * The reference (spinf-serve) has no FFI of its own: its seams for this path are Python callables (attention interface, quantized
+ * linear modules, the recurrent-layer functions, the scorer's lm-head read). Each entry point below is what a binding for one of
+ * those seams calls; the comment above it names the reference symbol (file:line inside the spinf-serve tree) whose arithmetic it
+ * replaces. Conventions:
+ *   - plain pointers and sizes only; every pointer is DEVICE memory unless the name ends in _host;
+ *   - `stream` is a cudaStream_t passed as void*; calls enqueue work and return without synchronising;
+ *   - no entry point allocates device memory except spinf_init (one 256-byte status word per device); scratch is passed in by
+ *     the caller and sized by the matching *_workspace_bytes query;
+ *   - return value: 0 = enqueued; negative = rejected on the host before any launch (SPINF_ERR_*);
+ *   - kernels never spin without bound: a wait that gives up writes a positive code to the per-device status word, which
+ *     spinf_last_status() returns (and clears). Outputs of a call that reported a status are undefined.
+ */
+#ifndef SPINF_B200_H
+#define SPINF_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SPINF_ERR_BAD_ARGUMENT (-1) /* null pointer, size or alignment the kernel does not support */
+#define SPINF_ERR_CUDA (-2)         /* a CUDA runtime call failed (no device, launch error) */
+#define SPINF_ERR_TENSORMAP (-3)    /* the TMA descriptor could not be encoded (unaligned base or pitch) */
+#define SPINF_ERR_TOO_LARGE (-4)    /* a size exceeds a documented maximum */
+
+/* device status codes returned by spinf_last_status */
+#define SPINF_ST_TIMEOUT_FULL 1
+#define SPINF_ST_TIMEOUT_EMPTY 2
+#define SPINF_ST_TIMEOUT_TMEM 3
+#define SPINF_ST_TIMEOUT_OTHER 4
+#define SPINF_ST_BAD_INDEX 5
+
+#define SPINF_BLOCK 128 /* stream block size: packed streams are multiples of it (packer.py:22) */
+
+/* Library version (major*10000 + minor*100 + patch). */
+int spinf_version(void);
+
+/* Prepares the current device: allocates its status word and raises the kernels' dynamic shared-memory limits. Call once per
+ * device before any other entry point (and before any stream capture). */
+int spinf_init(void);
+
+/* Synchronises `stream`, returns the device status word (0 = every kernel since the last call completed its waits) and clears it. */
+int spinf_last_status(void* stream);
+
+/* ------------------------------------------------------------------------------------------------------------ fp8 row-wise linear
+ * Replaces quant_act_row (spinf_serve/quant/linears.py:29-33): per row m of x [M,K] bf16,
+ *   xs[m] = max(|x[m,:]|, 1e-12) / 448 (fp32);  x8[m,k] = e4m3_rne(clamp(float(x[m,k]) / xs[m], -448, 448)).
+ * K must be a multiple of 8 and at most 32768. */
+int spinf_fp8_rowwise_quant(const void* x_bf16, int64_t M, int64_t K, void* x8, float* xs, void* stream);
+
+/* Replaces Fp8RowLinear.forward's torch._scaled_mm call (spinf_serve/quant/linears.py:93-96):
+ *   y[m,n] = bf16( (sum_k x8[m,k] * w8[n,k])_fp32 * xs[m] * ws[n] )
+ * x8 [M,K] e4m3 row-major; w8 [N,K] e4m3 row-major (the storage of the reference's `w8t` buffer, which is the [K,N] column-major
+ * view of it); xs [M], ws [N] fp32; y [M,N] bf16 row-major. K and N multiples of 16. A row of y does not depend on M. */
+int spinf_fp8_rowwise_gemm(const void* x8, const float* xs, const void* w8, const float* ws, void* y_bf16, int64_t M, int64_t N,
+                           int64_t K, void* stream);
+
+/* Plain bf16 linear y = bf16(x @ w^T) with fp32 accumulation: x [M,K], w [N,K], y [M,N], all bf16 row-major; K, N multiples of 8.
+ * Replaces the torch.nn.functional.linear / `x @ w.t()` calls on un-quantised weights (spinf_serve/models/qwen35/qwen.py:456-458
+ * "extra" rows, and bf16-scheme linears). */
+int spinf_bf16_gemm(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, void* stream);
+
+/* ------------------------------------------------------------------------------------------------------------ option log-probs
+ * Replaces Scorer._logprobs followed by the `[:, ci]` gather (spinf_serve/scorer.py:340-355 and :254): for read rows h [R,hidden]
+ * bf16 and the lm-head matrix W [vocab,hidden] bf16,
+ *   logits = h @ W^T (fp32 accumulate, fp32 out); if softcap > 0: logits = softcap * tanh(logits / softcap);
+ *   out[r,c] = logits[r, cols[c]] - logsumexp_v(logits[r, v])            (fp32 [R, n_cols])
+ * The [R,vocab] matrix is never written: the GEMM's epilogue keeps a running (max, sum-exp) per row and vocabulary tile and
+ * captures the option columns. `cols` are the sorted (ascending) distinct option token ids (Scorer._cols, scorer.py:420-430), on
+ * the device; an id outside [0, vocab) is skipped and its output column left unwritten. `workspace` needs spinf_option_logprobs_workspace_bytes(R, vocab, n_cols) bytes.
+ * hidden a multiple of 8. A row's result does not depend on R (no padding to lm_rows is needed, scorer.py:327-333). */
+int64_t spinf_option_logprobs_workspace_bytes(int64_t R, int64_t vocab, int64_t n_cols);
+int spinf_option_logprobs(const void* h, const void* W, int64_t R, int64_t hidden, int64_t vocab, const int32_t* cols,
+                          int64_t n_cols, float softcap, float* out, void* workspace,
+                          int64_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------------------ tree-mask attention
+ * Host function. Replaces packer.block_tables (spinf_serve/packer.py:426-491) for text-only streams: from the per-token arrays of
+ * a packed stream (art, end, pos: int32 [n], n a multiple of 128) builds, for each 128-row query block, the ascending list of
+ * 128-column key blocks it must visit and a flag per entry (1 = every pair attends, the mask need not be evaluated).
+ *   counts_host [nb], blocks_host [nb*nb] (row i holds counts[i] entries), flags_host [nb*nb] (uint8).
+ * window <= 0: full-attention table; window > 0: sliding table (no "full" flags, blocks wholly outside the window skipped).
+ * Returns the total number of visited blocks, or a negative error. */
+int64_t spinf_tile_desc_build_host(const int32_t* art_host, const int32_t* end_host, const int32_t* pos_host, int64_t n,
+                                   int32_t window, int32_t* counts_host, int32_t* blocks_host, uint8_t* flags_host);
+
+/* Replaces the "tree_flex" attention interface (spinf_serve/models/gemma4.py:99-121, mask rule spinf_serve/scorer.py:173-177) and
+ * qwen.tree_attention (spinf_serve/models/qwen35/qwen.py:605-623):
+ *   out[t,h,:] = sum_k softmax_k(scale * q[t,h,:].k[k,g,:] | visible(t,k)) v[k,g,:],   g = h / (H/Hkv)
+ *   visible(t,k) = (k <= t && art[t] >= 0 && art[k] == art[t] && t < end[k] && (window <= 0 || pos[t]-pos[k] < window)) || t == k
+ * q [n,H,D], k,v [n,Hkv,D], out [n,H,D] bf16, token-major with row pitches given in ELEMENTS (so q/k/v may be slices of one fused
+ * projection output); D in {128, 256}; n a multiple of 128. tile_offsets [nb+1] (prefix sums of counts), tile_blocks, tile_flags:
+ * the packed lists from spinf_tile_desc_build_host, on the device. Scores are fp32, P is rounded to bf16 before P.V, the running
+ * maximum is updated once per 64 keys in ascending key order: a row's result depends only on its own job's tokens. */
+int spinf_tree_attn_fwd(const void* q, const void* k, const void* v, void* out, int64_t n, int32_t H, int32_t Hkv, int32_t D,
+                        int64_t q_pitch, int64_t kv_pitch, int64_t out_pitch, const int32_t* art, const int32_t* end,
+                        const int32_t* pos, int32_t window, float scale, const int32_t* tile_offsets, const int32_t* tile_blocks,
+                        const uint8_t* tile_flags, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPINF_B200_H */

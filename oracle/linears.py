@@ -1,0 +1,71 @@
+"""Oracle of the quantized linears (CPU torch; test infrastructure only, never imported by the product).
+
+Row-wise fp8 follows spinf_serve/quant/linears.py:29-33 (quant_act_row) and :84-96 (Fp8RowLinear); torch._scaled_mm with row-wise
+scales has no CPU kernel, so the product is restated as the fp32 matmul of the e4m3 values times both scales, rounded once to bf16.
+The quantiser formula is pinned bit-for-bit by the reference's own test (tests/test_fp8_checkpoint.py:11-23, per-tensor variant).
+int4 follows spinf_serve/models/qwen35/qwen.py:383-391 (GPTQ unpack), :326-330 (dq_bf16) and :455-458 (bf16 mode)."""
+
+import torch
+
+FP8_MAX = 448.0  # spinf_serve/quant/fp8.py:11
+
+
+def quantize_weight_rowwise(w):
+    """bf16 [out, in] -> (w8 [out, in] e4m3, ws [1, out] fp32): Fp8RowLinear.__init__, linears.py:85-91"""
+    wf = w.float()
+    s = wf.abs().amax(-1, keepdim=True).clamp(min=1e-12) / FP8_MAX
+    return (wf / s).clamp_(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn), s.t().contiguous()
+
+
+def quant_act_row(x):
+    """[..., K] -> (x8 [M, K] e4m3, xs [M, 1] fp32): linears.py:29-33"""
+    xf = x.reshape(-1, x.shape[-1]).float()
+    s = xf.abs().amax(-1, keepdim=True).clamp_(min=1e-12) / FP8_MAX
+    return (xf / s).clamp_(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn), s
+
+
+def scaled_mm_rowwise(x8, xs, w8, ws, exact=False):
+    """bf16((x8 @ w8^T) * xs * ws): the row-wise torch._scaled_mm of linears.py:95. exact=True accumulates in float64 (the exact
+    product of the quantized operands, used to bound a kernel's error independently of summation order)"""
+    if exact:
+        acc = x8.double() @ w8.double().t()
+        return acc * xs.double().reshape(-1, 1) * ws.double().reshape(1, -1)
+    acc = x8.float() @ w8.float().t()
+    return (acc * xs.reshape(-1, 1) * ws.reshape(1, -1)).to(torch.bfloat16)
+
+
+def fp8_row_linear(x, w8, ws):
+    """Fp8RowLinear.forward, linears.py:93-96"""
+    x8, xs = quant_act_row(x)
+    return scaled_mm_rowwise(x8, xs, w8, ws).reshape(*x.shape[:-1], w8.shape[0])
+
+
+# ------------------------------------------------------------------------------------------------ int4 (GPTQ v1, symmetric)
+def gptq_unpack(qweight, scales):
+    """qweight int32 [K/8, N] (8 nibbles per word, shifts 0..28), scales fp16 [K/G, N] -> (q uint8 [N, K/2] low nibble = even k,
+    s fp16 [N, K/G]): Int4Linear.__init__, qwen.py:383-391"""
+    K8, N = qweight.shape
+    shifts = torch.arange(0, 32, 4, dtype=torch.int32)
+    nib = ((qweight[:, None, :] >> shifts[None, :, None]) & 15).reshape(K8 * 8, N).to(torch.uint8)  # [K, N]
+    nt = nib.t().contiguous()  # [N, K]
+    q = nt[:, 0::2] | (nt[:, 1::2] << 4)
+    return q.contiguous(), scales.t().contiguous()
+
+
+def dq_bf16(q, s, group):
+    """(nibble - 8) * scale in fp32, rounded once to bf16 -> [N, K]: qwen.py:326-330"""
+    lo = (q & 15).to(torch.int16) - 8
+    hi = (q >> 4).to(torch.int16) - 8
+    w = torch.stack((lo, hi), dim=-1).reshape(q.shape[0], -1).float()
+    return (w * s.float().repeat_interleave(group, dim=1)).to(torch.bfloat16)
+
+
+def int4_linear(x, q, s, group, extra=None, exact=False):
+    """Int4Linear.forward in bf16 mode, qwen.py:455-458: x @ dq(w)^T with fp32 accumulation, bf16 out; `extra` un-quantised bf16
+    rows are appended to the output channels (qwen.py:421-426)"""
+    w = dq_bf16(q, s, group)
+    if extra is not None:
+        w = torch.cat([w, extra.to(torch.bfloat16)], 0)
+    if exact:
+        return x.double() @ w.double().t()
+    return (x.float() @ w.float().t()).to(torch.bfloat16)

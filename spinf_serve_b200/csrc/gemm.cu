@@ -1,0 +1,269 @@
+// Launchers of the tcgen05 GEMMs: the row-wise fp8 linear, the plain bf16 linear and the fused option-log-prob read.
+#include "gemm_tc.cuh"
+#include "host_util.h"
+
+namespace spinf {
+
+// ------------------------------------------------------------------------------------------------ option log-prob epilogue
+// Per accumulator tile (128 read rows x 256 vocabulary columns) every thread keeps the running maximum and sum of exponentials
+// of its row, writes them to part_max/part_sum[tile_n][row], and copies the (soft-capped) logits of the option columns that fall
+// inside the tile to `out`. lse_finalize_kernel then merges the per-tile partials in ascending tile order.
+template <int BN>
+struct EpiLse {
+  static constexpr bool kReadsTmemInEnd = true;
+  float softcap;
+  float* part_max;  // [tiles_n, Mpad]
+  float* part_sum;  // [tiles_n, Mpad]
+  int Mpad;
+  const int* cols;            // sorted distinct option token ids
+  const int* col_tile_start;  // [tiles_n + 1]: cols[col_tile_start[t] .. col_tile_start[t+1]) lie in vocabulary tile t
+  float* out;                 // [M, n_cols]
+  int n_cols;
+  struct State {
+    float m, s;
+  };
+
+  __device__ __forceinline__ float cap(float v) const { return softcap > 0.f ? softcap * tanhf(v / softcap) : v; }
+
+  __device__ __forceinline__ void begin_tile(State& st, const GemmShape&, int, int, int, float*) const {
+    st.m = -INFINITY;
+    st.s = 0.f;
+  }
+  __device__ __forceinline__ void chunk(State& st, const GemmShape& s, int tm, int tn, int row, int et, int c,
+                                        const uint32_t (&v0)[32], const uint32_t (&v1)[32], const float*, uint8_t*) const {
+    const int n0 = tn * BN + c * 64;
+    float x[64];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      x[i] = n0 + i < s.N ? cap(__uint_as_float(v0[i])) : -INFINITY;
+      x[32 + i] = n0 + 32 + i < s.N ? cap(__uint_as_float(v1[i])) : -INFINITY;
+    }
+#pragma unroll
+    for (int i = 0; i < 64; ++i) mx = fmaxf(mx, x[i]);
+    const float m_new = fmaxf(st.m, mx);
+    if (m_new == -INFINITY) return;
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 64; ++i) acc += __expf(x[i] - m_new);
+    st.s = st.s * __expf(st.m - m_new) + acc;
+    st.m = m_new;
+  }
+  __device__ __forceinline__ void end_tile(State& st, const GemmShape& s, int tm, int tn, int row, int et, uint32_t t_row,
+                                           const float*) const {
+    const int m = tm * 128 + row;
+    part_max[static_cast<size_t>(tn) * Mpad + m] = st.m;
+    part_sum[static_cast<size_t>(tn) * Mpad + m] = st.s;
+    const int c0 = col_tile_start[tn], c1 = col_tile_start[tn + 1];
+    for (int ci = c0; ci < c1; ++ci) {  // uniform across the CTA
+      const int col = cols[ci] - tn * BN;
+      if (col < 0 || col >= BN) continue;  // malformed column table: skip, never index outside the accumulator
+      uint32_t r;
+      tmem_ld_x1(t_row + col, r);
+      tmem_wait_ld();
+      if (m < s.M) out[static_cast<size_t>(m) * n_cols + ci] = cap(__uint_as_float(r));
+    }
+  }
+  __device__ __forceinline__ void finish(State&, int) const {}
+};
+
+// start[t] = index of the first option column >= t * BN (cols ascending), t = 0..tiles_n
+__global__ void col_tile_start_kernel(const int* __restrict__ cols, int n_cols, int tiles_n, int BN, int* __restrict__ start) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t > tiles_n) return;
+  const long long key = static_cast<long long>(t) * BN;
+  int lo = 0, hi = n_cols;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (cols[mid] < key) lo = mid + 1; else hi = mid;
+  }
+  start[t] = lo;
+}
+
+__global__ void lse_finalize_kernel(const float* __restrict__ part_max, const float* __restrict__ part_sum, int tiles_n, int Mpad,
+                                    int M, float* __restrict__ out, int n_cols) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= M) return;
+  float m = -INFINITY, s = 0.f;
+  for (int t = 0; t < tiles_n; ++t) {
+    const float pm = part_max[static_cast<size_t>(t) * Mpad + r];
+    const float ps = part_sum[static_cast<size_t>(t) * Mpad + r];
+    const float mn = fmaxf(m, pm);
+    if (mn == -INFINITY) continue;
+    s = s * __expf(m - mn) + ps * __expf(pm - mn);
+    m = mn;
+  }
+  const float lse = m + logf(s);
+  for (int c = 0; c < n_cols; ++c) out[static_cast<size_t>(r) * n_cols + c] -= lse;
+}
+
+// ------------------------------------------------------------------------------------------------ per-row fp8 quantiser
+// One CTA per row: amax over the row in fp32, then x / s (a true division, as the reference computes it), clamped and cast to e4m3
+// with round-to-nearest-even.
+__global__ void __launch_bounds__(256) fp8_rowwise_quant_kernel(const __nv_bfloat16* __restrict__ x, int K, uint8_t* __restrict__ x8,
+                                                                float* __restrict__ xs) {
+  const size_t row = blockIdx.x;
+  const uint4* src = reinterpret_cast<const uint4*>(x + row * K);
+  const int nvec = K / 8;
+  __shared__ float red[8];
+  float amax = 0.f;
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    uint4 u = src[i];
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f = __bfloat1622float2(p[j]);
+      amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
+  }
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = red[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) amax = fmaxf(amax, red[w]);
+  const float s = __fdiv_rn(fmaxf(amax, 1e-12f), 448.f);
+  if (threadIdx.x == 0) xs[row] = s;
+  uint2* dst = reinterpret_cast<uint2*>(x8 + row * K);
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    uint4 u = src[i];
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+    uint32_t o[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      float2 a = __bfloat1622float2(p[2 * j]), b = __bfloat1622float2(p[2 * j + 1]);
+      const float q0 = fminf(fmaxf(__fdiv_rn(a.x, s), -448.f), 448.f), q1 = fminf(fmaxf(__fdiv_rn(a.y, s), -448.f), 448.f);
+      const float q2 = fminf(fmaxf(__fdiv_rn(b.x, s), -448.f), 448.f), q3 = fminf(fmaxf(__fdiv_rn(b.y, s), -448.f), 448.f);
+      const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(q0, q1), __NV_SATFINITE, __NV_E4M3);
+      const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(q2, q3), __NV_SATFINITE, __NV_E4M3);
+      o[j] = lo | (hi << 16);
+    }
+    dst[i] = make_uint2(o[0], o[1]);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ launch helpers
+template <int KIND, int BN, class Epi>
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmShape& shape, const Epi& epi, cudaStream_t stream) {
+  int dev = 0;
+  SPINF_CUDA_OK(cudaGetDevice(&dev));
+  int* status = status_word(dev);
+  if (!status) return SPINF_ERR_CUDA;
+  auto kern = gemm_tc_kernel<KIND, BN, Epi>;
+  static bool attr_set[64] = {false};
+  if (!attr_set[dev]) {
+    SPINF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN>::TOTAL));
+    attr_set[dev] = true;
+  }
+  const int tiles = shape.tiles_m * shape.tiles_n;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kern<<<grid, 192, GemmSmem<BN>::TOTAL, stream>>>(tmA, tmB, shape, epi, status);
+  SPINF_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+static GemmShape make_shape(int64_t M, int64_t N, int64_t K, int BN) {
+  GemmShape s;
+  s.M = static_cast<int>(M);
+  s.N = static_cast<int>(N);
+  s.K = static_cast<int>(K);
+  s.tiles_m = static_cast<int>((M + 127) / 128);
+  s.tiles_n = static_cast<int>((N + BN - 1) / BN);
+  s.group_m = 8;
+  return s;
+}
+
+}  // namespace spinf
+
+using namespace spinf;
+
+extern "C" int spinf_fp8_rowwise_quant(const void* x_bf16, int64_t M, int64_t K, void* x8, float* xs, void* stream) {
+  SPINF_CHECK_ARG(x_bf16 && x8 && xs && M >= 0 && K > 0 && K % 8 == 0 && K <= 32768 && M < (1ll << 31));
+  if (M == 0) return 0;
+  fp8_rowwise_quant_kernel<<<static_cast<unsigned>(M), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x_bf16), static_cast<int>(K), static_cast<uint8_t*>(x8), xs);
+  SPINF_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int spinf_fp8_rowwise_gemm(const void* x8, const float* xs, const void* w8, const float* ws, void* y_bf16, int64_t M,
+                                      int64_t N, int64_t K, void* stream) {
+  SPINF_CHECK_ARG(x8 && xs && w8 && ws && y_bf16 && M >= 0 && N > 0 && K > 0 && K % 16 == 0 && N % 16 == 0);
+  SPINF_CHECK_ARG(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31));
+  if (M == 0) return 0;
+  constexpr int BN = 256;
+  CUtensorMap tmA, tmB;
+  EpiStoreBf16<BN, true> epi;
+  int r;
+  if ((r = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x8, M, K, K, 128, 128))) return r;
+  if ((r = make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w8, N, K, K, 128, BN))) return r;
+  if ((r = make_tmap_2d(&epi.tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y_bf16, M, N, N * 2, 64, 128))) return r;
+  epi.rowscale = xs;
+  epi.colscale_g = ws;
+  return launch_gemm<KIND_F8, BN>(tmA, tmB, make_shape(M, N, K, BN), epi, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int spinf_bf16_gemm(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, void* stream) {
+  SPINF_CHECK_ARG(x && w && y && M >= 0 && N > 0 && K > 0 && K % 8 == 0 && N % 8 == 0);
+  SPINF_CHECK_ARG(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31));
+  if (M == 0) return 0;
+  constexpr int BN = 256;
+  CUtensorMap tmA, tmB;
+  EpiStoreBf16<BN, false> epi;
+  int r;
+  if ((r = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, M, K, K * 2, 64, 128))) return r;
+  if ((r = make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, N, K, K * 2, 64, BN))) return r;
+  if ((r = make_tmap_2d(&epi.tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y, M, N, N * 2, 64, 128))) return r;
+  epi.rowscale = nullptr;
+  epi.colscale_g = nullptr;
+  return launch_gemm<KIND_BF16, BN>(tmA, tmB, make_shape(M, N, K, BN), epi, static_cast<cudaStream_t>(stream));
+}
+
+// workspace layout: part_max [tiles_n * Mpad] f32 | part_sum [tiles_n * Mpad] f32 | col_tile_start [tiles_n + 1] i32
+extern "C" int64_t spinf_option_logprobs_workspace_bytes(int64_t R, int64_t vocab, int64_t n_cols) {
+  if (R < 0 || vocab <= 0 || n_cols < 0) return SPINF_ERR_BAD_ARGUMENT;
+  const int64_t tiles_n = (vocab + 255) / 256, Mpad = (R + 127) / 128 * 128;
+  return 2 * tiles_n * Mpad * 4 + (tiles_n + 1) * 4 + 256;
+}
+
+extern "C" int spinf_option_logprobs(const void* h, const void* W, int64_t R, int64_t hidden, int64_t vocab, const int32_t* cols,
+                                     int64_t n_cols, float softcap, float* out, void* workspace,
+                                     int64_t workspace_bytes, void* stream) {
+  SPINF_CHECK_ARG(h && W && out && workspace && R >= 0 && hidden > 0 && hidden % 8 == 0 && vocab > 0 && n_cols >= 0);
+  SPINF_CHECK_ARG(n_cols == 0 || cols);
+  SPINF_CHECK_ARG(R < (1ll << 31) && vocab < (1ll << 31) && hidden < (1ll << 31) && n_cols < (1ll << 24));
+  SPINF_CHECK_ARG((reinterpret_cast<uintptr_t>(workspace) & 15) == 0);
+  if (workspace_bytes < spinf_option_logprobs_workspace_bytes(R, vocab, n_cols)) return SPINF_ERR_BAD_ARGUMENT;
+  if (R == 0) return 0;
+  constexpr int BN = 256;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const GemmShape shape = make_shape(R, vocab, hidden, BN);
+  const int64_t Mpad = static_cast<int64_t>(shape.tiles_m) * 128;
+  float* part_max = static_cast<float*>(workspace);
+  float* part_sum = part_max + shape.tiles_n * Mpad;
+  int32_t* start_dev = reinterpret_cast<int32_t*>(part_sum + shape.tiles_n * Mpad);
+  col_tile_start_kernel<<<(shape.tiles_n + 1 + 255) / 256, 256, 0, st>>>(cols, static_cast<int>(n_cols), shape.tiles_n, BN, start_dev);
+  SPINF_CUDA_OK(cudaGetLastError());
+
+  CUtensorMap tmA, tmB;
+  int r;
+  if ((r = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, h, R, hidden, hidden * 2, 64, 128))) return r;
+  if ((r = make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, vocab, hidden, hidden * 2, 64, BN))) return r;
+  EpiLse<BN> epi;
+  epi.softcap = softcap;
+  epi.part_max = part_max;
+  epi.part_sum = part_sum;
+  epi.Mpad = static_cast<int>(Mpad);
+  epi.cols = cols;
+  epi.col_tile_start = start_dev;
+  epi.out = out;
+  epi.n_cols = static_cast<int>(n_cols);
+  GemmShape sh = shape;
+  sh.group_m = shape.tiles_m;  // all row tiles of one vocabulary tile run together: W is streamed from HBM once
+  if ((r = launch_gemm<KIND_BF16, BN>(tmA, tmB, sh, epi, st))) return r;
+  lse_finalize_kernel<<<static_cast<unsigned>((R + 127) / 128), 128, 0, st>>>(part_max, part_sum, shape.tiles_n,
+                                                                             static_cast<int>(Mpad), static_cast<int>(R), out,
+                                                                             static_cast<int>(n_cols));
+  SPINF_CUDA_OK(cudaGetLastError());
+  return 0;
+}

@@ -1,0 +1,94 @@
+"""Tensor-level wrappers over the C ABI: each function checks dtype / layout / device, allocates the outputs with torch (device
+memory and streams are torch's), and enqueues one entry point of libspinf_b200.so on the current stream. Nothing here computes on
+the CPU or through another library: a tensor that is not on a CUDA device is an error."""
+
+import ctypes
+
+import torch
+
+from spinf_serve_b200 import _lib
+from spinf_serve_b200._lib import SpinfError, check, ptr, stream_ptr
+
+FP8 = torch.float8_e4m3fn
+
+
+def _need(t, dtype, name, dims=None):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise SpinfError(f"{name}: expected a CUDA tensor (this library has no CPU path)")
+    if t.dtype != dtype:
+        raise SpinfError(f"{name}: expected {dtype}, got {t.dtype}")
+    if dims is not None and t.dim() != dims:
+        raise SpinfError(f"{name}: expected {dims} dimensions, got {t.dim()}")
+    if not t.is_contiguous():
+        raise SpinfError(f"{name}: expected a contiguous tensor")
+    _lib.init(t.device)
+
+
+def fp8_rowwise_quant(x):
+    """x [..., K] bf16 -> (x8 [M, K] e4m3, xs [M, 1] fp32), per-row dynamic scales (quant_act_row, spinf_serve/quant/linears.py:29-33)"""
+    x2 = x.reshape(-1, x.shape[-1])
+    _need(x2, torch.bfloat16, "x", 2)
+    M, K = x2.shape
+    x8 = torch.empty((M, K), dtype=FP8, device=x.device)
+    xs = torch.empty((M, 1), dtype=torch.float32, device=x.device)
+    check(_lib.lib().spinf_fp8_rowwise_quant(ptr(x2), M, K, ptr(x8), ptr(xs), stream_ptr()), "spinf_fp8_rowwise_quant")
+    return x8, xs
+
+
+def fp8_rowwise_gemm(x8, xs, w8, ws, out=None):
+    """y [M, N] bf16 = (x8 [M, K] @ w8 [N, K]^T) * xs [M] * ws [N] (spinf_serve/quant/linears.py:93-96)"""
+    _need(x8, FP8, "x8", 2)
+    _need(w8, FP8, "w8", 2)
+    xs1, ws1 = xs.reshape(-1), ws.reshape(-1)
+    _need(xs1, torch.float32, "xs", 1)
+    _need(ws1, torch.float32, "ws", 1)
+    M, K = x8.shape
+    N = w8.shape[0]
+    if w8.shape[1] != K or xs1.numel() != M or ws1.numel() != N:
+        raise SpinfError(f"fp8_rowwise_gemm: shapes do not agree: x8 {tuple(x8.shape)}, w8 {tuple(w8.shape)}, xs {xs1.numel()}, ws {ws1.numel()}")
+    y = out if out is not None else torch.empty((M, N), dtype=torch.bfloat16, device=x8.device)
+    if out is not None:
+        _need(out, torch.bfloat16, "out", 2)
+    check(
+        _lib.lib().spinf_fp8_rowwise_gemm(ptr(x8), ptr(xs1), ptr(w8), ptr(ws1), ptr(y), M, N, K, stream_ptr()),
+        "spinf_fp8_rowwise_gemm",
+    )
+    return y
+
+
+def bf16_gemm(x, w):
+    """y [M, N] bf16 = x [M, K] @ w [N, K]^T, fp32 accumulation"""
+    _need(x, torch.bfloat16, "x", 2)
+    _need(w, torch.bfloat16, "w", 2)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise SpinfError("bf16_gemm: inner dimensions differ")
+    y = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    check(_lib.lib().spinf_bf16_gemm(ptr(x), ptr(w), ptr(y), M, N, K, stream_ptr()), "spinf_bf16_gemm")
+    return y
+
+
+def option_logprobs(h, W, cols, softcap=None, workspace=None):
+    """log-probs of the option tokens `cols` (sorted distinct int32 ids, on the device) at read rows h [R, hidden] bf16 under the
+    lm head W [vocab, hidden] bf16 -> [R, len(cols)] fp32 (Scorer._logprobs + the column gather, spinf_serve/scorer.py:340-355,254)"""
+    _need(h, torch.bfloat16, "h", 2)
+    _need(W, torch.bfloat16, "W", 2)
+    _need(cols, torch.int32, "cols", 1)
+    R, hidden = h.shape
+    vocab = W.shape[0]
+    if W.shape[1] != hidden:
+        raise SpinfError("option_logprobs: hidden sizes differ")
+    n_cols = cols.numel()
+    out = torch.empty((R, n_cols), dtype=torch.float32, device=h.device)
+    need = _lib.lib().spinf_option_logprobs_workspace_bytes(R, vocab, n_cols)
+    if workspace is None or workspace.numel() < need:
+        workspace = torch.empty(need, dtype=torch.uint8, device=h.device)
+    check(
+        _lib.lib().spinf_option_logprobs(
+            ptr(h), ptr(W), R, hidden, vocab, ptr(cols), n_cols, ctypes.c_float(softcap or 0.0), ptr(out), ptr(workspace),
+            workspace.numel(), stream_ptr(),
+        ),
+        "spinf_option_logprobs",
+    )
+    return out

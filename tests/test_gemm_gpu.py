@@ -1,0 +1,83 @@
+"""GPU parity of the tcgen05 GEMMs (through the C ABI) against the CPU oracle: row-wise fp8 quantiser + GEMM
+(spinf_serve/quant/linears.py:29-33,84-96), plain bf16 GEMM, and batch invariance of rows across M."""
+
+import pytest
+import torch
+
+from oracle import linears as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _rand(shape, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("M,K", [(1, 64), (7, 3840), (128, 4096), (300, 15360), (1000, 5376)])
+def test_rowwise_quant_bit_exact(dev, M, K):
+    """x8 and xs equal the oracle's bit for bit (true division, clamp, round-to-nearest-even)"""
+    from spinf_serve_b200 import ops
+
+    x = _rand((M, K), 1, 3.0)
+    x[0, : min(K, 16)] = 0  # a run of zeros
+    if M > 2:
+        x[2] = 0  # an all-zero row: the scale clamps at 1e-12 / 448
+    x8, xs = ops.fp8_rowwise_quant(x.to(dev))
+    r8, rs = O.quant_act_row(x)
+    assert torch.equal(xs.cpu(), rs)
+    assert torch.equal(x8.cpu().view(torch.uint8), r8.view(torch.uint8))
+
+
+# (M, N, K): ragged M, one tile, the cfg-2 projection shapes at reduced M, K with a tail block
+SHAPES = [(128, 256, 128), (1, 256, 256), (130, 512, 384), (257, 2048, 3840), (640, 3840, 4096), (384, 15360, 3840), (200, 3840, 15360), (100, 304, 208)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_fp8_rowwise_gemm_vs_oracle(dev, M, N, K):
+    from spinf_serve_b200 import ops
+
+    x = _rand((M, K), 2)
+    w = _rand((N, K), 3, 0.02)
+    w8, ws = O.quantize_weight_rowwise(w)
+    x8, xs = O.quant_act_row(x)
+    y = ops.fp8_rowwise_gemm(x8.to(dev), xs.to(dev), w8.to(dev), ws.to(dev)).cpu()
+    exact = O.scaled_mm_rowwise(x8, xs, w8, ws, exact=True)
+    # the exact product rounded to bf16 is at most half an ulp away; the fp32 tensor-core accumulation adds a little
+    err = (y.double() - exact).abs()
+    tol = exact.abs() * 2.0**-7 + exact.abs().max() * 2.0**-14
+    assert bool((err <= tol).all()), f"max err {err.max():.3e} at |ref| {exact.abs().max():.3e}"
+    ref = O.scaled_mm_rowwise(x8, xs, w8, ws)
+    mism = (y != ref).float().mean().item()
+    print(f"fp8 gemm {M}x{N}x{K}: max abs err vs exact {err.max():.3e}, rows differing from fp32-oracle bf16: {mism:.4%}")
+    assert mism < 0.05  # same value up to the last bf16 bit on almost every element
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (3, 512, 128), (300, 3840, 4096), (1000, 1024, 5120)])
+def test_bf16_gemm_vs_oracle(dev, M, N, K):
+    from spinf_serve_b200 import ops
+
+    x = _rand((M, K), 4)
+    w = _rand((N, K), 5, 0.05)
+    y = ops.bf16_gemm(x.to(dev), w.to(dev)).cpu()
+    exact = x.double() @ w.double().t()
+    err = (y.double() - exact).abs()
+    tol = exact.abs() * 2.0**-7 + exact.abs().max() * 2.0**-13
+    assert bool((err <= tol).all()), f"max err {err.max():.3e}"
+
+
+def test_fp8_gemm_rows_do_not_depend_on_M(dev):
+    """batch invariance: the first rows of the product are bit-identical for M = 1, 100, 128, 1000, 4096"""
+    from spinf_serve_b200 import ops
+
+    K, N = 3840, 2048
+    x = _rand((4096, K), 6)
+    w8, ws = O.quantize_weight_rowwise(_rand((N, K), 7, 0.02))
+    x8, xs = O.quant_act_row(x)
+    x8, xs, w8, ws = x8.to(dev), xs.to(dev), w8.to(dev), ws.to(dev)
+    full = ops.fp8_rowwise_gemm(x8, xs, w8, ws)
+    for M in (1, 100, 128, 1000):
+        part = ops.fp8_rowwise_gemm(x8[:M].contiguous(), xs[:M].contiguous(), w8, ws)
+        assert torch.equal(part, full[:M])
+    again = ops.fp8_rowwise_gemm(x8, xs, w8, ws)
+    assert torch.equal(again, full)  # run-to-run determinism
