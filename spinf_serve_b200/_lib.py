@@ -27,7 +27,7 @@ SIGNATURES = {
     "spinf_option_logprobs_workspace_bytes": (_i64, [_i64, _i64, _i64]),
     "spinf_option_logprobs": (ctypes.c_int, [_p, _p, _i64, _i64, _i64, _p, _i64, _f32, _p, _p, _i64, _p]),
     "spinf_tile_desc_build_host": (_i64, [_p, _p, _p, _i64, _i32, _p, _p, _p]),
-    "spinf_tree_attn_fwd_PENDING": (
+    "spinf_tree_attn_fwd": (
         ctypes.c_int,
         [_p, _p, _p, _p, _i64, _i32, _i32, _i32, _i64, _i64, _i64, _p, _p, _p, _i32, _f32, _p, _p, _p, _p],
     ),

@@ -1,0 +1,363 @@
+// Tree-mask attention over one packed stream (prefill), tcgen05 + TMEM + TMA, for sm_100a.
+//
+// One CTA = one 128-row query block of one query head. It walks the block's tile list (built on the host from the packing
+// metadata) in ascending key order, 64 keys at a time:
+//   warp 0    one lane: TMA loads of Q (once) and of the K / V sub-tiles into a 2-deep ring
+//   warp 1    allocates tensor memory; one lane issues  S = Q K^T  (M=128, N=64, K=D)  into one of two S buffers and
+//             O += P V  (M=128, N=D, K=64)  into the O accumulator; S of sub-tile t+1 is issued before P V of sub-tile t, so the
+//             tensor core works on the next scores while the softmax warps work on the current ones
+//   warps 2-5 thread = query row: reads S from TMEM, applies scale and the tree mask, keeps the running maximum and sum in
+//             fp32, writes P (bf16) into a swizzled shared tile, rescales O in TMEM by exp2(m_old - m_new), and at the end
+//             divides by the sum and stores bf16
+// Numerics follow the reference's attention (bf16 Q/K/V, fp32 scores and softmax state, P rounded to bf16 before P V, fp32
+// accumulation). Reduction order per row = ascending 64-key sub-tiles of the row's own job, independent of what else is packed
+// in the stream; "full" tiles only skip the mask evaluation, never change the arithmetic.
+#include "common.cuh"
+#include "host_util.h"
+
+namespace spinf {
+
+static constexpr int KT = 64;  // keys per sub-tile
+
+template <int D>
+struct AttnSmem {
+  static constexpr int SLABS = D / 64;              // 64-element (128-byte) slabs along the head dimension
+  static constexpr int Q_BYTES = SLABS * 128 * 128;
+  static constexpr int KV_TILE = SLABS * KT * 128;  // one K (or V) sub-tile
+  static constexpr int P_BYTES = 128 * 128;
+  static constexpr int K_OFF = Q_BYTES;             // 2 stages of K then 2 stages of V
+  static constexpr int V_OFF = K_OFF + 2 * KV_TILE;
+  static constexpr int P_OFF = V_OFF + 2 * KV_TILE;
+  static constexpr int BAR_OFF = P_OFF + P_BYTES;
+  static constexpr int META_OFF = BAR_OFF + 128;    // key metadata: 2 buffers x 3 arrays x 64 ints
+  static constexpr int TOTAL = META_OFF + 2 * 3 * KT * 4 + 1024;
+  static constexpr int TMEM_COLS = D == 256 ? 512 : 256;  // 2 x 64 (S) + D (O), rounded up to a power of two
+  static constexpr int O_COL = 128;
+};
+
+struct AttnArgs {
+  __nv_bfloat16* out;
+  int64_t out_pitch;
+  const int32_t* art;
+  const int32_t* end;
+  const int32_t* pos;
+  const int32_t* tile_offsets;
+  const int32_t* tile_blocks;
+  const uint8_t* tile_flags;
+  int nb, H, group;  // group = H / Hkv
+  int window;
+  float scale_log2;
+};
+
+template <int D>
+__global__ void __launch_bounds__(192, 1)
+tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const AttnArgs a, int* __restrict__ status) {
+  using L = AttnSmem<D>;
+  constexpr int SLABS = L::SLABS;
+  constexpr uint32_t IDESC_S = make_idesc(FMT_BF16, FMT_BF16, 128, KT, 0, 0);
+  constexpr uint32_t IDESC_O = make_idesc(FMT_BF16, FMT_BF16, 128, D, 0, 1);  // B = V, MN-major (head dim contiguous)
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint64_t* q_full = bars;        // 1
+  uint64_t* k_full = bars + 1;    // 2
+  uint64_t* v_full = bars + 3;    // 2
+  uint64_t* kv_empty = bars + 5;  // 2
+  uint64_t* s_full = bars + 7;    // 2
+  uint64_t* p_ready = bars + 9;   // 1 (128 arrivals)
+  uint64_t* o_done = bars + 10;   // 1
+  uint32_t* tmem_base_p = reinterpret_cast<uint32_t*>(bars + 11);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_p + 1);
+  int* meta = reinterpret_cast<int*>(smem + L::META_OFF);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qb = blockIdx.x, h = blockIdx.y;
+  const int g = h / a.group;
+  const WaitCtx wc{abort_flag, status};
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+    }
+    mbar_init(p_ready, 128);
+    mbar_init(o_done, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_p, L::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_p;
+
+  const int e0 = a.tile_offsets[qb];
+  const int n_sub = 2 * (a.tile_offsets[qb + 1] - e0);
+
+  if (warp == 0) {
+    if (lane == 0 && n_sub > 0) {
+      mbar_expect_tx(q_full, L::Q_BYTES);
+      for (int s = 0; s < SLABS; ++s) tma_load_2d(smem + s * 128 * 128, &tmQ, h * D + s * 64, qb * 128, q_full);
+      int issued = 0;
+      for (int t = 0; t < n_sub; ++t, ++issued) {
+        const int st = t & 1;
+        const uint32_t ph = (t >> 1) & 1u;
+        const int j = a.tile_blocks[e0 + (t >> 1)];
+        if (j < 0 || j >= a.nb) {
+          *abort_flag = 1;
+          atomicCAS(status, 0, ST_BAD_INDEX);
+          break;
+        }
+        if (!mbar_wait(wc, &kv_empty[st], ph ^ 1u, ST_TIMEOUT_EMPTY)) break;
+        const int kv0 = j * 128 + (t & 1) * KT;
+        mbar_expect_tx(&k_full[st], L::KV_TILE);
+        for (int s = 0; s < SLABS; ++s) tma_load_2d(smem + L::K_OFF + st * L::KV_TILE + s * KT * 128, &tmK, g * D + s * 64, kv0, &k_full[st]);
+        mbar_expect_tx(&v_full[st], L::KV_TILE);
+        for (int s = 0; s < SLABS; ++s) tma_load_2d(smem + L::V_OFF + st * L::KV_TILE + s * KT * 128, &tmV, g * D + s * 64, kv0, &v_full[st]);
+      }
+      if (*abort_flag) {
+        // bounded wait for copies of this CTA that may still be in flight
+        for (int spin = 0; spin < 4096 && !mbar_try_wait(q_full, 0); ++spin) {}
+        for (int t = issued > 2 ? issued - 2 : 0; t < issued; ++t) {
+          for (int spin = 0; spin < 4096 && !mbar_try_wait(&k_full[t & 1], (t >> 1) & 1u); ++spin) {}
+          for (int spin = 0; spin < 4096 && !mbar_try_wait(&v_full[t & 1], (t >> 1) & 1u); ++spin) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_sub > 0) {
+      const uint32_t q_addr = smem_u32(smem);
+      const uint32_t p_addr = smem_u32(smem + L::P_OFF);
+      auto issue_s = [&](int t) {
+        const int st = t & 1;
+        const uint32_t k_addr = smem_u32(smem + L::K_OFF + st * L::KV_TILE);
+        const uint32_t d_tmem = tmem_base + (t & 1) * KT;
+#pragma unroll
+        for (int s = 0; s < SLABS; ++s) {
+          const uint64_t ad = make_smem_desc_sw128(q_addr + s * 128 * 128, 16, 1024);
+          const uint64_t bd = make_smem_desc_sw128(k_addr + s * KT * 128, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) umma_f16_ss(d_tmem, ad + 2 * k, bd + 2 * k, IDESC_S, (s | k) != 0);
+        }
+        umma_commit(&s_full[t & 1]);
+      };
+      bool ok = mbar_wait(wc, q_full, 0, ST_TIMEOUT_FULL);
+      if (ok) ok = mbar_wait(wc, &k_full[0], 0, ST_TIMEOUT_FULL);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+      }
+      for (int t = 0; t < n_sub && ok; ++t) {
+        const int st = t & 1;
+        const uint32_t ph = (t >> 1) & 1u;
+        if (t + 1 < n_sub) {
+          if (!mbar_wait(wc, &k_full[(t + 1) & 1], ((t + 1) >> 1) & 1u, ST_TIMEOUT_FULL)) break;
+          tc_fence_after();
+          issue_s(t + 1);
+        }
+        if (!mbar_wait(wc, p_ready, t & 1u, ST_TIMEOUT_OTHER)) break;
+        if (!mbar_wait(wc, &v_full[st], ph, ST_TIMEOUT_FULL)) break;
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(smem + L::V_OFF + st * L::KV_TILE);
+        const uint64_t pd = make_smem_desc_sw128(p_addr, 16, 1024);
+        // V sub-tile: slab s holds head-dim columns [64 s, 64 s + 64) of 64 keys, one key per 128-byte row:
+        // MN-major B operand, 64-column groups KT*128 bytes apart (LBO), 8-key groups 1024 bytes apart (SBO)
+        const uint64_t vd = make_smem_desc_sw128(v_addr, KT * 128, 1024);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)  // 16 keys per step: 32 bytes along P's rows, 16 rows (2048 bytes) down V
+          umma_f16_ss(tmem_base + L::O_COL, pd + 2 * k, vd + 128 * k, IDESC_O, (t | k) != 0);
+        umma_commit(&kv_empty[st]);
+        umma_commit(o_done);
+      }
+    }
+  } else if (n_sub > 0) {
+    const int et = threadIdx.x - 64;
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    const int tq = qb * 128 + row;  // stream position of this thread's query row
+    const int art_q = a.art[tq], pos_q = a.pos[tq];
+    const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
+    uint8_t* p_smem = smem + L::P_OFF;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool alive = true;
+
+    for (int t = 0; t < n_sub; ++t) {
+      const int e = e0 + (t >> 1);
+      const int j = a.tile_blocks[e];
+      const bool full_tile = a.tile_flags[e] != 0;
+      const int kv0 = j * 128 + (t & 1) * KT;
+      int* kart = meta + (t & 1) * 3 * KT;
+      int* kend = kart + KT;
+      int* kpos = kend + KT;
+      const bool j_ok = j >= 0 && j < a.nb;
+      if (!full_tile && j_ok && et < KT) {
+        kart[et] = a.art[kv0 + et];
+        kend[et] = a.end[kv0 + et];
+        kpos[et] = a.pos[kv0 + et];
+      }
+      bool got = j_ok && mbar_wait(wc, &s_full[t & 1], (t >> 1) & 1u, ST_TIMEOUT_TMEM);
+      if (!bar_red_and(1, 128, got)) { alive = false; break; }  // also publishes the key metadata to all 128 threads
+      tc_fence_after();
+      uint32_t v0[32], v1[32];
+      __syncwarp();
+      tmem_ld_x32(tmem_base + lane_off + (t & 1) * KT, v0);
+      tmem_ld_x32(tmem_base + lane_off + (t & 1) * KT + 32, v1);
+      tmem_wait_ld();
+      float s[KT];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        s[i] = __uint_as_float(v0[i]) * a.scale_log2;
+        s[32 + i] = __uint_as_float(v1[i]) * a.scale_log2;
+      }
+      if (!full_tile) {
+#pragma unroll
+        for (int i = 0; i < KT; ++i) {
+          const int tk = kv0 + i;
+          bool vis = tk <= tq && art_q >= 0 && kart[i] == art_q && tq < kend[i];
+          if (a.window > 0) vis = vis && (pos_q - kpos[i] < a.window);
+          vis = vis || tk == tq;
+          if (!vis) s[i] = -INFINITY;
+        }
+      }
+      float mx = s[0];
+#pragma unroll
+      for (int i = 1; i < KT; ++i) mx = fmaxf(mx, s[i]);
+      const float m_new = fmaxf(m_run, mx);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      const float alpha = exp2f(m_run - m_use);
+      float sum = 0.f;
+      uint32_t pk[KT / 2];
+#pragma unroll
+      for (int i = 0; i < KT / 2; ++i) {
+        const float p0 = exp2f(s[2 * i] - m_use), p1 = exp2f(s[2 * i + 1] - m_use);
+        sum += p0 + p1;
+        pk[i] = pack_bf16x2(p0, p1);
+      }
+      l_run = l_run * alpha + sum;
+      m_run = m_new;
+      if (t > 0) {
+        // P V of the previous sub-tile has completed: the P tile may be overwritten and O is stable
+        got = mbar_wait(wc, o_done, (t - 1) & 1u, ST_TIMEOUT_TMEM);
+        if (!bar_red_and(1, 128, got)) { alive = false; break; }
+        tc_fence_after();
+      }
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        *reinterpret_cast<uint4*>(p_smem + sw128_offset(row, c)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+      if (t > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld_x32(tmem_base + lane_off + L::O_COL + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_x32(tmem_base + lane_off + L::O_COL + c * 32, o);
+        }
+        tmem_wait_st();
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(p_ready);
+    }
+
+    if (alive) {
+      const bool got = mbar_wait(wc, o_done, (n_sub - 1) & 1u, ST_TIMEOUT_TMEM);
+      if (bar_red_and(1, 128, got)) {
+        tc_fence_after();
+        const float inv = 1.f / l_run;  // every row sees at least itself, so l_run > 0
+        __nv_bfloat16* dst = a.out + static_cast<int64_t>(tq) * a.out_pitch + h * D;
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          __syncwarp();
+          tmem_ld_x32(tmem_base + lane_off + L::O_COL + c * 32, o);
+          tmem_wait_ld();
+          uint32_t w[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) w[i] = pack_bf16x2(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv);
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            *reinterpret_cast<uint4*>(dst + c * 32 + i * 8) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, L::TMEM_COLS);
+  }
+}
+
+template <int D>
+static int launch_attn(const void* q, const void* k, const void* v, int64_t n, int H, int Hkv, int64_t q_pitch, int64_t kv_pitch,
+                       const AttnArgs& args, cudaStream_t stream) {
+  using L = AttnSmem<D>;
+  int dev = 0;
+  SPINF_CUDA_OK(cudaGetDevice(&dev));
+  int* status = status_word(dev);
+  if (!status) return SPINF_ERR_CUDA;
+  CUtensorMap tmQ, tmK, tmV;
+  int r;
+  if ((r = make_tmap_2d(&tmQ, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, q, n, static_cast<uint64_t>(H) * D, q_pitch * 2, 64, 128))) return r;
+  if ((r = make_tmap_2d(&tmK, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k, n, static_cast<uint64_t>(Hkv) * D, kv_pitch * 2, 64, KT))) return r;
+  if ((r = make_tmap_2d(&tmV, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, v, n, static_cast<uint64_t>(Hkv) * D, kv_pitch * 2, 64, KT))) return r;
+  auto kern = tree_attn_kernel<D>;
+  static bool attr_set[64] = {false};
+  if (!attr_set[dev]) {
+    SPINF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+    attr_set[dev] = true;
+  }
+  dim3 grid(static_cast<unsigned>(n / 128), static_cast<unsigned>(H));
+  kern<<<grid, 192, L::TOTAL, stream>>>(tmQ, tmK, tmV, args, status);
+  SPINF_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace spinf
+
+using namespace spinf;
+
+extern "C" int spinf_tree_attn_fwd(const void* q, const void* k, const void* v, void* out, int64_t n, int32_t H, int32_t Hkv,
+                                   int32_t D, int64_t q_pitch, int64_t kv_pitch, int64_t out_pitch, const int32_t* art,
+                                   const int32_t* end, const int32_t* pos, int32_t window, float scale, const int32_t* tile_offsets,
+                                   const int32_t* tile_blocks, const uint8_t* tile_flags, void* stream) {
+  SPINF_CHECK_ARG(q && k && v && out && art && end && pos && tile_offsets && tile_blocks && tile_flags);
+  SPINF_CHECK_ARG(n >= 0 && n % SPINF_BLOCK == 0 && n < (1ll << 30) && H > 0 && Hkv > 0 && H % Hkv == 0 && H <= 65535);
+  SPINF_CHECK_ARG(D == 128 || D == 256);
+  SPINF_CHECK_ARG(q_pitch >= static_cast<int64_t>(H) * D && kv_pitch >= static_cast<int64_t>(Hkv) * D && out_pitch >= static_cast<int64_t>(H) * D);
+  SPINF_CHECK_ARG(q_pitch % 8 == 0 && kv_pitch % 8 == 0 && out_pitch % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0);
+  if (n == 0) return 0;
+  AttnArgs a;
+  a.out = static_cast<__nv_bfloat16*>(out);
+  a.out_pitch = out_pitch;
+  a.art = art;
+  a.end = end;
+  a.pos = pos;
+  a.tile_offsets = tile_offsets;
+  a.tile_blocks = tile_blocks;
+  a.tile_flags = tile_flags;
+  a.nb = static_cast<int>(n / SPINF_BLOCK);
+  a.H = H;
+  a.group = H / Hkv;
+  a.window = window;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (D == 256) return launch_attn<256>(q, k, v, n, H, Hkv, q_pitch, kv_pitch, a, st);
+  return launch_attn<128>(q, k, v, n, H, Hkv, q_pitch, kv_pitch, a, st);
+}

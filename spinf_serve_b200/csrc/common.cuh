@@ -1,7 +1,7 @@
 // Device-side building blocks shared by the sm_100a kernels of this library: mbarrier, TMA (cp.async.bulk.tensor),
 // tcgen05 (TMEM allocation, MMA issue, commit, TMEM loads/stores) and the shared-memory / instruction descriptors.
 //
-// Every wait in here is BOUNDED: a wait that does not complete within WAIT_LIMIT polls records an error code in the
+// Every wait in here is BOUNDED: a wait that does not complete within WAIT_LIMIT_NS records an error code in the
 // kernel's status word, raises the CTA-wide abort flag and returns false; every later wait in the CTA then returns at once,
 // so a mis-programmed pipeline ends with a status the host can read instead of a hung GPU.
 #pragma once
@@ -24,7 +24,13 @@ enum : int {
   ST_BAD_INDEX = 5,       // an index read from a descriptor was out of range (access skipped)
 };
 
-static constexpr uint32_t WAIT_LIMIT = 1u << 24;  // polls; each poll may suspend for a hardware-defined slice
+static constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // a wait gives up after 2 s of wall time (read from %globaltimer)
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -65,9 +71,13 @@ struct WaitCtx {
 
 __device__ __forceinline__ bool mbar_wait(const WaitCtx& w, uint64_t* bar, uint32_t parity, int code) {
   if (mbar_try_wait(bar, parity)) return true;
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+  const uint64_t t0 = global_timer_ns();
+  for (uint32_t i = 0;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 255u) == 255u && *w.abort_flag) return false;
+    if ((i & 63u) == 63u) {
+      if (*w.abort_flag) return false;
+      if (global_timer_ns() - t0 > WAIT_LIMIT_NS) break;
+    }
   }
   *w.abort_flag = 1;
   atomicCAS(w.status, 0, code);
@@ -80,6 +90,17 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// barrier + AND-reduction of a predicate over `nthreads` threads: every participant learns whether all of them succeeded
+__device__ __forceinline__ uint32_t bar_red_and(uint32_t id, uint32_t nthreads, bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %3, 0;\n\tbarrier.cta.red.and.pred q, %1, %2, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(out)
+      : "r"(id), "r"(nthreads), "r"(static_cast<uint32_t>(pred))
+      : "memory");
+  return out;
 }
 
 // ---------------------------------------------------------------- TMA

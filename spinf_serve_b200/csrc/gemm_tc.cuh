@@ -48,16 +48,6 @@ __device__ __forceinline__ void tile_coords(const GemmShape& s, int tile, int& t
   tn = t / rows;
 }
 
-__device__ __forceinline__ uint32_t bar_red_and(uint32_t id, uint32_t nthreads, bool pred) {
-  uint32_t out;
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %3, 0;\n\tbarrier.cta.red.and.pred q, %1, %2, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
-      : "=r"(out)
-      : "r"(id), "r"(nthreads), "r"(static_cast<uint32_t>(pred))
-      : "memory");
-  return out;
-}
-
 // Epilogue functor contract (all calls are made by the 128 epilogue threads, thread = row `row` of the tile; the functor is a
 // __grid_constant__ kernel parameter, so it may hold a TMA descriptor; its mutable per-thread state lives in Epi::State):
 //   begin_tile(st, shape, tm, tn, et, ...)       once per tile before the accumulator is ready (et = 0..127)
