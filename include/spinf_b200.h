@@ -100,6 +100,39 @@ int spinf_tree_attn_fwd(const void* q, const void* k, const void* v, void* out, 
                         const int32_t* pos, int32_t window, float scale, const int32_t* tile_offsets, const int32_t* tile_blocks,
                         const uint8_t* tile_flags, void* stream);
 
+/* ------------------------------------------------------------------------------------------------------------ layer glue
+ * The reference runs these steps as inductor-fused pieces of the decoder layer (the layer code itself is the transformers
+ * Gemma 4 text model the reference instantiates at spinf_serve/models/gemma4.py:134-143 and calls at :407-415; Qwen's own layer
+ * at spinf_serve/models/qwen35/qwen.py:502-510,699-734). Each entry point fuses a chain of them so an activation row crosses HBM
+ * once; rounding points are the modules' (every module output bf16, norms in fp32).
+ *
+ * spinf_fused_norm: per output row r (input row rows[r] when `rows` is given, else r) of y [*, hidden] bf16:
+ *   a = y;  if w1: a = bf16(a * (mean(a^2) + eps)^-1/2 * w1);  if residual: a = bf16(a + residual[r]);  out_h[r] = a (optional);
+ *   if w2: b = bf16(rmsnorm(a) * w2) -> out_norm[r] (optional) and/or its per-row fp8 quantisation out_x8[r], out_xs[r]
+ *   (the arithmetic of spinf_fp8_rowwise_quant). plus1: weights enter as (1 + w). hidden a multiple of 8, at most 8192. */
+int spinf_fused_norm(const void* y, const int64_t* rows, const void* w1, const void* residual, const void* w2, int64_t n_out,
+                     int64_t hidden, float eps, int32_t plus1, void* out_h, void* out_norm, void* out_x8, float* out_xs,
+                     void* stream);
+
+/* In place on the fused q|k|v projection output qkv [n, pitch] bf16 (H query heads, then Hkv key heads, then Hkv value heads, D
+ * each): per head RMSNorm (q with wq [D], k with wk [D], v without weight when norm_v) rounded to bf16, then the rotary embedding
+ * of q and k over the first rot_dim dimensions, bf16(bf16(x cos) + bf16(rotate_half(x) sin)), with cos_t / sin_t [n, rot_dim/2]
+ * bf16 from spinf_rope_table. D in {128, 256}; rot_dim a multiple of D/16. */
+int spinf_qkv_norm_rope(void* qkv, int64_t pitch, int64_t n, int32_t H, int32_t Hkv, int32_t D, const void* wq, const void* wk,
+                        const void* cos_t, const void* sin_t, int32_t rot_dim, float eps, int32_t plus1, int32_t norm_v,
+                        void* stream);
+
+/* cos_t / sin_t [n, rot_dim/2] bf16 = bf16(cos / sin (float(pos[t]) * inv_freq[f])), inv_freq [rot_dim/2] fp32 on the device. */
+int spinf_rope_table(const int32_t* pos, int64_t n, int32_t rot_dim, const float* inv_freq, void* cos_t, void* sin_t, void* stream);
+
+/* gu [n, 2F] bf16 = gate | up (one fused projection): y = bf16(bf16(act(gate)) * up), act 0 = gelu (tanh form), 1 = silu; then
+ * its per-row fp8 quantisation (out_x8 [n,F], out_xs [n]) and/or y itself in bf16 (out_y [n,F]). F a multiple of 8. */
+int spinf_glu_quant(const void* gu, int64_t n, int64_t F, int32_t act, void* out_x8, float* out_xs, void* out_y, void* stream);
+
+/* out[t,:] = bf16(emb[ids[t],:] * scale): the scaled word embedding (ids int64; an id outside [0, vocab) reads row 0). */
+int spinf_embed_scale(const int64_t* ids, const void* emb, int64_t n, int64_t hidden, int64_t vocab, float scale, void* out,
+                      void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -27,6 +27,11 @@ SIGNATURES = {
     "spinf_option_logprobs_workspace_bytes": (_i64, [_i64, _i64, _i64]),
     "spinf_option_logprobs": (ctypes.c_int, [_p, _p, _i64, _i64, _i64, _p, _i64, _f32, _p, _p, _i64, _p]),
     "spinf_tile_desc_build_host": (_i64, [_p, _p, _p, _i64, _i32, _p, _p, _p]),
+    "spinf_fused_norm": (ctypes.c_int, [_p, _p, _p, _p, _p, _i64, _i64, _f32, _i32, _p, _p, _p, _p, _p]),
+    "spinf_qkv_norm_rope": (ctypes.c_int, [_p, _i64, _i64, _i32, _i32, _i32, _p, _p, _p, _p, _i32, _f32, _i32, _i32, _p]),
+    "spinf_rope_table": (ctypes.c_int, [_p, _i64, _i32, _p, _p, _p, _p]),
+    "spinf_glu_quant": (ctypes.c_int, [_p, _i64, _i64, _i32, _p, _p, _p, _p]),
+    "spinf_embed_scale": (ctypes.c_int, [_p, _p, _i64, _i64, _i64, _f32, _p, _p]),
     "spinf_tree_attn_fwd": (
         ctypes.c_int,
         [_p, _p, _p, _p, _i64, _i32, _i32, _i32, _i64, _i64, _i64, _p, _p, _p, _i32, _f32, _p, _p, _p, _p],
@@ -66,8 +71,6 @@ def lib():
                     raise SpinfError(f"{LIB_PATH} is missing: build it with `python -m spinf_serve_b200.csrc.build`; there is no fallback")
                 handle = ctypes.CDLL(LIB_PATH)
                 for name, (res, args) in SIGNATURES.items():
-                    if name.endswith("_PENDING"):
-                        continue
                     fn = getattr(handle, name)  # AttributeError if the header and the library disagree
                     fn.restype = res
                     fn.argtypes = args

@@ -1,0 +1,396 @@
+// Bandwidth-bound layer glue of the packed forward, fused so each activation row crosses HBM once per step:
+//   fused_norm      [RMSNorm] -> [+ residual] -> [RMSNorm] -> bf16 and/or per-row fp8 quantisation (feeds the next fp8 GEMM)
+//   qkv_norm_rope   per-head RMSNorm of q / k (with weight) and v (without), rotary embedding of q / k, in place
+//   glu_quant       act(gate) * up -> per-row fp8 quantisation (GeGLU for the Gemma stack, SwiGLU for the Qwen stack)
+//   embed_scale     embedding gather times the (bf16) embedding scale
+//   rope_table      cos / sin of pos * inv_freq, rounded to bf16 as the model code does before applying them
+// Rounding points follow the module code the reference runs (transformers' Gemma 4 text model, called from
+// spinf_serve/models/gemma4.py:134-143,407-415): every module output is bf16, norms compute in fp32 and round once, the rotary
+// product is three bf16 roundings (x*cos, rot(x)*sin, their sum), residual adds are bf16 + bf16 -> bf16.
+#include "common.cuh"
+#include "host_util.h"
+
+namespace spinf {
+
+static constexpr int NORM_THREADS = 256;
+static constexpr int NORM_MAX_VEC = 4;  // row cache: up to 256 * 4 * 8 = 8192 elements
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[w] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int i = 0; i < nw; ++i) t += red[i];
+  return t;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  const int w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[w] = v;
+  __syncthreads();
+  float t = red[0];
+  for (int i = 1; i < nw; ++i) t = fmaxf(t, red[i]);
+  return t;
+}
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 t = __bfloat1622float2(h[j]);
+    f[2 * j] = t.x;
+    f[2 * j + 1] = t.y;
+  }
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
+  uint4 u;
+  u.x = pack_bf16x2(f[0], f[1]);
+  u.y = pack_bf16x2(f[2], f[3]);
+  u.z = pack_bf16x2(f[4], f[5]);
+  u.w = pack_bf16x2(f[6], f[7]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+__device__ __forceinline__ uint2 quant8(const float (&f)[8], float s) {
+  uint32_t o[2];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const float q0 = fminf(fmaxf(__fdiv_rn(f[4 * j], s), -448.f), 448.f), q1 = fminf(fmaxf(__fdiv_rn(f[4 * j + 1], s), -448.f), 448.f);
+    const float q2 = fminf(fmaxf(__fdiv_rn(f[4 * j + 2], s), -448.f), 448.f), q3 = fminf(fmaxf(__fdiv_rn(f[4 * j + 3], s), -448.f), 448.f);
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(q0, q1), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(q2, q3), __NV_SATFINITE, __NV_E4M3);
+    o[j] = lo | (hi << 16);
+  }
+  return make_uint2(o[0], o[1]);
+}
+
+// RMSNorm as the model computes it: x * pow(mean(x^2) + eps, -0.5), times the weight, all in fp32, rounded once to bf16.
+// plus1: the weight enters as (1 + w) (Qwen's RMSNorm, spinf_serve/models/qwen35/qwen.py:502-510).
+struct FusedNormArgs {
+  const __nv_bfloat16* y;         // [*, hidden] input rows
+  const int64_t* rows;            // optional: output row r reads input row rows[r]
+  const __nv_bfloat16* w1;        // optional first norm weight
+  const __nv_bfloat16* residual;  // optional [n_out, hidden], added after the first norm
+  const __nv_bfloat16* w2;        // optional second norm weight
+  __nv_bfloat16* out_h;           // optional: the value after the residual add (the new residual stream)
+  __nv_bfloat16* out_norm;        // optional: the second norm's output in bf16
+  uint8_t* out_x8;                // optional: its per-row fp8 quantisation
+  float* out_xs;
+  int hidden;
+  float eps;
+  int plus1;
+};
+
+__global__ void __launch_bounds__(NORM_THREADS) fused_norm_kernel(const FusedNormArgs a) {
+  __shared__ float red[NORM_THREADS / 32];
+  const int64_t r = blockIdx.x;
+  const int64_t rin = a.rows ? a.rows[r] : r;
+  const int nvec = a.hidden / 8;
+  float x[NORM_MAX_VEC][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NORM_MAX_VEC; ++i) {
+    const int v = threadIdx.x + i * NORM_THREADS;
+    if (v < nvec) {
+      load8(a.y + rin * a.hidden + v * 8, x[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += x[i][j] * x[i][j];
+    }
+  }
+  if (a.w1) {
+    const float inv = powf(block_sum(ss, red) / a.hidden + a.eps, -0.5f);
+#pragma unroll
+    for (int i = 0; i < NORM_MAX_VEC; ++i) {
+      const int v = threadIdx.x + i * NORM_THREADS;
+      if (v < nvec) {
+        float w[8];
+        load8(a.w1 + v * 8, w);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[i][j] = round_bf16(x[i][j] * inv * (a.plus1 ? 1.f + w[j] : w[j]));
+      }
+    }
+  }
+  if (a.residual) {
+#pragma unroll
+    for (int i = 0; i < NORM_MAX_VEC; ++i) {
+      const int v = threadIdx.x + i * NORM_THREADS;
+      if (v < nvec) {
+        float res[8];
+        load8(a.residual + r * a.hidden + v * 8, res);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[i][j] = round_bf16(x[i][j] + res[j]);
+      }
+    }
+  }
+  if (a.out_h) {
+#pragma unroll
+    for (int i = 0; i < NORM_MAX_VEC; ++i) {
+      const int v = threadIdx.x + i * NORM_THREADS;
+      if (v < nvec) store8(a.out_h + r * a.hidden + v * 8, x[i]);
+    }
+  }
+  if (!a.w2) return;
+  ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NORM_MAX_VEC; ++i) {
+    const int v = threadIdx.x + i * NORM_THREADS;
+    if (v < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += x[i][j] * x[i][j];
+    }
+  }
+  const float inv2 = powf(block_sum(ss, red) / a.hidden + a.eps, -0.5f);
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < NORM_MAX_VEC; ++i) {
+    const int v = threadIdx.x + i * NORM_THREADS;
+    if (v < nvec) {
+      float w[8];
+      load8(a.w2 + v * 8, w);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        x[i][j] = round_bf16(x[i][j] * inv2 * (a.plus1 ? 1.f + w[j] : w[j]));
+        amax = fmaxf(amax, fabsf(x[i][j]));
+      }
+      if (a.out_norm) store8(a.out_norm + r * a.hidden + v * 8, x[i]);
+    }
+  }
+  if (!a.out_x8) return;
+  const float s = __fdiv_rn(fmaxf(block_max(amax, red), 1e-12f), 448.f);
+  if (threadIdx.x == 0) a.out_xs[r] = s;
+#pragma unroll
+  for (int i = 0; i < NORM_MAX_VEC; ++i) {
+    const int v = threadIdx.x + i * NORM_THREADS;
+    if (v < nvec) *reinterpret_cast<uint2*>(a.out_x8 + r * a.hidden + v * 8) = quant8(x[i], s);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ q/k/v head norms + rotary
+// One warp per (token, head) of the fused projection output [n, (H + 2 Hkv) * D]; lane l holds elements [l*V, l*V + V), V = D/32,
+// whose rotary partners (offset D/2) sit in lane l ^ 16.
+template <int D>
+__global__ void __launch_bounds__(256) qkv_norm_rope_kernel(__nv_bfloat16* __restrict__ qkv, int64_t pitch, int64_t n, int H, int Hkv,
+                                                            const __nv_bfloat16* __restrict__ wq, const __nv_bfloat16* __restrict__ wk,
+                                                            const __nv_bfloat16* __restrict__ cos_t, const __nv_bfloat16* __restrict__ sin_t,
+                                                            float eps, int plus1, int norm_v, int rot_dim) {
+  constexpr int V = D / 32;
+  const int heads = H + 2 * Hkv;
+  const int64_t gw = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (gw >= n * heads) return;
+  const int lane = threadIdx.x & 31;
+  const int64_t t = gw / heads;
+  const int hd = static_cast<int>(gw % heads);
+  const bool is_v = hd >= H + Hkv;
+  if (is_v && !norm_v) return;
+  __nv_bfloat16* p = qkv + t * pitch + static_cast<int64_t>(hd) * D + lane * V;
+  float x[V];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < V; ++j) {
+    x[j] = __bfloat162float(p[j]);
+    ss += x[j] * x[j];
+  }
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float inv = powf(ss / D + eps, -0.5f);
+  const __nv_bfloat16* w = is_v ? nullptr : (hd < H ? wq : wk);
+#pragma unroll
+  for (int j = 0; j < V; ++j) {
+    float wj = 1.f;
+    if (w) wj = plus1 ? 1.f + __bfloat162float(w[lane * V + j]) : __bfloat162float(w[lane * V + j]);
+    x[j] = round_bf16(x[j] * inv * wj);
+  }
+  if (!is_v) {
+    // rotate_half over the first R = rot_dim dimensions: out[i] = x[i] cos[i] - x[i + R/2] sin[i]  (i < R/2),
+    //                                                    out[i] = x[i] cos[i] + x[i - R/2] sin[i]  (R/2 <= i < R),
+    // cos / sin repeat with period R/2; dimensions >= R pass through. R/2 is a multiple of V, so a lane's partners sit in
+    // one other lane, `hl` lanes away.
+    const int half = rot_dim / 2;
+    const int hl = half / V;
+    const bool rotates = lane < 2 * hl;
+    const int partner_lane = !rotates ? lane : (lane < hl ? lane + hl : lane - hl);
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      const float partner = __shfl_sync(0xffffffffu, x[j], partner_lane);
+      if (rotates) {
+        const int i = lane * V + j;
+        const int f = i < half ? i : i - half;
+        const float c = __bfloat162float(cos_t[t * half + f]), s = __bfloat162float(sin_t[t * half + f]);
+        const float rot = i < half ? -partner : partner;
+        x[j] = round_bf16(round_bf16(x[j] * c) + round_bf16(rot * s));
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < V; ++j) p[j] = __float2bfloat16_rn(x[j]);
+}
+
+// ------------------------------------------------------------------------------------------------ gated activation + quantiser
+enum : int { ACT_GELU_TANH = 0, ACT_SILU = 1 };
+template <int ACT>
+__device__ __forceinline__ float act_fn(float x) {
+  if (ACT == ACT_GELU_TANH) {
+    const float inner = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+    return 0.5f * x * (1.f + tanhf(inner));
+  }
+  return x / (1.f + expf(-x));
+}
+
+// gu [n, 2F]: gate = columns [0, F), up = columns [F, 2F). y = bf16(bf16(act(gate)) * up); then the per-row fp8 quantisation of y
+// (out_x8 / out_xs), or y itself in bf16 (out_y) when the next linear takes bf16 activations.
+template <int ACT>
+__global__ void __launch_bounds__(512) glu_quant_kernel(const __nv_bfloat16* __restrict__ gu, int F, uint8_t* __restrict__ out_x8,
+                                                        float* __restrict__ out_xs, __nv_bfloat16* __restrict__ out_y) {
+  __shared__ float red[16];
+  const int64_t r = blockIdx.x;
+  const __nv_bfloat16* g = gu + r * 2 * F;
+  const __nv_bfloat16* u = g + F;
+  const int nvec = F / 8;
+  float amax = 0.f;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    float a[8], b[8];
+    load8(g + v * 8, a);
+    load8(u + v * 8, b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      a[j] = round_bf16(round_bf16(act_fn<ACT>(a[j])) * b[j]);
+      amax = fmaxf(amax, fabsf(a[j]));
+    }
+    if (out_y) store8(out_y + r * F + v * 8, a);
+  }
+  if (!out_x8) return;
+  const float s = __fdiv_rn(fmaxf(block_max(amax, red), 1e-12f), 448.f);
+  if (threadIdx.x == 0) out_xs[r] = s;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    float a[8], b[8];
+    load8(g + v * 8, a);
+    load8(u + v * 8, b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = round_bf16(round_bf16(act_fn<ACT>(a[j])) * b[j]);
+    *reinterpret_cast<uint2*>(out_x8 + r * F + v * 8) = quant8(a, s);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ embedding, rotary table
+__global__ void embed_scale_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict__ emb, int hidden, int64_t vocab,
+                                   float scale, __nv_bfloat16* __restrict__ out) {
+  const int64_t t = blockIdx.x;
+  int64_t id = ids[t];
+  if (id < 0 || id >= vocab) id = 0;  // never read outside the table
+  const __nv_bfloat16* src = emb + id * hidden;
+  for (int v = threadIdx.x; v < hidden / 8; v += blockDim.x) {
+    float x[8];
+    load8(src + v * 8, x);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] *= scale;
+    store8(out + t * hidden + v * 8, x);
+  }
+}
+
+// cos / sin of pos[t] * inv_freq[f] in fp32, rounded to bf16 (the model casts them to the activations' dtype before use)
+__global__ void rope_table_kernel(const int32_t* __restrict__ pos, int64_t n, int half, const float* __restrict__ inv_freq,
+                                  __nv_bfloat16* __restrict__ cos_t, __nv_bfloat16* __restrict__ sin_t) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n * half) return;
+  const int64_t t = i / half;
+  const int f = static_cast<int>(i % half);
+  const float ang = static_cast<float>(pos[t]) * inv_freq[f];
+  cos_t[i] = __float2bfloat16_rn(cosf(ang));
+  sin_t[i] = __float2bfloat16_rn(sinf(ang));
+}
+
+}  // namespace spinf
+
+using namespace spinf;
+
+extern "C" int spinf_fused_norm(const void* y, const int64_t* rows, const void* w1, const void* residual, const void* w2, int64_t n_out,
+                                int64_t hidden, float eps, int32_t plus1, void* out_h, void* out_norm, void* out_x8, float* out_xs,
+                                void* stream) {
+  SPINF_CHECK_ARG(y && n_out >= 0 && hidden > 0 && hidden % 8 == 0 && hidden <= NORM_THREADS * NORM_MAX_VEC * 8);
+  SPINF_CHECK_ARG((out_x8 == nullptr) == (out_xs == nullptr));
+  SPINF_CHECK_ARG(!(out_norm || out_x8) || w2);
+  SPINF_CHECK_ARG(n_out < (1ll << 31));
+  if (n_out == 0) return 0;
+  FusedNormArgs a;
+  a.y = static_cast<const __nv_bfloat16*>(y);
+  a.rows = rows;
+  a.w1 = static_cast<const __nv_bfloat16*>(w1);
+  a.residual = static_cast<const __nv_bfloat16*>(residual);
+  a.w2 = static_cast<const __nv_bfloat16*>(w2);
+  a.out_h = static_cast<__nv_bfloat16*>(out_h);
+  a.out_norm = static_cast<__nv_bfloat16*>(out_norm);
+  a.out_x8 = static_cast<uint8_t*>(out_x8);
+  a.out_xs = out_xs;
+  a.hidden = static_cast<int>(hidden);
+  a.eps = eps;
+  a.plus1 = plus1;
+  fused_norm_kernel<<<static_cast<unsigned>(n_out), NORM_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  SPINF_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int spinf_qkv_norm_rope(void* qkv, int64_t pitch, int64_t n, int32_t H, int32_t Hkv, int32_t D, const void* wq,
+                                   const void* wk, const void* cos_t, const void* sin_t, int32_t rot_dim, float eps, int32_t plus1,
+                                   int32_t norm_v, void* stream) {
+  SPINF_CHECK_ARG(qkv && wq && wk && cos_t && sin_t && n >= 0 && H > 0 && Hkv > 0 && (D == 128 || D == 256));
+  SPINF_CHECK_ARG(rot_dim > 0 && rot_dim <= D && rot_dim % (2 * (D / 32)) == 0);
+  SPINF_CHECK_ARG(pitch >= static_cast<int64_t>(H + 2 * Hkv) * D);
+  if (n == 0) return 0;
+  const int64_t warps = n * (H + 2 * Hkv);
+  const unsigned grid = static_cast<unsigned>((warps + 7) / 8);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  auto* p = static_cast<__nv_bfloat16*>(qkv);
+  auto* q = static_cast<const __nv_bfloat16*>(wq);
+  auto* k = static_cast<const __nv_bfloat16*>(wk);
+  auto* c = static_cast<const __nv_bfloat16*>(cos_t);
+  auto* s = static_cast<const __nv_bfloat16*>(sin_t);
+  if (D == 256)
+    qkv_norm_rope_kernel<256><<<grid, 256, 0, st>>>(p, pitch, n, H, Hkv, q, k, c, s, eps, plus1, norm_v, rot_dim);
+  else
+    qkv_norm_rope_kernel<128><<<grid, 256, 0, st>>>(p, pitch, n, H, Hkv, q, k, c, s, eps, plus1, norm_v, rot_dim);
+  SPINF_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int spinf_glu_quant(const void* gu, int64_t n, int64_t F, int32_t act, void* out_x8, float* out_xs, void* out_y,
+                               void* stream) {
+  SPINF_CHECK_ARG(gu && n >= 0 && F > 0 && F % 8 == 0 && (act == 0 || act == 1) && n < (1ll << 31) && F < (1ll << 28));
+  SPINF_CHECK_ARG((out_x8 == nullptr) == (out_xs == nullptr) && (out_x8 || out_y));
+  if (n == 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  auto* g = static_cast<const __nv_bfloat16*>(gu);
+  if (act == ACT_GELU_TANH)
+    glu_quant_kernel<ACT_GELU_TANH><<<static_cast<unsigned>(n), 512, 0, st>>>(g, static_cast<int>(F), static_cast<uint8_t*>(out_x8), out_xs,
+                                                                            static_cast<__nv_bfloat16*>(out_y));
+  else
+    glu_quant_kernel<ACT_SILU><<<static_cast<unsigned>(n), 512, 0, st>>>(g, static_cast<int>(F), static_cast<uint8_t*>(out_x8), out_xs,
+                                                                       static_cast<__nv_bfloat16*>(out_y));
+  SPINF_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int spinf_embed_scale(const int64_t* ids, const void* emb, int64_t n, int64_t hidden, int64_t vocab, float scale, void* out,
+                                 void* stream) {
+  SPINF_CHECK_ARG(ids && emb && out && n >= 0 && hidden > 0 && hidden % 8 == 0 && vocab > 0 && n < (1ll << 31));
+  if (n == 0) return 0;
+  embed_scale_kernel<<<static_cast<unsigned>(n), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      ids, static_cast<const __nv_bfloat16*>(emb), static_cast<int>(hidden), vocab, scale, static_cast<__nv_bfloat16*>(out));
+  SPINF_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int spinf_rope_table(const int32_t* pos, int64_t n, int32_t rot_dim, const float* inv_freq, void* cos_t, void* sin_t,
+                                void* stream) {
+  SPINF_CHECK_ARG(pos && cos_t && sin_t && inv_freq && n >= 0 && rot_dim > 0 && rot_dim % 2 == 0);
+  if (n == 0) return 0;
+  const int half = rot_dim / 2;
+  const int64_t total = n * half;
+  rope_table_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      pos, n, half, inv_freq, static_cast<__nv_bfloat16*>(cos_t), static_cast<__nv_bfloat16*>(sin_t));
+  SPINF_CUDA_OK(cudaGetLastError());
+  return 0;
+}

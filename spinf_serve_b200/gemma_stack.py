@@ -1,0 +1,182 @@
+"""The Gemma-style stack of the packed scoring path: the counterpart of Gemma4Stack (spinf_serve/models/gemma4.py:390-435), whose
+forward (gemma4.py:407-415) runs transformers' Gemma 4 decoder layers with fp8 row-wise linears and the tree attention. Here a
+layer is a fixed chain of library kernels over the packed stream [n, hidden]:
+
+    fused_norm (post-ffn norm of the previous layer + residual + input norm + fp8 quantisation)
+    fp8 GEMM q|k|v (one fused projection)  ->  head norms + rotary (in place)  ->  tree attention  ->  fp8 quantisation
+    fp8 GEMM o  ->  fused_norm (post-attention norm + residual + pre-ffn norm + fp8 quantisation)
+    fp8 GEMM gate|up (one fused projection)  ->  GeGLU + fp8 quantisation  ->  fp8 GEMM down
+
+Fusing q|k|v and gate|up is exact for this scheme: weight scales are per output channel and the activation scale is per token,
+so each output element is the one the separate linears give. The final norm runs on the read rows only (Scorer._forward reads
+nothing else, spinf_serve/scorer.py:248-254)."""
+
+from dataclasses import dataclass, field
+
+import torch
+
+from spinf_serve_b200 import attention, ops
+from spinf_serve_b200.linears import quantize_weight_rowwise
+
+
+@dataclass
+class GemmaConfig:
+    layers: int = 48
+    hidden: int = 3840
+    heads: int = 16
+    kv_heads: int = 8
+    head_dim: int = 256
+    ffn: int = 15360
+    vocab: int = 262144
+    window: int = 1024
+    pattern: int = 6  # every pattern-th layer is full attention, the rest sliding; the last layer is always full
+    eps: float = 1e-6
+    theta_sliding: float = 10_000.0
+    theta_full: float = 1_000_000.0
+    softcap: float | None = None
+    layer_types: list = field(default_factory=list)
+
+    def __post_init__(self):
+        if not self.layer_types:
+            self.layer_types = ["sliding_attention" if (i + 1) % self.pattern else "full_attention" for i in range(self.layers)]
+            self.layer_types[-1] = "full_attention"
+
+    @property
+    def linear_params(self) -> int:
+        """parameters of the quantized linears of one layer"""
+        qkv = (self.heads + 2 * self.kv_heads) * self.head_dim
+        return self.hidden * (qkv + self.heads * self.head_dim) + 3 * self.hidden * self.ffn
+
+
+CONFIGS = {
+    # BASELINE configuration 2 / 3: synthetic Gemma-style 12B
+    "gemma12b": dict(layers=48, hidden=3840, heads=16, kv_heads=8, head_dim=256, ffn=15360, vocab=262144, window=1024),
+    # BASELINE configuration 4: synthetic Gemma-style 31B-class
+    "gemma31b": dict(layers=60, hidden=5376, heads=32, kv_heads=16, head_dim=128, ffn=21504, vocab=262144, window=1024),
+}
+
+
+class GemmaWeights:
+    """device-resident weights: per layer the fused fp8 projections with their per-channel scales and the bf16 norm weights"""
+
+    def __init__(self, cfg: GemmaConfig, embed, norm, layers):
+        self.cfg, self.embed, self.norm, self.layers = cfg, embed, norm, layers
+
+    @staticmethod
+    def _layer(L):
+        def q8(*names):
+            parts = [quantize_weight_rowwise(L[k]) for k in names]
+            return torch.cat([p[0] for p in parts]).contiguous(), torch.cat([p[1] for p in parts], dim=1).reshape(-1).contiguous()
+
+        out = {}
+        out["qkv_w"], out["qkv_s"] = q8("q", "k", "v")
+        out["o_w"], out["o_s"] = q8("o")
+        out["gu_w"], out["gu_s"] = q8("gate", "up")
+        out["down_w"], out["down_s"] = q8("down")
+        for k in ("q_norm", "k_norm", "input_ln", "post_attn_ln", "pre_ffn_ln", "post_ffn_ln"):
+            out[k] = L[k].contiguous()
+        return out
+
+    @classmethod
+    def from_bf16(cls, cfg: GemmaConfig, W, device):
+        """W: {"embed", "norm", "layers": [{q,k,v,o,gate,up,down, q_norm,k_norm, input_ln,post_attn_ln,pre_ffn_ln,post_ffn_ln}]} of
+        bf16 tensors (any device); quantisation runs on `device`, one layer at a time"""
+        layers = [cls._layer({k: v.to(device) for k, v in L.items()}) for L in W["layers"]]
+        return cls(cfg, W["embed"].to(device).contiguous(), W["norm"].to(device).contiguous(), layers)
+
+    @classmethod
+    def random(cls, cfg: GemmaConfig, seed: int, device):
+        """random-init weights of the architecture generated on the device (N(0, 0.02) linears and embedding, norm weights near 1)"""
+        g = torch.Generator(device=device).manual_seed(seed)
+
+        def lin(o, i):
+            return (torch.randn((o, i), generator=g, device=device) * 0.02).to(torch.bfloat16)
+
+        def nw(d):
+            return (1.0 + 0.1 * torch.randn(d, generator=g, device=device)).to(torch.bfloat16)
+
+        H, K, D = cfg.heads, cfg.kv_heads, cfg.head_dim
+        embed, norm = lin(cfg.vocab, cfg.hidden), nw(cfg.hidden)
+        layers = []
+        for _ in range(cfg.layers):
+            L = {
+                "q": lin(H * D, cfg.hidden), "k": lin(K * D, cfg.hidden), "v": lin(K * D, cfg.hidden), "o": lin(cfg.hidden, H * D),
+                "gate": lin(cfg.ffn, cfg.hidden), "up": lin(cfg.ffn, cfg.hidden), "down": lin(cfg.hidden, cfg.ffn),
+                "q_norm": nw(D), "k_norm": nw(D),
+                "input_ln": nw(cfg.hidden), "post_attn_ln": nw(cfg.hidden), "pre_ffn_ln": nw(cfg.hidden), "post_ffn_ln": nw(cfg.hidden),
+            }
+            layers.append(cls._layer(L))
+        return cls(cfg, embed, norm, layers)
+
+    @property
+    def lm_weight(self):
+        return self.embed  # tied lm head (spinf_serve/models/gemma4.py:249)
+
+
+class GemmaStack:
+    """plan / stage / forward of the family (the Stack interface, spinf_serve/models/base.py:50-64), on library kernels only"""
+
+    family = "gemma"
+    hybrid = False
+
+    def __init__(self, weights: GemmaWeights, n_layers: int | None = None):
+        self.w = weights
+        self.cfg = weights.cfg
+        self.n_layers = self.cfg.layers if n_layers is None else n_layers  # the reference's EngineConfig.layers debug knob
+        dev = weights.embed.device
+        D = self.cfg.head_dim
+        expo = torch.arange(0, D, 2, dtype=torch.int64).float() / D
+        self.inv_freq = {
+            "sliding_attention": (1.0 / (self.cfg.theta_sliding**expo)).to(dev),
+            "full_attention": (1.0 / (self.cfg.theta_full**expo)).to(dev),
+        }
+        self.embed_scale = float(torch.tensor(self.cfg.hidden**0.5).to(torch.bfloat16))
+
+    def plan(self, b) -> None:
+        """nothing to prepare on the host for attention-only models (base.py:50-51)"""
+
+    def stage(self, b, device):
+        """batch arrays -> device inputs: ids int64 [n], pos int32 [n], the two TileMasks (the counterpart of Stack.stage +
+        Scorer._block_masks, base.py:53-60, scorer.py:207-238)"""
+        ids = torch.from_numpy(b.ids).pin_memory().to(device, non_blocking=True)
+        masks = attention.stream_masks(b.art, b.end, b.pos, self.cfg.window, device, always_window=True)
+        return {"ids": ids, "pos": masks["full_attention"].pos, "masks": masks}
+
+    def forward(self, inputs, rows=None, taps=None):
+        """packed forward -> final hidden states after the model's last norm, [n, hidden] bf16, or only the rows `rows` (int64
+        device tensor of stream positions). taps: optional dict filled with per-layer intermediates (tests)."""
+        cfg, w = self.cfg, self.w
+        H, K, D = cfg.heads, cfg.kv_heads, cfg.head_dim
+        ids, pos, masks = inputs["ids"], inputs["pos"], inputs["masks"]
+        n = ids.numel()
+        tables = {k: ops.rope_table(pos, f) for k, f in self.inv_freq.items()}
+        h = ops.embed_scale(ids, w.embed, self.embed_scale)
+        if self.n_layers == 0:
+            return ops.fused_norm(h, w2=w.norm, rows=rows, eps=cfg.eps, want_norm=True)["norm"]
+        r = ops.fused_norm(h, w2=w.layers[0]["input_ln"], eps=cfg.eps, want_fp8=True)
+        for i in range(self.n_layers):
+            L = w.layers[i]
+            kind = cfg.layer_types[i]
+            cos, sin = tables[kind]
+            qkv = ops.fp8_rowwise_gemm(r["x8"], r["xs"], L["qkv_w"], L["qkv_s"])
+            ops.qkv_norm_rope(qkv, H, K, D, L["q_norm"], L["k_norm"], cos, sin, cfg.eps)
+            q = qkv[:, : H * D].view(n, H, D)
+            k = qkv[:, H * D : (H + K) * D].view(n, K, D)
+            v = qkv[:, (H + K) * D :].view(n, K, D)
+            a = attention.tree_attention(q, k, v, masks[kind], 1.0)  # the model passes scaling = 1.0 (q and k are normed)
+            a8, a_s = ops.fp8_rowwise_quant(a.view(n, H * D))
+            o = ops.fp8_rowwise_gemm(a8, a_s, L["o_w"], L["o_s"])
+            r = ops.fused_norm(o, w1=L["post_attn_ln"], residual=h, w2=L["pre_ffn_ln"], eps=cfg.eps, want_h=True, want_fp8=True)
+            h = r["h"]
+            gu = ops.fp8_rowwise_gemm(r["x8"], r["xs"], L["gu_w"], L["gu_s"])
+            g8, g_s, _ = ops.glu_quant(gu, "gelu_tanh")
+            d = ops.fp8_rowwise_gemm(g8, g_s, L["down_w"], L["down_s"])
+            last = i == self.n_layers - 1
+            r = ops.fused_norm(
+                d, w1=L["post_ffn_ln"], residual=h, w2=None if last else w.layers[i + 1]["input_ln"], eps=cfg.eps, want_h=True,
+                want_fp8=not last,
+            )
+            h = r["h"]
+            if taps is not None:
+                taps[i] = {"q": q.clone(), "k": k.clone(), "v": v.clone(), "attn": a, "h": h}
+        return ops.fused_norm(h, w2=w.norm, rows=rows, eps=cfg.eps, want_norm=True)["norm"]

@@ -92,3 +92,88 @@ def option_logprobs(h, W, cols, softcap=None, workspace=None):
         "spinf_option_logprobs",
     )
     return out
+
+
+def fused_norm(y, w1=None, residual=None, w2=None, rows=None, eps=1e-6, plus1=False, want_h=False, want_norm=False, want_fp8=False):
+    """[RMSNorm w1] -> [+ residual] -> [RMSNorm w2] over the rows of y [*, hidden] bf16 (rows: int64 indices of the input rows to
+    read) -> dict with "h" (after the residual add), "norm" (bf16 of the second norm), "x8"/"xs" (its row-wise fp8 form)"""
+    _need(y, torch.bfloat16, "y", 2)
+    hidden = y.shape[1]
+    n_out = rows.numel() if rows is not None else y.shape[0]
+    dev = y.device
+    if rows is not None:
+        _need(rows, torch.int64, "rows", 1)
+    for name, w in (("w1", w1), ("w2", w2)):
+        if w is not None:
+            _need(w, torch.bfloat16, name, 1)
+    if residual is not None:
+        _need(residual, torch.bfloat16, "residual", 2)
+    out = {}
+    if want_h:
+        out["h"] = torch.empty((n_out, hidden), dtype=torch.bfloat16, device=dev)
+    if want_norm:
+        out["norm"] = torch.empty((n_out, hidden), dtype=torch.bfloat16, device=dev)
+    if want_fp8:
+        out["x8"] = torch.empty((n_out, hidden), dtype=FP8, device=dev)
+        out["xs"] = torch.empty((n_out, 1), dtype=torch.float32, device=dev)
+    check(
+        _lib.lib().spinf_fused_norm(
+            ptr(y), ptr(rows), ptr(w1), ptr(residual), ptr(w2), n_out, hidden, ctypes.c_float(eps), int(plus1), ptr(out.get("h")),
+            ptr(out.get("norm")), ptr(out.get("x8")), ptr(out.get("xs")), stream_ptr(),
+        ),
+        "spinf_fused_norm",
+    )
+    return out
+
+
+def rope_table(pos, inv_freq):
+    """pos int32 [n], inv_freq fp32 [R/2] -> (cos, sin) bf16 [n, R/2]"""
+    _need(pos, torch.int32, "pos", 1)
+    _need(inv_freq, torch.float32, "inv_freq", 1)
+    n, half = pos.numel(), inv_freq.numel()
+    cos = torch.empty((n, half), dtype=torch.bfloat16, device=pos.device)
+    sin = torch.empty_like(cos)
+    check(_lib.lib().spinf_rope_table(ptr(pos), n, 2 * half, ptr(inv_freq), ptr(cos), ptr(sin), stream_ptr()), "spinf_rope_table")
+    return cos, sin
+
+
+def qkv_norm_rope(qkv, H, Hkv, D, wq, wk, cos, sin, eps=1e-6, plus1=False, norm_v=True):
+    """in place on the fused projection output qkv [n, (H + 2 Hkv) D]: head norms, then rotary on q and k"""
+    _need(qkv, torch.bfloat16, "qkv", 2)
+    _need(wq, torch.bfloat16, "wq", 1)
+    _need(wk, torch.bfloat16, "wk", 1)
+    _need(cos, torch.bfloat16, "cos", 2)
+    _need(sin, torch.bfloat16, "sin", 2)
+    n = qkv.shape[0]
+    check(
+        _lib.lib().spinf_qkv_norm_rope(
+            ptr(qkv), qkv.stride(0), n, H, Hkv, D, ptr(wq), ptr(wk), ptr(cos), ptr(sin), 2 * cos.shape[1], ctypes.c_float(eps),
+            int(plus1), int(norm_v), stream_ptr(),
+        ),
+        "spinf_qkv_norm_rope",
+    )
+    return qkv
+
+
+def glu_quant(gu, act="gelu_tanh", want_fp8=True, want_y=False):
+    """gu [n, 2F] bf16 (gate | up) -> act(gate) * up as (x8 [n, F], xs [n, 1]) and/or bf16 y [n, F]"""
+    _need(gu, torch.bfloat16, "gu", 2)
+    n, F = gu.shape[0], gu.shape[1] // 2
+    x8 = torch.empty((n, F), dtype=FP8, device=gu.device) if want_fp8 else None
+    xs = torch.empty((n, 1), dtype=torch.float32, device=gu.device) if want_fp8 else None
+    y = torch.empty((n, F), dtype=torch.bfloat16, device=gu.device) if want_y else None
+    code = {"gelu_tanh": 0, "silu": 1}[act]
+    check(_lib.lib().spinf_glu_quant(ptr(gu), n, F, code, ptr(x8), ptr(xs), ptr(y), stream_ptr()), "spinf_glu_quant")
+    return x8, xs, y
+
+
+def embed_scale(ids, emb, scale):
+    """ids int64 [n], emb [vocab, hidden] bf16 -> bf16(emb[ids] * scale) [n, hidden]"""
+    _need(ids, torch.int64, "ids", 1)
+    _need(emb, torch.bfloat16, "emb", 2)
+    out = torch.empty((ids.numel(), emb.shape[1]), dtype=torch.bfloat16, device=emb.device)
+    check(
+        _lib.lib().spinf_embed_scale(ptr(ids), ptr(emb), ids.numel(), emb.shape[1], emb.shape[0], ctypes.c_float(scale), ptr(out), stream_ptr()),
+        "spinf_embed_scale",
+    )
+    return out
