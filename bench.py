@@ -1,0 +1,327 @@
+"""Throughput of the packed-prefill scoring path on the BASELINE configuration-2 workload.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P bench.py --gpus N ...
+
+One step = one pass of the hot path over one batch: the 24 contents x 56 two-option questions (1344 questions, 27408 real tokens)
+packed into one 27648-token stream and scored by the synthetic Gemma-style 12B with fp8 row-wise linears (random-init weights,
+uniform random token ids; the reference's benchmark text is not reproduced). Rank r of N scores its own 24 contents (replicas
+over a content-partitioned queue, no collective on the data path): weak scaling.
+
+  value   questions/s with the packed inputs already resident in HBM (stack forward + option log-prob read), K steps between
+          CUDA events, max over ranks
+  e2e     the same through the public call Scorer.score_grouped with host inputs: packing, tile descriptors, pinned host->device
+          copies, forward, device->host read of the log-probs, all inside the timed region
+  roofline   the row-wise fp8 GEMM (dominant kernel): algorithmic FLOPs / CUDA-event time of its launches in the timed region
+  cpu_baseline   the CPU oracle (a port of the reference's arithmetic; the reference has no CPU forward) on a bounded sample
+
+--impl reference times that CPU oracle alone, with all host threads, and prints the same line with "impl": "reference"."""
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "questions scored/sec"
+UNIT = "questions/s"
+WORKLOAD = "cfg2: gemma-style 12B fp8 row-wise, 24 contents x (470-token trunk + 56 questions x 12 tokens, 2 single-token options), one 27648-token forward"
+
+
+def _peaks():
+    """measured peaks of this pool (driver-written file), else the stated fallback"""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_burst": p["bf16_tflops"], "bf16_sustained": p["bf16_tflops_sustained"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_burst": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """samples nvidia-smi clocks and throttle reasons while the timed region runs"""
+
+    FIELDS = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------ CPU arm (the oracle, a port)
+def cpu_sample(threads: int):
+    """the CPU oracle on a bounded sample of the workload: 2 of the 24 contents (2284 tokens, 112 questions) through ONE of the
+    48 layers plus the lm-head read of their 112 rows; -> a closure that runs the sample once and returns (layer_s, head_s)"""
+    import numpy as np
+    import torch
+
+    from oracle import gemma as OG
+    from oracle import head as OH
+    from spinf_serve_b200 import packer as P
+    from spinf_serve_b200 import workloads
+
+    torch.set_num_threads(threads)
+    cfg = OG.GemmaConfig(layers=1)
+    g = torch.Generator().manual_seed(0)
+
+    def lin(o, i):
+        return torch.empty((o, i), dtype=torch.bfloat16).normal_(0.0, 0.02, generator=g)
+
+    H, K, D = cfg.heads, cfg.kv_heads, cfg.head_dim
+    ones = lambda d: torch.ones(d, dtype=torch.bfloat16)  # noqa: E731
+    L = {
+        "q": lin(H * D, cfg.hidden), "k": lin(K * D, cfg.hidden), "v": lin(K * D, cfg.hidden), "o": lin(cfg.hidden, H * D),
+        "gate": lin(cfg.ffn, cfg.hidden), "up": lin(cfg.ffn, cfg.hidden), "down": lin(cfg.hidden, cfg.ffn),
+        "q_norm": ones(D), "k_norm": ones(D), "input_ln": ones(cfg.hidden), "post_attn_ln": ones(cfg.hidden),
+        "pre_ffn_ln": ones(cfg.hidden), "post_ffn_ln": ones(cfg.hidden),
+    }
+    W = {"embed": lin(cfg.vocab, cfg.hidden), "norm": ones(cfg.hidden), "layers": [L]}
+    Q = OG.quantize(W)
+    wl = workloads.config2(seed=0, n_contents=2)
+    pk = P.Packer(32768, 65536, True, 1024)
+    batches = [b for key, first, t in wl.items for b in pk.push((key, first), t)] + list(pk.flush())
+    (b,) = batches
+    cols = sorted({int(t) for o in b.owners for pl in o.plans for t in pl.entry_tok})
+
+    def run():
+        t0 = time.perf_counter()
+        hf = OG.forward(cfg, W, Q, b.ids, b.art, b.end, b.pos)
+        t1 = time.perf_counter()
+        OH.option_logprobs(hf[torch.as_tensor(b.sel)], W["embed"], np.asarray(cols), None)
+        t2 = time.perf_counter()
+        return t1 - t0, t2 - t1
+
+    return run, wl
+
+
+def cpu_questions_per_s(layer_s: float, head_s: float, sample_tokens: int, sample_questions: int):
+    """extrapolation of the sample to the full workload: layers x tokens for the forward, rows for the head"""
+    full = layer_s * 48 * (27408 / sample_tokens) + head_s * (1344 / sample_questions)
+    return 1344 / full, full
+
+
+def cpu_baseline(threads: int, steps: int = 1):
+    run, wl = cpu_sample(threads)
+    times = [run() for _ in range(steps)]
+    layer_s = min(t[0] for t in times)
+    head_s = min(t[1] for t in times)
+    qps, full = cpu_questions_per_s(layer_s, head_s, wl.n_tokens, wl.n_questions)
+    return {
+        "value": qps,
+        "unit": UNIT,
+        "cores": threads,
+        "kind": "port",
+        "sample": f"CPU oracle (torch fp32, {threads} threads) on 2 of 24 contents ({wl.n_tokens} tokens, {wl.n_questions} questions) through 1 of 48 layers "
+        f"({layer_s:.2f} s) + lm-head read of their rows ({head_s:.2f} s); scaled x48 layers x{27408 / wl.n_tokens:.1f} tokens and x{1344 // wl.n_questions} rows "
+        f"to the full step ({full:.0f} s)",
+    }
+
+
+def reference_arm(args):
+    """--impl reference: the reference has no CPU forward of its own (its Scorer is CUDA-only), so this arm times the CPU oracle
+    assembled from its arithmetic, on the host cores, each step one bounded sample"""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    run, wl = cpu_sample(threads)
+    for _ in range(min(args.warmup, 1)):
+        run()
+    t0 = time.perf_counter()
+    times = [run() for _ in range(args.steps)]
+    wall = time.perf_counter() - t0
+    layer_s = sum(t[0] for t in times) / len(times)
+    head_s = sum(t[1] for t in times) / len(times)
+    qps, full = cpu_questions_per_s(layer_s, head_s, wl.n_tokens, wl.n_questions)
+    sample = (
+        f"CPU oracle port, {threads} threads: per step 2 of 24 contents ({wl.n_tokens} tokens) through 1 of 48 layers ({layer_s:.2f} s) + lm-head "
+        f"read of {wl.n_questions} rows ({head_s:.2f} s), scaled to the full step ({full:.0f} s)"
+    )
+    line = {
+        "impl": "reference", "metric": METRIC, "value": qps, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1000 * wall / max(args.steps, 1), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "l2": "inputs larger than L2"},
+        "cpu_baseline": {"value": qps, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": qps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------------ GPU arm
+def gpu_arm(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from spinf_serve_b200 import _lib, ops, workloads
+    from spinf_serve_b200.gemma_stack import CONFIGS, GemmaConfig, GemmaStack, GemmaWeights
+    from spinf_serve_b200.packer import Packer
+    from spinf_serve_b200.scorer import EngineConfig, Scorer
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the scoring path has no CPU fallback (use --impl reference for the CPU arm)")
+    dev = torch.device(f"cuda:{local}")
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.init(dev)
+
+    cfg = GemmaConfig(**CONFIGS["gemma12b"])
+    stack = GemmaStack(GemmaWeights.random(cfg, seed=0, device=dev))  # every replica regenerates the same weights from the seed
+    wl = workloads.config2(seed=rank, first_id=24 * rank)             # and scores its own 24 contents
+    ecfg = EngineConfig(token_budget=wl.token_budget, max_tokens=65536)
+    scorer = Scorer(stack, ecfg, dev)
+
+    # ---- device-resident leg: the packed batch, its masks, the read rows and the option columns are staged once
+    pk = Packer(ecfg.token_budget, ecfg.max_tokens, ecfg.align_jobs, ecfg.min_stream)
+    batches = [b for key, first, t in wl.items for b in pk.push((key, first), t)] + list(pk.flush())
+    assert len(batches) == 1, "configuration 2 is one forward"
+    b = batches[0]
+    cols = Scorer._cols(b)
+    inputs = stack.stage(b, dev)
+    sel = torch.from_numpy(b.sel).to(dev)
+    ci = torch.tensor(cols, dtype=torch.int32, device=dev)
+    W = stack.w.lm_weight
+    ws = torch.empty(int(_lib.lib().spinf_option_logprobs_workspace_bytes(len(b.sel), W.shape[0], len(cols))), dtype=torch.uint8, device=dev)
+
+    def step():
+        rows = stack.forward(inputs, rows=sel)
+        return ops.option_logprobs(rows, W, ci, None, ws)
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(args.warmup):
+        step()
+    sync()
+    _lib.last_status()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ops.PROFILE = []
+    launches0 = ops.COUNTS["launches"]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        lp = step()
+    e1.record()
+    sync()
+    launches = ops.COUNTS["launches"] - launches0
+    prof, ops.PROFILE = ops.PROFILE, None
+    ms = e0.elapsed_time(e1)
+    _lib.last_status()
+    assert bool(torch.isfinite(lp).all()), "non-finite log-probs"
+
+    # ---- end-to-end leg: the public call with host inputs, every step packs, stages, runs and reads back
+    for _ in range(min(args.warmup, 2)):
+        scorer.score_grouped(wl.items)
+    sync()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(args.steps):
+        out = scorer.score_grouped(wl.items)
+    f1.record()
+    sync()
+    ms_e2e = f0.elapsed_time(f1)
+    clocks = sampler.stop() if rank == 0 else None
+    assert len(out) == len(wl.items)
+
+    if world > 1:
+        t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = float(t[0]), float(t[1])
+    if rank == 0:
+        masks = inputs["masks"]
+        n = b.length
+        h2d = n * 8 + 3 * n * 4 + len(b.sel) * 8 + len(cols) * 4
+        for m in (masks["full_attention"], masks["sliding_attention"]):
+            h2d += m.offsets.numel() * 4 + m.blocks.numel() * 4 + m.flags.numel()
+        d2h = len(b.sel) * len(cols) * 4
+        peaks = _peaks()
+        fp8_peak = 2.0 * peaks["bf16_sustained"]
+        gemm_ms = sum(a.elapsed_time(c) for a, c, _ in prof)
+        gemm_flops = sum(f for _, _, f in prof)
+        achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
+        step_flops = workloads.gemm_flops(cfg, wl.n_tokens) + workloads.head_flops(cfg, wl.n_questions)
+        line = {
+            "metric": METRIC, "value": world * wl.n_questions * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
+            "config": {
+                "workload": WORKLOAD, "per_gpu": "24 contents / 1344 questions / 27408 tokens per step", "parallelism": f"{world} replicas, content-sharded",
+                "l2": "inputs larger than L2 (10.8 GB of weights and >2 GB of activations per step)",
+                "tiles_visited": masks["full_attention"].visited, "tiles_skipped_fraction": round(masks["full_attention"].skipped_fraction, 4),
+            },
+            "e2e": {"value": world * wl.n_questions * args.steps / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
+                    "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
+            "gpu_launches": int(launches),
+            "roofline": {
+                "kernel": "gemm_tc_kernel<fp8, 256, EpiStoreBf16<scaled>> (row-wise fp8 linear)", "bound": "tensor", "achieved": achieved,
+                "peak": fp8_peak, "unit": "TFLOP/s", "frac": achieved / fp8_peak, "traffic": None,
+                "peak_source": f"2 x bf16 sustained of {peaks['source']} (no fp8 figure in MEASURED_PEAKS.json)",
+                "launches": len(prof), "share_of_step": gemm_ms / ms if ms > 0 else None,
+                "step_tflops_all_kernels": step_flops * args.steps / (ms * 1e-3) / 1e12,
+            },
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(os.cpu_count() or 1)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle timing (profiling runs)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+    else:
+        gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -41,7 +41,8 @@ class GemmaConfig:
     def __post_init__(self):
         if not self.layer_types:
             self.layer_types = ["sliding_attention" if (i + 1) % self.pattern else "full_attention" for i in range(self.layers)]
-            self.layer_types[-1] = "full_attention"  # the model code forces the last layer to full attention
+            if self.layer_types:
+                self.layer_types[-1] = "full_attention"  # the model code forces the last layer to full attention
 
 
 def init_weights(cfg: GemmaConfig, seed: int = 0, device="cpu"):

@@ -10,7 +10,7 @@ from dataclasses import dataclass
 import numpy as np
 import torch
 
-from spinf_serve_b200 import _lib, packer
+from spinf_serve_b200 import _lib, ops, packer
 from spinf_serve_b200._lib import SpinfError, check, ptr, stream_ptr
 
 
@@ -76,6 +76,7 @@ def tree_attention(q, k, v, mask: TileMask, scale: float, out=None):
         ),
         "spinf_tree_attn_fwd",
     )
+    ops.COUNTS["launches"] += 1
     return out
 
 

@@ -39,7 +39,8 @@ class GemmaConfig:
     def __post_init__(self):
         if not self.layer_types:
             self.layer_types = ["sliding_attention" if (i + 1) % self.pattern else "full_attention" for i in range(self.layers)]
-            self.layer_types[-1] = "full_attention"
+            if self.layer_types:
+                self.layer_types[-1] = "full_attention"
 
     @property
     def linear_params(self) -> int:
@@ -63,9 +64,9 @@ class GemmaWeights:
         self.cfg, self.embed, self.norm, self.layers = cfg, embed, norm, layers
 
     @staticmethod
-    def _layer(L):
+    def _layer(L, pre=None):
         def q8(*names):
-            parts = [quantize_weight_rowwise(L[k]) for k in names]
+            parts = [pre[k] if pre is not None else quantize_weight_rowwise(L[k]) for k in names]
             return torch.cat([p[0] for p in parts]).contiguous(), torch.cat([p[1] for p in parts], dim=1).reshape(-1).contiguous()
 
         out = {}
@@ -82,6 +83,17 @@ class GemmaWeights:
         """W: {"embed", "norm", "layers": [{q,k,v,o,gate,up,down, q_norm,k_norm, input_ln,post_attn_ln,pre_ffn_ln,post_ffn_ln}]} of
         bf16 tensors (any device); quantisation runs on `device`, one layer at a time"""
         layers = [cls._layer({k: v.to(device) for k, v in L.items()}) for L in W["layers"]]
+        return cls(cfg, W["embed"].to(device).contiguous(), W["norm"].to(device).contiguous(), layers)
+
+    @classmethod
+    def from_quantized(cls, cfg: GemmaConfig, W, Q, device):
+        """as from_bf16 with the linears already quantized: Q[i][name] = (w8 [out, in] e4m3, ws [1, out] fp32), the tensors a
+        row-wise fp8 checkpoint would hold (the reference's `prequantized` path, spinf_serve/quant/linears.py:121-131)"""
+        names = ("q_norm", "k_norm", "input_ln", "post_attn_ln", "pre_ffn_ln", "post_ffn_ln")
+        layers = [
+            cls._layer({k: L[k].to(device) for k in names}, {k: (a.to(device), b.to(device)) for k, (a, b) in q.items()})
+            for L, q in zip(W["layers"], Q)
+        ]
         return cls(cfg, W["embed"].to(device).contiguous(), W["norm"].to(device).contiguous(), layers)
 
     @classmethod

@@ -11,6 +11,11 @@ from spinf_serve_b200._lib import SpinfError, check, ptr, stream_ptr
 
 FP8 = torch.float8_e4m3fn
 
+# Measurement hooks (bench.py): COUNTS["launches"] counts the kernels this module enqueued; when PROFILE is a list, every row-wise
+# fp8 GEMM is bracketed by CUDA events on its stream and (start, end, flops) is appended.
+COUNTS = {"launches": 0}
+PROFILE = None
+
 
 def _need(t, dtype, name, dims=None):
     if not isinstance(t, torch.Tensor) or not t.is_cuda:
@@ -32,6 +37,7 @@ def fp8_rowwise_quant(x):
     x8 = torch.empty((M, K), dtype=FP8, device=x.device)
     xs = torch.empty((M, 1), dtype=torch.float32, device=x.device)
     check(_lib.lib().spinf_fp8_rowwise_quant(ptr(x2), M, K, ptr(x8), ptr(xs), stream_ptr()), "spinf_fp8_rowwise_quant")
+    COUNTS["launches"] += 1
     return x8, xs
 
 
@@ -49,10 +55,18 @@ def fp8_rowwise_gemm(x8, xs, w8, ws, out=None):
     y = out if out is not None else torch.empty((M, N), dtype=torch.bfloat16, device=x8.device)
     if out is not None:
         _need(out, torch.bfloat16, "out", 2)
+    prof = PROFILE
+    if prof is not None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
     check(
         _lib.lib().spinf_fp8_rowwise_gemm(ptr(x8), ptr(xs1), ptr(w8), ptr(ws1), ptr(y), M, N, K, stream_ptr()),
         "spinf_fp8_rowwise_gemm",
     )
+    if prof is not None:
+        e1.record()
+        prof.append((e0, e1, 2.0 * M * N * K))
+    COUNTS["launches"] += 1
     return y
 
 
@@ -66,6 +80,7 @@ def bf16_gemm(x, w):
         raise SpinfError("bf16_gemm: inner dimensions differ")
     y = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
     check(_lib.lib().spinf_bf16_gemm(ptr(x), ptr(w), ptr(y), M, N, K, stream_ptr()), "spinf_bf16_gemm")
+    COUNTS["launches"] += 1
     return y
 
 
@@ -91,6 +106,7 @@ def option_logprobs(h, W, cols, softcap=None, workspace=None):
         ),
         "spinf_option_logprobs",
     )
+    COUNTS["launches"] += 3
     return out
 
 
@@ -123,6 +139,7 @@ def fused_norm(y, w1=None, residual=None, w2=None, rows=None, eps=1e-6, plus1=Fa
         ),
         "spinf_fused_norm",
     )
+    COUNTS["launches"] += 1
     return out
 
 
@@ -134,6 +151,7 @@ def rope_table(pos, inv_freq):
     cos = torch.empty((n, half), dtype=torch.bfloat16, device=pos.device)
     sin = torch.empty_like(cos)
     check(_lib.lib().spinf_rope_table(ptr(pos), n, 2 * half, ptr(inv_freq), ptr(cos), ptr(sin), stream_ptr()), "spinf_rope_table")
+    COUNTS["launches"] += 1
     return cos, sin
 
 
@@ -152,6 +170,7 @@ def qkv_norm_rope(qkv, H, Hkv, D, wq, wk, cos, sin, eps=1e-6, plus1=False, norm_
         ),
         "spinf_qkv_norm_rope",
     )
+    COUNTS["launches"] += 1
     return qkv
 
 
@@ -164,6 +183,7 @@ def glu_quant(gu, act="gelu_tanh", want_fp8=True, want_y=False):
     y = torch.empty((n, F), dtype=torch.bfloat16, device=gu.device) if want_y else None
     code = {"gelu_tanh": 0, "silu": 1}[act]
     check(_lib.lib().spinf_glu_quant(ptr(gu), n, F, code, ptr(x8), ptr(xs), ptr(y), stream_ptr()), "spinf_glu_quant")
+    COUNTS["launches"] += 1
     return x8, xs, y
 
 
@@ -176,4 +196,5 @@ def embed_scale(ids, emb, scale):
         _lib.lib().spinf_embed_scale(ptr(ids), ptr(emb), ids.numel(), emb.shape[1], emb.shape[0], ctypes.c_float(scale), ptr(out), stream_ptr()),
         "spinf_embed_scale",
     )
+    COUNTS["launches"] += 1
     return out
