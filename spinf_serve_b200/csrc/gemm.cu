@@ -267,3 +267,4 @@ extern "C" int spinf_option_logprobs(const void* h, const void* W, int64_t R, in
   SPINF_CUDA_OK(cudaGetLastError());
   return 0;
 }
+
