@@ -77,6 +77,24 @@ int spinf_option_logprobs(const void* h, const void* W, int64_t R, int64_t hidde
                           int64_t n_cols, float softcap, float* out, void* workspace,
                           int64_t workspace_bytes, void* stream);
 
+/* Allocation-free variant of spinf_option_logprobs (it has no counterpart in the reference: the reference's lm-head read always
+ * allocates its [rows, vocab] temporaries through torch). For callers that cannot allocate device memory at call time: a
+ * serving process whose own allocator already owns all of HBM, a host-language binding with no device allocator, or a code path
+ * where cudaMalloc's device-wide synchronisation is not acceptable. Same arithmetic and same result as spinf_option_logprobs;
+ * the per-tile partial maxima / sums and the column table live in a fixed array inside the library image (8 MiB + 8 KiB,
+ * resident on every GPU that loads the library until the process exits) instead of a caller workspace.
+ *   - limit: 256 + 8 * ceil(vocab / 256) * (ceil(R / 128) * 128) + 4 * (ceil(vocab / 256) + 1) bytes must fit in that array
+ *     (e.g. R <= 1024 rows at vocab 262144, R <= 2048 at vocab 131072); larger calls return SPINF_ERR_TOO_LARGE and launch nothing;
+ *   - the call itself performs no cudaMalloc / cudaFree and calls no allocating routine; spinf_init is not required;
+ *   - the first call on a device resolves the array's device address (cudaGetSymbolAddress): make that first call outside any
+ *     stream capture;
+ *   - all calls on a device share the one array: the array keeps the previous call's contents, none of which is read before being
+ *     rewritten, so back-to-back calls on one stream are safe; two calls that overlap on the GPU (different streams) race;
+ *   - status: optional device pointer to one int32 the caller owns and has zeroed; a bounded wait that gives up stores its code
+ *     there (SPINF_ST_*). NULL = not reported (the code lands in a slot of the array that nothing reads back). */
+int spinf_option_logprobs_static(const void* h, const void* W, int64_t R, int64_t hidden, int64_t vocab, const int32_t* cols,
+                                 int64_t n_cols, float softcap, float* out, int32_t* status, void* stream);
+
 /* ------------------------------------------------------------------------------------------------------------ tree-mask attention
  * Host function. Replaces packer.block_tables (spinf_serve/packer.py:426-491) for text-only streams: from the per-token arrays of
  * a packed stream (art, end, pos: int32 [n], n a multiple of 128) builds, for each 128-row query block, the ascending list of

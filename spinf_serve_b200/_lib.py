@@ -26,6 +26,7 @@ SIGNATURES = {
     "spinf_bf16_gemm": (ctypes.c_int, [_p, _p, _p, _i64, _i64, _i64, _p]),
     "spinf_option_logprobs_workspace_bytes": (_i64, [_i64, _i64, _i64]),
     "spinf_option_logprobs": (ctypes.c_int, [_p, _p, _i64, _i64, _i64, _p, _i64, _f32, _p, _p, _i64, _p]),
+    "spinf_option_logprobs_static": (ctypes.c_int, [_p, _p, _i64, _i64, _i64, _p, _i64, _f32, _p, _p, _p]),
     "spinf_tile_desc_build_host": (_i64, [_p, _p, _p, _i64, _i32, _p, _p, _p]),
     "spinf_fused_norm": (ctypes.c_int, [_p, _p, _p, _p, _p, _i64, _i64, _f32, _i32, _p, _p, _p, _p, _p]),
     "spinf_qkv_norm_rope": (ctypes.c_int, [_p, _i64, _i64, _i32, _i32, _i32, _p, _p, _p, _p, _i32, _f32, _i32, _i32, _p]),

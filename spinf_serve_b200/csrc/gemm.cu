@@ -1,4 +1,6 @@
 // Launchers of the tcgen05 GEMMs: the row-wise fp8 linear, the plain bf16 linear and the fused option-log-prob read.
+#include <mutex>
+
 #include "gemm_tc.cuh"
 #include "host_util.h"
 
@@ -268,3 +270,78 @@ extern "C" int spinf_option_logprobs(const void* h, const void* W, int64_t R, in
   return 0;
 }
 
+// ------------------------------------------------------------------------------------------------ allocation-free variant
+// The option log-prob read for callers that may not allocate device memory: a serving process that has handed all of its HBM to
+// its own allocator, a host binding that cannot reach an allocator at all, or code running where cudaMalloc is off limits (it
+// synchronises the device). The per-tile partials that spinf_option_logprobs keeps in a caller-provided workspace live here in a
+// fixed array that is part of the library image: every GPU that loads the library holds these bytes until the process exits.
+static constexpr size_t STATIC_SCRATCH_BYTES = (8u << 20) + 8192;  // 2 x 1 Mi partial floats + column-tile table + status slot
+static __device__ __align__(256) unsigned char g_option_scratch[STATIC_SCRATCH_BYTES];
+
+// In host code `g_option_scratch` names a host-side shadow of the symbol, not device memory: the address a kernel can use comes
+// from cudaGetSymbolAddress, asked once per device with that device current.
+static unsigned char* option_scratch_device_ptr(int dev) {
+  static unsigned char* ptrs[64] = {nullptr};
+  static std::mutex mu;
+  if (dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lk(mu);
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_option_scratch) != cudaSuccess) return nullptr;
+    ptrs[dev] = static_cast<unsigned char*>(p);
+  }
+  return ptrs[dev];
+}
+
+extern "C" int spinf_option_logprobs_static(const void* h, const void* W, int64_t R, int64_t hidden, int64_t vocab, const int32_t* cols,
+                                            int64_t n_cols, float softcap, float* out, int32_t* status, void* stream) {
+  SPINF_CHECK_ARG(h && W && out && R >= 0 && hidden > 0 && hidden % 8 == 0 && vocab > 0 && n_cols >= 0);
+  SPINF_CHECK_ARG(n_cols == 0 || cols);
+  SPINF_CHECK_ARG(R < (1ll << 31) && vocab < (1ll << 31) && hidden < (1ll << 31) && n_cols < (1ll << 24));
+  constexpr int BN = 256;
+  const GemmShape shape = make_shape(R, vocab, hidden, BN);
+  const int64_t Mpad = static_cast<int64_t>(shape.tiles_m) * 128;
+  const int64_t partial_floats = 2 * static_cast<int64_t>(shape.tiles_n) * Mpad;
+  // layout: [0, 256) status slot | partial maxima | partial sums | column-tile table
+  const int64_t need = 256 + partial_floats * 4 + (static_cast<int64_t>(shape.tiles_n) + 1) * 4;
+  if (need > static_cast<int64_t>(STATIC_SCRATCH_BYTES)) return SPINF_ERR_TOO_LARGE;
+  if (R == 0) return 0;
+  int dev = 0;
+  SPINF_CUDA_OK(cudaGetDevice(&dev));
+  unsigned char* base = option_scratch_device_ptr(dev);  // first call on a device resolves the symbol
+  if (!base) return SPINF_ERR_CUDA;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int* status_word_p = status ? status : reinterpret_cast<int*>(base);
+  float* part_max = reinterpret_cast<float*>(base + 256);
+  float* part_sum = part_max + shape.tiles_n * Mpad;
+  int32_t* start_dev = reinterpret_cast<int32_t*>(part_sum + shape.tiles_n * Mpad);
+  // nothing in the scratch has to start at zero: every partial of every row tile and the whole column-tile table are rewritten
+  // by this call before they are read; what the previous call left behind is never read
+  col_tile_start_kernel<<<(shape.tiles_n + 1 + 255) / 256, 256, 0, st>>>(cols, static_cast<int>(n_cols), shape.tiles_n, BN, start_dev);
+  SPINF_CUDA_OK(cudaGetLastError());
+  CUtensorMap tmA, tmB;
+  int r;
+  if ((r = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, h, R, hidden, hidden * 2, 64, 128))) return r;
+  if ((r = make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, vocab, hidden, hidden * 2, 64, BN))) return r;
+  EpiLse<BN> epi;
+  epi.softcap = softcap;
+  epi.part_max = part_max;
+  epi.part_sum = part_sum;
+  epi.Mpad = static_cast<int>(Mpad);
+  epi.cols = cols;
+  epi.col_tile_start = start_dev;
+  epi.out = out;
+  epi.n_cols = static_cast<int>(n_cols);
+  GemmShape sh = shape;
+  sh.group_m = shape.tiles_m;
+  auto kern = gemm_tc_kernel<KIND_BF16, BN, EpiLse<BN>>;
+  SPINF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN>::TOTAL));
+  const int tiles = sh.tiles_m * sh.tiles_n;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kern<<<grid, 192, GemmSmem<BN>::TOTAL, st>>>(tmA, tmB, sh, epi, status_word_p);
+  SPINF_CUDA_OK(cudaGetLastError());
+  lse_finalize_kernel<<<static_cast<unsigned>((R + 127) / 128), 128, 0, st>>>(part_max, part_sum, sh.tiles_n, static_cast<int>(Mpad),
+                                                                             static_cast<int>(R), out, static_cast<int>(n_cols));
+  SPINF_CUDA_OK(cudaGetLastError());
+  return 0;
+}
