@@ -58,6 +58,21 @@ int spinf_fp8_rowwise_quant(const void* x_bf16, int64_t M, int64_t K, void* x8, 
 int spinf_fp8_rowwise_gemm(const void* x8, const float* xs, const void* w8, const float* ws, void* y_bf16, int64_t M, int64_t N,
                            int64_t K, void* stream);
 
+/* The gate|up projection of a gated MLP with the activation fused into the GEMM epilogue (the reference runs
+ * act(gate_proj(x)) * up_proj(x) as two Fp8RowLinear calls and an inductor-fused pointwise kernel: transformers' Gemma4TextMLP,
+ * called through spinf_serve/models/gemma4.py:407-415; Qwen's MLP spinf_serve/models/qwen35/qwen.py:706-716):
+ *   gate = bf16((x8 . wg)_fp32 * xs * ws_g), up likewise;  y[m,f] = bf16(bf16(act(gate[m,f])) * up[m,f]);  row_amax[m] = max_f |y[m,f]|
+ * w8_tiled [2F, K] e4m3 / ws_tiled [2F] hold the gate and up channels in TILED order: for each group of 128 features, four
+ * blocks of (32 gate rows, then the 32 up rows of the same features). y [M, F] bf16; row_amax [M] fp32 (cleared by the call).
+ * F a multiple of 128, K a multiple of 16; act 0 = gelu (tanh form), 1 = silu. Same values as spinf_fp8_rowwise_gemm followed by
+ * spinf_glu_quant. */
+int spinf_fp8_rowwise_gemm_glu(const void* x8, const float* xs, const void* w8_tiled, const float* ws_tiled, void* y, float* row_amax,
+                               int64_t M, int64_t F, int64_t K, int32_t act, void* stream);
+
+/* Row-wise fp8 quantisation (arithmetic of spinf_fp8_rowwise_quant) of y [M, K] bf16 when the row maxima are already known:
+ * xs[m] = max(row_amax[m], 1e-12) / 448, x8 = e4m3(clamp(y / xs)). One pass over y. */
+int spinf_fp8_quant_from_amax(const void* y, const float* row_amax, int64_t M, int64_t K, void* x8, float* xs, void* stream);
+
 /* Plain bf16 linear y = bf16(x @ w^T) with fp32 accumulation: x [M,K], w [N,K], y [M,N], all bf16 row-major; K, N multiples of 8.
  * Replaces the torch.nn.functional.linear / `x @ w.t()` calls on un-quantised weights (spinf_serve/models/qwen35/qwen.py:456-458
  * "extra" rows, and bf16-scheme linears). */

@@ -69,6 +69,112 @@ struct EpiLse {
   __device__ __forceinline__ void finish(State&, int) const {}
 };
 
+// ------------------------------------------------------------------------------------------------ gated-activation epilogue
+// The gate|up projection with the activation fused: the weight rows are laid out (at load time) so that every 64-column chunk
+// of an accumulator tile holds 32 gate channels followed by the 32 up channels of the same features; tile tn covers features
+// [128 tn, 128 tn + 128). Per element: gate = bf16((acc rs) cs), up likewise (the linear's own bf16 outputs), then
+// y = bf16(bf16(act(gate)) up), written as bf16 [M, F]; the row maximum of |y| is merged into row_amax with an integer atomic
+// max (non-negative floats order like their bit patterns, so the result does not depend on tile order).
+template <int BN, int ACT>
+struct EpiGlu {
+  static constexpr bool kReadsTmemInEnd = false;
+  CUtensorMap tmC;  // y [M, F] bf16, box 64 x 128, 128-byte swizzle
+  const float* rowscale;
+  const float* colscale_g;  // [2F] in the tiled channel order
+  float* row_amax;          // [M], zeroed before the launch
+  struct State {
+    uint32_t nstores;
+    float amax;
+  };
+  __device__ __forceinline__ static float act(float x) {
+    if (ACT == 0) {
+      const float inner = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+      return 0.5f * x * (1.f + tanhf(inner));
+    }
+    return x / (1.f + expf(-x));
+  }
+  __device__ __forceinline__ void begin_tile(State& st, const GemmShape& s, int tm, int tn, int et, float* colscale) const {
+    named_bar_sync(2, 128);
+    for (int i = et; i < BN; i += 128) {
+      const int n = tn * BN + i;
+      colscale[i] = n < s.N ? colscale_g[n] : 0.f;
+    }
+    named_bar_sync(2, 128);
+    st.amax = 0.f;
+  }
+  __device__ __forceinline__ void chunk(State& st, const GemmShape& s, int tm, int tn, int row, int et, int c,
+                                        const uint32_t (&v0)[32], const uint32_t (&v1)[32], const float* colscale,
+                                        uint8_t* epi_stage) const {
+    const int m = tm * 128 + row;
+    const float rs = m < s.M ? rowscale[m] : 0.f;
+    uint32_t packed[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float y[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int j = 2 * i + h;
+        const float g = __bfloat162float(__float2bfloat16_rn((__uint_as_float(v0[j]) * rs) * colscale[c * 64 + j]));
+        const float u = __bfloat162float(__float2bfloat16_rn((__uint_as_float(v1[j]) * rs) * colscale[c * 64 + 32 + j]));
+        const float a = __bfloat162float(__float2bfloat16_rn(act(g)));
+        y[h] = __bfloat162float(__float2bfloat16_rn(a * u));
+        st.amax = fmaxf(st.amax, fabsf(y[h]));
+      }
+      packed[i] = pack_bf16x2(y[0], y[1]);
+    }
+    uint8_t* buf = epi_stage + (st.nstores & 1u) * (128 * 128);
+    if ((c & 1) == 0) {
+      if (et == 0) tma_store_wait_read<1>();
+      named_bar_sync(1, 128);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      *reinterpret_cast<uint4*>(buf + sw128_offset(row, (c & 1) * 4 + j)) =
+          make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+    if (c & 1) {
+      fence_proxy_async_smem();
+      named_bar_sync(1, 128);
+      if (et == 0) {
+        tma_store_2d(&tmC, buf, tn * (BN / 2) + (c >> 1) * 64, tm * 128);
+        tma_store_commit();
+      }
+      ++st.nstores;
+    }
+  }
+  __device__ __forceinline__ void end_tile(State& st, const GemmShape& s, int tm, int, int row, int, uint32_t, const float*) const {
+    const int m = tm * 128 + row;
+    if (m < s.M) atomicMax(reinterpret_cast<unsigned int*>(row_amax + m), __float_as_uint(st.amax));
+  }
+  __device__ __forceinline__ void finish(State&, int et) const {
+    if (et == 0) tma_store_wait_all<0>();
+  }
+};
+
+// x8 = e4m3(clamp(y / s)), s = max(amax, 1e-12) / 448 with the row maxima already known: one pass over y
+__global__ void __launch_bounds__(256) fp8_quant_from_amax_kernel(const __nv_bfloat16* __restrict__ y, const float* __restrict__ row_amax,
+                                                                  int K, uint8_t* __restrict__ x8, float* __restrict__ xs) {
+  const size_t row = blockIdx.x;
+  const float s = __fdiv_rn(fmaxf(row_amax[row], 1e-12f), 448.f);
+  if (threadIdx.x == 0) xs[row] = s;
+  const uint4* src = reinterpret_cast<const uint4*>(y + row * K);
+  uint2* dst = reinterpret_cast<uint2*>(x8 + row * K);
+  for (int i = threadIdx.x; i < K / 8; i += blockDim.x) {
+    const uint4 u = src[i];
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+    uint32_t o[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const float2 a = __bfloat1622float2(p[2 * j]), b = __bfloat1622float2(p[2 * j + 1]);
+      const float q0 = fminf(fmaxf(__fdiv_rn(a.x, s), -448.f), 448.f), q1 = fminf(fmaxf(__fdiv_rn(a.y, s), -448.f), 448.f);
+      const float q2 = fminf(fmaxf(__fdiv_rn(b.x, s), -448.f), 448.f), q3 = fminf(fmaxf(__fdiv_rn(b.y, s), -448.f), 448.f);
+      const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(q0, q1), __NV_SATFINITE, __NV_E4M3);
+      const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(q2, q3), __NV_SATFINITE, __NV_E4M3);
+      o[j] = lo | (hi << 16);
+    }
+    dst[i] = make_uint2(o[0], o[1]);
+  }
+}
+
 // start[t] = index of the first option column >= t * BN (cols ascending), t = 0..tiles_n
 __global__ void col_tile_start_kernel(const int* __restrict__ cols, int n_cols, int tiles_n, int BN, int* __restrict__ start) {
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
@@ -219,6 +325,39 @@ extern "C" int spinf_bf16_gemm(const void* x, const void* w, void* y, int64_t M,
   epi.rowscale = nullptr;
   epi.colscale_g = nullptr;
   return launch_gemm<KIND_BF16, BN>(tmA, tmB, make_shape(M, N, K, BN), epi, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int spinf_fp8_rowwise_gemm_glu(const void* x8, const float* xs, const void* w8_tiled, const float* ws_tiled, void* y,
+                                          float* row_amax, int64_t M, int64_t F, int64_t K, int32_t act, void* stream) {
+  SPINF_CHECK_ARG(x8 && xs && w8_tiled && ws_tiled && y && row_amax && M >= 0 && F > 0 && K > 0 && K % 16 == 0 && F % 128 == 0);
+  SPINF_CHECK_ARG(M < (1ll << 31) && F < (1ll << 30) && K < (1ll << 31) && (act == 0 || act == 1));
+  if (M == 0) return 0;
+  constexpr int BN = 256;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  SPINF_CUDA_OK(cudaMemsetAsync(row_amax, 0, static_cast<size_t>(M) * sizeof(float), st));
+  CUtensorMap tmA, tmB, tmC;
+  int r;
+  if ((r = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x8, M, K, K, 128, 128))) return r;
+  if ((r = make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w8_tiled, 2 * F, K, K, 128, BN))) return r;
+  if ((r = make_tmap_2d(&tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y, M, F, F * 2, 64, 128))) return r;
+  const GemmShape shape = make_shape(M, 2 * F, K, BN);
+  if (act == 0) {
+    EpiGlu<BN, 0> epi;
+    epi.tmC = tmC, epi.rowscale = xs, epi.colscale_g = ws_tiled, epi.row_amax = row_amax;
+    return launch_gemm<KIND_F8, BN>(tmA, tmB, shape, epi, st);
+  }
+  EpiGlu<BN, 1> epi;
+  epi.tmC = tmC, epi.rowscale = xs, epi.colscale_g = ws_tiled, epi.row_amax = row_amax;
+  return launch_gemm<KIND_F8, BN>(tmA, tmB, shape, epi, st);
+}
+
+extern "C" int spinf_fp8_quant_from_amax(const void* y, const float* row_amax, int64_t M, int64_t K, void* x8, float* xs, void* stream) {
+  SPINF_CHECK_ARG(y && row_amax && x8 && xs && M >= 0 && K > 0 && K % 8 == 0 && M < (1ll << 31) && K < (1ll << 31));
+  if (M == 0) return 0;
+  fp8_quant_from_amax_kernel<<<static_cast<unsigned>(M), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(y), row_amax, static_cast<int>(K), static_cast<uint8_t*>(x8), xs);
+  SPINF_CUDA_OK(cudaGetLastError());
+  return 0;
 }
 
 // workspace layout: part_max [tiles_n * Mpad] f32 | part_sum [tiles_n * Mpad] f32 | col_tile_start [tiles_n + 1] i32

@@ -86,50 +86,65 @@ struct FusedNormArgs {
   int plus1;
 };
 
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 t = __bfloat1622float2(h[j]);
+    f[2 * j] = t.x;
+    f[2 * j + 1] = t.y;
+  }
+}
+
+// One CTA per row. Every global load of the row (input, residual, both weights) is issued before the first reduction, so the
+// row costs one DRAM round trip instead of one per stage.
+template <int NVEC>
 __global__ void __launch_bounds__(NORM_THREADS) fused_norm_kernel(const FusedNormArgs a) {
   __shared__ float red[NORM_THREADS / 32];
   const int64_t r = blockIdx.x;
   const int64_t rin = a.rows ? a.rows[r] : r;
   const int nvec = a.hidden / 8;
-  float x[NORM_MAX_VEC][8];
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  uint4 ry[NVEC], rr[NVEC], rw1[NVEC], rw2[NVEC];
+#pragma unroll
+  for (int i = 0; i < NVEC; ++i) {
+    const int v = threadIdx.x + i * NORM_THREADS;
+    const bool on = v < nvec;
+    ry[i] = on ? *reinterpret_cast<const uint4*>(a.y + rin * a.hidden + v * 8) : zero;
+    rr[i] = on && a.residual ? *reinterpret_cast<const uint4*>(a.residual + r * a.hidden + v * 8) : zero;
+    rw1[i] = on && a.w1 ? *reinterpret_cast<const uint4*>(a.w1 + v * 8) : zero;
+    rw2[i] = on && a.w2 ? *reinterpret_cast<const uint4*>(a.w2 + v * 8) : zero;
+  }
+  float x[NVEC][8];
   float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < NORM_MAX_VEC; ++i) {
-    const int v = threadIdx.x + i * NORM_THREADS;
-    if (v < nvec) {
-      load8(a.y + rin * a.hidden + v * 8, x[i]);
+  for (int i = 0; i < NVEC; ++i) {
+    unpack8(ry[i], x[i]);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) ss += x[i][j] * x[i][j];
-    }
+    for (int j = 0; j < 8; ++j) ss += x[i][j] * x[i][j];
   }
   if (a.w1) {
     const float inv = powf(block_sum(ss, red) / a.hidden + a.eps, -0.5f);
 #pragma unroll
-    for (int i = 0; i < NORM_MAX_VEC; ++i) {
-      const int v = threadIdx.x + i * NORM_THREADS;
-      if (v < nvec) {
-        float w[8];
-        load8(a.w1 + v * 8, w);
+    for (int i = 0; i < NVEC; ++i) {
+      float w[8];
+      unpack8(rw1[i], w);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) x[i][j] = round_bf16(x[i][j] * inv * (a.plus1 ? 1.f + w[j] : w[j]));
-      }
+      for (int j = 0; j < 8; ++j) x[i][j] = round_bf16(x[i][j] * inv * (a.plus1 ? 1.f + w[j] : w[j]));
     }
   }
   if (a.residual) {
 #pragma unroll
-    for (int i = 0; i < NORM_MAX_VEC; ++i) {
-      const int v = threadIdx.x + i * NORM_THREADS;
-      if (v < nvec) {
-        float res[8];
-        load8(a.residual + r * a.hidden + v * 8, res);
+    for (int i = 0; i < NVEC; ++i) {
+      float res[8];
+      unpack8(rr[i], res);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) x[i][j] = round_bf16(x[i][j] + res[j]);
-      }
+      for (int j = 0; j < 8; ++j) x[i][j] = round_bf16(x[i][j] + res[j]);
     }
   }
   if (a.out_h) {
 #pragma unroll
-    for (int i = 0; i < NORM_MAX_VEC; ++i) {
+    for (int i = 0; i < NVEC; ++i) {
       const int v = threadIdx.x + i * NORM_THREADS;
       if (v < nvec) store8(a.out_h + r * a.hidden + v * 8, x[i]);
     }
@@ -137,7 +152,7 @@ __global__ void __launch_bounds__(NORM_THREADS) fused_norm_kernel(const FusedNor
   if (!a.w2) return;
   ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < NORM_MAX_VEC; ++i) {
+  for (int i = 0; i < NVEC; ++i) {
     const int v = threadIdx.x + i * NORM_THREADS;
     if (v < nvec) {
 #pragma unroll
@@ -147,11 +162,11 @@ __global__ void __launch_bounds__(NORM_THREADS) fused_norm_kernel(const FusedNor
   const float inv2 = powf(block_sum(ss, red) / a.hidden + a.eps, -0.5f);
   float amax = 0.f;
 #pragma unroll
-  for (int i = 0; i < NORM_MAX_VEC; ++i) {
+  for (int i = 0; i < NVEC; ++i) {
     const int v = threadIdx.x + i * NORM_THREADS;
     if (v < nvec) {
       float w[8];
-      load8(a.w2 + v * 8, w);
+      unpack8(rw2[i], w);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         x[i][j] = round_bf16(x[i][j] * inv2 * (a.plus1 ? 1.f + w[j] : w[j]));
@@ -164,7 +179,7 @@ __global__ void __launch_bounds__(NORM_THREADS) fused_norm_kernel(const FusedNor
   const float s = __fdiv_rn(fmaxf(block_max(amax, red), 1e-12f), 448.f);
   if (threadIdx.x == 0) a.out_xs[r] = s;
 #pragma unroll
-  for (int i = 0; i < NORM_MAX_VEC; ++i) {
+  for (int i = 0; i < NVEC; ++i) {
     const int v = threadIdx.x + i * NORM_THREADS;
     if (v < nvec) *reinterpret_cast<uint2*>(a.out_x8 + r * a.hidden + v * 8) = quant8(x[i], s);
   }
@@ -173,6 +188,26 @@ __global__ void __launch_bounds__(NORM_THREADS) fused_norm_kernel(const FusedNor
 // ------------------------------------------------------------------------------------------------ q/k/v head norms + rotary
 // One warp per (token, head) of the fused projection output [n, (H + 2 Hkv) * D]; lane l holds elements [l*V, l*V + V), V = D/32,
 // whose rotary partners (offset D/2) sit in lane l ^ 16.
+template <int V>
+__device__ __forceinline__ void load_vec(const __nv_bfloat16* p, float (&f)[V]) {
+  if constexpr (V == 8) {
+    load8(p, f);
+  } else {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+    const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+    f[0] = a.x, f[1] = a.y, f[2] = b.x, f[3] = b.y;
+  }
+}
+template <int V>
+__device__ __forceinline__ void store_vec(__nv_bfloat16* p, const float (&f)[V]) {
+  if constexpr (V == 8) {
+    store8(p, f);
+  } else {
+    *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]));
+  }
+}
+
 template <int D>
 __global__ void __launch_bounds__(256) qkv_norm_rope_kernel(__nv_bfloat16* __restrict__ qkv, int64_t pitch, int64_t n, int H, int Hkv,
                                                             const __nv_bfloat16* __restrict__ wq, const __nv_bfloat16* __restrict__ wk,
@@ -188,45 +223,41 @@ __global__ void __launch_bounds__(256) qkv_norm_rope_kernel(__nv_bfloat16* __res
   const bool is_v = hd >= H + Hkv;
   if (is_v && !norm_v) return;
   __nv_bfloat16* p = qkv + t * pitch + static_cast<int64_t>(hd) * D + lane * V;
-  float x[V];
+  // rotate_half over the first R = rot_dim dimensions: out[i] = x[i] cos[i] - x[i + R/2] sin[i]  (i < R/2),
+  //                                                    out[i] = x[i] cos[i] + x[i - R/2] sin[i]  (R/2 <= i < R),
+  // cos / sin repeat with period R/2; dimensions >= R pass through. R/2 is a multiple of V, so a lane's partners sit in
+  // one other lane, `hl` lanes away, and its V cos / sin values are contiguous in the table.
+  const int half = rot_dim / 2;
+  const int hl = half / V;
+  const bool rotates = !is_v && lane < 2 * hl;
+  const bool low = lane < hl;
+  const int partner_lane = !rotates ? lane : (low ? lane + hl : lane - hl);
+  float x[V], w[V], c[V], sn[V];
+  load_vec<V>(p, x);  // all loads of the warp are issued before the first reduction
+  if (!is_v) load_vec<V>((hd < H ? wq : wk) + lane * V, w);
+  if (rotates) {
+    const int f0 = (low ? lane : lane - hl) * V;
+    load_vec<V>(cos_t + t * half + f0, c);
+    load_vec<V>(sin_t + t * half + f0, sn);
+  }
   float ss = 0.f;
 #pragma unroll
-  for (int j = 0; j < V; ++j) {
-    x[j] = __bfloat162float(p[j]);
-    ss += x[j] * x[j];
-  }
+  for (int j = 0; j < V; ++j) ss += x[j] * x[j];
   for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
   const float inv = powf(ss / D + eps, -0.5f);
-  const __nv_bfloat16* w = is_v ? nullptr : (hd < H ? wq : wk);
 #pragma unroll
   for (int j = 0; j < V; ++j) {
-    float wj = 1.f;
-    if (w) wj = plus1 ? 1.f + __bfloat162float(w[lane * V + j]) : __bfloat162float(w[lane * V + j]);
+    const float wj = is_v ? 1.f : (plus1 ? 1.f + w[j] : w[j]);
     x[j] = round_bf16(x[j] * inv * wj);
   }
   if (!is_v) {
-    // rotate_half over the first R = rot_dim dimensions: out[i] = x[i] cos[i] - x[i + R/2] sin[i]  (i < R/2),
-    //                                                    out[i] = x[i] cos[i] + x[i - R/2] sin[i]  (R/2 <= i < R),
-    // cos / sin repeat with period R/2; dimensions >= R pass through. R/2 is a multiple of V, so a lane's partners sit in
-    // one other lane, `hl` lanes away.
-    const int half = rot_dim / 2;
-    const int hl = half / V;
-    const bool rotates = lane < 2 * hl;
-    const int partner_lane = !rotates ? lane : (lane < hl ? lane + hl : lane - hl);
 #pragma unroll
     for (int j = 0; j < V; ++j) {
       const float partner = __shfl_sync(0xffffffffu, x[j], partner_lane);
-      if (rotates) {
-        const int i = lane * V + j;
-        const int f = i < half ? i : i - half;
-        const float c = __bfloat162float(cos_t[t * half + f]), s = __bfloat162float(sin_t[t * half + f]);
-        const float rot = i < half ? -partner : partner;
-        x[j] = round_bf16(round_bf16(x[j] * c) + round_bf16(rot * s));
-      }
+      if (rotates) x[j] = round_bf16(round_bf16(x[j] * c[j]) + round_bf16((low ? -partner : partner) * sn[j]));
     }
   }
-#pragma unroll
-  for (int j = 0; j < V; ++j) p[j] = __float2bfloat16_rn(x[j]);
+  store_vec<V>(p, x);
 }
 
 // ------------------------------------------------------------------------------------------------ gated activation + quantiser
@@ -328,7 +359,15 @@ extern "C" int spinf_fused_norm(const void* y, const int64_t* rows, const void* 
   a.hidden = static_cast<int>(hidden);
   a.eps = eps;
   a.plus1 = plus1;
-  fused_norm_kernel<<<static_cast<unsigned>(n_out), NORM_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  const int per_thread = static_cast<int>((hidden / 8 + NORM_THREADS - 1) / NORM_THREADS);
+  const unsigned grid = static_cast<unsigned>(n_out);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (per_thread) {
+    case 1: fused_norm_kernel<1><<<grid, NORM_THREADS, 0, st>>>(a); break;
+    case 2: fused_norm_kernel<2><<<grid, NORM_THREADS, 0, st>>>(a); break;
+    case 3: fused_norm_kernel<3><<<grid, NORM_THREADS, 0, st>>>(a); break;
+    default: fused_norm_kernel<4><<<grid, NORM_THREADS, 0, st>>>(a); break;
+  }
   SPINF_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -5,7 +5,7 @@ layer is a fixed chain of library kernels over the packed stream [n, hidden]:
     fused_norm (post-ffn norm of the previous layer + residual + input norm + fp8 quantisation)
     fp8 GEMM q|k|v (one fused projection)  ->  head norms + rotary (in place)  ->  tree attention  ->  fp8 quantisation
     fp8 GEMM o  ->  fused_norm (post-attention norm + residual + pre-ffn norm + fp8 quantisation)
-    fp8 GEMM gate|up (one fused projection)  ->  GeGLU + fp8 quantisation  ->  fp8 GEMM down
+    fp8 GEMM gate|up with GeGLU in its epilogue (+ row maxima)  ->  one-pass fp8 quantisation  ->  fp8 GEMM down
 
 Fusing q|k|v and gate|up is exact for this scheme: weight scales are per output channel and the activation scale is per token,
 so each output element is the one the separate linears give. The final norm runs on the read rows only (Scorer._forward reads
@@ -72,7 +72,10 @@ class GemmaWeights:
         out = {}
         out["qkv_w"], out["qkv_s"] = q8("q", "k", "v")
         out["o_w"], out["o_s"] = q8("o")
-        out["gu_w"], out["gu_s"] = q8("gate", "up")
+        gu_w, gu_s = q8("gate", "up")
+        order = ops.glu_tile_order(gu_w.shape[0] // 2).to(gu_w.device)  # the fused GEMM + GeGLU epilogue reads this row order
+        out["gu_w"] = gu_w.view(torch.uint8)[order].view(torch.float8_e4m3fn).contiguous()
+        out["gu_s"] = gu_s[order].contiguous()
         out["down_w"], out["down_s"] = q8("down")
         for k in ("q_norm", "k_norm", "input_ln", "post_attn_ln", "pre_ffn_ln", "post_ffn_ln"):
             out[k] = L[k].contiguous()
@@ -180,8 +183,7 @@ class GemmaStack:
             o = ops.fp8_rowwise_gemm(a8, a_s, L["o_w"], L["o_s"])
             r = ops.fused_norm(o, w1=L["post_attn_ln"], residual=h, w2=L["pre_ffn_ln"], eps=cfg.eps, want_h=True, want_fp8=True)
             h = r["h"]
-            gu = ops.fp8_rowwise_gemm(r["x8"], r["xs"], L["gu_w"], L["gu_s"])
-            g8, g_s, _ = ops.glu_quant(gu, "gelu_tanh")
+            g8, g_s, _ = ops.fp8_gemm_glu(r["x8"], r["xs"], L["gu_w"], L["gu_s"], "gelu_tanh")
             d = ops.fp8_rowwise_gemm(g8, g_s, L["down_w"], L["down_s"])
             last = i == self.n_layers - 1
             r = ops.fused_norm(

@@ -70,6 +70,49 @@ def fp8_rowwise_gemm(x8, xs, w8, ws, out=None):
     return y
 
 
+def glu_tile_order(F: int):
+    """row permutation that puts a fused gate|up weight [2F, K] (gate rows first) into the tiled order of fp8_gemm_glu: per 128
+    features, four blocks of 32 gate rows followed by the 32 up rows of the same features"""
+    if F % 128:
+        raise SpinfError("the fused gate|up GEMM needs an intermediate size that is a multiple of 128")
+    f = torch.arange(F).view(F // 32, 1, 32)
+    return torch.cat([f, f + F], dim=1).reshape(-1)
+
+
+def fp8_gemm_glu(x8, xs, w8_tiled, ws_tiled, act="gelu_tanh"):
+    """gate|up projection + gated activation + row-wise fp8 quantisation: x8 [M, K], weights in glu_tile_order ->
+    (y8 [M, F] e4m3, ys [M, 1] fp32); equals fp8_rowwise_gemm followed by glu_quant"""
+    _need(x8, FP8, "x8", 2)
+    _need(w8_tiled, FP8, "w8_tiled", 2)
+    xs1, ws1 = xs.reshape(-1), ws_tiled.reshape(-1)
+    _need(xs1, torch.float32, "xs", 1)
+    _need(ws1, torch.float32, "ws_tiled", 1)
+    M, K = x8.shape
+    F = w8_tiled.shape[0] // 2
+    if w8_tiled.shape[1] != K or xs1.numel() != M or ws1.numel() != 2 * F:
+        raise SpinfError("fp8_gemm_glu: shapes do not agree")
+    dev = x8.device
+    y = torch.empty((M, F), dtype=torch.bfloat16, device=dev)
+    amax = torch.empty((M,), dtype=torch.float32, device=dev)
+    code = {"gelu_tanh": 0, "silu": 1}[act]
+    prof = PROFILE
+    if prof is not None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+    check(
+        _lib.lib().spinf_fp8_rowwise_gemm_glu(ptr(x8), ptr(xs1), ptr(w8_tiled), ptr(ws1), ptr(y), ptr(amax), M, F, K, code, stream_ptr()),
+        "spinf_fp8_rowwise_gemm_glu",
+    )
+    if prof is not None:
+        e1.record()
+        prof.append((e0, e1, 2.0 * M * 2 * F * K))
+    y8 = torch.empty((M, F), dtype=FP8, device=dev)
+    ys = torch.empty((M, 1), dtype=torch.float32, device=dev)
+    check(_lib.lib().spinf_fp8_quant_from_amax(ptr(y), ptr(amax), M, F, ptr(y8), ptr(ys), stream_ptr()), "spinf_fp8_quant_from_amax")
+    COUNTS["launches"] += 2
+    return y8, ys, y
+
+
 def bf16_gemm(x, w):
     """y [M, N] bf16 = x [M, K] @ w [N, K]^T, fp32 accumulation"""
     _need(x, torch.bfloat16, "x", 2)

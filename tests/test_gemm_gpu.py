@@ -81,3 +81,23 @@ def test_fp8_gemm_rows_do_not_depend_on_M(dev):
         assert torch.equal(part, full[:M])
     again = ops.fp8_rowwise_gemm(x8, xs, w8, ws)
     assert torch.equal(again, full)  # run-to-run determinism
+
+
+@pytest.mark.parametrize("M,F,K,act", [(300, 1024, 512, "gelu_tanh"), (130, 15360, 3840, "gelu_tanh"), (64, 256, 128, "silu")])
+def test_fused_glu_gemm_equals_the_unfused_chain(dev, M, F, K, act):
+    """gate|up GEMM with the gated activation in its epilogue == row-wise GEMM followed by the activation kernel, bit for bit
+    (same rounding chain), and both quantised forms agree with the oracle's quantiser applied to the kernel's bf16 output"""
+    from spinf_serve_b200 import ops
+
+    x = _rand((M, K), 8)
+    w8, ws = O.quantize_weight_rowwise(_rand((2 * F, K), 9, 0.02))
+    x8, xs = O.quant_act_row(x)
+    x8, xs, w8, ws = x8.to(dev), xs.to(dev), w8.to(dev), ws.to(dev).reshape(-1)
+    gu = ops.fp8_rowwise_gemm(x8, xs, w8, ws)
+    u8, us, y_ref = ops.glu_quant(gu, act, want_fp8=True, want_y=True)
+    order = ops.glu_tile_order(F).to(dev)
+    f8, fs, y = ops.fp8_gemm_glu(x8, xs, w8.view(torch.uint8)[order].view(torch.float8_e4m3fn).contiguous(), ws[order].contiguous(), act)
+    assert torch.equal(y, y_ref)
+    assert torch.equal(fs, us) and torch.equal(f8.view(torch.uint8), u8.view(torch.uint8))
+    k8, ks = O.quant_act_row(y.cpu())
+    assert torch.equal(fs.cpu(), ks) and torch.equal(f8.cpu().view(torch.uint8), k8.view(torch.uint8))
