@@ -113,7 +113,8 @@ int spinf_option_logprobs_static(const void* h, const void* W, int64_t R, int64_
 /* ------------------------------------------------------------------------------------------------------------ tree-mask attention
  * Host function. Replaces packer.block_tables (spinf_serve/packer.py:426-491) for text-only streams: from the per-token arrays of
  * a packed stream (art, end, pos: int32 [n], n a multiple of 128) builds, for each 128-row query block, the ascending list of
- * 128-column key blocks it must visit and a flag per entry (1 = every pair attends, the mask need not be evaluated).
+ * 128-column key blocks it must visit and a flag byte per entry: bit 0 = "full" in the reference's classification (every pair
+ * attends; never set on the sliding table), bit 1 = the kernel may skip the mask evaluation (every pair attends, window included).
  *   counts_host [nb], blocks_host [nb*nb] (row i holds counts[i] entries), flags_host [nb*nb] (uint8).
  * window <= 0: full-attention table; window > 0: sliding table (no "full" flags, blocks wholly outside the window skipped).
  * Returns the total number of visited blocks, or a negative error. */

@@ -1,23 +1,27 @@
 // Tree-mask attention over one packed stream (prefill), tcgen05 + TMEM + TMA, for sm_100a.
 //
 // One CTA = one 128-row query block of one query head. It walks the block's tile list (built on the host from the packing
-// metadata) in ascending key order, 64 keys at a time:
-//   warp 0    one lane: TMA loads of Q (once) and of the K / V sub-tiles into a 2-deep ring
+// metadata, copied to shared memory at start) in ascending key order, 64 keys at a time:
+//   warp 0    one lane: TMA loads of Q (once) and of the K sub-tiles into a 2-deep ring, released as soon as S = Q K^T has read them
+//   warp 6    one lane: TMA loads of the V sub-tiles into their own 2-deep ring, released when O += P V has read them
 //   warp 1    allocates tensor memory; one lane issues  S = Q K^T  (M=128, N=64, K=D)  into one of two S buffers and
 //             O += P V  (M=128, N=D, K=64)  into the O accumulator; S of sub-tile t+1 is issued before P V of sub-tile t, so the
 //             tensor core works on the next scores while the softmax warps work on the current ones
-//   warps 2-5 thread = query row: reads S from TMEM, applies scale and the tree mask, keeps the running maximum and sum in
-//             fp32, writes P (bf16) into a swizzled shared tile, rescales O in TMEM by exp2(m_old - m_new), and at the end
-//             divides by the sum and stores bf16
+//   warps 2-5 thread = query row: reads S from TMEM, applies scale and the tree mask, keeps the running reference maximum and
+//             the sum in fp32, writes P (bf16) into a swizzled shared tile, and at the end divides O by the sum and stores bf16.
+//             O is rescaled in TMEM only when a row's maximum grew by more than 2^8 since its reference maximum was last moved
+//             (probabilities then stay below 256, exact in the final division); the decision depends on the row's own scores only.
 // Numerics follow the reference's attention (bf16 Q/K/V, fp32 scores and softmax state, P rounded to bf16 before P V, fp32
 // accumulation). Reduction order per row = ascending 64-key sub-tiles of the row's own job, independent of what else is packed
-// in the stream; "full" tiles only skip the mask evaluation, never change the arithmetic.
+// in the stream; tiles flagged "no mask" only skip the mask evaluation, never change the arithmetic.
 #include "common.cuh"
 #include "host_util.h"
 
 namespace spinf {
 
-static constexpr int KT = 64;  // keys per sub-tile
+static constexpr int KT = 64;          // keys per sub-tile
+static constexpr int LIST_CAP = 512;   // tile-list entries kept in shared memory (longer lists read the rest from global)
+static constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
 
 template <int D>
 struct AttnSmem {
@@ -29,9 +33,10 @@ struct AttnSmem {
   static constexpr int V_OFF = K_OFF + 2 * KV_TILE;
   static constexpr int P_OFF = V_OFF + 2 * KV_TILE;
   static constexpr int BAR_OFF = P_OFF + P_BYTES;
-  static constexpr int META_OFF = BAR_OFF + 128;    // key metadata: 2 buffers x 3 arrays x 64 ints
-  static constexpr int TOTAL = META_OFF + 2 * 3 * KT * 4 + 1024;
-  static constexpr int TMEM_COLS = D == 256 ? 512 : 256;  // 2 x 64 (S) + D (O), rounded up to a power of two
+  static constexpr int LIST_OFF = BAR_OFF + 128;            // LIST_CAP ints + LIST_CAP bytes
+  static constexpr int META_OFF = LIST_OFF + LIST_CAP * 5;  // per softmax warp: 2 buffers x 3 arrays x 64 ints
+  static constexpr int TOTAL = META_OFF + 4 * 2 * 3 * KT * 4 + 1024;
+  static constexpr int TMEM_COLS = D == 256 ? 512 : 256;    // 2 x 64 (S) + D (O), rounded up to a power of two
   static constexpr int O_COL = 128;
 };
 
@@ -43,14 +48,14 @@ struct AttnArgs {
   const int32_t* pos;
   const int32_t* tile_offsets;
   const int32_t* tile_blocks;
-  const uint8_t* tile_flags;
-  int nb, H, group;  // group = H / Hkv
+  const uint8_t* tile_flags;  // bit 0: every pair attends under the tree rule; bit 1: no mask evaluation needed (window included)
+  int nb, H, group;           // group = H / Hkv
   int window;
   float scale_log2;
 };
 
 template <int D>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(224, 1)
 tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const AttnArgs a, int* __restrict__ status) {
   using L = AttnSmem<D>;
@@ -61,28 +66,35 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
-  uint64_t* q_full = bars;        // 1
-  uint64_t* k_full = bars + 1;    // 2
-  uint64_t* v_full = bars + 3;    // 2
-  uint64_t* kv_empty = bars + 5;  // 2
-  uint64_t* s_full = bars + 7;    // 2
-  uint64_t* p_ready = bars + 9;   // 1 (128 arrivals)
-  uint64_t* o_done = bars + 10;   // 1
-  uint32_t* tmem_base_p = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* q_full = bars;         // 1
+  uint64_t* k_full = bars + 1;     // 2
+  uint64_t* v_full = bars + 3;     // 2
+  uint64_t* k_empty = bars + 5;    // 2
+  uint64_t* v_empty = bars + 7;    // 2
+  uint64_t* s_full = bars + 9;     // 2
+  uint64_t* p_ready = bars + 11;   // 1 (128 arrivals)
+  uint64_t* o_done = bars + 12;    // 1
+  uint32_t* tmem_base_p = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_p + 1);
+  int* list_blocks = reinterpret_cast<int*>(smem + L::LIST_OFF);
+  uint8_t* list_flags = smem + L::LIST_OFF + LIST_CAP * 4;
   int* meta = reinterpret_cast<int*>(smem + L::META_OFF);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qb = blockIdx.x, h = blockIdx.y;
   const int g = h / a.group;
   const WaitCtx wc{abort_flag, status};
+  const int e0 = a.tile_offsets[qb];
+  const int n_tiles = a.tile_offsets[qb + 1] - e0;
+  const int n_sub = 2 * n_tiles;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&v_full[i], 1);
-      mbar_init(&kv_empty[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
     }
     mbar_init(p_ready, 128);
@@ -97,42 +109,50 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     tmem_alloc(tmem_base_p, L::TMEM_COLS);
     tmem_relinquish();
   }
+  for (int i = threadIdx.x; i < n_tiles && i < LIST_CAP; i += blockDim.x) {
+    list_blocks[i] = a.tile_blocks[e0 + i];
+    list_flags[i] = a.tile_flags[e0 + i];
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_p;
+  auto block_of = [&](int tile) { return tile < LIST_CAP ? list_blocks[tile] : a.tile_blocks[e0 + tile]; };
+  auto flags_of = [&](int tile) { return tile < LIST_CAP ? list_flags[tile] : a.tile_flags[e0 + tile]; };
 
-  const int e0 = a.tile_offsets[qb];
-  const int n_sub = 2 * (a.tile_offsets[qb + 1] - e0);
-
-  if (warp == 0) {
+  if (warp == 0 || warp == 6) {
+    // K producer (warp 0, also loads Q) and V producer (warp 6): one lane each
     if (lane == 0 && n_sub > 0) {
-      mbar_expect_tx(q_full, L::Q_BYTES);
-      for (int s = 0; s < SLABS; ++s) tma_load_2d(smem + s * 128 * 128, &tmQ, h * D + s * 64, qb * 128, q_full);
+      const bool is_k = warp == 0;
+      uint64_t* full = is_k ? k_full : v_full;
+      uint64_t* empty = is_k ? k_empty : v_empty;
+      const CUtensorMap* tm = is_k ? &tmK : &tmV;
+      const int base = is_k ? L::K_OFF : L::V_OFF;
+      if (is_k) {
+        mbar_expect_tx(q_full, L::Q_BYTES);
+        for (int s = 0; s < SLABS; ++s) tma_load_2d(smem + s * 128 * 128, &tmQ, h * D + s * 64, qb * 128, q_full);
+      }
       int issued = 0;
       for (int t = 0; t < n_sub; ++t, ++issued) {
         const int st = t & 1;
         const uint32_t ph = (t >> 1) & 1u;
-        const int j = a.tile_blocks[e0 + (t >> 1)];
+        const int j = block_of(t >> 1);
         if (j < 0 || j >= a.nb) {
           *abort_flag = 1;
           atomicCAS(status, 0, ST_BAD_INDEX);
           break;
         }
-        if (!mbar_wait(wc, &kv_empty[st], ph ^ 1u, ST_TIMEOUT_EMPTY)) break;
+        if (!mbar_wait(wc, &empty[st], ph ^ 1u, ST_TIMEOUT_EMPTY)) break;
         const int kv0 = j * 128 + (t & 1) * KT;
-        mbar_expect_tx(&k_full[st], L::KV_TILE);
-        for (int s = 0; s < SLABS; ++s) tma_load_2d(smem + L::K_OFF + st * L::KV_TILE + s * KT * 128, &tmK, g * D + s * 64, kv0, &k_full[st]);
-        mbar_expect_tx(&v_full[st], L::KV_TILE);
-        for (int s = 0; s < SLABS; ++s) tma_load_2d(smem + L::V_OFF + st * L::KV_TILE + s * KT * 128, &tmV, g * D + s * 64, kv0, &v_full[st]);
+        mbar_expect_tx(&full[st], L::KV_TILE);
+        for (int s = 0; s < SLABS; ++s) tma_load_2d(smem + base + st * L::KV_TILE + s * KT * 128, tm, g * D + s * 64, kv0, &full[st]);
       }
       if (*abort_flag) {
         // bounded wait for copies of this CTA that may still be in flight
-        for (int spin = 0; spin < 4096 && !mbar_try_wait(q_full, 0); ++spin) {}
-        for (int t = issued > 2 ? issued - 2 : 0; t < issued; ++t) {
-          for (int spin = 0; spin < 4096 && !mbar_try_wait(&k_full[t & 1], (t >> 1) & 1u); ++spin) {}
-          for (int spin = 0; spin < 4096 && !mbar_try_wait(&v_full[t & 1], (t >> 1) & 1u); ++spin) {}
-        }
+        if (is_k)
+          for (int spin = 0; spin < 4096 && !mbar_try_wait(q_full, 0); ++spin) {}
+        for (int t = issued > 2 ? issued - 2 : 0; t < issued; ++t)
+          for (int spin = 0; spin < 4096 && !mbar_try_wait(&full[t & 1], (t >> 1) & 1u); ++spin) {}
       }
     }
   } else if (warp == 1) {
@@ -150,6 +170,7 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
           for (int k = 0; k < 4; ++k) umma_f16_ss(d_tmem, ad + 2 * k, bd + 2 * k, IDESC_S, (s | k) != 0);
         }
+        umma_commit(&k_empty[st]);       // the K stage may be refilled as soon as these MMAs have read it
         umma_commit(&s_full[t & 1]);
       };
       bool ok = mbar_wait(wc, q_full, 0, ST_TIMEOUT_FULL);
@@ -162,6 +183,7 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const int st = t & 1;
         const uint32_t ph = (t >> 1) & 1u;
         if (t + 1 < n_sub) {
+          // S buffer (t+1)&1 was last read by the softmax of sub-tile t-1, which arrived on p_ready before P V (t-1) was issued
           if (!mbar_wait(wc, &k_full[(t + 1) & 1], ((t + 1) >> 1) & 1u, ST_TIMEOUT_FULL)) break;
           tc_fence_after();
           issue_s(t + 1);
@@ -177,40 +199,54 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
         for (int k = 0; k < 4; ++k)  // 16 keys per step: 32 bytes along P's rows, 16 rows (2048 bytes) down V
           umma_f16_ss(tmem_base + L::O_COL, pd + 2 * k, vd + 128 * k, IDESC_O, (t | k) != 0);
-        umma_commit(&kv_empty[st]);
+        umma_commit(&v_empty[st]);
         umma_commit(o_done);
       }
     }
   } else if (n_sub > 0) {
-    const int et = threadIdx.x - 64;
     const int q = warp & 3;
     const int row = q * 32 + lane;
     const int tq = qb * 128 + row;  // stream position of this thread's query row
     const int art_q = a.art[tq], pos_q = a.pos[tq];
     const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
     uint8_t* p_smem = smem + L::P_OFF;
-    float m_run = -INFINITY, l_run = 0.f;
+    int* wmeta = meta + (warp - 2) * 2 * 3 * KT;  // this warp's private copies of the key metadata
+    float m_ref = -INFINITY, l_run = 0.f;
     bool alive = true;
 
-    for (int t = 0; t < n_sub; ++t) {
-      const int e = e0 + (t >> 1);
-      const int j = a.tile_blocks[e];
-      const bool full_tile = a.tile_flags[e] != 0;
-      const int kv0 = j * 128 + (t & 1) * KT;
-      int* kart = meta + (t & 1) * 3 * KT;
-      int* kend = kart + KT;
-      int* kpos = kend + KT;
-      const bool j_ok = j >= 0 && j < a.nb;
-      if (!full_tile && j_ok && et < KT) {
-        kart[et] = a.art[kv0 + et];
-        kend[et] = a.end[kv0 + et];
-        kpos[et] = a.pos[kv0 + et];
+    // key metadata of sub-tile t (art, end, pos of its 64 keys): each lane fetches 2 keys one iteration ahead
+    int pre[6] = {0, 0, 0, 0, 0, 0};
+    auto fetch_meta = [&](int t) {
+      const int j = block_of(t >> 1);
+      if (!(flags_of(t >> 1) & 2) && j >= 0 && j < a.nb) {
+        const int kv0 = j * 128 + (t & 1) * KT;
+        pre[0] = a.art[kv0 + lane], pre[1] = a.art[kv0 + 32 + lane];
+        pre[2] = a.end[kv0 + lane], pre[3] = a.end[kv0 + 32 + lane];
+        pre[4] = a.pos[kv0 + lane], pre[5] = a.pos[kv0 + 32 + lane];
       }
-      bool got = j_ok && mbar_wait(wc, &s_full[t & 1], (t >> 1) & 1u, ST_TIMEOUT_TMEM);
-      if (!bar_red_and(1, 128, got)) { alive = false; break; }  // also publishes the key metadata to all 128 threads
+    };
+    auto stash_meta = [&](int t) {
+      int* mb = wmeta + (t & 1) * 3 * KT;
+      mb[lane] = pre[0], mb[32 + lane] = pre[1];
+      mb[KT + lane] = pre[2], mb[KT + 32 + lane] = pre[3];
+      mb[2 * KT + lane] = pre[4], mb[2 * KT + 32 + lane] = pre[5];
+    };
+    fetch_meta(0);
+    stash_meta(0);
+    __syncwarp();
+
+    for (int t = 0; t < n_sub; ++t) {
+      const int j = block_of(t >> 1);
+      const bool no_mask = (flags_of(t >> 1) & 2) != 0;
+      const int kv0 = j * 128 + (t & 1) * KT;
+      const int* kart = wmeta + (t & 1) * 3 * KT;
+      const int* kend = kart + KT;
+      const int* kpos = kend + KT;
+      if (t + 1 < n_sub) fetch_meta(t + 1);  // in flight while this sub-tile is processed
+      bool got = j >= 0 && j < a.nb && mbar_wait(wc, &s_full[t & 1], (t >> 1) & 1u, ST_TIMEOUT_TMEM);
+      if (!__all_sync(0xffffffffu, got)) { alive = false; break; }
       tc_fence_after();
       uint32_t v0[32], v1[32];
-      __syncwarp();
       tmem_ld_x32(tmem_base + lane_off + (t & 1) * KT, v0);
       tmem_ld_x32(tmem_base + lane_off + (t & 1) * KT + 32, v1);
       tmem_wait_ld();
@@ -220,7 +256,7 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         s[i] = __uint_as_float(v0[i]) * a.scale_log2;
         s[32 + i] = __uint_as_float(v1[i]) * a.scale_log2;
       }
-      if (!full_tile) {
+      if (!no_mask) {
 #pragma unroll
         for (int i = 0; i < KT; ++i) {
           const int tk = kv0 + i;
@@ -233,23 +269,26 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       float mx = s[0];
 #pragma unroll
       for (int i = 1; i < KT; ++i) mx = fmaxf(mx, s[i]);
-      const float m_new = fmaxf(m_run, mx);
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = exp2f(m_run - m_use);
+      // move the reference maximum only when the row's maximum has grown by more than the threshold
+      float alpha = 1.f;
+      if (mx - m_ref > RESCALE_THRESHOLD) {  // false for NaN (-inf minus -inf): a row that has seen nothing yet
+        alpha = fast_exp2(m_ref - mx);
+        m_ref = mx;
+      }
+      const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
       float sum = 0.f;
       uint32_t pk[KT / 2];
 #pragma unroll
       for (int i = 0; i < KT / 2; ++i) {
-        const float p0 = exp2f(s[2 * i] - m_use), p1 = exp2f(s[2 * i + 1] - m_use);
+        const float p0 = fast_exp2(s[2 * i] - m_use), p1 = fast_exp2(s[2 * i + 1] - m_use);
         sum += p0 + p1;
         pk[i] = pack_bf16x2(p0, p1);
       }
       l_run = l_run * alpha + sum;
-      m_run = m_new;
       if (t > 0) {
         // P V of the previous sub-tile has completed: the P tile may be overwritten and O is stable
         got = mbar_wait(wc, o_done, (t - 1) & 1u, ST_TIMEOUT_TMEM);
-        if (!bar_red_and(1, 128, got)) { alive = false; break; }
+        if (!__all_sync(0xffffffffu, got)) { alive = false; break; }
         tc_fence_after();
       }
 #pragma unroll
@@ -270,18 +309,21 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(p_ready);
+      if (t + 1 < n_sub) {
+        stash_meta(t + 1);  // buffer (t+1)&1 was last read in iteration t-1 by this warp only
+        __syncwarp();
+      }
     }
 
     if (alive) {
       const bool got = mbar_wait(wc, o_done, (n_sub - 1) & 1u, ST_TIMEOUT_TMEM);
-      if (bar_red_and(1, 128, got)) {
+      if (__all_sync(0xffffffffu, got)) {
         tc_fence_after();
         const float inv = 1.f / l_run;  // every row sees at least itself, so l_run > 0
         __nv_bfloat16* dst = a.out + static_cast<int64_t>(tq) * a.out_pitch + h * D;
 #pragma unroll 1
         for (int c = 0; c < D / 32; ++c) {
           uint32_t o[32];
-          __syncwarp();
           tmem_ld_x32(tmem_base + lane_off + L::O_COL + c * 32, o);
           tmem_wait_ld();
           uint32_t w[16];
@@ -324,7 +366,7 @@ static int launch_attn(const void* q, const void* k, const void* v, int64_t n, i
     attr_set[dev] = true;
   }
   dim3 grid(static_cast<unsigned>(n / 128), static_cast<unsigned>(H));
-  kern<<<grid, 192, L::TOTAL, stream>>>(tmQ, tmK, tmV, args, status);
+  kern<<<grid, 224, L::TOTAL, stream>>>(tmQ, tmK, tmV, args, status);
   SPINF_CUDA_OK(cudaGetLastError());
   return 0;
 }

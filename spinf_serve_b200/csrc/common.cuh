@@ -69,14 +69,30 @@ struct WaitCtx {
   int* status;               // global memory
 };
 
+// try_wait with a suspend-time hint: the thread may sleep in hardware for up to `hint_ns` before the instruction returns
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\tmbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait. The common case (already complete, or complete within a few polls) touches no timer; after that the wall
+// clock is read once per 1024 polls, so a wait that cannot complete gives up after WAIT_LIMIT_NS whatever a poll costs.
 __device__ __forceinline__ bool mbar_wait(const WaitCtx& w, uint64_t* bar, uint32_t parity, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
-  for (uint32_t i = 0;; ++i) {
+  for (int i = 0; i < 64; ++i)
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 63u) == 63u) {
+  uint64_t t0 = 0;
+  for (uint32_t i = 0;; ++i) {
+    if (mbar_try_wait_hint(bar, parity, 2000u)) return true;
+    if ((i & 1023u) == 0u) {
       if (*w.abort_flag) return false;
-      if (global_timer_ns() - t0 > WAIT_LIMIT_NS) break;
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > WAIT_LIMIT_NS) break;
     }
   }
   *w.abort_flag = 1;
@@ -232,6 +248,11 @@ __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ---------------------------------------------------------------- misc math
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);

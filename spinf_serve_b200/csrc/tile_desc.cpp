@@ -5,6 +5,8 @@
 //            or the blocks share no job; or every key subtree of block j ends at or before block i's first row
 //   full     j < i, both blocks lie inside one job and hold no pad, every key's subtree covers all of block i (not for sliding)
 //   partial  everything else that is visited (the diagonal always is)
+// flags: bit 0 = full (the reference's classification), bit 1 = the kernel may skip the mask evaluation (equal to bit 0 on the
+// full-attention table; on the sliding table also set for tree-full tiles that lie wholly inside the window).
 // The visited blocks of a query block are emitted in ascending order; that order is the kernel's reduction order.
 #include <algorithm>
 #include <climits>
@@ -59,7 +61,7 @@ extern "C" int64_t spinf_tile_desc_build_host(const int32_t* art, const int32_t*
     int32_t cnt = 0;
     for (int64_t j = 0; j <= i; ++j) {
       const BlockInfo& kj = info[j];
-      bool visit = false, full = false;
+      bool visit = false, full = false, no_mask = false;
       if (j == i) {
         visit = true;
       } else {
@@ -67,16 +69,20 @@ extern "C" int64_t spinf_tile_desc_build_host(const int32_t* art, const int32_t*
         const bool out_of_window = windowed && both_real && qi.min_pos - kj.max_pos >= window;
         if (!out_of_window && both_real) {
           const bool one_j = kj.arts.size() == 1 && !kj.has_pad;
-          if (!windowed && one_i && one_j && qi.arts[0] == kj.arts[0] && kj.min_end >= (i + 1) * SPINF_BLOCK) {
-            visit = full = true;
+          const bool tree_full = one_i && one_j && qi.arts[0] == kj.arts[0] && kj.min_end >= (i + 1) * SPINF_BLOCK;
+          if (!windowed && tree_full) {
+            visit = full = no_mask = true;
           } else if (share_job(qi, kj) && kj.max_end > i * SPINF_BLOCK) {
             visit = true;
+            // sliding table: the tile stays "partial" for the reference's table format, but when every pair attends under
+            // the tree rule and every pair lies inside the window the kernel need not evaluate the mask
+            no_mask = windowed && tree_full && qi.max_pos - kj.min_pos < window;
           }
         }
       }
       if (visit) {
         blocks[i * nb + cnt] = static_cast<int32_t>(j);
-        flags[i * nb + cnt] = full ? 1 : 0;
+        flags[i * nb + cnt] = static_cast<uint8_t>((full ? 1 : 0) | (no_mask ? 2 : 0));
         ++cnt;
       }
     }

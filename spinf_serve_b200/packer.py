@@ -409,7 +409,7 @@ class Packer:
 @dataclass
 class TileDesc:
     """tiles the attention kernel visits: for query block i, key blocks blocks[offsets[i]:offsets[i+1]] in ascending order;
-    flags = 1 where every pair attends (no mask evaluation needed). n_causal = nb (nb + 1) / 2, for the skipped fraction."""
+    flags bit 0 = "full" as the reference classifies tiles, bit 1 = the kernel may skip the mask evaluation. n_causal = nb (nb + 1) / 2, for the skipped fraction."""
 
     offsets: np.ndarray  # int32 [nb + 1]
     blocks: np.ndarray   # int32 [visited]
@@ -475,7 +475,7 @@ def _tables(td: TileDesc):
     for i in range(nb):
         sl = slice(td.offsets[i], td.offsets[i + 1])
         b, f = td.blocks[sl], td.flags[sl]
-        p, q = b[f == 0], b[f != 0]
+        p, q = b[(f & 1) == 0], b[(f & 1) != 0]
         pn[i], fn[i] = len(p), len(q)
         pi[i, : len(p)] = p
         fi[i, : len(q)] = q
