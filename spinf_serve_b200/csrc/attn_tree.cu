@@ -257,13 +257,25 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         s[32 + i] = __uint_as_float(v1[i]) * a.scale_log2;
       }
       if (!no_mask) {
+        // branch-free: every operand is loaded unconditionally (vector loads of the warp's metadata copy), the rule is a chain
+        // of bitwise ANDs; short-circuit evaluation here compiles to ~200 divergent branches per sub-tile
+        const bool q_real = art_q >= 0;
+        const bool windowed = a.window > 0;
 #pragma unroll
-        for (int i = 0; i < KT; ++i) {
-          const int tk = kv0 + i;
-          bool vis = tk <= tq && art_q >= 0 && kart[i] == art_q && tq < kend[i];
-          if (a.window > 0) vis = vis && (pos_q - kpos[i] < a.window);
-          vis = vis || tk == tq;
-          if (!vis) s[i] = -INFINITY;
+        for (int i4 = 0; i4 < KT / 4; ++i4) {
+          const int4 ka = reinterpret_cast<const int4*>(kart)[i4];
+          const int4 ke = reinterpret_cast<const int4*>(kend)[i4];
+          const int4 kp = reinterpret_cast<const int4*>(kpos)[i4];
+          const int kas[4] = {ka.x, ka.y, ka.z, ka.w}, kes[4] = {ke.x, ke.y, ke.z, ke.w}, kps[4] = {kp.x, kp.y, kp.z, kp.w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int i = 4 * i4 + u;
+            const int tk = kv0 + i;
+            const bool tree = (tk <= tq) & q_real & (kas[u] == art_q) & (tq < kes[u]);
+            const bool win = !windowed | (pos_q - kps[u] < a.window);
+            const bool vis = (tree & win) | (tk == tq);
+            s[i] = vis ? s[i] : -INFINITY;
+          }
         }
       }
       float mx = s[0];
