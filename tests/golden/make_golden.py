@@ -123,6 +123,48 @@ def main(ref_root):
             rec[f"{tag}_{nm}"] = arr
     for k, v in rec.items():
         cases[f"cfg1/{k}"] = v
+    # recurrent-layer plans (qwen.tree_plan, indexed path) of some of the batches above, with several option sets
+    from spinf_serve.models.qwen35.qwen import tree_plan
+
+    plans = {}
+    plan_meta = []
+    for name in ("pack0", "pack1", "pack4", "pack5", "cfg1"):
+        keys = sorted({k.split("/")[1] for k in cases if k.startswith(name + "/b")}) if name != "cfg1" else [None]
+        for bk in keys[:2]:
+            base = f"{name}/{bk}/" if bk else f"{name}/"
+            prev, art = cases[base + "prev"], cases[base + "art"]
+            real = art >= 0
+            n_real = int(real.sum())
+            for vi, kw in enumerate(
+                [
+                    dict(),
+                    dict(short=8, call_tokens=96),
+                    dict(rows=(n_real + 127) // 128 * 128, short=16),
+                    dict(keep=[int(x) for x in np.flatnonzero(real)[:: max(1, n_real // 5)]], short=4, call_tokens=40),
+                ]
+            ):
+                pl = tree_plan(prev, real, "cpu", **kw)
+                tag = f"{base}v{vi}/"
+                plan_meta.append({"batch": base, "tag": tag, "kw": kw, "n_levels": len(pl.levels), "n_calls": [len(c) for c in pl.levels],
+                                  "kinds": [[c.kind for c in calls] for calls in pl.levels], "n_keep": pl.n_keep, "n_segments": pl.n_segments})
+                plans[tag + "conv"] = pl.conv.numpy()
+                plans[tag + "seg_of_row"] = np.asarray(pl.seg_of_row)
+                plans[tag + "seg_level"] = np.asarray(pl.seg_level)
+                plans[tag + "seg_slot"] = np.asarray(pl.seg_slot)
+                if pl.sidx is not None:
+                    plans[tag + "sidx"] = pl.sidx.numpy()
+                for li, calls in enumerate(pl.levels):
+                    for ci, c in enumerate(calls):
+                        plans[f"{tag}L{li}/C{ci}/idx"] = c.idx.numpy()
+                        plans[f"{tag}L{li}/C{ci}/cu"] = c.cu_cpu.numpy()
+                        if c.h0_idx is not None:
+                            plans[f"{tag}L{li}/C{ci}/h0"] = c.h0_idx.numpy()
+                        if c.ht_idx is not None:
+                            plans[f"{tag}L{li}/C{ci}/ht"] = c.ht_idx.numpy()
+    np.savez_compressed(os.path.join(HERE, "plan_golden.npz"), **plans)
+    with gzip.open(os.path.join(HERE, "plan_golden.json.gz"), "wt") as f:
+        json.dump(plan_meta, f)
+    print(f"{len(plans)} plan arrays, {len(plan_meta)} plans")
     np.savez_compressed(os.path.join(HERE, "packer_golden.npz"), **cases)
     with gzip.open(os.path.join(HERE, "packer_golden.json.gz"), "wt") as f:
         json.dump({"meta": meta, "structs": structs}, f)
