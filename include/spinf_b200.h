@@ -167,6 +167,36 @@ int spinf_glu_quant(const void* gu, int64_t n, int64_t F, int32_t act, void* out
 int spinf_embed_scale(const int64_t* ids, const void* emb, int64_t n, int64_t hidden, int64_t vocab, float scale, void* out,
                       void* stream);
 
+/* ------------------------------------------------------------------------------------------------------------ Gated DeltaNet
+ * Replaces gdn.recurrent and gdn.chunked (spinf_serve/models/qwen35/gdn.py:197-235 and :109-133; the per-token arithmetic is
+ * gdn.py:176-186) with their calling contract: the n_seg segments of one plan call (cu [n_seg+1] int64, token t of the call =
+ * row idx[t] of the stream tensors, or row t when idx is NULL), per segment and value head a state S [K, V] fp32 that starts
+ * from h0[h0_idx[seg]] (zero when h0 is NULL or the index is negative) and is written to ht[ht_idx[seg]] where that index is >= 0:
+ *     S *= exp(g);  v' = (v - S^T k) * beta;  S += k (x) v';  o = S^T (q * scale)
+ * q, k [rows, Hk, K] bf16 (l2-normalised by the caller), v [rows, Hv, V] bf16, g fp32 / beta bf16 [rows, Hv], each with its row
+ * pitch in elements (g and beta share g_pitch); o [rows, Hv, V] bf16 contiguous, written at the same rows; h0 / ht
+ * [*, Hv, K, V] fp32. K = V = 128. Every segment length runs through the same token-serial kernel (the reference switches to
+ * a chunked form above 64 tokens; both compute this recurrence). */
+int spinf_gdn_recurrent(const void* q, const void* k, const void* v, const float* g, const void* beta, void* o, int64_t n_rows,
+                        int64_t q_pitch, int64_t v_pitch, int64_t g_pitch, int32_t Hk, int32_t Hv, int32_t K, int32_t V, float scale,
+                        const int64_t* cu, int64_t n_seg, const int64_t* idx, const float* h0, const int64_t* h0_idx, float* ht,
+                        const int64_t* ht_idx, void* stream);
+
+/* Replaces the steps of GatedDeltaNet.forward before the recurrence (spinf_serve/models/qwen35/qwen.py:651-668), fused: for each of
+ * the T tokens, from the in-projection rows y [n_rows, y_pitch] bf16 = [q | k | v | z | b | a]: the 4-tap path convolution over
+ * conv [T, 4] int64 (a tap index >= n_rows or < 0 is the zero row) with conv_w [2 Hk K + Hv V, 4] bf16 in fp32, SiLU, rounding
+ * to bf16; q and k then l2-normalised per head (x * rsqrt(sum x^2 + 1e-6)); beta = bf16(sigmoid(b));
+ * g = -exp(A_log) * softplus(a + dt_bias) in fp32. Outputs q, k [T, Hk, K], v [T, Hv, V] bf16, g [T, Hv] fp32, beta [T, Hv] bf16. */
+int spinf_gdn_prologue(const void* y, int64_t y_pitch, int64_t n_rows, int64_t T, const int64_t* conv, const void* conv_w,
+                       const float* A_log, const float* dt_bias, int32_t Hk, int32_t Hv, int32_t K, int32_t V, void* q, void* k,
+                       void* v, float* g, void* beta, void* stream);
+
+/* Replaces the gated RMS norm after the recurrence (spinf_serve/models/qwen35/qwen.py:670-673): per token and value head
+ * of = o * rsqrt(mean(o^2) + eps); out = bf16(float(bf16(norm_w * bf16(of))) * silu(z)). o [T, Hv, V] bf16 contiguous, z rows of
+ * pitch z_pitch (a slice of the in-projection output), norm_w [V] bf16, out [T, Hv V] bf16. */
+int spinf_gdn_epilogue(const void* o, const void* z, int64_t z_pitch, const void* norm_w, float eps, int64_t T, int32_t Hv, int32_t V,
+                       void* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -35,6 +35,12 @@ SIGNATURES = {
     "spinf_rope_table": (ctypes.c_int, [_p, _i64, _i32, _p, _p, _p, _p]),
     "spinf_glu_quant": (ctypes.c_int, [_p, _i64, _i64, _i32, _p, _p, _p, _p]),
     "spinf_embed_scale": (ctypes.c_int, [_p, _p, _i64, _i64, _i64, _f32, _p, _p]),
+    "spinf_gdn_recurrent": (
+        ctypes.c_int,
+        [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _f32, _p, _i64, _p, _p, _p, _p, _p, _p],
+    ),
+    "spinf_gdn_prologue": (ctypes.c_int, [_p, _i64, _i64, _i64, _p, _p, _p, _p, _i32, _i32, _i32, _i32, _p, _p, _p, _p, _p, _p]),
+    "spinf_gdn_epilogue": (ctypes.c_int, [_p, _p, _i64, _p, _f32, _i64, _i32, _i32, _p, _p]),
     "spinf_tree_attn_fwd": (
         ctypes.c_int,
         [_p, _p, _p, _p, _i64, _i32, _i32, _i32, _i64, _i64, _i64, _p, _p, _p, _i32, _f32, _p, _p, _p, _p],
