@@ -77,6 +77,19 @@ int spinf_fp8_quant_from_amax(const void* y, const float* row_amax, int64_t M, i
  * Replaces the torch.nn.functional.linear / `x @ w.t()` calls on un-quantised weights (spinf_serve/models/qwen35/qwen.py:456-458
  * "extra" rows, and bf16-scheme linears). */
 int spinf_bf16_gemm(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, void* stream);
+/* The same with a row pitch for y (in elements, a multiple of 8): writes an [M, N] block inside a wider output, as the reference's
+ * Int4Linear appends its un-quantised "extra" output channels to the int4 ones (spinf_serve/models/qwen35/qwen.py:421-426). */
+int spinf_bf16_gemm_ld(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, int64_t y_pitch, void* stream);
+
+/* ------------------------------------------------------------------------------------------------------------ int4 weight-only linear
+ * Replaces Int4Linear.forward in bf16 mode (spinf_serve/models/qwen35/qwen.py:455-458) with its per-call dequantisation dq_bf16
+ * (qwen.py:326-330):  y[m,n] = bf16( sum_k x[m,k] * w[n,k] ),  w[n,k] = bf16( (nibble(n,k) - 8) * float(scales[n, k / group]) ).
+ * x [M,K] bf16; qw uint8 [N, K/2] in the reference's engine layout (low nibble = even k, qwen.py:383-389); scales fp16
+ * [N, K/group]; y bf16 with row pitch y_pitch elements. The bf16 weight matrix is never materialised: nibbles are expanded inside
+ * the kernel on their way to the tensor core. K a multiple of 64 and of group, group a multiple of 8 (128 in the BASELINE
+ * configuration, 32 in the reference's checkpoints), N a multiple of 8. A row of y does not depend on M. */
+int spinf_w4_gemm(const void* x, const void* qw, const void* scales, int32_t group, void* y, int64_t M, int64_t N, int64_t K,
+                  int64_t y_pitch, void* stream);
 
 /* ------------------------------------------------------------------------------------------------------------ option log-probs
  * Replaces Scorer._logprobs followed by the `[:, ci]` gather (spinf_serve/scorer.py:340-355 and :254): for read rows h [R,hidden]

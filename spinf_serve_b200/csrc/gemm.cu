@@ -311,8 +311,8 @@ extern "C" int spinf_fp8_rowwise_gemm(const void* x8, const float* xs, const voi
   return launch_gemm<KIND_F8, BN>(tmA, tmB, make_shape(M, N, K, BN), epi, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int spinf_bf16_gemm(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, void* stream) {
-  SPINF_CHECK_ARG(x && w && y && M >= 0 && N > 0 && K > 0 && K % 8 == 0 && N % 8 == 0);
+extern "C" int spinf_bf16_gemm_ld(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, int64_t y_pitch, void* stream) {
+  SPINF_CHECK_ARG(x && w && y && M >= 0 && N > 0 && K > 0 && K % 8 == 0 && N % 8 == 0 && y_pitch >= N && y_pitch % 8 == 0);
   SPINF_CHECK_ARG(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31));
   if (M == 0) return 0;
   constexpr int BN = 256;
@@ -321,10 +321,14 @@ extern "C" int spinf_bf16_gemm(const void* x, const void* w, void* y, int64_t M,
   int r;
   if ((r = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, M, K, K * 2, 64, 128))) return r;
   if ((r = make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, N, K, K * 2, 64, BN))) return r;
-  if ((r = make_tmap_2d(&epi.tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y, M, N, N * 2, 64, 128))) return r;
+  if ((r = make_tmap_2d(&epi.tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y, M, N, y_pitch * 2, 64, 128))) return r;
   epi.rowscale = nullptr;
   epi.colscale_g = nullptr;
   return launch_gemm<KIND_BF16, BN>(tmA, tmB, make_shape(M, N, K, BN), epi, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int spinf_bf16_gemm(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, void* stream) {
+  return spinf_bf16_gemm_ld(x, w, y, M, N, K, N, stream);
 }
 
 extern "C" int spinf_fp8_rowwise_gemm_glu(const void* x8, const float* xs, const void* w8_tiled, const float* ws_tiled, void* y,

@@ -32,6 +32,21 @@ int make_tmap_2d(CUtensorMap* out, CUtensorMapDataType dt, int elem_bytes, const
   return r == CUDA_SUCCESS ? 0 : SPINF_ERR_TENSORMAP;
 }
 
+int make_tmap_2d_plain(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes, uint32_t box_cols,
+                       uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return SPINF_ERR_TENSORMAP;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (pitch_bytes & 15) || (box_cols & 15) || box_cols > 256 || box_rows > 256)
+    return SPINF_ERR_TENSORMAP;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : SPINF_ERR_TENSORMAP;
+}
+
 int make_tmap_3d(CUtensorMap* out, CUtensorMapDataType dt, int elem_bytes, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
                  uint64_t s1_bytes, uint64_t s2_bytes, uint32_t b0, uint32_t b1) {
   EncodeTiledFn fn = encode_tiled_fn();

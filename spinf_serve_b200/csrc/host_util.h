@@ -21,6 +21,9 @@ EncodeTiledFn encode_tiled_fn();
 // 128-byte swizzle (box_cols * elem_bytes must be 128). Returns 0 or SPINF_ERR_TENSORMAP.
 int make_tmap_2d(CUtensorMap* out, CUtensorMapDataType dt, int elem_bytes, const void* base, uint64_t rows, uint64_t cols,
                  uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows);
+// 2-D row-major byte tensor [rows, cols] without swizzle: box = box_cols x box_rows bytes (box_cols a multiple of 16).
+int make_tmap_2d_plain(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes, uint32_t box_cols,
+                       uint32_t box_rows);
 // 3-D tensor [d2, d1, d0] (d0 innermost) with byte strides s1 (between d1 steps) and s2; box = b0 x b1 x 1, 128-byte swizzle.
 int make_tmap_3d(CUtensorMap* out, CUtensorMapDataType dt, int elem_bytes, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
                  uint64_t s1_bytes, uint64_t s2_bytes, uint32_t b0, uint32_t b1);

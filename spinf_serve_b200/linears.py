@@ -57,3 +57,40 @@ def quant_linears(opts: dict | None, device) -> SimpleNamespace:
         Int8Linear=_outside("Int8Linear"), Fp8Linear=_outside("Fp8Linear"), Fp8RowLinear=Fp8RowLinear,
         Fp8StaticLinear=_outside("Fp8StaticLinear"), prequantized=prequantized,
     )
+
+
+def gptq_unpack(qweight, scales):
+    """GPTQ v1 storage -> the engine layout, at load time with the reference's eager torch ops (Int4Linear.__init__,
+    spinf_serve/models/qwen35/qwen.py:383-391): qweight int32 [K/8, N] (8 nibbles per word, shifts 0..28) -> q uint8 [N, K/2] with the
+    low nibble = even k; scales fp16 [K/G, N] -> [N, K/G]"""
+    sh = torch.arange(0, 32, 4, dtype=torch.int32, device=qweight.device)
+    q = ((qweight[:, None, :] >> sh[None, :, None]) & 15).reshape(-1, qweight.shape[1]).t()
+    return (q[:, 0::2] | (q[:, 1::2] << 4)).to(torch.uint8).contiguous(), scales.t().contiguous()
+
+
+class Int4Linear(nn.Module):
+    """GPTQ int4 symmetric weights, bf16 activations, dequantised inside the GEMM kernel (the reference's Int4Linear in bf16 mode,
+    qwen.py:378-458): same constructor arguments, buffers q / s / extra, set_extra and forward. The group size is inferred from
+    the scales' shape (the reference reads it from the checkpoint's quantization_config, qwen.py:301)."""
+
+    def __init__(self, qweight, scales):
+        super().__init__()
+        if not qweight.is_cuda:
+            raise RuntimeError("Int4Linear needs a CUDA device with sm_100a kernels; there is no CPU path")
+        q, s = gptq_unpack(qweight, scales)
+        self.out_features, self.in_features = q.shape[0], q.shape[1] * 2
+        self.group = self.in_features // s.shape[1]
+        self.register_buffer("q", q)
+        self.register_buffer("s", s.to(torch.float16))
+        self.extra = None
+        self.name = ""
+
+    def set_extra(self, w):
+        """bf16 rows [E, in] appended to the output (the Gated DeltaNet's b / a projections)"""
+        del self.extra
+        self.register_buffer("extra", w.to(torch.bfloat16).contiguous())
+
+    def forward(self, x):
+        x2 = x.reshape(-1, x.shape[-1])
+        y = ops.w4_gemm(x2 if x2.is_contiguous() else x2.contiguous(), self.q, self.s, self.group, self.extra)
+        return y.reshape(*x.shape[:-1], y.shape[-1])

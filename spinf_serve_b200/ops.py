@@ -70,6 +70,29 @@ def fp8_rowwise_gemm(x8, xs, w8, ws, out=None):
     return y
 
 
+def w4_gemm(x, qw, scales, group, extra=None):
+    """y [M, N (+ E)] bf16 = x [M, K] bf16 @ dq(qw, scales)^T, with E un-quantised bf16 output channels `extra` [E, K] appended
+    (Int4Linear.forward in bf16 mode, spinf_serve/models/qwen35/qwen.py:455-458); qw uint8 [N, K/2], scales fp16 [N, K/group]"""
+    _need(x, torch.bfloat16, "x", 2)
+    _need(qw, torch.uint8, "qw", 2)
+    _need(scales, torch.float16, "scales", 2)
+    M, K = x.shape
+    N = qw.shape[0]
+    if qw.shape[1] * 2 != K or scales.shape != (N, K // group):
+        raise SpinfError("w4_gemm: shapes do not agree")
+    E = 0 if extra is None else extra.shape[0]
+    if extra is not None:
+        _need(extra, torch.bfloat16, "extra", 2)
+    y = torch.empty((M, N + E), dtype=torch.bfloat16, device=x.device)
+    check(_lib.lib().spinf_w4_gemm(ptr(x), ptr(qw), ptr(scales), group, ptr(y), M, N, K, N + E, stream_ptr()), "spinf_w4_gemm")
+    COUNTS["launches"] += 1
+    if E:
+        tail = ctypes.c_void_p(y.data_ptr() + 2 * N)
+        check(_lib.lib().spinf_bf16_gemm_ld(ptr(x), ptr(extra), tail, M, E, K, N + E, stream_ptr()), "spinf_bf16_gemm_ld")
+        COUNTS["launches"] += 1
+    return y
+
+
 def glu_tile_order(F: int):
     """row permutation that puts a fused gate|up weight [2F, K] (gate rows first) into the tiled order of fp8_gemm_glu: per 128
     features, four blocks of 32 gate rows followed by the 32 up rows of the same features"""
