@@ -99,18 +99,19 @@ __global__ void __launch_bounds__(128) gdn_recurrent_kernel(const GdnArgs a, int
     if (t + 1 < eos) fetch(t + 1);  // in flight while this token is computed
     const float4* kv4 = reinterpret_cast<const float4*>(kq[buf][0]);
     const float4* qv4 = reinterpret_cast<const float4*>(kq[buf][1]);
-    float dot = 0.f;
+    // four independent partial sums per reduction: a single accumulator would serialise 128 dependent FMAs per token
+    float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
     for (int i = 0; i < GK / 4; ++i) {
       const float4 kk = kv4[i];
       S[4 * i] *= eg, S[4 * i + 1] *= eg, S[4 * i + 2] *= eg, S[4 * i + 3] *= eg;
-      dot = fmaf(S[4 * i], kk.x, dot);
-      dot = fmaf(S[4 * i + 1], kk.y, dot);
-      dot = fmaf(S[4 * i + 2], kk.z, dot);
-      dot = fmaf(S[4 * i + 3], kk.w, dot);
+      d0 = fmaf(S[4 * i], kk.x, d0);
+      d1 = fmaf(S[4 * i + 1], kk.y, d1);
+      d2 = fmaf(S[4 * i + 2], kk.z, d2);
+      d3 = fmaf(S[4 * i + 3], kk.w, d3);
     }
-    const float vn = (vt - dot) * bt;
-    float od = 0.f;
+    const float vn = (vt - ((d0 + d1) + (d2 + d3))) * bt;
+    float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
     for (int i = 0; i < GK / 4; ++i) {
       const float4 kk = kv4[i];
@@ -119,11 +120,12 @@ __global__ void __launch_bounds__(128) gdn_recurrent_kernel(const GdnArgs a, int
       S[4 * i + 1] = fmaf(kk.y, vn, S[4 * i + 1]);
       S[4 * i + 2] = fmaf(kk.z, vn, S[4 * i + 2]);
       S[4 * i + 3] = fmaf(kk.w, vn, S[4 * i + 3]);
-      od = fmaf(S[4 * i], qq.x, od);
-      od = fmaf(S[4 * i + 1], qq.y, od);
-      od = fmaf(S[4 * i + 2], qq.z, od);
-      od = fmaf(S[4 * i + 3], qq.w, od);
+      o0 = fmaf(S[4 * i], qq.x, o0);
+      o1 = fmaf(S[4 * i + 1], qq.y, o1);
+      o2 = fmaf(S[4 * i + 2], qq.z, o2);
+      o3 = fmaf(S[4 * i + 3], qq.w, o3);
     }
+    const float od = (o0 + o1) + (o2 + o3);
     a.o[(r * a.Hv + hv) * GV + c] = __float2bfloat16_rn(od);
     if (t + 1 < eos) stash(buf ^ 1);  // the other buffer was last read one token ago, before the previous barrier
     __syncthreads();

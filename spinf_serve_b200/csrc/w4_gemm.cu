@@ -4,9 +4,10 @@
 // core: nothing the size of the bf16 weight matrix is ever written.
 //
 // Persistent, one CTA per SM, 256 x 128 output tiles (two M=128 accumulators share every dequantised weight tile, halving the
-// expansion work per FLOP), K in steps of 64. 10 warps:
+// expansion work per FLOP), K in steps of 64. 14 warps:
 //   warp 0     one lane: TMA loads of the activation tile (256 x 128 B, swizzled) and the raw weight tile (128 rows x 32 B) into a 4-stage ring
-//   warps 6-9  dequantisers, thread = weight row: 64 nibbles -> 64 bf16 written as a K-major 128-byte-swizzled tile into a 3-stage ring
+//   warps 6-13 dequantisers in two groups of four warps that take alternate K steps (two steps in flight), thread = weight row:
+//              64 nibbles -> 64 bf16 written as a K-major 128-byte-swizzled tile into a 4-stage ring; a nibble becomes the float 128 + n with one byte permute, then one FMA gives (n - 8) * scale exactly
 //   warp 1     one lane: tcgen05.mma, 2 x (M=128, N=128, K=64) per step, into one of two accumulator pairs
 //   warps 2-5  epilogue: TMEM -> bf16 -> swizzled staging -> TMA store, overlapped with the next tile's main loop
 // K order per output element is ascending inside one CTA and the tile shape does not depend on M: rows are batch-invariant.
@@ -16,14 +17,14 @@
 namespace spinf {
 
 struct W4Smem {
-  static constexpr int STAGES = 4, BSTAGES = 3;
+  static constexpr int STAGES = 4, BSTAGES = 4;
   static constexpr int A_BYTES = 256 * 128;   // activations: 256 rows x 64 bf16
   static constexpr int RAW_BYTES = 128 * 32;  // raw weights: 128 rows x 64 nibbles
   static constexpr int STAGE_BYTES = A_BYTES + RAW_BYTES;
   static constexpr int B_BYTES = 128 * 128;   // dequantised weights: 128 rows x 64 bf16
   static constexpr int B_OFF = STAGES * STAGE_BYTES;
   static constexpr int EPI_OFF = B_OFF + BSTAGES * B_BYTES;
-  static constexpr int BAR_OFF = EPI_OFF + 2 * 128 * 128;
+  static constexpr int BAR_OFF = EPI_OFF + 128 * 128;  // one staging tile: the epilogue has a whole main loop of slack
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
@@ -33,7 +34,7 @@ struct W4Args {
   int tiles_m, tiles_n, group_m;
 };
 
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(448, 1)
 w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmC,
                const W4Args a, int* __restrict__ status) {
   using L = W4Smem;
@@ -137,19 +138,24 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
     }
   } else if (warp >= 6) {
-    // dequantisers: thread = weight row of the tile
-    const int n_local = threadIdx.x - 192;  // 0..127
+    // dequantisers: two groups of 128 threads take alternate K steps; thread = weight row of the tile
+    const int dt = threadIdx.x - 192;   // 0..255
+    const int grp = dt >> 7;
+    const int n_local = dt & 127;
     uint32_t it = 0;
     bool ok = true;
     const int groups = a.K / a.G;
+    const bool coarse = a.G % 64 == 0;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       int tm, tn;
       tile_coords(shape, tile, tm, tn);
       const int n = tn * 128 + n_local;
-      const __half* srow = a.scales + static_cast<int64_t>(n < a.N ? n : 0) * groups;
+      const bool n_ok = n < a.N;
+      const __half* srow = a.scales + static_cast<int64_t>(n_ok ? n : 0) * groups;
       int s_idx = -1;
-      float sc = 0.f;
+      float sc = 0.f, off = 0.f;
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        if ((it & 1u) != static_cast<uint32_t>(grp)) continue;
         const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
         const uint32_t bs = it % BSTAGES, bph = (it / BSTAGES) & 1u;
         bool got = mbar_wait(wc, &full[s], ph, ST_TIMEOUT_FULL);
@@ -159,20 +165,33 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const uint4 r0 = raw[0], r1 = raw[1];
         const uint32_t words[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
         uint8_t* btile = smem + L::B_OFF + bs * L::B_BYTES;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {  // 8 nibbles -> 8 bf16 = one 16-byte chunk of the row
-          const int gi = (kb * 64 + c * 8) / a.G;
+        if (coarse) {  // one scale for the whole 64-wide K step (group a multiple of 64): one division per step
+          const int gi = (kb * 64) / a.G;
           if (gi != s_idx) {
             s_idx = gi;
-            sc = n < a.N ? __half2float(srow[gi]) : 0.f;
+            sc = n_ok ? __half2float(srow[gi]) : 0.f;
+            off = -136.f * sc;  // exact: 136 has 5 significant bits, a half-precision scale 11
           }
-          const uint32_t w = words[c];
+        }
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {  // 8 nibbles -> 8 bf16 = one 16-byte chunk of the row
+          if (!coarse) {
+            const int gi = (kb * 64 + c * 8) / a.G;
+            if (gi != s_idx) {
+              s_idx = gi;
+              sc = n_ok ? __half2float(srow[gi]) : 0.f;
+              off = -136.f * sc;
+            }
+          }
+          const uint32_t even = words[c] & 0x0F0F0F0Fu;         // nibbles 0, 2, 4, 6 (k even), one per byte
+          const uint32_t odd = (words[c] >> 4) & 0x0F0F0F0Fu;   // nibbles 1, 3, 5, 7
           uint32_t out[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            // (nibble | 2^23 as float bits) - (2^23 + 8) = nibble - 8 exactly; times the scale is exact in fp32; one rounding to bf16
-            const float lo = (__uint_as_float(0x4B000000u | ((w >> (8 * j)) & 15u)) - 8388616.f) * sc;
-            const float hi = (__uint_as_float(0x4B000000u | ((w >> (8 * j + 4)) & 15u)) - 8388616.f) * sc;
+            // bytes [0, 0, nibble, 0x43] = the float 128 + nibble; fma(128 + n, s, -136 s) = (n - 8) s with no rounding
+            // (the product and the sum are exact inside the FMA and the result fits fp32); then one rounding to bf16
+            const float lo = fmaf(__uint_as_float(__byte_perm(even, 0x43000000u, 0x7044u | (j << 8))), sc, off);
+            const float hi = fmaf(__uint_as_float(__byte_perm(odd, 0x43000000u, 0x7044u | (j << 8))), sc, off);
             out[j] = pack_bf16x2(lo, hi);
           }
           *reinterpret_cast<uint4*>(btile + sw128_offset(n_local, c)) = make_uint4(out[0], out[1], out[2], out[3]);
@@ -215,8 +234,8 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           packed[i] = pack_bf16x2(__uint_as_float(v0[2 * i]), __uint_as_float(v0[2 * i + 1]));
           packed[16 + i] = pack_bf16x2(__uint_as_float(v1[2 * i]), __uint_as_float(v1[2 * i + 1]));
         }
-        uint8_t* buf = epi_stage + (nstores & 1u) * (128 * 128);
-        if (et == 0) tma_store_wait_read<1>();
+        uint8_t* buf = epi_stage;
+        if (et == 0) tma_store_wait_read<0>();
         named_bar_sync(1, 128);
 #pragma unroll
         for (int j = 0; j < 8; ++j)
@@ -273,7 +292,7 @@ extern "C" int spinf_w4_gemm(const void* x, const void* qw, const void* scales, 
   }
   const int tiles = a.tiles_m * a.tiles_n;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  w4_gemm_kernel<<<grid, 320, W4Smem::TOTAL, static_cast<cudaStream_t>(stream)>>>(tmA, tmW, tmC, a, status);
+  w4_gemm_kernel<<<grid, 448, W4Smem::TOTAL, static_cast<cudaStream_t>(stream)>>>(tmA, tmW, tmC, a, status);
   SPINF_CUDA_OK(cudaGetLastError());
   return 0;
 }
