@@ -248,6 +248,31 @@ __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ---------------------------------------------------------------- misc math
+// Correctly rounded x / s without the general division sequence, for a divisor that is shared by many elements (a row's
+// quantisation scale): r = RN(1/s) once per row, then per element q = RN(x r) followed by two corrections q <- RN(q + (x - s q) r),
+// each residual exact in one FMA. With r the correctly rounded reciprocal, the second correction starts within an ulp of the
+// quotient and lands on the correctly rounded quotient (Markstein's theorem) unless the divisor's significand is all ones; for
+// that divisor div_by falls back to the IEEE division. Operands here
+// are far from overflow (|x / s| <= 448) and results below the smallest e4m3 subnormal round to zero either way.
+struct DivBy {
+  float s, r;
+  bool slow;
+};
+__device__ __forceinline__ DivBy make_div_by(float scale) {
+  DivBy d;
+  d.s = scale;
+  d.r = __frcp_rn(scale);
+  d.slow = (__float_as_uint(scale) & 0x7FFFFFu) == 0x7FFFFFu;
+  return d;
+}
+__device__ __forceinline__ float div_by(const DivBy& d, float x) {
+  if (d.slow) return __fdiv_rn(x, d.s);
+  float q = x * d.r;
+  q = fmaf(fmaf(-d.s, q, x), d.r, q);     // residual x - s q is exact in the FMA; q is now within an ulp of the quotient
+  q = fmaf(fmaf(-d.s, q, x), d.r, q);     // a second correction from a within-an-ulp start rounds correctly
+  return x == 0.f ? x : q;                // a zero keeps its sign (the corrections would turn -0 into +0)
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

@@ -156,6 +156,7 @@ __global__ void __launch_bounds__(256) fp8_quant_from_amax_kernel(const __nv_bfl
   const size_t row = blockIdx.x;
   const float s = __fdiv_rn(fmaxf(row_amax[row], 1e-12f), 448.f);
   if (threadIdx.x == 0) xs[row] = s;
+  const DivBy div = make_div_by(s);
   const uint4* src = reinterpret_cast<const uint4*>(y + row * K);
   uint2* dst = reinterpret_cast<uint2*>(x8 + row * K);
   for (int i = threadIdx.x; i < K / 8; i += blockDim.x) {
@@ -165,8 +166,8 @@ __global__ void __launch_bounds__(256) fp8_quant_from_amax_kernel(const __nv_bfl
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       const float2 a = __bfloat1622float2(p[2 * j]), b = __bfloat1622float2(p[2 * j + 1]);
-      const float q0 = fminf(fmaxf(__fdiv_rn(a.x, s), -448.f), 448.f), q1 = fminf(fmaxf(__fdiv_rn(a.y, s), -448.f), 448.f);
-      const float q2 = fminf(fmaxf(__fdiv_rn(b.x, s), -448.f), 448.f), q3 = fminf(fmaxf(__fdiv_rn(b.y, s), -448.f), 448.f);
+      const float q0 = fminf(fmaxf(div_by(div, a.x), -448.f), 448.f), q1 = fminf(fmaxf(div_by(div, a.y), -448.f), 448.f);
+      const float q2 = fminf(fmaxf(div_by(div, b.x), -448.f), 448.f), q3 = fminf(fmaxf(div_by(div, b.y), -448.f), 448.f);
       const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(q0, q1), __NV_SATFINITE, __NV_E4M3);
       const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(q2, q3), __NV_SATFINITE, __NV_E4M3);
       o[j] = lo | (hi << 16);
@@ -232,6 +233,7 @@ __global__ void __launch_bounds__(256) fp8_rowwise_quant_kernel(const __nv_bfloa
   for (int w = 1; w < 8; ++w) amax = fmaxf(amax, red[w]);
   const float s = __fdiv_rn(fmaxf(amax, 1e-12f), 448.f);
   if (threadIdx.x == 0) xs[row] = s;
+  const DivBy div = make_div_by(s);
   uint2* dst = reinterpret_cast<uint2*>(x8 + row * K);
   for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
     uint4 u = src[i];
@@ -240,8 +242,8 @@ __global__ void __launch_bounds__(256) fp8_rowwise_quant_kernel(const __nv_bfloa
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       float2 a = __bfloat1622float2(p[2 * j]), b = __bfloat1622float2(p[2 * j + 1]);
-      const float q0 = fminf(fmaxf(__fdiv_rn(a.x, s), -448.f), 448.f), q1 = fminf(fmaxf(__fdiv_rn(a.y, s), -448.f), 448.f);
-      const float q2 = fminf(fmaxf(__fdiv_rn(b.x, s), -448.f), 448.f), q3 = fminf(fmaxf(__fdiv_rn(b.y, s), -448.f), 448.f);
+      const float q0 = fminf(fmaxf(div_by(div, a.x), -448.f), 448.f), q1 = fminf(fmaxf(div_by(div, a.y), -448.f), 448.f);
+      const float q2 = fminf(fmaxf(div_by(div, b.x), -448.f), 448.f), q3 = fminf(fmaxf(div_by(div, b.y), -448.f), 448.f);
       const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(q0, q1), __NV_SATFINITE, __NV_E4M3);
       const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(q2, q3), __NV_SATFINITE, __NV_E4M3);
       o[j] = lo | (hi << 16);

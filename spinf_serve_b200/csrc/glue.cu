@@ -54,14 +54,19 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
   u.w = pack_bf16x2(f[6], f[7]);
   *reinterpret_cast<uint4*>(p) = u;
 }
+// x^-1/2 to within an ulp: hardware estimate plus one Newton step (the model code's pow(x, -0.5) costs ~10x the instructions)
+__device__ __forceinline__ float inv_sqrt(float x) {
+  const float y = rsqrtf(x);
+  return y * fmaf(-0.5f * x * y, y, 1.5f);
+}
 __device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
-__device__ __forceinline__ uint2 quant8(const float (&f)[8], float s) {
+__device__ __forceinline__ uint2 quant8(const float (&f)[8], const DivBy& div) {
   uint32_t o[2];
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
-    const float q0 = fminf(fmaxf(__fdiv_rn(f[4 * j], s), -448.f), 448.f), q1 = fminf(fmaxf(__fdiv_rn(f[4 * j + 1], s), -448.f), 448.f);
-    const float q2 = fminf(fmaxf(__fdiv_rn(f[4 * j + 2], s), -448.f), 448.f), q3 = fminf(fmaxf(__fdiv_rn(f[4 * j + 3], s), -448.f), 448.f);
+    const float q0 = fminf(fmaxf(div_by(div, f[4 * j]), -448.f), 448.f), q1 = fminf(fmaxf(div_by(div, f[4 * j + 1]), -448.f), 448.f);
+    const float q2 = fminf(fmaxf(div_by(div, f[4 * j + 2]), -448.f), 448.f), q3 = fminf(fmaxf(div_by(div, f[4 * j + 3]), -448.f), 448.f);
     const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(q0, q1), __NV_SATFINITE, __NV_E4M3);
     const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(q2, q3), __NV_SATFINITE, __NV_E4M3);
     o[j] = lo | (hi << 16);
@@ -124,7 +129,7 @@ __global__ void __launch_bounds__(NORM_THREADS) fused_norm_kernel(const FusedNor
     for (int j = 0; j < 8; ++j) ss += x[i][j] * x[i][j];
   }
   if (a.w1) {
-    const float inv = powf(block_sum(ss, red) / a.hidden + a.eps, -0.5f);
+    const float inv = inv_sqrt(block_sum(ss, red) / a.hidden + a.eps);
 #pragma unroll
     for (int i = 0; i < NVEC; ++i) {
       float w[8];
@@ -159,7 +164,7 @@ __global__ void __launch_bounds__(NORM_THREADS) fused_norm_kernel(const FusedNor
       for (int j = 0; j < 8; ++j) ss += x[i][j] * x[i][j];
     }
   }
-  const float inv2 = powf(block_sum(ss, red) / a.hidden + a.eps, -0.5f);
+  const float inv2 = inv_sqrt(block_sum(ss, red) / a.hidden + a.eps);
   float amax = 0.f;
 #pragma unroll
   for (int i = 0; i < NVEC; ++i) {
@@ -178,10 +183,11 @@ __global__ void __launch_bounds__(NORM_THREADS) fused_norm_kernel(const FusedNor
   if (!a.out_x8) return;
   const float s = __fdiv_rn(fmaxf(block_max(amax, red), 1e-12f), 448.f);
   if (threadIdx.x == 0) a.out_xs[r] = s;
+  const DivBy div = make_div_by(s);
 #pragma unroll
   for (int i = 0; i < NVEC; ++i) {
     const int v = threadIdx.x + i * NORM_THREADS;
-    if (v < nvec) *reinterpret_cast<uint2*>(a.out_x8 + r * a.hidden + v * 8) = quant8(x[i], s);
+    if (v < nvec) *reinterpret_cast<uint2*>(a.out_x8 + r * a.hidden + v * 8) = quant8(x[i], div);
   }
 }
 
@@ -244,7 +250,7 @@ __global__ void __launch_bounds__(256) qkv_norm_rope_kernel(__nv_bfloat16* __res
 #pragma unroll
   for (int j = 0; j < V; ++j) ss += x[j] * x[j];
   for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-  const float inv = powf(ss / D + eps, -0.5f);
+  const float inv = inv_sqrt(ss / D + eps);
 #pragma unroll
   for (int j = 0; j < V; ++j) {
     const float wj = is_v ? 1.f : (plus1 ? 1.f + w[j] : w[j]);
@@ -296,13 +302,14 @@ __global__ void __launch_bounds__(512) glu_quant_kernel(const __nv_bfloat16* __r
   if (!out_x8) return;
   const float s = __fdiv_rn(fmaxf(block_max(amax, red), 1e-12f), 448.f);
   if (threadIdx.x == 0) out_xs[r] = s;
+  const DivBy div = make_div_by(s);
   for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
     float a[8], b[8];
     load8(g + v * 8, a);
     load8(u + v * 8, b);
 #pragma unroll
     for (int j = 0; j < 8; ++j) a[j] = round_bf16(round_bf16(act_fn<ACT>(a[j])) * b[j]);
-    *reinterpret_cast<uint2*>(out_x8 + r * F + v * 8) = quant8(a, s);
+    *reinterpret_cast<uint2*>(out_x8 + r * F + v * 8) = quant8(a, div);
   }
 }
 

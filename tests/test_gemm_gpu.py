@@ -21,6 +21,7 @@ def test_rowwise_quant_bit_exact(dev, M, K):
 
     x = _rand((M, K), 1, 3.0)
     x[0, : min(K, 16)] = 0  # a run of zeros
+    x[0, min(K, 16) : min(K, 32)] = -0.0  # negative zeros keep their sign through the division
     if M > 2:
         x[2] = 0  # an all-zero row: the scale clamps at 1e-12 / 448
     x8, xs = ops.fp8_rowwise_quant(x.to(dev))
