@@ -169,6 +169,18 @@ int spinf_qkv_norm_rope(void* qkv, int64_t pitch, int64_t n, int32_t H, int32_t 
                         const void* cos_t, const void* sin_t, int32_t rot_dim, float eps, int32_t plus1, int32_t norm_v,
                         void* stream);
 
+/* The Qwen attention layer's layout (spinf_serve/models/qwen35/qwen.py:683-697): the fused projection row is
+ * [H x (q (D) | gate (D))] | k (Hkv D) | v (Hkv D). Query heads are normed (RMSNorm with (1 + w) when plus1) and rotated over the
+ * first rot_dim dimensions like spinf_qkv_norm_rope and written DENSE to q_out [n, H, D]; key heads are normed and rotated in
+ * place; value heads and gates are left untouched. */
+int spinf_qkv_norm_rope_gated(void* y, int64_t pitch, int64_t n, int32_t H, int32_t Hkv, int32_t D, const void* wq, const void* wk,
+                              const void* cos_t, const void* sin_t, int32_t rot_dim, float eps, int32_t plus1, void* q_out,
+                              void* stream);
+
+/* In place o[t,h,:] = bf16(o[t,h,:] * bf16(sigmoid(gate[t,h,:]))), gate read from the same interleaved projection rows y (column
+ * h * 2 D + D): the output gate of the Qwen attention layer (qwen.py:696). o [n, H, D] bf16 dense. */
+int spinf_attn_gate(void* o, const void* y, int64_t pitch, int64_t n, int32_t H, int32_t D, void* stream);
+
 /* cos_t / sin_t [n, rot_dim/2] bf16 = bf16(cos / sin (float(pos[t]) * inv_freq[f])), inv_freq [rot_dim/2] fp32 on the device. */
 int spinf_rope_table(const int32_t* pos, int64_t n, int32_t rot_dim, const float* inv_freq, void* cos_t, void* sin_t, void* stream);
 

@@ -34,6 +34,8 @@ SIGNATURES = {
     "spinf_tile_desc_build_host": (_i64, [_p, _p, _p, _i64, _i32, _p, _p, _p]),
     "spinf_fused_norm": (ctypes.c_int, [_p, _p, _p, _p, _p, _i64, _i64, _f32, _i32, _p, _p, _p, _p, _p]),
     "spinf_qkv_norm_rope": (ctypes.c_int, [_p, _i64, _i64, _i32, _i32, _i32, _p, _p, _p, _p, _i32, _f32, _i32, _i32, _p]),
+    "spinf_qkv_norm_rope_gated": (ctypes.c_int, [_p, _i64, _i64, _i32, _i32, _i32, _p, _p, _p, _p, _i32, _f32, _i32, _p, _p]),
+    "spinf_attn_gate": (ctypes.c_int, [_p, _p, _i64, _i64, _i32, _i32, _p]),
     "spinf_rope_table": (ctypes.c_int, [_p, _i64, _i32, _p, _p, _p, _p]),
     "spinf_glu_quant": (ctypes.c_int, [_p, _i64, _i64, _i32, _p, _p, _p, _p]),
     "spinf_embed_scale": (ctypes.c_int, [_p, _p, _i64, _i64, _i64, _f32, _p, _p]),

@@ -218,7 +218,8 @@ template <int D>
 __global__ void __launch_bounds__(256) qkv_norm_rope_kernel(__nv_bfloat16* __restrict__ qkv, int64_t pitch, int64_t n, int H, int Hkv,
                                                             const __nv_bfloat16* __restrict__ wq, const __nv_bfloat16* __restrict__ wk,
                                                             const __nv_bfloat16* __restrict__ cos_t, const __nv_bfloat16* __restrict__ sin_t,
-                                                            float eps, int plus1, int norm_v, int rot_dim) {
+                                                            float eps, int plus1, int norm_v, int rot_dim, int q_stride, int k_off,
+                                                            __nv_bfloat16* __restrict__ q_out) {
   constexpr int V = D / 32;
   const int heads = H + 2 * Hkv;
   const int64_t gw = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
@@ -228,7 +229,10 @@ __global__ void __launch_bounds__(256) qkv_norm_rope_kernel(__nv_bfloat16* __res
   const int hd = static_cast<int>(gw % heads);
   const bool is_v = hd >= H + Hkv;
   if (is_v && !norm_v) return;
-  __nv_bfloat16* p = qkv + t * pitch + static_cast<int64_t>(hd) * D + lane * V;
+  // query head hd sits at column hd * q_stride (q_stride = D for a dense q block, 2 D when each head is followed by its gate);
+  // key / value heads follow from column k_off; a query head may be written to a separate dense tensor
+  const __nv_bfloat16* src = qkv + t * pitch + (hd < H ? static_cast<int64_t>(hd) * q_stride : k_off + static_cast<int64_t>(hd - H) * D) + lane * V;
+  __nv_bfloat16* p = (hd < H && q_out) ? q_out + (t * H + hd) * D + lane * V : const_cast<__nv_bfloat16*>(src);
   // rotate_half over the first R = rot_dim dimensions: out[i] = x[i] cos[i] - x[i + R/2] sin[i]  (i < R/2),
   //                                                    out[i] = x[i] cos[i] + x[i - R/2] sin[i]  (R/2 <= i < R),
   // cos / sin repeat with period R/2; dimensions >= R pass through. R/2 is a multiple of V, so a lane's partners sit in
@@ -239,7 +243,7 @@ __global__ void __launch_bounds__(256) qkv_norm_rope_kernel(__nv_bfloat16* __res
   const bool low = lane < hl;
   const int partner_lane = !rotates ? lane : (low ? lane + hl : lane - hl);
   float x[V], w[V], c[V], sn[V];
-  load_vec<V>(p, x);  // all loads of the warp are issued before the first reduction
+  load_vec<V>(src, x);  // all loads of the warp are issued before the first reduction
   if (!is_v) load_vec<V>((hd < H ? wq : wk) + lane * V, w);
   if (rotates) {
     const int f0 = (low ? lane : lane - hl) * V;
@@ -395,9 +399,61 @@ extern "C" int spinf_qkv_norm_rope(void* qkv, int64_t pitch, int64_t n, int32_t 
   auto* c = static_cast<const __nv_bfloat16*>(cos_t);
   auto* s = static_cast<const __nv_bfloat16*>(sin_t);
   if (D == 256)
-    qkv_norm_rope_kernel<256><<<grid, 256, 0, st>>>(p, pitch, n, H, Hkv, q, k, c, s, eps, plus1, norm_v, rot_dim);
+    qkv_norm_rope_kernel<256><<<grid, 256, 0, st>>>(p, pitch, n, H, Hkv, q, k, c, s, eps, plus1, norm_v, rot_dim, D, H * D, nullptr);
   else
-    qkv_norm_rope_kernel<128><<<grid, 256, 0, st>>>(p, pitch, n, H, Hkv, q, k, c, s, eps, plus1, norm_v, rot_dim);
+    qkv_norm_rope_kernel<128><<<grid, 256, 0, st>>>(p, pitch, n, H, Hkv, q, k, c, s, eps, plus1, norm_v, rot_dim, D, H * D, nullptr);
+  SPINF_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int spinf_qkv_norm_rope_gated(void* y, int64_t pitch, int64_t n, int32_t H, int32_t Hkv, int32_t D, const void* wq, const void* wk,
+                                         const void* cos_t, const void* sin_t, int32_t rot_dim, float eps, int32_t plus1, void* q_out,
+                                         void* stream) {
+  SPINF_CHECK_ARG(y && wq && wk && cos_t && sin_t && q_out && n >= 0 && H > 0 && Hkv > 0 && (D == 128 || D == 256));
+  SPINF_CHECK_ARG(rot_dim > 0 && rot_dim <= D && rot_dim % (2 * (D / 32)) == 0);
+  SPINF_CHECK_ARG(pitch >= static_cast<int64_t>(2 * H + 2 * Hkv) * D && pitch % 8 == 0);
+  if (n == 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  auto* p = static_cast<__nv_bfloat16*>(y);
+  auto* q = static_cast<const __nv_bfloat16*>(wq);
+  auto* k = static_cast<const __nv_bfloat16*>(wk);
+  auto* c = static_cast<const __nv_bfloat16*>(cos_t);
+  auto* s = static_cast<const __nv_bfloat16*>(sin_t);
+  auto* qo = static_cast<__nv_bfloat16*>(q_out);
+  // one warp per (token, head); the value heads' warps return at once (norm_v = 0: no norm, no rotary on values)
+  const int64_t warps_all = n * (H + 2 * Hkv);
+  const unsigned grid_all = static_cast<unsigned>((warps_all + 7) / 8);
+  if (D == 256)
+    qkv_norm_rope_kernel<256><<<grid_all, 256, 0, st>>>(p, pitch, n, H, Hkv, q, k, c, s, eps, plus1, 0, rot_dim, 2 * D, 2 * H * D, qo);
+  else
+    qkv_norm_rope_kernel<128><<<grid_all, 256, 0, st>>>(p, pitch, n, H, Hkv, q, k, c, s, eps, plus1, 0, rot_dim, 2 * D, 2 * H * D, qo);
+  SPINF_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// o[t, h, :] *= sigmoid(gate[t, h, :]) with the gate read from the interleaved projection output (column h * 2 D + D): the
+// sigmoid is rounded to bf16, then the product (both as the reference's bf16 tensor ops round them)
+__global__ void attn_gate_kernel(__nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ y, int64_t pitch, int64_t n, int H, int D) {
+  const int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
+  const int64_t per_tok = static_cast<int64_t>(H) * D;
+  if (i >= n * per_tok) return;
+  const int64_t t = i / per_tok;
+  const int r = static_cast<int>(i % per_tok);
+  const int h = r / D, d = r % D;
+  float x[8], g[8];
+  load8(o + i, x);
+  load8(y + t * pitch + static_cast<int64_t>(h) * 2 * D + D + d, g);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) x[j] = x[j] * round_bf16(1.f / (1.f + expf(-g[j])));
+  store8(o + i, x);
+}
+
+extern "C" int spinf_attn_gate(void* o, const void* y, int64_t pitch, int64_t n, int32_t H, int32_t D, void* stream) {
+  SPINF_CHECK_ARG(o && y && n >= 0 && H > 0 && D > 0 && D % 8 == 0 && pitch >= 2ll * H * D && pitch % 8 == 0);
+  if (n == 0) return 0;
+  const int64_t vecs = n * H * D / 8;
+  attn_gate_kernel<<<static_cast<unsigned>((vecs + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(y), pitch, n, H, D);
   SPINF_CUDA_OK(cudaGetLastError());
   return 0;
 }

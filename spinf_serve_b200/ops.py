@@ -240,6 +240,29 @@ def qkv_norm_rope(qkv, H, Hkv, D, wq, wk, cos, sin, eps=1e-6, plus1=False, norm_
     return qkv
 
 
+def qkv_norm_rope_gated(y, H, Hkv, D, wq, wk, cos, sin, eps=1e-6, plus1=True):
+    """the Qwen attention layout [H x (q | gate)] | k | v: -> dense q [n, H, D] (normed, rotated); k normed and rotated in place"""
+    _need(y, torch.bfloat16, "y", 2)
+    n = y.shape[0]
+    q = torch.empty((n, H, D), dtype=torch.bfloat16, device=y.device)
+    check(
+        _lib.lib().spinf_qkv_norm_rope_gated(
+            ptr(y), y.stride(0), n, H, Hkv, D, ptr(wq), ptr(wk), ptr(cos), ptr(sin), 2 * cos.shape[1], ctypes.c_float(eps), int(plus1),
+            ptr(q), stream_ptr(),
+        ),
+        "spinf_qkv_norm_rope_gated",
+    )
+    COUNTS["launches"] += 1
+    return q
+
+
+def attn_gate(o, y, H, D):
+    """in place o [n, H, D] *= sigmoid(gate), the gates read from the interleaved projection rows y"""
+    check(_lib.lib().spinf_attn_gate(ptr(o), ptr(y), y.stride(0), o.shape[0], H, D, stream_ptr()), "spinf_attn_gate")
+    COUNTS["launches"] += 1
+    return o
+
+
 def glu_quant(gu, act="gelu_tanh", want_fp8=True, want_y=False):
     """gu [n, 2F] bf16 (gate | up) -> act(gate) * up as (x8 [n, F], xs [n, 1]) and/or bf16 y [n, F]"""
     _need(gu, torch.bfloat16, "gu", 2)
