@@ -101,24 +101,23 @@ __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
   }
 }
 
-// One CTA per row. Every global load of the row (input, residual, both weights) is issued before the first reduction, so the
-// row costs one DRAM round trip instead of one per stage.
+// One CTA per row. Both streamed loads of the row (input, residual) are issued before the first reduction, so the row costs one
+// DRAM round trip instead of one per stage; the norm weights are cache hits and are loaded where they are used, which keeps the
+// register count low enough for four CTAs per SM at the common hidden sizes.
 template <int NVEC>
-__global__ void __launch_bounds__(NORM_THREADS) fused_norm_kernel(const FusedNormArgs a) {
+__global__ void __launch_bounds__(NORM_THREADS, NVEC <= 2 ? 4 : 2) fused_norm_kernel(const FusedNormArgs a) {
   __shared__ float red[NORM_THREADS / 32];
   const int64_t r = blockIdx.x;
   const int64_t rin = a.rows ? a.rows[r] : r;
   const int nvec = a.hidden / 8;
   const uint4 zero = make_uint4(0, 0, 0, 0);
-  uint4 ry[NVEC], rr[NVEC], rw1[NVEC], rw2[NVEC];
+  uint4 ry[NVEC], rr[NVEC];
 #pragma unroll
   for (int i = 0; i < NVEC; ++i) {
     const int v = threadIdx.x + i * NORM_THREADS;
     const bool on = v < nvec;
     ry[i] = on ? *reinterpret_cast<const uint4*>(a.y + rin * a.hidden + v * 8) : zero;
     rr[i] = on && a.residual ? *reinterpret_cast<const uint4*>(a.residual + r * a.hidden + v * 8) : zero;
-    rw1[i] = on && a.w1 ? *reinterpret_cast<const uint4*>(a.w1 + v * 8) : zero;
-    rw2[i] = on && a.w2 ? *reinterpret_cast<const uint4*>(a.w2 + v * 8) : zero;
   }
   float x[NVEC][8];
   float ss = 0.f;
@@ -132,8 +131,9 @@ __global__ void __launch_bounds__(NORM_THREADS) fused_norm_kernel(const FusedNor
     const float inv = inv_sqrt(block_sum(ss, red) / a.hidden + a.eps);
 #pragma unroll
     for (int i = 0; i < NVEC; ++i) {
+      const int v = threadIdx.x + i * NORM_THREADS;
       float w[8];
-      unpack8(rw1[i], w);
+      unpack8(v < nvec ? *reinterpret_cast<const uint4*>(a.w1 + v * 8) : zero, w);
 #pragma unroll
       for (int j = 0; j < 8; ++j) x[i][j] = round_bf16(x[i][j] * inv * (a.plus1 ? 1.f + w[j] : w[j]));
     }
@@ -171,7 +171,7 @@ __global__ void __launch_bounds__(NORM_THREADS) fused_norm_kernel(const FusedNor
     const int v = threadIdx.x + i * NORM_THREADS;
     if (v < nvec) {
       float w[8];
-      unpack8(rw2[i], w);
+      unpack8(*reinterpret_cast<const uint4*>(a.w2 + v * 8), w);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         x[i][j] = round_bf16(x[i][j] * inv2 * (a.plus1 ? 1.f + w[j] : w[j]));
@@ -214,6 +214,8 @@ __device__ __forceinline__ void store_vec(__nv_bfloat16* p, const float (&f)[V])
   }
 }
 
+// One warp per two consecutive (token, head) items: both heads' rows are loaded before either is reduced (twice the bytes in
+// flight per warp); norm weights and the rotary table are cache hits and are loaded where they are used.
 template <int D>
 __global__ void __launch_bounds__(256) qkv_norm_rope_kernel(__nv_bfloat16* __restrict__ qkv, int64_t pitch, int64_t n, int H, int Hkv,
                                                             const __nv_bfloat16* __restrict__ wq, const __nv_bfloat16* __restrict__ wk,
@@ -222,52 +224,69 @@ __global__ void __launch_bounds__(256) qkv_norm_rope_kernel(__nv_bfloat16* __res
                                                             __nv_bfloat16* __restrict__ q_out) {
   constexpr int V = D / 32;
   const int heads = H + 2 * Hkv;
-  const int64_t gw = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  if (gw >= n * heads) return;
+  const int64_t total = n * heads;
+  const int64_t first = ((static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5) * 2;
+  if (first >= total) return;
   const int lane = threadIdx.x & 31;
-  const int64_t t = gw / heads;
-  const int hd = static_cast<int>(gw % heads);
-  const bool is_v = hd >= H + Hkv;
-  if (is_v && !norm_v) return;
-  // query head hd sits at column hd * q_stride (q_stride = D for a dense q block, 2 D when each head is followed by its gate);
-  // key / value heads follow from column k_off; a query head may be written to a separate dense tensor
-  const __nv_bfloat16* src = qkv + t * pitch + (hd < H ? static_cast<int64_t>(hd) * q_stride : k_off + static_cast<int64_t>(hd - H) * D) + lane * V;
-  __nv_bfloat16* p = (hd < H && q_out) ? q_out + (t * H + hd) * D + lane * V : const_cast<__nv_bfloat16*>(src);
   // rotate_half over the first R = rot_dim dimensions: out[i] = x[i] cos[i] - x[i + R/2] sin[i]  (i < R/2),
   //                                                    out[i] = x[i] cos[i] + x[i - R/2] sin[i]  (R/2 <= i < R),
   // cos / sin repeat with period R/2; dimensions >= R pass through. R/2 is a multiple of V, so a lane's partners sit in
   // one other lane, `hl` lanes away, and its V cos / sin values are contiguous in the table.
   const int half = rot_dim / 2;
   const int hl = half / V;
-  const bool rotates = !is_v && lane < 2 * hl;
   const bool low = lane < hl;
-  const int partner_lane = !rotates ? lane : (low ? lane + hl : lane - hl);
-  float x[V], w[V], c[V], sn[V];
-  load_vec<V>(src, x);  // all loads of the warp are issued before the first reduction
-  if (!is_v) load_vec<V>((hd < H ? wq : wk) + lane * V, w);
-  if (rotates) {
-    const int f0 = (low ? lane : lane - hl) * V;
-    load_vec<V>(cos_t + t * half + f0, c);
-    load_vec<V>(sin_t + t * half + f0, sn);
+  float x[2][V];
+  const __nv_bfloat16* src[2];
+  __nv_bfloat16* dst[2];
+  int hd[2];
+  int64_t tok[2];
+  bool live[2];
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int64_t item = first + u;
+    live[u] = item < total;
+    tok[u] = live[u] ? item / heads : 0;
+    hd[u] = live[u] ? static_cast<int>(item % heads) : 0;
+    if (hd[u] >= H + Hkv && !norm_v) live[u] = false;  // value heads without a norm are left untouched
+    // query head hd sits at column hd * q_stride (q_stride = D for a dense q block, 2 D when each head is followed by its
+    // gate); key / value heads follow from column k_off; a query head may be written to a separate dense tensor
+    src[u] = qkv + tok[u] * pitch + (hd[u] < H ? static_cast<int64_t>(hd[u]) * q_stride : k_off + static_cast<int64_t>(hd[u] - H) * D) + lane * V;
+    dst[u] = (hd[u] < H && q_out) ? q_out + (tok[u] * H + hd[u]) * D + lane * V : const_cast<__nv_bfloat16*>(src[u]);
+    if (live[u]) load_vec<V>(src[u], x[u]);
   }
-  float ss = 0.f;
 #pragma unroll
-  for (int j = 0; j < V; ++j) ss += x[j] * x[j];
-  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-  const float inv = inv_sqrt(ss / D + eps);
+  for (int u = 0; u < 2; ++u) {
+    if (!live[u]) continue;  // uniform across the warp
+    const bool is_v = hd[u] >= H + Hkv;
+    float ss = 0.f;
 #pragma unroll
-  for (int j = 0; j < V; ++j) {
-    const float wj = is_v ? 1.f : (plus1 ? 1.f + w[j] : w[j]);
-    x[j] = round_bf16(x[j] * inv * wj);
-  }
-  if (!is_v) {
+    for (int j = 0; j < V; ++j) ss += x[u][j] * x[u][j];
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float inv = inv_sqrt(ss / D + eps);
+    if (is_v) {
 #pragma unroll
-    for (int j = 0; j < V; ++j) {
-      const float partner = __shfl_sync(0xffffffffu, x[j], partner_lane);
-      if (rotates) x[j] = round_bf16(round_bf16(x[j] * c[j]) + round_bf16((low ? -partner : partner) * sn[j]));
+      for (int j = 0; j < V; ++j) x[u][j] = round_bf16(x[u][j] * inv);
+    } else {
+      float w[V];
+      load_vec<V>((hd[u] < H ? wq : wk) + lane * V, w);
+#pragma unroll
+      for (int j = 0; j < V; ++j) x[u][j] = round_bf16(x[u][j] * inv * (plus1 ? 1.f + w[j] : w[j]));
+      const bool rotates = lane < 2 * hl;
+      const int partner_lane = !rotates ? lane : (low ? lane + hl : lane - hl);
+      float c[V], sn[V];
+      if (rotates) {
+        const int f0 = (low ? lane : lane - hl) * V;
+        load_vec<V>(cos_t + tok[u] * half + f0, c);
+        load_vec<V>(sin_t + tok[u] * half + f0, sn);
+      }
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const float partner = __shfl_sync(0xffffffffu, x[u][j], partner_lane);
+        if (rotates) x[u][j] = round_bf16(round_bf16(x[u][j] * c[j]) + round_bf16((low ? -partner : partner) * sn[j]));
+      }
     }
+    store_vec<V>(dst[u], x[u]);
   }
-  store_vec<V>(p, x);
 }
 
 // ------------------------------------------------------------------------------------------------ gated activation + quantiser
@@ -390,7 +409,7 @@ extern "C" int spinf_qkv_norm_rope(void* qkv, int64_t pitch, int64_t n, int32_t 
   SPINF_CHECK_ARG(rot_dim > 0 && rot_dim <= D && rot_dim % (2 * (D / 32)) == 0);
   SPINF_CHECK_ARG(pitch >= static_cast<int64_t>(H + 2 * Hkv) * D);
   if (n == 0) return 0;
-  const int64_t warps = n * (H + 2 * Hkv);
+  const int64_t warps = (n * (H + 2 * Hkv) + 1) / 2;  // two (token, head) items per warp
   const unsigned grid = static_cast<unsigned>((warps + 7) / 8);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   auto* p = static_cast<__nv_bfloat16*>(qkv);
@@ -421,7 +440,7 @@ extern "C" int spinf_qkv_norm_rope_gated(void* y, int64_t pitch, int64_t n, int3
   auto* s = static_cast<const __nv_bfloat16*>(sin_t);
   auto* qo = static_cast<__nv_bfloat16*>(q_out);
   // one warp per (token, head); the value heads' warps return at once (norm_v = 0: no norm, no rotary on values)
-  const int64_t warps_all = n * (H + 2 * Hkv);
+  const int64_t warps_all = (n * (H + 2 * Hkv) + 1) / 2;
   const unsigned grid_all = static_cast<unsigned>((warps_all + 7) / 8);
   if (D == 256)
     qkv_norm_rope_kernel<256><<<grid_all, 256, 0, st>>>(p, pitch, n, H, Hkv, q, k, c, s, eps, plus1, 0, rot_dim, 2 * D, 2 * H * D, qo);
