@@ -69,6 +69,18 @@ int spinf_fp8_rowwise_gemm(const void* x8, const float* xs, const void* w8, cons
 int spinf_fp8_rowwise_gemm_glu(const void* x8, const float* xs, const void* w8_tiled, const float* ws_tiled, void* y, float* row_amax,
                                int64_t M, int64_t F, int64_t K, int32_t act, void* stream);
 
+/* The fused q|k|v projection of an attention layer with the per-head RMS norms and the rotary embedding applied in the GEMM
+ * epilogue (the reference runs q_proj / k_proj / v_proj as Fp8RowLinear calls, then q_norm / k_norm / v_norm and
+ * apply_rotary_pos_emb as inductor-fused pointwise kernels: transformers' Gemma4TextAttention, called through
+ * spinf_serve/models/gemma4.py:383-405). w8 [(H + 2 Hkv) D, K] e4m3 holds the q heads, then the k heads, then the v heads; ws the
+ * per-channel scales; wq / wk [D] bf16 the head-norm weights (plus1: scale by 1 + w); cos_t / sin_t [M, D/2] bf16 the rotary table
+ * of the rows' positions (full rotary: the rotated width is D); norm_v: v heads get the weightless RMS norm. y [M, (H + 2 Hkv) D]
+ * bf16. D is 128 or 256, (H + 2 Hkv) D a multiple of 256; y, wq, wk, cos_t, sin_t 32-byte aligned. Same values as
+ * spinf_fp8_rowwise_gemm followed by spinf_qkv_norm_rope. */
+int spinf_fp8_rowwise_gemm_qkv(const void* x8, const float* xs, const void* w8, const float* ws, void* y, int64_t M, int32_t H,
+                               int32_t Hkv, int32_t D, int64_t K, const void* wq, const void* wk, const void* cos_t,
+                               const void* sin_t, float eps, int32_t plus1, int32_t norm_v, void* stream);
+
 /* Row-wise fp8 quantisation (arithmetic of spinf_fp8_rowwise_quant) of y [M, K] bf16 when the row maxima are already known:
  * xs[m] = max(row_amax[m], 1e-12) / 448, x8 = e4m3(clamp(y / xs)). One pass over y. */
 int spinf_fp8_quant_from_amax(const void* y, const float* row_amax, int64_t M, int64_t K, void* x8, float* xs, void* stream);

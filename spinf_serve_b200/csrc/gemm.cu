@@ -32,7 +32,7 @@ struct EpiLse {
     st.s = 0.f;
   }
   __device__ __forceinline__ void chunk(State& st, const GemmShape& s, int tm, int tn, int row, int et, int c,
-                                        const uint32_t (&v0)[32], const uint32_t (&v1)[32], const float*, uint8_t*) const {
+                                        const uint32_t (&v0)[32], const uint32_t (&v1)[32], const float*, uint8_t*, uint32_t) const {
     const int n0 = tn * BN + c * 64;
     float x[64];
     float mx = -INFINITY;
@@ -104,7 +104,7 @@ struct EpiGlu {
   }
   __device__ __forceinline__ void chunk(State& st, const GemmShape& s, int tm, int tn, int row, int et, int c,
                                         const uint32_t (&v0)[32], const uint32_t (&v1)[32], const float* colscale,
-                                        uint8_t* epi_stage) const {
+                                        uint8_t* epi_stage, uint32_t) const {
     const int m = tm * 128 + row;
     const float rs = m < s.M ? rowscale[m] : 0.f;
     uint32_t packed[16];
@@ -148,6 +148,148 @@ struct EpiGlu {
   __device__ __forceinline__ void finish(State&, int et) const {
     if (et == 0) tma_store_wait_all<0>();
   }
+};
+
+// ------------------------------------------------------------------------------------------------ q|k|v projection epilogue
+// The fused q|k|v projection with the per-head RMS norms and the rotary embedding applied before the tile leaves the SM. A
+// 128 x 256 accumulator tile holds whole heads (one of 256 dims, or two of 128), and an epilogue thread owns a full row of it, so
+// the head's sum of squares is thread-local. Pass 1 (chunk) rounds the linear's outputs y = bf16((acc * xs) * ws) as packed pairs,
+// accumulates their squares and parks the pairs in the accumulator's own TMEM columns (pair word q of the row in column q: always
+// behind the columns still to be read). Pass 2 (end_tile) reads the pairs back 16 words at a time, the group D/2 columns further
+// along with them, and applies
+//     x = bf16(y * rsqrt(mean y^2 + eps) * w)        (q with wq, k with wk, v without weight)
+//     out = bf16(bf16(x cos) + bf16(rotate_half(x) sin))      (q and k only; packed bf16 multiplies and adds)
+// before writing bf16 rows straight to global memory. Same rounding chain as the row-wise GEMM followed by the norm + rotary kernel.
+template <int BN, int D>
+struct EpiQkvNormRope {
+  static constexpr bool kReadsTmemInEnd = true;
+  static constexpr int HEADS = BN / D;
+  __nv_bfloat16* y;
+  int64_t y_pitch;
+  const float* rowscale;
+  const float* colscale_g;
+  const __nv_bfloat16 *wq, *wk, *cos_t, *sin_t;  // cos / sin [M, D/2]
+  int H, Hkv;
+  float eps;
+  int plus1, norm_v;
+  struct State {
+    float ss[HEADS];
+  };
+  __device__ __forceinline__ static float inv_sqrt(float v) {
+    const float r = rsqrtf(v);
+    return r * fmaf(-0.5f * v * r, r, 1.5f);
+  }
+  __device__ __forceinline__ void begin_tile(State& st, const GemmShape& s, int tm, int tn, int et, float* colscale) const {
+    named_bar_sync(2, 128);
+    for (int i = et; i < BN; i += 128) {
+      const int n = tn * BN + i;
+      colscale[i] = n < s.N ? colscale_g[n] : 0.f;
+    }
+    named_bar_sync(2, 128);
+#pragma unroll
+    for (int h = 0; h < HEADS; ++h) st.ss[h] = 0.f;
+  }
+  __device__ __forceinline__ void chunk(State& st, const GemmShape& s, int tm, int tn, int row, int et, int c,
+                                        const uint32_t (&v0)[32], const uint32_t (&v1)[32], const float* colscale, uint8_t*,
+                                        uint32_t t_row) const {
+    const int m = tm * 128 + row;
+    const float rs = m < s.M ? rowscale[m] : 0.f;
+    float acc0 = 0.f, acc1 = 0.f;
+    uint32_t pk[32];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float2 c0 = *reinterpret_cast<const float2*>(colscale + c * 64 + 2 * j);
+      const float2 c1 = *reinterpret_cast<const float2*>(colscale + c * 64 + 32 + 2 * j);
+      pk[j] = pack_bf16x2((__uint_as_float(v0[2 * j]) * rs) * c0.x, (__uint_as_float(v0[2 * j + 1]) * rs) * c0.y);
+      pk[16 + j] = pack_bf16x2((__uint_as_float(v1[2 * j]) * rs) * c1.x, (__uint_as_float(v1[2 * j + 1]) * rs) * c1.y);
+      acc0 = fmaf(bf2_lo(pk[j]), bf2_lo(pk[j]), acc0);
+      acc1 = fmaf(bf2_hi(pk[j]), bf2_hi(pk[j]), acc1);
+      acc0 = fmaf(bf2_lo(pk[16 + j]), bf2_lo(pk[16 + j]), acc0);
+      acc1 = fmaf(bf2_hi(pk[16 + j]), bf2_hi(pk[16 + j]), acc1);
+    }
+    __syncwarp();
+    tmem_st_x32(t_row + c * 32, pk);
+#pragma unroll
+    for (int h = 0; h < HEADS; ++h)
+      if ((c * 64) / D == h) st.ss[h] += acc0 + acc1;
+  }
+  // 32 columns [col_lo, col_lo + 32) of this thread's row with the 32 columns D/2 further along. MODE is a compile-time constant so
+  // that the block is straight-line code: 0 = q / k (norm weight + rotary), 1 = v with the weightless norm, 2 = v untouched.
+  template <int MODE>
+  __device__ __forceinline__ void granule_pair(uint32_t t_row, int col_lo, float inv, float p1, const __nv_bfloat16* w_lo,
+                                               const __nv_bfloat16* cs_row, const __nv_bfloat16* sn_row, __nv_bfloat16* dst,
+                                               bool live) const {
+    const int col_hi = col_lo + D / 2;
+    uint32_t a0[16], a1[16];
+    __syncwarp();
+    tmem_ld_x16(t_row + col_lo / 2, a0);
+    tmem_ld_x16(t_row + col_hi / 2, a1);
+    // 32 consecutive table / weight entries as two 32-byte loads each, issued while the TMEM load is in flight
+    uint32_t cv[2][8], sv[2][8], wl[2][8], wh[2][8];
+    if (MODE == 0) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        ldg_nc_v8(cs_row + i * 16, cv[i]);
+        ldg_nc_v8(sn_row + i * 16, sv[i]);
+        ldg_nc_v8(w_lo + i * 16, wl[i]);
+        ldg_nc_v8(w_lo + D / 2 + i * 16, wh[i]);
+      }
+    }
+    tmem_wait_ld();
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      uint32_t out_lo[8], out_hi[8];
+#pragma unroll
+      for (int p = 0; p < 8; ++p) {
+        uint32_t xl = a0[i * 8 + p], xh = a1[i * 8 + p];
+        if (MODE == 0) {
+          xl = pack_bf16x2(bf2_lo(xl) * inv * (bf2_lo(wl[i][p]) + p1), bf2_hi(xl) * inv * (bf2_hi(wl[i][p]) + p1));
+          xh = pack_bf16x2(bf2_lo(xh) * inv * (bf2_lo(wh[i][p]) + p1), bf2_hi(xh) * inv * (bf2_hi(wh[i][p]) + p1));
+          out_lo[p] = bf2_sub(bf2_mul(xl, cv[i][p]), bf2_mul(xh, sv[i][p]));
+          out_hi[p] = bf2_add(bf2_mul(xh, cv[i][p]), bf2_mul(xl, sv[i][p]));
+        } else if (MODE == 1) {
+          out_lo[p] = pack_bf16x2(bf2_lo(xl) * inv, bf2_hi(xl) * inv);
+          out_hi[p] = pack_bf16x2(bf2_lo(xh) * inv, bf2_hi(xh) * inv);
+        } else {
+          out_lo[p] = xl, out_hi[p] = xh;
+        }
+      }
+      if (live) {
+        stg_v8(dst + col_lo + i * 16, out_lo);
+        stg_v8(dst + col_hi + i * 16, out_hi);
+      }
+    }
+  }
+  __device__ __forceinline__ void end_tile(State& st, const GemmShape& s, int tm, int tn, int row, int et, uint32_t t_row,
+                                           const float* colscale) const {
+    constexpr int HALF = D / 64;  // 32-column granules per half head
+    const int m = tm * 128 + row;
+    const bool live = m < s.M;
+    const int64_t mrow = live ? m : 0;
+    __nv_bfloat16* dst = y + mrow * y_pitch + static_cast<int64_t>(tn) * BN;
+    const float p1 = plus1 ? 1.f : 0.f;  // w + 0 == w for every bf16 weight that is not -0
+    tmem_wait_st();                      // the pairs parked by pass 1 are in place
+#pragma unroll 1
+    for (int hl = 0; hl < HEADS; ++hl) {
+      const int hg = tn * HEADS + hl;  // head index in the fused projection: q heads, then k heads, then v heads
+      const int mode = hg < H + Hkv ? 0 : (norm_v ? 1 : 2);
+      const float inv = mode == 2 ? 1.f : inv_sqrt(st.ss[hl] / D + eps);
+      const __nv_bfloat16* w = hg < H ? wq : wk;
+#pragma unroll 1
+      for (int gi = 0; gi < HALF; ++gi) {
+        const int col_lo = hl * D + gi * 32;
+        const __nv_bfloat16* cs_row = cos_t + mrow * (D / 2) + gi * 32;
+        const __nv_bfloat16* sn_row = sin_t + mrow * (D / 2) + gi * 32;
+        if (mode == 0)
+          granule_pair<0>(t_row, col_lo, inv, p1, w + gi * 32, cs_row, sn_row, dst, live);
+        else if (mode == 1)
+          granule_pair<1>(t_row, col_lo, inv, p1, w, cs_row, sn_row, dst, live);
+        else
+          granule_pair<2>(t_row, col_lo, inv, p1, w, cs_row, sn_row, dst, live);
+      }
+    }
+  }
+  __device__ __forceinline__ void finish(State&, int) const {}
 };
 
 // x8 = e4m3(clamp(y / s)), s = max(amax, 1e-12) / 448 with the row maxima already known: one pass over y
@@ -357,6 +499,40 @@ extern "C" int spinf_fp8_rowwise_gemm_glu(const void* x8, const float* xs, const
   return launch_gemm<KIND_F8, BN>(tmA, tmB, shape, epi, st);
 }
 
+extern "C" int spinf_fp8_rowwise_gemm_qkv(const void* x8, const float* xs, const void* w8, const float* ws, void* y, int64_t M, int32_t H,
+                                          int32_t Hkv, int32_t D, int64_t K, const void* wq, const void* wk, const void* cos_t,
+                                          const void* sin_t, float eps, int32_t plus1, int32_t norm_v, void* stream) {
+  SPINF_CHECK_ARG(x8 && xs && w8 && ws && y && wq && wk && cos_t && sin_t && M >= 0 && K > 0 && K % 16 == 0);
+  SPINF_CHECK_ARG(H > 0 && Hkv > 0 && (D == 128 || D == 256) && M < (1ll << 31) && K < (1ll << 31));
+  const int64_t N = static_cast<int64_t>(H + 2 * Hkv) * D;
+  SPINF_CHECK_ARG(N % 256 == 0 && N < (1ll << 31));
+  // rows are read and written as 32-byte pieces
+  SPINF_CHECK_ARG(((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(cos_t) | reinterpret_cast<uintptr_t>(sin_t) |
+                    reinterpret_cast<uintptr_t>(wq) | reinterpret_cast<uintptr_t>(wk)) & 31) == 0);
+  if (M == 0) return 0;
+  constexpr int BN = 256;
+  CUtensorMap tmA, tmB;
+  int r;
+  if ((r = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x8, M, K, K, 128, 128))) return r;
+  if ((r = make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w8, N, K, K, 128, BN))) return r;
+  const GemmShape shape = make_shape(M, N, K, BN);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  auto fill = [&](auto& epi) {
+    epi.y = static_cast<__nv_bfloat16*>(y), epi.y_pitch = N, epi.rowscale = xs, epi.colscale_g = ws;
+    epi.wq = static_cast<const __nv_bfloat16*>(wq), epi.wk = static_cast<const __nv_bfloat16*>(wk);
+    epi.cos_t = static_cast<const __nv_bfloat16*>(cos_t), epi.sin_t = static_cast<const __nv_bfloat16*>(sin_t);
+    epi.H = H, epi.Hkv = Hkv, epi.eps = eps, epi.plus1 = plus1, epi.norm_v = norm_v;
+  };
+  if (D == 256) {
+    EpiQkvNormRope<BN, 256> epi;
+    fill(epi);
+    return launch_gemm<KIND_F8, BN>(tmA, tmB, shape, epi, st);
+  }
+  EpiQkvNormRope<BN, 128> epi;
+  fill(epi);
+  return launch_gemm<KIND_F8, BN>(tmA, tmB, shape, epi, st);
+}
+
 extern "C" int spinf_fp8_quant_from_amax(const void* y, const float* row_amax, int64_t M, int64_t K, void* x8, float* xs, void* stream) {
   SPINF_CHECK_ARG(y && row_amax && x8 && xs && M >= 0 && K > 0 && K % 8 == 0 && M < (1ll << 31) && K < (1ll << 31));
   if (M == 0) return 0;
@@ -490,3 +666,13 @@ extern "C" int spinf_option_logprobs_static(const void* h, const void* W, int64_
   SPINF_CUDA_OK(cudaGetLastError());
   return 0;
 }
+
+#ifdef SPINF_TRACE
+extern "C" int spinf_trace_read(long long* out) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out, spinf::g_trace, sizeof(long long) * 8);
+  long long z[8] = {0};
+  cudaMemcpyToSymbol(spinf::g_trace, z, sizeof(z));
+  return 0;
+}
+#endif

@@ -51,9 +51,15 @@ __device__ __forceinline__ void tile_coords(const GemmShape& s, int tile, int& t
 // Epilogue functor contract (all calls are made by the 128 epilogue threads, thread = row `row` of the tile; the functor is a
 // __grid_constant__ kernel parameter, so it may hold a TMA descriptor; its mutable per-thread state lives in Epi::State):
 //   begin_tile(st, shape, tm, tn, et, ...)       once per tile before the accumulator is ready (et = 0..127)
-//   chunk(st, shape, tm, tn, row, et, c, v0, v1) 64 accumulator columns [c*64, c*64+64) of this thread's row, as two x32 groups
+//   chunk(st, shape, tm, tn, row, et, c, v0, v1, ..., t_row) 64 accumulator columns [c*64, c*64+64) of this thread's row, as two x32
+//                                                groups (t_row = TMEM address of the row's first column)
 //   end_tile(st, ..., t_row, ...)                after the last chunk (may read single TMEM columns when kReadsTmemInEnd)
 //   finish(st, et)                               once, after the last tile
+#ifdef SPINF_TRACE
+// debugging aid, compiled out of the library: clocks the epilogue warps spend waiting for an accumulator, in the chunk loop and in
+// end_tile, summed over tiles by the first epilogue thread of every CTA ([0..2] cycles, [3] tiles)
+__device__ long long g_trace[8];
+#endif
 template <int KIND, int BN, class Epi>
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmShape shape,
@@ -170,7 +176,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t ab = tcount & 1u, aph = (tcount >> 1) & 1u;
       __syncwarp();
       epi.begin_tile(est, shape, tm, tn, et, colscale);
+#ifdef SPINF_TRACE
+      const long long tr0 = clock64();
+#endif
       const bool got = mbar_wait(wc, &acc_full[ab], aph, ST_TIMEOUT_TMEM);
+#ifdef SPINF_TRACE
+      const long long tr1 = clock64();
+#endif
       if (!bar_red_and(1, 128, got)) break;  // all 128 epilogue threads leave together
       tc_fence_after();
       const uint32_t t_row = tmem_base + ab * BN + (static_cast<uint32_t>(q * 32) << 16);
@@ -185,14 +197,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tc_fence_before();
           mbar_arrive(&acc_empty[ab]);
         }
-        epi.chunk(est, shape, tm, tn, row, et, c, v0, v1, colscale, epi_stage);
+        epi.chunk(est, shape, tm, tn, row, et, c, v0, v1, colscale, epi_stage, t_row);
       }
       __syncwarp();
+#ifdef SPINF_TRACE
+      const long long tr2 = clock64();
+#endif
       epi.end_tile(est, shape, tm, tn, row, et, t_row, colscale);
       if (Epi::kReadsTmemInEnd) {
         tc_fence_before();
         mbar_arrive(&acc_empty[ab]);
       }
+#ifdef SPINF_TRACE
+      if (et == 0) {
+        const long long tr3 = clock64();
+        atomicAdd(reinterpret_cast<unsigned long long*>(&g_trace[0]), static_cast<unsigned long long>(tr1 - tr0));
+        atomicAdd(reinterpret_cast<unsigned long long*>(&g_trace[1]), static_cast<unsigned long long>(tr2 - tr1));
+        atomicAdd(reinterpret_cast<unsigned long long*>(&g_trace[2]), static_cast<unsigned long long>(tr3 - tr2));
+        atomicAdd(reinterpret_cast<unsigned long long*>(&g_trace[3]), 1ull);
+      }
+#endif
     }
     epi.finish(est, et);
   }
@@ -231,7 +255,7 @@ struct EpiStoreBf16 {
   }
   __device__ __forceinline__ void chunk(State& st, const GemmShape& s, int tm, int tn, int row, int et, int c,
                                         const uint32_t (&v0)[32], const uint32_t (&v1)[32], const float* colscale,
-                                        uint8_t* epi_stage) const {
+                                        uint8_t* epi_stage, uint32_t) const {
     float rs = 1.f;
     if (SCALED) {
       const int m = tm * 128 + row;

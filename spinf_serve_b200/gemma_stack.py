@@ -146,6 +146,7 @@ class GemmaStack:
             "full_attention": (1.0 / (self.cfg.theta_full**expo)).to(dev),
         }
         self.embed_scale = float(torch.tensor(self.cfg.hidden**0.5).to(torch.bfloat16))
+        self.fuse_qkv = D in (128, 256) and ((self.cfg.heads + 2 * self.cfg.kv_heads) * D) % 256 == 0
 
     def plan(self, b) -> None:
         """nothing to prepare on the host for attention-only models (base.py:50-51)"""
@@ -173,8 +174,11 @@ class GemmaStack:
             L = w.layers[i]
             kind = cfg.layer_types[i]
             cos, sin = tables[kind]
-            qkv = ops.fp8_rowwise_gemm(r["x8"], r["xs"], L["qkv_w"], L["qkv_s"])
-            ops.qkv_norm_rope(qkv, H, K, D, L["q_norm"], L["k_norm"], cos, sin, cfg.eps)
+            if self.fuse_qkv:  # head norms + rotary in the projection's epilogue
+                qkv = ops.fp8_gemm_qkv(r["x8"], r["xs"], L["qkv_w"], L["qkv_s"], H, K, D, L["q_norm"], L["k_norm"], cos, sin, cfg.eps)
+            else:
+                qkv = ops.fp8_rowwise_gemm(r["x8"], r["xs"], L["qkv_w"], L["qkv_s"])
+                ops.qkv_norm_rope(qkv, H, K, D, L["q_norm"], L["k_norm"], cos, sin, cfg.eps)
             q = qkv[:, : H * D].view(n, H, D)
             k = qkv[:, H * D : (H + K) * D].view(n, K, D)
             v = qkv[:, (H + K) * D :].view(n, K, D)

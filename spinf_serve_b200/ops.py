@@ -136,6 +136,43 @@ def fp8_gemm_glu(x8, xs, w8_tiled, ws_tiled, act="gelu_tanh"):
     return y8, ys, y
 
 
+def fp8_gemm_qkv(x8, xs, w8, ws, H, Hkv, D, wq, wk, cos, sin, eps=1e-6, plus1=False, norm_v=True):
+    """fused q|k|v projection with the head norms and the (full-width) rotary embedding in the GEMM epilogue: equals
+    fp8_rowwise_gemm followed by qkv_norm_rope; -> [M, (H + 2 Hkv) D] bf16"""
+    _need(x8, FP8, "x8", 2)
+    _need(w8, FP8, "w8", 2)
+    xs1, ws1 = xs.reshape(-1), ws.reshape(-1)
+    _need(xs1, torch.float32, "xs", 1)
+    _need(ws1, torch.float32, "ws", 1)
+    for t, name in ((wq, "wq"), (wk, "wk")):
+        _need(t, torch.bfloat16, name, 1)
+    _need(cos, torch.bfloat16, "cos", 2)
+    _need(sin, torch.bfloat16, "sin", 2)
+    M, K = x8.shape
+    N = (H + 2 * Hkv) * D
+    if w8.shape != (N, K) or xs1.numel() != M or ws1.numel() != N or cos.shape != (M, D // 2) or sin.shape != (M, D // 2):
+        raise SpinfError("fp8_gemm_qkv: shapes do not agree (the rotary table must span the whole head)")
+    if wq.numel() != D or wk.numel() != D:
+        raise SpinfError("fp8_gemm_qkv: head-norm weights must have D entries")
+    y = torch.empty((M, N), dtype=torch.bfloat16, device=x8.device)
+    prof = PROFILE
+    if prof is not None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+    check(
+        _lib.lib().spinf_fp8_rowwise_gemm_qkv(
+            ptr(x8), ptr(xs1), ptr(w8), ptr(ws1), ptr(y), M, H, Hkv, D, K, ptr(wq), ptr(wk), ptr(cos), ptr(sin), ctypes.c_float(eps),
+            int(plus1), int(norm_v), stream_ptr(),
+        ),
+        "spinf_fp8_rowwise_gemm_qkv",
+    )
+    if prof is not None:
+        e1.record()
+        prof.append((e0, e1, 2.0 * M * N * K))
+    COUNTS["launches"] += 1
+    return y
+
+
 def bf16_gemm(x, w):
     """y [M, N] bf16 = x [M, K] @ w [N, K]^T, fp32 accumulation"""
     _need(x, torch.bfloat16, "x", 2)

@@ -1,6 +1,7 @@
 """GPU parity of the tcgen05 GEMMs (through the C ABI) against the CPU oracle: row-wise fp8 quantiser + GEMM
 (spinf_serve/quant/linears.py:29-33,84-96), plain bf16 GEMM, and batch invariance of rows across M."""
 
+import numpy as np
 import pytest
 import torch
 
@@ -102,3 +103,40 @@ def test_fused_glu_gemm_equals_the_unfused_chain(dev, M, F, K, act):
     assert torch.equal(fs, us) and torch.equal(f8.view(torch.uint8), u8.view(torch.uint8))
     k8, ks = O.quant_act_row(y.cpu())
     assert torch.equal(fs.cpu(), ks) and torch.equal(f8.cpu().view(torch.uint8), k8.view(torch.uint8))
+
+
+@pytest.mark.parametrize("M,H,Hkv,D,K", [(300, 4, 2, 128, 512), (517, 16, 8, 256, 3840), (64, 2, 1, 256, 256), (129, 6, 1, 128, 384)])
+def test_fused_qkv_gemm_equals_gemm_then_norm_rope(dev, M, H, Hkv, D, K):
+    """q|k|v projection with the head norms and rotary in its epilogue == the row-wise GEMM followed by the norm + rotary kernel.
+    The rounding chain is the same; the fp32 sum of squares of a head is added in another order, so a last bf16 bit may flip
+    on a few elements. A row's result does not depend on the rows packed beside it."""
+    from oracle import gemma as OG
+    from spinf_serve_b200 import ops
+
+    N = (H + 2 * Hkv) * D
+    x = _rand((M, K), 21)
+    w8, ws = O.quantize_weight_rowwise(_rand((N, K), 22, 0.05))
+    x8, xs = O.quant_act_row(x)
+    x8, xs, w8, ws = x8.to(dev), xs.to(dev), w8.to(dev), ws.to(dev).reshape(-1)
+    g = torch.Generator().manual_seed(23)
+    wq = (1 + 0.1 * torch.randn(D, generator=g)).to(torch.bfloat16).to(dev)
+    wk = (1 + 0.1 * torch.randn(D, generator=g)).to(torch.bfloat16).to(dev)
+    pos = np.random.default_rng(1).integers(0, 4000, M).astype(np.int32)
+    cos, sin = OG.rope_tables(pos, D, 10_000.0)
+    cos, sin = cos[:, : D // 2].contiguous().to(dev), sin[:, : D // 2].contiguous().to(dev)
+    for plus1, norm_v in ((False, True), (True, False)):
+        ref = ops.fp8_rowwise_gemm(x8, xs, w8, ws)
+        ops.qkv_norm_rope(ref, H, Hkv, D, wq, wk, cos, sin, 1e-6, plus1=plus1, norm_v=norm_v)
+        got = ops.fp8_gemm_qkv(x8, xs, w8, ws, H, Hkv, D, wq, wk, cos, sin, 1e-6, plus1=plus1, norm_v=norm_v)
+        differs = (got.float() != ref.float()).float().mean().item()
+        print(f"M {M} heads {H}+2x{Hkv} D {D}: {differs:.5%} of elements differ")
+        assert differs < 2e-3
+        # a flipped last bit of a normed value moves a rotated output by one ulp of the larger of the pair it mixes
+        assert (got.float() - ref.float()).abs().max() <= 2.0**-6 * ref.float().abs().max()
+        if not norm_v:
+            assert torch.equal(got[:, (H + Hkv) * D :], ref[:, (H + Hkv) * D :])  # values pass through untouched
+        for m in (1, 100):
+            m = min(m, M)
+            part = ops.fp8_gemm_qkv(x8[:m].contiguous(), xs[:m].contiguous(), w8, ws, H, Hkv, D, wq, wk, cos[:m].contiguous(),
+                                    sin[:m].contiguous(), 1e-6, plus1=plus1, norm_v=norm_v)
+            assert torch.equal(part, got[:m])
