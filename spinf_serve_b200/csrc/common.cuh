@@ -295,6 +295,23 @@ __device__ __forceinline__ float round_bf16_split(float x) {
   const float t = __fmul_rn(x, 65537.f);
   return __fsub_rn(t, __fsub_rn(t, x));
 }
+__device__ __forceinline__ uint32_t bf2_max(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("max.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+// GELU, tanh form, as the fp32 expression 0.5 x (1 + tanh(z)), z = sqrt(2/pi) (x + 0.044715 x^3), without a branch:
+// tanh(|z|) = 1 - 2 e / (1 + e) with e = exp(-2 |z|) <= 1 (no overflow; the subtraction rounds like a faithful tanh near 1, and
+// an absolute error of a few 1e-7 near 0 disappears in 1 + tanh). -2 z log2(e) = -x (K1 + K2 x^2).
+__device__ __forceinline__ float gelu_tanh_f32(float x) {
+  constexpr float K1 = 2.302208198144325f, K2 = 0.1029432395800235f;
+  const float zz = x * fmaf(x * x, K2, K1);
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-fabsf(zz)));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.f + e));
+  const float t = copysignf(fmaf(-2.f, e * r, 1.f), zz);
+  return (0.5f * x) * (1.f + t);
+}
 // 256-bit global accesses (32-byte aligned addresses): a thread that walks its own row moves a whole 32-byte sector per request
 __device__ __forceinline__ void ldg_nc_v8(const void* p, uint32_t (&r)[8]) {
   asm volatile("ld.global.nc.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"

@@ -84,13 +84,10 @@ struct EpiGlu {
   float* row_amax;          // [M], zeroed before the launch
   struct State {
     uint32_t nstores;
-    float amax;
+    uint32_t amax2;  // running maxima of |y| as a packed bf16 pair (even / odd columns)
   };
   __device__ __forceinline__ static float act(float x) {
-    if (ACT == 0) {
-      const float inner = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-      return 0.5f * x * (1.f + tanhf(inner));
-    }
+    if (ACT == 0) return gelu_tanh_f32(x);
     return x / (1.f + expf(-x));
   }
   __device__ __forceinline__ void begin_tile(State& st, const GemmShape& s, int tm, int tn, int et, float* colscale) const {
@@ -100,27 +97,24 @@ struct EpiGlu {
       colscale[i] = n < s.N ? colscale_g[n] : 0.f;
     }
     named_bar_sync(2, 128);
-    st.amax = 0.f;
+    st.amax2 = 0u;
   }
   __device__ __forceinline__ void chunk(State& st, const GemmShape& s, int tm, int tn, int row, int et, int c,
                                         const uint32_t (&v0)[32], const uint32_t (&v1)[32], const float* colscale,
                                         uint8_t* epi_stage, uint32_t) const {
     const int m = tm * 128 + row;
     const float rs = m < s.M ? rowscale[m] : 0.f;
+    // packed pairs throughout: the linear's bf16 outputs come out of the pack conversion, the gated product is one bf16x2 multiply
     uint32_t packed[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      float y[2];
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int j = 2 * i + h;
-        const float g = __bfloat162float(__float2bfloat16_rn((__uint_as_float(v0[j]) * rs) * colscale[c * 64 + j]));
-        const float u = __bfloat162float(__float2bfloat16_rn((__uint_as_float(v1[j]) * rs) * colscale[c * 64 + 32 + j]));
-        const float a = __bfloat162float(__float2bfloat16_rn(act(g)));
-        y[h] = __bfloat162float(__float2bfloat16_rn(a * u));
-        st.amax = fmaxf(st.amax, fabsf(y[h]));
-      }
-      packed[i] = pack_bf16x2(y[0], y[1]);
+      const float2 cg = *reinterpret_cast<const float2*>(colscale + c * 64 + 2 * i);
+      const float2 cu = *reinterpret_cast<const float2*>(colscale + c * 64 + 32 + 2 * i);
+      const uint32_t g = pack_bf16x2((__uint_as_float(v0[2 * i]) * rs) * cg.x, (__uint_as_float(v0[2 * i + 1]) * rs) * cg.y);
+      const uint32_t u = pack_bf16x2((__uint_as_float(v1[2 * i]) * rs) * cu.x, (__uint_as_float(v1[2 * i + 1]) * rs) * cu.y);
+      const uint32_t a = pack_bf16x2(act(bf2_lo(g)), act(bf2_hi(g)));
+      packed[i] = bf2_mul(a, u);
+      st.amax2 = bf2_max(st.amax2, packed[i] & 0x7fff7fffu);
     }
     uint8_t* buf = epi_stage + (st.nstores & 1u) * (128 * 128);
     if ((c & 1) == 0) {
@@ -143,7 +137,7 @@ struct EpiGlu {
   }
   __device__ __forceinline__ void end_tile(State& st, const GemmShape& s, int tm, int, int row, int, uint32_t, const float*) const {
     const int m = tm * 128 + row;
-    if (m < s.M) atomicMax(reinterpret_cast<unsigned int*>(row_amax + m), __float_as_uint(st.amax));
+    if (m < s.M) atomicMax(reinterpret_cast<unsigned int*>(row_amax + m), __float_as_uint(fmaxf(bf2_lo(st.amax2), bf2_hi(st.amax2))));
   }
   __device__ __forceinline__ void finish(State&, int et) const {
     if (et == 0) tma_store_wait_all<0>();

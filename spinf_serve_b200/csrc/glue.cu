@@ -102,92 +102,99 @@ __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
 }
 
 // One CTA per row. Both streamed loads of the row (input, residual) are issued before the first reduction, so the row costs one
-// DRAM round trip instead of one per stage; the norm weights are cache hits and are loaded where they are used, which keeps the
-// register count low enough for four CTAs per SM at the common hidden sizes.
-template <int NVEC>
+// DRAM round trip instead of one per stage; the norm weights are cache hits and are loaded where they are used. The row stays in
+// registers as packed bf16 pairs: a norm's output leaves the pack conversion already rounded, the residual add is the bf16x2
+// add (the exact sum rounded once, as the bf16 tensor add rounds), and the running |max| is a bf16x2 max.
+template <bool PLUS1>  // the weight enters as (1 + w)
+__device__ __forceinline__ uint32_t scale_pair(uint32_t x, float inv, uint32_t w) {
+  const float w0 = PLUS1 ? 1.f + bf2_lo(w) : bf2_lo(w), w1 = PLUS1 ? 1.f + bf2_hi(w) : bf2_hi(w);
+  return pack_bf16x2(bf2_lo(x) * inv * w0, bf2_hi(x) * inv * w1);
+}
+__device__ __forceinline__ float sumsq4(const uint4& u, float ss) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) ss = fmaf(bf2_hi(w[j]), bf2_hi(w[j]), fmaf(bf2_lo(w[j]), bf2_lo(w[j]), ss));
+  return ss;
+}
+// x / s for the eight values of a packed vector, converted to e4m3 with saturation (|x / s| exceeds 448 by rounding at most)
+__device__ __forceinline__ uint2 quant8_packed(const uint4& u, const DivBy& div) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    o[j] = __nv_cvt_float2_to_fp8x2(make_float2(div_by(div, bf2_lo(w[j])), div_by(div, bf2_hi(w[j]))), __NV_SATFINITE, __NV_E4M3);
+  return make_uint2(o[0] | (o[1] << 16), o[2] | (o[3] << 16));
+}
+
+template <int NVEC, bool PLUS1>
 __global__ void __launch_bounds__(NORM_THREADS, NVEC <= 2 ? 4 : 2) fused_norm_kernel(const FusedNormArgs a) {
   __shared__ float red[NORM_THREADS / 32];
   const int64_t r = blockIdx.x;
   const int64_t rin = a.rows ? a.rows[r] : r;
   const int nvec = a.hidden / 8;
   const uint4 zero = make_uint4(0, 0, 0, 0);
-  uint4 ry[NVEC], rr[NVEC];
+  uint4 cur[NVEC], rr[NVEC];
 #pragma unroll
   for (int i = 0; i < NVEC; ++i) {
     const int v = threadIdx.x + i * NORM_THREADS;
     const bool on = v < nvec;
-    ry[i] = on ? *reinterpret_cast<const uint4*>(a.y + rin * a.hidden + v * 8) : zero;
+    cur[i] = on ? *reinterpret_cast<const uint4*>(a.y + rin * a.hidden + v * 8) : zero;
     rr[i] = on && a.residual ? *reinterpret_cast<const uint4*>(a.residual + r * a.hidden + v * 8) : zero;
   }
-  float x[NVEC][8];
-  float ss = 0.f;
-#pragma unroll
-  for (int i = 0; i < NVEC; ++i) {
-    unpack8(ry[i], x[i]);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) ss += x[i][j] * x[i][j];
-  }
   if (a.w1) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NVEC; ++i) ss = sumsq4(cur[i], ss);
     const float inv = inv_sqrt(block_sum(ss, red) / a.hidden + a.eps);
 #pragma unroll
     for (int i = 0; i < NVEC; ++i) {
       const int v = threadIdx.x + i * NORM_THREADS;
-      float w[8];
-      unpack8(v < nvec ? *reinterpret_cast<const uint4*>(a.w1 + v * 8) : zero, w);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) x[i][j] = round_bf16(x[i][j] * inv * (a.plus1 ? 1.f + w[j] : w[j]));
+      const uint4 w = v < nvec ? *reinterpret_cast<const uint4*>(a.w1 + v * 8) : zero;
+      cur[i] = make_uint4(scale_pair<PLUS1>(cur[i].x, inv, w.x), scale_pair<PLUS1>(cur[i].y, inv, w.y), scale_pair<PLUS1>(cur[i].z, inv, w.z),
+                          scale_pair<PLUS1>(cur[i].w, inv, w.w));
     }
   }
   if (a.residual) {
 #pragma unroll
-    for (int i = 0; i < NVEC; ++i) {
-      float res[8];
-      unpack8(rr[i], res);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) x[i][j] = round_bf16(x[i][j] + res[j]);
-    }
+    for (int i = 0; i < NVEC; ++i)
+      cur[i] = make_uint4(bf2_add(cur[i].x, rr[i].x), bf2_add(cur[i].y, rr[i].y), bf2_add(cur[i].z, rr[i].z), bf2_add(cur[i].w, rr[i].w));
   }
   if (a.out_h) {
 #pragma unroll
     for (int i = 0; i < NVEC; ++i) {
       const int v = threadIdx.x + i * NORM_THREADS;
-      if (v < nvec) store8(a.out_h + r * a.hidden + v * 8, x[i]);
+      if (v < nvec) *reinterpret_cast<uint4*>(a.out_h + r * a.hidden + v * 8) = cur[i];
     }
   }
   if (!a.w2) return;
-  ss = 0.f;
+  float ss = 0.f;
 #pragma unroll
   for (int i = 0; i < NVEC; ++i) {
     const int v = threadIdx.x + i * NORM_THREADS;
-    if (v < nvec) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) ss += x[i][j] * x[i][j];
-    }
+    if (v < nvec) ss = sumsq4(cur[i], ss);  // (lanes past the row may hold a norm of zeros times 1 + w: keep them out)
   }
   const float inv2 = inv_sqrt(block_sum(ss, red) / a.hidden + a.eps);
-  float amax = 0.f;
+  uint32_t amax2 = 0u;
 #pragma unroll
   for (int i = 0; i < NVEC; ++i) {
     const int v = threadIdx.x + i * NORM_THREADS;
     if (v < nvec) {
-      float w[8];
-      unpack8(*reinterpret_cast<const uint4*>(a.w2 + v * 8), w);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        x[i][j] = round_bf16(x[i][j] * inv2 * (a.plus1 ? 1.f + w[j] : w[j]));
-        amax = fmaxf(amax, fabsf(x[i][j]));
-      }
-      if (a.out_norm) store8(a.out_norm + r * a.hidden + v * 8, x[i]);
+      const uint4 w = *reinterpret_cast<const uint4*>(a.w2 + v * 8);
+      cur[i] = make_uint4(scale_pair<PLUS1>(cur[i].x, inv2, w.x), scale_pair<PLUS1>(cur[i].y, inv2, w.y), scale_pair<PLUS1>(cur[i].z, inv2, w.z),
+                          scale_pair<PLUS1>(cur[i].w, inv2, w.w));
+      amax2 = bf2_max(bf2_max(amax2, cur[i].x & 0x7fff7fffu), bf2_max(cur[i].y & 0x7fff7fffu, bf2_max(cur[i].z & 0x7fff7fffu, cur[i].w & 0x7fff7fffu)));
+      if (a.out_norm) *reinterpret_cast<uint4*>(a.out_norm + r * a.hidden + v * 8) = cur[i];
     }
   }
   if (!a.out_x8) return;
+  const float amax = fmaxf(bf2_lo(amax2), bf2_hi(amax2));
   const float s = __fdiv_rn(fmaxf(block_max(amax, red), 1e-12f), 448.f);
   if (threadIdx.x == 0) a.out_xs[r] = s;
   const DivBy div = make_div_by(s);
 #pragma unroll
   for (int i = 0; i < NVEC; ++i) {
     const int v = threadIdx.x + i * NORM_THREADS;
-    if (v < nvec) *reinterpret_cast<uint2*>(a.out_x8 + r * a.hidden + v * 8) = quant8(x[i], div);
+    if (v < nvec) *reinterpret_cast<uint2*>(a.out_x8 + r * a.hidden + v * 8) = quant8_packed(cur[i], div);
   }
 }
 
@@ -293,10 +300,7 @@ __global__ void __launch_bounds__(256) qkv_norm_rope_kernel(__nv_bfloat16* __res
 enum : int { ACT_GELU_TANH = 0, ACT_SILU = 1 };
 template <int ACT>
 __device__ __forceinline__ float act_fn(float x) {
-  if (ACT == ACT_GELU_TANH) {
-    const float inner = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-    return 0.5f * x * (1.f + tanhf(inner));
-  }
+  if (ACT == ACT_GELU_TANH) return gelu_tanh_f32(x);
   return x / (1.f + expf(-x));
 }
 
@@ -392,12 +396,19 @@ extern "C" int spinf_fused_norm(const void* y, const int64_t* rows, const void* 
   const int per_thread = static_cast<int>((hidden / 8 + NORM_THREADS - 1) / NORM_THREADS);
   const unsigned grid = static_cast<unsigned>(n_out);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define SPINF_NORM_CASE(NV)                                                      \
+  if (plus1)                                                                     \
+    fused_norm_kernel<NV, true><<<grid, NORM_THREADS, 0, st>>>(a);               \
+  else                                                                           \
+    fused_norm_kernel<NV, false><<<grid, NORM_THREADS, 0, st>>>(a);              \
+  break;
   switch (per_thread) {
-    case 1: fused_norm_kernel<1><<<grid, NORM_THREADS, 0, st>>>(a); break;
-    case 2: fused_norm_kernel<2><<<grid, NORM_THREADS, 0, st>>>(a); break;
-    case 3: fused_norm_kernel<3><<<grid, NORM_THREADS, 0, st>>>(a); break;
-    default: fused_norm_kernel<4><<<grid, NORM_THREADS, 0, st>>>(a); break;
+    case 1: SPINF_NORM_CASE(1)
+    case 2: SPINF_NORM_CASE(2)
+    case 3: SPINF_NORM_CASE(3)
+    default: SPINF_NORM_CASE(4)
   }
+#undef SPINF_NORM_CASE
   SPINF_CUDA_OK(cudaGetLastError());
   return 0;
 }
