@@ -146,18 +146,27 @@ int spinf_option_logprobs_static(const void* h, const void* W, int64_t R, int64_
 int64_t spinf_tile_desc_build_host(const int32_t* art_host, const int32_t* end_host, const int32_t* pos_host, int64_t n,
                                    int32_t window, int32_t* counts_host, int32_t* blocks_host, uint8_t* flags_host);
 
+/* The mask rule of the packed stream (spinf_serve/scorer.py:173-177, the mask_mod the reference hands to create_block_mask) evaluated
+ * once per stream and mask type instead of once per layer and head: for entry e of the packed tile lists, key half hf (0 / 1) and
+ * row r of the entry's query block, bit c of bits[(e * 2 + hf) * 128 + r] = visible(128 qb + r, 128 j + 64 hf + c) as defined below.
+ * art / end / pos, tile_offsets / tile_blocks on the device; bits: 2 * 128 * (number of entries) uint64 on the device. */
+int spinf_tile_mask_bits(const int32_t* art, const int32_t* end, const int32_t* pos, int64_t n, int32_t window,
+                         const int32_t* tile_offsets, const int32_t* tile_blocks, uint64_t* bits, void* stream);
+
 /* Replaces the "tree_flex" attention interface (spinf_serve/models/gemma4.py:99-121, mask rule spinf_serve/scorer.py:173-177) and
  * qwen.tree_attention (spinf_serve/models/qwen35/qwen.py:605-623):
  *   out[t,h,:] = sum_k softmax_k(scale * q[t,h,:].k[k,g,:] | visible(t,k)) v[k,g,:],   g = h / (H/Hkv)
  *   visible(t,k) = (k <= t && art[t] >= 0 && art[k] == art[t] && t < end[k] && (window <= 0 || pos[t]-pos[k] < window)) || t == k
  * q [n,H,D], k,v [n,Hkv,D], out [n,H,D] bf16, token-major with row pitches given in ELEMENTS (so q/k/v may be slices of one fused
  * projection output); D in {128, 256}; n a multiple of 128. tile_offsets [nb+1] (prefix sums of counts), tile_blocks, tile_flags:
- * the packed lists from spinf_tile_desc_build_host, on the device. Scores are fp32, P is rounded to bf16 before P.V, the running
- * maximum is updated once per 64 keys in ascending key order: a row's result depends only on its own job's tokens. */
+ * the packed lists from spinf_tile_desc_build_host, on the device; tile_bits: the visibility words of spinf_tile_mask_bits for the
+ * same lists and window (entries flagged "no mask" are not read). Scores are fp32, P is rounded to bf16 before P.V, the running
+ * maximum is updated once per 128 keys in ascending key order: a row's result depends only on its own job's tokens. scale > 0;
+ * out 32-byte aligned with a row pitch that is a multiple of 16 elements. */
 int spinf_tree_attn_fwd(const void* q, const void* k, const void* v, void* out, int64_t n, int32_t H, int32_t Hkv, int32_t D,
                         int64_t q_pitch, int64_t kv_pitch, int64_t out_pitch, const int32_t* art, const int32_t* end,
                         const int32_t* pos, int32_t window, float scale, const int32_t* tile_offsets, const int32_t* tile_blocks,
-                        const uint8_t* tile_flags, void* stream);
+                        const uint8_t* tile_flags, const uint64_t* tile_bits, void* stream);
 
 /* ------------------------------------------------------------------------------------------------------------ layer glue
  * The reference runs these steps as inductor-fused pieces of the decoder layer (the layer code itself is the transformers

@@ -24,6 +24,7 @@ class TileMask:
     offsets: torch.Tensor  # int32 [nb + 1]
     blocks: torch.Tensor   # int32 [visited]
     flags: torch.Tensor    # uint8 [visited]
+    bits: torch.Tensor     # int64 [visited, 2, 128]: per entry, key half and query row, which of the half's 64 keys the row sees
     window: int            # 0 = full attention
     n: int
     visited: int
@@ -50,7 +51,16 @@ def stream_masks(art, end, pos, window, device, always_window=True):
         td = packer.tile_desc(art, end, pos, w)
         blocks = td.blocks if len(td.blocks) else np.zeros(1, np.int32)
         flags = td.flags if len(td.flags) else np.zeros(1, np.uint8)
-        return TileMask(d_art, d_end, d_pos, up(td.offsets), up(blocks), up(flags), int(w or 0), n, td.visited, td.skipped_fraction)
+        d_off, d_blocks = up(td.offsets), up(blocks)
+        # the mask rule, evaluated once for the stream: every layer of this type and every head reads these words
+        bits = torch.empty((len(blocks), 2, packer.BLOCK), dtype=torch.int64, device=device)
+        if n:
+            check(
+                _lib.lib().spinf_tile_mask_bits(ptr(d_art), ptr(d_end), ptr(d_pos), n, int(w or 0), ptr(d_off), ptr(d_blocks), ptr(bits), stream_ptr()),
+                "spinf_tile_mask_bits",
+            )
+            ops.COUNTS["launches"] += 1
+        return TileMask(d_art, d_end, d_pos, d_off, d_blocks, up(flags), bits, int(w or 0), n, td.visited, td.skipped_fraction)
 
     full = one(None)
     binding = window is not None and (always_window or (n > 0 and int(pos.max()) >= window))
@@ -72,7 +82,7 @@ def tree_attention(q, k, v, mask: TileMask, scale: float, out=None):
     check(
         _lib.lib().spinf_tree_attn_fwd(
             ptr(q), ptr(k), ptr(v), ptr(out), n, H, Hkv, D, q.stride(0), k.stride(0), out.stride(0), ptr(mask.art), ptr(mask.end),
-            ptr(mask.pos), mask.window, float(scale), ptr(mask.offsets), ptr(mask.blocks), ptr(mask.flags), stream_ptr(),
+            ptr(mask.pos), mask.window, float(scale), ptr(mask.offsets), ptr(mask.blocks), ptr(mask.flags), ptr(mask.bits), stream_ptr(),
         ),
         "spinf_tree_attn_fwd",
     )

@@ -1,43 +1,46 @@
 // Tree-mask attention over one packed stream (prefill), tcgen05 + TMEM + TMA, for sm_100a.
 //
-// One CTA = one 128-row query block of one query head. It walks the block's tile list (built on the host from the packing
-// metadata, copied to shared memory at start) in ascending key order, 64 keys at a time:
-//   warp 0    one lane: TMA loads of Q (once) and of the K sub-tiles into a 2-deep ring, released as soon as S = Q K^T has read them
-//   warp 6    one lane: TMA loads of the V sub-tiles into their own 2-deep ring, released when O += P V has read them
-//   warp 1    allocates tensor memory; one lane issues  S = Q K^T  (M=128, N=64, K=D)  into one of two S buffers and
-//             O += P V  (M=128, N=D, K=64)  into the O accumulator; S of sub-tile t+1 is issued before P V of sub-tile t, so the
-//             tensor core works on the next scores while the softmax warps work on the current ones
-//   warps 2-5 thread = query row: reads S from TMEM, applies scale and the tree mask, keeps the running reference maximum and
-//             the sum in fp32, writes P (bf16) into a swizzled shared tile, and at the end divides O by the sum and stores bf16.
-//             O is rescaled in TMEM only when a row's maximum grew by more than 2^8 since its reference maximum was last moved
-//             (probabilities then stay below 256, exact in the final division); the decision depends on the row's own scores only.
+// Persistent CTAs, one per SM; a work item is one 128-row tile of queries against the tile list of its 128-row query block
+// (built on the host from the packing metadata), walked in ascending key order, 128 keys at a time. The 128 rows of an item are
+// either one head's whole query block, or - when two query heads share a key/value head - the same 64 stream rows of both
+// heads, so that every K / V tile fetched serves two heads.
+//   warp 0     one lane: TMA loads of Q (per item) and of K, 64 keys at a time, into a ring
+//   warp 10    one lane: TMA loads of V, 64 keys at a time, into its own ring
+//   warp 1     owns tensor memory; one lane issues, per 128-key tile, S = Q K^T as two 128 x 64 halves into one of two S buffers,
+//              and O += P V as two K = 64 halves with P read from tensor memory; S of tile t+1 is issued before P V of tile t
+//   warps 2-9  two softmax groups of four warps; thread = query row, group A takes keys [0, 64) of the tile and group B keys
+//              [64, 128): S half from TMEM, the row's 64-bit visibility word of the tile (built once per stream by
+//              tile_mask_bits_kernel below: the mask is the same for every layer and head), row maximum (exchanged between the two groups through shared memory so that
+//              both take the same decisions), exponentials, P as packed bf16 written back over the S half in TMEM.
+//              O is rescaled in TMEM only when a row's maximum grew by more than 2^24 since its reference maximum was last moved
+//              (probabilities then stay below 2^24: no overflow in bf16 P, the fp32 sum or O, and rounding to bf16 is relative, so
+//              nothing is lost against a maximum that moves every tile); the decision depends on the row's own scores only.
+//              At the end of an item each group divides its half of the O columns by the row sum and stores bf16.
 // Numerics follow the reference's attention (bf16 Q/K/V, fp32 scores and softmax state, P rounded to bf16 before P V, fp32
-// accumulation). Reduction order per row = ascending 64-key sub-tiles of the row's own job, independent of what else is packed
-// in the stream; tiles flagged "no mask" only skip the mask evaluation, never change the arithmetic.
+// accumulation). Reduction order per row = ascending key tiles of the row's own job, independent of what else is packed in the
+// stream; tiles flagged "no mask" only skip the mask evaluation, never change the arithmetic.
 #include "common.cuh"
 #include "host_util.h"
 
 namespace spinf {
 
-static constexpr int KT = 64;          // keys per sub-tile
-static constexpr int LIST_CAP = 512;   // tile-list entries kept in shared memory (longer lists read the rest from global)
-static constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
+static constexpr int KH = 64;                    // keys per half tile (one softmax group's share, one ring stage)
+static constexpr float RESCALE_THRESHOLD = 24.f;  // log2 units
+static constexpr int ATTN_THREADS = 352;
 
 template <int D>
 struct AttnSmem {
   static constexpr int SLABS = D / 64;              // 64-element (128-byte) slabs along the head dimension
   static constexpr int Q_BYTES = SLABS * 128 * 128;
-  static constexpr int KV_TILE = SLABS * KT * 128;  // one K (or V) sub-tile
-  static constexpr int P_BYTES = 128 * 128;
-  static constexpr int K_OFF = Q_BYTES;             // 2 stages of K then 2 stages of V
-  static constexpr int V_OFF = K_OFF + 2 * KV_TILE;
-  static constexpr int P_OFF = V_OFF + 2 * KV_TILE;
-  static constexpr int BAR_OFF = P_OFF + P_BYTES;
-  static constexpr int LIST_OFF = BAR_OFF + 128;            // LIST_CAP ints + LIST_CAP bytes
-  static constexpr int META_OFF = LIST_OFF + LIST_CAP * 5;  // per softmax warp: 2 buffers x 3 arrays x 64 ints
-  static constexpr int TOTAL = META_OFF + 4 * 2 * 3 * KT * 4 + 1024;
-  static constexpr int TMEM_COLS = D == 256 ? 512 : 256;    // 2 x 64 (S) + D (O), rounded up to a power of two
-  static constexpr int O_COL = 128;
+  static constexpr int KV_HALF = SLABS * KH * 128;  // one ring stage: 64 keys of K (or V)
+  static constexpr int NS = D == 256 ? 2 : 4;       // ring depth in stages, a multiple of 2
+  static constexpr int K_OFF = Q_BYTES;
+  static constexpr int V_OFF = K_OFF + NS * KV_HALF;
+  static constexpr int BAR_OFF = V_OFF + NS * KV_HALF;
+  static constexpr int XCHG_OFF = BAR_OFF + 512;            // 3 x 2 x 128 floats: row maxima (two buffers), row sums
+  static constexpr int TOTAL = XCHG_OFF + 3 * 2 * 128 * 4 + 1024;
+  static constexpr int TMEM_COLS = 512;  // S: 2 buffers x 128 columns; O: D columns from column 256
+  static constexpr int O_COL = 256;
 };
 
 struct AttnArgs {
@@ -49,56 +52,85 @@ struct AttnArgs {
   const int32_t* tile_offsets;
   const int32_t* tile_blocks;
   const uint8_t* tile_flags;  // bit 0: every pair attends under the tree rule; bit 1: no mask evaluation needed (window included)
+  const uint64_t* tile_bits;  // per list entry, key half and query row of the block: visibility of the half's 64 keys
   int nb, H, group;           // group = H / Hkv
+  int hp;                     // query heads per item: 1, or 2 (64 rows of each of two heads that share a key/value head)
+  int n_items;                // nb * H
   int window;
   float scale_log2;
 };
 
+// item -> (query block, first head, first row of the block it covers)
+struct AttnItem {
+  int qb, h0, row0;
+};
+__device__ __forceinline__ AttnItem attn_item(const AttnArgs& a, int it) {
+  AttnItem r;
+  r.qb = it / a.H;
+  const int x = it - r.qb * a.H;
+  if (a.hp == 2) {
+    r.h0 = (x >> 1) * 2;
+    r.row0 = (x & 1) * 64;
+  } else {
+    r.h0 = x;
+    r.row0 = 0;
+  }
+  return r;
+}
+
+#ifdef SPINF_TRACE
+// debugging aid, compiled out of the library: cycles one softmax thread per CTA spends per phase, summed over tiles / items
+__device__ unsigned long long g_attn_trace[16];
+#define TR(var) const long long var = clock64()
+#define TR_ADD(slot, v) if (threadIdx.x == 64) atomicAdd(&g_attn_trace[slot], static_cast<unsigned long long>(v))
+#else
+#define TR(var)
+#define TR_ADD(slot, v)
+#endif
+
 template <int D>
-__global__ void __launch_bounds__(224, 1)
+__global__ void __launch_bounds__(ATTN_THREADS, 1)
 tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const AttnArgs a, int* __restrict__ status) {
   using L = AttnSmem<D>;
   constexpr int SLABS = L::SLABS;
-  constexpr uint32_t IDESC_S = make_idesc(FMT_BF16, FMT_BF16, 128, KT, 0, 0);
+  constexpr int NS = L::NS;
+  constexpr uint32_t IDESC_S = make_idesc(FMT_BF16, FMT_BF16, 128, KH, 0, 0);
   constexpr uint32_t IDESC_O = make_idesc(FMT_BF16, FMT_BF16, 128, D, 0, 1);  // B = V, MN-major (head dim contiguous)
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
-  uint64_t* q_full = bars;         // 1
-  uint64_t* k_full = bars + 1;     // 2
-  uint64_t* v_full = bars + 3;     // 2
-  uint64_t* k_empty = bars + 5;    // 2
-  uint64_t* v_empty = bars + 7;    // 2
-  uint64_t* s_full = bars + 9;     // 2
-  uint64_t* p_ready = bars + 11;   // 1 (128 arrivals)
-  uint64_t* o_done = bars + 12;    // 1
-  uint32_t* tmem_base_p = reinterpret_cast<uint32_t*>(bars + 13);
+  uint64_t* q_full = bars;                 // 1
+  uint64_t* q_empty = bars + 1;            // 1
+  uint64_t* k_full = bars + 2;             // NS
+  uint64_t* k_empty = k_full + NS;         // NS
+  uint64_t* v_full = k_empty + NS;         // NS
+  uint64_t* v_empty = v_full + NS;         // NS
+  uint64_t* s_full = v_empty + NS;         // 4: [buffer][half]
+  uint64_t* p_ready = s_full + 4;          // 1 (256 arrivals)
+  uint64_t* o_done = p_ready + 1;          // 1
+  uint64_t* o_free = o_done + 1;           // 1 (256 arrivals)
+  uint32_t* tmem_base_p = reinterpret_cast<uint32_t*>(o_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_p + 1);
-  int* list_blocks = reinterpret_cast<int*>(smem + L::LIST_OFF);
-  uint8_t* list_flags = smem + L::LIST_OFF + LIST_CAP * 4;
-  int* meta = reinterpret_cast<int*>(smem + L::META_OFF);
+  float* xchg = reinterpret_cast<float*>(smem + L::XCHG_OFF);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qb = blockIdx.x, h = blockIdx.y;
-  const int g = h / a.group;
   const WaitCtx wc{abort_flag, status};
-  const int e0 = a.tile_offsets[qb];
-  const int n_tiles = a.tile_offsets[qb + 1] - e0;
-  const int n_sub = 2 * n_tiles;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    mbar_init(q_empty, 1);
+    for (int i = 0; i < NS; ++i) {
       mbar_init(&k_full[i], 1);
-      mbar_init(&v_full[i], 1);
       mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1);
     }
-    mbar_init(p_ready, 128);
+    for (int i = 0; i < 4; ++i) mbar_init(&s_full[i], 1);
+    mbar_init(p_ready, 256);
     mbar_init(o_done, 1);
+    mbar_init(o_free, 256);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmQ);
@@ -109,243 +141,296 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     tmem_alloc(tmem_base_p, L::TMEM_COLS);
     tmem_relinquish();
   }
-  for (int i = threadIdx.x; i < n_tiles && i < LIST_CAP; i += blockDim.x) {
-    list_blocks[i] = a.tile_blocks[e0 + i];
-    list_flags[i] = a.tile_flags[e0 + i];
-  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_p;
-  auto block_of = [&](int tile) { return tile < LIST_CAP ? list_blocks[tile] : a.tile_blocks[e0 + tile]; };
-  auto flags_of = [&](int tile) { return tile < LIST_CAP ? list_flags[tile] : a.tile_flags[e0 + tile]; };
 
-  if (warp == 0 || warp == 6) {
-    // K producer (warp 0, also loads Q) and V producer (warp 6): one lane each
-    if (lane == 0 && n_sub > 0) {
+  if (warp == 0 || warp == 10) {
+    // K producer (warp 0, also loads Q) and V producer (warp 10): one lane each
+    if (lane == 0) {
       const bool is_k = warp == 0;
       uint64_t* full = is_k ? k_full : v_full;
       uint64_t* empty = is_k ? k_empty : v_empty;
       const CUtensorMap* tm = is_k ? &tmK : &tmV;
       const int base = is_k ? L::K_OFF : L::V_OFF;
-      if (is_k) {
-        mbar_expect_tx(q_full, L::Q_BYTES);
-        for (int s = 0; s < SLABS; ++s) tma_load_2d(smem + s * 128 * 128, &tmQ, h * D + s * 64, qb * 128, q_full);
-      }
-      int issued = 0;
-      for (int t = 0; t < n_sub; ++t, ++issued) {
-        const int st = t & 1;
-        const uint32_t ph = (t >> 1) & 1u;
-        const int j = block_of(t >> 1);
-        if (j < 0 || j >= a.nb) {
-          *abort_flag = 1;
-          atomicCAS(status, 0, ST_BAD_INDEX);
-          break;
+      uint32_t cnt = 0, item_n = 0;  // stages issued so far; items so far
+      bool ok = true;
+      for (int it = blockIdx.x; it < a.n_items && ok; it += gridDim.x) {
+        const AttnItem w = attn_item(a, it);
+        const int e0 = a.tile_offsets[w.qb];
+        const int n_tiles = a.tile_offsets[w.qb + 1] - e0;
+        if (n_tiles <= 0) continue;
+        const int g = w.h0 / a.group;
+        if (is_k) {
+          if (!mbar_wait(wc, q_empty, (item_n & 1u) ^ 1u, ST_TIMEOUT_EMPTY)) break;
+          mbar_expect_tx(q_full, L::Q_BYTES);
+          const int rows = 128 / a.hp;
+          for (int hh = 0; hh < a.hp; ++hh)
+            for (int s = 0; s < SLABS; ++s)
+              tma_load_2d(smem + s * 128 * 128 + hh * rows * 128, &tmQ, (w.h0 + hh) * D + s * 64, w.qb * 128 + w.row0, q_full);
         }
-        if (!mbar_wait(wc, &empty[st], ph ^ 1u, ST_TIMEOUT_EMPTY)) break;
-        const int kv0 = j * 128 + (t & 1) * KT;
-        mbar_expect_tx(&full[st], L::KV_TILE);
-        for (int s = 0; s < SLABS; ++s) tma_load_2d(smem + base + st * L::KV_TILE + s * KT * 128, tm, g * D + s * 64, kv0, &full[st]);
+        for (int t = 0; t < 2 * n_tiles; ++t, ++cnt) {
+          const int j = a.tile_blocks[e0 + (t >> 1)];
+          if (j < 0 || j >= a.nb) {
+            *abort_flag = 1;
+            atomicCAS(status, 0, ST_BAD_INDEX);
+            ok = false;
+            break;
+          }
+          const uint32_t st = cnt % NS, ph = (cnt / NS) & 1u;
+          if (!mbar_wait(wc, &empty[st], ph ^ 1u, ST_TIMEOUT_EMPTY)) { ok = false; break; }
+          const int kv0 = j * 128 + (t & 1) * KH;
+          mbar_expect_tx(&full[st], L::KV_HALF);
+          for (int s = 0; s < SLABS; ++s) tma_load_2d(smem + base + st * L::KV_HALF + s * KH * 128, tm, g * D + s * 64, kv0, &full[st]);
+        }
+        ++item_n;
       }
       if (*abort_flag) {
         // bounded wait for copies of this CTA that may still be in flight
         if (is_k)
-          for (int spin = 0; spin < 4096 && !mbar_try_wait(q_full, 0); ++spin) {}
-        for (int t = issued > 2 ? issued - 2 : 0; t < issued; ++t)
-          for (int spin = 0; spin < 4096 && !mbar_try_wait(&full[t & 1], (t >> 1) & 1u); ++spin) {}
+          for (int spin = 0; spin < 4096 && !mbar_try_wait(q_full, (item_n & 1u) ^ 1u); ++spin) {}
+        for (uint32_t c = cnt > static_cast<uint32_t>(NS) ? cnt - NS : 0; c < cnt; ++c)
+          for (int spin = 0; spin < 4096 && !mbar_try_wait(&full[c % NS], (c / NS) & 1u); ++spin) {}
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && n_sub > 0) {
+    if (lane == 0) {
       const uint32_t q_addr = smem_u32(smem);
-      const uint32_t p_addr = smem_u32(smem + L::P_OFF);
-      auto issue_s = [&](int t) {
-        const int st = t & 1;
-        const uint32_t k_addr = smem_u32(smem + L::K_OFF + st * L::KV_TILE);
-        const uint32_t d_tmem = tmem_base + (t & 1) * KT;
-#pragma unroll
-        for (int s = 0; s < SLABS; ++s) {
-          const uint64_t ad = make_smem_desc_sw128(q_addr + s * 128 * 128, 16, 1024);
-          const uint64_t bd = make_smem_desc_sw128(k_addr + s * KT * 128, 16, 1024);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) umma_f16_ss(d_tmem, ad + 2 * k, bd + 2 * k, IDESC_S, (s | k) != 0);
-        }
-        umma_commit(&k_empty[st]);       // the K stage may be refilled as soon as these MMAs have read it
-        umma_commit(&s_full[t & 1]);
-      };
-      bool ok = mbar_wait(wc, q_full, 0, ST_TIMEOUT_FULL);
-      if (ok) ok = mbar_wait(wc, &k_full[0], 0, ST_TIMEOUT_FULL);
-      if (ok) {
-        tc_fence_after();
-        issue_s(0);
-      }
-      for (int t = 0; t < n_sub && ok; ++t) {
-        const int st = t & 1;
-        const uint32_t ph = (t >> 1) & 1u;
-        if (t + 1 < n_sub) {
-          // S buffer (t+1)&1 was last read by the softmax of sub-tile t-1, which arrived on p_ready before P V (t-1) was issued
-          if (!mbar_wait(wc, &k_full[(t + 1) & 1], ((t + 1) >> 1) & 1u, ST_TIMEOUT_FULL)) break;
+      uint32_t kc = 0, vc = 0, gt = 0, item_n = 0;  // K / V stages consumed, tiles issued, items so far
+      bool ok = true;
+      auto issue_s = [&](uint32_t g) -> bool {  // both halves of S for tile g into S buffer g & 1
+        for (int hf = 0; hf < 2; ++hf, ++kc) {
+          const uint32_t st = kc % NS;
+          if (!mbar_wait(wc, &k_full[st], (kc / NS) & 1u, ST_TIMEOUT_FULL)) return false;
           tc_fence_after();
-          issue_s(t + 1);
-        }
-        if (!mbar_wait(wc, p_ready, t & 1u, ST_TIMEOUT_OTHER)) break;
-        if (!mbar_wait(wc, &v_full[st], ph, ST_TIMEOUT_FULL)) break;
-        tc_fence_after();
-        const uint32_t v_addr = smem_u32(smem + L::V_OFF + st * L::KV_TILE);
-        const uint64_t pd = make_smem_desc_sw128(p_addr, 16, 1024);
-        // V sub-tile: slab s holds head-dim columns [64 s, 64 s + 64) of 64 keys, one key per 128-byte row:
-        // MN-major B operand, 64-column groups KT*128 bytes apart (LBO), 8-key groups 1024 bytes apart (SBO)
-        const uint64_t vd = make_smem_desc_sw128(v_addr, KT * 128, 1024);
+          const uint32_t k_addr = smem_u32(smem + L::K_OFF + st * L::KV_HALF);
+          const uint32_t d_tmem = tmem_base + (g & 1u) * 128 + hf * KH;
 #pragma unroll
-        for (int k = 0; k < 4; ++k)  // 16 keys per step: 32 bytes along P's rows, 16 rows (2048 bytes) down V
-          umma_f16_ss(tmem_base + L::O_COL, pd + 2 * k, vd + 128 * k, IDESC_O, (t | k) != 0);
-        umma_commit(&v_empty[st]);
-        umma_commit(o_done);
+          for (int s = 0; s < SLABS; ++s) {
+            const uint64_t ad = make_smem_desc_sw128(q_addr + s * 128 * 128, 16, 1024);
+            const uint64_t bd = make_smem_desc_sw128(k_addr + s * KH * 128, 16, 1024);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) umma_f16_ss(d_tmem, ad + 2 * k, bd + 2 * k, IDESC_S, (s | k) != 0);
+          }
+          umma_commit(&k_empty[st]);  // the K stage may be refilled as soon as these MMAs have read it
+          umma_commit(&s_full[(g & 1u) * 2 + hf]);
+        }
+        return true;
+      };
+      for (int it = blockIdx.x; it < a.n_items && ok; it += gridDim.x) {
+        const AttnItem w = attn_item(a, it);
+        const int n_tiles = a.tile_offsets[w.qb + 1] - a.tile_offsets[w.qb];
+        if (n_tiles <= 0) continue;
+        if (!mbar_wait(wc, q_full, item_n & 1u, ST_TIMEOUT_FULL)) break;
+        tc_fence_after();
+        if (!issue_s(gt)) break;
+        for (int i = 0; i < n_tiles && ok; ++i) {
+          const uint32_t g = gt + i;
+          if (i + 1 < n_tiles) {
+            // S buffer (g+1)&1 last held P of tile g-1, whose P V MMAs were issued before these
+            if (!issue_s(g + 1)) { ok = false; break; }
+          } else {
+            umma_commit(q_empty);  // Q may be replaced once the last S MMAs of the item have read it
+          }
+          if (!mbar_wait(wc, p_ready, g & 1u, ST_TIMEOUT_OTHER)) { ok = false; break; }
+          if (i == 0 && item_n > 0 && !mbar_wait(wc, o_free, (item_n - 1) & 1u, ST_TIMEOUT_OTHER)) { ok = false; break; }
+          for (int hf = 0; hf < 2 && ok; ++hf, ++vc) {
+            const uint32_t st = vc % NS;
+            if (!mbar_wait(wc, &v_full[st], (vc / NS) & 1u, ST_TIMEOUT_FULL)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t v_addr = smem_u32(smem + L::V_OFF + st * L::KV_HALF);
+            // V stage: slab s holds head-dim columns [64 s, 64 s + 64) of 64 keys, one key per 128-byte row:
+            // MN-major B operand, 64-column groups KH*128 bytes apart (LBO), 8-key groups 1024 bytes apart (SBO)
+            const uint64_t vd = make_smem_desc_sw128(v_addr, KH * 128, 1024);
+            const uint32_t p_tmem = tmem_base + (g & 1u) * 128 + hf * KH;  // packed bf16 P: 16 keys per 8 columns
+#pragma unroll
+            for (int k = 0; k < 4; ++k)  // 16 keys per step: 8 columns along P, 16 rows (2048 bytes) down V
+              umma_f16_ts(tmem_base + L::O_COL, p_tmem + 8 * k, vd + 128 * k, IDESC_O, (i | hf | k) != 0);
+            umma_commit(&v_empty[st]);
+          }
+          if (ok) umma_commit(o_done);
+        }
+        gt += n_tiles;
+        ++item_n;
       }
     }
-  } else if (n_sub > 0) {
-    const int q = warp & 3;
-    const int row = q * 32 + lane;
-    const int tq = qb * 128 + row;  // stream position of this thread's query row
-    const int art_q = a.art[tq], pos_q = a.pos[tq];
-    const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
-    uint8_t* p_smem = smem + L::P_OFF;
-    int* wmeta = meta + (warp - 2) * 2 * 3 * KT;  // this warp's private copies of the key metadata
-    float m_ref = -INFINITY, l_run = 0.f;
+  } else {
+    // softmax warps 2..9
+    const int wg = (warp - 2) >> 2;  // 0: keys [0, 64) of a tile, 1: keys [64, 128)
+    const int qd = warp & 3;         // TMEM lane quarter this warp may access
+    const int row = qd * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>(qd * 32) << 16;
+    uint32_t gt = 0, item_n = 0;
     bool alive = true;
-
-    // key metadata of sub-tile t (art, end, pos of its 64 keys): each lane fetches 2 keys one iteration ahead
-    int pre[6] = {0, 0, 0, 0, 0, 0};
-    auto fetch_meta = [&](int t) {
-      const int j = block_of(t >> 1);
-      if (!(flags_of(t >> 1) & 2) && j >= 0 && j < a.nb) {
-        const int kv0 = j * 128 + (t & 1) * KT;
-        pre[0] = a.art[kv0 + lane], pre[1] = a.art[kv0 + 32 + lane];
-        pre[2] = a.end[kv0 + lane], pre[3] = a.end[kv0 + 32 + lane];
-        pre[4] = a.pos[kv0 + lane], pre[5] = a.pos[kv0 + 32 + lane];
+    // the list bounds, first entry and first visibility word of an item are fetched while the item before it is processed
+    const int rows_per_head = 128 / a.hp;
+    int pe0 = 0, pe1 = 0, pj = 0, pf = 0;
+    uint64_t pbits = 0;
+    auto first_entry = [&](const AttnItem& w, int e0, int e1) {
+      if (e1 > e0) {
+        pj = a.tile_blocks[e0];
+        pf = a.tile_flags[e0];
+        pbits = a.tile_bits[(static_cast<int64_t>(e0) * 2 + wg) * 128 + w.row0 + (row % rows_per_head)];
       }
     };
-    auto stash_meta = [&](int t) {
-      int* mb = wmeta + (t & 1) * 3 * KT;
-      mb[lane] = pre[0], mb[32 + lane] = pre[1];
-      mb[KT + lane] = pre[2], mb[KT + 32 + lane] = pre[3];
-      mb[2 * KT + lane] = pre[4], mb[2 * KT + 32 + lane] = pre[5];
-    };
-    fetch_meta(0);
-    stash_meta(0);
-    __syncwarp();
-
-    for (int t = 0; t < n_sub; ++t) {
-      const int j = block_of(t >> 1);
-      const bool no_mask = (flags_of(t >> 1) & 2) != 0;
-      const int kv0 = j * 128 + (t & 1) * KT;
-      const int* kart = wmeta + (t & 1) * 3 * KT;
-      const int* kend = kart + KT;
-      const int* kpos = kend + KT;
-      if (t + 1 < n_sub) fetch_meta(t + 1);  // in flight while this sub-tile is processed
-      bool got = j >= 0 && j < a.nb && mbar_wait(wc, &s_full[t & 1], (t >> 1) & 1u, ST_TIMEOUT_TMEM);
-      if (!__all_sync(0xffffffffu, got)) { alive = false; break; }
-      tc_fence_after();
-      uint32_t v0[32], v1[32];
-      tmem_ld_x32(tmem_base + lane_off + (t & 1) * KT, v0);
-      tmem_ld_x32(tmem_base + lane_off + (t & 1) * KT + 32, v1);
-      tmem_wait_ld();
-      float s[KT];
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        s[i] = __uint_as_float(v0[i]) * a.scale_log2;
-        s[32 + i] = __uint_as_float(v1[i]) * a.scale_log2;
+    if (static_cast<int>(blockIdx.x) < a.n_items) {
+      const AttnItem w = attn_item(a, blockIdx.x);
+      pe0 = a.tile_offsets[w.qb], pe1 = a.tile_offsets[w.qb + 1];
+      first_entry(w, pe0, pe1);
+    }
+    for (int it = blockIdx.x; it < a.n_items && alive; it += gridDim.x) {
+      const AttnItem w = attn_item(a, it);
+      const int e0 = pe0;
+      const int n_tiles = pe1 - pe0;
+      int j_next = pj, f_next = pf;
+      uint64_t bits_next = (pf & 2) ? ~0ull : pbits;
+      const int it_n = it + gridDim.x;
+      const bool have_n = it_n < a.n_items;
+      const AttnItem w_n = attn_item(a, have_n ? it_n : it);
+      if (have_n) pe0 = a.tile_offsets[w_n.qb], pe1 = a.tile_offsets[w_n.qb + 1];  // consumed at the end of this item
+      if (n_tiles <= 0) {
+        if (have_n) first_entry(w_n, pe0, pe1);
+        continue;
       }
-      if (!no_mask) {
-        // branch-free: every operand is loaded unconditionally (vector loads of the warp's metadata copy), the rule is a chain
-        // of bitwise ANDs; short-circuit evaluation here compiles to ~200 divergent branches per sub-tile
-        const bool q_real = art_q >= 0;
-        const bool windowed = a.window > 0;
+      const int head = w.h0 + row / rows_per_head;
+      const int tq = w.qb * 128 + w.row0 + (row % rows_per_head);  // stream position of this thread's query row
+      const int rowb = w.row0 + (row % rows_per_head);            // row within the query block
+      TR(t_item0);
+      float m_ref = -INFINITY, l_run = 0.f;
+
+      for (int i = 0; i < n_tiles; ++i) {
+        const uint32_t g = gt + i;
+        const int j = j_next;
+        const bool no_mask = (f_next & 2) != 0;
+        const uint64_t bits = bits_next;
+        if (i + 1 < n_tiles) {  // in flight while this tile is processed
+          j_next = a.tile_blocks[e0 + i + 1];
+          f_next = a.tile_flags[e0 + i + 1];
+          bits_next = (f_next & 2) ? ~0ull : a.tile_bits[(static_cast<int64_t>(e0 + i + 1) * 2 + wg) * 128 + rowb];
+        }
+        TR(t0);
+        bool got = j >= 0 && j < a.nb && mbar_wait(wc, &s_full[(g & 1u) * 2 + wg], (g >> 1) & 1u, ST_TIMEOUT_TMEM);
+        TR(t1);
+        float s[KH];
+        float mx = -INFINITY;
+        const uint32_t s_tmem = tmem_base + lane_off + (g & 1u) * 128 + wg * KH;
+        if (__all_sync(0xffffffffu, got)) {
+          tc_fence_after();
+          uint32_t v0[32], v1[32];
+          tmem_ld_x32(s_tmem, v0);
+          tmem_ld_x32(s_tmem + 32, v1);
+          tmem_wait_ld();
 #pragma unroll
-        for (int i4 = 0; i4 < KT / 4; ++i4) {
-          const int4 ka = reinterpret_cast<const int4*>(kart)[i4];
-          const int4 ke = reinterpret_cast<const int4*>(kend)[i4];
-          const int4 kp = reinterpret_cast<const int4*>(kpos)[i4];
-          const int kas[4] = {ka.x, ka.y, ka.z, ka.w}, kes[4] = {ke.x, ke.y, ke.z, ke.w}, kps[4] = {kp.x, kp.y, kp.z, kp.w};
+          for (int c = 0; c < 32; ++c) s[c] = __uint_as_float(v0[c]), s[32 + c] = __uint_as_float(v1[c]);
+          if (!no_mask) {
+            const uint32_t b_lo = static_cast<uint32_t>(bits), b_hi = static_cast<uint32_t>(bits >> 32);
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int i = 4 * i4 + u;
-            const int tk = kv0 + i;
-            const bool tree = (tk <= tq) & q_real & (kas[u] == art_q) & (tq < kes[u]);
-            const bool win = !windowed | (pos_q - kps[u] < a.window);
-            const bool vis = (tree & win) | (tk == tq);
-            s[i] = vis ? s[i] : -INFINITY;
+            for (int c = 0; c < 32; ++c) {
+              s[c] = (b_lo & (1u << c)) ? s[c] : -INFINITY;
+              s[32 + c] = (b_hi & (1u << c)) ? s[32 + c] : -INFINITY;
+            }
+          }
+#pragma unroll
+          for (int c = 0; c < KH; ++c) mx = fmaxf(mx, s[c]);
+        } else {
+          got = false;
+        }
+        // the two groups exchange their halves' row maxima: every decision below is taken on the maximum over the whole tile
+        float* xq = xchg + (g & 1u) * 256;
+        xq[wg * 128 + row] = mx;
+        TR(t2);
+        if (!bar_red_and(1 + qd, 64, got)) { alive = false; break; }  // the two warps that share these rows leave together
+        TR(t3);
+        mx = fmaxf(mx, xq[(wg ^ 1) * 128 + row]) * a.scale_log2;
+        // move the reference maximum only when the row's maximum has grown by more than the threshold
+        float alpha = 1.f;
+        if (mx - m_ref > RESCALE_THRESHOLD) {  // false for NaN (-inf minus -inf): a row that has seen nothing yet
+          alpha = fast_exp2(m_ref - mx);
+          m_ref = mx;
+        }
+        const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
+        float sum0 = 0.f, sum1 = 0.f;
+        uint32_t pk[KH / 2];
+#pragma unroll
+        for (int c = 0; c < KH / 2; ++c) {
+          const float p0 = fast_exp2(fmaf(s[2 * c], a.scale_log2, neg_m)), p1 = fast_exp2(fmaf(s[2 * c + 1], a.scale_log2, neg_m));
+          sum0 += p0;
+          sum1 += p1;
+          pk[c] = pack_bf16x2(p0, p1);
+        }
+        l_run = l_run * alpha + (sum0 + sum1);
+        TR(t4);
+        if (i > 0) {
+          // P V of the previous tile is waited for at every tile, not only before a rescale: a parity wait is only unambiguous
+          // while the waiter is at most one phase ahead of the barrier
+          const bool done = mbar_wait(wc, o_done, (g - 1) & 1u, ST_TIMEOUT_TMEM);
+          if (__any_sync(0xffffffffu, alpha != 1.f) && __all_sync(0xffffffffu, done)) {
+            // every P V issued so far has completed and none is in flight until all 256 threads have arrived on p_ready:
+            // this group rescales its half of the O columns
+            tc_fence_after();
+#pragma unroll 1
+            for (int c = 0; c < D / 64; ++c) {
+              uint32_t o[32];
+              const uint32_t o_tmem = tmem_base + lane_off + L::O_COL + wg * (D / 2) + c * 32;
+              tmem_ld_x32(o_tmem, o);
+              tmem_wait_ld();
+#pragma unroll
+              for (int x = 0; x < 32; ++x) o[x] = __float_as_uint(__uint_as_float(o[x]) * alpha);
+              tmem_st_x32(o_tmem, o);
+            }
           }
         }
-      }
-      float mx = s[0];
-#pragma unroll
-      for (int i = 1; i < KT; ++i) mx = fmaxf(mx, s[i]);
-      // move the reference maximum only when the row's maximum has grown by more than the threshold
-      float alpha = 1.f;
-      if (mx - m_ref > RESCALE_THRESHOLD) {  // false for NaN (-inf minus -inf): a row that has seen nothing yet
-        alpha = fast_exp2(m_ref - mx);
-        m_ref = mx;
-      }
-      const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-      float sum = 0.f;
-      uint32_t pk[KT / 2];
-#pragma unroll
-      for (int i = 0; i < KT / 2; ++i) {
-        const float p0 = fast_exp2(s[2 * i] - m_use), p1 = fast_exp2(s[2 * i + 1] - m_use);
-        sum += p0 + p1;
-        pk[i] = pack_bf16x2(p0, p1);
-      }
-      l_run = l_run * alpha + sum;
-      if (t > 0) {
-        // P V of the previous sub-tile has completed: the P tile may be overwritten and O is stable
-        got = mbar_wait(wc, o_done, (t - 1) & 1u, ST_TIMEOUT_TMEM);
-        if (!__all_sync(0xffffffffu, got)) { alive = false; break; }
-        tc_fence_after();
-      }
-#pragma unroll
-      for (int c = 0; c < 8; ++c)
-        *reinterpret_cast<uint4*>(p_smem + sw128_offset(row, c)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-      if (t > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-#pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t o[32];
-          tmem_ld_x32(tmem_base + lane_off + L::O_COL + c * 32, o);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st_x32(tmem_base + lane_off + L::O_COL + c * 32, o);
-        }
-        tmem_wait_st();
-      }
-      fence_proxy_async_smem();
-      tc_fence_before();
-      mbar_arrive(p_ready);
-      if (t + 1 < n_sub) {
-        stash_meta(t + 1);  // buffer (t+1)&1 was last read in iteration t-1 by this warp only
         __syncwarp();
+        TR(t5);
+        tmem_st_x32(s_tmem, pk);  // P over the first 32 columns of the S half this thread has already read
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(p_ready);
+        TR(t6);
+        TR_ADD(0, t1 - t0); TR_ADD(1, t2 - t1); TR_ADD(2, t3 - t2); TR_ADD(3, t4 - t3); TR_ADD(4, t5 - t4); TR_ADD(5, t6 - t5); TR_ADD(6, 1);
       }
-    }
+      if (!alive) break;
+      gt += n_tiles;
 
-    if (alive) {
-      const bool got = mbar_wait(wc, o_done, (n_sub - 1) & 1u, ST_TIMEOUT_TMEM);
-      if (__all_sync(0xffffffffu, got)) {
-        tc_fence_after();
-        const float inv = 1.f / l_run;  // every row sees at least itself, so l_run > 0
-        __nv_bfloat16* dst = a.out + static_cast<int64_t>(tq) * a.out_pitch + h * D;
+      // end of the item: O / l for this group's half of the columns
+      const uint32_t g_last = gt - 1;
+      float* xq = xchg + 2 * 256;  // its own buffer: the next item's first tile may already be writing maxima
+      xq[wg * 128 + row] = l_run;
+      if (have_n) first_entry(w_n, pe0, pe1);  // lands while O is read out
+      TR(t_e0);
+      const bool got = mbar_wait(wc, o_done, g_last & 1u, ST_TIMEOUT_TMEM);
+      if (!bar_red_and(1 + qd, 64, got)) { alive = false; break; }
+      TR(t_e1);
+      tc_fence_after();
+      const float inv = 1.f / (l_run + xq[(wg ^ 1) * 128 + row]);  // every row sees at least itself, so the sum is positive
+      __nv_bfloat16* dst = a.out + static_cast<int64_t>(tq) * a.out_pitch + head * D + wg * (D / 2);
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t o[32];
-          tmem_ld_x32(tmem_base + lane_off + L::O_COL + c * 32, o);
-          tmem_wait_ld();
-          uint32_t w[16];
+      for (int c = 0; c < D / 64; c += 2) {  // 64 columns at a time: both TMEM loads in flight together
+        uint32_t o0[32], o1[32];
+        __syncwarp();
+        tmem_ld_x32(tmem_base + lane_off + L::O_COL + wg * (D / 2) + c * 32, o0);
+        tmem_ld_x32(tmem_base + lane_off + L::O_COL + wg * (D / 2) + c * 32 + 32, o1);
+        tmem_wait_ld();
+        if (c + 2 >= D / 64) {  // O is in registers: the next item's first P V may overwrite it
+          tc_fence_before();
+          mbar_arrive(o_free);
+        }
 #pragma unroll
-          for (int i = 0; i < 16; ++i) w[i] = pack_bf16x2(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv);
+        for (int hfc = 0; hfc < 2; ++hfc) {
+          const uint32_t (&o)[32] = hfc ? o1 : o0;
+          uint32_t wv[16];
 #pragma unroll
-          for (int i = 0; i < 4; ++i)
-            *reinterpret_cast<uint4*>(dst + c * 32 + i * 8) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+          for (int x = 0; x < 16; ++x) wv[x] = pack_bf16x2(__uint_as_float(o[2 * x]) * inv, __uint_as_float(o[2 * x + 1]) * inv);
+          const uint32_t lo[8] = {wv[0], wv[1], wv[2], wv[3], wv[4], wv[5], wv[6], wv[7]};
+          const uint32_t hi[8] = {wv[8], wv[9], wv[10], wv[11], wv[12], wv[13], wv[14], wv[15]};
+          stg_v8(dst + (c + hfc) * 32, lo);
+          stg_v8(dst + (c + hfc) * 32 + 16, hi);
         }
       }
+      TR(t_e2);
+      TR_ADD(8, t_e1 - t_e0); TR_ADD(9, t_e2 - t_e1); TR_ADD(10, t_e2 - t_item0); TR_ADD(11, 1);
+      ++item_n;
     }
   }
 
@@ -355,6 +440,44 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, L::TMEM_COLS);
+  }
+}
+
+// Visibility words of a packed stream: for list entry e (query block qb against key block j), key half hf and row r of the query
+// block, bit c of bits[(e * 2 + hf) * 128 + r] says whether query t = 128 qb + r sees key k = 128 j + 64 hf + c:
+//   (k <= t && art[t] >= 0 && art[k] == art[t] && t < end[k] && (window <= 0 || pos[t] - pos[k] < window)) || t == k
+// One CTA per query block, thread = (row, half). Runs once per stream and mask type; every layer and head reads the result.
+__global__ void __launch_bounds__(256) tile_mask_bits_kernel(const int32_t* __restrict__ art, const int32_t* __restrict__ end,
+                                                             const int32_t* __restrict__ pos, int nb, int window,
+                                                             const int32_t* __restrict__ tile_offsets,
+                                                             const int32_t* __restrict__ tile_blocks, uint64_t* __restrict__ bits) {
+  __shared__ int k_art[128], k_end[128], k_pos[128];
+  const int qb = blockIdx.x;
+  const int r = threadIdx.x & 127, hf = threadIdx.x >> 7;
+  const int t = qb * 128 + r;
+  const int art_q = art[t], pos_q = pos[t];
+  const int e0 = tile_offsets[qb], e1 = tile_offsets[qb + 1];
+  for (int e = e0; e < e1; ++e) {
+    const int j = tile_blocks[e];
+    const bool valid = j >= 0 && j < nb;
+    __syncthreads();
+    if (threadIdx.x < 128 && valid) {
+      k_art[threadIdx.x] = art[j * 128 + threadIdx.x];
+      k_end[threadIdx.x] = end[j * 128 + threadIdx.x];
+      k_pos[threadIdx.x] = pos[j * 128 + threadIdx.x];
+    }
+    __syncthreads();
+    uint64_t word = 0;
+    if (valid) {
+      for (int c = 0; c < 64; ++c) {
+        const int kk = hf * 64 + c;
+        const int k = j * 128 + kk;
+        const bool tree = k <= t && art_q >= 0 && k_art[kk] == art_q && t < k_end[kk];
+        const bool win = window <= 0 || pos_q - k_pos[kk] < window;
+        if ((tree && win) || k == t) word |= 1ull << c;
+      }
+    }
+    bits[(static_cast<int64_t>(e) * 2 + hf) * 128 + r] = word;
   }
 }
 
@@ -368,17 +491,18 @@ static int launch_attn(const void* q, const void* k, const void* v, int64_t n, i
   if (!status) return SPINF_ERR_CUDA;
   CUtensorMap tmQ, tmK, tmV;
   int r;
-  if ((r = make_tmap_2d(&tmQ, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, q, n, static_cast<uint64_t>(H) * D, q_pitch * 2, 64, 128))) return r;
-  if ((r = make_tmap_2d(&tmK, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k, n, static_cast<uint64_t>(Hkv) * D, kv_pitch * 2, 64, KT))) return r;
-  if ((r = make_tmap_2d(&tmV, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, v, n, static_cast<uint64_t>(Hkv) * D, kv_pitch * 2, 64, KT))) return r;
+  if ((r = make_tmap_2d(&tmQ, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, q, n, static_cast<uint64_t>(H) * D, q_pitch * 2, 64, 128 / args.hp)))
+    return r;
+  if ((r = make_tmap_2d(&tmK, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k, n, static_cast<uint64_t>(Hkv) * D, kv_pitch * 2, 64, KH))) return r;
+  if ((r = make_tmap_2d(&tmV, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, v, n, static_cast<uint64_t>(Hkv) * D, kv_pitch * 2, 64, KH))) return r;
   auto kern = tree_attn_kernel<D>;
   static bool attr_set[64] = {false};
   if (!attr_set[dev]) {
     SPINF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
     attr_set[dev] = true;
   }
-  dim3 grid(static_cast<unsigned>(n / 128), static_cast<unsigned>(H));
-  kern<<<grid, 224, L::TOTAL, stream>>>(tmQ, tmK, tmV, args, status);
+  const int grid = args.n_items < sm_count() ? args.n_items : sm_count();
+  kern<<<grid, ATTN_THREADS, L::TOTAL, stream>>>(tmQ, tmK, tmV, args, status);
   SPINF_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -387,15 +511,27 @@ static int launch_attn(const void* q, const void* k, const void* v, int64_t n, i
 
 using namespace spinf;
 
+extern "C" int spinf_tile_mask_bits(const int32_t* art, const int32_t* end, const int32_t* pos, int64_t n, int32_t window,
+                                    const int32_t* tile_offsets, const int32_t* tile_blocks, uint64_t* bits, void* stream) {
+  SPINF_CHECK_ARG(art && end && pos && tile_offsets && tile_blocks && bits && n >= 0 && n % SPINF_BLOCK == 0 && n < (1ll << 30));
+  if (n == 0) return 0;
+  const int nb = static_cast<int>(n / SPINF_BLOCK);
+  tile_mask_bits_kernel<<<nb, 256, 0, static_cast<cudaStream_t>(stream)>>>(art, end, pos, nb, window, tile_offsets, tile_blocks, bits);
+  SPINF_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
 extern "C" int spinf_tree_attn_fwd(const void* q, const void* k, const void* v, void* out, int64_t n, int32_t H, int32_t Hkv,
                                    int32_t D, int64_t q_pitch, int64_t kv_pitch, int64_t out_pitch, const int32_t* art,
                                    const int32_t* end, const int32_t* pos, int32_t window, float scale, const int32_t* tile_offsets,
-                                   const int32_t* tile_blocks, const uint8_t* tile_flags, void* stream) {
-  SPINF_CHECK_ARG(q && k && v && out && art && end && pos && tile_offsets && tile_blocks && tile_flags);
+                                   const int32_t* tile_blocks, const uint8_t* tile_flags, const uint64_t* tile_bits, void* stream) {
+  SPINF_CHECK_ARG(q && k && v && out && art && end && pos && tile_offsets && tile_blocks && tile_flags && tile_bits);
   SPINF_CHECK_ARG(n >= 0 && n % SPINF_BLOCK == 0 && n < (1ll << 30) && H > 0 && Hkv > 0 && H % Hkv == 0 && H <= 65535);
   SPINF_CHECK_ARG(D == 128 || D == 256);
   SPINF_CHECK_ARG(q_pitch >= static_cast<int64_t>(H) * D && kv_pitch >= static_cast<int64_t>(Hkv) * D && out_pitch >= static_cast<int64_t>(H) * D);
-  SPINF_CHECK_ARG(q_pitch % 8 == 0 && kv_pitch % 8 == 0 && out_pitch % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0);
+  // rows of the output are written as 32-byte pieces
+  SPINF_CHECK_ARG(q_pitch % 8 == 0 && kv_pitch % 8 == 0 && out_pitch % 16 == 0 && (reinterpret_cast<uintptr_t>(out) & 31) == 0);
+  SPINF_CHECK_ARG(scale > 0.f && n / SPINF_BLOCK * static_cast<int64_t>(H) < (1ll << 31));
   if (n == 0) return 0;
   AttnArgs a;
   a.out = static_cast<__nv_bfloat16*>(out);
@@ -406,12 +542,25 @@ extern "C" int spinf_tree_attn_fwd(const void* q, const void* k, const void* v, 
   a.tile_offsets = tile_offsets;
   a.tile_blocks = tile_blocks;
   a.tile_flags = tile_flags;
+  a.tile_bits = tile_bits;
   a.nb = static_cast<int>(n / SPINF_BLOCK);
   a.H = H;
   a.group = H / Hkv;
+  a.hp = a.group % 2 == 0 ? 2 : 1;
+  a.n_items = a.nb * H;
   a.window = window;
   a.scale_log2 = scale * 1.4426950408889634f;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (D == 256) return launch_attn<256>(q, k, v, n, H, Hkv, q_pitch, kv_pitch, a, st);
   return launch_attn<128>(q, k, v, n, H, Hkv, q_pitch, kv_pitch, a, st);
 }
+
+#ifdef SPINF_TRACE
+extern "C" int spinf_attn_trace_read(unsigned long long* out) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out, spinf::g_attn_trace, sizeof(unsigned long long) * 16);
+  unsigned long long z[16] = {0};
+  cudaMemcpyToSymbol(spinf::g_attn_trace, z, sizeof(z));
+  return 0;
+}
+#endif
