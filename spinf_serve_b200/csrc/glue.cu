@@ -25,6 +25,26 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   for (int i = 0; i < nw; ++i) t += red[i];
   return t;
 }
+// One-barrier forms: each reduction of a row has its own array, so a value is only overwritten after every thread has passed a
+// later barrier (the next reduction's) and so has finished reading it.
+__device__ __forceinline__ float block_sum1(float v, float* red) {
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int i = 0; i < NORM_THREADS / 32; ++i) t += red[i];
+  return t;
+}
+__device__ __forceinline__ float block_max1(float v, float* red) {
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = red[0];
+#pragma unroll
+  for (int i = 1; i < NORM_THREADS / 32; ++i) t = fmaxf(t, red[i]);
+  return t;
+}
 __device__ __forceinline__ float block_max(float v, float* red) {
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   const int w = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -127,74 +147,88 @@ __device__ __forceinline__ uint2 quant8_packed(const uint4& u, const DivBy& div)
 }
 
 template <int NVEC, bool PLUS1>
-__global__ void __launch_bounds__(NORM_THREADS, NVEC <= 2 ? 4 : 2) fused_norm_kernel(const FusedNormArgs a) {
-  __shared__ float red[NORM_THREADS / 32];
-  const int64_t r = blockIdx.x;
-  const int64_t rin = a.rows ? a.rows[r] : r;
+__global__ void __launch_bounds__(NORM_THREADS, NVEC <= 2 ? 4 : 2) fused_norm_kernel(const FusedNormArgs a, int64_t n_out) {
+  __shared__ float red[3][NORM_THREADS / 32];  // one array per reduction of a row
   const int nvec = a.hidden / 8;
   const uint4 zero = make_uint4(0, 0, 0, 0);
-  uint4 cur[NVEC], rr[NVEC];
+  // a CTA walks rows blockIdx.x, blockIdx.x + gridDim.x, ...; the streamed loads of the next row are issued before the current
+  // row's reductions, so every CTA keeps a row in flight while it works on another
+  uint4 ny[NVEC], nr[NVEC];
+  auto load_row = [&](int64_t r) {
+    const int64_t rin = a.rows ? a.rows[r] : r;
 #pragma unroll
-  for (int i = 0; i < NVEC; ++i) {
-    const int v = threadIdx.x + i * NORM_THREADS;
-    const bool on = v < nvec;
-    cur[i] = on ? *reinterpret_cast<const uint4*>(a.y + rin * a.hidden + v * 8) : zero;
-    rr[i] = on && a.residual ? *reinterpret_cast<const uint4*>(a.residual + r * a.hidden + v * 8) : zero;
-  }
-  if (a.w1) {
+    for (int i = 0; i < NVEC; ++i) {
+      const int v = threadIdx.x + i * NORM_THREADS;
+      const bool on = v < nvec;
+      ny[i] = on ? *reinterpret_cast<const uint4*>(a.y + rin * a.hidden + v * 8) : zero;
+      nr[i] = on && a.residual ? *reinterpret_cast<const uint4*>(a.residual + r * a.hidden + v * 8) : zero;
+    }
+  };
+  if (static_cast<int64_t>(blockIdx.x) < n_out) load_row(blockIdx.x);
+  // with a single reduction per row nothing separates a row's reads of its array from the next row's writes
+  const bool lone_reduction = (a.w1 != nullptr) + (a.w2 != nullptr) + (a.out_x8 != nullptr) < 2;
+  for (int64_t r = blockIdx.x; r < n_out; r += gridDim.x) {
+    if (lone_reduction) __syncthreads();
+    uint4 cur[NVEC], rr[NVEC];
+#pragma unroll
+    for (int i = 0; i < NVEC; ++i) cur[i] = ny[i], rr[i] = nr[i];
+    if (r + gridDim.x < n_out) load_row(r + gridDim.x);
+    if (a.w1) {
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < NVEC; ++i) ss = sumsq4(cur[i], ss);
+      const float inv = inv_sqrt(block_sum1(ss, red[0]) / a.hidden + a.eps);
+#pragma unroll
+      for (int i = 0; i < NVEC; ++i) {
+        const int v = threadIdx.x + i * NORM_THREADS;
+        const uint4 w = v < nvec ? *reinterpret_cast<const uint4*>(a.w1 + v * 8) : zero;
+        cur[i] = make_uint4(scale_pair<PLUS1>(cur[i].x, inv, w.x), scale_pair<PLUS1>(cur[i].y, inv, w.y),
+                            scale_pair<PLUS1>(cur[i].z, inv, w.z), scale_pair<PLUS1>(cur[i].w, inv, w.w));
+      }
+    }
+    if (a.residual) {
+#pragma unroll
+      for (int i = 0; i < NVEC; ++i)
+        cur[i] = make_uint4(bf2_add(cur[i].x, rr[i].x), bf2_add(cur[i].y, rr[i].y), bf2_add(cur[i].z, rr[i].z), bf2_add(cur[i].w, rr[i].w));
+    }
+    if (a.out_h) {
+#pragma unroll
+      for (int i = 0; i < NVEC; ++i) {
+        const int v = threadIdx.x + i * NORM_THREADS;
+        if (v < nvec) *reinterpret_cast<uint4*>(a.out_h + r * a.hidden + v * 8) = cur[i];
+      }
+    }
+    if (!a.w2) continue;
     float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < NVEC; ++i) ss = sumsq4(cur[i], ss);
-    const float inv = inv_sqrt(block_sum(ss, red) / a.hidden + a.eps);
+    for (int i = 0; i < NVEC; ++i) {
+      const int v = threadIdx.x + i * NORM_THREADS;
+      if (v < nvec) ss = sumsq4(cur[i], ss);  // (lanes past the row may hold a norm of zeros times 1 + w: keep them out)
+    }
+    const float inv2 = inv_sqrt(block_sum1(ss, red[1]) / a.hidden + a.eps);
+    uint32_t amax2 = 0u;
 #pragma unroll
     for (int i = 0; i < NVEC; ++i) {
       const int v = threadIdx.x + i * NORM_THREADS;
-      const uint4 w = v < nvec ? *reinterpret_cast<const uint4*>(a.w1 + v * 8) : zero;
-      cur[i] = make_uint4(scale_pair<PLUS1>(cur[i].x, inv, w.x), scale_pair<PLUS1>(cur[i].y, inv, w.y), scale_pair<PLUS1>(cur[i].z, inv, w.z),
-                          scale_pair<PLUS1>(cur[i].w, inv, w.w));
+      if (v < nvec) {
+        const uint4 w = *reinterpret_cast<const uint4*>(a.w2 + v * 8);
+        cur[i] = make_uint4(scale_pair<PLUS1>(cur[i].x, inv2, w.x), scale_pair<PLUS1>(cur[i].y, inv2, w.y),
+                            scale_pair<PLUS1>(cur[i].z, inv2, w.z), scale_pair<PLUS1>(cur[i].w, inv2, w.w));
+        amax2 = bf2_max(bf2_max(amax2, cur[i].x & 0x7fff7fffu),
+                        bf2_max(cur[i].y & 0x7fff7fffu, bf2_max(cur[i].z & 0x7fff7fffu, cur[i].w & 0x7fff7fffu)));
+        if (a.out_norm) *reinterpret_cast<uint4*>(a.out_norm + r * a.hidden + v * 8) = cur[i];
+      }
     }
-  }
-  if (a.residual) {
-#pragma unroll
-    for (int i = 0; i < NVEC; ++i)
-      cur[i] = make_uint4(bf2_add(cur[i].x, rr[i].x), bf2_add(cur[i].y, rr[i].y), bf2_add(cur[i].z, rr[i].z), bf2_add(cur[i].w, rr[i].w));
-  }
-  if (a.out_h) {
+    if (!a.out_x8) continue;
+    const float amax = fmaxf(bf2_lo(amax2), bf2_hi(amax2));
+    const float s = __fdiv_rn(fmaxf(block_max1(amax, red[2]), 1e-12f), 448.f);
+    if (threadIdx.x == 0) a.out_xs[r] = s;
+    const DivBy div = make_div_by(s);
 #pragma unroll
     for (int i = 0; i < NVEC; ++i) {
       const int v = threadIdx.x + i * NORM_THREADS;
-      if (v < nvec) *reinterpret_cast<uint4*>(a.out_h + r * a.hidden + v * 8) = cur[i];
+      if (v < nvec) *reinterpret_cast<uint2*>(a.out_x8 + r * a.hidden + v * 8) = quant8_packed(cur[i], div);
     }
-  }
-  if (!a.w2) return;
-  float ss = 0.f;
-#pragma unroll
-  for (int i = 0; i < NVEC; ++i) {
-    const int v = threadIdx.x + i * NORM_THREADS;
-    if (v < nvec) ss = sumsq4(cur[i], ss);  // (lanes past the row may hold a norm of zeros times 1 + w: keep them out)
-  }
-  const float inv2 = inv_sqrt(block_sum(ss, red) / a.hidden + a.eps);
-  uint32_t amax2 = 0u;
-#pragma unroll
-  for (int i = 0; i < NVEC; ++i) {
-    const int v = threadIdx.x + i * NORM_THREADS;
-    if (v < nvec) {
-      const uint4 w = *reinterpret_cast<const uint4*>(a.w2 + v * 8);
-      cur[i] = make_uint4(scale_pair<PLUS1>(cur[i].x, inv2, w.x), scale_pair<PLUS1>(cur[i].y, inv2, w.y), scale_pair<PLUS1>(cur[i].z, inv2, w.z),
-                          scale_pair<PLUS1>(cur[i].w, inv2, w.w));
-      amax2 = bf2_max(bf2_max(amax2, cur[i].x & 0x7fff7fffu), bf2_max(cur[i].y & 0x7fff7fffu, bf2_max(cur[i].z & 0x7fff7fffu, cur[i].w & 0x7fff7fffu)));
-      if (a.out_norm) *reinterpret_cast<uint4*>(a.out_norm + r * a.hidden + v * 8) = cur[i];
-    }
-  }
-  if (!a.out_x8) return;
-  const float amax = fmaxf(bf2_lo(amax2), bf2_hi(amax2));
-  const float s = __fdiv_rn(fmaxf(block_max(amax, red), 1e-12f), 448.f);
-  if (threadIdx.x == 0) a.out_xs[r] = s;
-  const DivBy div = make_div_by(s);
-#pragma unroll
-  for (int i = 0; i < NVEC; ++i) {
-    const int v = threadIdx.x + i * NORM_THREADS;
-    if (v < nvec) *reinterpret_cast<uint2*>(a.out_x8 + r * a.hidden + v * 8) = quant8_packed(cur[i], div);
   }
 }
 
@@ -393,14 +427,16 @@ extern "C" int spinf_fused_norm(const void* y, const int64_t* rows, const void* 
   a.hidden = static_cast<int>(hidden);
   a.eps = eps;
   a.plus1 = plus1;
-  const int per_thread = static_cast<int>((hidden / 8 + NORM_THREADS - 1) / NORM_THREADS);
-  const unsigned grid = static_cast<unsigned>(n_out);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int per_thread = static_cast<int>((hidden / 8 + NORM_THREADS - 1) / NORM_THREADS);
+  // resident CTAs only (4 per SM at up to 2 vectors per thread, else 2): each walks its share of the rows
+  const int64_t resident = static_cast<int64_t>(sm_count()) * (per_thread <= 2 ? 4 : 2);
+  const unsigned grid = static_cast<unsigned>(n_out < resident ? n_out : resident);
 #define SPINF_NORM_CASE(NV)                                                      \
   if (plus1)                                                                     \
-    fused_norm_kernel<NV, true><<<grid, NORM_THREADS, 0, st>>>(a);               \
+    fused_norm_kernel<NV, true><<<grid, NORM_THREADS, 0, st>>>(a, n_out);        \
   else                                                                           \
-    fused_norm_kernel<NV, false><<<grid, NORM_THREADS, 0, st>>>(a);              \
+    fused_norm_kernel<NV, false><<<grid, NORM_THREADS, 0, st>>>(a, n_out);       \
   break;
   switch (per_thread) {
     case 1: SPINF_NORM_CASE(1)
