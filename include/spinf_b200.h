@@ -162,11 +162,12 @@ int spinf_tile_mask_bits(const int32_t* art, const int32_t* end, const int32_t* 
  * the packed lists from spinf_tile_desc_build_host, on the device; tile_bits: the visibility words of spinf_tile_mask_bits for the
  * same lists and window (entries flagged "no mask" are not read). Scores are fp32, P is rounded to bf16 before P.V, the running
  * maximum is updated once per 128 keys in ascending key order: a row's result depends only on its own job's tokens. scale > 0;
- * out 32-byte aligned with a row pitch that is a multiple of 16 elements. */
+ * out 32-byte aligned with a row pitch that is a multiple of 16 elements. row_amax: NULL, or [n] fp32 zeroed by the caller: receives
+ * max |out[t,:,:]| per token (the row maximum the fp8 quantiser of the output projection's input needs: spinf_fp8_quant_from_amax). */
 int spinf_tree_attn_fwd(const void* q, const void* k, const void* v, void* out, int64_t n, int32_t H, int32_t Hkv, int32_t D,
                         int64_t q_pitch, int64_t kv_pitch, int64_t out_pitch, const int32_t* art, const int32_t* end,
                         const int32_t* pos, int32_t window, float scale, const int32_t* tile_offsets, const int32_t* tile_blocks,
-                        const uint8_t* tile_flags, const uint64_t* tile_bits, void* stream);
+                        const uint8_t* tile_flags, const uint64_t* tile_bits, float* row_amax, void* stream);
 
 /* ------------------------------------------------------------------------------------------------------------ layer glue
  * The reference runs these steps as inductor-fused pieces of the decoder layer (the layer code itself is the transformers

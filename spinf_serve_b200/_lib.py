@@ -48,7 +48,7 @@ SIGNATURES = {
     "spinf_gdn_epilogue": (ctypes.c_int, [_p, _p, _i64, _p, _f32, _i64, _i32, _i32, _p, _p]),
     "spinf_tree_attn_fwd": (
         ctypes.c_int,
-        [_p, _p, _p, _p, _i64, _i32, _i32, _i32, _i64, _i64, _i64, _p, _p, _p, _i32, _f32, _p, _p, _p, _p, _p],
+        [_p, _p, _p, _p, _i64, _i32, _i32, _i32, _i64, _i64, _i64, _p, _p, _p, _i32, _f32, _p, _p, _p, _p, _p, _p],
     ),
     "spinf_tile_mask_bits": (ctypes.c_int, [_p, _p, _p, _i64, _i32, _p, _p, _p, _p]),
 }

@@ -67,8 +67,9 @@ def stream_masks(art, end, pos, window, device, always_window=True):
     return {"full_attention": full, "sliding_attention": one(window) if binding else full}
 
 
-def tree_attention(q, k, v, mask: TileMask, scale: float, out=None):
-    """q [n, H, D], k / v [n, Hkv, D] bf16 (the last two dimensions dense, any row pitch) -> out [n, H, D] bf16"""
+def tree_attention(q, k, v, mask: TileMask, scale: float, out=None, row_amax=None):
+    """q [n, H, D], k / v [n, Hkv, D] bf16 (the last two dimensions dense, any row pitch) -> out [n, H, D] bf16. row_amax: optional
+    zeroed fp32 [n] that receives max |out| per token (for ops.fp8_quant_from_amax)"""
     for name, t in (("q", q), ("k", k), ("v", v)):
         if not t.is_cuda or t.dtype != torch.bfloat16 or t.dim() != 3 or t.stride(2) != 1 or t.stride(1) != t.shape[2]:
             raise SpinfError(f"{name}: expected a CUDA bf16 [n, heads, head_dim] tensor with dense heads")
@@ -82,7 +83,8 @@ def tree_attention(q, k, v, mask: TileMask, scale: float, out=None):
     check(
         _lib.lib().spinf_tree_attn_fwd(
             ptr(q), ptr(k), ptr(v), ptr(out), n, H, Hkv, D, q.stride(0), k.stride(0), out.stride(0), ptr(mask.art), ptr(mask.end),
-            ptr(mask.pos), mask.window, float(scale), ptr(mask.offsets), ptr(mask.blocks), ptr(mask.flags), ptr(mask.bits), stream_ptr(),
+            ptr(mask.pos), mask.window, float(scale), ptr(mask.offsets), ptr(mask.blocks), ptr(mask.flags), ptr(mask.bits), ptr(row_amax),
+            stream_ptr(),
         ),
         "spinf_tree_attn_fwd",
     )

@@ -46,6 +46,7 @@ struct AttnSmem {
 struct AttnArgs {
   __nv_bfloat16* out;
   int64_t out_pitch;
+  float* row_amax;  // optional [n]: max |out| over a token's whole output row, merged with an integer atomic max
   const int32_t* art;
   const int32_t* end;
   const int32_t* pos;
@@ -405,6 +406,7 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc_fence_after();
       const float inv = 1.f / (l_run + xq[(wg ^ 1) * 128 + row]);  // every row sees at least itself, so the sum is positive
       __nv_bfloat16* dst = a.out + static_cast<int64_t>(tq) * a.out_pitch + head * D + wg * (D / 2);
+      uint32_t amax2 = 0u;  // running max of |out| over this thread's columns, as a packed bf16 pair
 #pragma unroll 1
       for (int c = 0; c < D / 64; c += 2) {  // 64 columns at a time: both TMEM loads in flight together
         uint32_t o0[32], o1[32];
@@ -421,13 +423,18 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           const uint32_t (&o)[32] = hfc ? o1 : o0;
           uint32_t wv[16];
 #pragma unroll
-          for (int x = 0; x < 16; ++x) wv[x] = pack_bf16x2(__uint_as_float(o[2 * x]) * inv, __uint_as_float(o[2 * x + 1]) * inv);
+          for (int x = 0; x < 16; ++x) {
+            wv[x] = pack_bf16x2(__uint_as_float(o[2 * x]) * inv, __uint_as_float(o[2 * x + 1]) * inv);
+            amax2 = bf2_max(amax2, wv[x] & 0x7fff7fffu);
+          }
           const uint32_t lo[8] = {wv[0], wv[1], wv[2], wv[3], wv[4], wv[5], wv[6], wv[7]};
           const uint32_t hi[8] = {wv[8], wv[9], wv[10], wv[11], wv[12], wv[13], wv[14], wv[15]};
           stg_v8(dst + (c + hfc) * 32, lo);
           stg_v8(dst + (c + hfc) * 32 + 16, hi);
         }
       }
+      // non-negative floats order like their bit patterns, so the merged maximum does not depend on the order of arrival
+      if (a.row_amax) atomicMax(reinterpret_cast<unsigned int*>(a.row_amax + tq), __float_as_uint(fmaxf(bf2_lo(amax2), bf2_hi(amax2))));
       TR(t_e2);
       TR_ADD(8, t_e1 - t_e0); TR_ADD(9, t_e2 - t_e1); TR_ADD(10, t_e2 - t_item0); TR_ADD(11, 1);
       ++item_n;
@@ -524,7 +531,8 @@ extern "C" int spinf_tile_mask_bits(const int32_t* art, const int32_t* end, cons
 extern "C" int spinf_tree_attn_fwd(const void* q, const void* k, const void* v, void* out, int64_t n, int32_t H, int32_t Hkv,
                                    int32_t D, int64_t q_pitch, int64_t kv_pitch, int64_t out_pitch, const int32_t* art,
                                    const int32_t* end, const int32_t* pos, int32_t window, float scale, const int32_t* tile_offsets,
-                                   const int32_t* tile_blocks, const uint8_t* tile_flags, const uint64_t* tile_bits, void* stream) {
+                                   const int32_t* tile_blocks, const uint8_t* tile_flags, const uint64_t* tile_bits, float* row_amax,
+                                   void* stream) {
   SPINF_CHECK_ARG(q && k && v && out && art && end && pos && tile_offsets && tile_blocks && tile_flags && tile_bits);
   SPINF_CHECK_ARG(n >= 0 && n % SPINF_BLOCK == 0 && n < (1ll << 30) && H > 0 && Hkv > 0 && H % Hkv == 0 && H <= 65535);
   SPINF_CHECK_ARG(D == 128 || D == 256);
@@ -536,6 +544,7 @@ extern "C" int spinf_tree_attn_fwd(const void* q, const void* k, const void* v, 
   AttnArgs a;
   a.out = static_cast<__nv_bfloat16*>(out);
   a.out_pitch = out_pitch;
+  a.row_amax = row_amax;
   a.art = art;
   a.end = end;
   a.pos = pos;

@@ -173,6 +173,20 @@ def fp8_gemm_qkv(x8, xs, w8, ws, H, Hkv, D, wq, wk, cos, sin, eps=1e-6, plus1=Fa
     return y
 
 
+def fp8_quant_from_amax(y, row_amax):
+    """row-wise fp8 quantisation of y [M, K] bf16 with the row maxima already known (fp32 [M]): one pass -> (x8 [M, K], xs [M, 1])"""
+    _need(y, torch.bfloat16, "y", 2)
+    _need(row_amax, torch.float32, "row_amax", 1)
+    M, K = y.shape
+    if row_amax.numel() != M:
+        raise SpinfError("fp8_quant_from_amax: one maximum per row")
+    x8 = torch.empty((M, K), dtype=FP8, device=y.device)
+    xs = torch.empty((M, 1), dtype=torch.float32, device=y.device)
+    check(_lib.lib().spinf_fp8_quant_from_amax(ptr(y), ptr(row_amax), M, K, ptr(x8), ptr(xs), stream_ptr()), "spinf_fp8_quant_from_amax")
+    COUNTS["launches"] += 1
+    return x8, xs
+
+
 def bf16_gemm(x, w):
     """y [M, N] bf16 = x [M, K] @ w [N, K]^T, fp32 accumulation"""
     _need(x, torch.bfloat16, "x", 2)

@@ -45,10 +45,10 @@ def test_argument_errors_are_reported_on_the_host():
     assert lib.spinf_option_logprobs_workspace_bytes(-1, 10, 1) == -1
     assert lib.spinf_option_logprobs(p, p, 4, 64, 1000, p, 2, ctypes.c_float(0.0), p, p, 8, NULL) == -1  # workspace too small
     assert lib.spinf_option_logprobs_static(p, p, 4096, 64, 262144, p, 2, ctypes.c_float(0.0), p, NULL, NULL) == -4  # beyond the static scratch
-    assert lib.spinf_tree_attn_fwd(p, p, p, p, 130, 4, 2, 128, 512, 256, 512, p, p, p, 0, ctypes.c_float(1.0), p, p, p, p, NULL) == -1  # n % 128
-    assert lib.spinf_tree_attn_fwd(p, p, p, p, 128, 4, 3, 128, 512, 384, 512, p, p, p, 0, ctypes.c_float(1.0), p, p, p, p, NULL) == -1  # H % Hkv
-    assert lib.spinf_tree_attn_fwd(p, p, p, p, 128, 4, 2, 64, 256, 128, 256, p, p, p, 0, ctypes.c_float(1.0), p, p, p, p, NULL) == -1   # head dim
-    assert lib.spinf_tree_attn_fwd(p, p, p, p, 128, 4, 2, 128, 512, 256, 512, p, p, p, 0, ctypes.c_float(1.0), p, p, p, NULL, NULL) == -1  # no visibility words
+    assert lib.spinf_tree_attn_fwd(p, p, p, p, 130, 4, 2, 128, 512, 256, 512, p, p, p, 0, ctypes.c_float(1.0), p, p, p, p, NULL, NULL) == -1  # n % 128
+    assert lib.spinf_tree_attn_fwd(p, p, p, p, 128, 4, 3, 128, 512, 384, 512, p, p, p, 0, ctypes.c_float(1.0), p, p, p, p, NULL, NULL) == -1  # H % Hkv
+    assert lib.spinf_tree_attn_fwd(p, p, p, p, 128, 4, 2, 64, 256, 128, 256, p, p, p, 0, ctypes.c_float(1.0), p, p, p, p, NULL, NULL) == -1   # head dim
+    assert lib.spinf_tree_attn_fwd(p, p, p, p, 128, 4, 2, 128, 512, 256, 512, p, p, p, 0, ctypes.c_float(1.0), p, p, p, NULL, NULL, NULL) == -1  # no visibility words
     assert lib.spinf_tile_mask_bits(p, p, p, 100, 0, p, p, p, NULL) == -1  # n % 128
     assert lib.spinf_fused_norm(p, NULL, NULL, NULL, NULL, 4, 16384, ctypes.c_float(1e-6), 0, NULL, NULL, NULL, NULL, NULL) == -1    # hidden > 8192
     assert lib.spinf_gdn_recurrent(p, p, p, p, p, p, 8, 256, 512, 4, 2, 4, 64, 128, ctypes.c_float(1.0), p, 1, NULL, NULL, NULL, NULL, NULL, NULL) == -1  # K != 128

@@ -128,3 +128,17 @@ def test_tree_flex_interface_shapes(dev):
     out, none = A.tree_flex_forward(None, qd, kd, vd, masks["full_attention"], scaling=1.0 / 16)
     assert none is None and out.shape == (1, b.length, 16, 256) and out.is_contiguous()
     assert torch.equal(out[0], A.tree_attention(q.to(dev), k.to(dev), v.to(dev), masks["full_attention"], 1.0 / 16))
+
+
+def test_row_maxima_of_the_output_come_with_it(dev):
+    """the optional per-token max |out| (what the row-wise quantiser of the output projection's input needs) equals the maximum of
+    the stored bf16 output, for both item layouts (one head per item; two heads sharing a key/value head)"""
+    from spinf_serve_b200 import attention as A
+
+    b = _cfg1_batch()
+    for H, Hkv, D in ((16, 8, 256), (3, 3, 128)):
+        q, k, v = _qkv(b.length, H, Hkv, D, 3)
+        masks = A.stream_masks(b.art, b.end, b.pos, 1024, dev, always_window=True)
+        amax = torch.zeros(b.length, dtype=torch.float32, device=dev)
+        out = A.tree_attention(q.to(dev), k.to(dev), v.to(dev), masks["full_attention"], D**-0.5, row_amax=amax)
+        assert torch.equal(amax, out.float().abs().amax(dim=(1, 2)))
