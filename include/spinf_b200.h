@@ -222,12 +222,27 @@ int spinf_embed_scale(const int64_t* ids, const void* emb, int64_t n, int64_t hi
  *     S *= exp(g);  v' = (v - S^T k) * beta;  S += k (x) v';  o = S^T (q * scale)
  * q, k [rows, Hk, K] bf16 (l2-normalised by the caller), v [rows, Hv, V] bf16, g fp32 / beta bf16 [rows, Hv], each with its row
  * pitch in elements (g and beta share g_pitch); o [rows, Hv, V] bf16 contiguous, written at the same rows; h0 / ht
- * [*, Hv, K, V] fp32. K = V = 128. Every segment length runs through the same token-serial kernel (the reference switches to
- * a chunked form above 64 tokens; both compute this recurrence). */
+ * [*, Hv, K, V] fp32. K = V = 128. Token-serial: any segment length is accepted; segments longer than 64 tokens are meant for
+ * spinf_gdn_chunked below. */
 int spinf_gdn_recurrent(const void* q, const void* k, const void* v, const float* g, const void* beta, void* o, int64_t n_rows,
                         int64_t q_pitch, int64_t v_pitch, int64_t g_pitch, int32_t Hk, int32_t Hv, int32_t K, int32_t V, float scale,
                         const int64_t* cu, int64_t n_seg, const int64_t* idx, const float* h0, const int64_t* h0_idx, float* ht,
                         const int64_t* ht_idx, void* stream);
+
+/* The same recurrence for long segments in the chunked (WY) form the reference switches to above 64 tokens (gdn.chunked,
+ * spinf_serve/models/qwen35/gdn.py:109-133, which runs flash-linear-attention 0.5.2's chunk pipeline: chunk_local_cumsum,
+ * chunk_gated_delta_rule_fwd_intra, the state kernel of gdn.py:21-106, chunk_fwd_o). Same arguments as spinf_gdn_recurrent, plus the
+ * chunk table of the call (64-token chunks, segments in order: chunk_seg [n_chunks] = segment, chunk_t0 [n_chunks] = first token of
+ * the chunk within its segment; int32 on the device), call_tokens = cu[n_seg], and a workspace of
+ * spinf_gdn_chunked_workspace_bytes(call_tokens, Hv) bytes (16-byte aligned) for W, U and the running log-decay. Operands of every
+ * product are rounded to bf16 and accumulated in fp32, the state stays fp32, as in the reference's pipeline; results differ from
+ * the token-serial form by those roundings. */
+int64_t spinf_gdn_chunked_workspace_bytes(int64_t call_tokens, int32_t Hv);
+int spinf_gdn_chunked(const void* q, const void* k, const void* v, const float* g, const void* beta, void* o, int64_t n_rows,
+                      int64_t q_pitch, int64_t v_pitch, int64_t g_pitch, int32_t Hk, int32_t Hv, int32_t K, int32_t V, float scale,
+                      const int64_t* cu, int64_t n_seg, const int64_t* idx, const float* h0, const int64_t* h0_idx, float* ht,
+                      const int64_t* ht_idx, const int32_t* chunk_seg, const int32_t* chunk_t0, int64_t n_chunks,
+                      int64_t call_tokens, void* workspace, int64_t workspace_bytes, void* stream);
 
 /* Replaces the steps of GatedDeltaNet.forward before the recurrence (spinf_serve/models/qwen35/qwen.py:651-668), fused: for each of
  * the T tokens, from the in-projection rows y [n_rows, y_pitch] bf16 = [q | k | v | z | b | a]: the 4-tap path convolution over

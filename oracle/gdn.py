@@ -40,6 +40,52 @@ def recurrent(q, k, v, g, beta, scale, cu, idx=None, h0=None, h0_idx=None, ht=No
     return o
 
 
+def chunked(q, k, v, g, beta, scale, cu, idx=None, h0=None, h0_idx=None, ht=None, ht_idx=None, o=None, chunk=64):
+    """The same recurrence in the chunked (WY) form of the reference's gdn.chunked (spinf_serve/models/qwen35/gdn.py:109-133). That
+    function runs kernels of a third-party dependency that is not part of the reference tree (flash-linear-attention, pinned 0.5.2:
+    chunk_local_cumsum, chunk_scaled_dot_kkt_fwd, solve_tril, recompute_w_u_fwd, chunk_fwd_o) around the reference's own state
+    kernel (gdn.py:21-106); this restates their published algorithm (Yang et al., Gated Delta Networks, the WY form) with their
+    rounding points: bf16 operands into every product, fp32 accumulation and state. With G the running sum of g inside a chunk in
+    log2 units:  A[t,s] = beta_t (k_t.k_s) 2^(G_t-G_s) (s < t);  T = (I+A)^-1;  W = T (beta K 2^G);  U = T (beta V);
+    v' = U - W S;  o = scale ((Q S) 2^G + tril(Q K^T 2^(G_t-G_s)) v');  S <- S 2^(G_last) + K^T (v' 2^(G_last-G))."""
+    rows, Hk, K = k.shape
+    Hv, V = v.shape[1], v.shape[2]
+    rep = Hv // Hk
+    bf = lambda x: x.to(torch.bfloat16).float()
+    if o is None:
+        o = torch.zeros_like(v)
+    cu = [int(x) for x in cu]
+    for n in range(len(cu) - 1):
+        S = torch.zeros((Hv, K, V), dtype=torch.float32)
+        if h0 is not None and h0_idx is not None and int(h0_idx[n]) >= 0:
+            S = h0[int(h0_idx[n])].float().clone()
+        for c0 in range(cu[n], cu[n + 1], chunk):
+            c1 = min(c0 + chunk, cu[n + 1])
+            r = torch.as_tensor([int(idx[t]) if idx is not None else t for t in range(c0, c1)], dtype=torch.int64)
+            C = len(r)
+            Q = q[r].float().repeat_interleave(rep, 1).transpose(0, 1)  # [Hv, C, K]
+            Kc = k[r].float().repeat_interleave(rep, 1).transpose(0, 1)
+            Vc = v[r].float().transpose(0, 1)                           # [Hv, C, V]
+            b = beta[r].float().transpose(0, 1)                         # [Hv, C]
+            G = torch.cumsum(g[r].float(), 0).transpose(0, 1) * 1.4426950408889634
+            dec = torch.exp2(G[:, :, None] - G[:, None, :])             # [Hv, t, s]
+            lower = torch.tril(torch.ones(C, C, dtype=torch.bool), -1)
+            A = torch.where(lower, (Kc @ Kc.transpose(1, 2)) * dec * b[:, :, None], torch.zeros(()))
+            T = bf(torch.linalg.solve_triangular(torch.eye(C) + A, torch.eye(C).expand(Hv, C, C), upper=False))
+            W = bf(T @ bf(Kc * b[:, :, None] * torch.exp2(G)[:, :, None]))
+            U = bf(T @ bf(Vc * b[:, :, None]))
+            Sb = bf(S)
+            vn = U - W @ Sb
+            P = torch.where(torch.tril(torch.ones(C, C, dtype=torch.bool)), (Q @ Kc.transpose(1, 2)) * dec, torch.zeros(()))
+            out = ((Q @ Sb) * torch.exp2(G)[:, :, None] + bf(P) @ bf(vn)) * scale
+            o[r] = out.transpose(0, 1).to(o.dtype)
+            g_last = G[:, -1]
+            S = S * torch.exp2(g_last)[:, None, None] + Kc.transpose(1, 2) @ bf(vn * torch.exp2(g_last[:, None] - G)[:, :, None])
+        if ht is not None and ht_idx is not None and int(ht_idx[n]) >= 0:
+            ht[int(ht_idx[n])] = S.to(ht.dtype)
+    return o
+
+
 def gdn_tree(q, k, v, g, beta, plan, dtype=torch.float32):
     """every segment from its parent's final state, level by level (gdn_indexed, qwen.py:550-590); plan: a TreePlan whose calls
     carry idx, cu_cpu, h0_idx, ht_idx (host or device tensors)"""

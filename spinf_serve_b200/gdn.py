@@ -59,9 +59,68 @@ def recurrent(q, k, v, g, beta, scale, cu, n, h0=None, h0_idx=None, ht=None, ht_
     return o
 
 
-def chunked(q, k, v, g, beta, scale, cu, cu_cpu, h0=None, h0_idx=None, ht=None, ht_idx=None, chunk_size=64):
-    """the reference's gdn.chunked contract (gathered tensors, rows 0.. in call order); the same recurrence, run by the same kernel"""
-    return recurrent(q, k, v, g, beta, scale, cu, len(cu_cpu) - 1, h0, h0_idx, ht, ht_idx)
+CHUNK = 64
+
+
+def chunk_table(cu_cpu, device):
+    """(chunk_seg, chunk_t0) int32 device tensors: the 64-token chunks of a call's segments, in order (what the reference gets
+    from fla's prepare_chunk_indices)"""
+    segs, t0s = [], []
+    for n in range(len(cu_cpu) - 1):
+        length = int(cu_cpu[n + 1]) - int(cu_cpu[n])
+        for t0 in range(0, length, CHUNK):
+            segs.append(n)
+            t0s.append(t0)
+    mk = lambda x: torch.tensor(x, dtype=torch.int32).pin_memory().to(device, non_blocking=True)
+    return mk(segs), mk(t0s)
+
+
+def chunked(q, k, v, g, beta, scale, cu, cu_cpu, h0=None, h0_idx=None, ht=None, ht_idx=None, chunk_size=64, idx=None, o=None, table=None):
+    """the reference's gdn.chunked contract (gdn.py:109-133): the recurrence in its chunked form, 64 tokens at a time. As in the
+    reference the tensors may be gathered (rows 0.. in call order, idx None); with idx the kernels read and write the stream rows
+    themselves. table: the call's chunk_table when the caller keeps it (built here otherwise)."""
+    if chunk_size != CHUNK:
+        raise SpinfError("gdn.chunked: the kernels are written for 64-token chunks")
+    Hk, K = q.shape[-2], q.shape[-1]
+    Hv, V = v.shape[-2], v.shape[-1]
+    q3, qp = _rows(q, Hk, K, "q")
+    k3, kp = _rows(k, Hk, K, "k")
+    v3, vp = _rows(v, Hv, V, "v")
+    g2 = g[0] if g.dim() == 3 else g
+    b2 = beta[0] if beta.dim() == 3 else beta
+    if qp != kp or g2.stride(0) != b2.stride(0) or g2.stride(1) != 1 or b2.stride(1) != 1:
+        raise SpinfError("gdn.chunked: q / k and g / beta must share their row pitches")
+    if g2.dtype != torch.float32 or b2.dtype != torch.bfloat16 or q3.dtype != torch.bfloat16 or v3.dtype != torch.bfloat16:
+        raise SpinfError("gdn.chunked: expected bf16 q / k / v / beta and fp32 g")
+    _lib.init(q3.device)
+    rows = v3.shape[0]
+    if o is None:
+        o = torch.zeros((1, rows, Hv, V), dtype=torch.bfloat16, device=v3.device)
+    o3 = o[0] if o.dim() == 4 else o
+    if not o3.is_contiguous() or o3.dtype != torch.bfloat16:
+        raise SpinfError("gdn.chunked: o must be a contiguous bf16 tensor")
+    for name, t in (("cu", cu), ("idx", idx), ("h0_idx", h0_idx), ("ht_idx", ht_idx)):
+        if t is not None and (t.dtype != torch.int64 or not t.is_cuda or not t.is_contiguous()):
+            raise SpinfError(f"gdn.chunked: {name} must be a contiguous int64 CUDA tensor")
+    for name, t in (("h0", h0), ("ht", ht)):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous() or tuple(t.shape[1:]) != (Hv, K, V)):
+            raise SpinfError(f"gdn.chunked: {name} must be a contiguous fp32 [*, Hv, K, V] tensor")
+    n = len(cu_cpu) - 1
+    tokens = int(cu_cpu[-1]) if n > 0 else 0
+    seg, t0 = table if table is not None else chunk_table(cu_cpu, q3.device)
+    need = _lib.lib().spinf_gdn_chunked_workspace_bytes(tokens, Hv)
+    ws = torch.empty(max(int(need), 16), dtype=torch.uint8, device=q3.device)
+    check(
+        _lib.lib().spinf_gdn_chunked(
+            ptr(q3), ptr(k3), ptr(v3), ptr(g2), ptr(b2), ptr(o3), rows, qp, vp, g2.stride(0), Hk, Hv, K, V, ctypes.c_float(scale),
+            ptr(cu), n, ptr(idx), ptr(h0 if h0_idx is not None else None), ptr(h0_idx if h0 is not None else None),
+            ptr(ht if ht_idx is not None else None), ptr(ht_idx if ht is not None else None), ptr(seg), ptr(t0), seg.numel(), tokens,
+            ptr(ws), ws.numel(), stream_ptr(),
+        ),
+        "spinf_gdn_chunked",
+    )
+    ops.COUNTS["launches"] += 2
+    return o
 
 
 def gdn_tree(q, k, v, g, beta, plan, mod=None):
@@ -73,11 +132,14 @@ def gdn_tree(q, k, v, g, beta, plan, mod=None):
     for calls, nk in zip(plan.levels, plan.n_keep):
         states = torch.empty((nk, v.shape[1], q.shape[-1], v.shape[-1]), dtype=torch.float32, device=q.device) if nk else None
         for c in calls:
-            recurrent(
-                q, k, v, g, beta, scale, c.cu, len(c.cu_cpu) - 1,
-                h0=prev_states if c.h0_idx is not None else None, h0_idx=c.h0_idx,
-                ht=states if c.ht_idx is not None else None, ht_idx=c.ht_idx, idx=c.idx, o=o,
-            )
+            h0 = prev_states if c.h0_idx is not None else None
+            ht = states if c.ht_idx is not None else None
+            if c.kind == "chunked":  # segments longer than the plan's `short` (64), as the reference dispatches them
+                if getattr(c, "table", None) is None:
+                    c.table = chunk_table(c.cu_cpu, q.device)  # kept on the call: every recurrent layer of the forward reuses it
+                chunked(q, k, v, g, beta, scale, c.cu, c.cu_cpu, h0=h0, h0_idx=c.h0_idx, ht=ht, ht_idx=c.ht_idx, idx=c.idx, o=o, table=c.table)
+            else:
+                recurrent(q, k, v, g, beta, scale, c.cu, len(c.cu_cpu) - 1, h0=h0, h0_idx=c.h0_idx, ht=ht, ht_idx=c.ht_idx, idx=c.idx, o=o)
         prev_states = states
     return o
 

@@ -22,6 +22,7 @@ class Call:
     kind: str = "chunked"            # chunked (longer than `short`) | recurrent
     h0_idx: object | None = None     # [segs] row of the previous level's states (-1 = zero state), None at level 0
     ht_idx: object | None = None     # [segs] row of this level's states to write (-1 = none), None when no segment keeps one
+    table: object | None = None      # the call's 64-token chunk table (chunked calls), built on first use
 
 
 @dataclass

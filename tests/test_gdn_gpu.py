@@ -53,7 +53,8 @@ def test_tree_recurrence_vs_oracle(dev):
         r = torch.from_numpy(real)
         err = (got[r].float() - want[r].float()).abs().max().item()
         print(f"seed {seed}: {plan.n_segments} segments, {len(plan.levels)} levels, max abs err {err:.3e} (|o| max {want[r].float().abs().max():.2f})")
-        assert err <= 2.0**-7 * want[r].float().abs().max().item()
+        # segments longer than `short` run the chunked form, whose bf16 operands put it a few last bits from the fp64 recurrence
+        assert err <= 2.0**-6 * want[r].float().abs().max().item()
         assert bool((got[~r] == 0).all())  # rows outside every segment are left zero
 
 
@@ -113,3 +114,36 @@ def test_prologue_and_epilogue_vs_oracle(dev):
     diff = (got.float() - want.float()).abs()
     print(f"epilogue: differing elements {(diff > 0).float().mean():.4%}, max abs {diff.max():.3e}")
     assert (diff > 0).float().mean() < 5e-3 and diff.max() <= 2.0**-6 * want.float().abs().max()
+
+
+def test_chunked_form_vs_its_oracle_and_the_token_recurrence(dev):
+    """the chunked (WY) kernels against the oracle's restatement of the chunk pipeline (same rounding points: bf16 operands, fp32
+    accumulation and state) and, more loosely, against the token recurrence they re-express; ragged segments (partial last chunks,
+    a one-token segment), scattered stream rows, initial and final states by index"""
+    from spinf_serve_b200 import gdn
+
+    T = 700
+    q, k, v, gl, beta = _inputs(T, 21)
+    lens = [130, 64, 257, 1, 200]
+    cu_cpu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+    idx = torch.from_numpy(np.random.default_rng(3).permutation(T)[: cu_cpu[-1]].astype(np.int64))
+    g0 = torch.Generator().manual_seed(5)
+    h0 = torch.randn((2, Hv, D, D), generator=g0) * 0.05
+    h0_idx = torch.tensor([1, -1, 0, 1, -1], dtype=torch.int64)
+    ht_idx = torch.tensor([0, -1, 1, 2, -1], dtype=torch.int64)
+    ht_ref, ht_ser = torch.zeros((3, Hv, D, D)), torch.zeros((3, Hv, D, D))
+    want = OGD.chunked(q, k, v, gl, beta, D**-0.5, cu_cpu, idx.numpy(), h0, h0_idx.numpy(), ht_ref, ht_idx.numpy())
+    serial = OGD.recurrent(q, k, v, gl, beta, D**-0.5, cu_cpu, idx.numpy(), h0, h0_idx.numpy(), ht_ser, ht_idx.numpy())
+    ht = torch.zeros((3, Hv, D, D), device=dev)
+    got = gdn.chunked(q.to(dev), k.to(dev), v.to(dev), gl.to(dev), beta.to(dev), D**-0.5, torch.from_numpy(cu_cpu).to(dev), cu_cpu,
+                      h0=h0.to(dev), h0_idx=h0_idx.to(dev), ht=ht, ht_idx=ht_idx.to(dev), idx=idx.to(dev))[0].cpu()
+    touched = torch.zeros(T, dtype=torch.bool)
+    touched[idx] = True
+    scale_o, scale_s = want.float().abs().max().item(), ht_ref.abs().max().item()
+    e_o = (got.float() - want.float())[touched].abs().max().item()
+    e_s = (ht.cpu() - ht_ref).abs().max().item()
+    e_ser = (got.float() - serial.float())[touched].abs().max().item()
+    print(f"chunked GDN: output err {e_o:.3e} of {scale_o:.3f} (vs token recurrence {e_ser:.3e}), state err {e_s:.3e} of {scale_s:.3f}")
+    assert e_o <= 2.0**-6 * scale_o and e_s <= 2e-3 * scale_s   # same roundings: a few bf16 last-bit flips apart
+    assert e_ser <= 2e-2 * scale_o                              # the two forms differ by the chunk pipeline's bf16 operands
+    assert bool((got[~touched] == 0).all())
