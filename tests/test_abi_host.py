@@ -53,6 +53,9 @@ def test_argument_errors_are_reported_on_the_host():
     assert lib.spinf_fused_norm(p, NULL, NULL, NULL, NULL, 4, 16384, ctypes.c_float(1e-6), 0, NULL, NULL, NULL, NULL, NULL) == -1    # hidden > 8192
     assert lib.spinf_gdn_recurrent(p, p, p, p, p, p, 8, 256, 512, 4, 2, 4, 64, 128, ctypes.c_float(1.0), p, 1, NULL, NULL, NULL, NULL, NULL, NULL) == -1  # K != 128
     assert lib.spinf_gdn_recurrent(p, p, p, p, p, p, 8, 256, 512, 4, 2, 4, 128, 128, ctypes.c_float(1.0), p, 1, NULL, p, NULL, NULL, NULL, NULL) == -1  # h0 without h0_idx
+    assert lib.spinf_gdn_chunked_workspace_bytes(-1, 4) == -1
+    assert lib.spinf_gdn_chunked(p, p, p, p, p, p, 8, 256, 512, 4, 2, 4, 64, 128, ctypes.c_float(1.0), p, 1, NULL, NULL, NULL, NULL, NULL, p, p, 1, 8, p, 1 << 20, NULL) == -1  # K != 128
+    assert lib.spinf_gdn_chunked(p, p, p, p, p, p, 8, 256, 512, 4, 2, 4, 128, 128, ctypes.c_float(1.0), p, 1, NULL, NULL, NULL, NULL, NULL, p, p, 1, 8, p, 16, NULL) == -1  # workspace too small
 
 
 def test_tile_descriptor_host_function_edge_cases():
