@@ -38,3 +38,38 @@ def test_bulk_pass_at_full_width_is_batch_invariant(dev, name, layers):
     assert n_q == wl.n_questions
     del stack, sc
     torch.cuda.empty_cache()
+
+
+def test_attention_at_full_stream_size_by_properties(dev):
+    """the tree attention over a whole configuration-2 stream (27 648 tokens, 16 query / 8 KV heads of 256) through properties
+    that need no oracle: with every value row of a KV head equal to one vector the output is that vector (the weights of a row sum
+    to one, whatever the mask); the per-token output maxima match the stored output; and the first content's rows are bit-identical
+    to the same content run alone"""
+    from spinf_serve_b200 import attention as A
+    from spinf_serve_b200 import workloads
+    from spinf_serve_b200.packer import Packer
+
+    def batches(wl):
+        pk = Packer(32768, 65536, True, 1024)
+        return [b for key, first, t in wl.items for b in pk.push((key, first), t)] + list(pk.flush())
+
+    (b,) = batches(workloads.config2(seed=0))
+    (b1,) = batches(workloads.config2(seed=0, n_contents=1))
+    n, H, Hkv, D = b.length, 16, 8, 256
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn((n, H, D), generator=g).to(torch.bfloat16).to(dev)
+    k = torch.randn((n, Hkv, D), generator=g).to(torch.bfloat16).to(dev)
+    v = torch.randn((n, Hkv, D), generator=g).to(torch.bfloat16).to(dev)
+    masks = A.stream_masks(b.art, b.end, b.pos, 1024, dev, always_window=True)
+    for kind in ("full_attention", "sliding_attention"):
+        const = torch.randn((1, Hkv, D), generator=g).to(torch.bfloat16).to(dev)
+        out = A.tree_attention(q, k, const.expand(n, Hkv, D).contiguous(), masks[kind], D**-0.5)
+        want = const.repeat_interleave(H // Hkv, dim=1).expand(n, H, D)
+        assert (out.float() - want.float()).abs().max() <= 2.0**-7 * want.float().abs().max()
+        amax = torch.zeros(n, dtype=torch.float32, device=dev)
+        full = A.tree_attention(q, k, v, masks[kind], D**-0.5, row_amax=amax)
+        assert torch.equal(amax, full.float().abs().amax(dim=(1, 2)))
+        m1 = A.stream_masks(b1.art, b1.end, b1.pos, 1024, dev, always_window=True)
+        n1 = b1.length
+        alone = A.tree_attention(q[:n1].contiguous(), k[:n1].contiguous(), v[:n1].contiguous(), m1[kind], D**-0.5)
+        assert torch.equal(alone, full[:n1])
