@@ -80,31 +80,70 @@ class QwenStack:
     family = "qwen"
     hybrid = True
 
-    def __init__(self, weights: QwenWeights, n_layers: int | None = None):
+    def __init__(self, weights: QwenWeights, n_layers: int | None = None, compact: bool = True, min_stream: int = 0, align_jobs: bool = True):
+        """compact (QwenOptions.compact, qwen.py:86, default on): the model runs on the stream's real tokens only, in stream order,
+        padded with zero rows to whole blocks; the stream layout (pads between aligned jobs) exists only around the attention"""
         self.w = weights
         self.cfg = weights.cfg
         self.n_layers = self.cfg.layers if n_layers is None else n_layers
+        self.compact, self.min_stream, self.align_jobs = compact, min_stream, align_jobs
         R = self.cfg.rotary
         self.inv_freq = (1.0 / (self.cfg.theta ** (torch.arange(0, R, 2, dtype=torch.float32) / R))).to(weights.embed.device)
 
+    def compact_rows(self, b) -> int | None:
+        """the rows the model runs on: the real tokens in whole blocks, at least the GEMM floor for aligned jobs, never more than the
+        stream (Qwen35Stack.compact_rows, qwen.py:1039-1048); None = the stream layout"""
+        from spinf_serve_b200.packer import BLOCK
+
+        if not self.compact:
+            return None
+        R = int((b.art >= 0).sum())
+        floor = self.min_stream if self.align_jobs else 0
+        return min(b.length, max((R + BLOCK - 1) // BLOCK * BLOCK, floor))
+
     def plan(self, b) -> None:
         """the recurrent layers' plan, on the host ahead of the GPU (the producer thread; Qwen35Stack.plan, qwen.py:1056)"""
-        b.gdn_plan_host = (b.prev, b.art >= 0)
+        b.gdn_plan_host = (b.prev, b.art >= 0, self.compact_rows(b))
 
     def stage(self, b, device):
-        ids = torch.from_numpy(b.ids).pin_memory().to(device, non_blocking=True)
+        import numpy as np
+
+        up = lambda a: torch.from_numpy(a).pin_memory().to(device, non_blocking=True)  # noqa: E731
         masks = attention.stream_masks(b.art, b.end, b.pos, None, device, always_window=False)
-        prev, real = getattr(b, "gdn_plan_host", (b.prev, b.art >= 0))
-        return {"ids": ids, "pos": masks["full_attention"].pos, "masks": masks, "plan": tree_plan(prev, real, device)}
+        prev, real, rows = getattr(b, "gdn_plan_host", (b.prev, b.art >= 0, self.compact_rows(b)))
+        plan = tree_plan(prev, real, device, rows=rows)
+        if rows is None:
+            return {"ids": up(b.ids), "pos": masks["full_attention"].pos, "masks": masks, "plan": plan, "n": b.length}
+        # compact rows: the real tokens' ids and positions, then zeros (Qwen35Stack.stage / forward, qwen.py:1064-1090)
+        R = int(real.sum())
+        ids = np.zeros(rows, np.int64)
+        ids[:R] = b.ids[real]
+        pos = np.zeros(rows, np.int32)
+        pos[:R] = b.pos[real]
+        to_row = np.cumsum(real) - 1  # stream position -> compact row (meaningful at real positions)
+        return {"ids": up(ids), "pos": up(pos), "masks": masks, "plan": plan, "n": b.length, "to_row": up(to_row.astype(np.int64))}
 
     def forward(self, inputs, rows=None, taps=None):
+        """packed forward -> final hidden states after the last norm: [stream length, hidden] bf16 in the stream layout, or only the
+        stream positions `rows`; taps: optional dict filled with the residual stream per layer, in the stream layout (tests)"""
         cfg, w = self.cfg, self.w
         ids, pos, mask, plan = inputs["ids"], inputs["pos"], inputs["masks"]["full_attention"], inputs["plan"]
-        n = ids.numel()
+        n = ids.numel()          # rows the layers run on
+        T = inputs["n"]          # stream length (the attention's layout)
+        sidx = plan.sidx if plan.rows is not None else None
+        R = sidx.numel() if sidx is not None else n
         H, K, D = cfg.heads, cfg.kv_heads, cfg.head_dim
         cos, sin = ops.rope_table(pos, self.inv_freq)
         x = ops.embed_scale(ids, w.embed, 1.0)
+        if sidx is not None and n > R:
+            x[R:].zero_()  # rows past the real tokens are zero rows
         h = ops.fused_norm(x, w2=w.layers[0]["input_ln"], eps=cfg.eps, plus1=True, want_norm=True)["norm"] if self.n_layers else None
+
+        def to_stream(t):  # compact rows -> the stream layout (pads zero)
+            if sidx is None:
+                return t
+            return torch.zeros((T,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device).index_copy_(0, sidx, t[:R])
+
         for i in range(self.n_layers):
             L = w.layers[i]
             if L["kind"] == "linear_attention":
@@ -117,7 +156,12 @@ class QwenStack:
                 q = ops.qkv_norm_rope_gated(y, H, K, D, L["q_norm"], L["k_norm"], cos, sin, cfg.eps, plus1=True)
                 kk = y[:, 2 * H * D : (2 * H + K) * D].view(n, K, D)
                 vv = y[:, (2 * H + K) * D :].view(n, K, D)
-                o = attention.tree_attention(q, kk, vv, mask, D**-0.5)
+                if sidx is None:
+                    o = attention.tree_attention(q, kk, vv, mask, D**-0.5)
+                else:  # the real rows scattered into the stream layout for the attention, its output gathered back (qwen.py:605-623)
+                    o_s = attention.tree_attention(to_stream(q), to_stream(kk), to_stream(vv), mask, D**-0.5)
+                    o = torch.zeros((n, H, D), dtype=o_s.dtype, device=o_s.device)
+                    o[:R] = o_s.index_select(0, sidx)
                 ops.attn_gate(o, y, H, D)
                 m = L["o_proj"](o.view(n, H * D))
             r = ops.fused_norm(m, residual=x, w2=L["post_ln"], eps=cfg.eps, plus1=True, want_h=True, want_norm=True)
@@ -130,5 +174,8 @@ class QwenStack:
             x = r["h"]
             h = None if last else r["norm"]
             if taps is not None:
-                taps[i] = x
-        return ops.fused_norm(x, w2=w.norm, rows=rows, eps=cfg.eps, plus1=True, want_norm=True)["norm"]
+                taps[i] = to_stream(x)
+        if rows is not None and sidx is not None:
+            rows = inputs["to_row"].index_select(0, rows)  # the read rows are stream positions
+        out = ops.fused_norm(x, w2=w.norm, rows=rows, eps=cfg.eps, plus1=True, want_norm=True)["norm"]
+        return out if rows is not None or sidx is None else to_stream(out)

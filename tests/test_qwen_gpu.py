@@ -67,3 +67,26 @@ def test_hybrid_scores_bit_identical_alone_and_packed(dev):
         for a, b in zip(r, res[0]):
             assert np.array_equal(a, b)
     assert all(np.isfinite(a).all() and (a < 0).all() for a in res[0])
+
+
+def test_compact_rows_equal_the_stream_layout(dev):
+    """the model on compact rows (real tokens only, the stream layout rebuilt around the attention; Qwen35Stack.compact_rows,
+    qwen.py:1039-1048) gives bit-identical hidden states at every real position, for the whole stream and for selected read rows"""
+    from spinf_serve_b200.qwen_stack import QwenStack
+
+    _, _, stack = _build(dev)
+    plain = QwenStack(stack.w, compact=False)
+    rng = np.random.default_rng(9)
+    pk = P.Packer(4096, 8192, align=True)
+    for j in range(4):
+        list(pk.push(j, _content(rng, int(rng.integers(30, 300)), 3)))
+    (b,) = list(pk.flush())
+    real = torch.from_numpy(b.art >= 0).to(dev)
+    assert stack.compact_rows(b) < b.length  # aligned jobs leave pads that the compact layout drops
+    stack.plan(b)
+    plain.plan(b)
+    a = stack.forward(stack.stage(b, dev))
+    c = plain.forward(plain.stage(b, dev))
+    assert a.shape == c.shape and torch.equal(a[real], c[real])
+    sel = torch.from_numpy(b.sel).to(dev)
+    assert torch.equal(stack.forward(stack.stage(b, dev), rows=sel), c.index_select(0, sel))
