@@ -3,8 +3,8 @@ forward (gemma4.py:407-415) runs transformers' Gemma 4 decoder layers with fp8 r
 layer is a fixed chain of library kernels over the packed stream [n, hidden]:
 
     fused_norm (post-ffn norm of the previous layer + residual + input norm + fp8 quantisation)
-    fp8 GEMM q|k|v (one fused projection)  ->  head norms + rotary (in place)  ->  tree attention  ->  fp8 quantisation
-    fp8 GEMM o  ->  fused_norm (post-attention norm + residual + pre-ffn norm + fp8 quantisation)
+    fp8 GEMM q|k|v (one fused projection, head norms + rotary in its epilogue)  ->  tree attention (+ the row maxima of its output)
+    ->  one-pass fp8 quantisation  ->  fp8 GEMM o  ->  fused_norm (post-attention norm + residual + pre-ffn norm + fp8 quantisation)
     fp8 GEMM gate|up with GeGLU in its epilogue (+ row maxima)  ->  one-pass fp8 quantisation  ->  fp8 GEMM down
 
 Fusing q|k|v and gate|up is exact for this scheme: weight scales are per output channel and the activation scale is per token,
