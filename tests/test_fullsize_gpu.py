@@ -73,3 +73,134 @@ def test_attention_at_full_stream_size_by_properties(dev):
         n1 = b1.length
         alone = A.tree_attention(q[:n1].contiguous(), k[:n1].contiguous(), v[:n1].contiguous(), m1[kind], D**-0.5)
         assert torch.equal(alone, full[:n1])
+
+
+def _rand_bf16(shape, seed, dev, std=1.0):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    return (torch.randn(shape, generator=g, device=dev) * std).to(torch.bfloat16)
+
+
+def test_fp8_linears_with_fused_epilogues_at_layer_shapes(dev):
+    """configuration 2's layer shapes at M = 8192 rows: the q|k|v projection with norm + rotary in its epilogue and the gate|up
+    projection with the GeGLU epilogue against the plain row-wise GEMM followed by the separate kernels (bit-equal for GeGLU and
+    its quantisation; for q|k|v up to last-bit flips from the order of the fp32 sums of squares), and rows independent of M"""
+    from spinf_serve_b200 import ops
+
+    M, hidden, H, Hkv, D, F = 8192, 3840, 16, 8, 256, 15360
+    x8, xs = ops.fp8_rowwise_quant(_rand_bf16((M, hidden), 1, dev))
+    # q|k|v
+    w8, ws = ops.fp8_rowwise_quant(_rand_bf16(((H + 2 * Hkv) * D, hidden), 2, dev, 0.02))
+    wq, wk = 1 + 0.1 * _rand_bf16((D,), 3, dev).float(), 1 + 0.1 * _rand_bf16((D,), 4, dev).float()
+    wq, wk = wq.to(torch.bfloat16), wk.to(torch.bfloat16)
+    pos = torch.arange(M, dtype=torch.int32, device=dev) % 1500
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, D, 2, dtype=torch.float32) / D))).to(dev)
+    cos, sin = ops.rope_table(pos, inv_freq)
+    ref = ops.fp8_rowwise_gemm(x8, xs, w8, ws)
+    ops.qkv_norm_rope(ref, H, Hkv, D, wq, wk, cos, sin, 1e-6)
+    got = ops.fp8_gemm_qkv(x8, xs, w8, ws, H, Hkv, D, wq, wk, cos, sin, 1e-6)
+    assert (got.float() != ref.float()).float().mean().item() < 2e-3
+    assert (got.float() - ref.float()).abs().max() <= 2.0**-6 * ref.float().abs().max()
+    part = ops.fp8_gemm_qkv(x8[:1000].contiguous(), xs[:1000].contiguous(), w8, ws, H, Hkv, D, wq, wk, cos[:1000].contiguous(),
+                            sin[:1000].contiguous(), 1e-6)
+    assert torch.equal(part, got[:1000])
+    del ref, got, part, w8
+    # gate|up
+    g8, gs = ops.fp8_rowwise_quant(_rand_bf16((2 * F, hidden), 5, dev, 0.02))
+    gu = ops.fp8_rowwise_gemm(x8, xs, g8, gs)
+    u8, us, y_ref = ops.glu_quant(gu, "gelu_tanh", want_fp8=True, want_y=True)
+    del gu
+    order = ops.glu_tile_order(F).to(dev)
+    f8, fs, y = ops.fp8_gemm_glu(x8, xs, g8.view(torch.uint8)[order].view(torch.float8_e4m3fn).contiguous(), gs.reshape(-1)[order].contiguous())
+    assert torch.equal(y, y_ref) and torch.equal(fs, us) and torch.equal(f8.view(torch.uint8), u8.view(torch.uint8))
+
+
+def test_fused_norm_at_full_stream_size(dev):
+    """the post-attention chain (norm, residual add, norm, row-wise fp8) over a whole 27 648 x 3840 stream: rows sampled across the
+    stream against the oracle's module arithmetic, every row's scale equal to its quantised maximum / 448, and the result
+    independent of how many rows the call covers"""
+    from oracle import gemma as OG
+    from oracle import linears as OL
+    from spinf_serve_b200 import ops
+
+    n, hidden = 27648, 3840
+    y, res = _rand_bf16((n, hidden), 1, dev, 2.0), _rand_bf16((n, hidden), 2, dev, 30.0)
+    w1 = (1 + 0.1 * _rand_bf16((hidden,), 3, dev).float()).to(torch.bfloat16)
+    w2 = (1 + 0.1 * _rand_bf16((hidden,), 4, dev).float()).to(torch.bfloat16)
+    r = ops.fused_norm(y, w1=w1, residual=res, w2=w2, eps=1e-6, want_h=True, want_norm=True, want_fp8=True)
+    # (the quotient on the CPU: a division by a scalar on the GPU becomes a multiplication by its reciprocal)
+    assert torch.equal(r["xs"].reshape(-1).cpu(), r["norm"].float().abs().amax(1).clamp_min(1e-12).cpu() / 448.0)
+    rows = torch.arange(0, n, 431, device=dev)
+    h_ref = res[rows].cpu() + OG.rmsnorm(y[rows].cpu(), w1.cpu(), 1e-6)
+    x_ref = OG.rmsnorm(h_ref, w2.cpu(), 1e-6)
+    assert (r["h"][rows].cpu().float() != h_ref.float()).float().mean() < 1e-3
+    assert (r["norm"][rows].cpu().float() != x_ref.float()).float().mean() < 2e-3
+    k8, ks = OL.quant_act_row(r["norm"][rows].cpu())
+    assert torch.equal(r["xs"][rows].cpu(), ks) and torch.equal(r["x8"][rows].cpu().view(torch.uint8), k8.view(torch.uint8))
+    few = ops.fused_norm(y[:300].contiguous(), w1=w1, residual=res[:300].contiguous(), w2=w2, eps=1e-6, want_h=True, want_fp8=True)
+    assert torch.equal(few["h"], r["h"][:300]) and torch.equal(few["x8"].view(torch.uint8), r["x8"][:300].view(torch.uint8))
+
+
+def test_int4_linear_at_the_hybrid_models_widest_shape(dev):
+    """the gate|up projection of configuration 5 (5120 -> 34 816, group 128) at M = 8192: against the bf16 GEMM on the dequantised
+    weight (the same products, the weight rounded to bf16 once in both), and rows independent of M"""
+    from spinf_serve_b200 import ops
+
+    M, K, N, G = 8192, 5120, 34816, 128
+    g = torch.Generator(device=dev).manual_seed(0)
+    qw = torch.randint(0, 256, (N, K // 2), generator=g, device=dev, dtype=torch.uint8)
+    sc = (torch.rand((N, K // G), generator=g, device=dev) * 0.02 + 0.005).to(torch.float16)
+    x = _rand_bf16((M, K), 1, dev)
+    y = ops.w4_gemm(x, qw, sc, G)
+    nib = torch.stack([qw & 15, qw >> 4], dim=-1).reshape(N, K).float() - 8.0
+    wd = (nib.view(N, K // G, G) * sc.float()[:, :, None]).reshape(N, K).to(torch.bfloat16)
+    ref = ops.bf16_gemm(x, wd)
+    assert (y.float() - ref.float()).abs().max() <= 2.0**-6 * ref.float().abs().max()
+    assert torch.equal(ops.w4_gemm(x[:777].contiguous(), qw, sc, G), y[:777])
+
+
+def test_recurrence_forms_agree_at_the_hybrid_models_shape(dev):
+    """configuration 5's recurrent layer (16 key / 32 value heads of 128) over a stream of 2 000-token trunks with 32 branches of
+    20 tokens: the plan's long segments through the chunked kernels and everything through the token-serial kernel agree to the
+    chunk pipeline's bf16 operand roundings; rows outside every segment stay zero"""
+    from spinf_serve_b200 import gdn, workloads
+    from spinf_serve_b200.gdn_plan import tree_plan
+    from spinf_serve_b200.packer import Packer
+
+    wl = workloads.fixed("cfg5", 6, 2000, 32, 20, 2, 248320, 16384, 0)
+    pk = Packer(16384, 65536, True, 1024)
+    (b,) = [x for key, first, t in wl.items for x in pk.push((key, first), t)] + list(pk.flush())
+    T, Hk, Hv, D = b.length, 16, 32, 128
+    q = torch.nn.functional.normalize(_rand_bf16((T, Hk, D), 1, dev).float(), dim=-1).to(torch.bfloat16)
+    k = torch.nn.functional.normalize(_rand_bf16((T, Hk, D), 2, dev).float(), dim=-1).to(torch.bfloat16)
+    v = _rand_bf16((T, Hv, D), 3, dev)
+    gl = -torch.rand((T, Hv), device=dev) * 0.1
+    beta = torch.rand((T, Hv), device=dev).to(torch.bfloat16)
+    real = b.art >= 0
+    plan = tree_plan(b.prev, real, dev)
+    assert any(c.kind == "chunked" for lv in plan.levels for c in lv) and any(c.kind == "recurrent" for lv in plan.levels for c in lv)
+    mixed = gdn.gdn_tree(q, k, v, gl, beta, plan)
+    serial_plan = tree_plan(b.prev, real, dev)
+    for lv in serial_plan.levels:
+        for c in lv:
+            c.kind = "recurrent"
+    serial = gdn.gdn_tree(q, k, v, gl, beta, serial_plan)
+    r = torch.from_numpy(real).to(dev)
+    assert (mixed[r].float() - serial[r].float()).abs().max() <= 2e-2 * serial[r].float().abs().max()
+    assert bool((mixed[~r] == 0).all())
+
+
+def test_option_read_at_full_vocabulary(dev):
+    """configuration 2's read: 1 344 rows against the 262 144 x 3840 tied head, two option columns per question among the batch's
+    union: sampled rows against torch's log_softmax of the same logits, every value a log-probability, rows independent of R"""
+    from spinf_serve_b200 import ops
+
+    R, hidden, vocab = 1344, 3840, 262144
+    h = _rand_bf16((R, hidden), 1, dev)
+    W = _rand_bf16((vocab, hidden), 2, dev, 0.02)
+    cols = torch.sort(torch.randperm(vocab, device=dev)[:2688]).values.to(torch.int32)
+    lp = ops.option_logprobs(h, W, cols, None)
+    assert lp.shape == (R, 2688) and bool((lp <= 0).all()) and bool(torch.isfinite(lp).all())
+    rows = torch.arange(0, R, 97, device=dev)
+    ref = torch.log_softmax(h[rows].float() @ W.float().t(), dim=-1)[:, cols.long()]
+    assert (lp[rows] - ref).abs().max() < 2e-3
+    assert torch.equal(ops.option_logprobs(h[:100].contiguous(), W, cols, None), lp[:100])
