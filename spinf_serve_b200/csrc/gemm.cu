@@ -325,21 +325,36 @@ __global__ void col_tile_start_kernel(const int* __restrict__ cols, int n_cols, 
   start[t] = lo;
 }
 
-__global__ void lse_finalize_kernel(const float* __restrict__ part_max, const float* __restrict__ part_sum, int tiles_n, int Mpad,
-                                    int M, float* __restrict__ out, int n_cols) {
-  const int r = blockIdx.x * blockDim.x + threadIdx.x;
-  if (r >= M) return;
+// One CTA per read row: thread i merges the partials of vocabulary tiles i, i + 128, ... in ascending order, the 128 running
+// (max, sum) pairs are merged by a fixed tree (shuffles, then the four warps' results in order), and the whole CTA subtracts the
+// row's log-sum-exp from its option logits. The order depends on the number of tiles only, never on the number of rows.
+__device__ __forceinline__ void lse_merge(float& m, float& s, float pm, float ps) {
+  const float mn = fmaxf(m, pm);
+  if (mn == -INFINITY) return;
+  s = s * __expf(m - mn) + ps * __expf(pm - mn);
+  m = mn;
+}
+__global__ void __launch_bounds__(128) lse_finalize_kernel(const float* __restrict__ part_max, const float* __restrict__ part_sum,
+                                                           int tiles_n, int Mpad, int M, float* __restrict__ out, int n_cols) {
+  __shared__ float red_m[4], red_s[4];
+  const int r = blockIdx.x;
   float m = -INFINITY, s = 0.f;
-  for (int t = 0; t < tiles_n; ++t) {
-    const float pm = part_max[static_cast<size_t>(t) * Mpad + r];
-    const float ps = part_sum[static_cast<size_t>(t) * Mpad + r];
-    const float mn = fmaxf(m, pm);
-    if (mn == -INFINITY) continue;
-    s = s * __expf(m - mn) + ps * __expf(pm - mn);
-    m = mn;
+  for (int t = threadIdx.x; t < tiles_n; t += 128)
+    lse_merge(m, s, part_max[static_cast<size_t>(t) * Mpad + r], part_sum[static_cast<size_t>(t) * Mpad + r]);
+  for (int o = 1; o < 32; o <<= 1) {
+    const float pm = __shfl_xor_sync(0xffffffffu, m, o), ps = __shfl_xor_sync(0xffffffffu, s, o);
+    // both partners must arrive at the same pair: the lower lane's value goes first
+    float a_m = (threadIdx.x & o) ? pm : m, a_s = (threadIdx.x & o) ? ps : s;
+    const float b_m = (threadIdx.x & o) ? m : pm, b_s = (threadIdx.x & o) ? s : ps;
+    lse_merge(a_m, a_s, b_m, b_s);
+    m = a_m, s = a_s;
   }
+  if ((threadIdx.x & 31) == 0) red_m[threadIdx.x >> 5] = m, red_s[threadIdx.x >> 5] = s;
+  __syncthreads();
+  m = red_m[0], s = red_s[0];
+  for (int w = 1; w < 4; ++w) lse_merge(m, s, red_m[w], red_s[w]);
   const float lse = m + logf(s);
-  for (int c = 0; c < n_cols; ++c) out[static_cast<size_t>(r) * n_cols + c] -= lse;
+  for (int c = threadIdx.x; c < n_cols; c += 128) out[static_cast<size_t>(r) * n_cols + c] -= lse;
 }
 
 // ------------------------------------------------------------------------------------------------ per-row fp8 quantiser
@@ -578,7 +593,7 @@ extern "C" int spinf_option_logprobs(const void* h, const void* W, int64_t R, in
   GemmShape sh = shape;
   sh.group_m = shape.tiles_m;  // all row tiles of one vocabulary tile run together: W is streamed from HBM once
   if ((r = launch_gemm<KIND_BF16, BN>(tmA, tmB, sh, epi, st))) return r;
-  lse_finalize_kernel<<<static_cast<unsigned>((R + 127) / 128), 128, 0, st>>>(part_max, part_sum, shape.tiles_n,
+  lse_finalize_kernel<<<static_cast<unsigned>(R), 128, 0, st>>>(part_max, part_sum, shape.tiles_n,
                                                                              static_cast<int>(Mpad), static_cast<int>(R), out,
                                                                              static_cast<int>(n_cols));
   SPINF_CUDA_OK(cudaGetLastError());
@@ -655,7 +670,7 @@ extern "C" int spinf_option_logprobs_static(const void* h, const void* W, int64_
   const int grid = tiles < sm_count() ? tiles : sm_count();
   kern<<<grid, 192, GemmSmem<BN>::TOTAL, st>>>(tmA, tmB, sh, epi, status_word_p);
   SPINF_CUDA_OK(cudaGetLastError());
-  lse_finalize_kernel<<<static_cast<unsigned>((R + 127) / 128), 128, 0, st>>>(part_max, part_sum, sh.tiles_n, static_cast<int>(Mpad),
+  lse_finalize_kernel<<<static_cast<unsigned>(R), 128, 0, st>>>(part_max, part_sum, sh.tiles_n, static_cast<int>(Mpad),
                                                                              static_cast<int>(R), out, static_cast<int>(n_cols));
   SPINF_CUDA_OK(cudaGetLastError());
   return 0;
