@@ -423,14 +423,20 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
   return 0;
 }
 
-static GemmShape make_shape(int64_t M, int64_t N, int64_t K, int BN) {
+static GemmShape make_shape(int64_t M, int64_t N, int64_t K, int BN, int elem_bytes = 1) {
   GemmShape s;
   s.M = static_cast<int>(M);
   s.N = static_cast<int>(N);
   s.K = static_cast<int>(K);
   s.tiles_m = static_cast<int>((M + 127) / 128);
   s.tiles_n = static_cast<int>((N + BN - 1) / BN);
-  s.group_m = 8;
+  // Row tiles are walked in groups, all column tiles of a group before the next group: the group's activation rows stay in L2
+  // while the weight matrix streams past once per group. The group is made as tall as about 32 MB of activations allow (8..64
+  // row tiles): with 8, the 118 MB gate|up weight of the 12B shapes crossed HBM 27 times per GEMM; the traffic costs power, and
+  // under the power cap power is time (2.52 -> 2.36 ms on that GEMM at 27 648 rows). The order changes no tile's arithmetic.
+  const int64_t per_tile = 128 * K * elem_bytes;
+  const int64_t g = (32ll << 20) / (per_tile > 0 ? per_tile : 1);
+  s.group_m = static_cast<int>(g < 8 ? 8 : (g > 64 ? 64 : g));
   return s;
 }
 
@@ -477,7 +483,7 @@ extern "C" int spinf_bf16_gemm_ld(const void* x, const void* w, void* y, int64_t
   if ((r = make_tmap_2d(&epi.tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y, M, N, y_pitch * 2, 64, 128))) return r;
   epi.rowscale = nullptr;
   epi.colscale_g = nullptr;
-  return launch_gemm<KIND_BF16, BN>(tmA, tmB, make_shape(M, N, K, BN), epi, static_cast<cudaStream_t>(stream));
+  return launch_gemm<KIND_BF16, BN>(tmA, tmB, make_shape(M, N, K, BN, 2), epi, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int spinf_bf16_gemm(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, void* stream) {

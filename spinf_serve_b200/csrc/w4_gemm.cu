@@ -284,7 +284,13 @@ extern "C" int spinf_w4_gemm(const void* x, const void* qw, const void* scales, 
   a.M = static_cast<int>(M), a.N = static_cast<int>(N), a.K = static_cast<int>(K), a.G = group;
   a.tiles_m = static_cast<int>((M + 255) / 256);
   a.tiles_n = static_cast<int>((N + 127) / 128);
-  a.group_m = 4;
+  // groups of row tiles as tall as about 32 MB of bf16 activations allow (4..32 tiles of 256 rows): the packed weight streams past
+  // once per group
+  {
+    const int64_t per_tile = 256 * K * 2;
+    const int64_t g = (32ll << 20) / per_tile;
+    a.group_m = static_cast<int>(g < 4 ? 4 : (g > 32 ? 32 : g));
+  }
   static bool attr_set[64] = {false};
   if (!attr_set[dev]) {
     SPINF_CUDA_OK(cudaFuncSetAttribute(w4_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, W4Smem::TOTAL));

@@ -204,3 +204,20 @@ def test_option_read_at_full_vocabulary(dev):
     ref = torch.log_softmax(h[rows].float() @ W.float().t(), dim=-1)[:, cols.long()]
     assert (lp[rows] - ref).abs().max() < 2e-3
     assert torch.equal(ops.option_logprobs(h[:100].contiguous(), W, cols, None), lp[:100])
+
+
+def test_down_projection_shape_rows_and_exact_product(dev):
+    """configuration 2's down projection (15 360 -> 3 840) at M = 8192: sampled rows against the float64 product of the same
+    quantised operands, and rows independent of M"""
+    from oracle import linears as OL
+    from spinf_serve_b200 import ops
+
+    M, K, N = 8192, 15360, 3840
+    x8, xs = ops.fp8_rowwise_quant(_rand_bf16((M, K), 1, dev))
+    w8, ws = ops.fp8_rowwise_quant(_rand_bf16((N, K), 2, dev, 0.02))
+    y = ops.fp8_rowwise_gemm(x8, xs, w8, ws)
+    rows = torch.arange(0, M, 521, device=dev)
+    ref = OL.scaled_mm_rowwise(x8[rows].cpu(), xs[rows].cpu(), w8.cpu(), ws.cpu().reshape(1, -1), exact=True)
+    err = (y[rows].cpu().double() - ref.double()).abs()
+    assert bool((err <= 2.0**-7 * ref.double().abs() + 2.0**-14 * ref.double().abs().max()).all())
+    assert torch.equal(ops.fp8_rowwise_gemm(x8[:1000].contiguous(), xs[:1000].contiguous(), w8, ws), y[:1000])
