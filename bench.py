@@ -297,8 +297,8 @@ def gpu_arm(args):
                 "kernel": "gemm_tc_kernel<fp8, 256, *> (row-wise fp8 linear: q|k|v, o, gate|up with the GeGLU epilogue, down)", "bound": "tensor",
                 "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s", "frac": achieved / fp8_peak,
                 # DRAM bytes per launch: the ncu capture of the down-projection shape at M = 8192 (profiles/fp8_gemm_down_proj_M8192.md:
-                # 619.1 MB for 966.4 GFLOP), scaled by FLOPs to this run's average launch
-                "traffic": 619.1e6 / 966.4e9 * (gemm_flops / max(len(prof), 1)), "traffic_unit": "bytes per launch (scaled from a smaller capture)",
+                # 588.8 MB for 966.4 GFLOP), scaled by FLOPs to this run's average launch
+                "traffic": 588.8e6 / 966.4e9 * (gemm_flops / max(len(prof), 1)), "traffic_unit": "bytes per launch (scaled from a smaller capture)",
                 "peak_source": f"2 x bf16 sustained of {peaks['source']} (no fp8 figure in MEASURED_PEAKS.json)",
                 "launches": len(prof), "share_of_step": gemm_ms / ms if ms > 0 else None,
                 "step_tflops_all_kernels": step_flops * args.steps / (ms * 1e-3) / 1e12,
