@@ -16,6 +16,9 @@
 //              (probabilities then stay below 2^24: no overflow in bf16 P, the fp32 sum or O, and rounding to bf16 is relative, so
 //              nothing is lost against a maximum that moves every tile); the decision depends on the row's own scores only.
 //              At the end of an item each group divides its half of the O columns by the row sum and stores bf16.
+// When two (or an even number of) query heads share a key/value head the kernel runs as CTA pairs (PAIR, below): the two 64-row
+// halves of a query block form a cluster of two CTAs that split every K / V tile between them, which leaves room for two whole
+// tiles of each in flight per CTA instead of one.
 // Numerics follow the reference's attention (bf16 Q/K/V, fp32 scores and softmax state, P rounded to bf16 before P V, fp32
 // accumulation). Reduction order per row = ascending key tiles of the row's own job, independent of what else is packed in the
 // stream; tiles flagged "no mask" only skip the mask evaluation, never change the arithmetic.
@@ -89,15 +92,86 @@ __device__ unsigned long long g_attn_trace[16];
 #define TR_ADD(slot, v)
 #endif
 
-template <int D>
+// ---------------------------------------------------------------- CTA pairs (thread-block clusters of 2, tcgen05 cta_group::2)
+// PAIR = true: the two 64-row halves of a query block (same two heads, same tile list) run in the two CTAs of a cluster and share
+// every K / V tile: CTA r holds keys [64 r, 64 r + 64) of the K tile and head dimensions [D/2 r, D/2 r + D/2) of the V tile, the
+// leader issues the pair's MMAs (M = 256: 128 query rows per CTA) and each CTA keeps its own S / P / O in its own tensor memory.
+// Half the K / V bytes per CTA leave room for two whole tiles of each in flight. No load is multicast: each CTA fetches exactly the
+// bytes it alone holds; the peer's barriers are reached through shared::cluster addresses.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(const void* p, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_u32(p)), "r"(rank));
+  return out;
+}
+// (default semantics: release at CTA scope. The data the leader's MMAs read after this arrival is in tensor memory and ordered by
+// the tcgen05 fences; a cluster-scope release here cost 1 200 cycles per arrival)
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load of this CTA's bytes that completes on a barrier given as a shared::cluster address (the leader's)
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* m, int c0, int c1, uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+template <bool PAIR>
+__device__ __forceinline__ void attn_mma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  if (PAIR)
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+  else
+    umma_f16_ss(d_tmem, adesc, bdesc, idesc, accumulate);
+}
+template <bool PAIR>
+__device__ __forceinline__ void attn_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  if (PAIR)
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+  else
+    umma_f16_ts(d_tmem, a_tmem, bdesc, idesc, accumulate);
+}
+// the MMAs issued so far by this thread arrive on `bar` when they have completed: in this CTA, or in both CTAs of the pair
+template <bool PAIR>
+__device__ __forceinline__ void attn_commit(uint64_t* bar) {
+  if (PAIR) {
+#pragma unroll
+    for (uint32_t r = 0; r < 2; ++r)
+      asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(map_to_cta(bar, r)) : "memory");
+  } else {
+    umma_commit(bar);
+  }
+}
+
+template <int D, bool PAIR>
 __global__ void __launch_bounds__(ATTN_THREADS, 1)
 tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const AttnArgs a, int* __restrict__ status) {
   using L = AttnSmem<D>;
   constexpr int SLABS = L::SLABS;
   constexpr int NS = L::NS;
-  constexpr uint32_t IDESC_S = make_idesc(FMT_BF16, FMT_BF16, 128, KH, 0, 0);
-  constexpr uint32_t IDESC_O = make_idesc(FMT_BF16, FMT_BF16, 128, D, 0, 1);  // B = V, MN-major (head dim contiguous)
+  // one CTA: S in two halves of 64 keys (one K stage each); a pair: the whole 128-key tile at once, 64 keys from each CTA
+  constexpr uint32_t IDESC_S = PAIR ? make_idesc(FMT_BF16, FMT_BF16, 256, 128, 0, 0) : make_idesc(FMT_BF16, FMT_BF16, 128, KH, 0, 0);
+  constexpr uint32_t IDESC_O = make_idesc(FMT_BF16, FMT_BF16, PAIR ? 256 : 128, D, 0, 1);  // B = V, MN-major (head dim contiguous)
+  constexpr int V_SLABS = PAIR ? SLABS / 2 : SLABS;  // 64-dimension slabs of V this CTA holds
+  constexpr int V_ROWS = PAIR ? 128 : KH;            // keys per V stage
+  constexpr int STAGES_PER_TILE = PAIR ? 1 : 2;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -109,15 +183,19 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* v_full = k_empty + NS;         // NS
   uint64_t* v_empty = v_full + NS;         // NS
   uint64_t* s_full = v_empty + NS;         // 4: [buffer][half]
-  uint64_t* p_ready = s_full + 4;          // 1 (256 arrivals)
+  uint64_t* p_ready = s_full + 4;          // 1 (one arrival per softmax warp)
   uint64_t* o_done = p_ready + 1;          // 1
-  uint64_t* o_free = o_done + 1;           // 1 (256 arrivals)
+  uint64_t* o_free = o_done + 1;           // 1 (one arrival per softmax warp)
   uint32_t* tmem_base_p = reinterpret_cast<uint32_t*>(o_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_p + 1);
   float* xchg = reinterpret_cast<float*>(smem + L::XCHG_OFF);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const WaitCtx wc{abort_flag, status};
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  // items of this CTA: item = (query block, head pair, 64-row half); a pair takes both halves, half = rank
+  const int item0 = PAIR ? 2 * (static_cast<int>(blockIdx.x) >> 1) + static_cast<int>(rank) : static_cast<int>(blockIdx.x);
+  const int item_step = PAIR ? static_cast<int>(gridDim.x) : static_cast<int>(gridDim.x);
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -129,9 +207,9 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(&v_empty[i], 1);
     }
     for (int i = 0; i < 4; ++i) mbar_init(&s_full[i], 1);
-    mbar_init(p_ready, 256);
+    mbar_init(p_ready, PAIR ? 16 : 8);  // one arrival per softmax warp; in a pair both CTAs' warps arrive on the leader's barrier
     mbar_init(o_done, 1);
-    mbar_init(o_free, 256);
+    mbar_init(o_free, PAIR ? 16 : 8);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmQ);
@@ -139,11 +217,17 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     tma_prefetch_desc(&tmV);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_base_p, L::TMEM_COLS);
-    tmem_relinquish();
+    if (PAIR) {  // the same warp in both CTAs allocates the pair's tensor memory
+      tmem_alloc_pair(tmem_base_p, L::TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_base_p, L::TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();  // both CTAs' barriers are initialised before any remote arrival or peer-signalled copy
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_p;
 
@@ -157,7 +241,15 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int base = is_k ? L::K_OFF : L::V_OFF;
       uint32_t cnt = 0, item_n = 0;  // stages issued so far; items so far
       bool ok = true;
-      for (int it = blockIdx.x; it < a.n_items && ok; it += gridDim.x) {
+      // in a pair every copy completes on the leader's barrier, which expects both CTAs' bytes
+      const uint32_t q_bar = PAIR ? map_to_cta(q_full, 0) : 0u;
+      auto load = [&](void* dst, const CUtensorMap* m, int c0, int c1, uint64_t* bar) {
+        if (PAIR)
+          tma_load_2d_pair(dst, m, c0, c1, map_to_cta(bar, 0));
+        else
+          tma_load_2d(dst, m, c0, c1, bar);
+      };
+      for (int it = item0; it < a.n_items && ok; it += item_step) {
         const AttnItem w = attn_item(a, it);
         const int e0 = a.tile_offsets[w.qb];
         const int n_tiles = a.tile_offsets[w.qb + 1] - e0;
@@ -165,14 +257,14 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const int g = w.h0 / a.group;
         if (is_k) {
           if (!mbar_wait(wc, q_empty, (item_n & 1u) ^ 1u, ST_TIMEOUT_EMPTY)) break;
-          mbar_expect_tx(q_full, L::Q_BYTES);
+          if (!PAIR || rank == 0) mbar_expect_tx(q_full, (PAIR ? 2 : 1) * L::Q_BYTES);
           const int rows = 128 / a.hp;
           for (int hh = 0; hh < a.hp; ++hh)
             for (int s = 0; s < SLABS; ++s)
-              tma_load_2d(smem + s * 128 * 128 + hh * rows * 128, &tmQ, (w.h0 + hh) * D + s * 64, w.qb * 128 + w.row0, q_full);
+              load(smem + s * 128 * 128 + hh * rows * 128, &tmQ, (w.h0 + hh) * D + s * 64, w.qb * 128 + w.row0, q_full);
         }
-        for (int t = 0; t < 2 * n_tiles; ++t, ++cnt) {
-          const int j = a.tile_blocks[e0 + (t >> 1)];
+        for (int t = 0; t < STAGES_PER_TILE * n_tiles; ++t, ++cnt) {
+          const int j = a.tile_blocks[e0 + t / STAGES_PER_TILE];
           if (j < 0 || j >= a.nb) {
             *abort_flag = 1;
             atomicCAS(status, 0, ST_BAD_INDEX);
@@ -181,14 +273,28 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
           const uint32_t st = cnt % NS, ph = (cnt / NS) & 1u;
           if (!mbar_wait(wc, &empty[st], ph ^ 1u, ST_TIMEOUT_EMPTY)) { ok = false; break; }
-          const int kv0 = j * 128 + (t & 1) * KH;
-          mbar_expect_tx(&full[st], L::KV_HALF);
-          for (int s = 0; s < SLABS; ++s) tma_load_2d(smem + base + st * L::KV_HALF + s * KH * 128, tm, g * D + s * 64, kv0, &full[st]);
+          if (PAIR) {
+            // K: this CTA's 64 keys of the tile, all head dimensions; V: all 128 keys, this CTA's half of the head dimensions
+            if (rank == 0) mbar_expect_tx(&full[st], 2 * L::KV_HALF);
+            if (is_k) {
+              for (int s = 0; s < SLABS; ++s)
+                load(smem + base + st * L::KV_HALF + s * KH * 128, tm, g * D + s * 64, j * 128 + static_cast<int>(rank) * KH, &full[st]);
+            } else {
+              for (int s = 0; s < V_SLABS; ++s)
+                load(smem + base + st * L::KV_HALF + s * V_ROWS * 128, tm, g * D + static_cast<int>(rank) * (D / 2) + s * 64, j * 128, &full[st]);
+            }
+          } else {
+            const int kv0 = j * 128 + (t & 1) * KH;
+            mbar_expect_tx(&full[st], L::KV_HALF);
+            for (int s = 0; s < SLABS; ++s) load(smem + base + st * L::KV_HALF + s * KH * 128, tm, g * D + s * 64, kv0, &full[st]);
+          }
         }
         ++item_n;
       }
-      if (*abort_flag) {
-        // bounded wait for copies of this CTA that may still be in flight
+      (void)q_bar;
+      if (*abort_flag && !PAIR) {
+        // bounded wait for copies of this CTA that may still be in flight (in a pair they complete on the leader's barriers; the
+        // cluster barrier at the end keeps both CTAs resident meanwhile)
         if (is_k)
           for (int spin = 0; spin < 4096 && !mbar_try_wait(q_full, (item_n & 1u) ^ 1u); ++spin) {}
         for (uint32_t c = cnt > static_cast<uint32_t>(NS) ? cnt - NS : 0; c < cnt; ++c)
@@ -196,12 +302,12 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    if (lane == 0 && rank == 0) {  // in a pair the leader issues for both CTAs
       const uint32_t q_addr = smem_u32(smem);
       uint32_t kc = 0, vc = 0, gt = 0, item_n = 0;  // K / V stages consumed, tiles issued, items so far
       bool ok = true;
-      auto issue_s = [&](uint32_t g) -> bool {  // both halves of S for tile g into S buffer g & 1
-        for (int hf = 0; hf < 2; ++hf, ++kc) {
+      auto issue_s = [&](uint32_t g) -> bool {  // S for tile g into S buffer g & 1: two halves of 64 keys, or (pair) the tile at once
+        for (int hf = 0; hf < STAGES_PER_TILE; ++hf, ++kc) {
           const uint32_t st = kc % NS;
           if (!mbar_wait(wc, &k_full[st], (kc / NS) & 1u, ST_TIMEOUT_FULL)) return false;
           tc_fence_after();
@@ -212,14 +318,15 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             const uint64_t ad = make_smem_desc_sw128(q_addr + s * 128 * 128, 16, 1024);
             const uint64_t bd = make_smem_desc_sw128(k_addr + s * KH * 128, 16, 1024);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) umma_f16_ss(d_tmem, ad + 2 * k, bd + 2 * k, IDESC_S, (s | k) != 0);
+            for (int k = 0; k < 4; ++k) attn_mma_ss<PAIR>(d_tmem, ad + 2 * k, bd + 2 * k, IDESC_S, (s | k) != 0);
           }
-          umma_commit(&k_empty[st]);  // the K stage may be refilled as soon as these MMAs have read it
-          umma_commit(&s_full[(g & 1u) * 2 + hf]);
+          attn_commit<PAIR>(&k_empty[st]);  // the K stage may be refilled as soon as these MMAs have read it
+          attn_commit<PAIR>(&s_full[(g & 1u) * 2 + hf]);
+          if (PAIR) attn_commit<PAIR>(&s_full[(g & 1u) * 2 + 1]);  // both softmax groups' halves come out of the one product
         }
         return true;
       };
-      for (int it = blockIdx.x; it < a.n_items && ok; it += gridDim.x) {
+      for (int it = item0; it < a.n_items && ok; it += item_step) {
         const AttnItem w = attn_item(a, it);
         const int n_tiles = a.tile_offsets[w.qb + 1] - a.tile_offsets[w.qb];
         if (n_tiles <= 0) continue;
@@ -232,25 +339,29 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             // S buffer (g+1)&1 last held P of tile g-1, whose P V MMAs were issued before these
             if (!issue_s(g + 1)) { ok = false; break; }
           } else {
-            umma_commit(q_empty);  // Q may be replaced once the last S MMAs of the item have read it
+            attn_commit<PAIR>(q_empty);  // Q may be replaced once the last S MMAs of the item have read it
           }
           if (!mbar_wait(wc, p_ready, g & 1u, ST_TIMEOUT_OTHER)) { ok = false; break; }
           if (i == 0 && item_n > 0 && !mbar_wait(wc, o_free, (item_n - 1) & 1u, ST_TIMEOUT_OTHER)) { ok = false; break; }
-          for (int hf = 0; hf < 2 && ok; ++hf, ++vc) {
+          for (int part = 0; part < STAGES_PER_TILE && ok; ++part, ++vc) {
             const uint32_t st = vc % NS;
             if (!mbar_wait(wc, &v_full[st], (vc / NS) & 1u, ST_TIMEOUT_FULL)) { ok = false; break; }
             tc_fence_after();
             const uint32_t v_addr = smem_u32(smem + L::V_OFF + st * L::KV_HALF);
-            // V stage: slab s holds head-dim columns [64 s, 64 s + 64) of 64 keys, one key per 128-byte row:
-            // MN-major B operand, 64-column groups KH*128 bytes apart (LBO), 8-key groups 1024 bytes apart (SBO)
-            const uint64_t vd = make_smem_desc_sw128(v_addr, KH * 128, 1024);
-            const uint32_t p_tmem = tmem_base + (g & 1u) * 128 + hf * KH;  // packed bf16 P: 16 keys per 8 columns
+            // V stage: slab s holds 64 head-dim columns of the stage's keys, one key per 128-byte row: MN-major B operand,
+            // 64-column groups V_ROWS*128 bytes apart (LBO), 8-key groups 1024 bytes apart (SBO)
+            const uint64_t vd = make_smem_desc_sw128(v_addr, V_ROWS * 128, 1024);
 #pragma unroll
-            for (int k = 0; k < 4; ++k)  // 16 keys per step: 8 columns along P, 16 rows (2048 bytes) down V
-              umma_f16_ts(tmem_base + L::O_COL, p_tmem + 8 * k, vd + 128 * k, IDESC_O, (i | hf | k) != 0);
-            umma_commit(&v_empty[st]);
+            for (int hh = 0; hh < (PAIR ? 2 : 1); ++hh) {  // a pair's V stage covers both softmax groups' keys
+              const int hf = PAIR ? hh : part;
+              const uint32_t p_tmem = tmem_base + (g & 1u) * 128 + hf * KH;  // packed bf16 P: 16 keys per 8 columns
+#pragma unroll
+              for (int k = 0; k < 4; ++k)  // 16 keys per step: 8 columns along P, 16 rows (2048 bytes) down V
+                attn_mma_ts<PAIR>(tmem_base + L::O_COL, p_tmem + 8 * k, vd + 128 * ((PAIR ? 4 * hh : 0) + k), IDESC_O, (i | hf | k) != 0);
+            }
+            attn_commit<PAIR>(&v_empty[st]);
           }
-          if (ok) umma_commit(o_done);
+          if (ok) attn_commit<PAIR>(o_done);
         }
         gt += n_tiles;
         ++item_n;
@@ -275,18 +386,18 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         pbits = a.tile_bits[(static_cast<int64_t>(e0) * 2 + wg) * 128 + w.row0 + (row % rows_per_head)];
       }
     };
-    if (static_cast<int>(blockIdx.x) < a.n_items) {
-      const AttnItem w = attn_item(a, blockIdx.x);
+    if (item0 < a.n_items) {
+      const AttnItem w = attn_item(a, item0);
       pe0 = a.tile_offsets[w.qb], pe1 = a.tile_offsets[w.qb + 1];
       first_entry(w, pe0, pe1);
     }
-    for (int it = blockIdx.x; it < a.n_items && alive; it += gridDim.x) {
+    for (int it = item0; it < a.n_items && alive; it += item_step) {
       const AttnItem w = attn_item(a, it);
       const int e0 = pe0;
       const int n_tiles = pe1 - pe0;
       int j_next = pj, f_next = pf;
       uint64_t bits_next = (pf & 2) ? ~0ull : pbits;
-      const int it_n = it + gridDim.x;
+      const int it_n = it + item_step;
       const bool have_n = it_n < a.n_items;
       const AttnItem w_n = attn_item(a, have_n ? it_n : it);
       if (have_n) pe0 = a.tile_offsets[w_n.qb], pe1 = a.tile_offsets[w_n.qb + 1];  // consumed at the end of this item
@@ -387,7 +498,13 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_st_x32(s_tmem, pk);  // P over the first 32 columns of the S half this thread has already read
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(p_ready);
+        __syncwarp();  // every lane's P is in tensor memory: one arrival per warp (a remote arrival per thread costs 1 200 cycles a tile)
+        if (lane == 0) {
+          if (PAIR)
+            mbar_arrive_cluster(map_to_cta(p_ready, 0));
+          else
+            mbar_arrive(p_ready);
+        }
         TR(t6);
         TR_ADD(0, t1 - t0); TR_ADD(1, t2 - t1); TR_ADD(2, t3 - t2); TR_ADD(3, t4 - t3); TR_ADD(4, t5 - t4); TR_ADD(5, t6 - t5); TR_ADD(6, 1);
       }
@@ -416,7 +533,13 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_wait_ld();
         if (c + 2 >= D / 64) {  // O is in registers: the next item's first P V may overwrite it
           tc_fence_before();
-          mbar_arrive(o_free);
+          __syncwarp();
+          if (lane == 0) {
+            if (PAIR)
+              mbar_arrive_cluster(map_to_cta(o_free, 0));
+            else
+              mbar_arrive(o_free);
+          }
         }
 #pragma unroll
         for (int hfc = 0; hfc < 2; ++hfc) {
@@ -443,10 +566,14 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();  // neither CTA leaves while its peer may still signal its barriers or read its shared memory
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
-    tmem_dealloc(tmem_base, L::TMEM_COLS);
+    if (PAIR)
+      tmem_dealloc_pair(tmem_base, L::TMEM_COLS);
+    else
+      tmem_dealloc(tmem_base, L::TMEM_COLS);
   }
 }
 
@@ -488,7 +615,7 @@ __global__ void __launch_bounds__(256) tile_mask_bits_kernel(const int32_t* __re
   }
 }
 
-template <int D>
+template <int D, bool PAIR>
 static int launch_attn(const void* q, const void* k, const void* v, int64_t n, int H, int Hkv, int64_t q_pitch, int64_t kv_pitch,
                        const AttnArgs& args, cudaStream_t stream) {
   using L = AttnSmem<D>;
@@ -501,15 +628,33 @@ static int launch_attn(const void* q, const void* k, const void* v, int64_t n, i
   if ((r = make_tmap_2d(&tmQ, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, q, n, static_cast<uint64_t>(H) * D, q_pitch * 2, 64, 128 / args.hp)))
     return r;
   if ((r = make_tmap_2d(&tmK, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k, n, static_cast<uint64_t>(Hkv) * D, kv_pitch * 2, 64, KH))) return r;
-  if ((r = make_tmap_2d(&tmV, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, v, n, static_cast<uint64_t>(Hkv) * D, kv_pitch * 2, 64, KH))) return r;
-  auto kern = tree_attn_kernel<D>;
+  // V boxes: 64 keys of all head dimensions for one CTA; all 128 keys of the CTA's half of the head dimensions in a pair
+  if ((r = make_tmap_2d(&tmV, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, v, n, static_cast<uint64_t>(Hkv) * D, kv_pitch * 2, 64, PAIR ? 128 : KH)))
+    return r;
+  auto kern = tree_attn_kernel<D, PAIR>;
   static bool attr_set[64] = {false};
   if (!attr_set[dev]) {
     SPINF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
     attr_set[dev] = true;
   }
-  const int grid = args.n_items < sm_count() ? args.n_items : sm_count();
-  kern<<<grid, ATTN_THREADS, L::TOTAL, stream>>>(tmQ, tmK, tmV, args, status);
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(ATTN_THREADS);
+  cfg.dynamicSmemBytes = L::TOTAL;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (PAIR) {
+    const int pairs = args.n_items / 2 < sm_count() / 2 ? args.n_items / 2 : sm_count() / 2;
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  } else {
+    cfg.gridDim = dim3(static_cast<unsigned>(args.n_items < sm_count() ? args.n_items : sm_count()));
+  }
+  SPINF_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, tmQ, tmK, tmV, args, status));
   SPINF_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -560,8 +705,13 @@ extern "C" int spinf_tree_attn_fwd(const void* q, const void* k, const void* v, 
   a.window = window;
   a.scale_log2 = scale * 1.4426950408889634f;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (D == 256) return launch_attn<256>(q, k, v, n, H, Hkv, q_pitch, kv_pitch, a, st);
-  return launch_attn<128>(q, k, v, n, H, Hkv, q_pitch, kv_pitch, a, st);
+  // two query heads per key/value head (or a multiple): the two 64-row halves of a query block run as a CTA pair sharing K / V
+  const bool pair = a.hp == 2 && a.n_items % 2 == 0 && a.n_items >= 2;
+  if (D == 256)
+    return pair ? launch_attn<256, true>(q, k, v, n, H, Hkv, q_pitch, kv_pitch, a, st)
+                : launch_attn<256, false>(q, k, v, n, H, Hkv, q_pitch, kv_pitch, a, st);
+  return pair ? launch_attn<128, true>(q, k, v, n, H, Hkv, q_pitch, kv_pitch, a, st)
+              : launch_attn<128, false>(q, k, v, n, H, Hkv, q_pitch, kv_pitch, a, st);
 }
 
 #ifdef SPINF_TRACE
