@@ -222,7 +222,8 @@ int spinf_embed_scale(const int64_t* ids, const void* emb, int64_t n, int64_t hi
  *     S *= exp(g);  v' = (v - S^T k) * beta;  S += k (x) v';  o = S^T (q * scale)
  * q, k [rows, Hk, K] bf16 (l2-normalised by the caller), v [rows, Hv, V] bf16, g fp32 / beta bf16 [rows, Hv], each with its row
  * pitch in elements (g and beta share g_pitch); o [rows, Hv, V] bf16 contiguous, written at the same rows; h0 / ht
- * [*, Hv, K, V] fp32. K = V = 128. Token-serial: any segment length is accepted; segments longer than 64 tokens are meant for
+ * [*, Hv, K, V] fp32. K = V = 128; Hv and g_pitch even, q / k / v 16-byte aligned with pitches that are multiples of 8 elements.
+ * Token-serial: any segment length is accepted; segments longer than 64 tokens are meant for
  * spinf_gdn_chunked below. */
 int spinf_gdn_recurrent(const void* q, const void* k, const void* v, const float* g, const void* beta, void* o, int64_t n_rows,
                         int64_t q_pitch, int64_t v_pitch, int64_t g_pitch, int32_t Hk, int32_t Hv, int32_t K, int32_t V, float scale,

@@ -323,6 +323,18 @@ __device__ __forceinline__ void stg_v8(void* p, const uint32_t (&r)[8]) {
                "r"(r[5]), "r"(r[6]), "r"(r[7])
                : "memory");
 }
+// asynchronous 16-byte copies global -> shared (a source size of 0 fills the destination with zeros and reads nothing)
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
 // packed bf16 pairs as 32-bit words: element 0 in the low half. The products and sums are the hardware's bf16 operations: the
 // exact result rounded once to bf16 (nearest-even), which is what rounding the fp32 product / sum of two bf16 values gives.
 __device__ __forceinline__ uint32_t bf2_mul(uint32_t a, uint32_t b) {

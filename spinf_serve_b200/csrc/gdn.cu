@@ -2,8 +2,8 @@
 //
 // gdn_recurrent_kernel: the gated delta rule, token by token, over the segments of one plan call. One CTA = one (segment, value
 // head); thread c owns column c of the state S [K=128, V=128] in 128 fp32 registers, so both reductions over K (S^T k and S^T q)
-// are thread-local and the state never leaves the register file between tokens. The token's k and q rows are staged through a
-// double-buffered shared tile (loaded one token ahead). A segment starts from h0[h0_idx] (the state its parent segment left) or
+// are thread-local and the state never leaves the register file between tokens. A token's operands arrive through a ring of shared
+// slots filled by cp.async three tokens ahead; k and q are converted to fp32 into a double-buffered tile one token ahead. A segment starts from h0[h0_idx] (the state its parent segment left) or
 // zero and writes its final state to ht[ht_idx] where a child will read it: a branch forks the trunk's state by index, the trunk
 // state itself is written once.
 //     S *= exp(g);  v' = (v - S^T k) beta;  S += k (x) v';  o = S^T (q scale)
@@ -36,8 +36,17 @@ struct GdnArgs {
   int64_t n_rows;           // rows of the tensors (index bound)
 };
 
+static constexpr int RING = 6;  // raw operand slots: tokens t .. t + 5 in flight (the copies of token t + 2 are waited for at step t)
+struct __align__(16) RawSlot {
+  uint4 kqv[3 * GK * 2 / 16];  // k, q, v rows of the head, bf16
+  float g;
+  uint32_t beta2;              // the aligned 4-byte word that holds the head's beta
+  int64_t row;
+};
+
 __global__ void __launch_bounds__(128) gdn_recurrent_kernel(const GdnArgs a, int* __restrict__ status) {
   __shared__ __align__(16) float kq[2][2][GK];  // [buffer][k | q][GK]
+  __shared__ RawSlot raw[RING];
   const int seg = blockIdx.x / a.Hv, hv = blockIdx.x % a.Hv;
   const int hk = hv / (a.Hv / a.Hk);
   const int c = threadIdx.x;
@@ -60,22 +69,30 @@ __global__ void __launch_bounds__(128) gdn_recurrent_kernel(const GdnArgs a, int
     }
     return r;
   };
-  // stage token `t`'s k and q rows: threads 0-15 carry k, 16-31 carry q (8 elements each)
-  uint4 pre = make_uint4(0, 0, 0, 0);
-  float pv = 0.f, pg = 0.f, pb = 0.f;
-  int64_t pr = 0;
-  auto fetch = [&](int64_t t) {
-    pr = row_of(t);
-    if (c < 32) {
-      const __nv_bfloat16* base = (c < 16 ? a.k : a.q) + pr * a.q_pitch + hk * GK + (c & 15) * 8;
-      pre = *reinterpret_cast<const uint4*>(base);
+  // A token's operands (k, q, v rows of the head, g, beta) travel through a ring of RING raw slots filled by cp.async three tokens
+  // ahead: a token step is shorter than a trip to HBM, so one token of prefetch left every step waiting for its loads. Threads
+  // 0-15 copy k, 16-31 q, 32-47 v (16 bytes each), 48 copies g, 49 the 4-byte word that holds beta.
+  auto issue = [&](int64_t t, int64_t r) {
+    RawSlot& sl = raw[(t - bos) % RING];
+    if (c < 50) {
+      if (c < 48) {
+        const int part = c >> 4, j = c & 15;
+        const __nv_bfloat16* src = part == 0 ? a.k + r * a.q_pitch + hk * GK : (part == 1 ? a.q + r * a.q_pitch + hk * GK : a.v + r * a.v_pitch + hv * GV);
+        cp_async16(reinterpret_cast<__nv_bfloat16*>(sl.kqv) + part * GK + j * 8, src + j * 8, 16);
+      } else if (c == 48) {
+        cp_async4(&sl.g, a.g + r * a.g_pitch + hv);
+        sl.row = r;
+      } else {
+        cp_async4(&sl.beta2, reinterpret_cast<const uint32_t*>(a.beta + r * a.g_pitch + (hv & ~1)));
+      }
     }
-    pv = __bfloat162float(a.v[pr * a.v_pitch + hv * GV + c]);
-    pg = a.g[pr * a.g_pitch + hv];
-    pb = __bfloat162float(a.beta[pr * a.g_pitch + hv]);
+    cp_async_commit();
   };
-  auto stash = [&](int buf) {
+  // k and q of token t, converted to fp32 (q scaled), into the fp32 buffer the inner loops read
+  auto stash = [&](int64_t t, int buf) {
     if (c < 32) {
+      const RawSlot& sl = raw[(t - bos) % RING];
+      const uint4 pre = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(sl.kqv) + (c >> 4) * GK + (c & 15) * 8);
       const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pre);
       float* dst = kq[buf][c < 16 ? 0 : 1] + (c & 15) * 8;
       const float sc = c < 16 ? 1.f : a.scale;
@@ -87,16 +104,32 @@ __global__ void __launch_bounds__(128) gdn_recurrent_kernel(const GdnArgs a, int
       }
     }
   };
-  if (bos < eos) {
-    fetch(bos);
-    stash(0);
+  const int64_t n_tok = eos - bos;
+  for (int64_t t = bos; t < bos + RING - 1; ++t) {
+    if (t < eos) issue(t, c < 50 ? row_of(t) : 0);
+    else cp_async_commit();  // keeps the group count uniform
+  }
+  // the row index of the token to be issued next is read one step ahead: the copy's address must not wait for it
+  int64_t r_ahead = (c < 50 && bos + RING - 1 < eos) ? row_of(bos + RING - 1) : 0;
+  if (n_tok > 0) {
+    cp_async_wait<RING - 3>();  // tokens 0 and 1 have landed
+    __syncthreads();
+    stash(bos, 0);
   }
   __syncthreads();
   for (int64_t t = bos; t < eos; ++t) {
     const int buf = static_cast<int>((t - bos) & 1);
-    const float vt = pv, eg = expf(pg), bt = pb;
-    const int64_t r = pr;
-    if (t + 1 < eos) fetch(t + 1);  // in flight while this token is computed
+    const RawSlot& sl = raw[(t - bos) % RING];
+    // token t + 1 landed before the barrier that ended the previous step; its fp32 buffer was last read one step ago
+    if (t + 1 < eos) stash(t + 1, buf ^ 1);
+    const float vt = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(sl.kqv)[2 * GK + c]);
+    const float eg = expf(sl.g);
+    const float bt = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(&sl.beta2)[hv & 1]);
+    const int64_t r = sl.row;
+    // the slot of token t + RING - 1 is the one token t - 1 used: every thread passed the barrier that ended that step
+    if (t + RING - 1 < eos) issue(t + RING - 1, r_ahead);
+    else cp_async_commit();
+    if (c < 50 && t + RING < eos) r_ahead = row_of(t + RING);
     const float4* kv4 = reinterpret_cast<const float4*>(kq[buf][0]);
     const float4* qv4 = reinterpret_cast<const float4*>(kq[buf][1]);
     // four independent partial sums per reduction: a single accumulator would serialise 128 dependent FMAs per token
@@ -127,9 +160,10 @@ __global__ void __launch_bounds__(128) gdn_recurrent_kernel(const GdnArgs a, int
     }
     const float od = (o0 + o1) + (o2 + o3);
     a.o[(r * a.Hv + hv) * GV + c] = __float2bfloat16_rn(od);
-    if (t + 1 < eos) stash(buf ^ 1);  // the other buffer was last read one token ago, before the previous barrier
+    cp_async_wait<RING - 3>();  // this thread's copies of token t + 2 have landed; the barrier covers the other threads'
     __syncthreads();
   }
+  cp_async_wait<0>();
   const int64_t dst = (a.ht && a.ht_idx) ? a.ht_idx[seg] : -1;
   if (dst >= 0) {
     float* p = a.ht + (dst * a.Hv + hv) * GK * GV + c;
@@ -284,6 +318,9 @@ extern "C" int spinf_gdn_recurrent(const void* q, const void* k, const void* v, 
   SPINF_CHECK_ARG(q_pitch >= static_cast<int64_t>(Hk) * GK && q_pitch % 8 == 0 && v_pitch >= static_cast<int64_t>(Hv) * GV && g_pitch >= Hv);
   SPINF_CHECK_ARG((h0 == nullptr) == (h0_idx == nullptr) && (ht == nullptr) == (ht_idx == nullptr));
   SPINF_CHECK_ARG(n_seg * Hv < (1ll << 31));
+  // rows are copied in 16-byte pieces, beta as the aligned 4-byte word around it
+  SPINF_CHECK_ARG(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) == 0);
+  SPINF_CHECK_ARG(v_pitch % 8 == 0 && g_pitch % 2 == 0 && Hv % 2 == 0 && (reinterpret_cast<uintptr_t>(beta) & 3) == 0);
   if (n_seg == 0) return 0;
   int dev = 0;
   SPINF_CUDA_OK(cudaGetDevice(&dev));

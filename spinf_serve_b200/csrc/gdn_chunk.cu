@@ -77,15 +77,6 @@ __device__ __forceinline__ const __nv_bfloat16* frag_b_t(const __nv_bfloat16* m,
   return m + (k0 + (lane & 7) + ((lane >> 3) & 1) * 8) * ld + n0 + (lane >> 4) * 8;
 }
 
-// asynchronous 16-byte copies global -> shared (a source size of 0 fills the destination with zeros and reads nothing)
-__device__ __forceinline__ void cp_async16(void* dst, const void* src, int src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
 // rows of a [CT x CK] bf16 tile from global rows src(t) (nullptr: zero row): every copy of the tile is in flight at once
 template <class RowPtr>
 __device__ __forceinline__ void load_tile(__nv_bfloat16* dst, RowPtr src, const __nv_bfloat16* any_valid, int tid, int nthreads) {
