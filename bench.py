@@ -81,9 +81,10 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------------ CPU arm (the oracle, a port)
-def cpu_sample(threads: int):
-    """the CPU oracle on a bounded sample of the workload: 2 of the 24 contents (2284 tokens, 112 questions) through ONE of the
-    48 layers plus the lm-head read of their 112 rows; -> a closure that runs the sample once and returns (layer_s, head_s)"""
+def cpu_sample(threads: int, n_contents: int = 2, layers: int = 1):
+    """the CPU oracle on a bounded sample of the workload: n_contents of the 24 contents (1142 tokens, 56 questions each) through
+    `layers` of the 48 layers plus the lm-head read of their rows; -> a closure that runs the sample once and returns
+    (seconds in the layers, seconds in the head read)"""
     import numpy as np
     import torch
 
@@ -93,7 +94,7 @@ def cpu_sample(threads: int):
     from spinf_serve_b200 import workloads
 
     torch.set_num_threads(threads)
-    cfg = OG.GemmaConfig(layers=1)
+    cfg = OG.GemmaConfig(layers=layers)
     g = torch.Generator().manual_seed(0)
 
     def lin(o, i):
@@ -107,9 +108,9 @@ def cpu_sample(threads: int):
         "q_norm": ones(D), "k_norm": ones(D), "input_ln": ones(cfg.hidden), "post_attn_ln": ones(cfg.hidden),
         "pre_ffn_ln": ones(cfg.hidden), "post_ffn_ln": ones(cfg.hidden),
     }
-    W = {"embed": lin(cfg.vocab, cfg.hidden), "norm": ones(cfg.hidden), "layers": [L]}
+    W = {"embed": lin(cfg.vocab, cfg.hidden), "norm": ones(cfg.hidden), "layers": [L] * layers}  # the same weights in every layer
     Q = OG.quantize(W)
-    wl = workloads.config2(seed=0, n_contents=2)
+    wl = workloads.config2(seed=0, n_contents=n_contents)
     pk = P.Packer(32768, 65536, True, 1024)
     batches = [b for key, first, t in wl.items for b in pk.push((key, first), t)] + list(pk.flush())
     (b,) = batches
@@ -126,25 +127,26 @@ def cpu_sample(threads: int):
     return run, wl
 
 
-def cpu_questions_per_s(layer_s: float, head_s: float, sample_tokens: int, sample_questions: int):
+def cpu_questions_per_s(layer_s: float, head_s: float, sample_tokens: int, sample_questions: int, sample_layers: int = 1):
     """extrapolation of the sample to the full workload: layers x tokens for the forward, rows for the head"""
-    full = layer_s * 48 * (27408 / sample_tokens) + head_s * (1344 / sample_questions)
+    full = layer_s * (48 / sample_layers) * (27408 / sample_tokens) + head_s * (1344 / sample_questions)
     return 1344 / full, full
 
 
-def cpu_baseline(threads: int, steps: int = 1):
-    run, wl = cpu_sample(threads)
+def cpu_baseline(threads: int, steps: int = 1, n_contents: int = 8, layers: int = 2):
+    """the sample is sized for roughly ten seconds of CPU work on a 16-core host: 8 contents through 2 layers + their 448 read rows"""
+    run, wl = cpu_sample(threads, n_contents, layers)
     times = [run() for _ in range(steps)]
     layer_s = min(t[0] for t in times)
     head_s = min(t[1] for t in times)
-    qps, full = cpu_questions_per_s(layer_s, head_s, wl.n_tokens, wl.n_questions)
+    qps, full = cpu_questions_per_s(layer_s, head_s, wl.n_tokens, wl.n_questions, layers)
     return {
         "value": qps,
         "unit": UNIT,
         "cores": threads,
         "kind": "port",
-        "sample": f"CPU oracle (torch fp32, {threads} threads) on 2 of 24 contents ({wl.n_tokens} tokens, {wl.n_questions} questions) through 1 of 48 layers "
-        f"({layer_s:.2f} s) + lm-head read of their rows ({head_s:.2f} s); scaled x48 layers x{27408 / wl.n_tokens:.1f} tokens and x{1344 // wl.n_questions} rows "
+        "sample": f"CPU oracle (torch fp32, {threads} threads) on {n_contents} of 24 contents ({wl.n_tokens} tokens, {wl.n_questions} questions) through {layers} of 48 layers "
+        f"({layer_s:.2f} s) + lm-head read of their rows ({head_s:.2f} s); scaled x{48 // layers} in layers, x{27408 / wl.n_tokens:.1f} in tokens and x{1344 // wl.n_questions} in rows "
         f"to the full step ({full:.0f} s)",
     }
 
