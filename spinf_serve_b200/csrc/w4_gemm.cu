@@ -43,8 +43,8 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);  // TMA landed (A + raw W)
-  uint64_t* empty = full + STAGES;                                   // 1 MMA commit + 128 dequantiser arrivals
-  uint64_t* b_full = empty + STAGES;                                 // 128 dequantiser arrivals
+  uint64_t* empty = full + STAGES;                                   // 1 MMA commit + 4 dequantiser-warp arrivals
+  uint64_t* b_full = empty + STAGES;                                 // 4 dequantiser-warp arrivals
   uint64_t* b_empty = b_full + BSTAGES;                              // 1 MMA commit
   uint64_t* acc_full = b_empty + BSTAGES;
   uint64_t* acc_empty = acc_full + 2;
@@ -56,10 +56,10 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&empty[s], 129);
+      mbar_init(&empty[s], 5);  // the MMA commit + one arrival per warp of the dequantising group
     }
     for (int s = 0; s < BSTAGES; ++s) {
-      mbar_init(&b_full[s], 128);
+      mbar_init(&b_full[s], 4);  // one arrival per warp of the dequantising group
       mbar_init(&b_empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -197,8 +197,11 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           *reinterpret_cast<uint4*>(btile + sw128_offset(n_local, c)) = make_uint4(out[0], out[1], out[2], out[3]);
         }
         fence_proxy_async_smem();
-        mbar_arrive(&b_full[bs]);
-        mbar_arrive(&empty[s]);  // the raw tile has been read
+        __syncwarp();  // every lane's chunk is written and fenced: one arrival per warp instead of 32
+        if (lane == 0) {
+          mbar_arrive(&b_full[bs]);
+          mbar_arrive(&empty[s]);  // the raw tile has been read
+        }
       }
     }
   } else {
