@@ -98,65 +98,27 @@ __device__ unsigned long long g_attn_trace[16];
 // leader issues the pair's MMAs (M = 256: 128 query rows per CTA) and each CTA keeps its own S / P / O in its own tensor memory.
 // Half the K / V bytes per CTA leave room for two whole tiles of each in flight. No load is multicast: each CTA fetches exactly the
 // bytes it alone holds; the peer's barriers are reached through shared::cluster addresses.
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
-__device__ __forceinline__ uint32_t map_to_cta(const void* p, uint32_t rank) {
-  uint32_t out;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_u32(p)), "r"(rank));
-  return out;
-}
-// (default semantics: release at CTA scope. The data the leader's MMAs read after this arrival is in tensor memory and ordered by
-// the tcgen05 fences; a cluster-scope release here cost 1 200 cycles per arrival)
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-// TMA load of this CTA's bytes that completes on a barrier given as a shared::cluster address (the leader's)
-__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* m, int c0, int c1, uint32_t bar_cluster_addr) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_dst, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish_pair() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
 template <bool PAIR>
 __device__ __forceinline__ void attn_mma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   if (PAIR)
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+    umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, accumulate);
   else
     umma_f16_ss(d_tmem, adesc, bdesc, idesc, accumulate);
 }
 template <bool PAIR>
 __device__ __forceinline__ void attn_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   if (PAIR)
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-                 ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+    umma_f16_ts_pair(d_tmem, a_tmem, bdesc, idesc, accumulate);
   else
     umma_f16_ts(d_tmem, a_tmem, bdesc, idesc, accumulate);
 }
 // the MMAs issued so far by this thread arrive on `bar` when they have completed: in this CTA, or in both CTAs of the pair
 template <bool PAIR>
 __device__ __forceinline__ void attn_commit(uint64_t* bar) {
-  if (PAIR) {
-#pragma unroll
-    for (uint32_t r = 0; r < 2; ++r)
-      asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(map_to_cta(bar, r)) : "memory");
-  } else {
+  if (PAIR)
+    umma_commit_pair(bar);
+  else
     umma_commit(bar);
-  }
 }
 
 template <int D, bool PAIR>

@@ -3,81 +3,101 @@
 // x bf16, fp32 accumulation in tensor memory, bf16 out. The weights stay int4 in HBM and are expanded on the way to the tensor
 // core: nothing the size of the bf16 weight matrix is ever written.
 //
-// Persistent, one CTA per SM, 256 x 128 output tiles (two M=128 accumulators share every dequantised weight tile, halving the
-// expansion work per FLOP), K in steps of 64. 14 warps:
-//   warp 0     one lane: TMA loads of the activation tile (256 x 128 B, swizzled) and the raw weight tile (128 rows x 32 B) into a 4-stage ring
-//   warps 6-13 dequantisers in two groups of four warps that take alternate K steps (two steps in flight), thread = weight row:
-//              64 nibbles -> 64 bf16 written as a K-major 128-byte-swizzled tile into a 4-stage ring; a nibble becomes the float 128 + n with one byte permute, then one FMA gives (n - 8) * scale exactly
-//   warp 1     one lane: tcgen05.mma, 2 x (M=128, N=128, K=64) per step, into one of two accumulator pairs
-//   warps 2-5  epilogue: TMEM -> bf16 -> swizzled staging -> TMA store, overlapped with the next tile's main loop
-// K order per output element is ascending inside one CTA and the tile shape does not depend on M: rows are batch-invariant.
+// Persistent CTA pairs (clusters of two, tcgen05 cta_group::2), one pair per two SMs. The product is computed transposed,
+// yT[n, m] = dq(W)[n, :] . x[m, :], with the WEIGHTS as the MMA's A operand, read from tensor memory: a dequantising thread owns one
+// weight row = one TMEM lane and writes its 64 expanded values straight into tensor memory (tcgen05.st), so the expansion never
+// passes through shared memory, and the activations (the B operand, from shared memory) are the only operand the tensor cores
+// fetch there. (Expanding into a shared-memory tile instead left the tensor pipe at 44-48 %: tile writes, operand reads and TMA
+// fills together saturate shared-memory bandwidth.) A pair's tile is 256 weight rows x 256 tokens: CTA r expands weight rows
+// [128 r, 128 r + 128) and loads tokens [128 r, 128 r + 128) of the tile; the leader issues one M = 256, N = 256 MMA per 16 of K
+// and each CTA keeps the accumulator of its own weight rows (128 lanes x 256 token columns). K in steps of 64. 14 warps per CTA:
+//   warp 0     one lane: TMA loads of this CTA's half of the activation tile (128 tokens x 128 B, swizzled; completes on the
+//              leader's barrier) and raw weight tile (128 rows x 32 B; completes on this CTA's barrier) into an 8-stage ring
+//   warps 6-13 dequantisers in two groups of four warps that take alternate K steps, thread = weight row = TMEM lane:
+//              64 nibbles -> 64 bf16 (32 packed columns of the stage's slot in tensor memory); a nibble becomes the float
+//              128 + n with one byte permute, then one FMA gives (n - 8) * scale exactly
+//   warp 1     leader only, one lane: tcgen05.mma (A from tensor memory), 4 x (M=256, N=256, K=16) per step, and one commit per
+//              step (multicast to both CTAs) that frees the stage for the loader and the dequantisers alike
+//   warps 2-5  epilogue: TMEM -> bf16 -> transposed into swizzled staging (lane pairs exchange so that every store is a pair of
+//              neighbouring output channels) -> TMA store
+// Tensor memory: one accumulator (256 columns) + 8 weight slots of 32 columns; the epilogue frees the accumulator as soon as it is
+// in registers / staging (about 3 % of a tile's main loop at K = 5120), while loads and expansion run ahead through the ring.
+// K order per output element is ascending and the tile shape does not depend on M: rows are batch-invariant.
 #include "gemm_tc.cuh"
 #include "host_util.h"
 
 namespace spinf {
 
 struct W4Smem {
-  static constexpr int STAGES = 4, BSTAGES = 4;
-  static constexpr int A_BYTES = 256 * 128;   // activations: 256 rows x 64 bf16
-  static constexpr int RAW_BYTES = 128 * 32;  // raw weights: 128 rows x 64 nibbles
-  static constexpr int STAGE_BYTES = A_BYTES + RAW_BYTES;
-  static constexpr int B_BYTES = 128 * 128;   // dequantised weights: 128 rows x 64 bf16
-  static constexpr int B_OFF = STAGES * STAGE_BYTES;
-  static constexpr int EPI_OFF = B_OFF + BSTAGES * B_BYTES;
-  static constexpr int BAR_OFF = EPI_OFF + 128 * 128;  // one staging tile: the epilogue has a whole main loop of slack
-  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+  static constexpr int STAGES = 8;            // stage s: activation half tile + raw weight tile in shared memory, expansion in TMEM
+  static constexpr int X_BYTES = 128 * 128;   // this CTA's activations: 128 tokens x 64 bf16
+  static constexpr int RAW_BYTES = 128 * 32;  // this CTA's raw weights: 128 rows x 64 nibbles
+  static constexpr int STAGE_BYTES = X_BYTES + RAW_BYTES;
+  static constexpr int EPI_OFF = STAGES * STAGE_BYTES;
+  static constexpr int EPI_BYTES = 64 * 256;  // one staging buffer: 64 tokens x 128 output channels (two swizzled 64 x 64 boxes)
+  static constexpr int BAR_OFF = EPI_OFF + 2 * EPI_BYTES;
+  static constexpr int TOTAL = BAR_OFF + 512 + 1024;
+  static constexpr uint32_t ACC_COL = 0, W_COL = 256;  // tensor-memory columns: accumulator, weight slots (32 columns each)
 };
+static_assert(W4Smem::STAGE_BYTES % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
 
 struct W4Args {
   const __half* scales;  // [N, K / G]
   int M, N, K, G;
-  int tiles_m, tiles_n, group_m;
+  int tiles_m, tiles_n, group_m;  // tiles of 256 tokens x 256 output channels
 };
+
+#ifdef SPINF_TRACE
+// debugging aid, compiled out of the library: cycles the MMA-issuing thread waits for [0] a free accumulator, [1] the activation
+// stage, [2] the dequantised weight stage; [3] K steps, [4] cycles from first to last issue
+__device__ unsigned long long g_w4_trace[8];
+#endif
 
 __global__ void __launch_bounds__(448, 1)
 w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmC,
                const W4Args a, int* __restrict__ status) {
   using L = W4Smem;
-  constexpr int STAGES = L::STAGES, BSTAGES = L::BSTAGES;
-  constexpr uint32_t IDESC = make_idesc(FMT_BF16, FMT_BF16, 128, 128, 0, 0);
+  constexpr int STAGES = L::STAGES;
+  constexpr uint32_t IDESC = make_idesc(FMT_BF16, FMT_BF16, 256, 256, 0, 0);  // M = weight rows, N = tokens (K-major in shared memory)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);  // TMA landed (A + raw W)
-  uint64_t* empty = full + STAGES;                                   // 1 MMA commit + 4 dequantiser-warp arrivals
-  uint64_t* b_full = empty + STAGES;                                 // 4 dequantiser-warp arrivals
-  uint64_t* b_empty = b_full + BSTAGES;                              // 1 MMA commit
-  uint64_t* acc_full = b_empty + BSTAGES;
-  uint64_t* acc_empty = acc_full + 2;
-  uint32_t* tmem_base_p = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* full_a = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);  // leader's: both halves of the activation tile landed
+  uint64_t* full_w = full_a + STAGES;                                  // this CTA's raw weight tile landed
+  uint64_t* mma_done = full_w + STAGES;                                // 1 MMA commit: the stage's MMAs have read their operands
+  uint64_t* raw_done = mma_done + STAGES;                              // 4 arrivals of this CTA's dequantiser warps: raw tile read
+  uint64_t* b_full = raw_done + STAGES;                                // leader's: 4 dequantiser-warp arrivals from each CTA
+  uint64_t* acc_full = b_full + STAGES;                                // 1 MMA commit
+  uint64_t* acc_empty = acc_full + 1;                                  // leader's: 4 epilogue-warp arrivals from each CTA
+  uint32_t* tmem_base_p = reinterpret_cast<uint32_t*>(acc_empty + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_p + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const WaitCtx wc{abort_flag, status};
+  const uint32_t rank = cluster_ctarank();
+  const int pair0 = static_cast<int>(blockIdx.x) >> 1, pair_step = static_cast<int>(gridDim.x) >> 1;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full[s], 1);
-      mbar_init(&empty[s], 5);  // the MMA commit + one arrival per warp of the dequantising group
+      mbar_init(&full_a[s], 1);
+      mbar_init(&full_w[s], 1);
+      mbar_init(&mma_done[s], 1);
+      mbar_init(&raw_done[s], 4);
+      mbar_init(&b_full[s], 8);
     }
-    for (int s = 0; s < BSTAGES; ++s) {
-      mbar_init(&b_full[s], 4);  // one arrival per warp of the dequantising group
-      mbar_init(&b_empty[s], 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 128);
-    }
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, 8);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmC);
   }
-  if (warp == 1) {
-    tmem_alloc(tmem_base_p, 512);
-    tmem_relinquish();
+  if (warp == 1) {  // the same warp in both CTAs allocates the pair's tensor memory
+    tmem_alloc_pair(tmem_base_p, 512);
+    tmem_relinquish_pair();
   }
   tc_fence_before();
   __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers are initialised before any remote arrival or peer-signalled copy
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_p;
   GemmShape shape;
@@ -89,67 +109,84 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = pair0; tile < num_tiles && ok; tile += pair_step) {
         int tm, tn;
         tile_coords(shape, tile, tm, tn);
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-          if (!mbar_wait(wc, &empty[s], ph ^ 1u, ST_TIMEOUT_EMPTY)) { ok = false; break; }
-          mbar_expect_tx(&full[s], L::STAGE_BYTES);
+          if (!mbar_wait(wc, &mma_done[s], ph ^ 1u, ST_TIMEOUT_EMPTY)) { ok = false; break; }
+          if (!mbar_wait(wc, &raw_done[s], ph ^ 1u, ST_TIMEOUT_EMPTY)) { ok = false; break; }
           uint8_t* sa = smem + s * L::STAGE_BYTES;
-          tma_load_2d(sa, &tmA, kb * 64, tm * 256, &full[s]);
-          tma_load_2d(sa + 128 * 128, &tmA, kb * 64, tm * 256 + 128, &full[s]);
-          tma_load_2d(sa + L::A_BYTES, &tmW, kb * 32, tn * 128, &full[s]);
+          if (rank == 0) mbar_expect_tx(&full_a[s], 2 * L::X_BYTES);  // the leader's barrier counts both CTAs' activation bytes
+          tma_load_2d_pair(sa, &tmA, kb * 64, tm * 256 + static_cast<int>(rank) * 128, map_to_cta(&full_a[s], 0));
+          mbar_expect_tx(&full_w[s], L::RAW_BYTES);
+          tma_load_2d(sa + L::X_BYTES, &tmW, kb * 32, tn * 256 + static_cast<int>(rank) * 128, &full_w[s]);
         }
       }
-      if (!ok) {
+      if (!ok) {  // bounded wait for this CTA's raw-weight copies that may still be in flight (activation copies complete on the
+                  // leader's barriers; the cluster barrier at the end keeps both CTAs resident meanwhile)
         const uint32_t first = it > STAGES ? it - STAGES : 0;
         for (uint32_t j = first; j < it; ++j)
-          for (int spin = 0; spin < 4096 && !mbar_try_wait(&full[j % STAGES], (j / STAGES) & 1u); ++spin) {}
+          for (int spin = 0; spin < 4096 && !mbar_try_wait(&full_w[j % STAGES], (j / STAGES) & 1u); ++spin) {}
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    if (lane == 0 && rank == 0) {
       uint32_t it = 0, tcount = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
-        const uint32_t ab = tcount & 1u, aph = (tcount >> 1) & 1u;
-        if (!mbar_wait(wc, &acc_empty[ab], aph ^ 1u, ST_TIMEOUT_TMEM)) { ok = false; break; }
+      for (int tile = pair0; tile < num_tiles && ok; tile += pair_step, ++tcount) {
+#ifdef SPINF_TRACE
+        long long w0 = clock64();
+#endif
+        if (!mbar_wait(wc, acc_empty, (tcount & 1u) ^ 1u, ST_TIMEOUT_TMEM)) { ok = false; break; }
+#ifdef SPINF_TRACE
+        long long w1 = clock64();
+        atomicAdd(&g_w4_trace[0], static_cast<unsigned long long>(w1 - w0));
+        const long long t_first = w1;
+#endif
         tc_fence_after();
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-          const uint32_t bs = it % BSTAGES, bph = (it / BSTAGES) & 1u;
-          if (!mbar_wait(wc, &full[s], ph, ST_TIMEOUT_FULL)) { ok = false; break; }
-          if (!mbar_wait(wc, &b_full[bs], bph, ST_TIMEOUT_OTHER)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
-          const uint64_t bdesc = make_smem_desc_sw128(smem_u32(smem + L::B_OFF + bs * L::B_BYTES), 16, 1024);
-#pragma unroll
-          for (int mh = 0; mh < 2; ++mh) {
-            const uint64_t adesc = make_smem_desc_sw128(sa + mh * 128 * 128, 16, 1024);
-            const uint32_t d_tmem = tmem_base + ab * 256 + mh * 128;
-#pragma unroll
-            for (int k = 0; k < 4; ++k) umma_f16_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, IDESC, (kb | k) != 0);
+#ifdef SPINF_TRACE
+          w0 = clock64();
+#endif
+          if (!mbar_wait(wc, &full_a[s], ph, ST_TIMEOUT_FULL)) { ok = false; break; }
+#ifdef SPINF_TRACE
+          w1 = clock64();
+#endif
+          if (!mbar_wait(wc, &b_full[s], ph, ST_TIMEOUT_OTHER)) { ok = false; break; }
+#ifdef SPINF_TRACE
+          {
+            const long long w2 = clock64();
+            atomicAdd(&g_w4_trace[1], static_cast<unsigned long long>(w1 - w0));
+            atomicAdd(&g_w4_trace[2], static_cast<unsigned long long>(w2 - w1));
+            atomicAdd(&g_w4_trace[3], 1ull);
+            if (kb == num_kb - 1) atomicAdd(&g_w4_trace[4], static_cast<unsigned long long>(w2 - t_first));
           }
-          umma_commit(&empty[s]);
-          umma_commit(&b_empty[bs]);
+#endif
+          tc_fence_after();
+          const uint64_t xdesc = make_smem_desc_sw128(smem_u32(smem + s * L::STAGE_BYTES), 16, 1024);
+          const uint32_t w_tmem = tmem_base + L::W_COL + s * 32;  // 16 bf16 of K = 8 packed columns per MMA
+#pragma unroll
+          for (int k = 0; k < 4; ++k) umma_f16_ts_pair(tmem_base + L::ACC_COL, w_tmem + 8 * k, xdesc + 2 * k, IDESC, (kb | k) != 0);
+          umma_commit_pair_both(&mma_done[s]);  // one commit per step: every commit is a bubble in the tensor pipe
         }
-        if (ok) umma_commit(&acc_full[ab]);
+        if (ok) umma_commit_pair_both(acc_full);
       }
     }
   } else if (warp >= 6) {
     // dequantisers: two groups of 128 threads take alternate K steps; thread = weight row of the tile
-    const int dt = threadIdx.x - 192;   // 0..255
-    const int grp = dt >> 7;
-    const int n_local = dt & 127;
+    const int grp = (warp - 6) >> 2;
+    const int n_local = (warp & 3) * 32 + lane;  // a warp reaches the 32 TMEM lanes of its quarter (warp index mod 4)
     uint32_t it = 0;
     bool ok = true;
     const int groups = a.K / a.G;
     const bool coarse = a.G % 64 == 0;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    const uint32_t b_full_leader = map_to_cta(b_full, 0);
+    for (int tile = pair0; tile < num_tiles && ok; tile += pair_step) {
       int tm, tn;
       tile_coords(shape, tile, tm, tn);
-      const int n = tn * 128 + n_local;
+      const int n = tn * 256 + static_cast<int>(rank) * 128 + n_local;
       const bool n_ok = n < a.N;
       const __half* srow = a.scales + static_cast<int64_t>(n_ok ? n : 0) * groups;
       int s_idx = -1;
@@ -157,14 +194,13 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         if ((it & 1u) != static_cast<uint32_t>(grp)) continue;
         const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-        const uint32_t bs = it % BSTAGES, bph = (it / BSTAGES) & 1u;
-        bool got = mbar_wait(wc, &full[s], ph, ST_TIMEOUT_FULL);
-        got = got && mbar_wait(wc, &b_empty[bs], bph ^ 1u, ST_TIMEOUT_EMPTY);
+        bool got = mbar_wait(wc, &full_w[s], ph, ST_TIMEOUT_FULL);
+        got = got && mbar_wait(wc, &mma_done[s], ph ^ 1u, ST_TIMEOUT_EMPTY);  // the stage's previous expansion has been consumed
         if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
-        const uint4* raw = reinterpret_cast<const uint4*>(smem + s * L::STAGE_BYTES + L::A_BYTES + n_local * 32);
+        const uint4* raw = reinterpret_cast<const uint4*>(smem + s * L::STAGE_BYTES + L::X_BYTES + n_local * 32);
         const uint4 r0 = raw[0], r1 = raw[1];
         const uint32_t words[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
-        uint8_t* btile = smem + L::B_OFF + bs * L::B_BYTES;
+        uint32_t out[32];  // column j of the slot = K elements (2 j, 2 j + 1) of this row
         if (coarse) {  // one scale for the whole 64-wide K step (group a multiple of 64): one division per step
           const int gi = (kb * 64) / a.G;
           if (gi != s_idx) {
@@ -185,81 +221,91 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
           const uint32_t even = words[c] & 0x0F0F0F0Fu;         // nibbles 0, 2, 4, 6 (k even), one per byte
           const uint32_t odd = (words[c] >> 4) & 0x0F0F0F0Fu;   // nibbles 1, 3, 5, 7
-          uint32_t out[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             // bytes [0, 0, nibble, 0x43] = the float 128 + nibble; fma(128 + n, s, -136 s) = (n - 8) s with no rounding
             // (the product and the sum are exact inside the FMA and the result fits fp32); then one rounding to bf16
             const float lo = fmaf(__uint_as_float(__byte_perm(even, 0x43000000u, 0x7044u | (j << 8))), sc, off);
             const float hi = fmaf(__uint_as_float(__byte_perm(odd, 0x43000000u, 0x7044u | (j << 8))), sc, off);
-            out[j] = pack_bf16x2(lo, hi);
+            out[4 * c + j] = pack_bf16x2(lo, hi);
           }
-          *reinterpret_cast<uint4*>(btile + sw128_offset(n_local, c)) = make_uint4(out[0], out[1], out[2], out[3]);
         }
-        fence_proxy_async_smem();
-        __syncwarp();  // every lane's chunk is written and fenced: one arrival per warp instead of 32
+        tc_fence_after();  // orders the store after the commit that freed the slot
+        tmem_st_x32(tmem_base + L::W_COL + s * 32 + (static_cast<uint32_t>((warp & 3) * 32) << 16), out);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();  // every lane's row is in tensor memory: one arrival per warp instead of 32
         if (lane == 0) {
-          mbar_arrive(&b_full[bs]);
-          mbar_arrive(&empty[s]);  // the raw tile has been read
+          mbar_arrive_cluster(b_full_leader + s * 8);  // the leader's barrier: the pair's MMA reads both CTAs' slots
+          mbar_arrive(&raw_done[s]);                   // the raw tile has been read
         }
       }
     }
   } else {
-    // epilogue: warps 2-5, thread = accumulator row of each 128-row half
+    // epilogue: warps 2-5, thread = TMEM lane = output channel of this CTA's 128; columns = the tile's 256 tokens
     const int et = threadIdx.x - 64;
+    const uint32_t acc_empty_leader = map_to_cta(acc_empty, 0);
     const int q = warp & 3;
-    const int row = q * 32 + lane;
-    uint8_t* epi_stage = smem + L::EPI_OFF;
-    uint32_t tcount = 0, nstores = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
+    const int ch = q * 32 + lane;            // output channel within this CTA's 128
+    const int hb = ch >> 6;                  // which 64-channel box of the staging buffer
+    const int ch2 = (ch & 63) & ~1;          // the even channel of this lane pair, within the box
+    const uint32_t odd = lane & 1u;
+    uint32_t tcount = 0, nchunks = 0;
+    for (int tile = pair0; tile < num_tiles; tile += pair_step, ++tcount) {
       int tm, tn;
       tile_coords(shape, tile, tm, tn);
-      const uint32_t ab = tcount & 1u, aph = (tcount >> 1) & 1u;
-      const bool got = mbar_wait(wc, &acc_full[ab], aph, ST_TIMEOUT_TMEM);
+      const bool got = mbar_wait(wc, acc_full, tcount & 1u, ST_TIMEOUT_TMEM);
       if (!bar_red_and(1, 128, got)) break;
       tc_fence_after();
 #pragma unroll 1
-      for (int part = 0; part < 4; ++part) {  // (row half, 64-column chunk)
-        const int mh = part >> 1, c = part & 1;
+      for (int c = 0; c < 4; ++c, ++nchunks) {  // 64-token chunks
         uint32_t v0[32], v1[32];
         __syncwarp();
-        const uint32_t taddr = tmem_base + ab * 256 + mh * 128 + c * 64 + (static_cast<uint32_t>(q * 32) << 16);
+        const uint32_t taddr = tmem_base + L::ACC_COL + c * 64 + (static_cast<uint32_t>(q * 32) << 16);
         tmem_ld_x32(taddr, v0);
         tmem_ld_x32(taddr + 32, v1);
         tmem_wait_ld();
-        if (part == 3) {
+        if (c == 3) {  // the accumulator is in registers: one arrival per warp on the leader's barrier
           tc_fence_before();
-          mbar_arrive(&acc_empty[ab]);
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
         }
+        // transpose through the lane pair: the even lane keeps token 2 i of both channels, the odd lane token 2 i + 1
         uint32_t packed[32];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          packed[i] = pack_bf16x2(__uint_as_float(v0[2 * i]), __uint_as_float(v0[2 * i + 1]));
-          packed[16 + i] = pack_bf16x2(__uint_as_float(v1[2 * i]), __uint_as_float(v1[2 * i + 1]));
+        for (int i = 0; i < 32; ++i) {
+          const uint32_t e = i < 16 ? v0[2 * i] : v1[2 * i - 32], o = i < 16 ? v0[2 * i + 1] : v1[2 * i - 31];
+          const uint32_t other = __shfl_xor_sync(0xffffffffu, odd ? e : o, 1);
+          packed[i] = odd ? pack_bf16x2(__uint_as_float(other), __uint_as_float(o)) : pack_bf16x2(__uint_as_float(e), __uint_as_float(other));
         }
-        uint8_t* buf = epi_stage;
-        if (et == 0) tma_store_wait_read<0>();
+        uint8_t* buf = smem + L::EPI_OFF + (nchunks & 1u) * L::EPI_BYTES;
+        if (et == 0) tma_store_wait_read<1>();  // the store that last read this buffer (two chunks ago) has finished reading
         named_bar_sync(1, 128);
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          *reinterpret_cast<uint4*>(buf + sw128_offset(row, j)) = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+        for (int i = 0; i < 32; ++i) {
+          const uint32_t tok = 2 * i + odd;
+          *reinterpret_cast<uint32_t*>(buf + hb * 8192 + sw128_offset(tok, ch2 >> 3) + (ch2 & 7) * 2) = packed[i];
+        }
         fence_proxy_async_smem();
         named_bar_sync(1, 128);
         if (et == 0) {
-          tma_store_2d(&tmC, buf, tn * 128 + c * 64, tm * 256 + mh * 128);
+          const int n0 = tn * 256 + static_cast<int>(rank) * 128, m0 = tm * 256 + c * 64;
+          if (m0 < a.M && n0 < a.N) tma_store_2d(&tmC, buf, n0, m0);  // boxes that lie wholly outside the output are skipped,
+          if (m0 < a.M && n0 + 64 < a.N) tma_store_2d(&tmC, buf + 8192, n0 + 64, m0);  // partial ones are clipped by the copy
           tma_store_commit();
         }
-        ++nstores;
       }
     }
     if (et == 0) tma_store_wait_all<0>();
   }
 
+  tc_fence_before();
   __syncthreads();
+  cluster_sync_all();  // neither CTA leaves while its peer may still signal its barriers or read its shared memory
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    tmem_dealloc_pair(tmem_base, 512);
   }
 }
 
@@ -281,12 +327,12 @@ extern "C" int spinf_w4_gemm(const void* x, const void* qw, const void* scales, 
   int r;
   if ((r = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, M, K, K * 2, 64, 128))) return r;
   if ((r = make_tmap_2d_plain(&tmW, qw, N, K / 2, K / 2, 32, 128))) return r;
-  if ((r = make_tmap_2d(&tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y, M, N, y_pitch * 2, 64, 128))) return r;
+  if ((r = make_tmap_2d(&tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y, M, N, y_pitch * 2, 64, 64))) return r;
   W4Args a;
   a.scales = static_cast<const __half*>(scales);
   a.M = static_cast<int>(M), a.N = static_cast<int>(N), a.K = static_cast<int>(K), a.G = group;
   a.tiles_m = static_cast<int>((M + 255) / 256);
-  a.tiles_n = static_cast<int>((N + 127) / 128);
+  a.tiles_n = static_cast<int>((N + 255) / 256);
   // groups of row tiles as tall as about 32 MB of bf16 activations allow (4..32 tiles of 256 rows): the packed weight streams past
   // once per group
   {
@@ -300,8 +346,30 @@ extern "C" int spinf_w4_gemm(const void* x, const void* qw, const void* scales, 
     attr_set[dev] = true;
   }
   const int tiles = a.tiles_m * a.tiles_n;
-  const int grid = tiles < sm_count() ? tiles : sm_count();
-  w4_gemm_kernel<<<grid, 448, W4Smem::TOTAL, static_cast<cudaStream_t>(stream)>>>(tmA, tmW, tmC, a, status);
+  const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+  cfg.blockDim = dim3(448);
+  cfg.dynamicSmemBytes = W4Smem::TOTAL;
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  SPINF_CUDA_OK(cudaLaunchKernelEx(&cfg, w4_gemm_kernel, tmA, tmW, tmC, a, status));
   SPINF_CUDA_OK(cudaGetLastError());
   return 0;
 }
+
+#ifdef SPINF_TRACE
+extern "C" int spinf_w4_trace_read(unsigned long long* out) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out, spinf::g_w4_trace, sizeof(unsigned long long) * 8);
+  unsigned long long z[8] = {0};
+  cudaMemcpyToSymbol(spinf::g_w4_trace, z, sizeof(z));
+  return 0;
+}
+#endif

@@ -19,7 +19,8 @@ def _gptq(N, K, G, seed):
     return qweight, scales
 
 
-@pytest.mark.parametrize("M,N,K,G,E", [(256, 128, 64, 32, 0), (1, 256, 128, 128, 0), (300, 384, 512, 128, 64), (700, 5120, 4096, 128, 0), (130, 1024, 5120, 32, 64)])
+@pytest.mark.parametrize("M,N,K,G,E", [(256, 128, 64, 32, 0), (1, 256, 128, 128, 0), (300, 384, 512, 128, 64), (700, 5120, 4096, 128, 0), (130, 1024, 5120, 32, 64),
+                                       (77, 200, 192, 64, 0), (513, 72, 128, 128, 0)])
 def test_w4_linear_vs_oracle(dev, M, N, K, G, E):
     from spinf_serve_b200.linears import Int4Linear
 
