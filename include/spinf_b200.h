@@ -58,6 +58,27 @@ int spinf_fp8_rowwise_quant(const void* x_bf16, int64_t M, int64_t K, void* x8, 
 int spinf_fp8_rowwise_gemm(const void* x8, const float* xs, const void* w8, const float* ws, void* y_bf16, int64_t M, int64_t N,
                            int64_t K, void* stream);
 
+/* ------------------------------------------------------------------------------------------------------------ fp8 per-tensor linears
+ * The reference's Fp8Linear (dynamic) and Fp8StaticLinear (calibrated static activation scale, "fp8s"), both with one weight scale
+ * per tensor (spinf_serve/quant/linears.py:66-119).
+ *
+ * spinf_abs_max: *out = max |x| over n bf16 elements (n a multiple of 8): the reduction of quant_act (linears.py:22-26). */
+int spinf_abs_max(const void* x_bf16, int64_t n, float* out, void* stream);
+
+/* x8[i] = e4m3_rne(clamp(float(x[i]) / s, -448, 448)) over n elements (a multiple of 8) with one scale read from device memory:
+ *   from_amax = 0: s = *scale            (Fp8StaticLinear.forward, linears.py:113, scale = the module's `xs` buffer)
+ *   from_amax = 1: s = max(*scale, 1e-12) / 448, *scale holding the tensor's max |x|      (quant_act, linears.py:22-26)
+ * scale_out (may be NULL) receives s. peak (may be NULL): *peak = max(*peak, max|x| / (s * 448)), the clipping monitor of
+ * Fp8StaticLinear (linears.py:111-112). */
+int spinf_fp8_tensor_quant(const void* x_bf16, int64_t n, const float* scale, int32_t from_amax, void* x8, float* scale_out,
+                           float* peak, void* stream);
+
+/* Replaces the per-tensor torch._scaled_mm of Fp8Linear / Fp8StaticLinear (linears.py:77,114):
+ *   y[m,n] = bf16( (sum_k x8[m,k] * w8[n,k])_fp32 * *xs * *ws ),   xs, ws: one fp32 each, in device memory.
+ * Layouts and size rules as spinf_fp8_rowwise_gemm; the same kernel, so a row of y does not depend on M. */
+int spinf_fp8_tensor_gemm(const void* x8, const float* xs, const void* w8, const float* ws, void* y_bf16, int64_t M, int64_t N,
+                          int64_t K, void* stream);
+
 /* The gate|up projection of a gated MLP with the activation fused into the GEMM epilogue (the reference runs
  * act(gate_proj(x)) * up_proj(x) as two Fp8RowLinear calls and an inductor-fused pointwise kernel: transformers' Gemma4TextMLP,
  * called through spinf_serve/models/gemma4.py:407-415; Qwen's MLP spinf_serve/models/qwen35/qwen.py:706-716):

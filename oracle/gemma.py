@@ -93,22 +93,43 @@ def apply_rope(x, cos, sin):
     return (x * cos[:, None, :]) + (rot * sin[:, None, :])
 
 
-def quantize(W):
-    """per-linear (w8 [out, in] e4m3, ws [1, out] fp32) with the q|k|v and gate|up projections kept separate, as the reference's
-    module swap leaves them (spinf_serve/quant/linears.py:85-91)"""
-    return [{k: OL.quantize_weight_rowwise(L[k]) for k in ("q", "k", "v", "o", "gate", "up", "down")} for L in W["layers"]]
+LINEARS = ("q", "k", "v", "o", "gate", "up", "down")
 
 
-def forward(cfg: GemmaConfig, W, Q, ids, art, end, pos, n_layers=None, taps=None):
+def quantize(W, scheme="fp8row"):
+    """per-linear (w8 [out, in] e4m3, ws fp32: [1, out] for fp8row, one scalar for the per-tensor schemes fp8 / fp8s) with the
+    q|k|v and gate|up projections kept separate, as the reference's module swap leaves them (spinf_serve/quant/linears.py:66-106)"""
+    fn = OL.quantize_weight_rowwise if scheme == "fp8row" else OL.quantize_weight
+    return [{k: fn(L[k]) for k in LINEARS} for L in W["layers"]]
+
+
+def forward(cfg: GemmaConfig, W, Q, ids, art, end, pos, n_layers=None, taps=None, scheme="fp8row", scales=None, amax=None, peaks=None):
     """packed forward -> final hidden states [n, hidden] bf16 (after the model's last norm), the oracle of Gemma4Stack.forward
-    (spinf_serve/models/gemma4.py:407-415). taps: optional dict filled with intermediate tensors for operator-level checks."""
+    (spinf_serve/models/gemma4.py:407-415). taps: optional dict filled with intermediate tensors for operator-level checks.
+    scheme: fp8row (Fp8RowLinear), fp8 (Fp8Linear: dynamic per-tensor) or fp8s (Fp8StaticLinear with scales[i][name]).
+    amax: optional list of per-layer dicts updated with the largest |input| of every linear (what the reference's calibration
+    hooks record, quant/calibrate.py:117-124); peaks: the same for the static scheme's monitor (max|x| / (448 scale))."""
     n = len(ids)
     H, K, D = cfg.heads, cfg.kv_heads, cfg.head_dim
-    lin = lambda x, key, q: OL.fp8_row_linear(x, *q[key])  # noqa: E731
+    layer = [0]
+
+    def lin(x, key, q):
+        if amax is not None:
+            amax[layer[0]][key] = max(amax[layer[0]][key], float(x.float().abs().max()))
+        if scheme == "fp8row":
+            return OL.fp8_row_linear(x, *q[key])
+        if scheme == "fp8":
+            return OL.fp8_linear(x, *q[key])
+        y, pk = OL.fp8_static_linear(x, *q[key], torch.tensor(scales[layer[0]][key], dtype=torch.float32))
+        if peaks is not None:
+            peaks[(layer[0], key)] = max(peaks.get((layer[0], key), 0.0), float(pk))
+        return y
+
     h = W["embed"][torch.as_tensor(np.asarray(ids), dtype=torch.int64)] * torch.tensor(cfg.hidden**0.5).to(torch.bfloat16)
     tables = {"sliding_attention": rope_tables(pos, D, cfg.theta_sliding), "full_attention": rope_tables(pos, D, cfg.theta_full)}
     for i in range(cfg.layers if n_layers is None else n_layers):
         L, q8 = W["layers"][i], Q[i]
+        layer[0] = i
         kind = cfg.layer_types[i]
         cos, sin = tables[kind]
         x = rmsnorm(h, L["input_ln"], cfg.eps)
@@ -127,6 +148,17 @@ def forward(cfg: GemmaConfig, W, Q, ids, art, end, pos, n_layers=None, taps=None
         if taps is not None:
             taps[i] = {"q": q, "k": k, "v": v, "attn": a, "h": h.clone()}
     return rmsnorm(h, W["norm"], cfg.eps)
+
+
+def calibrate(cfg: GemmaConfig, W, batches, headroom=2.0, n_layers=None):
+    """the fp8s scale table: the dynamic scheme run over `batches`, the largest input of every linear, and the power-of-two rule
+    (spinf_serve/quant/calibrate.py:100-178 without the service around it) -> {"amax": [...], "scales": [...]} per layer"""
+    nl = cfg.layers if n_layers is None else n_layers
+    Q = quantize(W, "fp8")
+    amax = [dict.fromkeys(LINEARS, 0.0) for _ in range(nl)]
+    for b in batches:
+        forward(cfg, W, Q, b.ids, b.art, b.end, b.pos, n_layers, scheme="fp8", amax=amax)
+    return {"amax": amax, "scales": [{k: OL.static_scale(v, headroom) for k, v in a.items()} for a in amax]}
 
 
 def score(cfg: GemmaConfig, W, Q, batch, cols, n_layers=None):

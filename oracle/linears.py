@@ -69,3 +69,51 @@ def int4_linear(x, q, s, group, extra=None, exact=False):
     if exact:
         return x.double() @ w.double().t()
     return (x.float() @ w.float().t()).to(torch.bfloat16)
+
+
+# ------------------------------------------------------------------------------------------------ per-tensor fp8 (dynamic and static)
+def quantize_weight(w):
+    """bf16 [out, in] -> (w8 [out, in] e4m3, fp32 scale []): Fp8Linear / Fp8StaticLinear.__init__, linears.py:69-71,104-106
+    (quant/fp8.py:14-21)"""
+    wf = w.float()
+    s = wf.abs().amax().clamp(min=1e-12) / FP8_MAX
+    return (wf / s).clamp_(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn), s.reshape(())
+
+
+def quant_act(x):
+    """[..., K] -> (x8 [M, K] e4m3, fp32 scale []), one scale from the tensor's maximum: linears.py:22-26"""
+    xf = x.reshape(-1, x.shape[-1]).float()
+    s = xf.abs().amax().clamp_(min=1e-12) / FP8_MAX
+    return (xf / s).clamp_(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn), s
+
+
+def quant_act_static(x, xs):
+    """[..., K] -> x8 [M, K] e4m3 with the fixed scale xs: Fp8StaticLinear.forward, linears.py:110,113"""
+    return (x.reshape(-1, x.shape[-1]).float() / xs).clamp_(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+
+
+def scaled_mm_tensor(x8, xs, w8, ws, exact=False):
+    """bf16((x8 @ w8^T) * xs * ws) with scalar scales: the per-tensor torch._scaled_mm of linears.py:77,114, restated as the fp32
+    matmul of the e4m3 values (exact=True: float64, unrounded)"""
+    if exact:
+        return (x8.double() @ w8.double().t()) * float(xs) * float(ws)
+    return ((x8.float() @ w8.float().t()) * xs * ws).to(torch.bfloat16)
+
+
+def fp8_linear(x, w8, ws):
+    """Fp8Linear.forward, linears.py:75-78"""
+    x8, xs = quant_act(x)
+    return scaled_mm_tensor(x8, xs, w8, ws).reshape(*x.shape[:-1], w8.shape[0])
+
+
+def fp8_static_linear(x, w8, ws, xs):
+    """Fp8StaticLinear.forward, linears.py:108-115 (without the monitor) -> (y, peak contribution max|x| / (xs * 448))"""
+    y = scaled_mm_tensor(quant_act_static(x, xs), xs, w8, ws).reshape(*x.shape[:-1], w8.shape[0])
+    return y, x.float().abs().amax() / (xs * FP8_MAX)
+
+
+def static_scale(amax, headroom=2.0):
+    """2^ceil(log2(headroom * amax / 448)): quant/calibrate.py:176-177"""
+    import math
+
+    return 2.0 ** math.ceil(math.log2(max(amax, 1e-6) * headroom / FP8_MAX))

@@ -403,6 +403,74 @@ __global__ void __launch_bounds__(256) fp8_rowwise_quant_kernel(const __nv_bfloa
   }
 }
 
+// ------------------------------------------------------------------------------------------------ per-tensor fp8 quantiser
+// max |x| over a whole tensor (bf16, n a multiple of 8): the reduction of the dynamic per-tensor scheme. Non-negative floats order
+// like their bit patterns, so the grid's maxima meet in one integer atomic; *out is zeroed by the caller.
+__global__ void __launch_bounds__(256) abs_max_kernel(const __nv_bfloat16* __restrict__ x, int64_t nvec, float* __restrict__ out) {
+  const uint4* src = reinterpret_cast<const uint4*>(x);
+  __shared__ float red[8];
+  float amax = 0.f;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nvec; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const uint4 u = src[i];
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(p[j]);
+      amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
+  }
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int w = 1; w < 8; ++w) amax = fmaxf(amax, red[w]);
+    atomicMax(reinterpret_cast<unsigned int*>(out), __float_as_uint(amax));
+  }
+}
+
+// x8 = e4m3(clamp(x / s)) with one scale for the tensor, read from device memory: s = *scale (the static scheme), or
+// s = max(*scale, 1e-12) / 448 with *scale the tensor's max |x| (the dynamic scheme). scale_out (optional) receives s.
+// peak (optional): *peak = max(*peak, max|x| / (s * 448)), the clipping monitor of the static scheme.
+__global__ void __launch_bounds__(256) fp8_tensor_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t nvec,
+                                                               const float* __restrict__ scale, int from_amax,
+                                                               uint8_t* __restrict__ x8, float* __restrict__ scale_out,
+                                                               float* __restrict__ peak) {
+  const float s = from_amax ? __fdiv_rn(fmaxf(*scale, 1e-12f), 448.f) : *scale;
+  if (scale_out && blockIdx.x == 0 && threadIdx.x == 0) *scale_out = s;
+  const DivBy div = make_div_by(s);
+  const uint4* src = reinterpret_cast<const uint4*>(x);
+  uint2* dst = reinterpret_cast<uint2*>(x8);
+  float amax = 0.f;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nvec; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const uint4 u = src[i];
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+    uint32_t o[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const float2 a = __bfloat1622float2(p[2 * j]), b = __bfloat1622float2(p[2 * j + 1]);
+      amax = fmaxf(amax, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y))));
+      // a true division, as the reference computes it; the conversion saturates at +-448 (the reference's clamp)
+      const float q0 = div_by(div, a.x), q1 = div_by(div, a.y), q2 = div_by(div, b.x), q3 = div_by(div, b.y);
+      const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(q0, q1), __NV_SATFINITE, __NV_E4M3);
+      const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(q2, q3), __NV_SATFINITE, __NV_E4M3);
+      o[j] = lo | (hi << 16);
+    }
+    dst[i] = make_uint2(o[0], o[1]);
+  }
+  if (peak) {
+    __shared__ float red[8];
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+#pragma unroll
+      for (int w = 1; w < 8; ++w) amax = fmaxf(amax, red[w]);
+      atomicMax(reinterpret_cast<unsigned int*>(peak), __float_as_uint(__fdiv_rn(amax, s * 448.f)));
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ launch helpers
 template <int KIND, int BN, class Epi>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmShape& shape, const Epi& epi, cudaStream_t stream) {
@@ -467,6 +535,49 @@ extern "C" int spinf_fp8_rowwise_gemm(const void* x8, const float* xs, const voi
   if ((r = make_tmap_2d(&epi.tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y_bf16, M, N, N * 2, 64, 128))) return r;
   epi.rowscale = xs;
   epi.colscale_g = ws;
+  return launch_gemm<KIND_F8, BN>(tmA, tmB, make_shape(M, N, K, BN), epi, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int spinf_abs_max(const void* x_bf16, int64_t n, float* out, void* stream) {
+  SPINF_CHECK_ARG(x_bf16 && out && n >= 0 && n % 8 == 0);
+  SPINF_CUDA_OK(cudaMemsetAsync(out, 0, sizeof(float), static_cast<cudaStream_t>(stream)));
+  if (n == 0) return 0;
+  const int64_t nvec = n / 8, blocks = (nvec + 255) / 256;
+  const int64_t cap = 8ll * sm_count();
+  abs_max_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x_bf16), nvec, out);
+  SPINF_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int spinf_fp8_tensor_quant(const void* x_bf16, int64_t n, const float* scale, int32_t from_amax, void* x8, float* scale_out,
+                                      float* peak, void* stream) {
+  SPINF_CHECK_ARG(x_bf16 && scale && x8 && n >= 0 && n % 8 == 0 && (from_amax == 0 || from_amax == 1));
+  if (n == 0) return 0;
+  const int64_t nvec = n / 8, blocks = (nvec + 255) / 256;
+  const int64_t cap = 8ll * sm_count();
+  fp8_tensor_quant_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x_bf16), nvec, scale, from_amax, static_cast<uint8_t*>(x8), scale_out, peak);
+  SPINF_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int spinf_fp8_tensor_gemm(const void* x8, const float* xs, const void* w8, const float* ws, void* y_bf16, int64_t M,
+                                     int64_t N, int64_t K, void* stream) {
+  SPINF_CHECK_ARG(x8 && xs && w8 && ws && y_bf16 && M >= 0 && N > 0 && K > 0 && K % 16 == 0 && N % 16 == 0);
+  SPINF_CHECK_ARG(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31));
+  if (M == 0) return 0;
+  constexpr int BN = 256;
+  CUtensorMap tmA, tmB;
+  EpiStoreBf16<BN, true> epi;
+  int r;
+  if ((r = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x8, M, K, K, 128, 128))) return r;
+  if ((r = make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w8, N, K, K, 128, BN))) return r;
+  if ((r = make_tmap_2d(&epi.tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y_bf16, M, N, N * 2, 64, 128))) return r;
+  epi.rowscale = xs;
+  epi.colscale_g = ws;
+  epi.rowscale_stride = 0;
+  epi.colscale_stride = 0;
   return launch_gemm<KIND_F8, BN>(tmA, tmB, make_shape(M, N, K, BN), epi, static_cast<cudaStream_t>(stream));
 }
 

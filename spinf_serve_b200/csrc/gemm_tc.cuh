@@ -239,6 +239,7 @@ struct EpiStoreBf16 {
   CUtensorMap tmC;  // [M, N] bf16, box 64 x 128, 128-byte swizzle
   const float* rowscale;
   const float* colscale_g;
+  int rowscale_stride = 1, colscale_stride = 1;  // 0: one scale for every row / column (the per-tensor fp8 linears)
   struct State {
     uint32_t nstores;
   };
@@ -248,7 +249,7 @@ struct EpiStoreBf16 {
       named_bar_sync(2, 128);  // the previous tile's readers of colscale are done
       for (int i = et; i < BN; i += 128) {
         const int n = tn * BN + i;
-        colscale[i] = n < s.N ? colscale_g[n] : 0.f;
+        colscale[i] = n < s.N ? colscale_g[static_cast<size_t>(n) * colscale_stride] : 0.f;
       }
       named_bar_sync(2, 128);
     }
@@ -259,7 +260,7 @@ struct EpiStoreBf16 {
     float rs = 1.f;
     if (SCALED) {
       const int m = tm * 128 + row;
-      rs = m < s.M ? rowscale[m] : 0.f;
+      rs = m < s.M ? rowscale[static_cast<size_t>(m) * rowscale_stride] : 0.f;
     }
     uint32_t packed[32];
 #pragma unroll

@@ -16,7 +16,10 @@ from dataclasses import dataclass, field
 import torch
 
 from spinf_serve_b200 import attention, ops
-from spinf_serve_b200.linears import quantize_weight_rowwise
+from spinf_serve_b200.linears import MONITOR, quantize_weight, quantize_weight_rowwise, static_scale
+
+LINEARS = ("q", "k", "v", "o", "gate", "up", "down")  # the quantized linears of a layer
+SCHEMES = ("fp8row", "fp8", "fp8s")  # the reference's EngineConfig.quant values that run here (spinf_serve/models/gemma4.py:170-215)
 
 
 @dataclass
@@ -60,44 +63,65 @@ CONFIGS = {
 class GemmaWeights:
     """device-resident weights: per layer the fused fp8 projections with their per-channel scales and the bf16 norm weights"""
 
-    def __init__(self, cfg: GemmaConfig, embed, norm, layers):
-        self.cfg, self.embed, self.norm, self.layers = cfg, embed, norm, layers
+    def __init__(self, cfg: GemmaConfig, embed, norm, layers, scheme="fp8row"):
+        if scheme not in SCHEMES:
+            raise RuntimeError(f"quant scheme {scheme} is outside the packed scoring path of this build (one of {SCHEMES})")
+        self.cfg, self.embed, self.norm, self.layers, self.scheme = cfg, embed, norm, layers, scheme
 
     @staticmethod
-    def _layer(L, pre=None):
+    def _layer(L, pre=None, scheme="fp8row", xs=None):
+        """one layer's device tensors. fp8row: per-channel weight scales, gate|up in the tiled order of the fused GeGLU GEMM.
+        fp8 / fp8s (per-tensor weight scales): the same fused [out, in] storage with each linear's scalar spread over its output
+        channels, gate|up in natural order; fp8s adds the calibrated activation scale and the clipping monitor of every linear
+        input (`xs`: {linear name: scale})."""
+        quant = quantize_weight_rowwise if scheme == "fp8row" else quantize_weight
+
         def q8(*names):
-            parts = [pre[k] if pre is not None else quantize_weight_rowwise(L[k]) for k in names]
-            return torch.cat([p[0] for p in parts]).contiguous(), torch.cat([p[1] for p in parts], dim=1).reshape(-1).contiguous()
+            parts = [pre[k] if pre is not None else quant(L[k]) for k in names]
+            w = torch.cat([p[0] for p in parts]).contiguous()
+            sc = torch.cat([p[1].float().reshape(-1).expand(p[0].shape[0]) if p[1].numel() == 1 else p[1].reshape(-1) for p in parts])
+            return w, sc.contiguous()
 
         out = {}
         out["qkv_w"], out["qkv_s"] = q8("q", "k", "v")
         out["o_w"], out["o_s"] = q8("o")
         gu_w, gu_s = q8("gate", "up")
-        order = ops.glu_tile_order(gu_w.shape[0] // 2).to(gu_w.device)  # the fused GEMM + GeGLU epilogue reads this row order
-        out["gu_w"] = gu_w.view(torch.uint8)[order].view(torch.float8_e4m3fn).contiguous()
-        out["gu_s"] = gu_s[order].contiguous()
+        if scheme == "fp8row":
+            order = ops.glu_tile_order(gu_w.shape[0] // 2).to(gu_w.device)  # the fused GEMM + GeGLU epilogue reads this row order
+            gu_w, gu_s = gu_w.view(torch.uint8)[order].view(torch.float8_e4m3fn).contiguous(), gu_s[order].contiguous()
+        out["gu_w"], out["gu_s"] = gu_w, gu_s
         out["down_w"], out["down_s"] = q8("down")
         for k in ("q_norm", "k_norm", "input_ln", "post_attn_ln", "pre_ffn_ln", "post_ffn_ln"):
             out[k] = L[k].contiguous()
+        if scheme == "fp8s":
+            dev = gu_w.device
+            out["xs"] = {k: torch.tensor(float(xs[k]), dtype=torch.float32, device=dev) for k in LINEARS}
+            out["peak"] = {k: torch.zeros((), dtype=torch.float32, device=dev) for k in LINEARS}
         return out
 
     @classmethod
-    def from_bf16(cls, cfg: GemmaConfig, W, device):
+    def from_bf16(cls, cfg: GemmaConfig, W, device, scheme="fp8row", scales=None):
         """W: {"embed", "norm", "layers": [{q,k,v,o,gate,up,down, q_norm,k_norm, input_ln,post_attn_ln,pre_ffn_ln,post_ffn_ln}]} of
-        bf16 tensors (any device); quantisation runs on `device`, one layer at a time"""
-        layers = [cls._layer({k: v.to(device) for k, v in L.items()}) for L in W["layers"]]
-        return cls(cfg, W["embed"].to(device).contiguous(), W["norm"].to(device).contiguous(), layers)
+        bf16 tensors (any device); quantisation runs on `device`, one layer at a time. scheme fp8s: scales[i][name] = the
+        calibrated activation scale of layer i's linear `name` (the table calibrate() returns)"""
+        layers = [
+            cls._layer({k: v.to(device) for k, v in L.items()}, None, scheme, scales[i] if scales is not None else None)
+            for i, L in enumerate(W["layers"])
+        ]
+        return cls(cfg, W["embed"].to(device).contiguous(), W["norm"].to(device).contiguous(), layers, scheme)
 
     @classmethod
-    def from_quantized(cls, cfg: GemmaConfig, W, Q, device):
-        """as from_bf16 with the linears already quantized: Q[i][name] = (w8 [out, in] e4m3, ws [1, out] fp32), the tensors a
-        row-wise fp8 checkpoint would hold (the reference's `prequantized` path, spinf_serve/quant/linears.py:121-131)"""
+    def from_quantized(cls, cfg: GemmaConfig, W, Q, device, scheme="fp8row", scales=None):
+        """as from_bf16 with the linears already quantized: Q[i][name] = (w8 [out, in] e4m3, ws fp32: [1, out] row-wise, one
+        element per-tensor), the tensors an fp8 checkpoint would hold (the reference's `prequantized` path,
+        spinf_serve/quant/linears.py:121-131); scales as in from_bf16 (an fp8-static checkpoint's input_scale tensors)"""
         names = ("q_norm", "k_norm", "input_ln", "post_attn_ln", "pre_ffn_ln", "post_ffn_ln")
         layers = [
-            cls._layer({k: L[k].to(device) for k in names}, {k: (a.to(device), b.to(device)) for k, (a, b) in q.items()})
-            for L, q in zip(W["layers"], Q)
+            cls._layer({k: L[k].to(device) for k in names}, {k: (a.to(device), b.to(device)) for k, (a, b) in q.items()}, scheme,
+                       scales[i] if scales is not None else None)
+            for i, (L, q) in enumerate(zip(W["layers"], Q))
         ]
-        return cls(cfg, W["embed"].to(device).contiguous(), W["norm"].to(device).contiguous(), layers)
+        return cls(cfg, W["embed"].to(device).contiguous(), W["norm"].to(device).contiguous(), layers, scheme)
 
     @classmethod
     def random(cls, cfg: GemmaConfig, seed: int, device):
@@ -147,6 +171,7 @@ class GemmaStack:
         }
         self.embed_scale = float(torch.tensor(self.cfg.hidden**0.5).to(torch.bfloat16))
         self.fuse_qkv = D in (128, 256) and ((self.cfg.heads + 2 * self.cfg.kv_heads) * D) % 256 == 0
+        self.amax_log = None  # calibrate() sets a list here: (linear name, device scalar) per quantised input of a forward
 
     def plan(self, b) -> None:
         """nothing to prepare on the host for attention-only models (base.py:50-51)"""
@@ -158,6 +183,35 @@ class GemmaStack:
         masks = attention.stream_masks(b.art, b.end, b.pos, self.cfg.window, device, always_window=True)
         return {"ids": ids, "pos": masks["full_attention"].pos, "masks": masks}
 
+    # ---- per-tensor schemes (fp8: the activation scale from the forward's own maximum; fp8s: a calibrated fixed scale). The
+    # GEMMs are the row-wise kernels with every row given the tensor's one scale, so their fused epilogues stay; the reference
+    # computes bf16(acc * xs * ws) with scalar scales (spinf_serve/quant/linears.py:77,114), the same product.
+    def _quant_in(self, x, L, names):
+        """x [n, K] bf16, the input of the linears `names` -> (x8, xs [n]). fp8s: the linears that share an input share its
+        quantisation when their calibrated scales agree (they do when calibrate() made the table: one input, one maximum)."""
+        n = x.shape[0]
+        if self.w.scheme == "fp8":
+            x8, s, amax = ops.fp8_tensor_quant(x, want_amax=True)
+            if self.amax_log is not None:  # calibration: the largest input of each linear (quant/calibrate.py:117-124)
+                for k in names:
+                    self.amax_log.append((k, amax))
+        else:
+            vals = {float(L["xs"][k]) for k in names} if len(names) > 1 and not L.get("xs_checked") else ()
+            if len(vals) > 1:
+                raise RuntimeError(f"fp8s: the linears {names} read one input but carry different activation scales {sorted(vals)}")
+            L["xs_checked"] = True
+            x8, s = ops.fp8_tensor_quant(x, L["xs"][names[0]], L["peak"][names[0]] if MONITOR["on"] else None)
+        return x8, s.reshape(1).expand(n).contiguous()
+
+    def peaks(self):
+        """fp8s: {(layer, linear name): largest |input| / (448 x scale) seen while linears.MONITOR["on"]} (above 1: clipped)"""
+        out = {}
+        for i, L in enumerate(self.w.layers[: self.n_layers]):
+            for group in (("q", "k", "v"), ("o",), ("gate", "up"), ("down",)):
+                for k in group:
+                    out[(i, k)] = float(L["peak"][group[0]])
+        return out
+
     def forward(self, inputs, rows=None, taps=None):
         """packed forward -> final hidden states after the model's last norm, [n, hidden] bf16, or only the rows `rows` (int64
         device tensor of stream positions). taps: optional dict filled with per-layer intermediates (tests)."""
@@ -165,38 +219,71 @@ class GemmaStack:
         H, K, D = cfg.heads, cfg.kv_heads, cfg.head_dim
         ids, pos, masks = inputs["ids"], inputs["pos"], inputs["masks"]
         n = ids.numel()
+        row = w.scheme == "fp8row"
         tables = {k: ops.rope_table(pos, f) for k, f in self.inv_freq.items()}
         h = ops.embed_scale(ids, w.embed, self.embed_scale)
         if self.n_layers == 0:
             return ops.fused_norm(h, w2=w.norm, rows=rows, eps=cfg.eps, want_norm=True)["norm"]
-        r = ops.fused_norm(h, w2=w.layers[0]["input_ln"], eps=cfg.eps, want_fp8=True)
+        r = ops.fused_norm(h, w2=w.layers[0]["input_ln"], eps=cfg.eps, want_fp8=row, want_norm=not row)
         for i in range(self.n_layers):
             L = w.layers[i]
             kind = cfg.layer_types[i]
             cos, sin = tables[kind]
+            x8, xs = (r["x8"], r["xs"]) if row else self._quant_in(r["norm"], L, ("q", "k", "v"))
             if self.fuse_qkv:  # head norms + rotary in the projection's epilogue
-                qkv = ops.fp8_gemm_qkv(r["x8"], r["xs"], L["qkv_w"], L["qkv_s"], H, K, D, L["q_norm"], L["k_norm"], cos, sin, cfg.eps)
+                qkv = ops.fp8_gemm_qkv(x8, xs, L["qkv_w"], L["qkv_s"], H, K, D, L["q_norm"], L["k_norm"], cos, sin, cfg.eps)
             else:
-                qkv = ops.fp8_rowwise_gemm(r["x8"], r["xs"], L["qkv_w"], L["qkv_s"])
+                qkv = ops.fp8_rowwise_gemm(x8, xs, L["qkv_w"], L["qkv_s"])
                 ops.qkv_norm_rope(qkv, H, K, D, L["q_norm"], L["k_norm"], cos, sin, cfg.eps)
             q = qkv[:, : H * D].view(n, H, D)
             k = qkv[:, H * D : (H + K) * D].view(n, K, D)
             v = qkv[:, (H + K) * D :].view(n, K, D)
-            amax = torch.zeros(n, dtype=torch.float32, device=qkv.device)
-            ops.COUNTS["launches"] += 1
+            amax = torch.zeros(n, dtype=torch.float32, device=qkv.device) if row else None
+            ops.COUNTS["launches"] += 1 if row else 0
             a = attention.tree_attention(q, k, v, masks[kind], 1.0, row_amax=amax)  # scaling = 1.0: q and k are normed
-            a8, a_s = ops.fp8_quant_from_amax(a.view(n, H * D), amax)  # the attention kernel has already found the row maxima
+            if row:  # the attention kernel has already found the row maxima
+                a8, a_s = ops.fp8_quant_from_amax(a.view(n, H * D), amax)
+            else:
+                a8, a_s = self._quant_in(a.view(n, H * D), L, ("o",))
             o = ops.fp8_rowwise_gemm(a8, a_s, L["o_w"], L["o_s"])
-            r = ops.fused_norm(o, w1=L["post_attn_ln"], residual=h, w2=L["pre_ffn_ln"], eps=cfg.eps, want_h=True, want_fp8=True)
+            r = ops.fused_norm(o, w1=L["post_attn_ln"], residual=h, w2=L["pre_ffn_ln"], eps=cfg.eps, want_h=True, want_fp8=row,
+                               want_norm=not row)
             h = r["h"]
-            g8, g_s, _ = ops.fp8_gemm_glu(r["x8"], r["xs"], L["gu_w"], L["gu_s"], "gelu_tanh")
+            if row:
+                g8, g_s, _ = ops.fp8_gemm_glu(r["x8"], r["xs"], L["gu_w"], L["gu_s"], "gelu_tanh")
+            else:
+                x8, xs = self._quant_in(r["norm"], L, ("gate", "up"))
+                gu = ops.fp8_rowwise_gemm(x8, xs, L["gu_w"], L["gu_s"])
+                g8, g_s = self._quant_in(ops.glu_quant(gu, "gelu_tanh", want_fp8=False, want_y=True)[2], L, ("down",))
             d = ops.fp8_rowwise_gemm(g8, g_s, L["down_w"], L["down_s"])
             last = i == self.n_layers - 1
             r = ops.fused_norm(
                 d, w1=L["post_ffn_ln"], residual=h, w2=None if last else w.layers[i + 1]["input_ln"], eps=cfg.eps, want_h=True,
-                want_fp8=not last,
+                want_fp8=row and not last, want_norm=not row and not last,
             )
             h = r["h"]
             if taps is not None:
                 taps[i] = {"q": q.clone(), "k": k.clone(), "v": v.clone(), "attn": a, "h": h}
         return ops.fused_norm(h, w2=w.norm, rows=rows, eps=cfg.eps, want_norm=True)["norm"]
+
+
+def calibrate(cfg: GemmaConfig, W, batches, device, headroom: float = 2.0, n_layers=None):
+    """Makes an fp8s scale table as the reference's calibration does (spinf_serve/quant/calibrate.py:100-178): run the model with the
+    dynamic fp8 scheme over `batches` (packer Batches covering what the model will see), record the largest |input| of every
+    quantized linear, and set scale = 2^ceil(log2(headroom x amax / 448)). -> {"scheme": "fp8s", "headroom", "amax": [{name: v}],
+    "scales": [{name: s}]}, one dict per layer; `scales` is what GemmaWeights.from_bf16(..., scheme="fp8s", scales=...) takes."""
+    stack = GemmaStack(GemmaWeights.from_bf16(cfg, W, device, scheme="fp8"), n_layers)
+    amax = [dict.fromkeys(LINEARS, 0.0) for _ in range(stack.n_layers)]
+    for b in batches:
+        stack.amax_log = []
+        stack.forward(stack.stage(b, device))
+        per_layer = len(LINEARS)
+        logged = [(k, float(v)) for k, v in stack.amax_log]  # read back after the forward: no sync inside it
+        for j, (k, v) in enumerate(logged):
+            i = j // per_layer
+            amax[i][k] = max(amax[i][k], v)
+        stack.amax_log = None
+    return {
+        "scheme": "fp8s", "headroom": headroom, "amax": amax,
+        "scales": [{k: static_scale(v, headroom) for k, v in a.items()} for a in amax],
+    }

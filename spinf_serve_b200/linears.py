@@ -1,10 +1,13 @@
 """Quantized linear modules with the reference's interface (spinf_serve/quant/linears.py:17-19,133-135): quant_linears(opts, device)
 returns a namespace of module classes built from a bf16 [out, in] weight on the device, exposing in_features / out_features and
-forward(x[..., K]) -> [..., N] bf16, with the same buffers (`w8t` = the [in, out] column-major view, `ws` [1, out]).
+forward(x[..., K]) -> [..., N] bf16, with the same buffers (`w8t` = the [in, out] column-major view, `ws`, and for the static
+scheme `xs` and `peak`).
 
-Fp8RowLinear (per-output-channel weight scales, per-token activation scales: the scheme of the BASELINE configurations) runs on
-the sm_100a kernels. The other schemes of the reference (dynamic / static per-tensor fp8, int8) are outside this path: their names
-resolve, constructing one raises RuntimeError, as the reference does for a scheme the device cannot run (gemma4.py:61-62)."""
+On the sm_100a kernels: Fp8RowLinear (per-output-channel weight scales, per-token activation scales: the scheme of the BASELINE
+configurations), Fp8Linear (per-tensor scales, the activation scale from the forward's own maximum) and Fp8StaticLinear
+(per-tensor scales, a calibrated fixed activation scale: the reference's "fp8s"), plus `prequantized` for the tensors of an
+fp8-static checkpoint. Int8Linear is outside this path: its name resolves and constructing one raises RuntimeError, as the
+reference does for a scheme the device cannot run (gemma4.py:61-62)."""
 
 from types import SimpleNamespace
 
@@ -22,6 +25,26 @@ def quantize_weight_rowwise(w):
     wf = w.float()
     s = wf.abs().amax(-1, keepdim=True).clamp(min=1e-12) / FP8_MAX
     return (wf / s).clamp_(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn), s.t().contiguous()
+
+
+def quantize_weight(w):
+    """bf16 [out, in] on the device -> (w8 [out, in] e4m3, fp32 scale []), one scale for the tensor: load-time arithmetic of
+    Fp8Linear / Fp8StaticLinear (spinf_serve/quant/linears.py:69-71, quant/fp8.py:14-21), same eager torch ops"""
+    wf = w.float()
+    s = wf.abs().amax().clamp(min=1e-12) / FP8_MAX
+    return (wf / s).clamp_(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn), s.reshape(())
+
+
+def static_scale(amax: float, headroom: float = 2.0) -> float:
+    """the calibrated activation scale of a linear whose largest input seen was `amax`: a power of two (exact in the kernel) at
+    least `headroom` times amax / 448 (spinf_serve/quant/calibrate.py:176-177)"""
+    import math
+
+    return 2.0 ** math.ceil(math.log2(max(amax, 1e-6) * headroom / FP8_MAX))
+
+
+# fp8s: a caller turns this on for sampled forwards; the peak check costs one block reduction per linear (linears.py:13-14)
+MONITOR = {"on": False}
 
 
 def quant_linears(opts: dict | None, device) -> SimpleNamespace:
@@ -42,6 +65,44 @@ def quant_linears(opts: dict | None, device) -> SimpleNamespace:
             y = ops.fp8_rowwise_gemm(x8, xs, self.w8t.t(), self.ws)
             return y.reshape(*x.shape[:-1], self.out_features)
 
+    class Fp8Linear(nn.Module):
+        """per-tensor scales both sides, the activation scale from this forward's maximum (linears.py:66-78): rows depend on
+        their neighbours in the stream through that maximum, as in the reference"""
+
+        def __init__(self, w):  # w: bf16 [out, in] on device
+            super().__init__()
+            if not w.is_cuda:
+                raise RuntimeError("Fp8Linear needs a CUDA device with sm_100a kernels; there is no CPU path")
+            w8, ws = quantize_weight(w)
+            self.register_buffer("w8t", w8.t())
+            self.register_buffer("ws", ws)
+            self.out_features, self.in_features = w.shape
+
+        def forward(self, x):
+            x8, xs = ops.fp8_tensor_quant(x if x.is_contiguous() else x.contiguous())
+            y = ops.fp8_tensor_gemm(x8, xs, self.w8t.t(), self.ws)
+            return y.reshape(*x.shape[:-1], self.out_features)
+
+    class Fp8StaticLinear(nn.Module):
+        """fp8 with a fixed activation scale (linears.py:98-116). `peak` keeps the largest |input| / (448 * scale) seen while
+        MONITOR["on"]: above 1 the input was clipped"""
+
+        def __init__(self, w, xs: float):  # w: bf16 [out, in] on device
+            super().__init__()
+            if not w.is_cuda:
+                raise RuntimeError("Fp8StaticLinear needs a CUDA device with sm_100a kernels; there is no CPU path")
+            w8, ws = quantize_weight(w)
+            self.register_buffer("w8t", w8.t())
+            self.register_buffer("ws", ws)
+            self.register_buffer("xs", torch.tensor(xs, dtype=torch.float32, device=w.device))
+            self.register_buffer("peak", torch.zeros((), dtype=torch.float32, device=w.device))
+            self.out_features, self.in_features = w.shape
+
+        def forward(self, x):
+            x8, _ = ops.fp8_tensor_quant(x if x.is_contiguous() else x.contiguous(), self.xs, self.peak if MONITOR["on"] else None)
+            y = ops.fp8_tensor_gemm(x8, self.xs, self.w8t.t(), self.ws)
+            return y.reshape(*x.shape[:-1], self.out_features)
+
     def _outside(name):
         class Unsupported(nn.Module):
             def __init__(self, *a, **k):
@@ -51,11 +112,23 @@ def quant_linears(opts: dict | None, device) -> SimpleNamespace:
         return Unsupported
 
     def prequantized(cls, w8, ws, xs=None):
-        raise RuntimeError("fp8-static checkpoints are outside the packed scoring path of this build (use fp8row)")
+        """Fp8StaticLinear / Fp8Linear from an fp8-static checkpoint's tensors: w8 e4m3 [out, in], ws fp32 [1], xs fp32 [1]
+        (linears.py:121-131)"""
+        if cls not in (Fp8Linear, Fp8StaticLinear):
+            raise RuntimeError(f"prequantized: {cls.__name__} is not a per-tensor fp8 linear")
+        lin = cls.__new__(cls)
+        nn.Module.__init__(lin)
+        lin.register_buffer("w8t", w8.to(device, non_blocking=True).contiguous().t())
+        lin.register_buffer("ws", ws.to(device, torch.float32).reshape(()))
+        if xs is not None:
+            lin.register_buffer("xs", xs.to(device, torch.float32).reshape(()))
+            lin.register_buffer("peak", torch.zeros((), dtype=torch.float32, device=device))
+        lin.out_features, lin.in_features = w8.shape
+        return lin
 
     return SimpleNamespace(
-        Int8Linear=_outside("Int8Linear"), Fp8Linear=_outside("Fp8Linear"), Fp8RowLinear=Fp8RowLinear,
-        Fp8StaticLinear=_outside("Fp8StaticLinear"), prequantized=prequantized,
+        Int8Linear=_outside("Int8Linear"), Fp8Linear=Fp8Linear, Fp8RowLinear=Fp8RowLinear, Fp8StaticLinear=Fp8StaticLinear,
+        prequantized=prequantized,
     )
 
 

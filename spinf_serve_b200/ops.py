@@ -70,6 +70,61 @@ def fp8_rowwise_gemm(x8, xs, w8, ws, out=None):
     return y
 
 
+def fp8_tensor_quant(x, scale=None, peak=None, want_amax=False):
+    """per-tensor fp8 quantisation of x [..., K] bf16 -> (x8 [M, K] e4m3, s fp32 scalar on the device).
+    scale = None: dynamic, s = max(max|x|, 1e-12) / 448 (quant_act, spinf_serve/quant/linears.py:22-26; two kernels, no host
+    sync); scale = fp32 device scalar: static, s = scale (Fp8StaticLinear.forward, linears.py:113). peak: optional fp32 device
+    scalar updated to max(peak, max|x| / (448 s)) (the static scheme's clipping monitor, linears.py:111-112). want_amax (dynamic
+    only): also return the device scalar max|x|."""
+    x2 = x.reshape(-1, x.shape[-1])
+    _need(x2, torch.bfloat16, "x", 2)
+    M, K = x2.shape
+    if (M * K) % 8:
+        raise SpinfError("fp8_tensor_quant: the element count must be a multiple of 8")
+    x8 = torch.empty((M, K), dtype=FP8, device=x.device)
+    L = _lib.lib()
+    if scale is None:
+        both = torch.empty(2, dtype=torch.float32, device=x.device)  # [max|x|, s]: other CTAs still read the maximum when s is written
+        amax, s = both[0], both[1]
+        check(L.spinf_abs_max(ptr(x2), M * K, ptr(amax), stream_ptr()), "spinf_abs_max")
+        check(L.spinf_fp8_tensor_quant(ptr(x2), M * K, ptr(amax), 1, ptr(x8), ptr(s), ptr(peak), stream_ptr()), "spinf_fp8_tensor_quant")
+        COUNTS["launches"] += 2
+        if want_amax:
+            return x8, s, amax
+    else:
+        s = scale
+        _need(s.reshape(1), torch.float32, "scale", 1)
+        check(L.spinf_fp8_tensor_quant(ptr(x2), M * K, ptr(s), 0, ptr(x8), None, ptr(peak), stream_ptr()), "spinf_fp8_tensor_quant")
+        COUNTS["launches"] += 1
+    return x8, s
+
+
+def fp8_tensor_gemm(x8, xs, w8, ws, out=None):
+    """y [M, N] bf16 = (x8 [M, K] @ w8 [N, K]^T) * xs * ws with one fp32 device scalar per operand (the per-tensor
+    torch._scaled_mm of Fp8Linear / Fp8StaticLinear, spinf_serve/quant/linears.py:77,114)"""
+    _need(x8, FP8, "x8", 2)
+    _need(w8, FP8, "w8", 2)
+    _need(xs.reshape(1), torch.float32, "xs", 1)
+    _need(ws.reshape(1), torch.float32, "ws", 1)
+    M, K = x8.shape
+    N = w8.shape[0]
+    if w8.shape[1] != K:
+        raise SpinfError(f"fp8_tensor_gemm: shapes do not agree: x8 {tuple(x8.shape)}, w8 {tuple(w8.shape)}")
+    y = out if out is not None else torch.empty((M, N), dtype=torch.bfloat16, device=x8.device)
+    if out is not None:
+        _need(out, torch.bfloat16, "out", 2)
+    prof = PROFILE
+    if prof is not None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+    check(_lib.lib().spinf_fp8_tensor_gemm(ptr(x8), ptr(xs), ptr(w8), ptr(ws), ptr(y), M, N, K, stream_ptr()), "spinf_fp8_tensor_gemm")
+    if prof is not None:
+        e1.record()
+        prof.append((e0, e1, 2.0 * M * N * K))
+    COUNTS["launches"] += 1
+    return y
+
+
 def w4_gemm(x, qw, scales, group, extra=None):
     """y [M, N (+ E)] bf16 = x [M, K] bf16 @ dq(qw, scales)^T, with E un-quantised bf16 output channels `extra` [E, K] appended
     (Int4Linear.forward in bf16 mode, spinf_serve/models/qwen35/qwen.py:455-458); qw uint8 [N, K/2], scales fp16 [N, K/group]"""

@@ -32,6 +32,7 @@ class EngineConfig:
     align_jobs: bool = True
     min_stream: int = 1024
     layers: int | None = None  # debug: run the first n layers only
+    fp8s_monitor_every: int = 0  # fp8s: check every k-th forward's linear inputs against their scales (0 = never)
 
 
 @dataclass
@@ -102,6 +103,11 @@ class Scorer:
         dev = self.device
         if not len(b.sel) or not cols:
             return torch.zeros((len(b.sel), len(cols)), dtype=torch.float32, device=dev)
+        if getattr(self.stack.w, "scheme", "") == "fp8s":  # sampled forwards only (spinf_serve/scorer.py:270-275)
+            from spinf_serve_b200.linears import MONITOR
+
+            k = self.cfg.fp8s_monitor_every
+            MONITOR["on"] = bool(k) and self.stats.forwards % k == 0
         inputs = self.stack.stage(b, dev)
         sel = torch.from_numpy(b.sel).pin_memory().to(dev, non_blocking=True)
         ci = torch.tensor(cols, dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
@@ -111,6 +117,15 @@ class Scorer:
         if self._workspace is None or self._workspace.numel() < need:
             self._workspace = torch.empty(int(need * 1.5), dtype=torch.uint8, device=dev)
         return ops.option_logprobs(rows, W, ci, self.softcap, self._workspace)
+
+    def fp8s_peak(self):
+        """fp8s with the monitor on: (the largest input / clip level over the linears since load, (layer, linear name)), else
+        None (spinf_serve/scorer.py:308-317); above 1 an input was clipped: the scale table did not cover it"""
+        if getattr(self.stack.w, "scheme", "") != "fp8s" or not self.cfg.fp8s_monitor_every:
+            return None
+        peaks = self.stack.peaks()
+        k = max(peaks, key=peaks.get)
+        return peaks[k], k
 
     def _readback(self, lp):
         host = torch.empty(lp.shape, dtype=lp.dtype).pin_memory()

@@ -38,6 +38,10 @@ def test_argument_errors_are_reported_on_the_host():
     assert lib.spinf_fp8_rowwise_quant(p, 4, 60, p, p, NULL) == -1              # K not a multiple of 8
     assert lib.spinf_fp8_rowwise_gemm(p, p, p, p, p, 4, 100, 64, NULL) == -1    # N not a multiple of 16
     assert lib.spinf_fp8_rowwise_gemm(p, p, p, p, p, -1, 128, 64, NULL) == -1   # negative M
+    assert lib.spinf_fp8_tensor_gemm(p, p, p, p, p, 4, 128, 60, NULL) == -1     # K not a multiple of 16
+    assert lib.spinf_fp8_tensor_quant(p, 100, p, 0, p, NULL, NULL, NULL) == -1  # element count not a multiple of 8
+    assert lib.spinf_fp8_tensor_quant(p, 64, p, 2, p, NULL, NULL, NULL) == -1   # from_amax is 0 or 1
+    assert lib.spinf_abs_max(p, 12, p, NULL) == -1                              # element count not a multiple of 8
     assert lib.spinf_bf16_gemm_ld(p, p, p, 4, 128, 64, 64, NULL) == -1          # pitch smaller than N
     assert lib.spinf_w4_gemm(p, p, p, 128, p, 4, 128, 100, 128, NULL) == -1     # K not a multiple of 64
     assert lib.spinf_w4_gemm(p, p, p, 12, p, 4, 128, 128, 128, NULL) == -1      # group not a multiple of 8

@@ -135,3 +135,92 @@ def test_scores_bit_identical_alone_and_packed(dev):
     for r in res[1:]:
         for a, b in zip(r, res[0]):
             assert np.array_equal(a, b)
+
+
+def test_per_tensor_schemes_vs_oracle(dev):
+    """the reference's other two fp8 schemes on the same stack: calibration (dynamic scheme + largest inputs -> power-of-two scales)
+    agrees with the oracle's, the static forward tracks the oracle's static forward like the row-wise one does, the monitor
+    reports no clipping on the calibration data, and only the static scheme's scores are independent of a content's neighbours"""
+    from spinf_serve_b200 import gemma_stack as GS
+    from spinf_serve_b200 import linears
+    from spinf_serve_b200.scorer import EngineConfig, Scorer
+
+    layers = 3
+    ocfg = OG.GemmaConfig(**_cfg(128, layers))
+    cfg = GS.GemmaConfig(**_cfg(128, layers))
+    W = OG.init_weights(ocfg, seed=3)
+    rng = np.random.default_rng(5)
+    pk = P.Packer(2048, 8192, align=True)
+    for j in range(3):
+        list(pk.push(j, _content(rng, int(rng.integers(40, 300)), 4)))
+    (b,) = list(pk.flush())
+    real = torch.from_numpy(b.art >= 0)
+
+    tab_o = OG.calibrate(ocfg, W, [b], 2.0)
+    tab_g = GS.calibrate(cfg, W, [b], dev, 2.0)
+    assert tab_g["scheme"] == "fp8s" and len(tab_g["scales"]) == layers
+    for k in ("q", "k", "v"):  # layer 0's first inputs are the same tensor on both sides
+        assert tab_g["amax"][0][k] == tab_o["amax"][0][k]
+    same = [tab_g["scales"][i][k] == tab_o["scales"][i][k] for i in range(layers) for k in OG.LINEARS]
+    ratio = [tab_g["amax"][i][k] / tab_o["amax"][i][k] for i in range(layers) for k in OG.LINEARS]
+    print(f"calibration: {sum(same)} of {len(same)} scales equal; amax ratio {min(ratio):.3f}..{max(ratio):.3f}")
+    # maxima are extreme values of activations that already differ by fp8 rounding noise; one beside a power of two may fall either side
+    assert sum(same) >= len(same) - 2 and 0.8 < min(ratio) and max(ratio) < 1.25
+
+    for scheme in ("fp8", "fp8s"):
+        Q = OG.quantize(W, scheme)
+        stack = GS.GemmaStack(GS.GemmaWeights.from_quantized(cfg, W, Q, dev, scheme, tab_o["scales"]))
+        taps_o, taps_g, peaks_o = {}, {}, {}
+        OG.forward(ocfg, W, Q, b.ids, b.art, b.end, b.pos, taps=taps_o, scheme=scheme, scales=tab_o["scales"], peaks=peaks_o)
+        linears.MONITOR["on"] = scheme == "fp8s"
+        try:
+            stack.forward(stack.stage(b, dev), taps=taps_g)
+        finally:
+            linears.MONITOR["on"] = False
+        for key in ("q", "k", "v"):
+            g, o = taps_g[0][key].cpu()[real].float(), taps_o[0][key][real].float()
+            frac = (g != o).float().mean().item()
+            print(f"{scheme} layer0 {key}: differing elements {frac:.4%}")
+            assert frac < 0.01 and (g - o).abs().max() <= 2.0**-6 * o.abs().max()
+        # later layers: statistical, against the oracle's own sensitivity to one legitimate rounding change (P rounded to bf16
+        # before P V), as in test_forward_vs_oracle_layer_by_layer; one scale per tensor makes the fp8 steps coarser than row-wise
+        taps_p = {}
+        exact = OA.tree_attention
+        try:
+            OA.tree_attention = lambda *a, **k: exact(*a, **{**k, "round_p": True})
+            OG.forward(ocfg, W, Q, b.ids, b.art, b.end, b.pos, taps=taps_p, scheme=scheme, scales=tab_o["scales"])
+        finally:
+            OA.tree_attention = exact
+        for i in range(layers):
+            o = taps_o[i]["h"][real].float()
+            rms = lambda x: (x.pow(2).mean().sqrt() / o.pow(2).mean().sqrt()).item()  # noqa: E731
+            err, floor = rms(taps_g[i]["h"].cpu()[real].float() - o), rms(taps_p[i]["h"][real].float() - o)
+            print(f"{scheme} hidden after layer {i}: rms err / rms = {err:.3e} (oracle's own rounding sensitivity {floor:.3e})")
+            assert err < 3 * floor + 1e-3
+        if scheme == "fp8s":
+            pk_g = stack.peaks()
+            assert pk_g[(0, "q")] == peaks_o[(0, "q")]  # the same input, the same scale
+            assert 0.0 < max(pk_g.values()) <= 0.55  # headroom 2 over this very batch: nothing clips
+            assert all(abs(pk_g[k] - v) <= 0.1 * v for k, v in peaks_o.items())
+
+    # neighbours: static scores are the same bits alone and packed; the dynamic scheme's move with the stream's maximum
+    target = (("T",), 0, _content(rng, 200, 5))
+    others = _items(rng, 6)
+    res = {}
+    for scheme in ("fp8", "fp8s"):
+        stack = GS.GemmaStack(GS.GemmaWeights.from_bf16(cfg, W, dev, scheme, tab_o["scales"]))
+        sc = Scorer(stack, EngineConfig(token_budget=4096, max_tokens=8192), dev)
+        res[scheme] = [sc.score_grouped(r)[("T",)] for r in ([target], others[:3] + [target] + others[3:])]
+    assert all(np.array_equal(a, c) for a, c in zip(*res["fp8s"]))
+    assert not all(np.array_equal(a, c) for a, c in zip(*res["fp8"]))
+
+    # the sampled monitor through the scorer: nothing seen without it, a clipped input shows as a peak above 1
+    tight = [{k: v / 16 for k, v in d.items()} for d in tab_o["scales"]]  # a table whose calibration did not cover these inputs
+    stack = GS.GemmaStack(GS.GemmaWeights.from_bf16(cfg, W, dev, "fp8s", tight))
+    assert Scorer(stack, EngineConfig(token_budget=4096, max_tokens=8192), dev).fp8s_peak() is None
+    sc = Scorer(stack, EngineConfig(token_budget=4096, max_tokens=8192, fp8s_monitor_every=1), dev)
+    sc.score_grouped([target])
+    worst, where = sc.fp8s_peak()
+    assert worst > 1.0 and where[1] in OG.LINEARS
+    assert linears.MONITOR["on"]
+    linears.MONITOR["on"] = False
