@@ -10,8 +10,9 @@ over a content-partitioned queue, no collective on the data path): weak scaling.
 
   value   questions/s with the packed inputs already resident in HBM (stack forward + option log-prob read), K steps between
           CUDA events, max over ranks
-  e2e     the same through the public call Scorer.score_grouped with host inputs: packing, tile descriptors, pinned host->device
-          copies, forward, device->host read of the log-probs, all inside the timed region
+  e2e     the same through the public call Scorer.score_grouped with host inputs: one call over the K steps' contents (K forwards),
+          with packing, tile descriptors, pinned host->device copies, forward and device->host read of the log-probs of every
+          forward inside the timed region; the scorer's producer thread packs the next forward while the GPU runs this one
   roofline   the row-wise fp8 GEMM (dominant kernel): algorithmic FLOPs / CUDA-event time of its launches in the timed region
   cpu_baseline   the CPU oracle (a port of the reference's arithmetic; the reference has no CPU forward) on a bounded sample
 
@@ -252,19 +253,23 @@ def gpu_arm(args):
     _lib.last_status()
     assert bool(torch.isfinite(lp).all()), "non-finite log-probs"
 
-    # ---- end-to-end leg: the public call with host inputs, every step packs, stages, runs and reads back
+    # ---- end-to-end leg: ONE public call with host inputs over the contents of all the steps (a bulk request: `steps` x 24
+    # contents = `steps` forwards). Every forward's batch is packed, described, staged through pinned memory, run and read back
+    # inside the timed region; the scorer's producer thread packs forward i + 1 while the GPU runs forward i, which is the
+    # overlap the reference's Scorer._execute provides (spinf_serve/scorer.py:432-510).
     for _ in range(min(args.warmup, 2)):
         scorer.score_grouped(wl.items)
+    bulk = [((s,) + tuple(key), first, tree) for s in range(args.steps) for key, first, tree in wl.items]
+    f0_forwards = scorer.stats.forwards
     sync()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     f0.record()
-    for _ in range(args.steps):
-        out = scorer.score_grouped(wl.items)
+    out = scorer.score_grouped(bulk)
     f1.record()
     sync()
     ms_e2e = f0.elapsed_time(f1)
     clocks = sampler.stop() if rank == 0 else None
-    assert len(out) == len(wl.items)
+    assert len(out) == len(bulk) and scorer.stats.forwards - f0_forwards == args.steps, "one forward per step"
 
     if world > 1:
         t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
