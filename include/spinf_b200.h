@@ -79,6 +79,22 @@ int spinf_fp8_tensor_quant(const void* x_bf16, int64_t n, const float* scale, in
 int spinf_fp8_tensor_gemm(const void* x8, const float* xs, const void* w8, const float* ws, void* y_bf16, int64_t M, int64_t N,
                           int64_t K, void* stream);
 
+/* ------------------------------------------------------------------------------------------------------------ int8 linear (w8a8)
+ * The reference's Int8Linear with int8 activations (spinf_serve/quant/linears.py:40-64, act8 = True).
+ *
+ * Replaces quant_act_int8 (linears.py:34-38): per row m of x [M,K] bf16,
+ *   xs[m] = max(|x[m,:]|, 1e-12) / 127 (fp32);  x8[m,k] = int8(clamp(round_half_even(float(x[m,k]) / xs[m]), -127, 127)).
+ * K must be a multiple of 8 and at most 32768. */
+int spinf_int8_rowwise_quant(const void* x_bf16, int64_t M, int64_t K, void* x8, float* xs, void* stream);
+
+/* Replaces torch._int_mm and the scaling after it (linears.py:61):
+ *   y[m,n] = bf16( float(sum_k x8[m,k] * w8[n,k])_int32 * xs[m] * ws[n] )
+ * x8 [M,K] int8 row-major; w8 [N,K] int8 row-major (the storage of the reference's `w8t` buffer); xs [M], ws [N] fp32; y [M,N]
+ * bf16. K and N multiples of 16. Integer accumulation is exact, so a row of y depends on nothing but its own operands; unlike
+ * torch._int_mm there is no lower limit on M (the reference pads to 17 rows, linears.py:59-60). */
+int spinf_int8_rowwise_gemm(const void* x8, const float* xs, const void* w8, const float* ws, void* y_bf16, int64_t M, int64_t N,
+                            int64_t K, void* stream);
+
 /* The gate|up projection of a gated MLP with the activation fused into the GEMM epilogue (the reference runs
  * act(gate_proj(x)) * up_proj(x) as two Fp8RowLinear calls and an inductor-fused pointwise kernel: transformers' Gemma4TextMLP,
  * called through spinf_serve/models/gemma4.py:407-415; Qwen's MLP spinf_serve/models/qwen35/qwen.py:706-716):

@@ -117,3 +117,31 @@ def static_scale(amax, headroom=2.0):
     import math
 
     return 2.0 ** math.ceil(math.log2(max(amax, 1e-6) * headroom / FP8_MAX))
+
+
+# ------------------------------------------------------------------------------------------------ int8 (w8a8 and w8a16)
+def quantize_weight_int8(w):
+    """bf16 [out, in] -> (w8 [out, in] int8, s [out] fp32): Int8Linear.__init__, linears.py:43-46"""
+    wf = w.float()
+    s = wf.abs().amax(-1).clamp(min=1e-12) / 127.0
+    return (wf / s[:, None]).round_().clamp_(-127, 127).to(torch.int8), s
+
+
+def quant_act_int8(x):
+    """[..., K] -> (x8 [M, K] int8, xs [M, 1] fp32): linears.py:34-38"""
+    xf = x.reshape(-1, x.shape[-1]).float()
+    s = xf.abs().amax(-1, keepdim=True).clamp_(min=1e-12) / 127.0
+    return (xf / s).round_().clamp_(-127, 127).to(torch.int8), s
+
+
+def int8_linear(x, w8, ws, act8=True):
+    """Int8Linear.forward, linears.py:55-64. act8: the int32 product (exact; restated as an int64 matmul, torch._int_mm needs CUDA
+    or M > 16) converted to fp32 and scaled; else the weight dequantised to bf16 against bf16 activations"""
+    x2 = x.reshape(-1, x.shape[-1])
+    if act8:
+        x8, xs = quant_act_int8(x2)
+        acc = (x8.long() @ w8.long().t()).to(torch.int32)
+        y = (acc.float() * xs * ws).to(torch.bfloat16)
+    else:
+        y = torch.nn.functional.linear(x2, w8.to(torch.bfloat16) * ws.to(torch.bfloat16)[:, None])
+    return y.reshape(*x.shape[:-1], w8.shape[0])

@@ -26,6 +26,8 @@ SIGNATURES = {
     "spinf_abs_max": (ctypes.c_int, [_p, _i64, _p, _p]),
     "spinf_fp8_tensor_quant": (ctypes.c_int, [_p, _i64, _p, _i32, _p, _p, _p, _p]),
     "spinf_fp8_tensor_gemm": (ctypes.c_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _p]),
+    "spinf_int8_rowwise_quant": (ctypes.c_int, [_p, _i64, _i64, _p, _p, _p]),
+    "spinf_int8_rowwise_gemm": (ctypes.c_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _p]),
     "spinf_fp8_rowwise_gemm_glu": (ctypes.c_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i32, _p]),
     "spinf_fp8_rowwise_gemm_qkv": (ctypes.c_int, [_p, _p, _p, _p, _p, _i64, _i32, _i32, _i32, _i64, _p, _p, _p, _p, _f32, _i32, _i32, _p]),
     "spinf_fp8_quant_from_amax": (ctypes.c_int, [_p, _p, _i64, _i64, _p, _p, _p]),

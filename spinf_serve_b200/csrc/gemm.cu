@@ -360,6 +360,9 @@ __global__ void __launch_bounds__(128) lse_finalize_kernel(const float* __restri
 // ------------------------------------------------------------------------------------------------ per-row fp8 quantiser
 // One CTA per row: amax over the row in fp32, then x / s (a true division, as the reference computes it), clamped and cast to e4m3
 // with round-to-nearest-even.
+// INT8: the int8 scheme's quantiser instead (quant_act_int8): s = amax / 127, round(x / s) to the nearest integer (ties to even),
+// clamped to +-127.
+template <bool INT8>
 __global__ void __launch_bounds__(256) fp8_rowwise_quant_kernel(const __nv_bfloat16* __restrict__ x, int K, uint8_t* __restrict__ x8,
                                                                 float* __restrict__ xs) {
   const size_t row = blockIdx.x;
@@ -382,7 +385,7 @@ __global__ void __launch_bounds__(256) fp8_rowwise_quant_kernel(const __nv_bfloa
   amax = red[0];
 #pragma unroll
   for (int w = 1; w < 8; ++w) amax = fmaxf(amax, red[w]);
-  const float s = __fdiv_rn(fmaxf(amax, 1e-12f), 448.f);
+  const float s = __fdiv_rn(fmaxf(amax, 1e-12f), INT8 ? 127.f : 448.f);
   if (threadIdx.x == 0) xs[row] = s;
   const DivBy div = make_div_by(s);
   uint2* dst = reinterpret_cast<uint2*>(x8 + row * K);
@@ -395,9 +398,14 @@ __global__ void __launch_bounds__(256) fp8_rowwise_quant_kernel(const __nv_bfloa
       float2 a = __bfloat1622float2(p[2 * j]), b = __bfloat1622float2(p[2 * j + 1]);
       // no explicit clamp: |x / s| can exceed 448 only by rounding, and the conversion saturates
       const float q0 = div_by(div, a.x), q1 = div_by(div, a.y), q2 = div_by(div, b.x), q3 = div_by(div, b.y);
-      const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(q0, q1), __NV_SATFINITE, __NV_E4M3);
-      const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(q2, q3), __NV_SATFINITE, __NV_E4M3);
-      o[j] = lo | (hi << 16);
+      if (INT8) {
+        auto r8 = [](float q) { return static_cast<uint32_t>(max(-127, min(127, __float2int_rn(q)))) & 0xffu; };
+        o[j] = r8(q0) | (r8(q1) << 8) | (r8(q2) << 16) | (r8(q3) << 24);
+      } else {
+        const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(q0, q1), __NV_SATFINITE, __NV_E4M3);
+        const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(q2, q3), __NV_SATFINITE, __NV_E4M3);
+        o[j] = lo | (hi << 16);
+      }
     }
     dst[i] = make_uint2(o[0], o[1]);
   }
@@ -515,10 +523,36 @@ using namespace spinf;
 extern "C" int spinf_fp8_rowwise_quant(const void* x_bf16, int64_t M, int64_t K, void* x8, float* xs, void* stream) {
   SPINF_CHECK_ARG(x_bf16 && x8 && xs && M >= 0 && K > 0 && K % 8 == 0 && K <= 32768 && M < (1ll << 31));
   if (M == 0) return 0;
-  fp8_rowwise_quant_kernel<<<static_cast<unsigned>(M), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  fp8_rowwise_quant_kernel<false><<<static_cast<unsigned>(M), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x_bf16), static_cast<int>(K), static_cast<uint8_t*>(x8), xs);
   SPINF_CUDA_OK(cudaGetLastError());
   return 0;
+}
+
+extern "C" int spinf_int8_rowwise_quant(const void* x_bf16, int64_t M, int64_t K, void* x8, float* xs, void* stream) {
+  SPINF_CHECK_ARG(x_bf16 && x8 && xs && M >= 0 && K > 0 && K % 8 == 0 && K <= 32768 && M < (1ll << 31));
+  if (M == 0) return 0;
+  fp8_rowwise_quant_kernel<true><<<static_cast<unsigned>(M), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x_bf16), static_cast<int>(K), static_cast<uint8_t*>(x8), xs);
+  SPINF_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int spinf_int8_rowwise_gemm(const void* x8, const float* xs, const void* w8, const float* ws, void* y_bf16, int64_t M,
+                                       int64_t N, int64_t K, void* stream) {
+  SPINF_CHECK_ARG(x8 && xs && w8 && ws && y_bf16 && M >= 0 && N > 0 && K > 0 && K % 16 == 0 && N % 16 == 0);
+  SPINF_CHECK_ARG(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31));
+  if (M == 0) return 0;
+  constexpr int BN = 256;
+  CUtensorMap tmA, tmB;
+  EpiStoreBf16<BN, true, true> epi;
+  int r;
+  if ((r = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x8, M, K, K, 128, 128))) return r;
+  if ((r = make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w8, N, K, K, 128, BN))) return r;
+  if ((r = make_tmap_2d(&epi.tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y_bf16, M, N, N * 2, 64, 128))) return r;
+  epi.rowscale = xs;
+  epi.colscale_g = ws;
+  return launch_gemm<KIND_S8, BN>(tmA, tmB, make_shape(M, N, K, BN), epi, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int spinf_fp8_rowwise_gemm(const void* x8, const float* xs, const void* w8, const float* ws, void* y_bf16, int64_t M,

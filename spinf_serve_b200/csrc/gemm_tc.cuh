@@ -17,7 +17,7 @@
 
 namespace spinf {
 
-enum : int { KIND_F8 = 0, KIND_BF16 = 1 };
+enum : int { KIND_F8 = 0, KIND_BF16 = 1, KIND_S8 = 2 };  // operand types: e4m3 (fp32 accumulators), bf16 (fp32), int8 (int32)
 
 struct GemmShape {
   int M, N, K;
@@ -66,8 +66,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                const __grid_constant__ Epi epi, int* __restrict__ status) {
   using L = GemmSmem<BN>;
   constexpr int STAGES = L::STAGES;
-  constexpr int KE = KIND == KIND_F8 ? 128 : 64;  // K elements per stage (128 bytes)
-  constexpr uint32_t IDESC = KIND == KIND_F8 ? make_idesc(FMT_E4M3, FMT_E4M3, 128, BN, 0, 0) : make_idesc(FMT_BF16, FMT_BF16, 128, BN, 0, 0);
+  constexpr int KE = KIND == KIND_BF16 ? 64 : 128;  // K elements per stage (128 bytes)
+  constexpr uint32_t IDESC = KIND == KIND_F8   ? make_idesc(FMT_E4M3, FMT_E4M3, 128, BN, 0, 0)
+                             : KIND == KIND_S8 ? make_idesc_s8(128, BN)
+                                               : make_idesc(FMT_BF16, FMT_BF16, 128, BN, 0, 0);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -156,6 +158,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             // 32 bytes along K per step: +2 in the descriptor's 16-byte address units
             if (KIND == KIND_F8)
               umma_f8_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, IDESC, (kb | k) != 0);
+            else if (KIND == KIND_S8)
+              umma_i8_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, IDESC, (kb | k) != 0);
             else
               umma_f16_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, IDESC, (kb | k) != 0);
           }
@@ -233,7 +237,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
 // bf16 output through a swizzled staging buffer and TMA stores of 128 x 64 boxes.
 //   SCALED: y = bf16((acc * rowscale[m]) * colscale[n])   (the row-wise fp8 linear)       else: y = bf16(acc)
-template <int BN, bool SCALED>
+//   ACC_S32: the accumulators are 32-bit integers (int8 operands), converted to fp32 first as the reference's `.float()` does
+template <int BN, bool SCALED, bool ACC_S32 = false>
 struct EpiStoreBf16 {
   static constexpr bool kReadsTmemInEnd = false;
   CUtensorMap tmC;  // [M, N] bf16, box 64 x 128, 128-byte swizzle
@@ -265,8 +270,14 @@ struct EpiStoreBf16 {
     uint32_t packed[32];
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      float a = __uint_as_float(v0[2 * i]), b = __uint_as_float(v0[2 * i + 1]);
-      float d = __uint_as_float(v1[2 * i]), e = __uint_as_float(v1[2 * i + 1]);
+      float a, b, d, e;
+      if (ACC_S32) {
+        a = __int2float_rn(static_cast<int>(v0[2 * i])), b = __int2float_rn(static_cast<int>(v0[2 * i + 1]));
+        d = __int2float_rn(static_cast<int>(v1[2 * i])), e = __int2float_rn(static_cast<int>(v1[2 * i + 1]));
+      } else {
+        a = __uint_as_float(v0[2 * i]), b = __uint_as_float(v0[2 * i + 1]);
+        d = __uint_as_float(v1[2 * i]), e = __uint_as_float(v1[2 * i + 1]);
+      }
       if (SCALED) {
         a = (a * rs) * colscale[c * 64 + 2 * i];
         b = (b * rs) * colscale[c * 64 + 2 * i + 1];

@@ -5,9 +5,10 @@ scheme `xs` and `peak`).
 
 On the sm_100a kernels: Fp8RowLinear (per-output-channel weight scales, per-token activation scales: the scheme of the BASELINE
 configurations), Fp8Linear (per-tensor scales, the activation scale from the forward's own maximum) and Fp8StaticLinear
-(per-tensor scales, a calibrated fixed activation scale: the reference's "fp8s"), plus `prequantized` for the tensors of an
-fp8-static checkpoint. Int8Linear is outside this path: its name resolves and constructing one raises RuntimeError, as the
-reference does for a scheme the device cannot run (gemma4.py:61-62)."""
+(per-tensor scales, a calibrated fixed activation scale: the reference's "fp8s"), `prequantized` for the tensors of an
+fp8-static checkpoint, and Int8Linear (int8 weights; int8 per-token activations on the int8 tensor cores, or bf16 activations).
+Constructing any of them on a device without the kernels raises RuntimeError, as the reference does for a scheme the device
+cannot run (gemma4.py:61-62): there is no CPU path."""
 
 from types import SimpleNamespace
 
@@ -103,13 +104,36 @@ def quant_linears(opts: dict | None, device) -> SimpleNamespace:
             y = ops.fp8_tensor_gemm(x8, self.xs, self.w8t.t(), self.ws)
             return y.reshape(*x.shape[:-1], self.out_features)
 
-    def _outside(name):
-        class Unsupported(nn.Module):
-            def __init__(self, *a, **k):
-                raise RuntimeError(f"quant scheme {name} is outside the packed scoring path of this build (use fp8row)")
+    class Int8Linear(nn.Module):
+        """int8 weights with per-output-channel scales; act8: int8 per-token activations on the int8 tensor cores (w8a8), else
+        bf16 activations against the weight dequantised to bf16 (w8a16) (linears.py:40-64). Load-time arithmetic with the
+        reference's eager torch ops."""
 
-        Unsupported.__name__ = name
-        return Unsupported
+        def __init__(self, w, act8):
+            super().__init__()
+            if not w.is_cuda:
+                raise RuntimeError("Int8Linear needs a CUDA device with sm_100a kernels; there is no CPU path")
+            wf = w.float()
+            s = wf.abs().amax(-1).clamp(min=1e-12) / 127.0
+            w8 = (wf / s[:, None]).round_().clamp_(-127, 127).to(torch.int8)
+            if act8:
+                self.register_buffer("w8t", w8.t())  # [in, out] column-major view of the [out, in] storage
+                self.register_buffer("ws", s)  # [out] fp32
+            else:
+                self.register_buffer("w8", w8)  # [out, in]
+                self.register_buffer("ws", s.to(torch.bfloat16)[:, None])  # [out, 1]
+            self.act8 = act8
+            self.out_features, self.in_features = w.shape
+
+        def forward(self, x):
+            x2 = x.reshape(-1, x.shape[-1])
+            x2 = x2 if x2.is_contiguous() else x2.contiguous()
+            if self.act8:
+                x8, xs = ops.int8_rowwise_quant(x2)
+                y = ops.int8_rowwise_gemm(x8, xs, self.w8t.t(), self.ws)
+            else:  # the scale folded into the weight, one bf16 rounding per element, as the reference folds it on every call
+                y = ops.bf16_gemm(x2, self.w8.to(torch.bfloat16) * self.ws)
+            return y.reshape(*x.shape[:-1], self.out_features)
 
     def prequantized(cls, w8, ws, xs=None):
         """Fp8StaticLinear / Fp8Linear from an fp8-static checkpoint's tensors: w8 e4m3 [out, in], ws fp32 [1], xs fp32 [1]
@@ -127,7 +151,7 @@ def quant_linears(opts: dict | None, device) -> SimpleNamespace:
         return lin
 
     return SimpleNamespace(
-        Int8Linear=_outside("Int8Linear"), Fp8Linear=Fp8Linear, Fp8RowLinear=Fp8RowLinear, Fp8StaticLinear=Fp8StaticLinear,
+        Int8Linear=Int8Linear, Fp8Linear=Fp8Linear, Fp8RowLinear=Fp8RowLinear, Fp8StaticLinear=Fp8StaticLinear,
         prequantized=prequantized,
     )
 

@@ -125,6 +125,37 @@ def fp8_tensor_gemm(x8, xs, w8, ws, out=None):
     return y
 
 
+def int8_rowwise_quant(x):
+    """x [..., K] bf16 -> (x8 [M, K] int8, xs [M, 1] fp32), per-row dynamic scales amax / 127, round half to even
+    (quant_act_int8, spinf_serve/quant/linears.py:34-38)"""
+    x2 = x.reshape(-1, x.shape[-1])
+    _need(x2, torch.bfloat16, "x", 2)
+    M, K = x2.shape
+    x8 = torch.empty((M, K), dtype=torch.int8, device=x.device)
+    xs = torch.empty((M, 1), dtype=torch.float32, device=x.device)
+    check(_lib.lib().spinf_int8_rowwise_quant(ptr(x2), M, K, ptr(x8), ptr(xs), stream_ptr()), "spinf_int8_rowwise_quant")
+    COUNTS["launches"] += 1
+    return x8, xs
+
+
+def int8_rowwise_gemm(x8, xs, w8, ws):
+    """y [M, N] bf16 = float(x8 [M, K] @ w8 [N, K]^T as int32) * xs [M] * ws [N] (torch._int_mm and the scaling after it,
+    spinf_serve/quant/linears.py:61)"""
+    _need(x8, torch.int8, "x8", 2)
+    _need(w8, torch.int8, "w8", 2)
+    xs1, ws1 = xs.reshape(-1), ws.reshape(-1)
+    _need(xs1, torch.float32, "xs", 1)
+    _need(ws1, torch.float32, "ws", 1)
+    M, K = x8.shape
+    N = w8.shape[0]
+    if w8.shape[1] != K or xs1.numel() != M or ws1.numel() != N:
+        raise SpinfError(f"int8_rowwise_gemm: shapes do not agree: x8 {tuple(x8.shape)}, w8 {tuple(w8.shape)}, xs {xs1.numel()}, ws {ws1.numel()}")
+    y = torch.empty((M, N), dtype=torch.bfloat16, device=x8.device)
+    check(_lib.lib().spinf_int8_rowwise_gemm(ptr(x8), ptr(xs1), ptr(w8), ptr(ws1), ptr(y), M, N, K, stream_ptr()), "spinf_int8_rowwise_gemm")
+    COUNTS["launches"] += 1
+    return y
+
+
 def w4_gemm(x, qw, scales, group, extra=None):
     """y [M, N (+ E)] bf16 = x [M, K] bf16 @ dq(qw, scales)^T, with E un-quantised bf16 output channels `extra` [E, K] appended
     (Int4Linear.forward in bf16 mode, spinf_serve/models/qwen35/qwen.py:455-458); qw uint8 [N, K/2], scales fp16 [N, K/group]"""

@@ -1,11 +1,12 @@
-"""Writes tests/golden/fp8_tensor_golden.npz: inputs and outputs of the reference's own per-tensor fp8 linears run on the CPU.
+"""Writes tests/golden/fp8_tensor_golden.npz: inputs and outputs of the reference's own per-tensor fp8 and int8 linears run on the CPU.
 
     TORCHDYNAMO_DISABLE=1 python tests/golden/make_fp8_golden.py <path of the reference checkout>
 
 Fp8Linear and Fp8StaticLinear (spinf_serve/quant/linears.py:66-116) are built by the reference's quant_linears and called as the
 reference calls them; torch._scaled_mm with per-tensor scales has a CPU kernel, so nothing is restated. TORCHDYNAMO_DISABLE makes
 the reference's torch.compile decorators run their functions eagerly (the arithmetic is the same ops). The static scale comes from
-the reference's calibration rule restated in one line (quant/calibrate.py:176-177; its main() needs a model and a GPU)."""
+the reference's calibration rule restated in one line (quant/calibrate.py:176-177; its main() needs a model and a GPU).
+Int8Linear (linears.py:40-64) in both modes: torch._int_mm has a CPU kernel (the reference pads to 17 rows itself)."""
 
 import math
 import os
@@ -46,6 +47,10 @@ def main(ref_root):
         out[f"xs{i}"] = np.float32(xs).reshape(1)
         out[f"y_dyn{i}"], out[f"y_sta{i}"] = bits(y_dyn), bits(y_sta)
         out[f"peak{i}"] = sta.peak.numpy().reshape(1)
+        i8a, i8w = ns.Int8Linear(w, True), ns.Int8Linear(w, False)
+        out[f"i8_w8_{i}"] = i8a.w8t.t().contiguous().numpy()
+        out[f"i8_ws{i}"] = i8a.ws.numpy()
+        out[f"y_i8a{i}"], out[f"y_i8w{i}"] = bits(i8a(x)), bits(i8w(x))
     np.savez_compressed(os.path.join(os.path.dirname(os.path.abspath(__file__)), "fp8_tensor_golden.npz"), **out)
     print("cases", len(cases), "peaks", [float(out[f"peak{i}"][0]) for i in range(len(cases))])
 

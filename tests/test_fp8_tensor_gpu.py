@@ -107,3 +107,50 @@ def test_static_rows_do_not_depend_on_the_stream(dev):
         assert torch.equal(sta(x[:M].contiguous()), full[:M])
     dyn = ns.Fp8Linear(w)
     assert not torch.equal(dyn(x[:300].contiguous()), dyn(x)[:300])
+
+
+@pytest.mark.parametrize("M,K", [(1, 64), (7, 3840), (300, 15360)])
+def test_int8_quant_bit_exact(dev, M, K):
+    from spinf_serve_b200 import ops
+
+    x = _rand((M, K), 1, 3.0)
+    x[0, :8] = 0
+    if M > 2:
+        x[2] = 0  # an all-zero row: the scale clamps at 1e-12 / 127
+    x8, xs = ops.int8_rowwise_quant(x.to(dev))
+    r8, rs = O.quant_act_int8(x)
+    assert torch.equal(xs.cpu(), rs) and torch.equal(x8.cpu(), r8)
+
+
+def test_int8_linear_matches_the_reference_outputs(dev):
+    """Int8Linear on the int8 tensor cores against the reference's own module outputs (CPU run): the integer product is exact and
+    the scaling is the same two fp32 multiplications, so the w8a8 outputs are the same bits"""
+    from spinf_serve_b200 import linears, ops
+
+    ns = linears.quant_linears(None, dev)
+    for i in range(3):
+        w, x = bf16(G[f"w{i}"]), bf16(G[f"x{i}"])
+        w8, ws = torch.from_numpy(G[f"i8_w8_{i}"]), torch.from_numpy(G[f"i8_ws{i}"])
+        x8, xs = ops.int8_rowwise_quant(x.to(dev))
+        y = ops.int8_rowwise_gemm(x8, xs, w8.to(dev), ws.to(dev)).cpu()
+        assert torch.equal(y, bf16(G[f"y_i8a{i}"]))
+        a8, a16 = ns.Int8Linear(w.to(dev), True), ns.Int8Linear(w.to(dev), False)
+        # the module quantises its weight on the device (the scale's last bit may differ from the CPU's, see above)
+        ya, ra = a8(x.to(dev)).cpu().float(), bf16(G[f"y_i8a{i}"]).float()
+        # (a weight that moves by one int8 step moves an output by about |x| * scale: an absolute term, not a relative one)
+        assert (ya != ra).float().mean().item() < 0.05 and bool(((ya - ra).abs() <= ra.abs() * 2.0**-6 + ra.abs().max() * 2.0**-8).all())
+        yw, rw = a16(x.to(dev)).cpu().float(), bf16(G[f"y_i8w{i}"]).float()
+        assert bool(((yw - rw).abs() <= rw.abs() * 2.0**-6 + rw.abs().max() * 2.0**-12).all())
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 256, 128), (130, 512, 384), (640, 3840, 4096), (200, 3840, 15360)])
+def test_int8_gemm_exact(dev, M, N, K):
+    """every output equals the oracle's: int32 accumulation has no summation order (|sum| < 2^31 at these K)"""
+    from spinf_serve_b200 import ops
+
+    x, w = _rand((M, K), 2), _rand((N, K), 3, 0.02)
+    w8, ws = O.quantize_weight_int8(w)
+    x8, xs = O.quant_act_int8(x)
+    y = ops.int8_rowwise_gemm(x8.to(dev), xs.to(dev), w8.to(dev), ws.to(dev)).cpu()
+    acc = (x8.long() @ w8.long().t()).to(torch.int32)
+    assert torch.equal(y, (acc.float() * xs * ws).to(torch.bfloat16))

@@ -67,3 +67,15 @@ def test_product_side_host_logic():
             make()
     with pytest.raises(RuntimeError):
         GS.GemmaWeights(GS.GemmaConfig(layers=0), None, None, [], scheme="int8")
+
+
+def test_int8_linear_matches_the_reference_outputs():
+    """the oracle's Int8Linear (both modes) against the reference's own module run on the CPU: integer accumulation is exact, so
+    the w8a8 outputs are the same bits; the w8a16 mode is a bf16 matmul (summation order may move a last bit)"""
+    for i in range(3):
+        w, x = bf16(G[f"w{i}"]), bf16(G[f"x{i}"])
+        w8, ws = O.quantize_weight_int8(w)
+        assert np.array_equal(w8.numpy(), G[f"i8_w8_{i}"]) and np.array_equal(ws.numpy(), G[f"i8_ws{i}"])
+        assert torch.equal(O.int8_linear(x, w8, ws, True), bf16(G[f"y_i8a{i}"]))
+        mine, ref = O.int8_linear(x, w8, ws, False), bf16(G[f"y_i8w{i}"])
+        assert bool(((mine.float() - ref.float()).abs() <= ref.float().abs() * 2.0**-7 + 1e-30).all())
