@@ -142,3 +142,30 @@ def test_row_maxima_of_the_output_come_with_it(dev):
         amax = torch.zeros(b.length, dtype=torch.float32, device=dev)
         out = A.tree_attention(q.to(dev), k.to(dev), v.to(dev), masks["full_attention"], D**-0.5, row_amax=amax)
         assert torch.equal(amax, out.float().abs().amax(dim=(1, 2)))
+
+
+@pytest.mark.parametrize("H,Hkv", [(2, 2), (2, 1)])
+def test_very_long_stream_takes_the_unsorted_walk_with_the_same_bits(dev, H, Hkv):
+    """beyond 2048 query blocks the kernel walks the stream in natural order instead of ranking blocks by cost: the order only moves
+    whole items between CTAs, so a job's rows are the same bits inside a 2100-block stream as alone (one CTA each, and CTA pairs)"""
+    from spinf_serve_b200 import attention as A
+
+    nb, D = 2100, 128
+    lens = np.where(np.arange(nb) % 3 == 0, 256, 128)  # jobs of one or two blocks, causal inside a job
+    lens = lens[np.cumsum(lens) <= nb * 128]
+    n = int(lens.sum())
+    assert n // 128 > 2048
+    start = np.concatenate(([0], np.cumsum(lens)[:-1]))
+    art = np.repeat(np.arange(len(lens)), lens).astype(np.int32)
+    end = np.repeat(start + lens, lens).astype(np.int32)
+    pos = (np.arange(n) - np.repeat(start, lens)).astype(np.int32)
+    g = torch.Generator().manual_seed(3)
+    q = torch.randn((n, H, D), generator=g).to(torch.bfloat16).to(dev)
+    k = torch.randn((n, Hkv, D), generator=g).to(torch.bfloat16).to(dev)
+    v = torch.randn((n, Hkv, D), generator=g).to(torch.bfloat16).to(dev)
+    full = A.tree_attention(q, k, v, A.stream_masks(art, end, pos, None, dev)["full_attention"], D**-0.5)
+    for j in (0, 1, 700, len(lens) - 1):
+        a, e = int(start[j]), int(start[j] + lens[j])
+        m = A.stream_masks(np.zeros(e - a, np.int32), np.full(e - a, e - a, np.int32), pos[a:e], None, dev)["full_attention"]
+        alone = A.tree_attention(q[a:e].contiguous(), k[a:e].contiguous(), v[a:e].contiguous(), m, D**-0.5)
+        assert torch.equal(alone, full[a:e])
