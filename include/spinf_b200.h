@@ -133,12 +133,18 @@ int spinf_bf16_gemm_ld(const void* x, const void* w, void* y, int64_t M, int64_t
 /* ------------------------------------------------------------------------------------------------------------ int4 weight-only linear
  * Replaces Int4Linear.forward in bf16 mode (spinf_serve/models/qwen35/qwen.py:455-458) with its per-call dequantisation dq_bf16
  * (qwen.py:326-330):  y[m,n] = bf16( sum_k x[m,k] * w[n,k] ),  w[n,k] = bf16( (nibble(n,k) - 8) * float(scales[n, k / group]) ).
- * x [M,K] bf16; qw uint8 [N, K/2] in the reference's engine layout (low nibble = even k, qwen.py:383-389); scales fp16
+ * x [M,K] bf16; qw uint8 [N, K/2] as spinf_w4_repack leaves it (below); scales fp16
  * [N, K/group]; y bf16 with row pitch y_pitch elements. The bf16 weight matrix is never materialised: nibbles are expanded inside
  * the kernel on their way to the tensor core. K a multiple of 64 and of group, group a multiple of 8 (128 in the BASELINE
  * configuration, 32 in the reference's checkpoints), N a multiple of 8. A row of y does not depend on M. */
 int spinf_w4_gemm(const void* x, const void* qw, const void* scales, int32_t group, void* y, int64_t M, int64_t N, int64_t K,
                   int64_t y_pitch, void* stream);
+
+/* Load-time re-ordering of the packed int4 weights for spinf_w4_gemm. q_in: uint8 [N, K/2] in the reference's engine layout (byte b
+ * of a row = k 2b in the low nibble, k 2b+1 in the high nibble: the `q` buffer of Int4Linear, qwen.py:383-389). q_out (may be
+ * q_in): per 32-bit word of 8 consecutive k, the even k in nibbles 0..3 and the odd k in nibbles 4..7, so that the kernel takes a
+ * pair (k, k+1) out of a word with one shift and one mask. Both 4-byte aligned, K a multiple of 8. */
+int spinf_w4_repack(const void* q_in, void* q_out, int64_t N, int64_t K, void* stream);
 
 /* ------------------------------------------------------------------------------------------------------------ option log-probs
  * Replaces Scorer._logprobs followed by the `[:, ci]` gather (spinf_serve/scorer.py:340-355 and :254): for read rows h [R,hidden]

@@ -14,8 +14,8 @@
 //   warp 0     one lane: TMA loads of this CTA's half of the activation tile (128 tokens x 128 B, swizzled; completes on the
 //              leader's barrier) and raw weight tile (128 rows x 32 B; completes on this CTA's barrier) into an 8-stage ring
 //   warps 6-13 dequantisers in two groups of four warps that take alternate K steps, thread = weight row = TMEM lane:
-//              64 nibbles -> 64 bf16 (32 packed columns of the stage's slot in tensor memory); a nibble becomes the float
-//              128 + n with one byte permute, then one FMA gives (n - 8) * scale exactly
+//              64 nibbles -> 64 bf16 (32 packed columns of the stage's slot in tensor memory), two weights per instruction in
+//              packed bf16 arithmetic that rounds the exact product (n - 8) * scale once (see the loop)
 //   warp 1     leader only, one lane: tcgen05.mma (A from tensor memory), 4 x (M=256, N=256, K=16) per step, and one commit per
 //              step (multicast to both CTAs) that frees the stage for the loader and the dequantisers alike
 //   warps 2-5  epilogue: TMEM -> bf16 -> transposed into swizzled staging (lane pairs exchange so that every store is a pair of
@@ -190,7 +190,14 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const bool n_ok = n < a.N;
       const __half* srow = a.scales + static_cast<int64_t>(n_ok ? n : 0) * groups;
       int s_idx = -1;
-      float sc = 0.f, off = 0.f;
+      uint32_t s_hi2 = 0u, s_lo2 = 0u;  // the group's scale as two packed bf16 pairs: its top 8 significant bits and the rest
+      auto load_scale = [&](int gi) {
+        // a half-precision scale has 11 significant bits: the bf16 truncation keeps 8, the remainder (at most 3 bits) is a bf16 too
+        const float sc = n_ok ? __half2float(srow[gi]) : 0.f;
+        const uint32_t hi = __float_as_uint(sc) >> 16;
+        const uint32_t lo = __float_as_uint(sc - __uint_as_float(hi << 16)) >> 16;
+        s_hi2 = hi | (hi << 16), s_lo2 = lo | (lo << 16);
+      };
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         if ((it & 1u) != static_cast<uint32_t>(grp)) continue;
         const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
@@ -205,8 +212,7 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const int gi = (kb * 64) / a.G;
           if (gi != s_idx) {
             s_idx = gi;
-            sc = n_ok ? __half2float(srow[gi]) : 0.f;
-            off = -136.f * sc;  // exact: 136 has 5 significant bits, a half-precision scale 11
+            load_scale(gi);
           }
         }
 #pragma unroll
@@ -215,19 +221,18 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const int gi = (kb * 64 + c * 8) / a.G;
             if (gi != s_idx) {
               s_idx = gi;
-              sc = n_ok ? __half2float(srow[gi]) : 0.f;
-              off = -136.f * sc;
+              load_scale(gi);
             }
           }
-          const uint32_t even = words[c] & 0x0F0F0F0Fu;         // nibbles 0, 2, 4, 6 (k even), one per byte
-          const uint32_t odd = (words[c] >> 4) & 0x0F0F0F0Fu;   // nibbles 1, 3, 5, 7
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            // bytes [0, 0, nibble, 0x43] = the float 128 + nibble; fma(128 + n, s, -136 s) = (n - 8) s with no rounding
-            // (the product and the sum are exact inside the FMA and the result fits fp32); then one rounding to bf16
-            const float lo = fmaf(__uint_as_float(__byte_perm(even, 0x43000000u, 0x7044u | (j << 8))), sc, off);
-            const float hi = fmaf(__uint_as_float(__byte_perm(odd, 0x43000000u, 0x7044u | (j << 8))), sc, off);
-            out[4 * c + j] = pack_bf16x2(lo, hi);
+            // the word holds its even k in the low half and its odd k in the high half (spinf_w4_repack), so one shift and one
+            // mask-or give the pair (k, k + 1) as the packed bf16 values 128 + nibble (0x4300 | nibble); d = nibble - 8 exactly;
+            // d * s_lo is exact (4 x 3 bits), and fma(d, s_hi, d * s_lo) rounds the exact product d * s once: the reference's
+            // bf16((nibble - 8) * scale), two weights per instruction and no conversion
+            const uint32_t v = ((words[c] >> (4 * j)) & 0x000F000Fu) | 0x43004300u;
+            const uint32_t d = bf2_sub(v, 0x43084308u);
+            out[4 * c + j] = bf2_fma(d, s_hi2, bf2_mul(d, s_lo2));
           }
         }
         tc_fence_after();  // orders the store after the commit that freed the slot
@@ -309,9 +314,37 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
 }
 
+// Load-time re-ordering of the packed weights for the kernel above. In: the reference's engine layout (byte b of a row holds k = 2b
+// in its low nibble and k = 2b + 1 in its high nibble, qwen.py:383-389), read as 32-bit words of 8 consecutive k. Out: the same
+// word with its even k in nibbles 0..3 and its odd k in nibbles 4..7, so that (word >> 4j) & 0x000F000F is the pair (2j, 2j + 1).
+__global__ void __launch_bounds__(256) w4_repack_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out, int64_t n_words) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n_words; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const uint32_t w = in[i];
+    uint32_t r = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      r |= ((w >> (8 * j)) & 0xFu) << (4 * j);             // k = 2j
+      r |= ((w >> (8 * j + 4)) & 0xFu) << (16 + 4 * j);    // k = 2j + 1
+    }
+    out[i] = r;
+  }
+}
+
 }  // namespace spinf
 
 using namespace spinf;
+
+extern "C" int spinf_w4_repack(const void* q_in, void* q_out, int64_t N, int64_t K, void* stream) {
+  SPINF_CHECK_ARG(q_in && q_out && N >= 0 && K > 0 && K % 8 == 0);
+  SPINF_CHECK_ARG((reinterpret_cast<uintptr_t>(q_in) & 3) == 0 && (reinterpret_cast<uintptr_t>(q_out) & 3) == 0);
+  const int64_t n_words = N * (K / 8);
+  if (n_words == 0) return 0;
+  const int64_t blocks = (n_words + 255) / 256, cap = 16ll * sm_count();
+  w4_repack_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint32_t*>(q_in), static_cast<uint32_t*>(q_out), n_words);
+  SPINF_CUDA_OK(cudaGetLastError());
+  return 0;
+}
 
 extern "C" int spinf_w4_gemm(const void* x, const void* qw, const void* scales, int32_t group, void* y, int64_t M, int64_t N, int64_t K,
                              int64_t y_pitch, void* stream) {

@@ -177,7 +177,7 @@ class Int4Linear(nn.Module):
         q, s = gptq_unpack(qweight, scales)
         self.out_features, self.in_features = q.shape[0], q.shape[1] * 2
         self.group = self.in_features // s.shape[1]
-        self.register_buffer("q", q)
+        self.register_buffer("q", ops.w4_repack(q))  # the reference's bytes, nibbles re-ordered inside each 8-k word for the kernel
         self.register_buffer("s", s.to(torch.float16))
         self.extra = None
         self.name = ""

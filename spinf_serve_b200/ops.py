@@ -156,8 +156,21 @@ def int8_rowwise_gemm(x8, xs, w8, ws):
     return y
 
 
+def w4_repack(q):
+    """q uint8 [N, K/2] in the reference's engine layout (low nibble = even k) -> the same bytes re-ordered for w4_gemm (per 8
+    consecutive k: even k in the low half of the 32-bit word, odd k in the high half). Load time, once per weight."""
+    _need(q, torch.uint8, "q", 2)
+    N, K2 = q.shape
+    if (2 * K2) % 8:
+        raise SpinfError("w4_repack: K must be a multiple of 8")
+    out = torch.empty_like(q)
+    check(_lib.lib().spinf_w4_repack(ptr(q), ptr(out), N, 2 * K2, stream_ptr()), "spinf_w4_repack")
+    COUNTS["launches"] += 1
+    return out
+
+
 def w4_gemm(x, qw, scales, group, extra=None):
-    """y [M, N (+ E)] bf16 = x [M, K] bf16 @ dq(qw, scales)^T, with E un-quantised bf16 output channels `extra` [E, K] appended
+    """y [M, N (+ E)] bf16 = x [M, K] bf16 @ dq(qw, scales)^T (qw as w4_repack leaves it), with E un-quantised bf16 output channels `extra` [E, K] appended
     (Int4Linear.forward in bf16 mode, spinf_serve/models/qwen35/qwen.py:455-458); qw uint8 [N, K/2], scales fp16 [N, K/group]"""
     _need(x, torch.bfloat16, "x", 2)
     _need(qw, torch.uint8, "qw", 2)

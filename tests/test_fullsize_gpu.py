@@ -150,12 +150,13 @@ def test_int4_linear_at_the_hybrid_models_widest_shape(dev):
     qw = torch.randint(0, 256, (N, K // 2), generator=g, device=dev, dtype=torch.uint8)
     sc = (torch.rand((N, K // G), generator=g, device=dev) * 0.02 + 0.005).to(torch.float16)
     x = _rand_bf16((M, K), 1, dev)
-    y = ops.w4_gemm(x, qw, sc, G)
+    qk = ops.w4_repack(qw)
+    y = ops.w4_gemm(x, qk, sc, G)
     nib = torch.stack([qw & 15, qw >> 4], dim=-1).reshape(N, K).float() - 8.0
     wd = (nib.view(N, K // G, G) * sc.float()[:, :, None]).reshape(N, K).to(torch.bfloat16)
     ref = ops.bf16_gemm(x, wd)
     assert (y.float() - ref.float()).abs().max() <= 2.0**-6 * ref.float().abs().max()
-    assert torch.equal(ops.w4_gemm(x[:777].contiguous(), qw, sc, G), y[:777])
+    assert torch.equal(ops.w4_gemm(x[:777].contiguous(), qk, sc, G), y[:777])
 
 
 def test_recurrence_forms_agree_at_the_hybrid_models_shape(dev):

@@ -19,6 +19,16 @@ def _gptq(N, K, G, seed):
     return qweight, scales
 
 
+def _repack_host(q):
+    """the layout spinf_w4_repack documents, restated with numpy: per 8 consecutive k (4 bytes), even k in nibbles 0..3, odd k in 4..7"""
+    import numpy as np
+
+    b = q.numpy().reshape(q.shape[0], -1, 4).astype(np.uint32)
+    lo, hi = b & 15, b >> 4  # k = 2j, k = 2j + 1 of byte j
+    w = sum(lo[..., j] << (4 * j) for j in range(4)) | sum(hi[..., j] << (16 + 4 * j) for j in range(4))
+    return torch.from_numpy(w.astype("<u4").view(np.uint8).reshape(q.shape[0], -1).copy())
+
+
 @pytest.mark.parametrize("M,N,K,G,E", [(256, 128, 64, 32, 0), (1, 256, 128, 128, 0), (300, 384, 512, 128, 64), (700, 5120, 4096, 128, 0), (130, 1024, 5120, 32, 64),
                                        (77, 200, 192, 64, 0), (513, 72, 128, 128, 0)])
 def test_w4_linear_vs_oracle(dev, M, N, K, G, E):
@@ -31,7 +41,7 @@ def test_w4_linear_vs_oracle(dev, M, N, K, G, E):
     lin = Int4Linear(qweight.to(dev), scales.to(dev))
     assert lin.group == G and (lin.out_features, lin.in_features) == (N, K)
     q, s = O.gptq_unpack(qweight, scales)
-    assert torch.equal(lin.q.cpu(), q) and torch.equal(lin.s.cpu(), s)
+    assert torch.equal(lin.q.cpu(), _repack_host(q)) and torch.equal(lin.s.cpu(), s)  # the oracle's bytes, re-ordered for the kernel
     if E:
         lin.set_extra(extra.to(dev))
     y = lin(x.to(dev)).cpu()
@@ -50,8 +60,25 @@ def test_w4_rows_do_not_depend_on_M(dev):
 
     qweight, scales = _gptq(512, 1024, 128, 3)
     q, s = O.gptq_unpack(qweight, scales)
-    q, s = q.to(dev), s.to(dev)
+    q, s = ops.w4_repack(q.to(dev)), s.to(dev)
     x = torch.randn((1000, 1024), generator=torch.Generator().manual_seed(4)).to(torch.bfloat16).to(dev)
     full = ops.w4_gemm(x, q, s, 128)
     for M in (1, 255, 256, 257):
         assert torch.equal(ops.w4_gemm(x[:M].contiguous(), q, s, 128), full[:M])
+
+
+@pytest.mark.parametrize("G", [32, 64, 128])
+def test_w4_expansion_is_the_reference_dequantisation_bit_for_bit(dev, G):
+    """x = identity reads the expanded weight back through the GEMM: every element equals dq_bf16's (nibble - 8) * scale rounded once
+    to bf16, for all 16 nibble values under scales that use all 11 significant bits of half precision (and subnormal ones)"""
+    from spinf_serve_b200 import ops
+
+    N, K = 512, 256
+    g = torch.Generator().manual_seed(7)
+    qweight, _ = _gptq(N, K, G, 9)
+    scales = torch.randint(1, 0x7BFF, (K // G, N), generator=g, dtype=torch.int16).view(torch.float16)  # every positive finite pattern
+    scales[0, :8] = torch.tensor([6e-8, 1e-7, 5.96e-8, 6.1e-5, 1.0, 0.333, 65504.0, 3e-5]).to(torch.float16)
+    q, s = O.gptq_unpack(qweight, scales)
+    y = ops.w4_gemm(torch.eye(K, dtype=torch.bfloat16, device=dev), ops.w4_repack(q.to(dev)), s.to(dev), G).cpu()
+    want = O.dq_bf16(q, s, G).t()
+    assert torch.equal(y.view(torch.int16), want.contiguous().view(torch.int16))
