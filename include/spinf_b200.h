@@ -146,6 +146,15 @@ int spinf_w4_gemm(const void* x, const void* qw, const void* scales, int32_t gro
  * pair (k, k+1) out of a word with one shift and one mask. Both 4-byte aligned, K a multiple of 8. */
 int spinf_w4_repack(const void* q_in, void* q_out, int64_t N, int64_t K, void* stream);
 
+/* The gate|up projection of a gated MLP with its activation in the GEMM epilogue: replaces Int4Linear.forward on the fused gate_up
+ * weight followed by act(gate) * up (spinf_serve/models/qwen35/qwen.py:455-458 and the MLP around it, :700-712):
+ *   y[m,c] = bf16( bf16(act(g)) * u ),  g = bf16(sum_k x[m,k] w[2c,k]),  u = bf16(sum_k x[m,k] w[2c+1,k]),   c < N2 / 2,
+ * act = 0: GELU (tanh form), 1: SiLU. qw / scales hold the N2 = 2F rows INTERLEAVED (row 2c = gate channel c, row 2c+1 = up channel
+ * c), each row as spinf_w4_repack leaves it. y [M, N2/2] bf16 with row pitch y_pitch. Other rules as spinf_w4_gemm; N2 a multiple
+ * of 16. The [M, N2] intermediate is never written. */
+int spinf_w4_gemm_glu(const void* x, const void* qw, const void* scales, int32_t group, int32_t act, void* y, int64_t M, int64_t N2,
+                      int64_t K, int64_t y_pitch, void* stream);
+
 /* ------------------------------------------------------------------------------------------------------------ option log-probs
  * Replaces Scorer._logprobs followed by the `[:, ci]` gather (spinf_serve/scorer.py:340-355 and :254): for read rows h [R,hidden]
  * bf16 and the lm-head matrix W [vocab,hidden] bf16,

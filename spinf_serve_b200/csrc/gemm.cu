@@ -88,7 +88,7 @@ struct EpiGlu {
   };
   __device__ __forceinline__ static float act(float x) {
     if (ACT == 0) return gelu_tanh_f32(x);
-    return x / (1.f + expf(-x));
+    return silu_f32(x);
   }
   __device__ __forceinline__ void begin_tile(State& st, const GemmShape& s, int tm, int tn, int et, float* colscale) const {
     named_bar_sync(2, 128);

@@ -335,7 +335,7 @@ enum : int { ACT_GELU_TANH = 0, ACT_SILU = 1 };
 template <int ACT>
 __device__ __forceinline__ float act_fn(float x) {
   if (ACT == ACT_GELU_TANH) return gelu_tanh_f32(x);
-  return x / (1.f + expf(-x));
+  return silu_f32(x);
 }
 
 // gu [n, 2F]: gate = columns [0, F), up = columns [F, 2F). y = bf16(bf16(act(gate)) * up); then the per-row fp8 quantisation of y

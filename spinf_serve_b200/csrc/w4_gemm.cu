@@ -53,6 +53,11 @@ struct W4Args {
 __device__ unsigned long long g_w4_trace[8];
 #endif
 
+// ACT: -1 = plain linear; 0 / 1 = gated linear unit in the epilogue (GELU-tanh / SiLU): the weight rows are interleaved at load
+// time (row 2c = gate channel c, row 2c + 1 = up channel c), so a lane pair of the epilogue holds a channel's gate and up values
+// and writes y[m, c] = bf16(bf16(act(bf16 gate)) * bf16 up): the arithmetic of the linear followed by the gated-activation pass,
+// without the [M, 2F] intermediate.
+template <int ACT>
 __global__ void __launch_bounds__(448, 1)
 w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmC,
                const W4Args a, int* __restrict__ status) {
@@ -277,26 +282,63 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         // transpose through the lane pair: the even lane keeps token 2 i of both channels, the odd lane token 2 i + 1
         uint32_t packed[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const uint32_t e = i < 16 ? v0[2 * i] : v1[2 * i - 32], o = i < 16 ? v0[2 * i + 1] : v1[2 * i - 31];
-          const uint32_t other = __shfl_xor_sync(0xffffffffu, odd ? e : o, 1);
-          packed[i] = odd ? pack_bf16x2(__uint_as_float(other), __uint_as_float(o)) : pack_bf16x2(__uint_as_float(e), __uint_as_float(other));
-        }
         uint8_t* buf = smem + L::EPI_OFF + (nchunks & 1u) * L::EPI_BYTES;
+        if (ACT < 0) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const uint32_t e = i < 16 ? v0[2 * i] : v1[2 * i - 32], o = i < 16 ? v0[2 * i + 1] : v1[2 * i - 31];
+            const uint32_t other = __shfl_xor_sync(0xffffffffu, odd ? e : o, 1);
+            packed[i] = odd ? pack_bf16x2(__uint_as_float(other), __uint_as_float(o)) : pack_bf16x2(__uint_as_float(e), __uint_as_float(other));
+          }
+        } else {
+          // the lane pair is (gate, up) of one output channel: after the exchange both values of token 2 i + odd are here
+          float yv[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const uint32_t e = i < 16 ? v0[2 * i] : v1[2 * i - 32], o = i < 16 ? v0[2 * i + 1] : v1[2 * i - 31];
+            const uint32_t other = __shfl_xor_sync(0xffffffffu, odd ? e : o, 1);
+            const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(odd ? other : e)));
+            const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(odd ? o : other)));
+            const float act = ACT == 0 ? gelu_tanh_f32(g) : silu_f32(g);
+            yv[i] = __bfloat162float(__float2bfloat16_rn(act)) * u;  // the product of two bf16 values is exact in fp32: rounded by the pack
+          }
+          // second exchange, with the neighbouring channel's lane pair: even channels keep their even i, odd channels their odd i
+          const bool oddc = (lane & 2u) != 0u;
+#pragma unroll
+          for (int h = 0; h < 16; ++h) {
+            const float keep = oddc ? yv[2 * h + 1] : yv[2 * h], send = oddc ? yv[2 * h] : yv[2 * h + 1];
+            const float other = __shfl_xor_sync(0xffffffffu, send, 2);
+            packed[h] = oddc ? pack_bf16x2(other, keep) : pack_bf16x2(keep, other);
+          }
+        }
         if (et == 0) tma_store_wait_read<1>();  // the store that last read this buffer (two chunks ago) has finished reading
         named_bar_sync(1, 128);
+        if (ACT < 0) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const uint32_t tok = 2 * i + odd;
-          *reinterpret_cast<uint32_t*>(buf + hb * 8192 + sw128_offset(tok, ch2 >> 3) + (ch2 & 7) * 2) = packed[i];
+          for (int i = 0; i < 32; ++i) {
+            const uint32_t tok = 2 * i + odd;
+            *reinterpret_cast<uint32_t*>(buf + hb * 8192 + sw128_offset(tok, ch2 >> 3) + (ch2 & 7) * 2) = packed[i];
+          }
+        } else {
+          const int oc2 = (ch >> 1) & ~1;  // the even one of the two output channels this lane writes, within the CTA's 64
+#pragma unroll
+          for (int h = 0; h < 16; ++h) {
+            const uint32_t tok = 2 * (2 * h + ((lane >> 1) & 1u)) + odd;
+            *reinterpret_cast<uint32_t*>(buf + sw128_offset(tok, oc2 >> 3) + (oc2 & 7) * 2) = packed[h];
+          }
         }
         fence_proxy_async_smem();
         named_bar_sync(1, 128);
         if (et == 0) {
-          const int n0 = tn * 256 + static_cast<int>(rank) * 128, m0 = tm * 256 + c * 64;
-          if (m0 < a.M && n0 < a.N) tma_store_2d(&tmC, buf, n0, m0);  // boxes that lie wholly outside the output are skipped,
-          if (m0 < a.M && n0 + 64 < a.N) tma_store_2d(&tmC, buf + 8192, n0 + 64, m0);  // partial ones are clipped by the copy
+          const int m0 = tm * 256 + c * 64;
+          if (ACT < 0) {
+            const int n0 = tn * 256 + static_cast<int>(rank) * 128;
+            if (m0 < a.M && n0 < a.N) tma_store_2d(&tmC, buf, n0, m0);  // boxes that lie wholly outside the output are skipped,
+            if (m0 < a.M && n0 + 64 < a.N) tma_store_2d(&tmC, buf + 8192, n0 + 64, m0);  // partial ones are clipped by the copy
+          } else {
+            const int f0 = tn * 128 + static_cast<int>(rank) * 64;  // 128 interleaved weight rows = 64 output channels
+            if (m0 < a.M && f0 < a.N / 2) tma_store_2d(&tmC, buf, f0, m0);
+          }
           tma_store_commit();
         }
       }
@@ -346,10 +388,12 @@ extern "C" int spinf_w4_repack(const void* q_in, void* q_out, int64_t N, int64_t
   return 0;
 }
 
-extern "C" int spinf_w4_gemm(const void* x, const void* qw, const void* scales, int32_t group, void* y, int64_t M, int64_t N, int64_t K,
-                             int64_t y_pitch, void* stream) {
+template <int ACT>
+static int launch_w4(const void* x, const void* qw, const void* scales, int32_t group, void* y, int64_t M, int64_t N, int64_t K,
+                     int64_t y_pitch, void* stream) {
+  const int64_t n_out = ACT < 0 ? N : N / 2;
   SPINF_CHECK_ARG(x && qw && scales && y && M >= 0 && N > 0 && K > 0 && group > 0);
-  SPINF_CHECK_ARG(K % 64 == 0 && group % 8 == 0 && K % group == 0 && N % 8 == 0 && y_pitch >= N && y_pitch % 8 == 0);
+  SPINF_CHECK_ARG(K % 64 == 0 && group % 8 == 0 && K % group == 0 && N % (ACT < 0 ? 8 : 16) == 0 && y_pitch >= n_out && y_pitch % 8 == 0);
   SPINF_CHECK_ARG(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31));
   if (M == 0) return 0;
   int dev = 0;
@@ -360,7 +404,7 @@ extern "C" int spinf_w4_gemm(const void* x, const void* qw, const void* scales, 
   int r;
   if ((r = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, M, K, K * 2, 64, 128))) return r;
   if ((r = make_tmap_2d_plain(&tmW, qw, N, K / 2, K / 2, 32, 128))) return r;
-  if ((r = make_tmap_2d(&tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y, M, N, y_pitch * 2, 64, 64))) return r;
+  if ((r = make_tmap_2d(&tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y, M, n_out, y_pitch * 2, 64, 64))) return r;
   W4Args a;
   a.scales = static_cast<const __half*>(scales);
   a.M = static_cast<int>(M), a.N = static_cast<int>(N), a.K = static_cast<int>(K), a.G = group;
@@ -373,9 +417,10 @@ extern "C" int spinf_w4_gemm(const void* x, const void* qw, const void* scales, 
     const int64_t g = (32ll << 20) / per_tile;
     a.group_m = static_cast<int>(g < 4 ? 4 : (g > 32 ? 32 : g));
   }
+  auto kern = w4_gemm_kernel<ACT>;
   static bool attr_set[64] = {false};
   if (!attr_set[dev]) {
-    SPINF_CUDA_OK(cudaFuncSetAttribute(w4_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, W4Smem::TOTAL));
+    SPINF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, W4Smem::TOTAL));
     attr_set[dev] = true;
   }
   const int tiles = a.tiles_m * a.tiles_n;
@@ -392,9 +437,21 @@ extern "C" int spinf_w4_gemm(const void* x, const void* qw, const void* scales, 
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  SPINF_CUDA_OK(cudaLaunchKernelEx(&cfg, w4_gemm_kernel, tmA, tmW, tmC, a, status));
+  SPINF_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, tmA, tmW, tmC, a, status));
   SPINF_CUDA_OK(cudaGetLastError());
   return 0;
+}
+
+extern "C" int spinf_w4_gemm(const void* x, const void* qw, const void* scales, int32_t group, void* y, int64_t M, int64_t N, int64_t K,
+                             int64_t y_pitch, void* stream) {
+  return launch_w4<-1>(x, qw, scales, group, y, M, N, K, y_pitch, stream);
+}
+
+extern "C" int spinf_w4_gemm_glu(const void* x, const void* qw, const void* scales, int32_t group, int32_t act, void* y, int64_t M,
+                                 int64_t N2, int64_t K, int64_t y_pitch, void* stream) {
+  SPINF_CHECK_ARG(act == 0 || act == 1);
+  return act == 0 ? launch_w4<0>(x, qw, scales, group, y, M, N2, K, y_pitch, stream)
+                  : launch_w4<1>(x, qw, scales, group, y, M, N2, K, y_pitch, stream);
 }
 
 #ifdef SPINF_TRACE

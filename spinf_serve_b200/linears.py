@@ -180,7 +180,20 @@ class Int4Linear(nn.Module):
         self.register_buffer("q", ops.w4_repack(q))  # the reference's bytes, nibbles re-ordered inside each 8-k word for the kernel
         self.register_buffer("s", s.to(torch.float16))
         self.extra = None
+        self.glu = None
         self.name = ""
+
+    def fuse_glu(self, act: str):
+        """for a fused gate|up projection (gate channels first, then up): from now on forward returns act(gate) * up [.., out/2],
+        computed in the GEMM's epilogue. The rows are interleaved once, here (gate c, up c, gate c + 1, ...), which is the order the
+        kernel's lane pairs read them in; the values are those of forward followed by the gated-activation pass."""
+        if self.extra is not None or self.glu is not None or self.out_features % 16:
+            raise RuntimeError("fuse_glu: a plain fused gate|up projection with an output width that is a multiple of 16")
+        F = self.out_features // 2
+        order = torch.stack((torch.arange(F), torch.arange(F) + F), dim=1).reshape(-1).to(self.q.device)
+        self.q, self.s = self.q[order].contiguous(), self.s[order].contiguous()
+        self.glu = act
+        return self
 
     def set_extra(self, w):
         """bf16 rows [E, in] appended to the output (the Gated DeltaNet's b / a projections)"""
@@ -189,5 +202,8 @@ class Int4Linear(nn.Module):
 
     def forward(self, x):
         x2 = x.reshape(-1, x.shape[-1])
+        if self.glu is not None:
+            y = ops.w4_gemm_glu(x2 if x2.is_contiguous() else x2.contiguous(), self.q, self.s, self.group, self.glu)
+            return y.reshape(*x.shape[:-1], y.shape[-1])
         y = ops.w4_gemm(x2 if x2.is_contiguous() else x2.contiguous(), self.q, self.s, self.group, self.extra)
         return y.reshape(*x.shape[:-1], y.shape[-1])

@@ -169,6 +169,23 @@ def w4_repack(q):
     return out
 
 
+def w4_gemm_glu(x, qw, scales, group, act="silu"):
+    """y [M, F] bf16 = act(gate) * up of the fused gate|up int4 projection, the activation inside the GEMM epilogue: qw [2F, K/2]
+    and scales [2F, K/group] hold the rows interleaved (2c = gate channel c, 2c + 1 = up channel c), each row as w4_repack leaves it"""
+    _need(x, torch.bfloat16, "x", 2)
+    _need(qw, torch.uint8, "qw", 2)
+    _need(scales, torch.float16, "scales", 2)
+    M, K = x.shape
+    N2 = qw.shape[0]
+    if qw.shape[1] * 2 != K or scales.shape[0] != N2 or N2 % 16:
+        raise SpinfError(f"w4_gemm_glu: shapes do not agree: x {tuple(x.shape)}, qw {tuple(qw.shape)}, scales {tuple(scales.shape)}")
+    y = torch.empty((M, N2 // 2), dtype=torch.bfloat16, device=x.device)
+    code = {"gelu_tanh": 0, "silu": 1}[act]
+    check(_lib.lib().spinf_w4_gemm_glu(ptr(x), ptr(qw), ptr(scales), group, code, ptr(y), M, N2, K, N2 // 2, stream_ptr()), "spinf_w4_gemm_glu")
+    COUNTS["launches"] += 1
+    return y
+
+
 def w4_gemm(x, qw, scales, group, extra=None):
     """y [M, N (+ E)] bf16 = x [M, K] bf16 @ dq(qw, scales)^T (qw as w4_repack leaves it), with E un-quantised bf16 output channels `extra` [E, K] appended
     (Int4Linear.forward in bf16 mode, spinf_serve/models/qwen35/qwen.py:455-458); qw uint8 [N, K/2], scales fp16 [N, K/group]"""

@@ -49,8 +49,10 @@ class QwenWeights:
     "gate_up", "down", and per kind "in_proj" / "in_extra" / "out_proj" / "conv_w" / "A_log" / "dt_bias" / "gdn_norm" or
     "qkv_proj" / "o_proj" / "q_norm" / "k_norm"}]}; int4 linears are (qweight int32 [K/8, N], scales fp16 [K/G, N]) pairs"""
 
-    def __init__(self, cfg: QwenConfig, W, device):
+    def __init__(self, cfg: QwenConfig, W, device, fuse_glu: bool = True):
+        """fuse_glu: the MLP's SiLU(gate) * up inside the gate|up GEMM's epilogue (the same values as the separate pass)"""
         self.cfg = cfg
+        self.fuse_glu = fuse_glu
         dev = torch.device(device)
         self.embed = W["embed"].to(dev).contiguous()
         self.lm_head = W["lm_head"].to(dev).contiguous()
@@ -69,6 +71,8 @@ class QwenWeights:
                     out[k] = v.to(dev).contiguous()
             if "in_extra" in out:
                 out["in_proj"].set_extra(out.pop("in_extra"))  # the b and a rows ride in the same output (qwen.py:421-426)
+            if fuse_glu:
+                out["gate_up"].fuse_glu("silu")
             self.layers.append(out)
 
     @property
@@ -166,7 +170,10 @@ class QwenStack:
                 m = L["o_proj"](o.view(n, H * D))
             r = ops.fused_norm(m, residual=x, w2=L["post_ln"], eps=cfg.eps, plus1=True, want_h=True, want_norm=True)
             x = r["h"]
-            _, _, act = ops.glu_quant(L["gate_up"](r["norm"]), "silu", want_fp8=False, want_y=True)
+            if w.fuse_glu:
+                act = L["gate_up"](r["norm"])
+            else:
+                _, _, act = ops.glu_quant(L["gate_up"](r["norm"]), "silu", want_fp8=False, want_y=True)
             d = L["down"](act)
             last = i == self.n_layers - 1
             r = ops.fused_norm(d, residual=x, w2=None if last else w.layers[i + 1]["input_ln"], eps=cfg.eps, plus1=True, want_h=True,

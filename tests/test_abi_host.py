@@ -45,6 +45,8 @@ def test_argument_errors_are_reported_on_the_host():
     assert lib.spinf_bf16_gemm_ld(p, p, p, 4, 128, 64, 64, NULL) == -1          # pitch smaller than N
     assert lib.spinf_w4_gemm(p, p, p, 128, p, 4, 128, 100, 128, NULL) == -1     # K not a multiple of 64
     assert lib.spinf_w4_gemm(p, p, p, 12, p, 4, 128, 128, 128, NULL) == -1      # group not a multiple of 8
+    assert lib.spinf_w4_gemm_glu(p, p, p, 128, 2, p, 4, 128, 128, 64, NULL) == -1  # activation code
+    assert lib.spinf_w4_gemm_glu(p, p, p, 128, 1, p, 4, 136, 128, 72, NULL) == -1  # 2F not a multiple of 16
     assert lib.spinf_w4_repack(p, p, 4, 100, NULL) == -1                        # K not a multiple of 8
     assert lib.spinf_w4_repack(ctypes.c_void_p(18), p, 4, 128, NULL) == -1      # not 4-byte aligned
     assert lib.spinf_fp8_rowwise_gemm_glu(p, p, p, p, p, p, 4, 100, 64, 0, NULL) == -1  # F not a multiple of 128

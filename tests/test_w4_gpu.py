@@ -82,3 +82,21 @@ def test_w4_expansion_is_the_reference_dequantisation_bit_for_bit(dev, G):
     y = ops.w4_gemm(torch.eye(K, dtype=torch.bfloat16, device=dev), ops.w4_repack(q.to(dev)), s.to(dev), G).cpu()
     want = O.dq_bf16(q, s, G).t()
     assert torch.equal(y.view(torch.int16), want.contiguous().view(torch.int16))
+
+
+@pytest.mark.parametrize("M,F,K,G,act", [(300, 384, 512, 128, "silu"), (77, 104, 192, 64, "silu"), (513, 1024, 1024, 32, "gelu_tanh"), (1, 64, 128, 128, "silu")])
+def test_w4_glu_epilogue_equals_the_separate_pass(dev, M, F, K, G, act):
+    """the fused gate|up projection with the gated activation in its epilogue gives the bits of the plain projection followed by
+    the gated-activation pass (ragged M, F not a multiple of the tile, both activations)"""
+    from spinf_serve_b200 import ops
+    from spinf_serve_b200.linears import Int4Linear
+
+    qweight, scales = _gptq(2 * F, K, G, 11)
+    x = torch.randn((M, K), generator=torch.Generator().manual_seed(12)).to(torch.bfloat16).to(dev)
+    plain = Int4Linear(qweight.to(dev), scales.to(dev))
+    _, _, want = ops.glu_quant(plain(x), act, want_fp8=False, want_y=True)
+    fused = Int4Linear(qweight.to(dev), scales.to(dev)).fuse_glu(act)
+    got = fused(x)
+    assert got.shape == (M, F) and torch.equal(got, want)
+    with pytest.raises(RuntimeError):
+        fused.fuse_glu(act)
