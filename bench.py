@@ -1,4 +1,4 @@
-"""Throughput of the packed-prefill scoring path on the BASELINE configuration-2 workload.
+"""Throughput of the packed-prefill scoring path on the benchmark configuration-2 workload.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P bench.py --gpus N ...

@@ -135,7 +135,7 @@ int spinf_bf16_gemm_ld(const void* x, const void* w, void* y, int64_t M, int64_t
  * (qwen.py:326-330):  y[m,n] = bf16( sum_k x[m,k] * w[n,k] ),  w[n,k] = bf16( (nibble(n,k) - 8) * float(scales[n, k / group]) ).
  * x [M,K] bf16; qw uint8 [N, K/2] as spinf_w4_repack leaves it (below); scales fp16
  * [N, K/group]; y bf16 with row pitch y_pitch elements. The bf16 weight matrix is never materialised: nibbles are expanded inside
- * the kernel on their way to the tensor core. K a multiple of 64 and of group, group a multiple of 8 (128 in the BASELINE
+ * the kernel on their way to the tensor core. K a multiple of 64 and of group, group a multiple of 8 (128 in the benchmark
  * configuration, 32 in the reference's checkpoints), N a multiple of 8. A row of y does not depend on M. */
 int spinf_w4_gemm(const void* x, const void* qw, const void* scales, int32_t group, void* y, int64_t M, int64_t N, int64_t K,
                   int64_t y_pitch, void* stream);

@@ -9,7 +9,7 @@ published layer with the reference's own pieces plugged in: row-wise fp8 linears
 tests/test_model_host.py pins it against the installed transformers model run with the same weights.
 
 Synthetic configuration: every layer has the same head_dim and default rotary embeddings (theta 10 000 on sliding layers, 1 000 000
-on full layers); per-layer inputs, KV sharing, MoE blocks and soft-capping are off, as in the BASELINE configurations."""
+on full layers); per-layer inputs, KV sharing, MoE blocks and soft-capping are off, as in the benchmark configurations."""
 
 from dataclasses import dataclass, field
 

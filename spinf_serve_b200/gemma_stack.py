@@ -53,9 +53,9 @@ class GemmaConfig:
 
 
 CONFIGS = {
-    # BASELINE configuration 2 / 3: synthetic Gemma-style 12B
+    # benchmark configuration 2 / 3: synthetic Gemma-style 12B
     "gemma12b": dict(layers=48, hidden=3840, heads=16, kv_heads=8, head_dim=256, ffn=15360, vocab=262144, window=1024),
-    # BASELINE configuration 4: synthetic Gemma-style 31B-class
+    # benchmark configuration 4: synthetic Gemma-style 31B-class
     "gemma31b": dict(layers=60, hidden=5376, heads=32, kv_heads=16, head_dim=128, ffn=21504, vocab=262144, window=1024),
 }
 

@@ -3,7 +3,7 @@ returns a namespace of module classes built from a bf16 [out, in] weight on the 
 forward(x[..., K]) -> [..., N] bf16, with the same buffers (`w8t` = the [in, out] column-major view, `ws`, and for the static
 scheme `xs` and `peak`).
 
-On the sm_100a kernels: Fp8RowLinear (per-output-channel weight scales, per-token activation scales: the scheme of the BASELINE
+On the sm_100a kernels: Fp8RowLinear (per-output-channel weight scales, per-token activation scales: the scheme of the benchmark
 configurations), Fp8Linear (per-tensor scales, the activation scale from the forward's own maximum) and Fp8StaticLinear
 (per-tensor scales, a calibrated fixed activation scale: the reference's "fp8s"), `prequantized` for the tensors of an
 fp8-static checkpoint, and Int8Linear (int8 weights; int8 per-token activations on the int8 tensor cores, or bf16 activations).

@@ -1,4 +1,4 @@
-"""Seeded synthetic workloads with the shapes of the BASELINE configurations (they stand in for the reference's Wikinews benchmark
+"""Seeded synthetic workloads with the shapes of the benchmark configurations (they stand in for the reference's Wikinews benchmark
 of 24 articles x 56 two-option questions, benchmarks/README.md:31-37 in the spinf-serve tree: same token counts, uniform random
 token ids, no text). A workload is a list of score_grouped items: ((content id,), 0, GroupedTree)."""
 

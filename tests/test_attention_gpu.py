@@ -47,7 +47,7 @@ def _check(out, ref, real, what):
 @pytest.mark.parametrize("reading", ["scale_arg", "pre_scaled"])
 @pytest.mark.parametrize("layer", ["full_attention", "sliding_attention"])
 def test_config1_attention(dev, reading, layer):
-    """BASELINE config 1: 2 contents x (470 + 8 x 16), 16 query / 8 KV heads, head_dim 256, seed 0. Two readings of "scaled by
+    """benchmark config 1: 2 contents x (470 + 8 x 16), 16 query / 8 KV heads, head_dim 256, seed 0. Two readings of "scaled by
     1/sqrt(256)": N(0,1) inputs with scale = 1/16 passed to the operator (primary), or inputs pre-multiplied with scale = 1"""
     b = _cfg1_batch()
     pre, scale = (1.0, 1.0 / 16) if reading == "scale_arg" else (1.0 / 16, 1.0)

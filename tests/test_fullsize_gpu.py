@@ -1,4 +1,4 @@
-"""Size-independent properties at the BASELINE configurations' full layer shapes and stream sizes (depth reduced to keep the test
+"""Size-independent properties at the benchmark configurations' full layer shapes and stream sizes (depth reduced to keep the test
 short): a content scores bit-identically alone and inside a 32 768-token bulk pass whose trunks run past the sliding window, on the
 12B shapes (head_dim 256) and the 31B-class shapes (head_dim 128); every option log-prob is a log-probability."""
 

@@ -30,7 +30,7 @@ def test_option_logprobs_vs_oracle(dev, R, hidden, vocab, n_cols, softcap):
     ref = OH.option_logprobs(h, W, cols, softcap)
     err = (out - ref).abs().max().item()
     print(f"option logprobs R={R} vocab={vocab}: max abs err {err:.3e}")
-    assert err < 2e-3  # the tolerance BASELINE states for option log-probs
+    assert err < 2e-3  # the tolerance the benchmark specification states for option log-probs
 
 
 def test_option_logprobs_rows_do_not_depend_on_R(dev):

@@ -82,7 +82,7 @@ def _items(rng, n):
 @pytest.mark.parametrize("layers", [0, 1, 2, 4])
 def test_scorer_logprobs_vs_oracle(dev, layers):
     """option log-probs through the public scorer against the oracle. With no decoder layer (embedding, final norm, lm-head read)
-    the 2e-3 absolute tolerance BASELINE states holds; with fp8 layers in between the error is bounded by a multiple of the
+    the 2e-3 absolute tolerance the benchmark specification states holds; with fp8 layers in between the error is bounded by a multiple of the
     oracle's own sensitivity to one legitimate rounding change (see test_forward_vs_oracle_layer_by_layer)"""
     from spinf_serve_b200.scorer import EngineConfig, Scorer, read_grouped
 
