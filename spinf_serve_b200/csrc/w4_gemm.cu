@@ -12,7 +12,7 @@
 // [128 r, 128 r + 128) and loads tokens [128 r, 128 r + 128) of the tile; the leader issues one M = 256, N = 256 MMA per 16 of K
 // and each CTA keeps the accumulator of its own weight rows (128 lanes x 256 token columns). K in steps of 64. 14 warps per CTA:
 //   warp 0     one lane: TMA loads of this CTA's half of the activation tile (128 tokens x 128 B, swizzled; completes on the
-//              leader's barrier) and raw weight tile (128 rows x 32 B; completes on this CTA's barrier) into an 8-stage ring
+//              leader's barrier) and raw weight tile (128 rows x 32 B; completes on this CTA's barrier) into a 6-stage ring
 //   warps 6-13 dequantisers in two groups of four warps that take alternate K steps, thread = weight row = TMEM lane:
 //              64 nibbles -> 64 bf16 (32 packed columns of the stage's slot in tensor memory), two weights per instruction in
 //              packed bf16 arithmetic that rounds the exact product (n - 8) * scale once (see the loop)
@@ -20,8 +20,9 @@
 //              step (multicast to both CTAs) that frees the stage for the loader and the dequantisers alike
 //   warps 2-5  epilogue: TMEM -> bf16 -> transposed into swizzled staging (lane pairs exchange so that every store is a pair of
 //              neighbouring output channels) -> TMA store
-// Tensor memory: one accumulator (256 columns) + 8 weight slots of 32 columns; the epilogue frees the accumulator as soon as it is
-// in registers / staging (about 3 % of a tile's main loop at K = 5120), while loads and expansion run ahead through the ring.
+// Tensor memory: one accumulator (256 columns) + 6 weight slots of 32 columns; the epilogue frees the accumulator as soon as its last
+// chunk is in registers (a staging buffer per chunk, so no chunk waits for an earlier chunk's store): about 5 % of a tile's main
+// loop at K = 5120, while loads and expansion run ahead through the ring.
 // K order per output element is ascending and the tile shape does not depend on M: rows are batch-invariant.
 #include "gemm_tc.cuh"
 #include "host_util.h"
@@ -29,13 +30,14 @@
 namespace spinf {
 
 struct W4Smem {
-  static constexpr int STAGES = 8;            // stage s: activation half tile + raw weight tile in shared memory, expansion in TMEM
+  static constexpr int STAGES = 6;            // stage s: activation half tile + raw weight tile in shared memory, expansion in TMEM
+  static constexpr int EPI_BUFS = 4;          // one staging buffer per 64-token chunk of a tile: no chunk waits for an earlier store
   static constexpr int X_BYTES = 128 * 128;   // this CTA's activations: 128 tokens x 64 bf16
   static constexpr int RAW_BYTES = 128 * 32;  // this CTA's raw weights: 128 rows x 64 nibbles
   static constexpr int STAGE_BYTES = X_BYTES + RAW_BYTES;
   static constexpr int EPI_OFF = STAGES * STAGE_BYTES;
   static constexpr int EPI_BYTES = 64 * 256;  // one staging buffer: 64 tokens x 128 output channels (two swizzled 64 x 64 boxes)
-  static constexpr int BAR_OFF = EPI_OFF + 2 * EPI_BYTES;
+  static constexpr int BAR_OFF = EPI_OFF + EPI_BUFS * EPI_BYTES;
   static constexpr int TOTAL = BAR_OFF + 512 + 1024;
   static constexpr uint32_t ACC_COL = 0, W_COL = 256;  // tensor-memory columns: accumulator, weight slots (32 columns each)
 };
@@ -282,7 +284,7 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         // transpose through the lane pair: the even lane keeps token 2 i of both channels, the odd lane token 2 i + 1
         uint32_t packed[32];
-        uint8_t* buf = smem + L::EPI_OFF + (nchunks & 1u) * L::EPI_BYTES;
+        uint8_t* buf = smem + L::EPI_OFF + (nchunks % L::EPI_BUFS) * L::EPI_BYTES;
         if (ACT < 0) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -311,7 +313,7 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             packed[h] = oddc ? pack_bf16x2(other, keep) : pack_bf16x2(keep, other);
           }
         }
-        if (et == 0) tma_store_wait_read<1>();  // the store that last read this buffer (two chunks ago) has finished reading
+        if (et == 0) tma_store_wait_read<L::EPI_BUFS - 1>();  // the store that last read this buffer (a tile ago) has finished reading
         named_bar_sync(1, 128);
         if (ACT < 0) {
 #pragma unroll
