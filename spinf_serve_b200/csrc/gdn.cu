@@ -190,7 +190,7 @@ struct GdnProArgs {
   int Hk, Hv;
 };
 
-__device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
+__device__ __forceinline__ float silu_f(float x) { return silu_f32(x); }
 
 __global__ void __launch_bounds__(256) gdn_prologue_kernel(const GdnProArgs a) {
   extern __shared__ float xs[];  // conv+silu of the q and k channels (as bf16-rounded floats): 2 Hk GK floats
