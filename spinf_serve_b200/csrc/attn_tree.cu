@@ -663,6 +663,7 @@ using namespace spinf;
 
 extern "C" int spinf_tile_mask_bits(const int32_t* art, const int32_t* end, const int32_t* pos, int64_t n, int32_t window,
                                     const int32_t* tile_offsets, const int32_t* tile_blocks, uint64_t* bits, void* stream) {
+  if (n == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(art && end && pos && tile_offsets && tile_blocks && bits && n >= 0 && n % SPINF_BLOCK == 0 && n < (1ll << 30));
   if (n == 0) return 0;
   const int nb = static_cast<int>(n / SPINF_BLOCK);
@@ -676,6 +677,7 @@ extern "C" int spinf_tree_attn_fwd(const void* q, const void* k, const void* v, 
                                    const int32_t* end, const int32_t* pos, int32_t window, float scale, const int32_t* tile_offsets,
                                    const int32_t* tile_blocks, const uint8_t* tile_flags, const uint64_t* tile_bits, float* row_amax,
                                    void* stream) {
+  if (n == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(q && k && v && out && art && end && pos && tile_offsets && tile_blocks && tile_flags && tile_bits);
   SPINF_CHECK_ARG(n >= 0 && n % SPINF_BLOCK == 0 && n < (1ll << 30) && H > 0 && Hkv > 0 && H % Hkv == 0 && H <= 65535);
   SPINF_CHECK_ARG(D == 128 || D == 256);

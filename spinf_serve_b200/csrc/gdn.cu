@@ -313,6 +313,7 @@ extern "C" int spinf_gdn_recurrent(const void* q, const void* k, const void* v, 
                                    int64_t n_rows, int64_t q_pitch, int64_t v_pitch, int64_t g_pitch, int32_t Hk, int32_t Hv,
                                    int32_t K, int32_t V, float scale, const int64_t* cu, int64_t n_seg, const int64_t* idx,
                                    const float* h0, const int64_t* h0_idx, float* ht, const int64_t* ht_idx, void* stream) {
+  if (n_seg == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(q && k && v && g && beta && o && cu && n_rows >= 0 && n_seg >= 0 && Hk > 0 && Hv > 0 && Hv % Hk == 0);
   SPINF_CHECK_ARG(K == GK && V == GV);  // the kernel is written for 128 x 128 states, as the reference's is for K = 128
   SPINF_CHECK_ARG(q_pitch >= static_cast<int64_t>(Hk) * GK && q_pitch % 8 == 0 && v_pitch >= static_cast<int64_t>(Hv) * GV && g_pitch >= Hv);
@@ -339,6 +340,7 @@ extern "C" int spinf_gdn_recurrent(const void* q, const void* k, const void* v, 
 extern "C" int spinf_gdn_prologue(const void* y, int64_t y_pitch, int64_t n_rows, int64_t T, const int64_t* conv, const void* conv_w,
                                   const float* A_log, const float* dt_bias, int32_t Hk, int32_t Hv, int32_t K, int32_t V, void* q,
                                   void* k, void* v, float* g, void* beta, void* stream) {
+  if (T == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(y && conv && conv_w && A_log && dt_bias && q && k && v && g && beta && T >= 0 && n_rows >= T);
   SPINF_CHECK_ARG(K == GK && V == GV && Hk > 0 && Hv > 0 && Hv <= 256 && Hk <= 96 && T < (1ll << 31));
   SPINF_CHECK_ARG(y_pitch >= 2ll * Hk * GK + 2ll * Hv * GV + 2 * Hv && y_pitch % 8 == 0);
@@ -363,6 +365,7 @@ extern "C" int spinf_gdn_prologue(const void* y, int64_t y_pitch, int64_t n_rows
 
 extern "C" int spinf_gdn_epilogue(const void* o, const void* z, int64_t z_pitch, const void* norm_w, float eps, int64_t T, int32_t Hv,
                                   int32_t V, void* out, void* stream) {
+  if (T == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(o && z && norm_w && out && T >= 0 && Hv > 0 && V == GV && z_pitch >= static_cast<int64_t>(Hv) * GV && z_pitch % 4 == 0);
   if (T == 0) return 0;
   const int64_t warps = T * Hv;

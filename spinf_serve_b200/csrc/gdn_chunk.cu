@@ -476,6 +476,7 @@ extern "C" int spinf_gdn_chunked(const void* q, const void* k, const void* v, co
                                  const int64_t* h0_idx, float* ht, const int64_t* ht_idx, const int32_t* chunk_seg,
                                  const int32_t* chunk_t0, int64_t n_chunks, int64_t call_tokens, void* workspace,
                                  int64_t workspace_bytes, void* stream) {
+  if (n_seg == 0 || n_chunks == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(q && k && v && g && beta && o && cu && n_rows >= 0 && n_seg >= 0 && Hk > 0 && Hv > 0 && Hv % Hk == 0);
   SPINF_CHECK_ARG(K == CK && V == CK);
   SPINF_CHECK_ARG(q_pitch >= static_cast<int64_t>(Hk) * CK && q_pitch % 8 == 0 && v_pitch >= static_cast<int64_t>(Hv) * CK && v_pitch % 8 == 0 && g_pitch >= Hv);

@@ -521,6 +521,7 @@ static GemmShape make_shape(int64_t M, int64_t N, int64_t K, int BN, int elem_by
 using namespace spinf;
 
 extern "C" int spinf_fp8_rowwise_quant(const void* x_bf16, int64_t M, int64_t K, void* x8, float* xs, void* stream) {
+  if (M == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(x_bf16 && x8 && xs && M >= 0 && K > 0 && K % 8 == 0 && K <= 32768 && M < (1ll << 31));
   if (M == 0) return 0;
   fp8_rowwise_quant_kernel<false><<<static_cast<unsigned>(M), 256, 0, static_cast<cudaStream_t>(stream)>>>(
@@ -530,6 +531,7 @@ extern "C" int spinf_fp8_rowwise_quant(const void* x_bf16, int64_t M, int64_t K,
 }
 
 extern "C" int spinf_int8_rowwise_quant(const void* x_bf16, int64_t M, int64_t K, void* x8, float* xs, void* stream) {
+  if (M == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(x_bf16 && x8 && xs && M >= 0 && K > 0 && K % 8 == 0 && K <= 32768 && M < (1ll << 31));
   if (M == 0) return 0;
   fp8_rowwise_quant_kernel<true><<<static_cast<unsigned>(M), 256, 0, static_cast<cudaStream_t>(stream)>>>(
@@ -540,6 +542,7 @@ extern "C" int spinf_int8_rowwise_quant(const void* x_bf16, int64_t M, int64_t K
 
 extern "C" int spinf_int8_rowwise_gemm(const void* x8, const float* xs, const void* w8, const float* ws, void* y_bf16, int64_t M,
                                        int64_t N, int64_t K, void* stream) {
+  if (M == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(x8 && xs && w8 && ws && y_bf16 && M >= 0 && N > 0 && K > 0 && K % 16 == 0 && N % 16 == 0);
   SPINF_CHECK_ARG(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31));
   if (M == 0) return 0;
@@ -557,6 +560,7 @@ extern "C" int spinf_int8_rowwise_gemm(const void* x8, const float* xs, const vo
 
 extern "C" int spinf_fp8_rowwise_gemm(const void* x8, const float* xs, const void* w8, const float* ws, void* y_bf16, int64_t M,
                                       int64_t N, int64_t K, void* stream) {
+  if (M == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(x8 && xs && w8 && ws && y_bf16 && M >= 0 && N > 0 && K > 0 && K % 16 == 0 && N % 16 == 0);
   SPINF_CHECK_ARG(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31));
   if (M == 0) return 0;
@@ -573,6 +577,7 @@ extern "C" int spinf_fp8_rowwise_gemm(const void* x8, const float* xs, const voi
 }
 
 extern "C" int spinf_abs_max(const void* x_bf16, int64_t n, float* out, void* stream) {
+  if (n == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(x_bf16 && out && n >= 0 && n % 8 == 0);
   SPINF_CUDA_OK(cudaMemsetAsync(out, 0, sizeof(float), static_cast<cudaStream_t>(stream)));
   if (n == 0) return 0;
@@ -586,6 +591,7 @@ extern "C" int spinf_abs_max(const void* x_bf16, int64_t n, float* out, void* st
 
 extern "C" int spinf_fp8_tensor_quant(const void* x_bf16, int64_t n, const float* scale, int32_t from_amax, void* x8, float* scale_out,
                                       float* peak, void* stream) {
+  if (n == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(x_bf16 && scale && x8 && n >= 0 && n % 8 == 0 && (from_amax == 0 || from_amax == 1));
   if (n == 0) return 0;
   const int64_t nvec = n / 8, blocks = (nvec + 255) / 256;
@@ -598,6 +604,7 @@ extern "C" int spinf_fp8_tensor_quant(const void* x_bf16, int64_t n, const float
 
 extern "C" int spinf_fp8_tensor_gemm(const void* x8, const float* xs, const void* w8, const float* ws, void* y_bf16, int64_t M,
                                      int64_t N, int64_t K, void* stream) {
+  if (M == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(x8 && xs && w8 && ws && y_bf16 && M >= 0 && N > 0 && K > 0 && K % 16 == 0 && N % 16 == 0);
   SPINF_CHECK_ARG(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31));
   if (M == 0) return 0;
@@ -616,6 +623,7 @@ extern "C" int spinf_fp8_tensor_gemm(const void* x8, const float* xs, const void
 }
 
 extern "C" int spinf_bf16_gemm_ld(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, int64_t y_pitch, void* stream) {
+  if (M == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(x && w && y && M >= 0 && N > 0 && K > 0 && K % 8 == 0 && N % 8 == 0 && y_pitch >= N && y_pitch % 8 == 0);
   SPINF_CHECK_ARG(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31));
   if (M == 0) return 0;
@@ -637,6 +645,7 @@ extern "C" int spinf_bf16_gemm(const void* x, const void* w, void* y, int64_t M,
 
 extern "C" int spinf_fp8_rowwise_gemm_glu(const void* x8, const float* xs, const void* w8_tiled, const float* ws_tiled, void* y,
                                           float* row_amax, int64_t M, int64_t F, int64_t K, int32_t act, void* stream) {
+  if (M == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(x8 && xs && w8_tiled && ws_tiled && y && row_amax && M >= 0 && F > 0 && K > 0 && K % 16 == 0 && F % 128 == 0);
   SPINF_CHECK_ARG(M < (1ll << 31) && F < (1ll << 30) && K < (1ll << 31) && (act == 0 || act == 1));
   if (M == 0) return 0;
@@ -662,6 +671,7 @@ extern "C" int spinf_fp8_rowwise_gemm_glu(const void* x8, const float* xs, const
 extern "C" int spinf_fp8_rowwise_gemm_qkv(const void* x8, const float* xs, const void* w8, const float* ws, void* y, int64_t M, int32_t H,
                                           int32_t Hkv, int32_t D, int64_t K, const void* wq, const void* wk, const void* cos_t,
                                           const void* sin_t, float eps, int32_t plus1, int32_t norm_v, void* stream) {
+  if (M == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(x8 && xs && w8 && ws && y && wq && wk && cos_t && sin_t && M >= 0 && K > 0 && K % 16 == 0);
   SPINF_CHECK_ARG(H > 0 && Hkv > 0 && (D == 128 || D == 256) && M < (1ll << 31) && K < (1ll << 31));
   const int64_t N = static_cast<int64_t>(H + 2 * Hkv) * D;
@@ -694,6 +704,7 @@ extern "C" int spinf_fp8_rowwise_gemm_qkv(const void* x8, const float* xs, const
 }
 
 extern "C" int spinf_fp8_quant_from_amax(const void* y, const float* row_amax, int64_t M, int64_t K, void* x8, float* xs, void* stream) {
+  if (M == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(y && row_amax && x8 && xs && M >= 0 && K > 0 && K % 8 == 0 && M < (1ll << 31) && K < (1ll << 31));
   if (M == 0) return 0;
   fp8_quant_from_amax_kernel<<<static_cast<unsigned>(M), 256, 0, static_cast<cudaStream_t>(stream)>>>(
@@ -712,6 +723,7 @@ extern "C" int64_t spinf_option_logprobs_workspace_bytes(int64_t R, int64_t voca
 extern "C" int spinf_option_logprobs(const void* h, const void* W, int64_t R, int64_t hidden, int64_t vocab, const int32_t* cols,
                                      int64_t n_cols, float softcap, float* out, void* workspace,
                                      int64_t workspace_bytes, void* stream) {
+  if (R == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(h && W && out && workspace && R >= 0 && hidden > 0 && hidden % 8 == 0 && vocab > 0 && n_cols >= 0);
   SPINF_CHECK_ARG(n_cols == 0 || cols);
   SPINF_CHECK_ARG(R < (1ll << 31) && vocab < (1ll << 31) && hidden < (1ll << 31) && n_cols < (1ll << 24));
@@ -776,6 +788,7 @@ static unsigned char* option_scratch_device_ptr(int dev) {
 
 extern "C" int spinf_option_logprobs_static(const void* h, const void* W, int64_t R, int64_t hidden, int64_t vocab, const int32_t* cols,
                                             int64_t n_cols, float softcap, float* out, int32_t* status, void* stream) {
+  if (R == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(h && W && out && R >= 0 && hidden > 0 && hidden % 8 == 0 && vocab > 0 && n_cols >= 0);
   SPINF_CHECK_ARG(n_cols == 0 || cols);
   SPINF_CHECK_ARG(R < (1ll << 31) && vocab < (1ll << 31) && hidden < (1ll << 31) && n_cols < (1ll << 24));

@@ -409,6 +409,7 @@ using namespace spinf;
 extern "C" int spinf_fused_norm(const void* y, const int64_t* rows, const void* w1, const void* residual, const void* w2, int64_t n_out,
                                 int64_t hidden, float eps, int32_t plus1, void* out_h, void* out_norm, void* out_x8, float* out_xs,
                                 void* stream) {
+  if (n_out == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(y && n_out >= 0 && hidden > 0 && hidden % 8 == 0 && hidden <= NORM_THREADS * NORM_MAX_VEC * 8);
   SPINF_CHECK_ARG((out_x8 == nullptr) == (out_xs == nullptr));
   SPINF_CHECK_ARG(!(out_norm || out_x8) || w2);
@@ -452,6 +453,7 @@ extern "C" int spinf_fused_norm(const void* y, const int64_t* rows, const void* 
 extern "C" int spinf_qkv_norm_rope(void* qkv, int64_t pitch, int64_t n, int32_t H, int32_t Hkv, int32_t D, const void* wq,
                                    const void* wk, const void* cos_t, const void* sin_t, int32_t rot_dim, float eps, int32_t plus1,
                                    int32_t norm_v, void* stream) {
+  if (n == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(qkv && wq && wk && cos_t && sin_t && n >= 0 && H > 0 && Hkv > 0 && (D == 128 || D == 256));
   SPINF_CHECK_ARG(rot_dim > 0 && rot_dim <= D && rot_dim % (2 * (D / 32)) == 0);
   SPINF_CHECK_ARG(pitch >= static_cast<int64_t>(H + 2 * Hkv) * D);
@@ -475,6 +477,7 @@ extern "C" int spinf_qkv_norm_rope(void* qkv, int64_t pitch, int64_t n, int32_t 
 extern "C" int spinf_qkv_norm_rope_gated(void* y, int64_t pitch, int64_t n, int32_t H, int32_t Hkv, int32_t D, const void* wq, const void* wk,
                                          const void* cos_t, const void* sin_t, int32_t rot_dim, float eps, int32_t plus1, void* q_out,
                                          void* stream) {
+  if (n == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(y && wq && wk && cos_t && sin_t && q_out && n >= 0 && H > 0 && Hkv > 0 && (D == 128 || D == 256));
   SPINF_CHECK_ARG(rot_dim > 0 && rot_dim <= D && rot_dim % (2 * (D / 32)) == 0);
   SPINF_CHECK_ARG(pitch >= static_cast<int64_t>(2 * H + 2 * Hkv) * D && pitch % 8 == 0);
@@ -515,6 +518,7 @@ __global__ void attn_gate_kernel(__nv_bfloat16* __restrict__ o, const __nv_bfloa
 }
 
 extern "C" int spinf_attn_gate(void* o, const void* y, int64_t pitch, int64_t n, int32_t H, int32_t D, void* stream) {
+  if (n == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(o && y && n >= 0 && H > 0 && D > 0 && D % 8 == 0 && pitch >= 2ll * H * D && pitch % 8 == 0);
   if (n == 0) return 0;
   const int64_t vecs = n * H * D / 8;
@@ -526,6 +530,7 @@ extern "C" int spinf_attn_gate(void* o, const void* y, int64_t pitch, int64_t n,
 
 extern "C" int spinf_glu_quant(const void* gu, int64_t n, int64_t F, int32_t act, void* out_x8, float* out_xs, void* out_y,
                                void* stream) {
+  if (n == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(gu && n >= 0 && F > 0 && F % 8 == 0 && (act == 0 || act == 1) && n < (1ll << 31) && F < (1ll << 28));
   SPINF_CHECK_ARG((out_x8 == nullptr) == (out_xs == nullptr) && (out_x8 || out_y));
   if (n == 0) return 0;
@@ -543,6 +548,7 @@ extern "C" int spinf_glu_quant(const void* gu, int64_t n, int64_t F, int32_t act
 
 extern "C" int spinf_embed_scale(const int64_t* ids, const void* emb, int64_t n, int64_t hidden, int64_t vocab, float scale, void* out,
                                  void* stream) {
+  if (n == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(ids && emb && out && n >= 0 && hidden > 0 && hidden % 8 == 0 && vocab > 0 && n < (1ll << 31));
   if (n == 0) return 0;
   embed_scale_kernel<<<static_cast<unsigned>(n), 256, 0, static_cast<cudaStream_t>(stream)>>>(
@@ -553,6 +559,7 @@ extern "C" int spinf_embed_scale(const int64_t* ids, const void* emb, int64_t n,
 
 extern "C" int spinf_rope_table(const int32_t* pos, int64_t n, int32_t rot_dim, const float* inv_freq, void* cos_t, void* sin_t,
                                 void* stream) {
+  if (n == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(pos && cos_t && sin_t && inv_freq && n >= 0 && rot_dim > 0 && rot_dim % 2 == 0);
   if (n == 0) return 0;
   const int half = rot_dim / 2;

@@ -379,6 +379,7 @@ __global__ void __launch_bounds__(256) w4_repack_kernel(const uint32_t* __restri
 using namespace spinf;
 
 extern "C" int spinf_w4_repack(const void* q_in, void* q_out, int64_t N, int64_t K, void* stream) {
+  if (N == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(q_in && q_out && N >= 0 && K > 0 && K % 8 == 0);
   SPINF_CHECK_ARG((reinterpret_cast<uintptr_t>(q_in) & 3) == 0 && (reinterpret_cast<uintptr_t>(q_out) & 3) == 0);
   const int64_t n_words = N * (K / 8);
@@ -393,6 +394,7 @@ extern "C" int spinf_w4_repack(const void* q_in, void* q_out, int64_t N, int64_t
 template <int ACT>
 static int launch_w4(const void* x, const void* qw, const void* scales, int32_t group, void* y, int64_t M, int64_t N, int64_t K,
                      int64_t y_pitch, void* stream) {
+  if (M == 0) return 0;  // nothing to do: the row pointers may be null
   const int64_t n_out = ACT < 0 ? N : N / 2;
   SPINF_CHECK_ARG(x && qw && scales && y && M >= 0 && N > 0 && K > 0 && group > 0);
   SPINF_CHECK_ARG(K % 64 == 0 && group % 8 == 0 && K % group == 0 && N % (ACT < 0 ? 8 : 16) == 0 && y_pitch >= n_out && y_pitch % 8 == 0);

@@ -83,6 +83,9 @@ def fp8_tensor_quant(x, scale=None, peak=None, want_amax=False):
         raise SpinfError("fp8_tensor_quant: the element count must be a multiple of 8")
     x8 = torch.empty((M, K), dtype=FP8, device=x.device)
     L = _lib.lib()
+    if scale is None and M * K == 0:  # no maximum to take: the scale at its floor, max(0, 1e-12) / 448
+        s = torch.full((), float(torch.tensor(1e-12) / 448.0), dtype=torch.float32, device=x.device)
+        return (x8, s, torch.zeros((), dtype=torch.float32, device=x.device)) if want_amax else (x8, s)
     if scale is None:
         both = torch.empty(2, dtype=torch.float32, device=x.device)  # [max|x|, s]: other CTAs still read the maximum when s is written
         amax, s = both[0], both[1]

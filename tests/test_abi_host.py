@@ -50,6 +50,10 @@ def test_argument_errors_are_reported_on_the_host():
     assert lib.spinf_w4_repack(p, p, 4, 100, NULL) == -1                        # K not a multiple of 8
     assert lib.spinf_w4_repack(ctypes.c_void_p(18), p, 4, 128, NULL) == -1      # not 4-byte aligned
     assert lib.spinf_fp8_rowwise_gemm_glu(p, p, p, p, p, p, 4, 100, 64, 0, NULL) == -1  # F not a multiple of 128
+    # zero rows are nothing to do, whatever the row pointers are (an empty tensor has a null data pointer)
+    assert lib.spinf_fp8_rowwise_quant(NULL, 0, 64, NULL, NULL, NULL) == 0
+    assert lib.spinf_fp8_rowwise_gemm(NULL, NULL, p, p, NULL, 0, 128, 64, NULL) == 0
+    assert lib.spinf_w4_gemm(NULL, p, p, 128, NULL, 0, 128, 128, 128, NULL) == 0
     assert lib.spinf_option_logprobs_workspace_bytes(-1, 10, 1) == -1
     assert lib.spinf_option_logprobs(p, p, 4, 64, 1000, p, 2, ctypes.c_float(0.0), p, p, 8, NULL) == -1  # workspace too small
     assert lib.spinf_option_logprobs_static(p, p, 4096, 64, 262144, p, 2, ctypes.c_float(0.0), p, NULL, NULL) == -4  # beyond the static scratch
