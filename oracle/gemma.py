@@ -99,14 +99,16 @@ LINEARS = ("q", "k", "v", "o", "gate", "up", "down")
 def quantize(W, scheme="fp8row"):
     """per-linear (w8 [out, in] e4m3, ws fp32: [1, out] for fp8row, one scalar for the per-tensor schemes fp8 / fp8s) with the
     q|k|v and gate|up projections kept separate, as the reference's module swap leaves them (spinf_serve/quant/linears.py:66-106)"""
-    fn = OL.quantize_weight_rowwise if scheme == "fp8row" else OL.quantize_weight
+    fn = {"fp8row": OL.quantize_weight_rowwise, "fp8": OL.quantize_weight, "fp8s": OL.quantize_weight,
+          "w8a8": OL.quantize_weight_int8, "w8a16": OL.quantize_weight_int8, "bf16": lambda w: (w, None)}[scheme]
     return [{k: fn(L[k]) for k in LINEARS} for L in W["layers"]]
 
 
 def forward(cfg: GemmaConfig, W, Q, ids, art, end, pos, n_layers=None, taps=None, scheme="fp8row", scales=None, amax=None, peaks=None):
     """packed forward -> final hidden states [n, hidden] bf16 (after the model's last norm), the oracle of Gemma4Stack.forward
     (spinf_serve/models/gemma4.py:407-415). taps: optional dict filled with intermediate tensors for operator-level checks.
-    scheme: fp8row (Fp8RowLinear), fp8 (Fp8Linear: dynamic per-tensor) or fp8s (Fp8StaticLinear with scales[i][name]).
+    scheme: fp8row (Fp8RowLinear), fp8 (Fp8Linear: dynamic per-tensor), fp8s (Fp8StaticLinear with scales[i][name]), w8a8 / w8a16
+    (Int8Linear with int8 / bf16 activations) or bf16 (the unquantized linears).
     amax: optional list of per-layer dicts updated with the largest |input| of every linear (what the reference's calibration
     hooks record, quant/calibrate.py:117-124); peaks: the same for the static scheme's monitor (max|x| / (448 scale))."""
     n = len(ids)
@@ -120,6 +122,10 @@ def forward(cfg: GemmaConfig, W, Q, ids, art, end, pos, n_layers=None, taps=None
             return OL.fp8_row_linear(x, *q[key])
         if scheme == "fp8":
             return OL.fp8_linear(x, *q[key])
+        if scheme in ("w8a8", "w8a16"):  # Int8Linear with int8 or bf16 activations (linears.py:55-64)
+            return OL.int8_linear(x, *q[key], scheme == "w8a8")
+        if scheme == "bf16":
+            return torch.nn.functional.linear(x, q[key][0])
         y, pk = OL.fp8_static_linear(x, *q[key], torch.tensor(scales[layer[0]][key], dtype=torch.float32))
         if peaks is not None:
             peaks[(layer[0], key)] = max(peaks.get((layer[0], key), 0.0), float(pk))

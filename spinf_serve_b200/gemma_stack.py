@@ -19,7 +19,8 @@ from spinf_serve_b200 import attention, ops
 from spinf_serve_b200.linears import MONITOR, quantize_weight, quantize_weight_rowwise, static_scale
 
 LINEARS = ("q", "k", "v", "o", "gate", "up", "down")  # the quantized linears of a layer
-SCHEMES = ("fp8row", "fp8", "fp8s")  # the reference's EngineConfig.quant values that run here (spinf_serve/models/gemma4.py:170-215)
+# the reference's EngineConfig.quant values for this family (spinf_serve/config.py:6, models/gemma4.py:170-235)
+SCHEMES = ("fp8row", "fp8", "fp8s", "w8a8", "w8a16", "bf16")
 
 
 @dataclass
@@ -73,11 +74,27 @@ class GemmaWeights:
         """one layer's device tensors. fp8row: per-channel weight scales, gate|up in the tiled order of the fused GeGLU GEMM.
         fp8 / fp8s (per-tensor weight scales): the same fused [out, in] storage with each linear's scalar spread over its output
         channels, gate|up in natural order; fp8s adds the calibrated activation scale and the clipping monitor of every linear
-        input (`xs`: {linear name: scale})."""
-        quant = quantize_weight_rowwise if scheme == "fp8row" else quantize_weight
+        input (`xs`: {linear name: scale}). w8a8: int8 weights with per-channel scales; w8a16 / bf16: bf16 weights (int8 values with
+        the scale folded in, or the originals) and no scales."""
+
+        def quant_int8(w):  # Int8Linear.__init__ (spinf_serve/quant/linears.py:43-46), the same eager ops
+            wf = w.float()
+            sc = wf.abs().amax(-1).clamp(min=1e-12) / 127.0
+            return (wf / sc[:, None]).round_().clamp_(-127, 127).to(torch.int8), sc
+
+        def fold(w):  # w8a16: the scale folded into the weight in bf16, as Int8Linear.forward folds it on every call (:63)
+            w8, sc = quant_int8(w)
+            return w8.to(torch.bfloat16) * sc.to(torch.bfloat16)[:, None], None
+
+        quant = {"fp8row": quantize_weight_rowwise, "fp8": quantize_weight, "fp8s": quantize_weight, "w8a8": quant_int8,
+                 "w8a16": fold, "bf16": lambda w: (w, None)}[scheme]
 
         def q8(*names):
             parts = [pre[k] if pre is not None else quant(L[k]) for k in names]
+            if scheme == "w8a16" and pre is not None:  # int8 tensors given: fold as above
+                parts = [(p[0].to(torch.bfloat16) * p[1].to(torch.bfloat16).reshape(-1)[:, None], None) for p in parts]
+            if parts[0][1] is None:  # bf16 weights, no scales
+                return torch.cat([p[0] for p in parts]).contiguous(), None
             w = torch.cat([p[0] for p in parts]).contiguous()
             sc = torch.cat([p[1].float().reshape(-1).expand(p[0].shape[0]) if p[1].numel() == 1 else p[1].reshape(-1) for p in parts])
             return w, sc.contiguous()
@@ -117,7 +134,7 @@ class GemmaWeights:
         spinf_serve/quant/linears.py:121-131); scales as in from_bf16 (an fp8-static checkpoint's input_scale tensors)"""
         names = ("q_norm", "k_norm", "input_ln", "post_attn_ln", "pre_ffn_ln", "post_ffn_ln")
         layers = [
-            cls._layer({k: L[k].to(device) for k in names}, {k: (a.to(device), b.to(device)) for k, (a, b) in q.items()}, scheme,
+            cls._layer({k: L[k].to(device) for k in names}, {k: (a.to(device), None if b is None else b.to(device)) for k, (a, b) in q.items()}, scheme,
                        scales[i] if scales is not None else None)
             for i, (L, q) in enumerate(zip(W["layers"], Q))
         ]
@@ -186,6 +203,17 @@ class GemmaStack:
     # ---- per-tensor schemes (fp8: the activation scale from the forward's own maximum; fp8s: a calibrated fixed scale). The
     # GEMMs are the row-wise kernels with every row given the tensor's one scale, so their fused epilogues stay; the reference
     # computes bf16(acc * xs * ws) with scalar scales (spinf_serve/quant/linears.py:77,114), the same product.
+    def _linear(self, x, L, key, names):
+        """x [n, K] bf16 through the fused linear `key` (the linears `names` of the layer) under the stack's scheme -> bf16 [n, N]"""
+        sch = self.w.scheme
+        if sch in ("bf16", "w8a16"):
+            return ops.bf16_gemm(x, L[key + "_w"])
+        if sch == "w8a8":
+            x8, xs = ops.int8_rowwise_quant(x)
+            return ops.int8_rowwise_gemm(x8, xs, L[key + "_w"], L[key + "_s"])
+        x8, xs = self._quant_in(x, L, names)
+        return ops.fp8_rowwise_gemm(x8, xs, L[key + "_w"], L[key + "_s"])
+
     def _quant_in(self, x, L, names):
         """x [n, K] bf16, the input of the linears `names` -> (x8, xs [n]). fp8s: the linears that share an input share its
         quantisation when their calibrated scales agree (they do when calibrate() made the table: one input, one maximum)."""
@@ -220,6 +248,7 @@ class GemmaStack:
         ids, pos, masks = inputs["ids"], inputs["pos"], inputs["masks"]
         n = ids.numel()
         row = w.scheme == "fp8row"
+        fp8 = w.scheme in ("fp8row", "fp8", "fp8s")
         tables = {k: ops.rope_table(pos, f) for k, f in self.inv_freq.items()}
         h = ops.embed_scale(ids, w.embed, self.embed_scale)
         if self.n_layers == 0:
@@ -229,11 +258,12 @@ class GemmaStack:
             L = w.layers[i]
             kind = cfg.layer_types[i]
             cos, sin = tables[kind]
-            x8, xs = (r["x8"], r["xs"]) if row else self._quant_in(r["norm"], L, ("q", "k", "v"))
-            if self.fuse_qkv:  # head norms + rotary in the projection's epilogue
+            if fp8:
+                x8, xs = (r["x8"], r["xs"]) if row else self._quant_in(r["norm"], L, ("q", "k", "v"))
+            if fp8 and self.fuse_qkv:  # head norms + rotary in the projection's epilogue
                 qkv = ops.fp8_gemm_qkv(x8, xs, L["qkv_w"], L["qkv_s"], H, K, D, L["q_norm"], L["k_norm"], cos, sin, cfg.eps)
             else:
-                qkv = ops.fp8_rowwise_gemm(x8, xs, L["qkv_w"], L["qkv_s"])
+                qkv = ops.fp8_rowwise_gemm(x8, xs, L["qkv_w"], L["qkv_s"]) if fp8 else self._linear(r["norm"], L, "qkv", ("q", "k", "v"))
                 ops.qkv_norm_rope(qkv, H, K, D, L["q_norm"], L["k_norm"], cos, sin, cfg.eps)
             q = qkv[:, : H * D].view(n, H, D)
             k = qkv[:, H * D : (H + K) * D].view(n, K, D)
@@ -243,19 +273,18 @@ class GemmaStack:
             a = attention.tree_attention(q, k, v, masks[kind], 1.0, row_amax=amax)  # scaling = 1.0: q and k are normed
             if row:  # the attention kernel has already found the row maxima
                 a8, a_s = ops.fp8_quant_from_amax(a.view(n, H * D), amax)
+                o = ops.fp8_rowwise_gemm(a8, a_s, L["o_w"], L["o_s"])
             else:
-                a8, a_s = self._quant_in(a.view(n, H * D), L, ("o",))
-            o = ops.fp8_rowwise_gemm(a8, a_s, L["o_w"], L["o_s"])
+                o = self._linear(a.view(n, H * D), L, "o", ("o",))
             r = ops.fused_norm(o, w1=L["post_attn_ln"], residual=h, w2=L["pre_ffn_ln"], eps=cfg.eps, want_h=True, want_fp8=row,
                                want_norm=not row)
             h = r["h"]
             if row:
                 g8, g_s, _ = ops.fp8_gemm_glu(r["x8"], r["xs"], L["gu_w"], L["gu_s"], "gelu_tanh")
+                d = ops.fp8_rowwise_gemm(g8, g_s, L["down_w"], L["down_s"])
             else:
-                x8, xs = self._quant_in(r["norm"], L, ("gate", "up"))
-                gu = ops.fp8_rowwise_gemm(x8, xs, L["gu_w"], L["gu_s"])
-                g8, g_s = self._quant_in(ops.glu_quant(gu, "gelu_tanh", want_fp8=False, want_y=True)[2], L, ("down",))
-            d = ops.fp8_rowwise_gemm(g8, g_s, L["down_w"], L["down_s"])
+                gu = self._linear(r["norm"], L, "gu", ("gate", "up"))
+                d = self._linear(ops.glu_quant(gu, "gelu_tanh", want_fp8=False, want_y=True)[2], L, "down", ("down",))
             last = i == self.n_layers - 1
             r = ops.fused_norm(
                 d, w1=L["post_ffn_ln"], residual=h, w2=None if last else w.layers[i + 1]["input_ln"], eps=cfg.eps, want_h=True,

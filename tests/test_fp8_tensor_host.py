@@ -59,7 +59,7 @@ def test_product_side_host_logic():
     for amax in (0.0, 1e-3, 0.7, 100.0, 448.0, 449.0, 3.0e4):
         assert linears.static_scale(amax, 2.0) == O.static_scale(amax, 2.0)
         assert linears.static_scale(amax, 1.0) == O.static_scale(amax, 1.0)
-    assert GS.SCHEMES == ("fp8row", "fp8", "fp8s") and GS.LINEARS == ("q", "k", "v", "o", "gate", "up", "down")
+    assert GS.SCHEMES == ("fp8row", "fp8", "fp8s", "w8a8", "w8a16", "bf16") and GS.LINEARS == ("q", "k", "v", "o", "gate", "up", "down")
     ns = linears.quant_linears(None, "cpu")
     w = torch.zeros((16, 16), dtype=torch.bfloat16)
     for make in (lambda: ns.Fp8Linear(w), lambda: ns.Fp8StaticLinear(w, 0.5), lambda: ns.Fp8RowLinear(w), lambda: ns.Int8Linear(w, True)):

@@ -224,3 +224,48 @@ def test_per_tensor_schemes_vs_oracle(dev):
     assert worst > 1.0 and where[1] in OG.LINEARS
     assert linears.MONITOR["on"]
     linears.MONITOR["on"] = False
+
+
+@pytest.mark.parametrize("scheme", ["w8a8", "w8a16", "bf16"])
+def test_int8_and_bf16_schemes_vs_oracle(dev, scheme):
+    """the reference's remaining quant options on the same stack: forward against the oracle's (statistical beyond the first layer,
+    as above) and scores bit-identical alone and packed (every one of these schemes is row-independent)"""
+    from spinf_serve_b200 import gemma_stack as GS
+    from spinf_serve_b200.scorer import EngineConfig, Scorer
+
+    layers = 3
+    ocfg, cfg = OG.GemmaConfig(**_cfg(128, layers)), GS.GemmaConfig(**_cfg(128, layers))
+    W = OG.init_weights(ocfg, seed=4)
+    Q = OG.quantize(W, scheme)
+    rng = np.random.default_rng(6)
+    pk = P.Packer(2048, 8192, align=True)
+    for j in range(3):
+        list(pk.push(j, _content(rng, int(rng.integers(40, 300)), 4)))
+    (b,) = list(pk.flush())
+    real = torch.from_numpy(b.art >= 0)
+    stack = GS.GemmaStack(GS.GemmaWeights.from_quantized(cfg, W, Q, dev, scheme))
+    taps_o, taps_g, taps_p = {}, {}, {}
+    OG.forward(ocfg, W, Q, b.ids, b.art, b.end, b.pos, taps=taps_o, scheme=scheme)
+    stack.forward(stack.stage(b, dev), taps=taps_g)
+    exact = OA.tree_attention
+    try:
+        OA.tree_attention = lambda *a, **k: exact(*a, **{**k, "round_p": True})
+        OG.forward(ocfg, W, Q, b.ids, b.art, b.end, b.pos, taps=taps_p, scheme=scheme)
+    finally:
+        OA.tree_attention = exact
+    for key in ("q", "k", "v"):
+        g, o = taps_g[0][key].cpu()[real].float(), taps_o[0][key][real].float()
+        frac = (g != o).float().mean().item()
+        print(f"{scheme} layer0 {key}: differing elements {frac:.4%}")
+        assert frac < 0.02 and (g - o).abs().max() <= 2.0**-6 * o.abs().max()
+    for i in range(layers):
+        o = taps_o[i]["h"][real].float()
+        rms = lambda x: (x.pow(2).mean().sqrt() / o.pow(2).mean().sqrt()).item()  # noqa: E731
+        err, floor = rms(taps_g[i]["h"].cpu()[real].float() - o), rms(taps_p[i]["h"][real].float() - o)
+        print(f"{scheme} hidden after layer {i}: rms err / rms = {err:.3e} (oracle's own rounding sensitivity {floor:.3e})")
+        assert err < 3 * floor + 2e-3
+    target = (("T",), 0, _content(rng, 200, 5))
+    others = _items(rng, 6)
+    sc = Scorer(GS.GemmaStack(GS.GemmaWeights.from_bf16(cfg, W, dev, scheme)), EngineConfig(token_budget=4096, max_tokens=8192), dev)
+    alone, packed = (sc.score_grouped(r)[("T",)] for r in ([target], others[:3] + [target] + others[3:]))
+    assert all(np.array_equal(a, c) for a, c in zip(alone, packed))
