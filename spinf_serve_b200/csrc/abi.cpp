@@ -3,7 +3,7 @@
 
 using namespace spinf;
 
-extern "C" int spinf_version(void) { return 100; }
+extern "C" int spinf_version(void) { return 200; }  // 0.2.0: the int4 weight layout of spinf_w4_gemm changed (spinf_w4_repack); per-tensor fp8, int8 and GLU entry points added
 
 extern "C" int spinf_init(void) {
   int dev = 0;
