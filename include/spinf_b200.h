@@ -45,6 +45,11 @@ int spinf_init(void);
 /* Synchronises `stream`, returns the device status word (0 = every kernel since the last call completed its waits) and clears it. */
 int spinf_last_status(void* stream);
 
+/* Self-test of the error path every kernel of the library shares: launches one CTA that waits, for at most limit_ns (<= 1 s), on a
+ * barrier nothing completes. The wait gives up, the kernel returns normally, and the next spinf_last_status reports
+ * SPINF_ST_TIMEOUT_OTHER; the context stays usable. Nothing faults and nothing hangs. */
+int spinf_selftest_bounded_wait(int64_t limit_ns, void* stream);
+
 /* ------------------------------------------------------------------------------------------------------------ fp8 row-wise linear
  * Replaces quant_act_row (spinf_serve/quant/linears.py:29-33): per row m of x [M,K] bf16,
  *   xs[m] = max(|x[m,:]|, 1e-12) / 448 (fp32);  x8[m,k] = e4m3_rne(clamp(float(x[m,k]) / xs[m], -448, 448)).

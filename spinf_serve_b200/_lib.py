@@ -21,6 +21,7 @@ SIGNATURES = {
     "spinf_version": (ctypes.c_int, []),
     "spinf_init": (ctypes.c_int, []),
     "spinf_last_status": (ctypes.c_int, [_p]),
+    "spinf_selftest_bounded_wait": (ctypes.c_int, [_i64, _p]),
     "spinf_fp8_rowwise_quant": (ctypes.c_int, [_p, _i64, _i64, _p, _p, _p]),
     "spinf_fp8_rowwise_gemm": (ctypes.c_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _p]),
     "spinf_abs_max": (ctypes.c_int, [_p, _i64, _p, _p]),

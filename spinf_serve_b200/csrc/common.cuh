@@ -82,7 +82,7 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parit
 
 // Bounded wait. The common case (already complete, or complete within a few polls) touches no timer; after that the wall
 // clock is read once per 1024 polls, so a wait that cannot complete gives up after WAIT_LIMIT_NS whatever a poll costs.
-__device__ __forceinline__ bool mbar_wait(const WaitCtx& w, uint64_t* bar, uint32_t parity, int code) {
+__device__ __forceinline__ bool mbar_wait(const WaitCtx& w, uint64_t* bar, uint32_t parity, int code, uint64_t limit_ns = WAIT_LIMIT_NS) {
   for (int i = 0; i < 64; ++i)
     if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
@@ -92,7 +92,7 @@ __device__ __forceinline__ bool mbar_wait(const WaitCtx& w, uint64_t* bar, uint3
       if (*w.abort_flag) return false;
       const uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > WAIT_LIMIT_NS) break;
+      else if (now - t0 > limit_ns) break;
     }
   }
   *w.abort_flag = 1;

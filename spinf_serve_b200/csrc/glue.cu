@@ -402,9 +402,39 @@ __global__ void rope_table_kernel(const int32_t* __restrict__ pos, int64_t n, in
   sin_t[i] = __float2bfloat16_rn(sinf(ang));
 }
 
+// ------------------------------------------------------------------------------------------------ self-test of the bounded wait
+// One CTA waits on a barrier that nothing will ever complete, with the limit the caller gives: the wait gives up, records
+// ST_TIMEOUT_OTHER in the device status word and the kernel returns normally, which is what every pipeline role of the library
+// does when a peer stops. Lets a test see the error path end to end without a fault and without a hang.
+__global__ void __launch_bounds__(32) bounded_wait_selftest_kernel(uint64_t limit_ns, int* __restrict__ status) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncwarp();
+  if (threadIdx.x == 0) {
+    const WaitCtx wc{&abort_flag, status};
+    mbar_wait(wc, &bar, 0u, ST_TIMEOUT_OTHER, limit_ns);
+  }
+}
+
 }  // namespace spinf
 
 using namespace spinf;
+
+extern "C" int spinf_selftest_bounded_wait(int64_t limit_ns, void* stream) {
+  SPINF_CHECK_ARG(limit_ns > 0 && limit_ns <= 1000000000ll);
+  int dev = 0;
+  SPINF_CUDA_OK(cudaGetDevice(&dev));
+  int* status = status_word(dev);
+  if (!status) return SPINF_ERR_CUDA;
+  bounded_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<uint64_t>(limit_ns), status);
+  SPINF_CUDA_OK(cudaGetLastError());
+  return 0;
+}
 
 extern "C" int spinf_fused_norm(const void* y, const int64_t* rows, const void* w1, const void* residual, const void* w2, int64_t n_out,
                                 int64_t hidden, float eps, int32_t plus1, void* out_h, void* out_norm, void* out_x8, float* out_xs,
