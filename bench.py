@@ -1,22 +1,31 @@
-"""Throughput of the packed-prefill scoring path on the benchmark configuration-2 workload.
+"""Throughput of the packed-prefill scoring path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P bench.py --gpus N ...
 
-One step = one pass of the hot path over one batch: the 24 contents x 56 two-option questions (1344 questions, 27408 real tokens)
-packed into one 27648-token stream and scored by the synthetic Gemma-style 12B with fp8 row-wise linears (random-init weights,
-uniform random token ids; the reference's benchmark text is not reproduced). Rank r of N scores its own 24 contents (replicas
-over a content-partitioned queue, no collective on the data path): weak scaling.
+Headline workload (benchmark configuration 2, at every N): one step = one pass of the hot path over one batch, the 24 contents x
+56 two-option questions (1344 questions, 27408 real tokens) packed into one 27648-token stream and scored by the synthetic
+Gemma-style 12B with fp8 row-wise linears (random-init weights, uniform random token ids; the reference's benchmark text is not
+reproduced). Rank r of N scores its own 24 contents (replicas, no collective on the data path): weak scaling.
 
-  value   questions/s with the packed inputs already resident in HBM (stack forward + option log-prob read), K steps between
-          CUDA events, max over ranks
-  e2e     the same through the public call Scorer.score_grouped with host inputs: one call over the K steps' contents (K forwards),
-          with packing, tile descriptors, pinned host->device copies, forward and device->host read of the log-probs of every
-          forward inside the timed region; the scorer's producer thread packs the next forward while the GPU runs this one
-  roofline   the row-wise fp8 GEMM (dominant kernel): algorithmic FLOPs / CUDA-event time of its launches in the timed region
+  value      questions/s with the packed inputs already resident in HBM (stack forward + option log-prob read), K steps between
+             CUDA events, max over ranks
+  e2e        the same through the public call Scorer.score_grouped with host inputs: one call over the K steps' contents, which
+             the packer turns into K forwards of the same 27648-token shape; packing, tile lists, the pinned host->device copy,
+             forward and device->host read of every forward's log-probs inside the timed region (the packing thread prepares the
+             next forward while the GPU runs this one). forwards / tokens report what actually ran.
+  roofline   the row-wise fp8 GEMM (dominant kernel): algorithmic FLOPs / CUDA-event time of its launches in the timed region,
+             against an fp8 peak measured in this run (torch._scaled_mm per-tensor 8192^3, burst and sustained)
+  attention  the tree attention alone on configuration 1 (2 contents x (470 + 8 x 16) tokens, H16 / Hkv8 / D256, N(0,1) inputs
+             with scale 1/16): time per launch (L2 flushed between launches), TFLOP/s on the unmasked pairs, tiles visited; and
+             its share and rate inside the configuration-2 step
+  bulk       benchmark configuration 3 in small: a seeded slice of the bulk workload (trunks U[200, 2000], 56 questions, branches
+             U[8, 24], 2-5 options, 32768-token passes) scored through the replica runner, the N replicas drawing content chunks
+             from one shared host-side queue: strong scaling (the slice is the same at every N), with per-rank busy fractions
+             and a bit-equality check of sampled contents scored alone
   cpu_baseline   the CPU oracle (a port of the reference's arithmetic; the reference has no CPU forward) on a bounded sample
 
---impl reference times that CPU oracle alone, with all host threads, and prints the same line with "impl": "reference"."""
+--impl reference times that CPU oracle alone, with all host threads, on the same sample, and prints the line with "impl": "reference"."""
 
 import argparse
 import json
@@ -33,6 +42,7 @@ if ROOT not in sys.path:
 METRIC = "questions scored/sec"
 UNIT = "questions/s"
 WORKLOAD = "cfg2: gemma-style 12B fp8 row-wise, 24 contents x (470-token trunk + 56 questions x 12 tokens, 2 single-token options), one 27648-token forward"
+CPU_SAMPLE = {"n_contents": 2, "layers": 2}  # the one sample both CPU legs time
 
 
 def _peaks():
@@ -82,10 +92,10 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------------ CPU arm (the oracle, a port)
-def cpu_sample(threads: int, n_contents: int = 2, layers: int = 1):
+def cpu_sample(threads: int, n_contents: int, layers: int):
     """the CPU oracle on a bounded sample of the workload: n_contents of the 24 contents (1142 tokens, 56 questions each) through
-    `layers` of the 48 layers plus the lm-head read of their rows; -> a closure that runs the sample once and returns
-    (seconds in the layers, seconds in the head read)"""
+    `layers` of the 48 layers plus the lm-head read of their rows; -> (a closure that runs the sample once and returns
+    (seconds in the layers, seconds in the head read), the sample's workload)"""
     import numpy as np
     import torch
 
@@ -93,6 +103,7 @@ def cpu_sample(threads: int, n_contents: int = 2, layers: int = 1):
     from oracle import head as OH
     from spinf_serve_b200 import packer as P
     from spinf_serve_b200 import workloads
+    from spinf_serve_b200.scorer import option_columns
 
     torch.set_num_threads(threads)
     cfg = OG.GemmaConfig(layers=layers)
@@ -115,7 +126,7 @@ def cpu_sample(threads: int, n_contents: int = 2, layers: int = 1):
     pk = P.Packer(32768, 65536, True, 1024)
     batches = [b for key, first, t in wl.items for b in pk.push((key, first), t)] + list(pk.flush())
     (b,) = batches
-    cols = sorted({int(t) for o in b.owners for pl in o.plans for t in pl.entry_tok})
+    cols = option_columns(b)
 
     def run():
         t0 = time.perf_counter()
@@ -128,38 +139,37 @@ def cpu_sample(threads: int, n_contents: int = 2, layers: int = 1):
     return run, wl
 
 
-def cpu_questions_per_s(layer_s: float, head_s: float, sample_tokens: int, sample_questions: int, sample_layers: int = 1):
-    """extrapolation of the sample to the full workload: layers x tokens for the forward, rows for the head"""
-    full = layer_s * (48 / sample_layers) * (27408 / sample_tokens) + head_s * (1344 / sample_questions)
-    return 1344 / full, full
+def cpu_extrapolate(layer_s: float, head_s: float, wl, layers: int, threads: int):
+    """the sample's times scaled to the full step (linear in layers x tokens for the forward, in rows for the head read)
+    -> (questions/s, the words that say what was timed and how it was scaled)"""
+    kl, kt, kr = 48 / layers, 27408 / wl.n_tokens, 1344 / wl.n_questions
+    full = layer_s * kl * kt + head_s * kr
+    words = (
+        f"CPU oracle port (torch fp32, {threads} threads) on {CPU_SAMPLE['n_contents']} of 24 contents ({wl.n_tokens} tokens, {wl.n_questions} questions) "
+        f"through {layers} of 48 layers ({layer_s:.2f} s) + the lm-head read of their rows ({head_s:.2f} s); extrapolated x{kl:.0f} in layers, "
+        f"x{kt:.1f} in tokens, x{kr:.0f} in read rows to the full step ({full:.0f} s)"
+    )
+    return 1344 / full, words
 
 
-def cpu_baseline(threads: int, steps: int = 1, n_contents: int = 8, layers: int = 2):
-    """the sample is sized for roughly ten seconds of CPU work on a 16-core host: 8 contents through 2 layers + their 448 read rows"""
-    run, wl = cpu_sample(threads, n_contents, layers)
-    times = [run() for _ in range(steps)]
-    layer_s = min(t[0] for t in times)
-    head_s = min(t[1] for t in times)
-    qps, full = cpu_questions_per_s(layer_s, head_s, wl.n_tokens, wl.n_questions, layers)
-    return {
-        "value": qps,
-        "unit": UNIT,
-        "cores": threads,
-        "kind": "port",
-        "sample": f"CPU oracle (torch fp32, {threads} threads) on {n_contents} of 24 contents ({wl.n_tokens} tokens, {wl.n_questions} questions) through {layers} of 48 layers "
-        f"({layer_s:.2f} s) + lm-head read of their rows ({head_s:.2f} s); scaled x{48 // layers} in layers, x{27408 / wl.n_tokens:.1f} in tokens and x{1344 // wl.n_questions} in rows "
-        f"to the full step ({full:.0f} s)",
-    }
+def cpu_baseline(threads: int, repeats: int = 4):
+    run, wl = cpu_sample(threads, **CPU_SAMPLE)
+    run()
+    times = [run() for _ in range(repeats)]
+    layer_s = sum(t[0] for t in times) / repeats
+    head_s = sum(t[1] for t in times) / repeats
+    qps, words = cpu_extrapolate(layer_s, head_s, wl, CPU_SAMPLE["layers"], threads)
+    return {"value": qps, "unit": UNIT, "cores": threads, "kind": "port", "sample": words + f"; mean of {repeats} runs after one warm-up"}
 
 
 def reference_arm(args):
     """--impl reference: the reference has no CPU forward of its own (its Scorer is CUDA-only), so this arm times the CPU oracle
-    assembled from its arithmetic, on the host cores, each step one bounded sample"""
+    assembled from its arithmetic, on the host cores, each step one run of the bounded sample; no GPU is used"""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    run, wl = cpu_sample(threads)
+    run, wl = cpu_sample(threads, **CPU_SAMPLE)
     for _ in range(min(args.warmup, 1)):
         run()
     t0 = time.perf_counter()
@@ -167,16 +177,12 @@ def reference_arm(args):
     wall = time.perf_counter() - t0
     layer_s = sum(t[0] for t in times) / len(times)
     head_s = sum(t[1] for t in times) / len(times)
-    qps, full = cpu_questions_per_s(layer_s, head_s, wl.n_tokens, wl.n_questions)
-    sample = (
-        f"CPU oracle port, {threads} threads: per step 2 of 24 contents ({wl.n_tokens} tokens) through 1 of 48 layers ({layer_s:.2f} s) + lm-head "
-        f"read of {wl.n_questions} rows ({head_s:.2f} s), scaled to the full step ({full:.0f} s)"
-    )
+    qps, words = cpu_extrapolate(layer_s, head_s, wl, CPU_SAMPLE["layers"], threads)
     line = {
-        "impl": "reference", "metric": METRIC, "value": qps, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": 1000 * wall / max(args.steps, 1), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3",
-        "data": "synthetic", "config": {"workload": WORKLOAD, "l2": "inputs larger than L2"},
-        "cpu_baseline": {"value": qps, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "impl": "reference", "metric": METRIC, "value": qps, "unit": UNIT, "n_gpus": 0, "n_gpus_requested": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1000 * wall / max(args.steps, 1), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp8_e4m3", "data": "synthetic", "config": {"workload": WORKLOAD, "l2": "inputs larger than L2", "step": "one run of the CPU sample"},
+        "cpu_baseline": {"value": qps, "unit": UNIT, "cores": threads, "kind": "port", "sample": words + f"; mean of {args.steps} steps"},
         "e2e": {"value": qps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -184,15 +190,146 @@ def reference_arm(args):
 
 
 # ------------------------------------------------------------------------------------------------ GPU arm
-def gpu_arm(args):
+def measure_fp8_peak(dev, seconds: float = 2.0):
+    """a library fp8 GEMM of the size the bf16 figures of MEASURED_PEAKS.json were taken at (8192^3, per-tensor scales, bf16 out):
+    best of 10 (burst) and back to back for `seconds` (sustained) -> TFLOP/s. The denominator of the fp8 roofline fraction."""
+    import torch
+
+    n = 8192
+    a = torch.randn((n, n), device=dev).to(torch.float8_e4m3fn)
+    b = torch.randn((n, n), device=dev).to(torch.float8_e4m3fn).t()
+    one = torch.ones((), dtype=torch.float32, device=dev)
+    flops = 2.0 * n**3
+
+    def mm():
+        return torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+
+    for _ in range(3):
+        mm()
+    best = 0.0
+    for _ in range(10):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        mm()
+        e1.record()
+        e1.synchronize()
+        best = max(best, flops / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = max(int(seconds / (flops / (best * 1e12))), 10)
+    e0.record()
+    for _ in range(reps):
+        mm()
+    e1.record()
+    e1.synchronize()
+    return {"burst": best, "sustained": reps * flops / (e0.elapsed_time(e1) * 1e-3) / 1e12}
+
+
+def attention_alone(dev, peaks, repeats: int = 30):
+    """benchmark configuration 1: the tree attention on 2 contents x (470-token trunk + 8 branches of 16), H16 / Hkv8 / D256,
+    Q K V ~ N(0,1) bf16 seed 0 with scale 1/16; L2 flushed (a 256 MB write) before every timed launch"""
+    import torch
+
+    from spinf_serve_b200 import attention, workloads
+    from spinf_serve_b200.packer import Packer
+
+    wl = workloads.config1(seed=0)
+    pk = Packer(16384, 65536, True, 1024)
+    (b,) = [x for key, first, t in wl.items for x in pk.push((key, first), t)] + list(pk.flush())
+    n, H, K, D = b.length, 16, 8, 256
+    g = torch.Generator().manual_seed(0)
+    q, k, v = (torch.randn((n, h, D), generator=g).to(torch.bfloat16).to(dev) for h in (H, K, K))
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    out = {}
+    for name, window in (("full", None), ("sliding_1024", 1024)):
+        mask = attention.stream_masks(b.art, b.end, b.pos, window, dev, always_window=True)["sliding_attention" if window else "full_attention"]
+        pairs = workloads.attended_pairs(b, window)
+        flops = 4.0 * D * H * pairs
+        for _ in range(3):
+            attention.tree_attention(q, k, v, mask, 1.0 / 16)
+        ms = []
+        for _ in range(repeats):
+            flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            attention.tree_attention(q, k, v, mask, 1.0 / 16)
+            e1.record()
+            e1.synchronize()
+            ms.append(e0.elapsed_time(e1))
+        ms.sort()
+        med = ms[len(ms) // 2]
+        nb = n // 128
+        out[name] = {
+            "ms": med, "ms_min": ms[0], "unmasked_pairs": pairs, "unmasked_gflop": flops / 1e9, "tflops_unmasked": flops / (med * 1e-3) / 1e12,
+            "frac_of_bf16_burst": flops / (med * 1e-3) / 1e12 / peaks["bf16_burst"], "tiles_visited": mask.visited, "tiles_causal": nb * (nb + 1) // 2,
+            "tiles_total": nb * nb,
+        }
+    return {"workload": "cfg1: 2 contents x (470 + 8 x 16) tokens in a 1280-row stream, H16/Hkv8/D256, N(0,1) bf16 inputs, scale 1/16", "l2": "flushed before every launch", **out}
+
+
+def bulk_leg(args, stack, dev, rank, world, sync, host_group):
+    """benchmark configuration 3 in small, through the replica runner with a shared content queue (strong scaling)"""
     import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from spinf_serve_b200 import replicas, workloads
+    from spinf_serve_b200.scorer import EngineConfig, Scorer
+
+    n = args.bulk_contents
+    t0 = time.perf_counter()
+    wl = workloads.bulk_slice(seed=0, n_contents=n)
+    gen_s = time.perf_counter() - t0
+    scorer = Scorer(stack, EngineConfig(token_budget=32768, max_tokens=65536, prefetch=2), dev)
+    scorer.score_grouped(wl.items[: min(n, 32)])  # warm-up: two passes of this shape
+    s0 = (scorer.stats.forwards, scorer.stats.tokens, scorer.stats.busy_s, scorer.stats.stall_s)
+    sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    w0 = time.perf_counter()
+    e0.record()
+    merged, queue = replicas.score_queued(scorer, wl.items, chunk=8, group=host_group, name=f"spinf/bulk/{args.steps}/{n}")
+    e1.record()
+    sync()
+    wall = time.perf_counter() - w0
+    ms = e0.elapsed_time(e1)
+    mine = [scorer.stats.forwards - s0[0], scorer.stats.tokens - s0[1], scorer.stats.busy_s - s0[2], scorer.stats.stall_s - s0[3], wall, float(len(queue.taken))]
+    per_rank = [mine]
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+        parts = [None] * world if rank == 0 else None
+        dist.gather_object(mine, parts, dst=0, group=host_group)
+        per_rank = parts
+    if rank != 0:
+        return None
+    # contents scored alone must equal, bit for bit, what the replicas returned for them (whatever they were packed with)
+    sample = sorted({0, 1, n // 3, n // 2, n - 1})
+    same = True
+    for c in sample:
+        alone = scorer.score_grouped([wl.items[c]])
+        key = wl.items[c][0]
+        same &= all(np.array_equal(a, m) for a, m in zip(alone[key], merged[key]))
+    missing = sum(1 for key, _, _ in wl.items if key not in merged or any(v is None for v in merged[key]))
+    return {
+        "workload": f"cfg3 slice: {n} contents (trunks U[200,2000], 56 questions, branches U[8,24], 2-5 options; seed 0, per-content streams), 32768-token passes",
+        "scaling": "strong", "value": wl.n_questions / (ms * 1e-3), "unit": UNIT, "tokens_per_s": wl.n_tokens / (ms * 1e-3), "ms": ms, "questions": wl.n_questions,
+        "tokens": wl.n_tokens, "queue": "shared counter in the process group's host-side store, chunks of 8 contents; no collective on the data path",
+        "per_rank": [
+            {"forwards": int(p[0]), "tokens": int(p[1]), "gpu_busy_fraction": round(p[2] / p[4], 4), "waited_for_packing_s": round(p[3], 3), "chunks": int(p[5])}
+            for p in per_rank
+        ],
+        "contents_missing": missing, "alone_equals_packed_bitwise": bool(same), "sampled_contents": sample, "host_generation_s": round(gen_s, 2),
+    }
+
+
+def gpu_arm(args):
     import torch
     import torch.distributed as dist
 
     from spinf_serve_b200 import _lib, ops, workloads
     from spinf_serve_b200.gemma_stack import CONFIGS, GemmaConfig, GemmaStack, GemmaWeights
     from spinf_serve_b200.packer import Packer
-    from spinf_serve_b200.scorer import EngineConfig, Scorer
+    from spinf_serve_b200.scorer import EngineConfig, Scorer, stage_one
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -201,8 +338,10 @@ def gpu_arm(args):
         raise RuntimeError("bench.py needs a CUDA device: the scoring path has no CPU fallback (use --impl reference for the CPU arm)")
     dev = torch.device(f"cuda:{local}")
     torch.cuda.set_device(dev)
+    host_group = None
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+        host_group = dist.new_group(backend="gloo")  # host objects (results, counters) travel over gloo, never over the GPUs
     _lib.init(dev)
 
     cfg = GemmaConfig(**CONFIGS["gemma12b"])
@@ -214,18 +353,16 @@ def gpu_arm(args):
     # ---- device-resident leg: the packed batch, its masks, the read rows and the option columns are staged once
     pk = Packer(ecfg.token_budget, ecfg.max_tokens, ecfg.align_jobs, ecfg.min_stream)
     batches = [b for key, first, t in wl.items for b in pk.push((key, first), t)] + list(pk.flush())
-    assert len(batches) == 1, "configuration 2 is one forward"
+    if len(batches) != 1 or batches[0].length != 27648:
+        raise RuntimeError(f"configuration 2 should pack into one 27648-token forward, got {[b.length for b in batches]}")
     b = batches[0]
-    cols = Scorer._cols(b)
-    inputs = stack.stage(b, dev)
-    sel = torch.from_numpy(b.sel).to(dev)
-    ci = torch.tensor(cols, dtype=torch.int32, device=dev)
+    sc, inputs, masks, st = stage_one(stack, b, dev, ecfg)
     W = stack.w.lm_weight
-    ws = torch.empty(int(_lib.lib().spinf_option_logprobs_workspace_bytes(len(b.sel), W.shape[0], len(cols))), dtype=torch.uint8, device=dev)
+    ws = torch.empty(int(_lib.lib().spinf_option_logprobs_workspace_bytes(len(b.sel), W.shape[0], st["cols"].numel())), dtype=torch.uint8, device=dev)
 
     def step():
-        rows = stack.forward(inputs, rows=sel)
-        return ops.option_logprobs(rows, W, ci, None, ws)
+        rows = stack.forward(sc, b, inputs, masks, rows=st["sel"])
+        return ops.option_logprobs(rows, W, st["cols"], None, ws)
 
     def sync():
         if world > 1:
@@ -251,16 +388,15 @@ def gpu_arm(args):
     prof, ops.PROFILE = ops.PROFILE, None
     ms = e0.elapsed_time(e1)
     _lib.last_status()
-    assert bool(torch.isfinite(lp).all()), "non-finite log-probs"
+    if not bool(torch.isfinite(lp).all()):
+        raise RuntimeError("non-finite log-probs")
 
-    # ---- end-to-end leg: ONE public call with host inputs over the contents of all the steps (a bulk request: `steps` x 24
-    # contents = `steps` forwards). Every forward's batch is packed, described, staged through pinned memory, run and read back
-    # inside the timed region; the scorer's producer thread packs forward i + 1 while the GPU runs forward i, which is the
-    # overlap the reference's Scorer._execute provides (spinf_serve/scorer.py:432-510).
+    # ---- end-to-end leg: ONE public call with host inputs over the contents of all the steps (a bulk request of `steps` x 24
+    # contents; the 27648-token budget makes every forward the shape of the resident leg's step)
     for _ in range(min(args.warmup, 2)):
         scorer.score_grouped(wl.items)
     bulk = [((s,) + tuple(key), first, tree) for s in range(args.steps) for key, first, tree in wl.items]
-    f0_forwards = scorer.stats.forwards
+    s0 = (scorer.stats.forwards, scorer.stats.tokens, scorer.stats.h2d_bytes, scorer.stats.d2h_bytes, scorer.stats.stall_s)
     sync()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     f0.record()
@@ -269,24 +405,29 @@ def gpu_arm(args):
     sync()
     ms_e2e = f0.elapsed_time(f1)
     clocks = sampler.stop() if rank == 0 else None
-    assert len(out) == len(bulk) and scorer.stats.forwards - f0_forwards == args.steps, "one forward per step"
+    forwards = scorer.stats.forwards - s0[0]
+    e2e_tokens = scorer.stats.tokens - s0[1]
+    h2d, d2h = scorer.stats.h2d_bytes - s0[2], scorer.stats.d2h_bytes - s0[3]
+    scored = sum(1 for v in out.values() for x in v if x is not None)
+
+    attn1 = attention_alone(dev, _peaks()) if rank == 0 and not args.no_attention else None
+    bulk_block = bulk_leg(args, stack, dev, rank, world, sync, host_group) if args.bulk_contents > 0 else None
 
     if world > 1:
         t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, ms_e2e = float(t[0]), float(t[1])
     if rank == 0:
-        masks = inputs["masks"]
-        n = b.length
-        h2d = n * 8 + 3 * n * 4 + len(b.sel) * 8 + len(cols) * 4
-        for m in (masks["full_attention"], masks["sliding_attention"]):
-            h2d += m.offsets.numel() * 4 + m.blocks.numel() * 4 + m.flags.numel()
-        d2h = len(b.sel) * len(cols) * 4
         peaks = _peaks()
-        fp8_peak = 2.0 * peaks["bf16_sustained"]
-        gemm_ms = sum(a.elapsed_time(c) for a, c, _ in prof)
-        gemm_flops = sum(f for _, _, f in prof)
+        fp8 = measure_fp8_peak(dev)
+        gemm = [(a.elapsed_time(c), f) for a, c, f, kind in prof if kind == "fp8_gemm"]
+        gemm_ms, gemm_flops = sum(t for t, _ in gemm), sum(f for _, f in gemm)
         achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
+        attn_ms = {w: sum(a.elapsed_time(c) for a, c, _, kind in prof if kind == f"attn:{w}") for w in (0, cfg.window)}
+        n_full = sum(1 for t in cfg.layer_types if t == "full_attention")
+        pairs = {0: workloads.attended_pairs(b), cfg.window: workloads.attended_pairs(b, cfg.window)}
+        attn_flops = 4.0 * cfg.head_dim * cfg.heads * (pairs[0] * n_full + pairs[cfg.window] * (cfg.layers - n_full)) * args.steps
+        attn_total_ms = sum(attn_ms.values())
         step_flops = workloads.gemm_flops(cfg, wl.n_tokens) + workloads.head_flops(cfg, wl.n_questions)
         line = {
             "metric": METRIC, "value": world * wl.n_questions * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
@@ -297,25 +438,41 @@ def gpu_arm(args):
                 "l2": "inputs larger than L2 (10.8 GB of weights and >2 GB of activations per step)",
                 "tiles_visited": masks["full_attention"].visited, "tiles_skipped_fraction": round(masks["full_attention"].skipped_fraction, 4),
             },
-            "e2e": {"value": world * wl.n_questions * args.steps / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
-                    "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
+            "e2e": {
+                "value": world * scored / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e / max(forwards, 1),
+                "h2d_bytes_per_step": int(h2d // max(forwards, 1)), "d2h_bytes_per_step": int(d2h // max(forwards, 1)),
+                "forwards": forwards, "tokens": e2e_tokens, "questions_scored_per_gpu": scored, "forwards_match_steps": forwards == args.steps,
+                "waited_for_packing_s": round(scorer.stats.stall_s - s0[4], 3),
+            },
             "gpu_launches": int(launches),
             "roofline": {
                 "kernel": "gemm_tc_kernel<fp8, 256, *> (row-wise fp8 linear: q|k|v, o, gate|up with the GeGLU epilogue, down)", "bound": "tensor",
-                "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s", "frac": achieved / fp8_peak,
-                # DRAM bytes per launch: the ncu capture of the down-projection shape at M = 8192 (profiles/fp8_gemm_down_proj_M8192.md:
-                # 588.8 MB for 966.4 GFLOP), scaled by FLOPs to this run's average launch
-                "traffic": 588.8e6 / 966.4e9 * (gemm_flops / max(len(prof), 1)), "traffic_unit": "bytes per launch (scaled from a smaller capture)",
-                "peak_source": f"2 x bf16 sustained of {peaks['source']} (no fp8 figure in MEASURED_PEAKS.json)",
-                "launches": len(prof), "share_of_step": gemm_ms / ms if ms > 0 else None,
+                "achieved": achieved, "peak": fp8["sustained"], "unit": "TFLOP/s", "frac": achieved / fp8["sustained"],
+                "peak_source": "library per-tensor fp8 GEMM 8192^3 measured in this run, back to back for 2 s (the kernel is timed inside a long step)",
+                "peak_burst": fp8["burst"], "frac_of_burst": achieved / fp8["burst"], "frac_of_nominal_4500": achieved / 4500.0,
+                "bf16_peaks": {"burst": peaks["bf16_burst"], "sustained": peaks["bf16_sustained"], "source": peaks["source"]},
+                "traffic": 588.8e6 / 966.4e9 * (gemm_flops / max(len(gemm), 1)),
+                "traffic_source": "not measured in this run: DRAM bytes of an ncu capture of the down-projection shape at M = 8192 (588.8 MB per 966.4 GFLOP), scaled by FLOPs to this run's average launch",
+                "launches": len(gemm), "share_of_step": gemm_ms / ms if ms > 0 else None,
                 "step_tflops_all_kernels": step_flops * args.steps / (ms * 1e-3) / 1e12,
             },
+            "attention": {
+                "in_step": {
+                    "ms_per_step": attn_total_ms / args.steps, "share_of_step": attn_total_ms / ms if ms > 0 else None,
+                    "unmasked_tflop_per_step": attn_flops / args.steps / 1e12,
+                    "tflops_unmasked": attn_flops / (attn_total_ms * 1e-3) / 1e12 if attn_total_ms > 0 else None,
+                    "frac_of_bf16_sustained": attn_flops / (attn_total_ms * 1e-3) / 1e12 / peaks["bf16_sustained"] if attn_total_ms > 0 else None,
+                },
+                "alone_cfg1": attn1,
+            },
+            "bulk": bulk_block,
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(os.cpu_count() or 1)
         print(json.dumps(line))
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 
@@ -325,6 +482,8 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--bulk-contents", type=int, default=2624, help="contents of the bulk (configuration-3) leg, about 160 passes; 0 skips the leg")
+    ap.add_argument("--no-attention", action="store_true", help="skip the attention-alone (configuration-1) block")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle timing (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":

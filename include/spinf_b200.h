@@ -182,7 +182,8 @@ int spinf_option_logprobs(const void* h, const void* W, int64_t R, int64_t hidde
  * resident on every GPU that loads the library until the process exits) instead of a caller workspace.
  *   - limit: 256 + 8 * ceil(vocab / 256) * (ceil(R / 128) * 128) + 4 * (ceil(vocab / 256) + 1) bytes must fit in that array
  *     (e.g. R <= 1024 rows at vocab 262144, R <= 2048 at vocab 131072); larger calls return SPINF_ERR_TOO_LARGE and launch nothing;
- *   - the call itself performs no cudaMalloc / cudaFree and calls no allocating routine; spinf_init is not required;
+ *   - the call itself performs no cudaMalloc / cudaFree and calls no allocating routine; spinf_init is not required (the first
+ *     call on a device also sets the kernel's shared-memory attribute, once);
  *   - the first call on a device resolves the array's device address (cudaGetSymbolAddress): make that first call outside any
  *     stream capture;
  *   - all calls on a device share the one array: the array keeps the previous call's contents, none of which is read before being

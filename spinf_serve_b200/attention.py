@@ -31,40 +31,75 @@ class TileMask:
     skipped_fraction: float
 
 
-def stream_masks(art, end, pos, window, device, always_window=True):
-    """{"full_attention": TileMask, "sliding_attention": TileMask} for one packed stream, as Scorer._block_masks builds them
-    (spinf_serve/scorer.py:207-238): the sliding table is used when a position reaches the window or always_window is set (aligned
-    jobs), else sliding layers share the full table. Host arrays go up through pinned memory on the current stream."""
+@dataclass
+class HostTiles:
+    """the host half of a stream's masks: the per-token arrays and the tile lists of both layer types, built ahead of the GPU (the
+    scorer's producer thread); `sliding` is None when sliding layers share the full table"""
+
+    art: np.ndarray
+    end: np.ndarray
+    pos: np.ndarray
+    window: int
+    full: "packer.TileDesc"
+    sliding: "packer.TileDesc | None"
+
+    @property
+    def n(self) -> int:
+        return len(self.art)
+
+    def arrays(self) -> dict:
+        """name -> array, everything the device half needs (one staging copy carries them all)"""
+        out = {"art": self.art, "end": self.end, "pos32": self.pos}
+        for name, td in (("full", self.full), ("sliding", self.sliding)):
+            if td is not None:
+                out[name + ".offsets"] = td.offsets
+                out[name + ".blocks"] = td.blocks if len(td.blocks) else np.zeros(1, np.int32)
+                out[name + ".flags"] = td.flags if len(td.flags) else np.zeros(1, np.uint8)
+        return out
+
+
+def host_tiles(art, end, pos, window, always_window=True) -> HostTiles:
+    """the tile lists of one packed stream as Scorer._block_masks takes them from block_tables (spinf_serve/scorer.py:207-238,
+    packer.py:426-491): the sliding table is used when a position reaches the window or always_window is set (aligned jobs),
+    else sliding layers share the full table. Host work only (the library's C++ descriptor builder)."""
     art = np.ascontiguousarray(art, np.int32)
     end = np.ascontiguousarray(end, np.int32)
     pos = np.ascontiguousarray(pos, np.int32)
     n = len(art)
     if n % packer.BLOCK:
         raise SpinfError(f"stream length {n} is not a multiple of {packer.BLOCK}")
+    binding = window is not None and (always_window or (n > 0 and int(pos.max()) >= window))
+    return HostTiles(art, end, pos, int(window or 0), packer.tile_desc(art, end, pos, None), packer.tile_desc(art, end, pos, window) if binding else None)
 
-    def up(a):
-        return torch.from_numpy(a).pin_memory().to(device, non_blocking=True)
 
-    d_art, d_end, d_pos = up(art), up(end), up(pos)
+def device_masks(ht: HostTiles, st: dict, device) -> dict:
+    """the device half: st maps the names of HostTiles.arrays() to device tensors (already copied, or in flight on the current
+    stream). Evaluates the mask rule once per layer type (spinf_tile_mask_bits): every layer of the type and every head reads
+    those words. -> {"full_attention": TileMask, "sliding_attention": TileMask}"""
+    n = ht.n
 
-    def one(w):
-        td = packer.tile_desc(art, end, pos, w)
-        blocks = td.blocks if len(td.blocks) else np.zeros(1, np.int32)
-        flags = td.flags if len(td.flags) else np.zeros(1, np.uint8)
-        d_off, d_blocks = up(td.offsets), up(blocks)
-        # the mask rule, evaluated once for the stream: every layer of this type and every head reads these words
-        bits = torch.empty((len(blocks), 2, packer.BLOCK), dtype=torch.int64, device=device)
+    def one(name, td, w):
+        d_off, d_blocks, d_flags = st[name + ".offsets"], st[name + ".blocks"], st[name + ".flags"]
+        bits = torch.empty((d_blocks.numel(), 2, packer.BLOCK), dtype=torch.int64, device=device)
         if n:
             check(
-                _lib.lib().spinf_tile_mask_bits(ptr(d_art), ptr(d_end), ptr(d_pos), n, int(w or 0), ptr(d_off), ptr(d_blocks), ptr(bits), stream_ptr()),
+                _lib.lib().spinf_tile_mask_bits(ptr(st["art"]), ptr(st["end"]), ptr(st["pos32"]), n, int(w), ptr(d_off), ptr(d_blocks), ptr(bits),
+                                                stream_ptr()),
                 "spinf_tile_mask_bits",
             )
             ops.COUNTS["launches"] += 1
-        return TileMask(d_art, d_end, d_pos, d_off, d_blocks, up(flags), bits, int(w or 0), n, td.visited, td.skipped_fraction)
+        return TileMask(st["art"], st["end"], st["pos32"], d_off, d_blocks, d_flags, bits, int(w), n, td.visited, td.skipped_fraction)
 
-    full = one(None)
-    binding = window is not None and (always_window or (n > 0 and int(pos.max()) >= window))
-    return {"full_attention": full, "sliding_attention": one(window) if binding else full}
+    full = one("full", ht.full, 0)
+    return {"full_attention": full, "sliding_attention": one("sliding", ht.sliding, ht.window) if ht.sliding is not None else full}
+
+
+def stream_masks(art, end, pos, window, device, always_window=True):
+    """host_tiles + device_masks in one call, each array going up through pinned memory on the current stream (one-off streams:
+    tests, calibration; the scorer stages a forward's arrays in one copy instead)"""
+    ht = host_tiles(art, end, pos, window, always_window)
+    st = {k: torch.from_numpy(a).pin_memory().to(device, non_blocking=True) for k, a in ht.arrays().items()}
+    return device_masks(ht, st, device)
 
 
 def tree_attention(q, k, v, mask: TileMask, scale: float, out=None, row_amax=None):
@@ -80,6 +115,10 @@ def tree_attention(q, k, v, mask: TileMask, scale: float, out=None, row_amax=Non
     _lib.init(q.device)
     if out is None:
         out = torch.empty((n, H, D), dtype=torch.bfloat16, device=q.device)
+    prof = ops.PROFILE
+    if prof is not None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
     check(
         _lib.lib().spinf_tree_attn_fwd(
             ptr(q), ptr(k), ptr(v), ptr(out), n, H, Hkv, D, q.stride(0), k.stride(0), out.stride(0), ptr(mask.art), ptr(mask.end),
@@ -88,6 +127,9 @@ def tree_attention(q, k, v, mask: TileMask, scale: float, out=None, row_amax=Non
         ),
         "spinf_tree_attn_fwd",
     )
+    if prof is not None:
+        e1.record()
+        prof.append((e0, e1, 0.0, f"attn:{mask.window}"))
     ops.COUNTS["launches"] += 1
     return out
 

@@ -22,6 +22,7 @@
 // Numerics follow the reference's attention (bf16 Q/K/V, fp32 scores and softmax state, P rounded to bf16 before P V, fp32
 // accumulation). Reduction order per row = ascending key tiles of the row's own job, independent of what else is packed in the
 // stream; tiles flagged "no mask" only skip the mask evaluation, never change the arithmetic.
+#include <atomic>
 #include "common.cuh"
 #include "host_util.h"
 
@@ -84,15 +85,6 @@ __device__ __forceinline__ AttnItem attn_item(const AttnArgs& a, int it) {
   return r;
 }
 
-#ifdef SPINF_TRACE
-// debugging aid, compiled out of the library: cycles one softmax thread per CTA spends per phase, summed over tiles / items
-__device__ unsigned long long g_attn_trace[16];
-#define TR(var) const long long var = clock64()
-#define TR_ADD(slot, v) if (threadIdx.x == 64) atomicAdd(&g_attn_trace[slot], static_cast<unsigned long long>(v))
-#else
-#define TR(var)
-#define TR_ADD(slot, v)
-#endif
 
 // ---------------------------------------------------------------- CTA pairs (thread-block clusters of 2, tcgen05 cta_group::2)
 // PAIR = true: the two 64-row halves of a query block (same two heads, same tile list) run in the two CTAs of a cluster and share
@@ -406,7 +398,6 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int head = w.h0 + row / rows_per_head;
       const int tq = w.qb * 128 + w.row0 + (row % rows_per_head);  // stream position of this thread's query row
       const int rowb = w.row0 + (row % rows_per_head);            // row within the query block
-      TR(t_item0);
       float m_ref = -INFINITY, l_run = 0.f;
 
       for (int i = 0; i < n_tiles; ++i) {
@@ -419,9 +410,7 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           f_next = a.tile_flags[e0 + i + 1];
           bits_next = (f_next & 2) ? ~0ull : a.tile_bits[(static_cast<int64_t>(e0 + i + 1) * 2 + wg) * 128 + rowb];
         }
-        TR(t0);
         bool got = j >= 0 && j < a.nb && mbar_wait(wc, &s_full[(g & 1u) * 2 + wg], (g >> 1) & 1u, ST_TIMEOUT_TMEM);
-        TR(t1);
         float s[KH];
         float mx = -INFINITY;
         const uint32_t s_tmem = tmem_base + lane_off + (g & 1u) * 128 + wg * KH;
@@ -449,9 +438,7 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         // the two groups exchange their halves' row maxima: every decision below is taken on the maximum over the whole tile
         float* xq = xchg + (g & 1u) * 256;
         xq[wg * 128 + row] = mx;
-        TR(t2);
         if (!bar_red_and(1 + qd, 64, got)) { alive = false; break; }  // the two warps that share these rows leave together
-        TR(t3);
         mx = fmaxf(mx, xq[(wg ^ 1) * 128 + row]) * a.scale_log2;
         // move the reference maximum only when the row's maximum has grown by more than the threshold
         float alpha = 1.f;
@@ -470,7 +457,6 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           pk[c] = pack_bf16x2(p0, p1);
         }
         l_run = l_run * alpha + (sum0 + sum1);
-        TR(t4);
         if (i > 0) {
           // P V of the previous tile is waited for at every tile, not only before a rescale: a parity wait is only unambiguous
           // while the waiter is at most one phase ahead of the barrier
@@ -492,7 +478,6 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
         }
         __syncwarp();
-        TR(t5);
         tmem_st_x32(s_tmem, pk);  // P over the first 32 columns of the S half this thread has already read
         tmem_wait_st();
         tc_fence_before();
@@ -503,8 +488,6 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           else
             mbar_arrive(p_ready);
         }
-        TR(t6);
-        TR_ADD(0, t1 - t0); TR_ADD(1, t2 - t1); TR_ADD(2, t3 - t2); TR_ADD(3, t4 - t3); TR_ADD(4, t5 - t4); TR_ADD(5, t6 - t5); TR_ADD(6, 1);
       }
       if (!alive) break;
       gt += n_tiles;
@@ -514,10 +497,8 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       float* xq = xchg + 2 * 256;  // its own buffer: the next item's first tile may already be writing maxima
       xq[wg * 128 + row] = l_run;
       if (have_n) first_entry(w_n, pe0, pe1);  // lands while O is read out
-      TR(t_e0);
       const bool got = mbar_wait(wc, o_done, g_last & 1u, ST_TIMEOUT_TMEM);
       if (!bar_red_and(1 + qd, 64, got)) { alive = false; break; }
-      TR(t_e1);
       tc_fence_after();
       const float inv = 1.f / (l_run + xq[(wg ^ 1) * 128 + row]);  // every row sees at least itself, so the sum is positive
       __nv_bfloat16* dst = a.out + static_cast<int64_t>(tq) * a.out_pitch + head * D + wg * (D / 2);
@@ -556,8 +537,6 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       // non-negative floats order like their bit patterns, so the merged maximum does not depend on the order of arrival
       if (a.row_amax) atomicMax(reinterpret_cast<unsigned int*>(a.row_amax + tq), __float_as_uint(fmaxf(bf2_lo(amax2), bf2_hi(amax2))));
-      TR(t_e2);
-      TR_ADD(8, t_e1 - t_e0); TR_ADD(9, t_e2 - t_e1); TR_ADD(10, t_e2 - t_item0); TR_ADD(11, 1);
       ++item_n;
     }
   }
@@ -630,10 +609,10 @@ static int launch_attn(const void* q, const void* k, const void* v, int64_t n, i
   if ((r = make_tmap_2d(&tmV, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, v, n, static_cast<uint64_t>(Hkv) * D, kv_pitch * 2, 64, PAIR ? 128 : KH)))
     return r;
   auto kern = tree_attn_kernel<D, PAIR>;
-  static bool attr_set[64] = {false};
-  if (!attr_set[dev]) {
+  static std::atomic<bool> attr_set[64];  // zero-initialised; setting the attribute twice from two threads is harmless
+  if (!attr_set[dev].load(std::memory_order_acquire)) {
     SPINF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
-    attr_set[dev] = true;
+    attr_set[dev].store(true, std::memory_order_release);
   }
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(ATTN_THREADS);
@@ -665,7 +644,6 @@ extern "C" int spinf_tile_mask_bits(const int32_t* art, const int32_t* end, cons
                                     const int32_t* tile_offsets, const int32_t* tile_blocks, uint64_t* bits, void* stream) {
   if (n == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(art && end && pos && tile_offsets && tile_blocks && bits && n >= 0 && n % SPINF_BLOCK == 0 && n < (1ll << 30));
-  if (n == 0) return 0;
   const int nb = static_cast<int>(n / SPINF_BLOCK);
   tile_mask_bits_kernel<<<nb, 256, 0, static_cast<cudaStream_t>(stream)>>>(art, end, pos, nb, window, tile_offsets, tile_blocks, bits);
   SPINF_CUDA_OK(cudaGetLastError());
@@ -685,7 +663,6 @@ extern "C" int spinf_tree_attn_fwd(const void* q, const void* k, const void* v, 
   // rows of the output are written as 32-byte pieces
   SPINF_CHECK_ARG(q_pitch % 8 == 0 && kv_pitch % 8 == 0 && out_pitch % 16 == 0 && (reinterpret_cast<uintptr_t>(out) & 31) == 0);
   SPINF_CHECK_ARG(scale > 0.f && n / SPINF_BLOCK * static_cast<int64_t>(H) < (1ll << 31));
-  if (n == 0) return 0;
   AttnArgs a;
   a.out = static_cast<__nv_bfloat16*>(out);
   a.out_pitch = out_pitch;
@@ -714,12 +691,3 @@ extern "C" int spinf_tree_attn_fwd(const void* q, const void* k, const void* v, 
               : launch_attn<128, false>(q, k, v, n, H, Hkv, q_pitch, kv_pitch, a, st);
 }
 
-#ifdef SPINF_TRACE
-extern "C" int spinf_attn_trace_read(unsigned long long* out) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out, spinf::g_attn_trace, sizeof(unsigned long long) * 16);
-  unsigned long long z[16] = {0};
-  cudaMemcpyToSymbol(spinf::g_attn_trace, z, sizeof(z));
-  return 0;
-}
-#endif

@@ -9,6 +9,7 @@
 //     S *= exp(g);  v' = (v - S^T k) beta;  S += k (x) v';  o = S^T (q scale)
 // gdn_prologue_kernel / gdn_epilogue_kernel: the bandwidth-bound steps around it (path convolution + SiLU, l2 norms, beta, g;
 // gated RMS norm), one pass over the rows each.
+#include <atomic>
 #include "common.cuh"
 #include "host_util.h"
 
@@ -322,7 +323,6 @@ extern "C" int spinf_gdn_recurrent(const void* q, const void* k, const void* v, 
   // rows are copied in 16-byte pieces, beta as the aligned 4-byte word around it
   SPINF_CHECK_ARG(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) == 0);
   SPINF_CHECK_ARG(v_pitch % 8 == 0 && g_pitch % 2 == 0 && Hv % 2 == 0 && (reinterpret_cast<uintptr_t>(beta) & 3) == 0);
-  if (n_seg == 0) return 0;
   int dev = 0;
   SPINF_CUDA_OK(cudaGetDevice(&dev));
   int* status = status_word(dev);
@@ -344,19 +344,18 @@ extern "C" int spinf_gdn_prologue(const void* y, int64_t y_pitch, int64_t n_rows
   SPINF_CHECK_ARG(y && conv && conv_w && A_log && dt_bias && q && k && v && g && beta && T >= 0 && n_rows >= T);
   SPINF_CHECK_ARG(K == GK && V == GV && Hk > 0 && Hv > 0 && Hv <= 256 && Hk <= 96 && T < (1ll << 31));
   SPINF_CHECK_ARG(y_pitch >= 2ll * Hk * GK + 2ll * Hv * GV + 2 * Hv && y_pitch % 8 == 0);
-  if (T == 0) return 0;
   GdnProArgs a;
   a.y = static_cast<const __nv_bfloat16*>(y), a.y_pitch = y_pitch, a.n_rows = n_rows, a.conv = conv;
   a.conv_w = static_cast<const __nv_bfloat16*>(conv_w), a.A_log = A_log, a.dt_bias = dt_bias;
   a.q = static_cast<__nv_bfloat16*>(q), a.k = static_cast<__nv_bfloat16*>(k), a.v = static_cast<__nv_bfloat16*>(v);
   a.g = g, a.beta = static_cast<__nv_bfloat16*>(beta), a.Hk = Hk, a.Hv = Hv;
   const size_t smem = static_cast<size_t>(2) * Hk * GK * sizeof(float);
-  static bool attr_set[64] = {false};
+  static std::atomic<bool> attr_set[64];  // zero-initialised; setting the attribute twice from two threads is harmless
   int dev = 0;
   SPINF_CUDA_OK(cudaGetDevice(&dev));
-  if (!attr_set[dev]) {
+  if (!attr_set[dev].load(std::memory_order_acquire)) {
     SPINF_CUDA_OK(cudaFuncSetAttribute(gdn_prologue_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 96 * GK * 4));
-    attr_set[dev] = true;
+    attr_set[dev].store(true, std::memory_order_release);
   }
   gdn_prologue_kernel<<<static_cast<unsigned>(T), 256, smem, static_cast<cudaStream_t>(stream)>>>(a);
   SPINF_CUDA_OK(cudaGetLastError());
@@ -367,7 +366,6 @@ extern "C" int spinf_gdn_epilogue(const void* o, const void* z, int64_t z_pitch,
                                   int32_t V, void* out, void* stream) {
   if (T == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(o && z && norm_w && out && T >= 0 && Hv > 0 && V == GV && z_pitch >= static_cast<int64_t>(Hv) * GV && z_pitch % 4 == 0);
-  if (T == 0) return 0;
   const int64_t warps = T * Hv;
   gdn_epilogue_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(z), z_pitch, static_cast<const __nv_bfloat16*>(norm_w), eps,

@@ -12,6 +12,7 @@
 // of warp-level bf16 MMAs. The chain per chunk is five small products (64..128 rows) that depend on one another, so the kernel is
 // bound by their latency, not by tensor throughput: operands stay in shared memory and registers of one CTA (ldmatrix + mma.sync),
 // with no tensor-memory round trip between the steps.
+#include <atomic>
 #include "common.cuh"
 #include "host_util.h"
 
@@ -498,11 +499,11 @@ extern "C" int spinf_gdn_chunked(const void* q, const void* k, const void* v, co
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int dev = 0;
   SPINF_CUDA_OK(cudaGetDevice(&dev));
-  static bool attr_set[64] = {false};
-  if (!attr_set[dev]) {
+  static std::atomic<bool> attr_set[64];  // zero-initialised; setting the attribute twice from two threads is harmless
+  if (!attr_set[dev].load(std::memory_order_acquire)) {
     SPINF_CUDA_OK(cudaFuncSetAttribute(gdn_chunk_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(PrepSmem))));
     SPINF_CUDA_OK(cudaFuncSetAttribute(gdn_chunk_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(ScanSmem))));
-    attr_set[dev] = true;
+    attr_set[dev].store(true, std::memory_order_release);
   }
   gdn_chunk_prep_kernel<<<dim3(static_cast<unsigned>(n_chunks), static_cast<unsigned>(Hv)), 128, sizeof(PrepSmem), st>>>(a);
   SPINF_CUDA_OK(cudaGetLastError());

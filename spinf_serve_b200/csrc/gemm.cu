@@ -1,4 +1,5 @@
 // Launchers of the tcgen05 GEMMs: the row-wise fp8 linear, the plain bf16 linear and the fused option-log-prob read.
+#include <atomic>
 #include <mutex>
 
 #include "gemm_tc.cuh"
@@ -487,10 +488,10 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
   int* status = status_word(dev);
   if (!status) return SPINF_ERR_CUDA;
   auto kern = gemm_tc_kernel<KIND, BN, Epi>;
-  static bool attr_set[64] = {false};
-  if (!attr_set[dev]) {
+  static std::atomic<bool> attr_set[64];  // zero-initialised; setting the attribute twice from two threads is harmless
+  if (!attr_set[dev].load(std::memory_order_acquire)) {
     SPINF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN>::TOTAL));
-    attr_set[dev] = true;
+    attr_set[dev].store(true, std::memory_order_release);
   }
   const int tiles = shape.tiles_m * shape.tiles_n;
   const int grid = tiles < sm_count() ? tiles : sm_count();
@@ -523,7 +524,6 @@ using namespace spinf;
 extern "C" int spinf_fp8_rowwise_quant(const void* x_bf16, int64_t M, int64_t K, void* x8, float* xs, void* stream) {
   if (M == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(x_bf16 && x8 && xs && M >= 0 && K > 0 && K % 8 == 0 && K <= 32768 && M < (1ll << 31));
-  if (M == 0) return 0;
   fp8_rowwise_quant_kernel<false><<<static_cast<unsigned>(M), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x_bf16), static_cast<int>(K), static_cast<uint8_t*>(x8), xs);
   SPINF_CUDA_OK(cudaGetLastError());
@@ -533,7 +533,6 @@ extern "C" int spinf_fp8_rowwise_quant(const void* x_bf16, int64_t M, int64_t K,
 extern "C" int spinf_int8_rowwise_quant(const void* x_bf16, int64_t M, int64_t K, void* x8, float* xs, void* stream) {
   if (M == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(x_bf16 && x8 && xs && M >= 0 && K > 0 && K % 8 == 0 && K <= 32768 && M < (1ll << 31));
-  if (M == 0) return 0;
   fp8_rowwise_quant_kernel<true><<<static_cast<unsigned>(M), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x_bf16), static_cast<int>(K), static_cast<uint8_t*>(x8), xs);
   SPINF_CUDA_OK(cudaGetLastError());
@@ -545,7 +544,6 @@ extern "C" int spinf_int8_rowwise_gemm(const void* x8, const float* xs, const vo
   if (M == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(x8 && xs && w8 && ws && y_bf16 && M >= 0 && N > 0 && K > 0 && K % 16 == 0 && N % 16 == 0);
   SPINF_CHECK_ARG(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31));
-  if (M == 0) return 0;
   constexpr int BN = 256;
   CUtensorMap tmA, tmB;
   EpiStoreBf16<BN, true, true> epi;
@@ -563,7 +561,6 @@ extern "C" int spinf_fp8_rowwise_gemm(const void* x8, const float* xs, const voi
   if (M == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(x8 && xs && w8 && ws && y_bf16 && M >= 0 && N > 0 && K > 0 && K % 16 == 0 && N % 16 == 0);
   SPINF_CHECK_ARG(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31));
-  if (M == 0) return 0;
   constexpr int BN = 256;
   CUtensorMap tmA, tmB;
   EpiStoreBf16<BN, true> epi;
@@ -577,10 +574,13 @@ extern "C" int spinf_fp8_rowwise_gemm(const void* x8, const float* xs, const voi
 }
 
 extern "C" int spinf_abs_max(const void* x_bf16, int64_t n, float* out, void* stream) {
-  if (n == 0) return 0;  // nothing to do: the row pointers may be null
+  if (n == 0) {  // the maximum over nothing is 0: the output is still written (the input pointer may be null)
+    SPINF_CHECK_ARG(out);
+    SPINF_CUDA_OK(cudaMemsetAsync(out, 0, sizeof(float), static_cast<cudaStream_t>(stream)));
+    return 0;
+  }
   SPINF_CHECK_ARG(x_bf16 && out && n >= 0 && n % 8 == 0);
   SPINF_CUDA_OK(cudaMemsetAsync(out, 0, sizeof(float), static_cast<cudaStream_t>(stream)));
-  if (n == 0) return 0;
   const int64_t nvec = n / 8, blocks = (nvec + 255) / 256;
   const int64_t cap = 8ll * sm_count();
   abs_max_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
@@ -593,7 +593,6 @@ extern "C" int spinf_fp8_tensor_quant(const void* x_bf16, int64_t n, const float
                                       float* peak, void* stream) {
   if (n == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(x_bf16 && scale && x8 && n >= 0 && n % 8 == 0 && (from_amax == 0 || from_amax == 1));
-  if (n == 0) return 0;
   const int64_t nvec = n / 8, blocks = (nvec + 255) / 256;
   const int64_t cap = 8ll * sm_count();
   fp8_tensor_quant_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
@@ -607,7 +606,6 @@ extern "C" int spinf_fp8_tensor_gemm(const void* x8, const float* xs, const void
   if (M == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(x8 && xs && w8 && ws && y_bf16 && M >= 0 && N > 0 && K > 0 && K % 16 == 0 && N % 16 == 0);
   SPINF_CHECK_ARG(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31));
-  if (M == 0) return 0;
   constexpr int BN = 256;
   CUtensorMap tmA, tmB;
   EpiStoreBf16<BN, true> epi;
@@ -626,7 +624,6 @@ extern "C" int spinf_bf16_gemm_ld(const void* x, const void* w, void* y, int64_t
   if (M == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(x && w && y && M >= 0 && N > 0 && K > 0 && K % 8 == 0 && N % 8 == 0 && y_pitch >= N && y_pitch % 8 == 0);
   SPINF_CHECK_ARG(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31));
-  if (M == 0) return 0;
   constexpr int BN = 256;
   CUtensorMap tmA, tmB;
   EpiStoreBf16<BN, false> epi;
@@ -648,7 +645,6 @@ extern "C" int spinf_fp8_rowwise_gemm_glu(const void* x8, const float* xs, const
   if (M == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(x8 && xs && w8_tiled && ws_tiled && y && row_amax && M >= 0 && F > 0 && K > 0 && K % 16 == 0 && F % 128 == 0);
   SPINF_CHECK_ARG(M < (1ll << 31) && F < (1ll << 30) && K < (1ll << 31) && (act == 0 || act == 1));
-  if (M == 0) return 0;
   constexpr int BN = 256;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   SPINF_CUDA_OK(cudaMemsetAsync(row_amax, 0, static_cast<size_t>(M) * sizeof(float), st));
@@ -679,7 +675,6 @@ extern "C" int spinf_fp8_rowwise_gemm_qkv(const void* x8, const float* xs, const
   // rows are read and written as 32-byte pieces
   SPINF_CHECK_ARG(((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(cos_t) | reinterpret_cast<uintptr_t>(sin_t) |
                     reinterpret_cast<uintptr_t>(wq) | reinterpret_cast<uintptr_t>(wk)) & 31) == 0);
-  if (M == 0) return 0;
   constexpr int BN = 256;
   CUtensorMap tmA, tmB;
   int r;
@@ -706,7 +701,6 @@ extern "C" int spinf_fp8_rowwise_gemm_qkv(const void* x8, const float* xs, const
 extern "C" int spinf_fp8_quant_from_amax(const void* y, const float* row_amax, int64_t M, int64_t K, void* x8, float* xs, void* stream) {
   if (M == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(y && row_amax && x8 && xs && M >= 0 && K > 0 && K % 8 == 0 && M < (1ll << 31) && K < (1ll << 31));
-  if (M == 0) return 0;
   fp8_quant_from_amax_kernel<<<static_cast<unsigned>(M), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(y), row_amax, static_cast<int>(K), static_cast<uint8_t*>(x8), xs);
   SPINF_CUDA_OK(cudaGetLastError());
@@ -729,7 +723,6 @@ extern "C" int spinf_option_logprobs(const void* h, const void* W, int64_t R, in
   SPINF_CHECK_ARG(R < (1ll << 31) && vocab < (1ll << 31) && hidden < (1ll << 31) && n_cols < (1ll << 24));
   SPINF_CHECK_ARG((reinterpret_cast<uintptr_t>(workspace) & 15) == 0);
   if (workspace_bytes < spinf_option_logprobs_workspace_bytes(R, vocab, n_cols)) return SPINF_ERR_BAD_ARGUMENT;
-  if (R == 0) return 0;
   constexpr int BN = 256;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const GemmShape shape = make_shape(R, vocab, hidden, BN);
@@ -799,7 +792,6 @@ extern "C" int spinf_option_logprobs_static(const void* h, const void* W, int64_
   // layout: [0, 256) status slot | partial maxima | partial sums | column-tile table
   const int64_t need = 256 + partial_floats * 4 + (static_cast<int64_t>(shape.tiles_n) + 1) * 4;
   if (need > static_cast<int64_t>(STATIC_SCRATCH_BYTES)) return SPINF_ERR_TOO_LARGE;
-  if (R == 0) return 0;
   int dev = 0;
   SPINF_CUDA_OK(cudaGetDevice(&dev));
   unsigned char* base = option_scratch_device_ptr(dev);  // first call on a device resolves the symbol
@@ -829,7 +821,12 @@ extern "C" int spinf_option_logprobs_static(const void* h, const void* W, int64_
   GemmShape sh = shape;
   sh.group_m = shape.tiles_m;
   auto kern = gemm_tc_kernel<KIND_BF16, BN, EpiLse<BN>>;
-  SPINF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN>::TOTAL));
+  static std::atomic<bool> smem_set[64];  // the kernel's shared-memory attribute, set on this entry point's first call per device
+  if (dev < 0 || dev >= 64) return SPINF_ERR_CUDA;
+  if (!smem_set[dev].load(std::memory_order_acquire)) {
+    SPINF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN>::TOTAL));
+    smem_set[dev].store(true, std::memory_order_release);
+  }
   const int tiles = sh.tiles_m * sh.tiles_n;
   const int grid = tiles < sm_count() ? tiles : sm_count();
   kern<<<grid, 192, GemmSmem<BN>::TOTAL, st>>>(tmA, tmB, sh, epi, status_word_p);
@@ -840,12 +837,3 @@ extern "C" int spinf_option_logprobs_static(const void* h, const void* W, int64_
   return 0;
 }
 
-#ifdef SPINF_TRACE
-extern "C" int spinf_trace_read(long long* out) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out, spinf::g_trace, sizeof(long long) * 8);
-  long long z[8] = {0};
-  cudaMemcpyToSymbol(spinf::g_trace, z, sizeof(z));
-  return 0;
-}
-#endif

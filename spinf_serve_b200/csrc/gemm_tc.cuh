@@ -55,11 +55,6 @@ __device__ __forceinline__ void tile_coords(const GemmShape& s, int tile, int& t
 //                                                groups (t_row = TMEM address of the row's first column)
 //   end_tile(st, ..., t_row, ...)                after the last chunk (may read single TMEM columns when kReadsTmemInEnd)
 //   finish(st, et)                               once, after the last tile
-#ifdef SPINF_TRACE
-// debugging aid, compiled out of the library: clocks the epilogue warps spend waiting for an accumulator, in the chunk loop and in
-// end_tile, summed over tiles by the first epilogue thread of every CTA ([0..2] cycles, [3] tiles)
-__device__ long long g_trace[8];
-#endif
 template <int KIND, int BN, class Epi>
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmShape shape,
@@ -180,13 +175,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t ab = tcount & 1u, aph = (tcount >> 1) & 1u;
       __syncwarp();
       epi.begin_tile(est, shape, tm, tn, et, colscale);
-#ifdef SPINF_TRACE
-      const long long tr0 = clock64();
-#endif
       const bool got = mbar_wait(wc, &acc_full[ab], aph, ST_TIMEOUT_TMEM);
-#ifdef SPINF_TRACE
-      const long long tr1 = clock64();
-#endif
       if (!bar_red_and(1, 128, got)) break;  // all 128 epilogue threads leave together
       tc_fence_after();
       const uint32_t t_row = tmem_base + ab * BN + (static_cast<uint32_t>(q * 32) << 16);
@@ -204,23 +193,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         epi.chunk(est, shape, tm, tn, row, et, c, v0, v1, colscale, epi_stage, t_row);
       }
       __syncwarp();
-#ifdef SPINF_TRACE
-      const long long tr2 = clock64();
-#endif
       epi.end_tile(est, shape, tm, tn, row, et, t_row, colscale);
       if (Epi::kReadsTmemInEnd) {
         tc_fence_before();
         mbar_arrive(&acc_empty[ab]);
       }
-#ifdef SPINF_TRACE
-      if (et == 0) {
-        const long long tr3 = clock64();
-        atomicAdd(reinterpret_cast<unsigned long long*>(&g_trace[0]), static_cast<unsigned long long>(tr1 - tr0));
-        atomicAdd(reinterpret_cast<unsigned long long*>(&g_trace[1]), static_cast<unsigned long long>(tr2 - tr1));
-        atomicAdd(reinterpret_cast<unsigned long long*>(&g_trace[2]), static_cast<unsigned long long>(tr3 - tr2));
-        atomicAdd(reinterpret_cast<unsigned long long*>(&g_trace[3]), 1ull);
-      }
-#endif
     }
     epi.finish(est, et);
   }

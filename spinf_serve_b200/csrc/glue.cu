@@ -444,7 +444,6 @@ extern "C" int spinf_fused_norm(const void* y, const int64_t* rows, const void* 
   SPINF_CHECK_ARG((out_x8 == nullptr) == (out_xs == nullptr));
   SPINF_CHECK_ARG(!(out_norm || out_x8) || w2);
   SPINF_CHECK_ARG(n_out < (1ll << 31));
-  if (n_out == 0) return 0;
   FusedNormArgs a;
   a.y = static_cast<const __nv_bfloat16*>(y);
   a.rows = rows;
@@ -487,7 +486,6 @@ extern "C" int spinf_qkv_norm_rope(void* qkv, int64_t pitch, int64_t n, int32_t 
   SPINF_CHECK_ARG(qkv && wq && wk && cos_t && sin_t && n >= 0 && H > 0 && Hkv > 0 && (D == 128 || D == 256));
   SPINF_CHECK_ARG(rot_dim > 0 && rot_dim <= D && rot_dim % (2 * (D / 32)) == 0);
   SPINF_CHECK_ARG(pitch >= static_cast<int64_t>(H + 2 * Hkv) * D);
-  if (n == 0) return 0;
   const int64_t warps = (n * (H + 2 * Hkv) + 1) / 2;  // two (token, head) items per warp
   const unsigned grid = static_cast<unsigned>((warps + 7) / 8);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -511,7 +509,6 @@ extern "C" int spinf_qkv_norm_rope_gated(void* y, int64_t pitch, int64_t n, int3
   SPINF_CHECK_ARG(y && wq && wk && cos_t && sin_t && q_out && n >= 0 && H > 0 && Hkv > 0 && (D == 128 || D == 256));
   SPINF_CHECK_ARG(rot_dim > 0 && rot_dim <= D && rot_dim % (2 * (D / 32)) == 0);
   SPINF_CHECK_ARG(pitch >= static_cast<int64_t>(2 * H + 2 * Hkv) * D && pitch % 8 == 0);
-  if (n == 0) return 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   auto* p = static_cast<__nv_bfloat16*>(y);
   auto* q = static_cast<const __nv_bfloat16*>(wq);
@@ -550,7 +547,6 @@ __global__ void attn_gate_kernel(__nv_bfloat16* __restrict__ o, const __nv_bfloa
 extern "C" int spinf_attn_gate(void* o, const void* y, int64_t pitch, int64_t n, int32_t H, int32_t D, void* stream) {
   if (n == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(o && y && n >= 0 && H > 0 && D > 0 && D % 8 == 0 && pitch >= 2ll * H * D && pitch % 8 == 0);
-  if (n == 0) return 0;
   const int64_t vecs = n * H * D / 8;
   attn_gate_kernel<<<static_cast<unsigned>((vecs + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<__nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(y), pitch, n, H, D);
@@ -563,7 +559,6 @@ extern "C" int spinf_glu_quant(const void* gu, int64_t n, int64_t F, int32_t act
   if (n == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(gu && n >= 0 && F > 0 && F % 8 == 0 && (act == 0 || act == 1) && n < (1ll << 31) && F < (1ll << 28));
   SPINF_CHECK_ARG((out_x8 == nullptr) == (out_xs == nullptr) && (out_x8 || out_y));
-  if (n == 0) return 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   auto* g = static_cast<const __nv_bfloat16*>(gu);
   if (act == ACT_GELU_TANH)
@@ -580,7 +575,6 @@ extern "C" int spinf_embed_scale(const int64_t* ids, const void* emb, int64_t n,
                                  void* stream) {
   if (n == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(ids && emb && out && n >= 0 && hidden > 0 && hidden % 8 == 0 && vocab > 0 && n < (1ll << 31));
-  if (n == 0) return 0;
   embed_scale_kernel<<<static_cast<unsigned>(n), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       ids, static_cast<const __nv_bfloat16*>(emb), static_cast<int>(hidden), vocab, scale, static_cast<__nv_bfloat16*>(out));
   SPINF_CUDA_OK(cudaGetLastError());
@@ -591,7 +585,6 @@ extern "C" int spinf_rope_table(const int32_t* pos, int64_t n, int32_t rot_dim, 
                                 void* stream) {
   if (n == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(pos && cos_t && sin_t && inv_freq && n >= 0 && rot_dim > 0 && rot_dim % 2 == 0);
-  if (n == 0) return 0;
   const int half = rot_dim / 2;
   const int64_t total = n * half;
   rope_table_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(

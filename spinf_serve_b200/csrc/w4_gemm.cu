@@ -24,6 +24,7 @@
 // chunk is in registers (a staging buffer per chunk, so no chunk waits for an earlier chunk's store): about 5 % of a tile's main
 // loop at K = 5120, while loads and expansion run ahead through the ring.
 // K order per output element is ascending and the tile shape does not depend on M: rows are batch-invariant.
+#include <atomic>
 #include "gemm_tc.cuh"
 #include "host_util.h"
 
@@ -49,11 +50,6 @@ struct W4Args {
   int tiles_m, tiles_n, group_m;  // tiles of 256 tokens x 256 output channels
 };
 
-#ifdef SPINF_TRACE
-// debugging aid, compiled out of the library: cycles the MMA-issuing thread waits for [0] a free accumulator, [1] the activation
-// stage, [2] the dequantised weight stage; [3] K steps, [4] cycles from first to last issue
-__device__ unsigned long long g_w4_trace[8];
-#endif
 
 // ACT: -1 = plain linear; 0 / 1 = gated linear unit in the epilogue (GELU-tanh / SiLU): the weight rows are interleaved at load
 // time (row 2c = gate channel c, row 2c + 1 = up channel c), so a lane pair of the epilogue holds a channel's gate and up values
@@ -142,35 +138,12 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t it = 0, tcount = 0;
       bool ok = true;
       for (int tile = pair0; tile < num_tiles && ok; tile += pair_step, ++tcount) {
-#ifdef SPINF_TRACE
-        long long w0 = clock64();
-#endif
         if (!mbar_wait(wc, acc_empty, (tcount & 1u) ^ 1u, ST_TIMEOUT_TMEM)) { ok = false; break; }
-#ifdef SPINF_TRACE
-        long long w1 = clock64();
-        atomicAdd(&g_w4_trace[0], static_cast<unsigned long long>(w1 - w0));
-        const long long t_first = w1;
-#endif
         tc_fence_after();
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-#ifdef SPINF_TRACE
-          w0 = clock64();
-#endif
           if (!mbar_wait(wc, &full_a[s], ph, ST_TIMEOUT_FULL)) { ok = false; break; }
-#ifdef SPINF_TRACE
-          w1 = clock64();
-#endif
           if (!mbar_wait(wc, &b_full[s], ph, ST_TIMEOUT_OTHER)) { ok = false; break; }
-#ifdef SPINF_TRACE
-          {
-            const long long w2 = clock64();
-            atomicAdd(&g_w4_trace[1], static_cast<unsigned long long>(w1 - w0));
-            atomicAdd(&g_w4_trace[2], static_cast<unsigned long long>(w2 - w1));
-            atomicAdd(&g_w4_trace[3], 1ull);
-            if (kb == num_kb - 1) atomicAdd(&g_w4_trace[4], static_cast<unsigned long long>(w2 - t_first));
-          }
-#endif
           tc_fence_after();
           const uint64_t xdesc = make_smem_desc_sw128(smem_u32(smem + s * L::STAGE_BYTES), 16, 1024);
           const uint32_t w_tmem = tmem_base + L::W_COL + s * 32;  // 16 bf16 of K = 8 packed columns per MMA
@@ -399,7 +372,6 @@ static int launch_w4(const void* x, const void* qw, const void* scales, int32_t 
   SPINF_CHECK_ARG(x && qw && scales && y && M >= 0 && N > 0 && K > 0 && group > 0);
   SPINF_CHECK_ARG(K % 64 == 0 && group % 8 == 0 && K % group == 0 && N % (ACT < 0 ? 8 : 16) == 0 && y_pitch >= n_out && y_pitch % 8 == 0);
   SPINF_CHECK_ARG(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31));
-  if (M == 0) return 0;
   int dev = 0;
   SPINF_CUDA_OK(cudaGetDevice(&dev));
   int* status = status_word(dev);
@@ -422,10 +394,10 @@ static int launch_w4(const void* x, const void* qw, const void* scales, int32_t 
     a.group_m = static_cast<int>(g < 4 ? 4 : (g > 32 ? 32 : g));
   }
   auto kern = w4_gemm_kernel<ACT>;
-  static bool attr_set[64] = {false};
-  if (!attr_set[dev]) {
+  static std::atomic<bool> attr_set[64];  // zero-initialised; setting the attribute twice from two threads is harmless
+  if (!attr_set[dev].load(std::memory_order_acquire)) {
     SPINF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, W4Smem::TOTAL));
-    attr_set[dev] = true;
+    attr_set[dev].store(true, std::memory_order_release);
   }
   const int tiles = a.tiles_m * a.tiles_n;
   const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
@@ -458,12 +430,3 @@ extern "C" int spinf_w4_gemm_glu(const void* x, const void* qw, const void* scal
                   : launch_w4<1>(x, qw, scales, group, y, M, N2, K, y_pitch, stream);
 }
 
-#ifdef SPINF_TRACE
-extern "C" int spinf_w4_trace_read(unsigned long long* out) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out, spinf::g_w4_trace, sizeof(unsigned long long) * 8);
-  unsigned long long z[8] = {0};
-  cudaMemcpyToSymbol(spinf::g_w4_trace, z, sizeof(z));
-  return 0;
-}
-#endif

@@ -190,15 +190,19 @@ class GemmaStack:
         self.fuse_qkv = D in (128, 256) and ((self.cfg.heads + 2 * self.cfg.kv_heads) * D) % 256 == 0
         self.amax_log = None  # calibrate() sets a list here: (linear name, device scalar) per quantised input of a forward
 
-    def plan(self, b) -> None:
-        """nothing to prepare on the host for attention-only models (base.py:50-51)"""
+    @property
+    def window(self):
+        """the sliding layers' window (the text config's sliding_window, read by the scorer when it builds the tile lists)"""
+        return self.cfg.window
 
-    def stage(self, b, device):
-        """batch arrays -> device inputs: ids int64 [n], pos int32 [n], the two TileMasks (the counterpart of Stack.stage +
-        Scorer._block_masks, base.py:53-60, scorer.py:207-238)"""
-        ids = torch.from_numpy(b.ids).pin_memory().to(device, non_blocking=True)
-        masks = attention.stream_masks(b.art, b.end, b.pos, self.cfg.window, device, always_window=True)
-        return {"ids": ids, "pos": masks["full_attention"].pos, "masks": masks}
+    def plan(self, sc, b) -> None:
+        """nothing to prepare on the host for attention-only models (Stack.plan, base.py:50-51)"""
+
+    def stage(self, sc, b, st: dict) -> dict:
+        """what forward reads of the staged arrays (Stack.stage, base.py:53-60, returns {"ids": [1, n], "pos": [1, n]}). `st` maps
+        array names to device tensors: the scorer has laid the batch's arrays out in one pinned block and queued its single
+        upload, so there is nothing left to copy here."""
+        return {"ids": st["ids"][None], "pos": st["pos32"][None]}
 
     # ---- per-tensor schemes (fp8: the activation scale from the forward's own maximum; fp8s: a calibrated fixed scale). The
     # GEMMs are the row-wise kernels with every row given the tensor's one scale, so their fused epilogues stay; the reference
@@ -240,19 +244,22 @@ class GemmaStack:
                     out[(i, k)] = float(L["peak"][group[0]])
         return out
 
-    def forward(self, inputs, rows=None, taps=None):
-        """packed forward -> final hidden states after the model's last norm, [n, hidden] bf16, or only the rows `rows` (int64
-        device tensor of stream positions). taps: optional dict filled with per-layer intermediates (tests)."""
+    def forward(self, sc, b, inputs: dict, masks: dict, rows=None, taps=None):
+        """packed forward (Stack.forward, base.py:62-64) -> final hidden states after the model's last norm, [1, n, hidden] bf16 in
+        the stream layout. masks = {"full_attention": TileMask, "sliding_attention": TileMask} (attention.device_masks). Beyond the
+        reference's signature: rows (int64 device tensor of stream positions) returns only those rows, [len(rows), hidden], the
+        last norm running on them alone; taps: optional dict filled with per-layer intermediates (tests)."""
         cfg, w = self.cfg, self.w
         H, K, D = cfg.heads, cfg.kv_heads, cfg.head_dim
-        ids, pos, masks = inputs["ids"], inputs["pos"], inputs["masks"]
+        ids, pos = inputs["ids"].reshape(-1), inputs["pos"].reshape(-1)
         n = ids.numel()
         row = w.scheme == "fp8row"
         fp8 = w.scheme in ("fp8row", "fp8", "fp8s")
         tables = {k: ops.rope_table(pos, f) for k, f in self.inv_freq.items()}
         h = ops.embed_scale(ids, w.embed, self.embed_scale)
         if self.n_layers == 0:
-            return ops.fused_norm(h, w2=w.norm, rows=rows, eps=cfg.eps, want_norm=True)["norm"]
+            out = ops.fused_norm(h, w2=w.norm, rows=rows, eps=cfg.eps, want_norm=True)["norm"]
+            return out if rows is not None else out[None]
         r = ops.fused_norm(h, w2=w.layers[0]["input_ln"], eps=cfg.eps, want_fp8=row, want_norm=not row)
         for i in range(self.n_layers):
             L = w.layers[i]
@@ -293,7 +300,8 @@ class GemmaStack:
             h = r["h"]
             if taps is not None:
                 taps[i] = {"q": q.clone(), "k": k.clone(), "v": v.clone(), "attn": a, "h": h}
-        return ops.fused_norm(h, w2=w.norm, rows=rows, eps=cfg.eps, want_norm=True)["norm"]
+        out = ops.fused_norm(h, w2=w.norm, rows=rows, eps=cfg.eps, want_norm=True)["norm"]
+        return out if rows is not None else out[None]
 
 
 def calibrate(cfg: GemmaConfig, W, batches, device, headroom: float = 2.0, n_layers=None):
@@ -301,11 +309,14 @@ def calibrate(cfg: GemmaConfig, W, batches, device, headroom: float = 2.0, n_lay
     dynamic fp8 scheme over `batches` (packer Batches covering what the model will see), record the largest |input| of every
     quantized linear, and set scale = 2^ceil(log2(headroom x amax / 448)). -> {"scheme": "fp8s", "headroom", "amax": [{name: v}],
     "scales": [{name: s}]}, one dict per layer; `scales` is what GemmaWeights.from_bf16(..., scheme="fp8s", scales=...) takes."""
+    from spinf_serve_b200.scorer import stage_one
+
     stack = GemmaStack(GemmaWeights.from_bf16(cfg, W, device, scheme="fp8"), n_layers)
     amax = [dict.fromkeys(LINEARS, 0.0) for _ in range(stack.n_layers)]
     for b in batches:
         stack.amax_log = []
-        stack.forward(stack.stage(b, device))
+        sc, inputs, masks, _ = stage_one(stack, b, device)
+        stack.forward(sc, b, inputs, masks)
         per_layer = len(LINEARS)
         logged = [(k, float(v)) for k, v in stack.amax_log]  # read back after the forward: no sync inside it
         for j, (k, v) in enumerate(logged):

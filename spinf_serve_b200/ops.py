@@ -12,7 +12,8 @@ from spinf_serve_b200._lib import SpinfError, check, ptr, stream_ptr
 FP8 = torch.float8_e4m3fn
 
 # Measurement hooks (bench.py): COUNTS["launches"] counts the kernels this module enqueued; when PROFILE is a list, every row-wise
-# fp8 GEMM is bracketed by CUDA events on its stream and (start, end, flops) is appended.
+# fp8 GEMM and every attention launch is bracketed by CUDA events on its stream and (start, end, flops, kind) is appended (kind
+# "fp8_gemm" with its 2 M N K, or "attn:<window>" with flops left 0: the caller knows the stream's unmasked pairs).
 COUNTS = {"launches": 0}
 PROFILE = None
 
@@ -65,7 +66,7 @@ def fp8_rowwise_gemm(x8, xs, w8, ws, out=None):
     )
     if prof is not None:
         e1.record()
-        prof.append((e0, e1, 2.0 * M * N * K))
+        prof.append((e0, e1, 2.0 * M * N * K, "fp8_gemm"))
     COUNTS["launches"] += 1
     return y
 
@@ -123,7 +124,7 @@ def fp8_tensor_gemm(x8, xs, w8, ws, out=None):
     check(_lib.lib().spinf_fp8_tensor_gemm(ptr(x8), ptr(xs), ptr(w8), ptr(ws), ptr(y), M, N, K, stream_ptr()), "spinf_fp8_tensor_gemm")
     if prof is not None:
         e1.record()
-        prof.append((e0, e1, 2.0 * M * N * K))
+        prof.append((e0, e1, 2.0 * M * N * K, "fp8_gemm"))
     COUNTS["launches"] += 1
     return y
 
@@ -247,7 +248,7 @@ def fp8_gemm_glu(x8, xs, w8_tiled, ws_tiled, act="gelu_tanh"):
     )
     if prof is not None:
         e1.record()
-        prof.append((e0, e1, 2.0 * M * 2 * F * K))
+        prof.append((e0, e1, 2.0 * M * 2 * F * K, "fp8_gemm"))
     y8 = torch.empty((M, F), dtype=FP8, device=dev)
     ys = torch.empty((M, 1), dtype=torch.float32, device=dev)
     check(_lib.lib().spinf_fp8_quant_from_amax(ptr(y), ptr(amax), M, F, ptr(y8), ptr(ys), stream_ptr()), "spinf_fp8_quant_from_amax")
@@ -287,7 +288,7 @@ def fp8_gemm_qkv(x8, xs, w8, ws, H, Hkv, D, wq, wk, cos, sin, eps=1e-6, plus1=Fa
     )
     if prof is not None:
         e1.record()
-        prof.append((e0, e1, 2.0 * M * N * K))
+        prof.append((e0, e1, 2.0 * M * N * K, "fp8_gemm"))
     COUNTS["launches"] += 1
     return y
 

@@ -105,33 +105,44 @@ class QwenStack:
         floor = self.min_stream if self.align_jobs else 0
         return min(b.length, max((R + BLOCK - 1) // BLOCK * BLOCK, floor))
 
-    def plan(self, b) -> None:
-        """the recurrent layers' plan, on the host ahead of the GPU (the producer thread; Qwen35Stack.plan, qwen.py:1056)"""
-        b.gdn_plan_host = (b.prev, b.art >= 0, self.compact_rows(b))
+    window = None  # every attention layer of the family is full attention
 
-    def stage(self, b, device):
+    def plan(self, sc, b) -> None:
+        """the host half of the recurrent layers' plan, ahead of the GPU (the packing thread; Qwen35Stack.plan, qwen.py:1056): the
+        compact-row count and, for compact rows, the real tokens' ids / positions and the stream-position -> row map, which ride
+        in the batch's staging block (b.staged)"""
         import numpy as np
 
-        up = lambda a: torch.from_numpy(a).pin_memory().to(device, non_blocking=True)  # noqa: E731
-        masks = attention.stream_masks(b.art, b.end, b.pos, None, device, always_window=False)
-        prev, real, rows = getattr(b, "gdn_plan_host", (b.prev, b.art >= 0, self.compact_rows(b)))
-        plan = tree_plan(prev, real, device, rows=rows)
-        if rows is None:
-            return {"ids": up(b.ids), "pos": masks["full_attention"].pos, "masks": masks, "plan": plan, "n": b.length}
-        # compact rows: the real tokens' ids and positions, then zeros (Qwen35Stack.stage / forward, qwen.py:1064-1090)
-        R = int(real.sum())
-        ids = np.zeros(rows, np.int64)
-        ids[:R] = b.ids[real]
-        pos = np.zeros(rows, np.int32)
-        pos[:R] = b.pos[real]
-        to_row = np.cumsum(real) - 1  # stream position -> compact row (meaningful at real positions)
-        return {"ids": up(ids), "pos": up(pos), "masks": masks, "plan": plan, "n": b.length, "to_row": up(to_row.astype(np.int64))}
+        real = b.art >= 0
+        rows = self.compact_rows(b)
+        b.gdn_plan_host = (b.prev, real, rows)
+        if rows is not None:
+            R = int(real.sum())
+            ids = np.zeros(rows, np.int64)
+            ids[:R] = b.ids[real]
+            pos = np.zeros(rows, np.int32)
+            pos[:R] = b.pos[real]
+            b.staged = {"compact.ids": ids, "compact.pos": pos, "compact.to_row": (np.cumsum(real) - 1).astype(np.int64)}
 
-    def forward(self, inputs, rows=None, taps=None):
-        """packed forward -> final hidden states after the last norm: [stream length, hidden] bf16 in the stream layout, or only the
-        stream positions `rows`; taps: optional dict filled with the residual stream per layer, in the stream layout (tests)"""
+    def stage(self, sc, b, st: dict) -> dict:
+        """what forward reads (Qwen35Stack.stage, qwen.py:1064): the staged ids / positions (compact rows: the real tokens', then
+        zeros, qwen.py:1064-1090) and the recurrent layers' TreePlan, whose index arrays go up here"""
+        if not hasattr(b, "gdn_plan_host"):
+            self.plan(sc, b)
+        prev, real, rows = b.gdn_plan_host
+        plan = tree_plan(prev, real, sc.device, rows=rows)
+        if rows is None:
+            return {"ids": st["ids"][None], "pos": st["pos32"][None], "plan": plan, "n": b.length}
+        if "compact.ids" not in st:
+            raise RuntimeError("compact rows: the batch was staged without its plan (call stack.plan(sc, b) before staging)")
+        return {"ids": st["compact.ids"][None], "pos": st["compact.pos"][None], "plan": plan, "n": b.length, "to_row": st["compact.to_row"]}
+
+    def forward(self, sc, b, inputs: dict, masks: dict, rows=None, taps=None):
+        """packed forward (Stack.forward, base.py:62-64) -> final hidden states after the last norm, [1, stream length, hidden] bf16
+        in the stream layout. Beyond the reference's signature: rows (stream positions) returns only those rows, [len(rows),
+        hidden]; taps: optional dict filled with the residual stream per layer, in the stream layout (tests)"""
         cfg, w = self.cfg, self.w
-        ids, pos, mask, plan = inputs["ids"], inputs["pos"], inputs["masks"]["full_attention"], inputs["plan"]
+        ids, pos, mask, plan = inputs["ids"].reshape(-1), inputs["pos"].reshape(-1), masks["full_attention"], inputs["plan"]
         n = ids.numel()          # rows the layers run on
         T = inputs["n"]          # stream length (the attention's layout)
         sidx = plan.sidx if plan.rows is not None else None
@@ -185,4 +196,6 @@ class QwenStack:
         if rows is not None and sidx is not None:
             rows = inputs["to_row"].index_select(0, rows)  # the read rows are stream positions
         out = ops.fused_norm(x, w2=w.norm, rows=rows, eps=cfg.eps, plus1=True, want_norm=True)["norm"]
-        return out if rows is not None or sidx is None else to_stream(out)
+        if rows is not None:
+            return out
+        return (out if sidx is None else to_stream(out))[None]

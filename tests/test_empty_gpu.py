@@ -41,6 +41,18 @@ def test_zero_rows_everywhere(dev):
     torch.cuda.synchronize(dev)
 
 
+def test_abs_max_of_nothing_writes_zero_through_the_c_abi(dev):
+    """*out = max |x| over n elements holds for n = 0 too: a caller that feeds it to spinf_fp8_tensor_quant(from_amax = 1) must not
+    read what the buffer held before"""
+    from spinf_serve_b200 import _lib
+
+    out = torch.full((1,), 123.0, dtype=torch.float32, device=dev)
+    assert _lib.lib().spinf_abs_max(None, 0, _lib.ptr(out), _lib.stream_ptr()) == 0
+    torch.cuda.synchronize(dev)
+    assert float(out) == 0.0
+    assert _lib.lib().spinf_abs_max(None, 0, None, _lib.stream_ptr()) == -1
+
+
 def test_scorer_with_nothing_to_score(dev):
     from spinf_serve_b200.gemma_stack import GemmaConfig, GemmaStack, GemmaWeights
     from spinf_serve_b200.scorer import EngineConfig, Scorer

@@ -8,6 +8,7 @@ import torch
 from oracle import attention as OA
 from oracle import gemma as OG
 from spinf_serve_b200 import packer as P
+from spinf_serve_b200.scorer import forward_one
 
 pytestmark = pytest.mark.gpu
 
@@ -45,7 +46,7 @@ def test_forward_vs_oracle_layer_by_layer(dev, D):
     (b,) = list(pk.flush())
     taps_o, taps_g = {}, {}
     ref = OG.forward(ocfg, W, Q, b.ids, b.art, b.end, b.pos, taps=taps_o)
-    out = stack.forward(stack.stage(b, dev), taps=taps_g).cpu()
+    out = forward_one(stack, b, dev, taps=taps_g)[0].cpu()
     real = torch.from_numpy(b.art >= 0)
     # layer 0 inputs are identical, so q / k / v (projection, head norm, rotary) agree up to rare last-bit flips
     for key in ("q", "k", "v"):
@@ -174,7 +175,7 @@ def test_per_tensor_schemes_vs_oracle(dev):
         OG.forward(ocfg, W, Q, b.ids, b.art, b.end, b.pos, taps=taps_o, scheme=scheme, scales=tab_o["scales"], peaks=peaks_o)
         linears.MONITOR["on"] = scheme == "fp8s"
         try:
-            stack.forward(stack.stage(b, dev), taps=taps_g)
+            forward_one(stack, b, dev, taps=taps_g)[0]
         finally:
             linears.MONITOR["on"] = False
         for key in ("q", "k", "v"):
@@ -246,7 +247,7 @@ def test_int8_and_bf16_schemes_vs_oracle(dev, scheme):
     stack = GS.GemmaStack(GS.GemmaWeights.from_quantized(cfg, W, Q, dev, scheme))
     taps_o, taps_g, taps_p = {}, {}, {}
     OG.forward(ocfg, W, Q, b.ids, b.art, b.end, b.pos, taps=taps_o, scheme=scheme)
-    stack.forward(stack.stage(b, dev), taps=taps_g)
+    forward_one(stack, b, dev, taps=taps_g)[0]
     exact = OA.tree_attention
     try:
         OA.tree_attention = lambda *a, **k: exact(*a, **{**k, "round_p": True})

@@ -123,7 +123,7 @@ def test_read_geometry_with_a_fake_model():
 
 
 def test_v0_drain_with_a_fake_model():
-    from spinf_serve_b200.scorer import JobResult, Scorer
+    from spinf_serve_b200.scorer import JobResult, Scorer, read_trees
 
     def fake_lp(prev, target):
         return -((prev * 13 + target * 5) % 89) / 10.0
@@ -137,13 +137,7 @@ def test_v0_drain_with_a_fake_model():
     cols = Scorer._cols(b)
     lp = np.array([[fake_lp(int(b.ids[q]), c) for c in cols] for q in b.sel], np.float32)
     res = {"a": JobResult([[0.0] * len(o) for o in options])}
-    host = torch.from_numpy(lp)
-
-    class Ev:
-        def synchronize(self):
-            pass
-
-    Scorer._drain(((host, Ev()), cols, b), res)
+    read_trees(lp, cols, b, res)
     for pr, opts, got in zip(prompts, options, res["a"].logprobs):
         for opt, g in zip(opts, got):
             want = sum(fake_lp((pr + opt)[len(pr) - 1 + i], opt[i]) for i in range(len(opt)))

@@ -7,6 +7,7 @@ import torch
 
 from oracle import qwen as OQ
 from spinf_serve_b200 import packer as P
+from spinf_serve_b200.scorer import forward_one
 from spinf_serve_b200.gdn_plan import tree_plan
 
 pytestmark = pytest.mark.gpu
@@ -40,8 +41,7 @@ def test_hybrid_forward_vs_oracle(dev):
     real = torch.from_numpy(b.art >= 0)
     taps_o, taps_g = {}, {}
     ref = OQ.forward(ocfg, W, b.ids, b.art, b.end, b.pos, tree_plan(b.prev, b.art >= 0, "cpu"), taps=taps_o)
-    stack.plan(b)
-    out = stack.forward(stack.stage(b, dev), taps=taps_g).cpu()
+    out = forward_one(stack, b, dev, taps=taps_g)[0].cpu()
     for i in range(ocfg.layers):
         o = taps_o[i][real].float()
         err = ((taps_g[i].cpu()[real].float() - o).pow(2).mean().sqrt() / o.pow(2).mean().sqrt()).item()
@@ -83,10 +83,8 @@ def test_compact_rows_equal_the_stream_layout(dev):
     (b,) = list(pk.flush())
     real = torch.from_numpy(b.art >= 0).to(dev)
     assert stack.compact_rows(b) < b.length  # aligned jobs leave pads that the compact layout drops
-    stack.plan(b)
-    plain.plan(b)
-    a = stack.forward(stack.stage(b, dev))
-    c = plain.forward(plain.stage(b, dev))
+    a = forward_one(stack, b, dev)[0]
+    c = forward_one(plain, b, dev)[0]
     assert a.shape == c.shape and torch.equal(a[real], c[real])
     sel = torch.from_numpy(b.sel).to(dev)
-    assert torch.equal(stack.forward(stack.stage(b, dev), rows=sel), c.index_select(0, sel))
+    assert torch.equal(forward_one(stack, b, dev, rows=sel), c.index_select(0, sel))

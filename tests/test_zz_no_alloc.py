@@ -65,3 +65,26 @@ def test_static_scratch_variant_rejects_oversize_calls(dev):
     )
     torch.cuda.synchronize()
     assert rc == -4 and bool((out == 7.0).all())
+
+
+def test_static_scratch_variant_allocates_nothing_and_works_without_a_status_pointer(dev):
+    """after a first call has resolved the array's address, a call moves neither the driver's free-memory figure nor torch's
+    allocation count (the output is allocated before the window); with status NULL the status word sits in the array's first bytes
+    and the result is the same"""
+    from spinf_serve_b200 import _lib, ops
+
+    h, W, c = _case(200, 512, 20000, 5, 34, dev)
+    want = ops.option_logprobs(h, W, c, None)
+    _static(h, W, c, None, None)  # first call on the device done
+    out = torch.empty((h.shape[0], c.numel()), dtype=torch.float32, device=dev)
+    torch.cuda.synchronize()
+    free0 = torch.cuda.mem_get_info(dev)[0]
+    allocs0 = torch.cuda.memory_stats(dev)["allocation.all.allocated"]
+    rc = _lib.lib().spinf_option_logprobs_static(
+        _lib.ptr(h), _lib.ptr(W), h.shape[0], h.shape[1], W.shape[0], _lib.ptr(c), c.numel(), ctypes.c_float(0.0), _lib.ptr(out), None,
+        _lib.stream_ptr(),
+    )
+    torch.cuda.synchronize()
+    assert rc == 0
+    assert torch.cuda.mem_get_info(dev)[0] == free0 and torch.cuda.memory_stats(dev)["allocation.all.allocated"] == allocs0
+    assert torch.equal(out, want)
