@@ -303,6 +303,33 @@ int spinf_gdn_chunked(const void* q, const void* k, const void* v, const float* 
                       const int64_t* ht_idx, const int32_t* chunk_seg, const int32_t* chunk_t0, int64_t n_chunks,
                       int64_t call_tokens, void* workspace, int64_t workspace_bytes, void* stream);
 
+/* A whole trie plan in the chunked form: replaces the reference's per-level driver gdn_indexed and the kernels it calls
+ * (spinf_serve/models/qwen35/qwen.py:550-590; gdn.py:109-133 and :197-235) for one recurrent layer. Every segment of the plan,
+ * long or short, runs in chunks of at most 64 tokens with the rounding points of spinf_gdn_chunked; a segment's values depend
+ * only on its own tokens and its parent's final state. The host describes the plan once per stream (gdn_plan.fused_schedule):
+ *   row_of [plan_tokens] int64   stream (or compact) row of plan token p; plan order = the segments one after the other
+ *   chunk_p0 / chunk_len [n_chunks] int32   every chunk of every segment: first plan token, length (1..64)
+ * spinf_gdn_tree_prep (ONE launch for the layer: nothing in it depends on a state) fills the workspace of
+ * spinf_gdn_tree_workspace_bytes(plan_tokens, Hv) bytes (256-byte aligned): W, U [plan_tokens, Hv, 128] bf16,
+ * P [plan_tokens, Hv, 64] bf16, G [plan_tokens, Hv] fp32.
+ * spinf_gdn_tree_scan runs one level of the trie (levels in order, after prep, on the same stream): the level's segments are
+ * grouped by parent; group i reads the parent's final state h_in[grp_parent[i]] (negative: the zero state) once and walks its units
+ * grp_ubeg[i] .. grp_ubeg[i+1]. A unit is 12 int32 words: number of pieces (1..4), flags (1 = the chunk updates the state, 2 =
+ * the unit must see the parent's state), the row of h_out the state is stored to after the update (-1: none), a pad word, and
+ * per piece (first plan token, length). Pieces are children that only read the state (one chunk, no state to keep), laid out at
+ * 16-row-aligned offsets of one 64-row tile; a child with several chunks, or whose state a deeper level reads, is one unit per
+ * chunk with flag 1 (its first with flags 1 | 2). h_in / h_out [slots, Hv, 128, 128] fp32. Outputs o [rows, Hv, 128] bf16
+ * contiguous at the tokens' rows. q / k / v / g / beta as for spinf_gdn_recurrent. */
+int64_t spinf_gdn_tree_workspace_bytes(int64_t plan_tokens, int32_t Hv);
+int spinf_gdn_tree_prep(const void* q, const void* k, const void* v, const float* g, const void* beta, int64_t n_rows, int64_t q_pitch,
+                        int64_t v_pitch, int64_t g_pitch, int32_t Hk, int32_t Hv, int32_t K, int32_t V, const int64_t* row_of,
+                        int64_t plan_tokens, const int32_t* chunk_p0, const int32_t* chunk_len, int64_t n_chunks, void* workspace,
+                        int64_t workspace_bytes, void* stream);
+int spinf_gdn_tree_scan(const void* q, const void* k, void* o, int64_t n_rows, int64_t q_pitch, int32_t Hk, int32_t Hv, int32_t K,
+                        int32_t V, float scale, const int64_t* row_of, int64_t plan_tokens, const int32_t* grp_parent,
+                        const int32_t* grp_ubeg, const int32_t* units, int64_t n_groups, const float* h_in, float* h_out,
+                        void* workspace, int64_t workspace_bytes, void* stream);
+
 /* Replaces the steps of GatedDeltaNet.forward before the recurrence (spinf_serve/models/qwen35/qwen.py:651-668), fused: for each of
  * the T tokens, from the in-projection rows y [n_rows, y_pitch] bf16 = [q | k | v | z | b | a]: the 4-tap path convolution over
  * conv [T, 4] int64 (a tap index >= n_rows or < 0 is the zero row) with conv_w [2 Hk K + Hv V, 4] bf16 in fp32, SiLU, rounding

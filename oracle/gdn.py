@@ -86,20 +86,25 @@ def chunked(q, k, v, g, beta, scale, cu, idx=None, h0=None, h0_idx=None, ht=None
     return o
 
 
-def gdn_tree(q, k, v, g, beta, plan, dtype=torch.float32):
+def gdn_tree(q, k, v, g, beta, plan, dtype=torch.float32, form="recurrent"):
     """every segment from its parent's final state, level by level (gdn_indexed, qwen.py:550-590); plan: a TreePlan whose calls
-    carry idx, cu_cpu, h0_idx, ht_idx (host or device tensors)"""
+    carry idx, cu_cpu, h0_idx, ht_idx (host or device tensors). form "chunked": every segment, short ones too, through chunked()
+    (the rounding points of the kernels that run whole plans in the chunked form)"""
     scale = q.shape[-1] ** -0.5
     o = torch.zeros_like(v)
     prev_states = None
     for calls, nk in zip(plan.levels, plan.n_keep):
         states = torch.zeros((nk, v.shape[1], q.shape[-1], v.shape[-1]), dtype=torch.float32) if nk else None
         for c in calls:
-            recurrent(
+            args = (
                 q, k, v, g, beta, scale, np.asarray(c.cu_cpu), np.asarray(c.idx.cpu()),
                 prev_states if c.h0_idx is not None else None, None if c.h0_idx is None else np.asarray(c.h0_idx.cpu()),
-                states if c.ht_idx is not None else None, None if c.ht_idx is None else np.asarray(c.ht_idx.cpu()), o, dtype,
+                states if c.ht_idx is not None else None, None if c.ht_idx is None else np.asarray(c.ht_idx.cpu()), o,
             )
+            if form == "chunked":
+                chunked(*args)
+            else:
+                recurrent(*args, dtype)
         prev_states = states
     return o
 

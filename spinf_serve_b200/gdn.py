@@ -123,9 +123,59 @@ def chunked(q, k, v, g, beta, scale, cu, cu_cpu, h0=None, h0_idx=None, ht=None, 
     return o
 
 
+FUSED = True  # gdn_tree runs the one-launch-per-level kernels when the plan carries their schedule (False: the per-call kernels)
+
+
+def gdn_tree_fused(q, k, v, g, beta, plan):
+    """gdn_tree on the fused kernels: one preparation launch for the layer (every chunk of every segment), then one scan launch per
+    level of the trie, a parent's state read once per group of siblings. The workspace is kept on the plan: every recurrent layer
+    of the forward reuses it."""
+    f = plan.fused
+    Hk, K = q.shape[-2], q.shape[-1]
+    Hv, V = v.shape[-2], v.shape[-1]
+    q3, qp = _rows(q, Hk, K, "q")
+    k3, kp = _rows(k, Hk, K, "k")
+    v3, vp = _rows(v, Hv, V, "v")
+    if qp != kp or g.stride(0) != beta.stride(0) or g.stride(1) != 1 or beta.stride(1) != 1:
+        raise SpinfError("gdn_tree: q / k and g / beta must share their row pitches")
+    if g.dtype != torch.float32 or beta.dtype != torch.bfloat16 or q3.dtype != torch.bfloat16 or v3.dtype != torch.bfloat16:
+        raise SpinfError("gdn_tree: expected bf16 q / k / v / beta and fp32 g")
+    _lib.init(q3.device)
+    rows = v3.shape[0]
+    o = torch.zeros((rows, Hv, V), dtype=torch.bfloat16, device=v3.device)
+    if f.plan_tokens == 0:
+        return o
+    L = _lib.lib()
+    need = int(L.spinf_gdn_tree_workspace_bytes(f.plan_tokens, Hv))
+    if f.workspace is None or f.workspace.numel() < need or f.workspace.device != q3.device:
+        f.workspace = torch.empty(need, dtype=torch.uint8, device=q3.device)
+    ws = f.workspace
+    check(
+        L.spinf_gdn_tree_prep(ptr(q3), ptr(k3), ptr(v3), ptr(g), ptr(beta), rows, qp, vp, g.stride(0), Hk, Hv, K, V, ptr(f.row_of), f.plan_tokens,
+                              ptr(f.chunk_p0), ptr(f.chunk_len), f.chunk_p0.numel(), ptr(ws), ws.numel(), stream_ptr()),
+        "spinf_gdn_tree_prep",
+    )
+    ops.COUNTS["launches"] += 1
+    scale = K**-0.5
+    prev_states = None
+    for (grp_parent, grp_ubeg, units), nk in zip(f.levels, f.n_keep):
+        states = torch.empty((nk, Hv, K, V), dtype=torch.float32, device=q3.device) if nk else None
+        check(
+            L.spinf_gdn_tree_scan(ptr(q3), ptr(k3), ptr(o), rows, qp, Hk, Hv, K, V, ctypes.c_float(scale), ptr(f.row_of), f.plan_tokens,
+                                  ptr(grp_parent), ptr(grp_ubeg), ptr(units), grp_parent.numel(), ptr(prev_states), ptr(states), ptr(ws),
+                                  ws.numel(), stream_ptr()),
+            "spinf_gdn_tree_scan",
+        )
+        ops.COUNTS["launches"] += 1
+        prev_states = states
+    return o
+
+
 def gdn_tree(q, k, v, g, beta, plan, mod=None):
     """q, k [T, Hk, Dk], v [T, Hv, Dv], g, beta [T, Hv] -> [T, Hv, Dv]: every segment of the plan from its parent's final state,
     level by level (gdn_indexed, qwen.py:550-590); the kernel reads and writes the stream rows itself through each call's idx"""
+    if FUSED and getattr(plan, "fused", None) is not None and q.shape[-1] == 128 and v.shape[-1] == 128 and q.is_cuda:
+        return gdn_tree_fused(q, k, v, g, beta, plan)
     scale = q.shape[-1] ** -0.5
     o = torch.zeros_like(v)
     prev_states = None

@@ -38,6 +38,91 @@ class TreePlan:
     seg_level: object | None = None
     seg_slot: object | None = None
     cap: dict | None = None
+    fused: object | None = None   # FusedSchedule: the same plan laid out for the one-launch-per-level kernels (this build's)
+
+
+UNIT_WORDS = 12
+UF_UPDATE, UF_PARENT = 1, 2
+LIGHT_UNITS = 4  # units per CTA in a group of read-only children
+
+
+@dataclass
+class FusedSchedule:
+    """The plan as the fused kernels read it (spinf_gdn_tree_prep / spinf_gdn_tree_scan). Plan order = the segments one after the
+    other in stream order; every segment is cut into chunks of at most 64 tokens. Per level the segments are grouped by parent: a
+    group's CTA holds the parent's state while it walks the group's units. A child that only reads that state (one chunk, no state
+    to keep) is "light": up to four light siblings share a 64-row unit at 16-row-aligned offsets. Any other child is "heavy": one
+    unit per chunk, each updating the state, the last one storing it where the child's own children will read it."""
+
+    plan_tokens: int
+    row_of: object      # int64 [plan_tokens]
+    chunk_p0: object    # int32 [n_chunks]
+    chunk_len: object   # int32 [n_chunks]
+    levels: list        # per level: (grp_parent int32 [G], grp_ubeg int32 [G + 1], units int32 [U, 12])
+    n_keep: list        # state slots per level
+    workspace: object = None
+
+
+def fused_schedule(starts, lens, parent_seg, depth, keeps, slot, row_of):
+    """host arrays of the fused kernels from the segment structure tree_plan derives (all numpy)"""
+    n_seg = len(starts)
+    pt0 = np.concatenate(([0], np.cumsum(lens)))[:-1] if n_seg else np.zeros(0, np.int64)
+    n_chunks_seg = (lens + 63) // 64
+    seg_of_chunk = np.repeat(np.arange(n_seg), n_chunks_seg)
+    first_chunk = np.concatenate(([0], np.cumsum(n_chunks_seg)))[:-1] if n_seg else np.zeros(0, np.int64)
+    t0 = (np.arange(len(seg_of_chunk)) - first_chunk[seg_of_chunk]) * 64
+    chunk_p0 = (pt0[seg_of_chunk] + t0).astype(np.int32)
+    chunk_len = np.minimum(64, lens[seg_of_chunk] - t0).astype(np.int32)
+    levels = []
+    for d in range(int(depth.max()) + 1 if n_seg else 0):
+        level = np.flatnonzero(depth == d)
+        # groups: siblings share a parent; roots are groups of their own (stream order is kept inside a group)
+        key = np.where(parent_seg[level] >= 0, parent_seg[level], -1 - level)
+        order = np.argsort(key, kind="stable")
+        level, key = level[order], key[order]
+        bounds = np.concatenate(([0], np.flatnonzero(np.diff(key)) + 1, [len(level)]))
+        grp_parent, grp_ubeg, units = [], [0], []
+        for a, b in zip(bounds[:-1], bounds[1:]):
+            ps = parent_seg[level[a]]
+            pslot = int(slot[ps]) if ps >= 0 else -1
+            first_unit = len(units)
+            open_unit = None  # the light unit being filled: [pieces, rows used]
+            for sgm in level[a:b]:
+                L, p0 = int(lens[sgm]), int(pt0[sgm])
+                if L <= 64 and not keeps[sgm]:
+                    need = (L + 15) // 16 * 16
+                    if open_unit is None or len(open_unit[0]) == 4 or open_unit[1] + need > 64:
+                        open_unit = [[], 0]
+                        units.append(open_unit)
+                    open_unit[0].append((p0, L))
+                    open_unit[1] += need
+                else:
+                    open_unit = None
+                    n = (L + 63) // 64
+                    for c in range(n):
+                        flags = UF_UPDATE | (UF_PARENT if c == 0 else 0)
+                        store = int(slot[sgm]) if (c == n - 1 and keeps[sgm]) else -1
+                        units.append((flags, store, (p0 + 64 * c, min(64, L - 64 * c))))
+            # a group whose children all only read the parent's state has no order to keep: it is cut into CTAs of at most
+            # LIGHT_UNITS units (each reads the parent's state once more, from L2), so that many leaves do not queue behind one CTA
+            n_units = len(units) - first_unit
+            if n_units > LIGHT_UNITS and all(isinstance(u, list) for u in units[first_unit:]):
+                for cut in range(first_unit + LIGHT_UNITS, len(units), LIGHT_UNITS):
+                    grp_parent.append(pslot)
+                    grp_ubeg.append(cut)
+            grp_parent.append(pslot)
+            grp_ubeg.append(len(units))
+        words = np.zeros((len(units), UNIT_WORDS), np.int32)
+        for i, u in enumerate(units):
+            if isinstance(u, list):
+                words[i, 0], words[i, 1], words[i, 2] = len(u[0]), UF_PARENT, -1
+                for j, (p0, L) in enumerate(u[0]):
+                    words[i, 4 + 2 * j], words[i, 5 + 2 * j] = p0, L
+            else:
+                words[i, 0], words[i, 1], words[i, 2] = 1, u[0], u[1]
+                words[i, 4], words[i, 5] = u[2]
+        levels.append((np.asarray(grp_parent, np.int32), np.asarray(grp_ubeg, np.int32), words))
+    return FusedSchedule(int(lens.sum()) if n_seg else 0, np.asarray(row_of, np.int64), chunk_p0, chunk_len, levels, [])
 
 
 def tree_plan(prev, real, device, max_init: int = 96, path: str = "indexed", short: int = 64, rows: int | None = None, keep=None,
@@ -116,6 +201,13 @@ def tree_plan(prev, real, device, max_init: int = 96, path: str = "indexed", sho
                 calls.append(Call(dev(token_rows(part)), cu.to(device, non_blocking=True), cu, None, False, kind, h0, ht))
         levels.append(calls)
 
+    all_rows = token_rows(np.arange(n_seg)) if n_seg else np.zeros(0, np.int64)
+    fused = fused_schedule(starts, lens, parent_seg, depth, keeps, slot, all_rows)
+    fused.n_keep = list(n_keep)
+    fused.row_of = dev(fused.row_of)
+    fused.chunk_p0, fused.chunk_len = dev(fused.chunk_p0), dev(fused.chunk_len)
+    fused.levels = [tuple(dev(x) for x in lv) for lv in fused.levels]
+
     conv = np.empty((T, 4), np.int64)
     conv[:, 3] = pos
     p = np.where(real, prev, -1)
@@ -130,4 +222,4 @@ def tree_plan(prev, real, device, max_init: int = 96, path: str = "indexed", sho
         sidx = dev(real_idx)
         seg_rows = np.full(rows, -1, np.int64)
         seg_rows[: len(real_idx)] = seg[real_idx]
-    return TreePlan(dev(conv), levels, n_seg, path, n_keep, rows, sidx, seg_rows, depth, slot)
+    return TreePlan(dev(conv), levels, n_seg, path, n_keep, rows, sidx, seg_rows, depth, slot, None, fused)

@@ -6,7 +6,10 @@ Fp8Linear and Fp8StaticLinear (spinf_serve/quant/linears.py:66-116) are built by
 reference calls them; torch._scaled_mm with per-tensor scales has a CPU kernel, so nothing is restated. TORCHDYNAMO_DISABLE makes
 the reference's torch.compile decorators run their functions eagerly (the arithmetic is the same ops). The static scale comes from
 the reference's calibration rule restated in one line (quant/calibrate.py:176-177; its main() needs a model and a GPU).
-Int8Linear (linears.py:40-64) in both modes: torch._int_mm has a CPU kernel (the reference pads to 17 rows itself)."""
+Int8Linear (linears.py:40-64) in both modes: torch._int_mm has a CPU kernel (the reference pads to 17 rows itself).
+Row-wise scheme (the benchmark's): Fp8RowLinear's constructor (linears.py:85-91: w8t, ws) and the reference's quant_act_row
+(linears.py:29-33, taken from the closure of Fp8RowLinear.forward) run eagerly on the CPU and are recorded; only the row-wise
+torch._scaled_mm of its forward has no CPU kernel, so no row-wise output is recorded (it is compared on the GPU instead)."""
 
 import math
 import os
@@ -47,6 +50,14 @@ def main(ref_root):
         out[f"xs{i}"] = np.float32(xs).reshape(1)
         out[f"y_dyn{i}"], out[f"y_sta{i}"] = bits(y_dyn), bits(y_sta)
         out[f"peak{i}"] = sta.peak.numpy().reshape(1)
+        row = ns.Fp8RowLinear(w)
+        fwd = type(row).forward
+        quant_act_row = fwd.__closure__[fwd.__code__.co_freevars.index("quant_act_row")].cell_contents
+        x8r, xsr = quant_act_row(x)
+        out[f"row_w8_{i}"] = row.w8t.t().contiguous().view(torch.uint8).numpy()
+        out[f"row_ws{i}"] = row.ws.numpy()
+        out[f"row_x8_{i}"] = x8r.contiguous().view(torch.uint8).numpy()
+        out[f"row_xs{i}"] = xsr.numpy()
         i8a, i8w = ns.Int8Linear(w, True), ns.Int8Linear(w, False)
         out[f"i8_w8_{i}"] = i8a.w8t.t().contiguous().numpy()
         out[f"i8_ws{i}"] = i8a.ws.numpy()

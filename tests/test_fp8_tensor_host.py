@@ -79,3 +79,14 @@ def test_int8_linear_matches_the_reference_outputs():
         assert torch.equal(O.int8_linear(x, w8, ws, True), bf16(G[f"y_i8a{i}"]))
         mine, ref = O.int8_linear(x, w8, ws, False), bf16(G[f"y_i8w{i}"])
         assert bool(((mine.float() - ref.float()).abs() <= ref.float().abs() * 2.0**-7 + 1e-30).all())
+
+
+def test_rowwise_quantisers_are_the_reference_s():
+    """the benchmark's scheme: the oracle's weight and activation quantisers against Fp8RowLinear's buffers and the reference's
+    quant_act_row run on the CPU (bit for bit: bytes and fp32 scales)"""
+    for i in range(3):
+        w, x = bf16(G[f"w{i}"]), bf16(G[f"x{i}"])
+        w8, ws = O.quantize_weight_rowwise(w)
+        assert np.array_equal(w8.view(torch.uint8).numpy(), G[f"row_w8_{i}"]) and np.array_equal(ws.numpy(), G[f"row_ws{i}"])
+        x8, xs = O.quant_act_row(x)
+        assert np.array_equal(x8.view(torch.uint8).numpy(), G[f"row_x8_{i}"]) and np.array_equal(xs.numpy(), G[f"row_xs{i}"])

@@ -147,3 +147,79 @@ def test_chunked_form_vs_its_oracle_and_the_token_recurrence(dev):
     assert e_o <= 2.0**-6 * scale_o and e_s <= 2e-3 * scale_s   # same roundings: a few bf16 last-bit flips apart
     assert e_ser <= 2e-2 * scale_o                              # the two forms differ by the chunk pipeline's bf16 operands
     assert bool((got[~touched] == 0).all())
+
+
+def test_fused_tree_kernels_vs_oracles(dev):
+    """the one-launch-per-level kernels (every segment in the chunked form, light siblings packed into shared tiles, a parent's
+    state read once per group) on tries with nested forks: against the chunk-form oracle (same rounding points) and the fp64
+    token recurrence; rows outside every segment stay zero; the per-call kernels agree to the chunk pipeline's roundings"""
+    from spinf_serve_b200 import gdn
+
+    for seed, long_trunk in ((0, 150), (1, 150), (2, 700)):
+        b = _batch(seed, long_trunk)
+        real = b.art >= 0
+        q, k, v, gl, beta = _inputs(b.length, seed)
+        plan_cpu = tree_plan(b.prev, real, "cpu")
+        want64 = OGD.gdn_tree(q, k, v, gl, beta, plan_cpu, dtype=torch.float64)
+        want_c = OGD.gdn_tree(q, k, v, gl, beta, plan_cpu, form="chunked")
+        plan = tree_plan(b.prev, real, dev)
+        assert plan.fused is not None and plan.fused.plan_tokens == int(real.sum())
+        dq, dk, dv, dg, db = (t.to(dev) for t in (q, k, v, gl, beta))
+        got = gdn.gdn_tree(dq, dk, dv, dg, db, plan).cpu()
+        gdn.FUSED = False
+        try:
+            calls = gdn.gdn_tree(dq, dk, dv, dg, db, plan).cpu()
+        finally:
+            gdn.FUSED = True
+        r = torch.from_numpy(real)
+        big = want64[r].float().abs().max().item()
+        e64 = (got[r].float() - want64[r].float()).abs().max().item()
+        ec = (got[r].float() - want_c[r].float()).abs().max().item()
+        ek = (got[r].float() - calls[r].float()).abs().max().item()
+        units = [int(u.shape[0]) for _, _, u in plan.fused.levels]
+        print(f"seed {seed}: {plan.n_segments} segments, units per level {units}: vs fp64 recurrence {e64:.3e}, vs chunk-form oracle {ec:.3e}, "
+              f"vs per-call kernels {ek:.3e} (|o| max {big:.3f})")
+        assert ec <= 2.0**-6 * big and e64 <= 2e-2 * big and ek <= 2e-2 * big
+        assert bool((got[~r] == 0).all())
+
+
+def test_fused_tree_rows_do_not_depend_on_the_packing(dev):
+    """a content's recurrent outputs are bit-identical whether its trie runs alone or packed after others (light siblings share
+    tiles, groups share launches: none of it may reach the values)"""
+    from spinf_serve_b200 import gdn
+
+    rng = np.random.default_rng(11)
+    trees = []
+    for j in range(3):
+        trunk = rng.integers(5, 50, int(rng.integers(70, 300))).tolist()
+        prompts = [trunk + [60 + i] + rng.integers(5, 50, int(rng.integers(3, 30))).tolist() for i in range(int(rng.integers(3, 9)))]
+        trees.append(P.build_grouped_tree(prompts, [P.ReadPlan.build([[5], [6, 7]]) for _ in prompts]))
+
+    def run(order):
+        pk = P.Packer(4096, 8192, align=True)
+        for j in order:
+            list(pk.push(j, trees[j]))
+        (b,) = list(pk.flush())
+        g = torch.Generator().manual_seed(3)
+        # every job draws its own inputs from its own generator, so that a job's tokens are the same in both packings
+        q = torch.zeros((b.length, Hk, D), dtype=torch.bfloat16)
+        k, v = torch.zeros_like(q), torch.zeros((b.length, Hv, D), dtype=torch.bfloat16)
+        gl, beta = torch.zeros((b.length, Hv)), torch.zeros((b.length, Hv), dtype=torch.bfloat16)
+        where = {}
+        for o in b.owners:
+            gj = torch.Generator().manual_seed(100 + o.job_id)
+            n = o.n_tokens
+            sl = slice(o.start, o.start + n)
+            q[sl] = torch.nn.functional.normalize(torch.randn((n, Hk, D), generator=gj), dim=-1).to(torch.bfloat16)
+            k[sl] = torch.nn.functional.normalize(torch.randn((n, Hk, D), generator=gj), dim=-1).to(torch.bfloat16)
+            v[sl] = torch.randn((n, Hv, D), generator=gj).to(torch.bfloat16)
+            gl[sl] = -torch.rand((n, Hv), generator=gj) * 0.3
+            beta[sl] = torch.rand((n, Hv), generator=gj).to(torch.bfloat16)
+            where[o.job_id] = sl
+        plan = tree_plan(b.prev, b.art >= 0, dev)
+        out = gdn.gdn_tree(q.to(dev), k.to(dev), v.to(dev), gl.to(dev), beta.to(dev), plan).cpu()
+        return {j: out[sl] for j, sl in where.items()}
+
+    alone = run([1])
+    packed = run([0, 2, 1])
+    assert torch.equal(alone[1], packed[1])
