@@ -88,3 +88,29 @@ def test_compact_rows_equal_the_stream_layout(dev):
     assert a.shape == c.shape and torch.equal(a[real], c[real])
     sel = torch.from_numpy(b.sel).to(dev)
     assert torch.equal(forward_one(stack, b, dev, rows=sel), c.index_select(0, sel))
+
+
+def test_hybrid_scores_within_the_stated_tolerance(dev):
+    """int4 weights with bf16 activations: no re-quantisation between the layers, so the option log-probs of the 4-layer hybrid
+    stack through the public scorer stay within 2e-3 of the oracle on average, p within 1e-3"""
+    from oracle import head as OH
+    from spinf_serve_b200 import parity, reads
+    from spinf_serve_b200.scorer import EngineConfig, Scorer, read_grouped
+
+    ocfg, W, stack = _build(dev)
+    rng = np.random.default_rng(12)
+    items = [((f"c{j}",), 0, _content(rng, int(rng.integers(30, 300)), int(rng.integers(2, 6)))) for j in range(5)]
+    sc = Scorer(stack, EngineConfig(token_budget=2048, max_tokens=8192), dev)
+    got = sc.score_grouped(items)
+    pk = P.Packer(2048, 8192, True, 1024)
+    want = {key: [None] * len(t.plans) for key, _, t in items}
+    for b in [b for key, first, t in items for b in pk.push((key, first), t)] + list(pk.flush()):
+        cols = Scorer._cols(b)
+        hf = OQ.forward(ocfg, W, b.ids, b.art, b.end, b.pos, tree_plan(b.prev, b.art >= 0, "cpu"))
+        lp = OH.option_logprobs(hf[torch.as_tensor(b.sel, dtype=torch.int64)], W["lm_head"], cols, None)
+        read_grouped(lp.numpy(), cols, b, want)
+    m = parity.compare(want, got)
+    dp = np.concatenate([np.abs(reads.option_probs(g)[1] - reads.option_probs(w)[1]) for k in want for g, w in zip(got[k], want[k])])
+    print(f"int4 hybrid, 4 layers: {m}; p max abs {dp.max():.3e}, mean {dp.mean():.3e}")
+    assert m["lp_mean_abs"] < 2e-3 and m["lp_max_abs"] < 2e-2
+    assert dp.mean() < 1e-3 and dp.max() < 1e-2
