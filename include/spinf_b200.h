@@ -330,6 +330,16 @@ int spinf_gdn_tree_scan(const void* q, const void* k, void* o, int64_t n_rows, i
                         const int32_t* grp_ubeg, const int32_t* units, int64_t n_groups, const float* h_in, float* h_out,
                         void* workspace, int64_t workspace_bytes, void* stream);
 
+/* spinf_gdn_tree_scan on the 5th-generation tensor cores: the same units, arithmetic and rounding points, with tcgen05.mma on
+ * 128-byte-swizzled operand tiles in shared memory and the state (whole 128 x 128, no column slices) in tensor memory for the
+ * CTA's lifetime. Takes the workspace spinf_gdn_tree_prep filled, and unit_rows [units, 4, 64] int32, the units' rows spelled
+ * out by the host: per row its plan token (-1: no token), its stream row (< 2^31), the plan token of its piece's last token, its
+ * piece's first row. Every wait inside the kernel is bounded; one that gives up is reported through spinf_last_status. */
+int spinf_gdn_tree_scan_tc(const void* q, const void* k, void* o, int64_t n_rows, int64_t q_pitch, int32_t Hk, int32_t Hv, int32_t K,
+                           int32_t V, float scale, int64_t plan_tokens, const int32_t* grp_parent, const int32_t* grp_ubeg,
+                           const int32_t* units, const int32_t* unit_rows, int64_t n_groups, const float* h_in, float* h_out,
+                           void* workspace, int64_t workspace_bytes, void* stream);
+
 /* Replaces the steps of GatedDeltaNet.forward before the recurrence (spinf_serve/models/qwen35/qwen.py:651-668), fused: for each of
  * the T tokens, from the in-projection rows y [n_rows, y_pitch] bf16 = [q | k | v | z | b | a]: the 4-tap path convolution over
  * conv [T, 4] int64 (a tap index >= n_rows or < 0 is the zero row) with conv_w [2 Hk K + Hv V, 4] bf16 in fp32, SiLU, rounding

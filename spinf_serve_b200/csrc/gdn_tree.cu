@@ -182,7 +182,15 @@ __global__ void __launch_bounds__(128, 2) gdn_tree_prep_kernel(const GdnTreeArgs
     if (active)
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) {
-      if (nt > 2 * warp + 1) break;  // columns past this warp's diagonal block are never read
+      if (nt > 2 * warp + 1) {  // columns past this warp's diagonal block: A there is never read, P is zero (a scan that multiplies
+        // whole 64 x 64 tiles reads every column of a row)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int t = 16 * warp + gq + 8 * h;
+          if (t < len) *reinterpret_cast<uint32_t*>(a.p_ws + (static_cast<int64_t>(p0 + t) * a.Hv + hv) * CT + 8 * nt + 2 * tq) = 0u;
+        }
+        continue;
+      }
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const int t = 16 * warp + gq + 8 * h, s0 = 8 * nt + 2 * tq;

@@ -124,6 +124,7 @@ def chunked(q, k, v, g, beta, scale, cu, cu_cpu, h0=None, h0_idx=None, ht=None, 
 
 
 FUSED = True  # gdn_tree runs the one-launch-per-level kernels when the plan carries their schedule (False: the per-call kernels)
+SCAN = "tc"  # the level scan: "tc" = tcgen05 / tensor memory (spinf_gdn_tree_scan_tc), "mma" = warp-level MMAs (spinf_gdn_tree_scan)
 
 
 def gdn_tree_fused(q, k, v, g, beta, plan):
@@ -158,14 +159,22 @@ def gdn_tree_fused(q, k, v, g, beta, plan):
     ops.COUNTS["launches"] += 1
     scale = K**-0.5
     prev_states = None
-    for (grp_parent, grp_ubeg, units), nk in zip(f.levels, f.n_keep):
+    for (grp_parent, grp_ubeg, units, unit_rows), nk in zip(f.levels, f.n_keep):
         states = torch.empty((nk, Hv, K, V), dtype=torch.float32, device=q3.device) if nk else None
-        check(
-            L.spinf_gdn_tree_scan(ptr(q3), ptr(k3), ptr(o), rows, qp, Hk, Hv, K, V, ctypes.c_float(scale), ptr(f.row_of), f.plan_tokens,
-                                  ptr(grp_parent), ptr(grp_ubeg), ptr(units), grp_parent.numel(), ptr(prev_states), ptr(states), ptr(ws),
-                                  ws.numel(), stream_ptr()),
-            "spinf_gdn_tree_scan",
-        )
+        if SCAN == "tc":
+            check(
+                L.spinf_gdn_tree_scan_tc(ptr(q3), ptr(k3), ptr(o), rows, qp, Hk, Hv, K, V, ctypes.c_float(scale), f.plan_tokens, ptr(grp_parent),
+                                         ptr(grp_ubeg), ptr(units), ptr(unit_rows), grp_parent.numel(), ptr(prev_states), ptr(states), ptr(ws),
+                                         ws.numel(), stream_ptr()),
+                "spinf_gdn_tree_scan_tc",
+            )
+        else:
+            check(
+                L.spinf_gdn_tree_scan(ptr(q3), ptr(k3), ptr(o), rows, qp, Hk, Hv, K, V, ctypes.c_float(scale), ptr(f.row_of), f.plan_tokens,
+                                      ptr(grp_parent), ptr(grp_ubeg), ptr(units), grp_parent.numel(), ptr(prev_states), ptr(states), ptr(ws),
+                                      ws.numel(), stream_ptr()),
+                "spinf_gdn_tree_scan",
+            )
         ops.COUNTS["launches"] += 1
         prev_states = states
     return o

@@ -58,7 +58,7 @@ class FusedSchedule:
     row_of: object      # int64 [plan_tokens]
     chunk_p0: object    # int32 [n_chunks]
     chunk_len: object   # int32 [n_chunks]
-    levels: list        # per level: (grp_parent int32 [G], grp_ubeg int32 [G + 1], units int32 [U, 12])
+    levels: list        # per level: (grp_parent int32 [G], grp_ubeg int32 [G + 1], units int32 [U, 12], unit_rows int32 [U, 4, 64])
     n_keep: list        # state slots per level
     workspace: object = None
 
@@ -66,6 +66,9 @@ class FusedSchedule:
 def fused_schedule(starts, lens, parent_seg, depth, keeps, slot, row_of):
     """host arrays of the fused kernels from the segment structure tree_plan derives (all numpy)"""
     n_seg = len(starts)
+    row_of = np.asarray(row_of, np.int64)
+    if len(row_of) and int(row_of.max()) >= 2**31:
+        raise ValueError("fused_schedule: stream rows must fit 31 bits")
     pt0 = np.concatenate(([0], np.cumsum(lens)))[:-1] if n_seg else np.zeros(0, np.int64)
     n_chunks_seg = (lens + 63) // 64
     seg_of_chunk = np.repeat(np.arange(n_seg), n_chunks_seg)
@@ -113,16 +116,25 @@ def fused_schedule(starts, lens, parent_seg, depth, keeps, slot, row_of):
             grp_parent.append(pslot)
             grp_ubeg.append(len(units))
         words = np.zeros((len(units), UNIT_WORDS), np.int32)
+        rows = np.zeros((len(units), 4, 64), np.int32)  # per unit row: plan token (-1: none), stream row, the piece's last token, its first row
+        rows[:, 0] = -1
         for i, u in enumerate(units):
             if isinstance(u, list):
                 words[i, 0], words[i, 1], words[i, 2] = len(u[0]), UF_PARENT, -1
-                for j, (p0, L) in enumerate(u[0]):
-                    words[i, 4 + 2 * j], words[i, 5 + 2 * j] = p0, L
+                pieces = u[0]
             else:
                 words[i, 0], words[i, 1], words[i, 2] = 1, u[0], u[1]
-                words[i, 4], words[i, 5] = u[2]
-        levels.append((np.asarray(grp_parent, np.int32), np.asarray(grp_ubeg, np.int32), words))
-    return FusedSchedule(int(lens.sum()) if n_seg else 0, np.asarray(row_of, np.int64), chunk_p0, chunk_len, levels, [])
+                pieces = [u[2]]
+            off = 0
+            for j, (p0, L) in enumerate(pieces):
+                words[i, 4 + 2 * j], words[i, 5 + 2 * j] = p0, L
+                rows[i, 0, off : off + L] = np.arange(p0, p0 + L)
+                rows[i, 1, off : off + L] = row_of[p0 : p0 + L]
+                rows[i, 2, off : off + L] = p0 + L - 1
+                rows[i, 3, off : off + L] = off
+                off += (L + 15) // 16 * 16
+        levels.append((np.asarray(grp_parent, np.int32), np.asarray(grp_ubeg, np.int32), words, rows))
+    return FusedSchedule(int(lens.sum()) if n_seg else 0, row_of, chunk_p0, chunk_len, levels, [])
 
 
 def tree_plan(prev, real, device, max_init: int = 96, path: str = "indexed", short: int = 64, rows: int | None = None, keep=None,

@@ -161,8 +161,9 @@ def test_int4_linear_at_the_hybrid_models_widest_shape(dev):
 
 def test_recurrence_forms_agree_at_the_hybrid_models_shape(dev):
     """configuration 5's recurrent layer (16 key / 32 value heads of 128) over a stream of 2 000-token trunks with 32 branches of
-    20 tokens: the plan's long segments through the chunked kernels and everything through the token-serial kernel agree to the
-    chunk pipeline's bf16 operand roundings; rows outside every segment stay zero"""
+    20 tokens: the whole plan through the one-launch-per-level kernels, the plan's long segments through the per-call chunked kernels,
+    and everything through the token-serial kernel agree to the chunk pipeline's bf16 operand roundings; rows outside every segment
+    stay zero"""
     from spinf_serve_b200 import gdn, workloads
     from spinf_serve_b200.gdn_plan import tree_plan
     from spinf_serve_b200.packer import Packer
@@ -179,15 +180,22 @@ def test_recurrence_forms_agree_at_the_hybrid_models_shape(dev):
     real = b.art >= 0
     plan = tree_plan(b.prev, real, dev)
     assert any(c.kind == "chunked" for lv in plan.levels for c in lv) and any(c.kind == "recurrent" for lv in plan.levels for c in lv)
-    mixed = gdn.gdn_tree(q, k, v, gl, beta, plan)
+    fused = gdn.gdn_tree(q, k, v, gl, beta, plan)  # the one-launch-per-level kernels (every segment in the chunked form)
     serial_plan = tree_plan(b.prev, real, dev)
     for lv in serial_plan.levels:
         for c in lv:
             c.kind = "recurrent"
-    serial = gdn.gdn_tree(q, k, v, gl, beta, serial_plan)
+    gdn.FUSED = False
+    try:
+        mixed = gdn.gdn_tree(q, k, v, gl, beta, plan)          # the per-call kernels as the reference dispatches them
+        serial = gdn.gdn_tree(q, k, v, gl, beta, serial_plan)  # everything token by token
+    finally:
+        gdn.FUSED = True
     r = torch.from_numpy(real).to(dev)
-    assert (mixed[r].float() - serial[r].float()).abs().max() <= 2e-2 * serial[r].float().abs().max()
-    assert bool((mixed[~r] == 0).all())
+    big = serial[r].float().abs().max()
+    assert (mixed[r].float() - serial[r].float()).abs().max() <= 2e-2 * big
+    assert (fused[r].float() - serial[r].float()).abs().max() <= 2e-2 * big
+    assert bool((mixed[~r] == 0).all()) and bool((fused[~r] == 0).all())
 
 
 def test_option_read_at_full_vocabulary(dev):

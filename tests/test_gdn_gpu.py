@@ -149,12 +149,21 @@ def test_chunked_form_vs_its_oracle_and_the_token_recurrence(dev):
     assert bool((got[~touched] == 0).all())
 
 
-def test_fused_tree_kernels_vs_oracles(dev):
+@pytest.mark.parametrize("scan", ["mma", "tc"])
+def test_fused_tree_kernels_vs_oracles(dev, scan):
     """the one-launch-per-level kernels (every segment in the chunked form, light siblings packed into shared tiles, a parent's
     state read once per group) on tries with nested forks: against the chunk-form oracle (same rounding points) and the fp64
     token recurrence; rows outside every segment stay zero; the per-call kernels agree to the chunk pipeline's roundings"""
     from spinf_serve_b200 import gdn
 
+    old, gdn.SCAN = gdn.SCAN, scan
+    try:
+        _fused_cases(dev, gdn, scan)
+    finally:
+        gdn.SCAN = old
+
+
+def _fused_cases(dev, gdn, scan):
     for seed, long_trunk in ((0, 150), (1, 150), (2, 700)):
         b = _batch(seed, long_trunk)
         real = b.art >= 0
@@ -176,14 +185,15 @@ def test_fused_tree_kernels_vs_oracles(dev):
         e64 = (got[r].float() - want64[r].float()).abs().max().item()
         ec = (got[r].float() - want_c[r].float()).abs().max().item()
         ek = (got[r].float() - calls[r].float()).abs().max().item()
-        units = [int(u.shape[0]) for _, _, u in plan.fused.levels]
-        print(f"seed {seed}: {plan.n_segments} segments, units per level {units}: vs fp64 recurrence {e64:.3e}, vs chunk-form oracle {ec:.3e}, "
+        units = [int(lv[2].shape[0]) for lv in plan.fused.levels]
+        print(f"scan {scan}, seed {seed}: {plan.n_segments} segments, units per level {units}: vs fp64 recurrence {e64:.3e}, vs chunk-form oracle {ec:.3e}, "
               f"vs per-call kernels {ek:.3e} (|o| max {big:.3f})")
         assert ec <= 2.0**-6 * big and e64 <= 2e-2 * big and ek <= 2e-2 * big
         assert bool((got[~r] == 0).all())
 
 
-def test_fused_tree_rows_do_not_depend_on_the_packing(dev):
+@pytest.mark.parametrize("scan", ["mma", "tc"])
+def test_fused_tree_rows_do_not_depend_on_the_packing(dev, scan):
     """a content's recurrent outputs are bit-identical whether its trie runs alone or packed after others (light siblings share
     tiles, groups share launches: none of it may reach the values)"""
     from spinf_serve_b200 import gdn
@@ -220,6 +230,10 @@ def test_fused_tree_rows_do_not_depend_on_the_packing(dev):
         out = gdn.gdn_tree(q.to(dev), k.to(dev), v.to(dev), gl.to(dev), beta.to(dev), plan).cpu()
         return {j: out[sl] for j, sl in where.items()}
 
-    alone = run([1])
-    packed = run([0, 2, 1])
+    old, gdn.SCAN = gdn.SCAN, scan
+    try:
+        alone = run([1])
+        packed = run([0, 2, 1])
+    finally:
+        gdn.SCAN = old
     assert torch.equal(alone[1], packed[1])
