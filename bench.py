@@ -476,18 +476,156 @@ def gpu_arm(args):
         dist.destroy_process_group()
 
 
+def other_config_arm(args):
+    """--config 4 / 5: the same two legs (resident and end to end) on the other single-GPU benchmark configurations, full models at
+    full depth: 4 = the Gemma-style 31B-class fp8 model over contents of a 1000-token trunk + 32 questions of 16 tokens with 5
+    options (21 contents = 672 questions per 32256-token forward); 5 = the Qwen-style 27B hybrid with int4 weights over contents of a
+    2000-token trunk + 32 questions of 20 tokens with 5 options (12 contents = 384 questions per 32256-token forward)"""
+    import torch
+    import torch.distributed as dist
+
+    from spinf_serve_b200 import _lib, ops, workloads
+    from spinf_serve_b200.packer import Packer
+    from spinf_serve_b200.scorer import EngineConfig, Scorer, stage_one
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the scoring path has no CPU fallback")
+    dev = torch.device(f"cuda:{local}")
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.init(dev)
+    if args.config == 4:
+        from spinf_serve_b200.gemma_stack import CONFIGS, GemmaConfig, GemmaStack, GemmaWeights
+
+        cfg = GemmaConfig(**CONFIGS["gemma31b"])
+        stack = GemmaStack(GemmaWeights.random(cfg, seed=0, device=dev))
+        per, name = 21, "cfg4: gemma-style 31B-class fp8 row-wise (60 layers, hidden 5376, 32 / 16 heads of 128), 21 contents x (1000-token trunk + 32 questions x 16 tokens, 5 single-token options), one 32256-token forward"
+        wl = workloads.fixed("cfg4", per, 1000, 32, 16, 5, 262144, per * 1536, seed=rank, first_id=per * rank)
+        kernel, kind, dtype = "gemm_tc_kernel<fp8, 256, *> (row-wise fp8 linears)", "fp8_gemm", "fp8_e4m3"
+    else:
+        from spinf_serve_b200.qwen_stack import QwenConfig, QwenStack, QwenWeights
+
+        cfg = QwenConfig()
+        stack = QwenStack(QwenWeights.random(cfg, seed=0, device=dev))
+        per, name = 12, "cfg5: qwen-style 27B hybrid, int4 group-128 weights (64 layers, 3 Gated DeltaNet : 1 attention, hidden 5120), 12 contents x (2000-token trunk + 32 questions x 20 tokens, 5 single-token options), one 32256-token forward"
+        wl = workloads.fixed("cfg5", per, 2000, 32, 20, 5, 248320, per * 2688, seed=rank, first_id=per * rank)
+        kernel, kind, dtype = "w4_gemm_kernel (int4 group-128 weight-only linears, bf16 tensor cores)", "w4_gemm", "int4_w_bf16_a"
+    ecfg = EngineConfig(token_budget=wl.token_budget, max_tokens=65536)
+    scorer = Scorer(stack, ecfg, dev)
+    pk = Packer(ecfg.token_budget, ecfg.max_tokens, ecfg.align_jobs, ecfg.min_stream)
+    (b,) = [x for key, first, t in wl.items for x in pk.push((key, first), t)] + list(pk.flush())
+    sc, inputs, masks, st = stage_one(stack, b, dev, ecfg)
+    W = stack.w.lm_weight
+    ws = torch.empty(int(_lib.lib().spinf_option_logprobs_workspace_bytes(len(b.sel), W.shape[0], st["cols"].numel())), dtype=torch.uint8, device=dev)
+
+    def step():
+        rows = stack.forward(sc, b, inputs, masks, rows=st["sel"])
+        return ops.option_logprobs(rows, W, st["cols"], None, ws)
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(args.warmup):
+        step()
+    sync()
+    _lib.last_status()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ops.PROFILE = []
+    launches0 = ops.COUNTS["launches"]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        lp = step()
+    e1.record()
+    sync()
+    launches = ops.COUNTS["launches"] - launches0
+    prof, ops.PROFILE = ops.PROFILE, None
+    ms = e0.elapsed_time(e1)
+    _lib.last_status()
+    if not bool(torch.isfinite(lp).all()):
+        raise RuntimeError("non-finite log-probs")
+    for _ in range(min(args.warmup, 2)):
+        scorer.score_grouped(wl.items)
+    bulk = [((s,) + tuple(key), first, tree) for s in range(args.steps) for key, first, tree in wl.items]
+    s0 = (scorer.stats.forwards, scorer.stats.tokens, scorer.stats.h2d_bytes, scorer.stats.d2h_bytes)
+    sync()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    out = scorer.score_grouped(bulk)
+    f1.record()
+    sync()
+    ms_e2e = f0.elapsed_time(f1)
+    clocks = sampler.stop() if rank == 0 else None
+    forwards = scorer.stats.forwards - s0[0]
+    scored = sum(1 for v in out.values() for x in v if x is not None)
+    if world > 1:
+        t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = float(t[0]), float(t[1])
+    if rank == 0:
+        peaks = _peaks()
+        gemm = [(x.elapsed_time(y), f) for x, y, f, k in prof if k == kind]
+        gemm_ms, gemm_flops = sum(t for t, _ in gemm), sum(f for _, f in gemm)
+        achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
+        if args.config == 4:
+            fp8 = measure_fp8_peak(dev)
+            peak, src = fp8["sustained"], "library per-tensor fp8 GEMM 8192^3 measured in this run, back to back for 2 s"
+        else:
+            peak, src = peaks["bf16_sustained"], f"bf16 matmul 8192^3 back to back, {peaks['source']} (MEASURED_PEAKS.json)"
+        line = {
+            "metric": METRIC, "value": world * wl.n_questions * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype,
+            "data": "synthetic",
+            "config": {"workload": name, "per_gpu": f"{per} contents / {wl.n_questions} questions / {wl.n_tokens} tokens per step",
+                       "parallelism": f"{world} replicas, content-sharded", "l2": "inputs larger than L2 (weights and activations of a full-depth forward)"},
+            "e2e": {"value": world * scored / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e / max(forwards, 1),
+                    "h2d_bytes_per_step": int((scorer.stats.h2d_bytes - s0[2]) // max(forwards, 1)),
+                    "d2h_bytes_per_step": int((scorer.stats.d2h_bytes - s0[3]) // max(forwards, 1)), "forwards": forwards,
+                    "tokens": scorer.stats.tokens - s0[1], "forwards_match_steps": forwards == args.steps},
+            "gpu_launches": int(launches),
+            "roofline": {"kernel": kernel, "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                         "peak_source": src, "traffic": None, "launches": len(gemm), "share_of_step": gemm_ms / ms if ms > 0 else None},
+            "clocks": clocks,
+        }
+        attn_ms = sum(x.elapsed_time(y) for x, y, _, k in prof if k.startswith("attn:"))
+        line["attention"] = {"ms_per_step": attn_ms / args.steps, "share_of_step": attn_ms / ms}
+        gdn = [(x.elapsed_time(y), f) for x, y, f, k in prof if k == "gdn"]
+        if gdn:
+            g_ms, g_bytes = sum(t for t, _ in gdn), sum(f for _, f in gdn)
+            line["recurrence"] = {
+                "kernel": "gdn_tree_prep + gdn_tree_scan_tc (one layer pass = one preparation launch + one scan launch per level)", "bound": "hbm",
+                "ms_per_layer_pass": g_ms / len(gdn), "achieved": g_bytes / (g_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": g_bytes / (g_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "share_of_step": g_ms / ms, "layer_passes": len(gdn),
+            }
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--config", type=int, default=2, choices=[2, 4, 5], help="benchmark configuration: 2 (the headline, default), 4 (31B-class fp8), 5 (27B hybrid int4)")
     ap.add_argument("--bulk-contents", type=int, default=2624, help="contents of the bulk (configuration-3) leg, about 160 passes; 0 skips the leg")
     ap.add_argument("--no-attention", action="store_true", help="skip the attention-alone (configuration-1) block")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle timing (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
+    elif args.config != 2:
+        other_config_arm(args)
     else:
         gpu_arm(args)
 

@@ -151,6 +151,10 @@ def gdn_tree_fused(q, k, v, g, beta, plan):
     if f.workspace is None or f.workspace.numel() < need or f.workspace.device != q3.device:
         f.workspace = torch.empty(need, dtype=torch.uint8, device=q3.device)
     ws = f.workspace
+    prof = ops.PROFILE
+    if prof is not None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
     check(
         L.spinf_gdn_tree_prep(ptr(q3), ptr(k3), ptr(v3), ptr(g), ptr(beta), rows, qp, vp, g.stride(0), Hk, Hv, K, V, ptr(f.row_of), f.plan_tokens,
                               ptr(f.chunk_p0), ptr(f.chunk_len), f.chunk_p0.numel(), ptr(ws), ws.numel(), stream_ptr()),
@@ -177,6 +181,10 @@ def gdn_tree_fused(q, k, v, g, beta, plan):
             )
         ops.COUNTS["launches"] += 1
         prev_states = states
+    if prof is not None:
+        e1.record()
+        # q, k in; v in and o out (bf16); g fp32 and beta bf16: the bytes a pass must move per real token
+        prof.append((e0, e1, float(f.plan_tokens) * (2 * Hk * K * 2 + 2 * Hv * V * 2 + Hv * 6), "gdn"))
     return o
 
 

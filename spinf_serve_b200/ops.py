@@ -12,8 +12,9 @@ from spinf_serve_b200._lib import SpinfError, check, ptr, stream_ptr
 FP8 = torch.float8_e4m3fn
 
 # Measurement hooks (bench.py): COUNTS["launches"] counts the kernels this module enqueued; when PROFILE is a list, every row-wise
-# fp8 GEMM and every attention launch is bracketed by CUDA events on its stream and (start, end, flops, kind) is appended (kind
-# "fp8_gemm" with its 2 M N K, or "attn:<window>" with flops left 0: the caller knows the stream's unmasked pairs).
+# fp8 or int4 GEMM, every attention launch and every recurrent layer pass is bracketed by CUDA events on its stream and
+# (start, end, work, kind) is appended: kind "fp8_gemm" / "w4_gemm" with 2 M N K, "attn:<window>" with 0 (the caller knows the
+# stream's unmasked pairs), "gdn" with the pass's algorithmic bytes.
 COUNTS = {"launches": 0}
 PROFILE = None
 
@@ -185,7 +186,14 @@ def w4_gemm_glu(x, qw, scales, group, act="silu"):
         raise SpinfError(f"w4_gemm_glu: shapes do not agree: x {tuple(x.shape)}, qw {tuple(qw.shape)}, scales {tuple(scales.shape)}")
     y = torch.empty((M, N2 // 2), dtype=torch.bfloat16, device=x.device)
     code = {"gelu_tanh": 0, "silu": 1}[act]
+    prof = PROFILE
+    if prof is not None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
     check(_lib.lib().spinf_w4_gemm_glu(ptr(x), ptr(qw), ptr(scales), group, code, ptr(y), M, N2, K, N2 // 2, stream_ptr()), "spinf_w4_gemm_glu")
+    if prof is not None:
+        e1.record()
+        prof.append((e0, e1, 2.0 * M * N2 * K, "w4_gemm"))
     COUNTS["launches"] += 1
     return y
 
@@ -204,7 +212,14 @@ def w4_gemm(x, qw, scales, group, extra=None):
     if extra is not None:
         _need(extra, torch.bfloat16, "extra", 2)
     y = torch.empty((M, N + E), dtype=torch.bfloat16, device=x.device)
+    prof = PROFILE
+    if prof is not None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
     check(_lib.lib().spinf_w4_gemm(ptr(x), ptr(qw), ptr(scales), group, ptr(y), M, N, K, N + E, stream_ptr()), "spinf_w4_gemm")
+    if prof is not None:
+        e1.record()
+        prof.append((e0, e1, 2.0 * M * N * K, "w4_gemm"))
     COUNTS["launches"] += 1
     if E:
         tail = ctypes.c_void_p(y.data_ptr() + 2 * N)

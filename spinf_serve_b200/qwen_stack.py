@@ -57,23 +57,64 @@ class QwenWeights:
         self.embed = W["embed"].to(dev).contiguous()
         self.lm_head = W["lm_head"].to(dev).contiguous()
         self.norm = W["norm"].to(dev).contiguous()
+        self.layers = [self._layer(L, dev, fuse_glu) for L in W["layers"]]
+
+    @staticmethod
+    def _layer(L, dev, fuse_glu):
+        out = {"kind": L["kind"]}
+        for k, v in L.items():
+            if k == "kind":
+                continue
+            if isinstance(v, tuple):
+                out[k] = Int4Linear(v[0].to(dev), v[1].to(dev))
+            elif k in ("A_log", "dt_bias"):
+                out[k] = v.to(dev, torch.float32).contiguous()
+            else:
+                out[k] = v.to(dev).contiguous()
+        if "in_extra" in out:
+            out["in_proj"].set_extra(out.pop("in_extra"))  # the b and a rows ride in the same output (qwen.py:421-426)
+        if fuse_glu:
+            out["gate_up"].fuse_glu("silu")
+        return out
+
+    @classmethod
+    def random(cls, cfg: QwenConfig, seed: int, device, fuse_glu: bool = True):
+        """random-init weights of the architecture, generated on the device one layer at a time (GPTQ-format int4 linears with
+        uniform random nibbles and small positive scales, bf16 / fp32 small parameters): the benchmark's synthetic hybrid model"""
+        dev = torch.device(device)
+        g = torch.Generator(device=dev).manual_seed(seed)
+
+        def bf(*shape, std=0.05):
+            return (torch.randn(shape, generator=g, device=dev) * std).to(torch.bfloat16)
+
+        def int4(out_f, in_f):
+            qweight = torch.randint(-(2**31), 2**31 - 1, (in_f // 8, out_f), generator=g, device=dev, dtype=torch.int64).to(torch.int32)
+            scales = (torch.rand((in_f // cfg.group, out_f), generator=g, device=dev) * 0.01 + 0.001).to(torch.float16)
+            return qweight, scales
+
+        self = cls.__new__(cls)
+        self.cfg, self.fuse_glu = cfg, fuse_glu
+        self.embed, self.lm_head, self.norm = bf(cfg.vocab, cfg.hidden, std=0.5), bf(cfg.vocab, cfg.hidden), bf(cfg.hidden, std=0.1)
+        kd, vd = cfg.hk * cfg.dk, cfg.hv * cfg.dv
         self.layers = []
-        for L in W["layers"]:
-            out = {"kind": L["kind"]}
-            for k, v in L.items():
-                if k == "kind":
-                    continue
-                if isinstance(v, tuple):
-                    out[k] = Int4Linear(v[0].to(dev), v[1].to(dev))
-                elif k in ("A_log", "dt_bias"):
-                    out[k] = v.to(dev, torch.float32).contiguous()
-                else:
-                    out[k] = v.to(dev).contiguous()
-            if "in_extra" in out:
-                out["in_proj"].set_extra(out.pop("in_extra"))  # the b and a rows ride in the same output (qwen.py:421-426)
-            if fuse_glu:
-                out["gate_up"].fuse_glu("silu")
-            self.layers.append(out)
+        for kind in cfg.layer_types:
+            L = {"kind": kind, "input_ln": bf(cfg.hidden, std=0.1), "post_ln": bf(cfg.hidden, std=0.1),
+                 "gate_up": int4(2 * cfg.ffn, cfg.hidden), "down": int4(cfg.hidden, cfg.ffn)}
+            if kind == "linear_attention":
+                L["in_proj"] = int4(2 * kd + 2 * vd, cfg.hidden)
+                L["in_extra"] = bf(2 * cfg.hv, cfg.hidden, std=0.02)
+                L["out_proj"] = int4(cfg.hidden, vd)
+                L["conv_w"] = bf(2 * kd + vd, 4, std=0.5)
+                L["A_log"] = torch.randn(cfg.hv, generator=g, device=dev) * 0.5
+                L["dt_bias"] = torch.randn(cfg.hv, generator=g, device=dev)
+                L["gdn_norm"] = (1 + 0.1 * torch.randn(cfg.dv, generator=g, device=dev)).to(torch.bfloat16)
+            else:
+                L["qkv_proj"] = int4((2 * cfg.heads + 2 * cfg.kv_heads) * cfg.head_dim, cfg.hidden)
+                L["o_proj"] = int4(cfg.hidden, cfg.heads * cfg.head_dim)
+                L["q_norm"], L["k_norm"] = bf(cfg.head_dim, std=0.1), bf(cfg.head_dim, std=0.1)
+            self.layers.append(cls._layer(L, dev, fuse_glu))
+            del L
+        return self
 
     @property
     def lm_weight(self):
