@@ -151,6 +151,16 @@ int spinf_w4_gemm(const void* x, const void* qw, const void* scales, int32_t gro
  * pair (k, k+1) out of a word with one shift and one mask. Both 4-byte aligned, K a multiple of 8. */
 int spinf_w4_repack(const void* q_in, void* q_out, int64_t N, int64_t K, void* stream);
 
+/* Replaces the W4A16 linear of the extraction decoder's steps (spinf_serve/quant/w4gemm.py:17-66, `linear`): a few rows (M <= 128)
+ * against int4 weights read as the engine stores them, streamed once. x [M, K] bf16 (rounded to fp16 as the reference does);
+ * q uint8 [N, K/2] in the ENGINE layout (byte b = k 2b in the low nibble, k 2b + 1 in the high one; value nibble - 8; not
+ * re-ordered by spinf_w4_repack); scales fp16 [N, K / group]. y[m, n] = bf16( sum over split-K partial sums, in split order, of
+ * fp32 sums of fp16 products x[m, k] * fp16((nibble - 8) * scale) ); y bf16 with row pitch y_pitch. K a multiple of 256, group a
+ * multiple of 32 that divides 256. The split count follows the reference (about 512 programs of 64 output channels). */
+int64_t spinf_w4_small_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int spinf_w4_small(const void* x, const void* q, const void* scales, int32_t group, void* y, int64_t M, int64_t N, int64_t K,
+                   int64_t y_pitch, void* workspace, int64_t workspace_bytes, void* stream);
+
 /* The gate|up projection of a gated MLP with its activation in the GEMM epilogue: replaces Int4Linear.forward on the fused gate_up
  * weight followed by act(gate) * up (spinf_serve/models/qwen35/qwen.py:455-458 and the MLP around it, :700-712):
  *   y[m,c] = bf16( bf16(act(g)) * u ),  g = bf16(sum_k x[m,k] w[2c,k]),  u = bf16(sum_k x[m,k] w[2c+1,k]),   c < N2 / 2,
@@ -339,6 +349,25 @@ int spinf_gdn_tree_scan_tc(const void* q, const void* k, void* o, int64_t n_rows
                            int32_t V, float scale, int64_t plan_tokens, const int32_t* grp_parent, const int32_t* grp_ubeg,
                            const int32_t* units, const int32_t* unit_rows, int64_t n_groups, const float* h_in, float* h_out,
                            void* workspace, int64_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------- extraction decoder's attention
+ * Replaces `_x_attention` (spinf_serve/decode.py:71-104), the attention of a batched decoding step: G groups, Q slots each (one new
+ * token per slot), H query heads over h key/value heads of D. Token-major tensors, all bf16:
+ *   q   rows (g * Q + slot) of q_pitch elements, head j at offset j * D          out  the same shape, row pitch out_pitch
+ *   kp, vp [G, Lp, h, D]  the groups' prefixes, pos_p [G, Lp] int32 positions (-1: padding, never attended)
+ *   kt, vt [G, Tt, h, D]  the templates, pos_t their positions, own_t [G, Tt] the owning prompt (-1: padding): slot s attends to
+ *                         the tokens of prompt s / beam only
+ *   gk, gv [G, Q, S, h, D] the tokens generated by each slot's own beam: tokens 0 .. *step are attended (step: int32 on the device,
+ *                         so that a captured launch can be replayed at the next step)
+ *   qpos [G, Q] int32 the queries' positions; window > 0 also hides keys with qpos - pos >= window (sliding layers)
+ * Rounding points as the reference: scores rounded to bf16 before scaling, soft cap (0: none) and mask; softmax in fp32 over the
+ * three ranges together; probabilities rounded to bf16; each range's value product rounded to bf16, the three added in fp32. */
+int64_t spinf_x_attention_workspace_bytes(int64_t G, int64_t Q, int64_t H, int64_t Lp, int64_t Tt, int64_t S);
+int spinf_x_attention(const void* q, int64_t q_pitch, const void* kp, const void* vp, const int32_t* pos_p, int64_t Lp,
+                      const void* kt, const void* vt, const int32_t* pos_t, const int32_t* own_t, int64_t Tt, const void* gk,
+                      const void* gv, int64_t S, const int32_t* qpos, const int32_t* step, int64_t G, int64_t Q, int64_t H, int64_t h,
+                      int64_t D, int32_t beam, int32_t window, float scale, float softcap, void* out, int64_t out_pitch,
+                      void* workspace, int64_t workspace_bytes, void* stream);
 
 /* Replaces the steps of GatedDeltaNet.forward before the recurrence (spinf_serve/models/qwen35/qwen.py:651-668), fused: for each of
  * the T tokens, from the in-projection rows y [n_rows, y_pitch] bf16 = [q | k | v | z | b | a]: the 4-tap path convolution over

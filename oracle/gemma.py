@@ -104,13 +104,16 @@ def quantize(W, scheme="fp8row"):
     return [{k: fn(L[k]) for k in LINEARS} for L in W["layers"]]
 
 
-def forward(cfg: GemmaConfig, W, Q, ids, art, end, pos, n_layers=None, taps=None, scheme="fp8row", scales=None, amax=None, peaks=None):
+def forward(cfg: GemmaConfig, W, Q, ids, art, end, pos, n_layers=None, taps=None, scheme="fp8row", scales=None, amax=None, peaks=None,
+            attend=None):
     """packed forward -> final hidden states [n, hidden] bf16 (after the model's last norm), the oracle of Gemma4Stack.forward
     (spinf_serve/models/gemma4.py:407-415). taps: optional dict filled with intermediate tensors for operator-level checks.
     scheme: fp8row (Fp8RowLinear), fp8 (Fp8Linear: dynamic per-tensor), fp8s (Fp8StaticLinear with scales[i][name]), w8a8 / w8a16
     (Int8Linear with int8 / bf16 activations) or bf16 (the unquantized linears).
     amax: optional list of per-layer dicts updated with the largest |input| of every linear (what the reference's calibration
-    hooks record, quant/calibrate.py:117-124); peaks: the same for the static scheme's monitor (max|x| / (448 scale))."""
+    hooks record, quant/calibrate.py:117-124); peaks: the same for the static scheme's monitor (max|x| / (448 scale)).
+    attend(layer, kind, q, k, v) -> [n, H, D]: another attention in place of the tree attention (a decoding step, where
+    transformers' layers call the "x_decode" interface instead: spinf_serve/decode.py:359-377); art / end are unused then."""
     n = len(ids)
     H, K, D = cfg.heads, cfg.kv_heads, cfg.head_dim
     layer = [0]
@@ -144,7 +147,10 @@ def forward(cfg: GemmaConfig, W, Q, ids, art, end, pos, n_layers=None, taps=None
         v = rmsnorm(lin(x, "v", q8).view(n, K, D), None, cfg.eps)
         q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
         window = cfg.window if kind == "sliding_attention" else None
-        a = OA.tree_attention(q, k, v, art, end, pos, 1.0, window).to(torch.bfloat16)  # the model passes scaling = 1.0
+        if attend is not None:
+            a = attend(i, kind, q, k, v)
+        else:
+            a = OA.tree_attention(q, k, v, art, end, pos, 1.0, window).to(torch.bfloat16)  # the model passes scaling = 1.0
         o = lin(a.reshape(n, H * D), "o", q8)
         h = h + rmsnorm(o, L["post_attn_ln"], cfg.eps)
         x = rmsnorm(h, L["pre_ffn_ln"], cfg.eps)

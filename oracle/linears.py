@@ -71,6 +71,44 @@ def int4_linear(x, q, s, group, extra=None, exact=False):
     return (x.float() @ w.float().t()).to(torch.bfloat16)
 
 
+def w4_small_splits(N, K, bn=64, bk=256, programs=512):
+    """the split-K count of the few-row W4A16 linear (spinf_serve/quant/w4gemm.py:51-56)"""
+    n_blocks = -(-N // bn)
+    splits = max(1, min(K // bk, programs // n_blocks))
+    while (K // bk) % splits:
+        splits -= 1
+    return splits
+
+
+def w4_small_linear(x, q, s, group=32, extra=None, exact=False):
+    """the W4A16 linear of the decoding steps, spinf_serve/quant/w4gemm.py:17-66: x [M, K] bf16 rounded to fp16; q uint8 [N, K/2]
+    (low nibble = even k, value nibble - 8), s fp16 [N, K/group]; the weight (nibble - 8) * scale formed in fp16; fp16 products
+    summed in fp32 per K slice, the slices' partial sums added in order, bf16 out. The order of the fp32 additions inside a slice
+    is the tensor core's: here they are summed exactly (float64) and rounded to fp32 once, which a kernel meets to the last bit or
+    two of the fp32 partial sum. `extra` [E, K] bf16 rows are appended as a plain product (w4gemm.py:63-64)."""
+    M, K = x.shape
+    N = q.shape[0]
+    lo = (q & 15).to(torch.float16) - 8.0
+    hi = (q >> 4).to(torch.float16) - 8.0
+    w = torch.stack([lo, hi], -1).reshape(N, K)
+    w = (w.reshape(N, K // group, group) * s.to(torch.float16)[:, :, None]).reshape(N, K)  # fp16 product, rounded to fp16
+    xh = x.to(torch.float16)
+    if exact:
+        y = xh.double() @ w.double().t()
+    else:
+        splits = w4_small_splits(N, K)
+        k_per = K // splits
+        y = torch.zeros((M, N), dtype=torch.float32)
+        for sp in range(splits):
+            sl = slice(sp * k_per, (sp + 1) * k_per)
+            y = y + (xh[:, sl].double() @ w[:, sl].double().t()).float()
+        y = y.to(torch.bfloat16)
+    if extra is not None:
+        e = x.double() @ extra.double().t() if exact else (x.to(extra.dtype) @ extra.t()).to(torch.bfloat16)
+        y = torch.cat([y, e], -1)
+    return y
+
+
 # ------------------------------------------------------------------------------------------------ per-tensor fp8 (dynamic and static)
 def quantize_weight(w):
     """bf16 [out, in] -> (w8 [out, in] e4m3, fp32 scale []): Fp8Linear / Fp8StaticLinear.__init__, linears.py:69-71,104-106

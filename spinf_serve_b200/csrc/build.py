@@ -12,7 +12,7 @@ from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB = os.path.join(HERE, "libspinf_b200.so")
-SOURCES = ["host_util.cpp", "abi.cpp", "tile_desc.cpp", "gemm.cu", "glue.cu", "attn_tree.cu", "w4_gemm.cu", "gdn.cu", "gdn_chunk.cu", "gdn_tree.cu", "gdn_tree_tc.cu"]
+SOURCES = ["host_util.cpp", "abi.cpp", "tile_desc.cpp", "gemm.cu", "glue.cu", "attn_tree.cu", "w4_gemm.cu", "gdn.cu", "gdn_chunk.cu", "gdn_tree.cu", "gdn_tree_tc.cu", "x_attn.cu", "w4_small.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
     "-gencode",

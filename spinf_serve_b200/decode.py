@@ -1,0 +1,243 @@
+"""Batched decoding of extraction slots right after the scoring pass that read them: the counterpart of spinf_serve/decode.py
+(Group :23-36, GroupKV :53-68, Decoder :107-189 and its step :334-377, `_reorder` :322-329) on this library's kernels.
+
+The scoring pass captured (GemmaStack.capture) the K/V of a tree's shared prefix and of every template branch. All slots of all
+groups of a chunk then decode together, one token per slot and step: one row of the step's batch per (group, slot). A slot
+attends to its group's prefix (stored once per group), to its own prompt's template and to the tokens its own beam generated
+(ops.x_attention): nothing is copied per slot or beam. The step is the stack's ordinary layer chain (GemmaStack.forward) with that
+attention in place of the tree attention, on static buffers, so it can be captured in a CUDA graph and replayed.
+
+Tensors are token-major here ([groups, tokens, kv heads, dim]), the form the capture delivers, where the reference keeps
+[groups, kv heads, tokens, dim]."""
+
+from dataclasses import dataclass, field
+
+import torch
+
+from spinf_serve_b200 import ops
+
+BEAM = 6  # live beams per prompt and step (extract.BEAM, spinf_serve/extract.py:33)
+PAD_TOKEN = 0
+
+
+@dataclass
+class Group:
+    """one tree's captured state: prefix K/V by layer ((k, v), each [stored tokens, kv heads, dim]; sliding layers the last
+    window - 1 tokens), the prefix length P, and the prompts: (prompt, {layer: (k, v)} of its template, template length T, the
+    final hidden state [hidden] at the template's last token, from which step 0 reads its log-probs: the reference keeps the
+    [vocab] log-probs themselves there). A prompt needs `.key` and `.max_tokens`."""
+
+    prefix_kv: dict
+    P: int
+    prompts: list = field(default_factory=list)
+    extra: dict | None = None
+    extra_bytes: int = 0
+
+
+def group_bytes(g: Group, per_tok_kv: dict, S: int, beam: int = BEAM) -> int:
+    """the decoder's memory for one group (decode.group_bytes, :392-402): prefix and templates once, generated K/V per slot"""
+    J = len(g.prompts)
+    T = sum(t for _, _, t, _ in g.prompts)
+    total = g.extra_bytes
+    for li, per_tok in per_tok_kv.items():
+        lp = g.prefix_kv[li][0].shape[0] if g.prefix_kv.get(li) is not None else g.P
+        total += per_tok * (lp + T + J * beam * S)
+    return total
+
+
+def chunk_bytes(groups: list, per_tok_kv: dict, extra: int = 0, beam: int = BEAM) -> int:
+    """the decoder's memory for groups decoded together (decode.chunk_bytes, :378-391): every group is padded to the chunk's
+    largest prefix, template total, prompt count and token limit, so a chunk costs more than the sum of its groups"""
+    G = len(groups)
+    J = max(len(g.prompts) for g in groups)
+    S = max(p.max_tokens for g in groups for p, *_ in g.prompts) + 1
+    Tt = max(sum(T for _, _, T, _ in g.prompts) for g in groups)
+    total = extra
+    for li, per_tok in per_tok_kv.items():
+        Lp = max((g.prefix_kv[li][0].shape[0] if g.prefix_kv.get(li) is not None else g.P) for g in groups)
+        total += per_tok * G * (Lp + Tt + J * beam * S)
+    return total
+
+
+class Decoder:
+    """one chunk of groups decoded together"""
+
+    def __init__(self, stack, groups: list, device, beam: int = BEAM, graphs: bool = False):
+        self.stack, self.groups, self.device, self.beam, self.graphs = stack, groups, device, beam, graphs
+        cfg = stack.cfg
+        self.kv_layers = sorted(groups[0].prefix_kv)
+        G = self.G = len(groups)
+        J = max(len(g.prompts) for g in groups)
+        Q = self.Q = J * beam
+        S = self.S = max(p.max_tokens for g in groups for p, *_ in g.prompts) + 1
+        h, D = cfg.kv_heads, cfg.head_dim
+        Tt = self.Tt = max(sum(T for _, _, T, _ in g.prompts) for g in groups)
+        pos_t = torch.full((G, Tt), -1, dtype=torch.int32)
+        own_t = torch.full((G, Tt), -1, dtype=torch.int32)
+        base = torch.zeros((G, Q), dtype=torch.int32)
+        for gi, g in enumerate(groups):
+            o = 0
+            pos0 = g.extra.get("pos0") if g.extra else None
+            for j, (_, _, T, _) in enumerate(g.prompts):
+                pos_t[gi, o : o + T] = torch.arange(g.P, g.P + T, dtype=torch.int32)
+                own_t[gi, o : o + T] = j
+                base[gi, j * beam : (j + 1) * beam] = pos0[j] if pos0 else g.P + T
+                o += T
+        self.pos_t, self.own_t, self.base = pos_t.to(device), own_t.to(device), base.to(device)
+        self.kp, self.vp, self.pos_p, self.kt, self.vt, self.gk, self.gv = {}, {}, {}, {}, {}, {}, {}
+        bf = torch.bfloat16
+        for li in self.kv_layers:
+            Lp = max(g.prefix_kv[li][0].shape[0] for g in groups)
+            kp, vp = torch.zeros((G, Lp, h, D), dtype=bf, device=device), torch.zeros((G, Lp, h, D), dtype=bf, device=device)
+            pos = torch.full((G, Lp), -1, dtype=torch.int32)
+            kt, vt = torch.zeros((G, Tt, h, D), dtype=bf, device=device), torch.zeros((G, Tt, h, D), dtype=bf, device=device)
+            for gi, g in enumerate(groups):
+                k, v = g.prefix_kv[li]
+                n = k.shape[0]
+                kp[gi, :n], vp[gi, :n] = k, v
+                pos[gi, :n] = torch.arange(g.P - n, g.P, dtype=torch.int32)  # a sliding layer keeps the last n of the prefix
+                o = 0
+                for _, tkv, T, _ in g.prompts:
+                    kt[gi, o : o + T], vt[gi, o : o + T] = tkv[li]
+                    o += T
+            self.kp[li], self.vp[li], self.pos_p[li], self.kt[li], self.vt[li] = kp, vp, pos.to(device), kt, vt
+            self.gk[li] = torch.zeros((G, Q, S, h, D), dtype=bf, device=device)
+            self.gv[li] = torch.zeros((G, Q, S, h, D), dtype=bf, device=device)
+            for g in groups:  # the captured tensors are copied: let them go
+                g.prefix_kv[li] = None
+        for g in groups:
+            for p in g.prompts:
+                p[1].clear()
+        # the static buffers of a step (a captured graph replays on them)
+        self.qpos = self.base.clone()
+        self.tok_buf = torch.full((G, Q), PAD_TOKEN, dtype=torch.int64, device=device)
+        self.step_t = torch.zeros(1, dtype=torch.int64, device=device)
+        self.step32 = torch.zeros(1, dtype=torch.int32, device=device)
+        need = int(ops._lib.lib().spinf_x_attention_workspace_bytes(G, Q, cfg.heads, max(k.shape[1] for k in self.kp.values()), Tt, S))
+        self.workspace = torch.empty(need, dtype=torch.uint8, device=device)
+        self.step = 0
+        self.graph, self.h_out = None, None
+
+    def _attend(self, i, kind, q, k, v):
+        """a layer's attention inside a step: the new tokens' K/V into the generated range at the current step (GroupKV.update),
+        then the three-range attention"""
+        G, Q, S = self.G, self.Q, self.S
+        cfg = self.stack.cfg
+        h, D = cfg.kv_heads, cfg.head_dim
+        self.gk[i].index_copy_(2, self.step_t, k.reshape(G, Q, 1, h, D))
+        self.gv[i].index_copy_(2, self.step_t, v.reshape(G, Q, 1, h, D))
+        window = cfg.window if kind == "sliding_attention" else None
+        out = ops.x_attention(
+            q.view(G, Q, cfg.heads, D), self.kp[i], self.vp[i], self.pos_p[i], self.kt[i], self.vt[i], self.pos_t, self.own_t, self.gk[i],
+            self.gv[i], self.qpos, self.step32, self.beam, 1.0, window, None, workspace=self.workspace,
+        )
+        return out.view(G * Q, cfg.heads, D)
+
+    def _step_once(self):
+        inputs = {"ids": self.tok_buf.reshape(1, -1), "pos": self.qpos.reshape(1, -1)}
+        return self.stack.forward(None, None, inputs, None, attend=self._attend).reshape(self.G, self.Q, -1)
+
+    def forward(self, tokens, step: int | None = None):
+        """one decoding step: tokens [G, Q] int64 (PAD_TOKEN in unused slots) at step `step` (default: the next one) -> hidden
+        states after the last norm [G, Q, hidden]. With graphs=True the step is captured once, after one run outside the capture,
+        and replayed afterwards (Decoder._forward, decode.py:334-357)."""
+        if step is not None:
+            self.step = step
+        self.tok_buf.copy_(tokens)
+        self.qpos.copy_(self.base + self.step)
+        self.step_t.fill_(self.step)
+        self.step32.fill_(self.step)
+        self.step += 1
+        if self.graph is not None:
+            self.graph.replay()
+            return self.h_out
+        if not self.graphs:
+            return self._step_once()
+        side = torch.cuda.Stream(self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            self._step_once()  # lazy initialisations must not happen inside the capture
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.h_out = self._step_once()
+        self.graph = g
+        g.replay()
+        return self.h_out
+
+    def reorder(self, parent) -> None:
+        """the generated K/V follow their beams: slot s takes slot parent[s]'s (parent: int64 [G * Q] on the device), in place"""
+        for li in self.kv_layers:
+            for t in (self.gk[li], self.gv[li]):
+                flat = t.view(self.G * self.Q, *t.shape[2:])
+                flat.copy_(flat[parent])
+
+
+def search_text(dec: Decoder, lm_weight, stop_ids, banned_ids=(), topk: int | None = None, min_p: float = 0.002, softcap=None):
+    """beam search over every prompt of the decoder's groups at once, the text kind of Decoder.run (decode.py:191-320 with
+    extract.py's constants): a beam ends with the summed probability of the stop tokens; the `topk` best continuations of every
+    live beam compete for the prompt's `beam` slots; beams below min_p are dropped. -> {prompt key: [(tokens, log-prob)] best
+    first}. Candidates are picked from bf16 logits (twice as many as needed) and ranked by their exact fp32 log-probs."""
+    import math
+
+    beam = dec.beam
+    topk = topk or beam
+    G, Q = dec.G, dec.Q
+    dev = dec.device
+    stop = torch.as_tensor(sorted(stop_ids), dtype=torch.int64, device=dev)
+    mask_ids = torch.as_tensor(sorted(set(stop_ids) | set(banned_ids)), dtype=torch.int64, device=dev)
+    prompts = [(gi, j, p) for gi, g in enumerate(dec.groups) for j, (p, *_) in enumerate(g.prompts)]
+    found = {p.key: [] for _, _, p in prompts}
+    live = {p.key: [(0.0, [])] for _, _, p in prompts}
+    slots = {p.key: [gi * Q + j * beam] for gi, j, p in prompts}
+    floor = math.log(min_p)
+
+    def read(h_rows):
+        """h_rows [R, hidden] -> (end log-prob [R], candidate ids [R, 2 topk], their log-probs)"""
+        logits = ops.bf16_gemm(h_rows, lm_weight).float()
+        logits[:, mask_ids] = -float("inf")
+        cand = logits.topk(2 * topk, -1).indices
+        cols = torch.unique(torch.cat([cand.reshape(-1), stop]))
+        lp = ops.option_logprobs(h_rows, lm_weight, cols.to(torch.int32), softcap)
+        end = torch.logsumexp(lp[:, torch.searchsorted(cols, stop)], -1)
+        return end.cpu().numpy(), cand.cpu().numpy(), torch.gather(lp, 1, torch.searchsorted(cols, cand)).cpu().numpy()
+
+    # step 0 reads the scoring pass's hidden state at the end of each template: the caller put it in the prompt tuple as the 4th item
+    h0 = torch.stack([dec.groups[gi].prompts[j][3] for gi, j, _ in prompts])
+    end, cand, clp = read(h0)
+    row_of = {gi * Q + j * beam: k for k, (gi, j, _) in enumerate(prompts)}
+    for step in range(dec.S):
+        tokens = torch.full((G * Q,), PAD_TOKEN, dtype=torch.int64)
+        parent = torch.arange(G * Q)
+        new_slots = {}
+        for gi, j, p in prompts:
+            beams, old = live[p.key], slots[p.key]
+            if not beams:
+                continue
+            pool = []
+            for b, (s, toks) in enumerate(beams):
+                r = row_of[old[b]]
+                if toks:
+                    found[p.key].append((toks, s + float(end[r])))
+                order = sorted(range(cand.shape[1]), key=lambda t: -clp[r, t])[:topk]
+                pool += [(s + float(clp[r, t]), b, int(cand[r, t])) for t in order]
+            if step >= p.max_tokens:
+                live[p.key], new_slots[p.key] = [], []
+                continue
+            best = max((x[1] for x in found[p.key]), default=-float("inf"))
+            pool = [c for c in sorted(pool, key=lambda c: -c[0]) if c[0] >= max(floor, best + math.log(0.02))][:beam]
+            live[p.key] = [(c[0], beams[c[1]][1] + [c[2]]) for c in pool]
+            new_slots[p.key] = [gi * Q + j * beam + b for b in range(len(pool))]
+            for sl, c in zip(new_slots[p.key], pool, strict=True):
+                parent[sl] = old[c[1]]
+                tokens[sl] = c[2]
+        slots = {k: new_slots.get(k, []) for k in slots}
+        alive = sorted(s for v in slots.values() for s in v)
+        if not alive:
+            break
+        if step > 0 and not bool((parent == torch.arange(G * Q)).all()):
+            dec.reorder(parent.to(dev))
+        h = dec.forward(tokens.view(G, Q).to(dev), step)
+        row_of = {s: k for k, s in enumerate(alive)}
+        end, cand, clp = read(h.reshape(G * Q, -1)[torch.as_tensor(alive, device=dev)].contiguous())
+    return {k: sorted(v, key=lambda x: -x[1]) for k, v in found.items()}

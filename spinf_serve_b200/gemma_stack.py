@@ -11,6 +11,7 @@ Fusing q|k|v and gate|up is exact for this scheme: weight scales are per output 
 so each output element is the one the separate linears give. The final norm runs on the read rows only (Scorer._forward reads
 nothing else, spinf_serve/scorer.py:248-254)."""
 
+from contextlib import contextmanager
 from dataclasses import dataclass, field
 
 import torch
@@ -189,6 +190,7 @@ class GemmaStack:
         self.embed_scale = float(torch.tensor(self.cfg.hidden**0.5).to(torch.bfloat16))
         self.fuse_qkv = D in (128, 256) and ((self.cfg.heads + 2 * self.cfg.kv_heads) * D) % 256 == 0
         self.amax_log = None  # calibrate() sets a list here: (linear name, device scalar) per quantised input of a forward
+        self._cap = None  # capture_ranges() sets {"window", "ranges", "kv"} here for the forwards inside it
 
     @property
     def window(self):
@@ -197,6 +199,36 @@ class GemmaStack:
 
     def plan(self, sc, b) -> None:
         """nothing to prepare on the host for attention-only models (Stack.plan, base.py:50-51)"""
+
+    # ---- K/V capture for the extraction decoder (Gemma4Stack.capture_ranges / capture, spinf_serve/models/gemma4.py:417-435, and
+    # the hook inside the attention, :100-106)
+    @contextmanager
+    def capture_ranges(self, sc, ranges: list):
+        """the K/V of the stream ranges [(start, n, key)] kept by the forwards inside -> the dict they fill under "kv":
+        {key: {layer: (k [n', kv heads, D], v [n', kv heads, D])}}, token-major copies of the rows start .. start + n - 1 after
+        head norm and rotary embedding; sliding layers keep the last window - 1 tokens of a range only"""
+        cap = {"window": self.cfg.window, "ranges": list(ranges), "kv": {}}
+        self._cap = cap
+        try:
+            yield cap
+        finally:
+            self._cap = None
+
+    @contextmanager
+    def capture(self, sc, b, xo: list):
+        """around the forward of a batch whose owners `xo` have extraction branches (Stack.capture, base.py:66-70): every owner's
+        prefix under ("p", id(owner)) and every template branch under ("t", prompt key)"""
+        rs = [(o.start, o.prefix_len, ("p", id(o))) for o in xo] + [(bs, bl, ("t", pr.key)) for o in xo for bs, bl, pr in o.xbranches]
+        with self.capture_ranges(sc, rs) as cap:
+            yield {"kv": cap["kv"], "extra": None, "pos0": None}
+
+    def abandon(self, sc) -> None:
+        """drop a capture left open by a failed call (Stack.abandon)"""
+        self._cap = None
+
+    def kv_bytes_per_token(self) -> dict:
+        """{layer: bytes of K and V one stored token takes} (what decode.group_bytes / chunk_bytes count with)"""
+        return {i: 2 * self.cfg.kv_heads * self.cfg.head_dim * 2 for i in range(self.n_layers)}
 
     def stage(self, sc, b, st: dict) -> dict:
         """what forward reads of the staged arrays (Stack.stage, base.py:53-60, returns {"ids": [1, n], "pos": [1, n]}). `st` maps
@@ -244,11 +276,12 @@ class GemmaStack:
                     out[(i, k)] = float(L["peak"][group[0]])
         return out
 
-    def forward(self, sc, b, inputs: dict, masks: dict, rows=None, taps=None):
+    def forward(self, sc, b, inputs: dict, masks: dict, rows=None, taps=None, attend=None):
         """packed forward (Stack.forward, base.py:62-64) -> final hidden states after the model's last norm, [1, n, hidden] bf16 in
         the stream layout. masks = {"full_attention": TileMask, "sliding_attention": TileMask} (attention.device_masks). Beyond the
         reference's signature: rows (int64 device tensor of stream positions) returns only those rows, [len(rows), hidden], the
-        last norm running on them alone; taps: optional dict filled with per-layer intermediates (tests)."""
+        last norm running on them alone; taps: optional dict filled with per-layer intermediates (tests); attend(layer, kind, q, k,
+        v) -> [n, H, D] replaces the tree attention (the extraction decoder's steps: masks is unused then)."""
         cfg, w = self.cfg, self.w
         H, K, D = cfg.heads, cfg.kv_heads, cfg.head_dim
         ids, pos = inputs["ids"].reshape(-1), inputs["pos"].reshape(-1)
@@ -275,11 +308,20 @@ class GemmaStack:
             q = qkv[:, : H * D].view(n, H, D)
             k = qkv[:, H * D : (H + K) * D].view(n, K, D)
             v = qkv[:, (H + K) * D :].view(n, K, D)
-            amax = torch.zeros(n, dtype=torch.float32, device=qkv.device) if row else None
-            ops.COUNTS["launches"] += 1 if row else 0
-            a = attention.tree_attention(q, k, v, masks[kind], 1.0, row_amax=amax)  # scaling = 1.0: q and k are normed
-            if row:  # the attention kernel has already found the row maxima
-                a8, a_s = ops.fp8_quant_from_amax(a.view(n, H * D), amax)
+            if self._cap is not None:
+                keep = self._cap["window"] - 1
+                for start, cnt, key in self._cap["ranges"]:
+                    a0 = start + (max(0, cnt - keep) if kind == "sliding_attention" else 0)
+                    self._cap["kv"].setdefault(key, {})[i] = (k[a0 : start + cnt].clone(), v[a0 : start + cnt].clone())
+            if attend is not None:
+                a = attend(i, kind, q, k, v)
+                amax = None
+            else:
+                amax = torch.zeros(n, dtype=torch.float32, device=qkv.device) if row else None
+                ops.COUNTS["launches"] += 1 if row else 0
+                a = attention.tree_attention(q, k, v, masks[kind], 1.0, row_amax=amax)  # scaling = 1.0: q and k are normed
+            if row:  # the tree attention kernel has already found the row maxima
+                a8, a_s = ops.fp8_quant_from_amax(a.view(n, H * D), amax) if amax is not None else ops.fp8_rowwise_quant(a.view(n, H * D))
                 o = ops.fp8_rowwise_gemm(a8, a_s, L["o_w"], L["o_s"])
             else:
                 o = self._linear(a.view(n, H * D), L, "o", ("o",))

@@ -228,6 +228,68 @@ def w4_gemm(x, qw, scales, group, extra=None):
     return y
 
 
+def w4_small(x, q, scales, group, extra=None, workspace=None):
+    """the W4A16 linear of a decoding step (w4gemm.linear, spinf_serve/quant/w4gemm.py:44-66): x [M <= 128, K] bf16, q uint8
+    [N, K/2] in the ENGINE layout (not w4_repack'ed), scales fp16 [N, K/group] -> [M, N (+ E)] bf16, `extra` [E, K] bf16 rows
+    appended as a plain product"""
+    _need(x, torch.bfloat16, "x", 2)
+    _need(q, torch.uint8, "q", 2)
+    _need(scales, torch.float16, "scales", 2)
+    M, K = x.shape
+    N = q.shape[0]
+    if q.shape[1] * 2 != K or scales.shape != (N, K // group) or M > 128:
+        raise SpinfError(f"w4_small: shapes do not agree: x {tuple(x.shape)}, q {tuple(q.shape)}, scales {tuple(scales.shape)}")
+    E = 0 if extra is None else extra.shape[0]
+    if extra is not None:
+        _need(extra, torch.bfloat16, "extra", 2)
+    y = torch.empty((M, N + E), dtype=torch.bfloat16, device=x.device)
+    need = int(_lib.lib().spinf_w4_small_workspace_bytes(M, N, K))
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    check(_lib.lib().spinf_w4_small(ptr(x), ptr(q), ptr(scales), group, ptr(y), M, N, K, N + E, ptr(workspace), workspace.numel(), stream_ptr()), "spinf_w4_small")
+    COUNTS["launches"] += 3
+    if E:
+        tail = ctypes.c_void_p(y.data_ptr() + 2 * N)
+        check(_lib.lib().spinf_bf16_gemm_ld(ptr(x), ptr(extra), tail, M, E, K, N + E, stream_ptr()), "spinf_bf16_gemm_ld")
+        COUNTS["launches"] += 1
+    return y
+
+
+def x_attention(q, kp, vp, pos_p, kt, vt, pos_t, own_t, gk, gv, qpos, step, beam, scaling, window=None, softcap=None, out=None, workspace=None):
+    """the decoding step's attention (`_x_attention`, spinf_serve/decode.py:71-104) on token-major tensors: q [G, Q, H, D] (a view
+    with unit stride over (H, D) and any row pitch); prefix kp / vp [G, Lp, h, D] + pos_p [G, Lp] int32 (-1: padding); templates
+    kt / vt [G, Tt, h, D] + pos_t, own_t [G, Tt] int32; generated gk / gv [G, Q, S, h, D]; qpos [G, Q] int32; step: int32 device
+    scalar (tokens 0..step of the generated range are live) -> [G, Q, H, D] bf16"""
+    G, Q, H, D = q.shape
+    if q.dtype != torch.bfloat16 or not q.is_cuda or q.stride(3) != 1 or q.stride(2) != D or q.stride(0) != Q * q.stride(1):
+        raise SpinfError("x_attention: q must be a CUDA bf16 [G, Q, H, D] view with contiguous heads and evenly pitched rows")
+    for name, t, dt in (("kp", kp, torch.bfloat16), ("vp", vp, torch.bfloat16), ("kt", kt, torch.bfloat16), ("vt", vt, torch.bfloat16),
+                        ("gk", gk, torch.bfloat16), ("gv", gv, torch.bfloat16), ("pos_p", pos_p, torch.int32), ("pos_t", pos_t, torch.int32),
+                        ("own_t", own_t, torch.int32), ("qpos", qpos, torch.int32), ("step", step, torch.int32)):
+        _need(t, dt, name)
+    Lp, h = kp.shape[1], kp.shape[2]
+    Tt, S = kt.shape[1], gk.shape[2]
+    if kp.shape != (G, Lp, h, D) or vp.shape != kp.shape or kt.shape != (G, Tt, h, D) or vt.shape != kt.shape or gk.shape != (G, Q, S, h, D) or gv.shape != gk.shape:
+        raise SpinfError("x_attention: key / value shapes do not agree")
+    if pos_p.shape != (G, Lp) or pos_t.shape != (G, Tt) or own_t.shape != (G, Tt) or qpos.shape != (G, Q) or step.numel() != 1:
+        raise SpinfError("x_attention: position / owner shapes do not agree")
+    if out is None:
+        out = torch.empty((G, Q, H, D), dtype=torch.bfloat16, device=q.device)
+    need = int(_lib.lib().spinf_x_attention_workspace_bytes(G, Q, H, Lp, Tt, S))
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+    check(
+        _lib.lib().spinf_x_attention(
+            ptr(q), q.stride(1), ptr(kp), ptr(vp), ptr(pos_p), Lp, ptr(kt), ptr(vt), ptr(pos_t), ptr(own_t), Tt, ptr(gk), ptr(gv), S,
+            ptr(qpos), ptr(step), G, Q, H, h, D, beam, int(window or 0), float(scaling), float(softcap or 0.0), ptr(out), out.stride(1),
+            ptr(workspace), workspace.numel(), stream_ptr(),
+        ),
+        "spinf_x_attention",
+    )
+    COUNTS["launches"] += 3
+    return out
+
+
 def glu_tile_order(F: int):
     """row permutation that puts a fused gate|up weight [2F, K] (gate rows first) into the tiled order of fp8_gemm_glu: per 128
     features, four blocks of 32 gate rows followed by the 32 up rows of the same features"""

@@ -401,3 +401,78 @@ def test_int4_linear_bf16_mode(dev):
         "ms_here": t_mine, "speedup": t_ref / t_mine, "tflops_here": 2.0 * M * N * K / t_mine / 1e9, "tflops_reference": 2.0 * M * N * K / t_ref / 1e9,
     }
     assert float(d.max()) <= 2.0**-7 * float(y_ref.float().abs().max()) and same > 0.98
+
+
+@pytest.mark.parametrize("M,N,K", [(36, 5120, 5120), (36, 34816, 5120), (36, 5120, 17408)])
+def test_w4_small_linear(dev, M, N, K):
+    """the decoding steps' W4A16 linear (spinf_serve/quant/w4gemm.py:44-66, a Triton kernel) at the hybrid model's widths"""
+    from spinf_serve_b200 import ops
+
+    g = torch.Generator().manual_seed(N + K)
+    q = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, generator=g).to(dev)
+    s = (torch.rand((N, K // 32), generator=g) * 0.02 + 0.001).to(torch.float16).to(dev)
+    x = torch.randn((M, K), generator=g).to(torch.bfloat16).to(dev)
+
+    def ref_fn():
+        from spinf_serve.quant import w4gemm
+
+        return w4gemm.linear(x, q, s)
+
+    ref = reference("w4_small", ref_fn)
+    got = ops.w4_small(x, q, s, 32)
+    same = float((got == ref).float().mean())
+    worst = float(((got.float() - ref.float()).abs() / (ref.float().abs() + 1e-2)).max())
+    from spinf_serve.quant import w4gemm
+
+    ws = torch.empty(int(ops._lib.lib().spinf_w4_small_workspace_bytes(M, N, K)), dtype=torch.uint8, device=dev)
+    t_ref, t_mine = timed(lambda: w4gemm.linear(x, q, s)), timed(lambda: ops.w4_small(x, q, s, 32, workspace=ws))
+    gbs = N * K / 2 / (t_mine * 1e-3) / 1e9
+    RESULTS[f"w4_small_{N}x{K}"] = {"equal_share": same, "max_rel": worst, "ref_ms": t_ref, "mine_ms": t_mine, "weight_GBs": gbs}
+    print(f"w4 small M {M} N {N} K {K}: equal {same:.4%}, max rel {worst:.2e}; reference {t_ref:.3f} ms, here {t_mine:.3f} ms ({gbs:.0f} GB/s of int4 weights)")
+    assert same > 0.99 and worst < 2.0**-6
+
+
+def test_x_attention(dev):
+    """the decoding step's attention as the reference runs it on the GPU (eager einsums, spinf_serve/decode.py:71-104) against the
+    library's three kernels, at a 12B-like layer: 4 groups of 1 500-token prefixes, 5 prompts x 6 beams, 17 generated tokens"""
+    import types
+
+    from spinf_serve import decode as RD
+    from spinf_serve_b200 import ops
+
+    G, H, h, Dh, beam, J, Lp, T, S, step = 4, 16, 8, 256, 6, 5, 1500, 12, 17, 9
+    Q, Tt = J * beam, J * T
+    g = torch.Generator().manual_seed(77)
+    rnd = lambda *s: torch.randn(s, generator=g).to(torch.bfloat16).to(dev)  # noqa: E731
+    q, kp, vp, kt, vt, gk, gv = rnd(G, Q, H, Dh), rnd(G, Lp, h, Dh), rnd(G, Lp, h, Dh), rnd(G, Tt, h, Dh), rnd(G, Tt, h, Dh), rnd(G, Q, S, h, Dh), rnd(G, Q, S, h, Dh)
+    pos_p = torch.arange(Lp, device=dev)[None].expand(G, Lp).contiguous()
+    pos_t = (Lp + torch.arange(Tt, device=dev) % T)[None].expand(G, Tt).contiguous()
+    own_t = (torch.arange(Tt, device=dev) // T)[None].expand(G, Tt).contiguous()
+    qpos = torch.full((G, Q), Lp + T + step, device=dev)
+    d = types.SimpleNamespace()
+    li = 0
+    d.kp, d.vp, d.kt, d.vt = ({li: t.permute(0, 2, 1, 3).contiguous()} for t in (kp, vp, kt, vt))
+    d.gk, d.gv = ({li: t.permute(0, 3, 1, 2, 4).contiguous()} for t in (gk, gv))
+    d.pos_p, d.mask_p = {li: pos_p}, {li: (pos_p >= 0)[:, None, :].expand(G, Q, Lp)}
+    d.pos_t, d.mask_t = pos_t, own_t[:, None, :] == (torch.arange(Q, device=dev) // beam)[None, :, None]
+    d.step_t, d.gen_idx, d.qpos = torch.tensor([step], device=dev), torch.arange(S, device=dev), qpos
+    qr = q.permute(0, 2, 1, 3).contiguous()
+    res = {}
+    for window in (None, 1024):
+        def ref_fn(window=window):
+            RD._CURRENT[0] = d
+            try:
+                return RD._x_attention(None, qr, ("x", li), ("x", li), None, scaling=1.0, sliding_window=window)[0]
+            finally:
+                RD._CURRENT[0] = None
+
+        ref = reference("x_attention", ref_fn)
+        i32 = lambda t: t.to(torch.int32).contiguous()  # noqa: E731
+        st = torch.tensor([step], dtype=torch.int32, device=dev)
+        mine = lambda window=window: ops.x_attention(q, kp, vp, i32(pos_p), kt, vt, i32(pos_t), i32(own_t), gk, gv, i32(qpos), st, beam, 1.0, window)  # noqa: E731
+        got = mine()
+        diff = (got.float() - ref.float()).abs()
+        res[str(window)] = {"max_abs": float(diff.max()), "equal_share": float((diff == 0).float().mean()), "ref_ms": timed(ref_fn), "mine_ms": timed(mine)}
+        print(f"x_attention window {window}: {res[str(window)]}")
+        assert float(diff.max()) <= 2.0**-6 * float(ref.float().abs().max()) + 2e-3
+    RESULTS["x_attention"] = res
