@@ -185,6 +185,7 @@ extern "C" int spinf_w4_small(const void* x, const void* q, const void* scales, 
   int rc;
   if (M <= 16) rc = w4_small_launch<1>(xh, qq, ss, part, m, n, k, group, splits, st);
   else if (M <= 32) rc = w4_small_launch<2>(xh, qq, ss, part, m, n, k, group, splits, st);
+  else if (M <= 48) rc = w4_small_launch<3>(xh, qq, ss, part, m, n, k, group, splits, st);
   else if (M <= 64) rc = w4_small_launch<4>(xh, qq, ss, part, m, n, k, group, splits, st);
   else rc = w4_small_launch<8>(xh, qq, ss, part, m, n, k, group, splits, st);
   if (rc) return rc;

@@ -69,22 +69,37 @@ __global__ void __launch_bounds__(128) x_scores_kernel(const XAttnArgs a) {
   const int np = a.Lp64 / XT, nt = a.Tt64 / XT;
   const int step = *a.step;
 
-  if (tile == np + nt) {
-    // the generated range: slot q's rows against the S keys of slot q; one warp per (slot, key), all r heads of the pair at once
-    const int vec = a.D / 8;  // 16-byte pieces of a row
-    for (int i = warp; i < a.Q * a.S64; i += 4) {
-      const int q = i / a.S64, s = i % a.S64;
-      const bool live = s < a.S && s <= step;
-      for (int rr = 0; rr < r; ++rr) {
-        float acc = 0.f;
-        if (live) {
-          const __nv_bfloat16* kr = a.gk + (((static_cast<int64_t>(g) * a.Q + q) * a.S + s) * a.h + hk) * a.D;
-          const __nv_bfloat16* qr = x_q_row(a, g, hk, r, q * r + rr);
-          for (int c = lane; c < vec; c += 32) {
-            const uint4 ku = *reinterpret_cast<const uint4*>(kr + c * 8);
-            const uint4 qu = *reinterpret_cast<const uint4*>(qr + c * 8);
-            const __nv_bfloat162* kb = reinterpret_cast<const __nv_bfloat162*>(&ku);
-            const __nv_bfloat162* qb = reinterpret_cast<const __nv_bfloat162*>(&qu);
+  if (tile >= np + nt) {
+    // the generated range: slot q's rows against the keys slot q's own beam wrote; one warp per slot, four slots per CTA. The r query
+    // rows of the slot stay in registers (lane l holds elements 8 l .. 8 l + 7 of every 256), the key rows stream past them.
+    const int q = (tile - np - nt) * 4 + warp;
+    if (q >= a.Q) return;
+    const int vec = a.D / 8;
+    const int n_live = min(step + 1, a.S);
+    for (int rr = 0; rr < r; ++rr) {
+      uint4 qv[2] = {};
+      const __nv_bfloat16* const qr = x_q_row(a, g, hk, r, q * r + rr);
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+        if (lane + j * 32 < vec) qv[j] = *reinterpret_cast<const uint4*>(qr + (lane + j * 32) * 8);
+      float* const dst = a.scores + x_ws_row(a, g, hk, r, q * r + rr) + a.Lp64 + a.Tt64;
+      const __nv_bfloat16* const kbase = a.gk + (((static_cast<int64_t>(g) * a.Q + q) * a.S) * a.h + hk) * a.D;
+      for (int s0 = 0; s0 < a.S64; s0 += 4) {
+        uint4 kv[4][2] = {};
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (s0 + u < n_live) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+              if (lane + j * 32 < vec) kv[u][j] = *reinterpret_cast<const uint4*>(kbase + static_cast<int64_t>(s0 + u) * a.h * a.D + (lane + j * 32) * 8);
+          }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          float acc = 0.f;
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const __nv_bfloat162* kb = reinterpret_cast<const __nv_bfloat162*>(&kv[u][j]);
+            const __nv_bfloat162* qb = reinterpret_cast<const __nv_bfloat162*>(&qv[j]);
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const float2 kf = __bfloat1622float2(kb[e]), qf = __bfloat1622float2(qb[e]);
@@ -93,8 +108,8 @@ __global__ void __launch_bounds__(128) x_scores_kernel(const XAttnArgs a) {
             }
           }
           for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+          if (lane == u) dst[s0 + u] = s0 + u < n_live ? x_finish_score(acc, a.scale, a.softcap) : X_NINF;
         }
-        if (lane == 0) a.scores[x_ws_row(a, g, hk, r, q * r + rr) + a.Lp64 + a.Tt64 + s] = live ? x_finish_score(acc, a.scale, a.softcap) : X_NINF;
       }
     }
     return;
@@ -166,77 +181,108 @@ __global__ void __launch_bounds__(128) x_scores_kernel(const XAttnArgs a) {
 }
 
 __global__ void __launch_bounds__(128) x_softmax_kernel(const XAttnArgs a) {
-  __shared__ float red[4];
+  __shared__ float red[8];
   const int64_t row = blockIdx.x;
   const float* const s = a.scores + row * a.pitch;
   __nv_bfloat16* const p = a.probs + row * a.pitch;
   const int tid = threadIdx.x;
+  constexpr int CACHE = 24;  // rows of up to 3072 columns stay in registers; longer ones are read again
+  float v[CACHE];
   float m = X_NINF;
-  for (int i = tid; i < a.pitch; i += 128) m = fmaxf(m, s[i]);
+#pragma unroll
+  for (int j = 0; j < CACHE; ++j) {
+    const int i = tid + j * 128;
+    v[j] = i < a.pitch ? s[i] : X_NINF;
+    m = fmaxf(m, v[j]);
+  }
+  for (int i = tid + CACHE * 128; i < a.pitch; i += 128) m = fmaxf(m, s[i]);
   for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
   if ((tid & 31) == 0) red[tid >> 5] = m;
   __syncthreads();
   m = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
-  __syncthreads();
   float sum = 0.f;
-  for (int i = tid; i < a.pitch; i += 128) sum += expf(s[i] - m);
+#pragma unroll
+  for (int j = 0; j < CACHE; ++j) {
+    v[j] = expf(v[j] - m);
+    sum += v[j];
+  }
+  for (int i = tid + CACHE * 128; i < a.pitch; i += 128) sum += expf(s[i] - m);
   for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-  if ((tid & 31) == 0) red[tid >> 5] = sum;
+  if ((tid & 31) == 0) red[4 + (tid >> 5)] = sum;
   __syncthreads();
-  sum = (red[0] + red[1]) + (red[2] + red[3]);
-  for (int i = tid; i < a.pitch; i += 128) p[i] = __float2bfloat16_rn(expf(s[i] - m) / sum);
+  sum = (red[4] + red[5]) + (red[6] + red[7]);
+#pragma unroll
+  for (int j = 0; j < CACHE; ++j) {
+    const int i = tid + j * 128;
+    if (i < a.pitch) p[i] = __float2bfloat16_rn(v[j] / sum);
+  }
+  for (int i = tid + CACHE * 128; i < a.pitch; i += 128) p[i] = __float2bfloat16_rn(expf(s[i] - m) / sum);
 }
 
-// dynamic shared memory: [XT][XT + 8] probabilities, [XT][XT + 8] values (keys x 64 dims of this CTA)
+// dynamic shared memory, two stages of: [XT][XT + 8] probabilities, [XT][XT + 8] values (keys x 64 dims of this CTA)
 __global__ void __launch_bounds__(128) x_values_kernel(const XAttnArgs a) {
   extern __shared__ __align__(16) uint8_t xv_raw[];
   constexpr int ld = XT + 8;
-  __nv_bfloat16* const ps = reinterpret_cast<__nv_bfloat16*>(xv_raw);
-  __nv_bfloat16* const vs = ps + XT * ld;
+  constexpr int STAGE = 2 * XT * ld;  // elements
+  __nv_bfloat16* const sm = reinterpret_cast<__nv_bfloat16*>(xv_raw);
   const int d0 = blockIdx.x * XT, hk = blockIdx.y, g = blockIdx.z;
   const int r = a.H / a.h, R = a.Q * r;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int gq = lane >> 2, tq = lane & 3;
   const int step = *a.step;
+  const int np = a.Lp64 / XT, n_tiles = np + a.Tt64 / XT;
   for (int m0 = 0; m0 < R; m0 += XT) {
+    auto stage = [&](int tile, int buf) {
+      const bool pre = tile < np;
+      const int L = pre ? a.Lp : a.Tt, k0 = (pre ? tile : tile - np) * XT, col0 = pre ? 0 : a.Lp64;
+      const __nv_bfloat16* const vbase = pre ? a.vp : a.vt;
+      __nv_bfloat16* const ps = sm + buf * STAGE;
+      __nv_bfloat16* const vs = ps + XT * ld;
+      for (int i = tid; i < XT * 8; i += 128) {
+        const int t = i >> 3, c = i & 7;
+        const bool okp = m0 + t < R;
+        cp_async16(ps + t * ld + c * 8, okp ? a.probs + x_ws_row(a, g, hk, r, m0 + t) + col0 + k0 + c * 8 : a.probs, okp ? 16 : 0);
+        const bool okv = k0 + t < L;
+        const __nv_bfloat16* p = vbase + ((static_cast<int64_t>(g) * L + (okv ? k0 + t : 0)) * a.h + hk) * a.D + d0 + c * 8;
+        cp_async16(vs + t * ld + c * 8, okv ? p : vbase, okv ? 16 : 0);
+      }
+    };
     float total[8][4] = {};
-    for (int part = 0; part < 2; ++part) {
-      const int L = part == 0 ? a.Lp : a.Tt;
-      const int col0 = part == 0 ? 0 : a.Lp64;
-      const __nv_bfloat16* const vbase = part == 0 ? a.vp : a.vt;
-      float acc[8][4] = {};
-      for (int k0 = 0; k0 < L; k0 += XT) {
-        __syncthreads();
-        for (int i = tid; i < XT * 8; i += 128) {
-          const int t = i >> 3, c = i & 7;
-          const bool okp = m0 + t < R;
-          cp_async16(ps + t * ld + c * 8, okp ? a.probs + x_ws_row(a, g, hk, r, m0 + t) + col0 + k0 + c * 8 : a.probs, okp ? 16 : 0);
-          const bool okv = k0 + t < L;
-          const __nv_bfloat16* p = vbase + ((static_cast<int64_t>(g) * L + (okv ? k0 + t : 0)) * a.h + hk) * a.D + d0 + c * 8;
-          cp_async16(vs + t * ld + c * 8, okv ? p : vbase, okv ? 16 : 0);
-        }
-        cp_async_commit();
-        cp_async_wait<0>();
-        __syncthreads();
-        if (m0 + warp * 16 < R) {
+    float acc[8][4] = {};
+    __syncthreads();  // the previous pass has read both stages
+    if (n_tiles > 0) stage(0, 0);
+    cp_async_commit();
+    for (int tile = 0; tile < n_tiles; ++tile) {
+      if (tile + 1 < n_tiles) stage(tile + 1, (tile + 1) & 1);
+      cp_async_commit();
+      cp_async_wait<1>();
+      __syncthreads();
+      const __nv_bfloat16* const ps = sm + (tile & 1) * STAGE;
+      const __nv_bfloat16* const vs = ps + XT * ld;
+      if (m0 + warp * 16 < R) {
 #pragma unroll
-          for (int kk = 0; kk < XT; kk += 16) {
-            uint32_t af[4];
-            ldsm_x4(af, frag_a(ps, ld, warp * 16, kk, lane));
+        for (int kk = 0; kk < XT; kk += 16) {
+          uint32_t af[4];
+          ldsm_x4(af, frag_a(ps, ld, warp * 16, kk, lane));
 #pragma unroll
-            for (int n2 = 0; n2 < 4; ++n2) {
-              uint32_t bf[4];
-              ldsm_x4_t(bf, frag_b_t(vs, ld, kk, n2 * 16, lane));
-              mma_bf16(acc[2 * n2], af, bf[0], bf[1]);
-              mma_bf16(acc[2 * n2 + 1], af, bf[2], bf[3]);
-            }
+          for (int n2 = 0; n2 < 4; ++n2) {
+            uint32_t bf[4];
+            ldsm_x4_t(bf, frag_b_t(vs, ld, kk, n2 * 16, lane));
+            mma_bf16(acc[2 * n2], af, bf[0], bf[1]);
+            mma_bf16(acc[2 * n2 + 1], af, bf[2], bf[3]);
           }
         }
       }
+      if (tile == np - 1 || tile == n_tiles - 1) {  // a range is complete: its product is rounded to bf16 on its own
 #pragma unroll
-      for (int n = 0; n < 8; ++n)
+        for (int n = 0; n < 8; ++n)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) total[n][e] += x_round_bf16(acc[n][e]);
+          for (int e = 0; e < 4; ++e) {
+            total[n][e] += x_round_bf16(acc[n][e]);
+            acc[n][e] = 0.f;
+          }
+      }
+      __syncthreads();  // this stage is free for the tile after the next
     }
     // the generated range: a row's own slot's tokens 0..step, on the FMA pipe for exactly the elements this thread holds
 #pragma unroll
@@ -319,7 +365,7 @@ extern "C" int spinf_x_attention(const void* q, int64_t q_pitch, const void* kp,
   a.out = static_cast<__nv_bfloat16*>(out);
   a.out_pitch = out_pitch;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int smem_s = 2 * XT * (a.D + 8) * 2, smem_v = 2 * XT * (XT + 8) * 2;
+  const int smem_s = 2 * XT * (a.D + 8) * 2, smem_v = 2 * 2 * XT * (XT + 8) * 2;
   static std::atomic<bool> attr_set[64];
   int dev = 0;
   SPINF_CUDA_OK(cudaGetDevice(&dev));
@@ -327,7 +373,7 @@ extern "C" int spinf_x_attention(const void* q, int64_t q_pitch, const void* kp,
     SPINF_CUDA_OK(cudaFuncSetAttribute(x_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * XT * (512 + 8) * 2));
     if (dev >= 0 && dev < 64) attr_set[dev].store(true, std::memory_order_release);
   }
-  x_scores_kernel<<<dim3(a.Lp64 / XT + a.Tt64 / XT + 1, static_cast<unsigned>(h), static_cast<unsigned>(G)), 128, smem_s, st>>>(a);
+  x_scores_kernel<<<dim3(a.Lp64 / XT + a.Tt64 / XT + (a.Q + 3) / 4, static_cast<unsigned>(h), static_cast<unsigned>(G)), 128, smem_s, st>>>(a);
   SPINF_CUDA_OK(cudaGetLastError());
   x_softmax_kernel<<<static_cast<unsigned>(rows), 128, 0, st>>>(a);
   SPINF_CUDA_OK(cudaGetLastError());
