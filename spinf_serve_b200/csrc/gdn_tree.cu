@@ -10,8 +10,8 @@
 //     v' = U - W S           o = scale [(Q S) 2^G + P v']          S <- S 2^(G_last) + K^T (v' 2^(G_last - G))
 //
 // Two kernels.
-//   gdn_tree_prep_kernel   one CTA per (chunk, key head), every chunk of every segment of the plan in ONE launch: the products K K^T
-//                          and Q K^T once per key head, then per value head of the group G, T (a blocked inverse: the 16 x 16
+//   gdn_tree_prep_kernel   one CTA per (chunk, value head), four to an SM, every chunk of every segment of the plan in ONE launch:
+//                          the products K K^T and Q K^T, the running log-decay G, T (a blocked inverse: the 16 x 16
 //                          diagonal blocks by substitution in fp32, one column per thread; the blocks below them merged in rounds
 //                          of 16 x 16 TF32 tensor-core products, one block per warp), W, U and P into a workspace indexed by plan
 //                          token. Blocks past the chunk's tokens are skipped everywhere (a 20-token branch costs two blocks).
@@ -89,23 +89,35 @@ __device__ __forceinline__ void block16_mma(float (&acc)[2][4], const float* pa,
   }
 }
 
+// Shared memory of a preparation CTA, 56 832 bytes so that four CTAs share an SM. Three regions are reused as the steps go:
+//   r1  K (padded rows)                      -> K~ = bf16(k beta 2^G), in place
+//   r2  Q (padded rows) -> the inverse X in fp32 ([64][65]) -> T = bf16(X) as an MMA operand ([64][72])
+//   r3  A in fp32 ([64][65])                 -> V (64 rows of 256 bytes, 16-byte pieces XOR-swizzled by the row) -> V~ = bf16(v beta)
 struct TreePrepSmem {
-  __nv_bfloat16 k[CT * LD];
-  __nv_bfloat16 q[CT * LD];   // Q, then (per value head) K~ = bf16(k beta 2^G)
-  __nv_bfloat16 v[CT * LD];
-  float a[CT * (CT + 1)];     // A, strictly lower; later T as bf16 (aliased)
-  float x[CT * (CT + 1)];     // the inverse, assembled in fp32
+  __nv_bfloat16 r1[CT * LD];
+  __nv_bfloat16 r2[CT * LD];
+  float r3[CT * (CT + 1)];
   float m[4 * 16 * 17];       // a warp's inner sums of a merge round (one 16 x 16 block each)
   float g[CT], beta[CT];
   int64_t row[CT];
 };
+static_assert(sizeof(TreePrepSmem) <= 56 * 1024, "four preparation CTAs per SM");
+static_assert(CT * (CT + 1) * 4 <= CT * LD * 2 && CT * CK * 2 <= CT * (CT + 1) * 4, "the aliased tiles fit their regions");
 
-__global__ void __launch_bounds__(128, 2) gdn_tree_prep_kernel(const GdnTreeArgs a) {
+// element (row t, column c) of the swizzled V tile: 16-byte piece c / 8 of row t sits at piece (c / 8) ^ (t & 7)
+__device__ __forceinline__ int vsw(int t, int c) { return t * CK + ((((c >> 3) ^ (t & 7)) << 3) | (c & 7)); }
+
+__global__ void __launch_bounds__(128, 4) gdn_tree_prep_kernel(const GdnTreeArgs a) {
   extern __shared__ __align__(16) uint8_t tprep_raw[];
   TreePrepSmem& sm = *reinterpret_cast<TreePrepSmem*>(tprep_raw);
-  __nv_bfloat16* const tb = reinterpret_cast<__nv_bfloat16*>(sm.a);  // T in bf16, [64][72]
-  const int chunk = blockIdx.x, hk = blockIdx.y;
-  const int rep = a.Hv / a.Hk;
+  __nv_bfloat16* const ktile = sm.r1;
+  __nv_bfloat16* const qtile = sm.r2;
+  float* const xm = reinterpret_cast<float*>(sm.r2);               // the inverse, fp32 [64][65]
+  __nv_bfloat16* const tb = sm.r2;                                 // T in bf16, [64][72]
+  float* const am = sm.r3;                                         // A, fp32 [64][65]
+  __nv_bfloat16* const vtile = reinterpret_cast<__nv_bfloat16*>(sm.r3);
+  const int chunk = blockIdx.x, hv = blockIdx.y;
+  const int hk = hv / (a.Hv / a.Hk);
   const int p0 = a.chunk_p0[chunk], len = a.chunk_len[chunk];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int gq = lane >> 2, tq = lane & 3;
@@ -119,185 +131,201 @@ __global__ void __launch_bounds__(128, 2) gdn_tree_prep_kernel(const GdnTreeArgs
       if (r < 0 || r >= a.n_rows) r = -1;  // never read outside the stream: the row counts as padding
     }
     sm.row[tid] = r;
+    sm.g[tid] = r >= 0 ? a.g[r * a.g_pitch + hv] : 0.f;
+    sm.beta[tid] = r >= 0 ? __bfloat162float(a.beta[r * a.g_pitch + hv]) : 0.f;
   }
   __syncthreads();
-  load_tile(sm.k, [&](int t) { return sm.row[t] >= 0 ? a.k + sm.row[t] * a.q_pitch + hk * CK : nullptr; }, a.k, tid, 128);
-  load_tile(sm.q, [&](int t) { return sm.row[t] >= 0 ? a.q + sm.row[t] * a.q_pitch + hk * CK : nullptr; }, a.q, tid, 128);
+  load_tile(ktile, [&](int t) { return sm.row[t] >= 0 ? a.k + sm.row[t] * a.q_pitch + hk * CK : nullptr; }, a.k, tid, 128);
+  load_tile(qtile, [&](int t) { return sm.row[t] >= 0 ? a.q + sm.row[t] * a.q_pitch + hk * CK : nullptr; }, a.q, tid, 128);
   cp_async_commit();
+  if (warp == 0) {
+    // inclusive running sum of g over the chunk (two tokens per lane), then log2 units
+    float x0 = sm.g[2 * lane], x1 = sm.g[2 * lane + 1];
+    float s = x0 + x1;
+    for (int o = 1; o < 32; o <<= 1) {
+      const float y = __shfl_up_sync(0xffffffffu, s, o);
+      if (lane >= o) s += y;
+    }
+    const float before = s - (x0 + x1);
+    sm.g[2 * lane] = (before + x0) * RCP_LN2;
+    sm.g[2 * lane + 1] = (before + x0 + x1) * RCP_LN2;
+  }
   cp_async_wait<0>();
   __syncthreads();
+  if (tid < len) a.g_ws[static_cast<int64_t>(p0 + tid) * a.Hv + hv] = sm.g[tid];
 
-  // K K^T and Q K^T for rows [16 w, 16 w + 16): shared by the key head's value heads
-  float kk[8][4], qk[8][4];
+  {
+    // K K^T and Q K^T for rows [16 w, 16 w + 16), in registers until A and P are formed from them
+    float kk[8][4], qk[8][4];
 #pragma unroll
-  for (int nt = 0; nt < 8; ++nt)
+    for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-    for (int e = 0; e < 4; ++e) kk[nt][e] = qk[nt][e] = 0.f;
-  if (active) {
+      for (int e = 0; e < 4; ++e) kk[nt][e] = qk[nt][e] = 0.f;
+    if (active) {
 #pragma unroll
-    for (int ks = 0; ks < CK / 16; ++ks) {
-      uint32_t fk[4], fq[4];
-      ldsm_x4(fk, frag_a(sm.k, LD, 16 * warp, 16 * ks, lane));
-      ldsm_x4(fq, frag_a(sm.q, LD, 16 * warp, 16 * ks, lane));
+      for (int ks = 0; ks < CK / 16; ++ks) {
+        uint32_t fk[4], fq[4];
+        ldsm_x4(fk, frag_a(ktile, LD, 16 * warp, 16 * ks, lane));
+        ldsm_x4(fq, frag_a(qtile, LD, 16 * warp, 16 * ks, lane));
 #pragma unroll
-      for (int np = 0; np < 4; ++np) {
-        if (np > warp) break;  // columns past the diagonal block are masked anyway
-        uint32_t fb[4];
-        ldsm_x4(fb, frag_b(sm.k, LD, 16 * np, 16 * ks, lane));
-        mma_bf16(kk[2 * np], fk, fb[0], fb[1]);
-        mma_bf16(kk[2 * np + 1], fk, fb[2], fb[3]);
-        mma_bf16(qk[2 * np], fq, fb[0], fb[1]);
-        mma_bf16(qk[2 * np + 1], fq, fb[2], fb[3]);
+        for (int np = 0; np < 4; ++np) {
+          if (np > warp) break;  // columns past the diagonal block are masked anyway
+          uint32_t fb[4];
+          ldsm_x4(fb, frag_b(ktile, LD, 16 * np, 16 * ks, lane));
+          mma_bf16(kk[2 * np], fk, fb[0], fb[1]);
+          mma_bf16(kk[2 * np + 1], fk, fb[2], fb[3]);
+          mma_bf16(qk[2 * np], fq, fb[0], fb[1]);
+          mma_bf16(qk[2 * np + 1], fq, fb[2], fb[3]);
+        }
       }
     }
-  }
-  __syncthreads();  // every warp has read Q: the tile is free for K~
-
-  for (int j = 0; j < rep; ++j) {
-    const int hv = hk * rep + j;
-    load_tile(sm.v, [&](int t) { return sm.row[t] >= 0 ? a.v + sm.row[t] * a.v_pitch + hv * CK : nullptr; }, a.v, tid, 128);
-    cp_async_commit();
-    if (tid < CT) {
-      const int64_t r = sm.row[tid];
-      sm.g[tid] = r >= 0 ? a.g[r * a.g_pitch + hv] : 0.f;
-      sm.beta[tid] = r >= 0 ? __bfloat162float(a.beta[r * a.g_pitch + hv]) : 0.f;
-    }
-    __syncthreads();
-    if (warp == 0) {
-      // inclusive running sum of g over the chunk (two tokens per lane), then log2 units
-      float x0 = sm.g[2 * lane], x1 = sm.g[2 * lane + 1];
-      float s = x0 + x1;
-      for (int o = 1; o < 32; o <<= 1) {
-        const float y = __shfl_up_sync(0xffffffffu, s, o);
-        if (lane >= o) s += y;
-      }
-      const float before = s - (x0 + x1);
-      sm.g[2 * lane] = (before + x0) * RCP_LN2;
-      sm.g[2 * lane + 1] = (before + x0 + x1) * RCP_LN2;
-    }
-    __syncthreads();
-    if (tid < len) a.g_ws[static_cast<int64_t>(p0 + tid) * a.Hv + hv] = sm.g[tid];
-
     // A (strictly lower, fp32) into shared memory; P (lower with the diagonal, bf16) straight to the workspace
     if (active)
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
-      if (nt > 2 * warp + 1) {  // columns past this warp's diagonal block: A there is never read, P is zero (a scan that multiplies
-        // whole 64 x 64 tiles reads every column of a row)
+      for (int nt = 0; nt < 8; ++nt) {
+        if (nt > 2 * warp + 1) {  // columns past this warp's diagonal block: A there is never read, P is zero (a scan that multiplies
+          // whole 64 x 64 tiles reads every column of a row)
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int t = 16 * warp + gq + 8 * h;
+            if (t < len) *reinterpret_cast<uint32_t*>(a.p_ws + (static_cast<int64_t>(p0 + t) * a.Hv + hv) * CT + 8 * nt + 2 * tq) = 0u;
+          }
+          continue;
+        }
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          const int t = 16 * warp + gq + 8 * h;
-          if (t < len) *reinterpret_cast<uint32_t*>(a.p_ws + (static_cast<int64_t>(p0 + t) * a.Hv + hv) * CT + 8 * nt + 2 * tq) = 0u;
+          const int t = 16 * warp + gq + 8 * h, s0 = 8 * nt + 2 * tq;
+          const float gt = sm.g[t], bt = sm.beta[t];
+          const float d0 = fast_exp2(gt - sm.g[s0]), d1 = fast_exp2(gt - sm.g[s0 + 1]);
+          am[t * (CT + 1) + s0] = s0 < t ? kk[nt][2 * h] * d0 * bt : 0.f;
+          am[t * (CT + 1) + s0 + 1] = s0 + 1 < t ? kk[nt][2 * h + 1] * d1 * bt : 0.f;
+          if (t < len) {
+            const float p0v = s0 <= t ? qk[nt][2 * h] * d0 : 0.f, p1v = s0 + 1 <= t ? qk[nt][2 * h + 1] * d1 : 0.f;
+            *reinterpret_cast<uint32_t*>(a.p_ws + (static_cast<int64_t>(p0 + t) * a.Hv + hv) * CT + s0) = pack_bf16x2(p0v, p1v);
+          }
         }
-        continue;
+      }
+  }
+  __syncthreads();  // A is complete; every warp has read Q: its tile is free for the inverse
+
+  // T = (I + A)^-1. Stage 1: the diagonal 16 x 16 blocks that hold tokens, one column per thread (forward substitution in
+  // registers, fp32)
+  if (tid < 16 * mtiles) {
+    const int b = tid >> 4, c = tid & 15;
+    float x[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float s = i == c ? 1.f : 0.f;
+#pragma unroll
+      for (int t = 0; t < i; ++t) s = fmaf(-am[(16 * b + i) * (CT + 1) + 16 * b + t], x[t], s);
+      x[i] = s;
+      xm[(16 * b + i) * (CT + 1) + 16 * b + c] = s;
+    }
+  }
+  __syncthreads();
+  // Stage 2: the blocks below the diagonal, by distance d from it: T_ij = -T_ii sum_{k = j}^{i - 1} A_ik T_kj, one block per warp
+#pragma unroll 1
+  for (int d = 1; d < mtiles; ++d) {
+    const int jb = warp, ib = warp + d;
+    if (ib < mtiles) {
+      float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      for (int kb = jb; kb < ib; ++kb)
+        block16_mma(acc, am + (16 * ib) * (CT + 1) + 16 * kb, CT + 1, xm + (16 * kb) * (CT + 1) + 16 * jb, CT + 1, lane);
+      float* mw = sm.m + warp * 16 * 17;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        mw[gq * 17 + 8 * nt + 2 * tq] = acc[nt][0], mw[gq * 17 + 8 * nt + 2 * tq + 1] = acc[nt][1];
+        mw[(gq + 8) * 17 + 8 * nt + 2 * tq] = acc[nt][2], mw[(gq + 8) * 17 + 8 * nt + 2 * tq + 1] = acc[nt][3];
+      }
+      __syncwarp();
+      float out[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      block16_mma(out, xm + (16 * ib) * (CT + 1) + 16 * ib, CT + 1, mw, 17, lane);
+      float* dst = xm + (16 * ib) * (CT + 1) + 16 * jb;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        dst[gq * (CT + 1) + 8 * nt + 2 * tq] = -out[nt][0], dst[gq * (CT + 1) + 8 * nt + 2 * tq + 1] = -out[nt][1];
+        dst[(gq + 8) * (CT + 1) + 8 * nt + 2 * tq] = -out[nt][2], dst[(gq + 8) * (CT + 1) + 8 * nt + 2 * tq + 1] = -out[nt][3];
+      }
+    }
+    __syncthreads();
+  }
+  // A is dead: V comes into its place (in flight while T and K~ are formed)
+  for (int i = tid; i < CT * (CK / 8); i += 128) {
+    const int t = i / (CK / 8), c = i % (CK / 8);
+    const int64_t r = sm.row[t];
+    cp_async16(vtile + vsw(t, c * 8), r >= 0 ? a.v + r * a.v_pitch + hv * CK + c * 8 : a.v, r >= 0 ? 16 : 0);
+  }
+  cp_async_commit();
+  {
+    // T as the bf16 A operand, over the fp32 inverse it is read from: through registers, a barrier between reading and writing
+    float tx[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const int i = tid + 128 * j, t = i >> 6, s = i & 63;
+      tx[j] = (s >> 4) <= (t >> 4) && t < 16 * mtiles ? xm[t * (CT + 1) + s] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const int i = tid + 128 * j, t = i >> 6, s = i & 63;
+      tb[t * LDS + s] = __float2bfloat16_rn(tx[j]);
+    }
+  }
+  // K~ = bf16(k beta 2^G) in place
+  for (int i = tid; i < 16 * mtiles * (CK / 2); i += 128) {
+    const int t = i / (CK / 2), c = (i % (CK / 2)) * 2;
+    const float b = sm.beta[t], e = fast_exp2(sm.g[t]);
+    uint32_t* pk = reinterpret_cast<uint32_t*>(ktile + t * LD + c);
+    *pk = pack_bf16x2(bf2_lo(*pk) * b * e, bf2_hi(*pk) * b * e);
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+  // V~ = bf16(v beta) in place (a row's pieces are permuted inside the row only, so the physical row is the token)
+  for (int i = tid; i < 16 * mtiles * (CK / 2); i += 128) {
+    const int t = i / (CK / 2), c = (i % (CK / 2)) * 2;
+    const float b = sm.beta[t];
+    uint32_t* pv = reinterpret_cast<uint32_t*>(vtile + t * CK + c);
+    *pv = pack_bf16x2(bf2_lo(*pv) * b, bf2_hi(*pv) * b);
+  }
+  __syncthreads();
+  // W = T K~, U = T V~ for rows [16 w, 16 w + 16); T is block lower-triangular: k-steps up to the diagonal block only
+  if (active) {
+#pragma unroll 1
+    for (int which = 0; which < 2; ++which) {
+      __nv_bfloat16* dst = which ? a.u_ws : a.w_ws;
+      float acc[16][4];
+#pragma unroll
+      for (int nt = 0; nt < 16; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < CT / 16; ++ks) {
+        if (ks > warp) break;
+        uint32_t fa[4];
+        ldsm_x4(fa, frag_a(tb, LDS, 16 * warp, 16 * ks, lane));
+#pragma unroll
+        for (int np = 0; np < 8; ++np) {
+          uint32_t fb[4];
+          if (which) {
+            // the [k][n] pattern of frag_b_t on the swizzled tile: row k0 + (lane & 7) + 8 ((lane >> 3) & 1), column n0 + 8 (lane >> 4)
+            const int kr = 16 * ks + (lane & 7) + ((lane >> 3) & 1) * 8;
+            ldsm_x4_t(fb, vtile + vsw(kr, 16 * np + (lane >> 4) * 8));
+          } else {
+            ldsm_x4_t(fb, frag_b_t(ktile, LD, 16 * ks, 16 * np, lane));
+          }
+          mma_bf16(acc[2 * np], fa, fb[0], fb[1]);
+          mma_bf16(acc[2 * np + 1], fa, fb[2], fb[3]);
+        }
       }
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        const int t = 16 * warp + gq + 8 * h, s0 = 8 * nt + 2 * tq;
-        const float gt = sm.g[t], bt = sm.beta[t];
-        const float d0 = fast_exp2(gt - sm.g[s0]), d1 = fast_exp2(gt - sm.g[s0 + 1]);
-        sm.a[t * (CT + 1) + s0] = s0 < t ? kk[nt][2 * h] * d0 * bt : 0.f;
-        sm.a[t * (CT + 1) + s0 + 1] = s0 + 1 < t ? kk[nt][2 * h + 1] * d1 * bt : 0.f;
+        const int t = 16 * warp + gq + 8 * h;
         if (t < len) {
-          const float p0v = s0 <= t ? qk[nt][2 * h] * d0 : 0.f, p1v = s0 + 1 <= t ? qk[nt][2 * h + 1] * d1 : 0.f;
-          *reinterpret_cast<uint32_t*>(a.p_ws + (static_cast<int64_t>(p0 + t) * a.Hv + hv) * CT + s0) = pack_bf16x2(p0v, p1v);
+          __nv_bfloat16* row = dst + (static_cast<int64_t>(p0 + t) * a.Hv + hv) * CK;
+#pragma unroll
+          for (int nt = 0; nt < 16; ++nt)
+            *reinterpret_cast<uint32_t*>(row + 8 * nt + 2 * tq) = pack_bf16x2(acc[nt][2 * h], acc[nt][2 * h + 1]);
         }
       }
     }
-    __syncthreads();
-
-    // T = (I + A)^-1. Stage 1: the diagonal 16 x 16 blocks that hold tokens, one column per thread (forward substitution in
-    // registers, fp32)
-    if (tid < 16 * mtiles) {
-      const int b = tid >> 4, c = tid & 15;
-      float x[16];
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        float s = i == c ? 1.f : 0.f;
-#pragma unroll
-        for (int t = 0; t < i; ++t) s = fmaf(-sm.a[(16 * b + i) * (CT + 1) + 16 * b + t], x[t], s);
-        x[i] = s;
-        sm.x[(16 * b + i) * (CT + 1) + 16 * b + c] = s;
-      }
-    }
-    __syncthreads();
-    // Stage 2: the blocks below the diagonal, by distance d from it: T_ij = -T_ii sum_{k = j}^{i - 1} A_ik T_kj, one block per warp
-#pragma unroll 1
-    for (int d = 1; d < mtiles; ++d) {
-      const int jb = warp, ib = warp + d;
-      if (ib < mtiles) {
-        float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-        for (int kb = jb; kb < ib; ++kb)
-          block16_mma(acc, sm.a + (16 * ib) * (CT + 1) + 16 * kb, CT + 1, sm.x + (16 * kb) * (CT + 1) + 16 * jb, CT + 1, lane);
-        float* mw = sm.m + warp * 16 * 17;
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-          mw[gq * 17 + 8 * nt + 2 * tq] = acc[nt][0], mw[gq * 17 + 8 * nt + 2 * tq + 1] = acc[nt][1];
-          mw[(gq + 8) * 17 + 8 * nt + 2 * tq] = acc[nt][2], mw[(gq + 8) * 17 + 8 * nt + 2 * tq + 1] = acc[nt][3];
-        }
-        __syncwarp();
-        float out[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-        block16_mma(out, sm.x + (16 * ib) * (CT + 1) + 16 * ib, CT + 1, mw, 17, lane);
-        float* dst = sm.x + (16 * ib) * (CT + 1) + 16 * jb;
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-          dst[gq * (CT + 1) + 8 * nt + 2 * tq] = -out[nt][0], dst[gq * (CT + 1) + 8 * nt + 2 * tq + 1] = -out[nt][1];
-          dst[(gq + 8) * (CT + 1) + 8 * nt + 2 * tq] = -out[nt][2], dst[(gq + 8) * (CT + 1) + 8 * nt + 2 * tq + 1] = -out[nt][3];
-        }
-      }
-      __syncthreads();
-    }
-    // T as the bf16 A operand (over A, which is dead); K~ = bf16(k beta 2^G) into the Q tile; V~ = bf16(v beta) in place
-    for (int i = tid; i < 16 * mtiles * CT; i += 128) {
-      const int t = i >> 6, s = i & 63;
-      tb[t * LDS + s] = __float2bfloat16_rn((s >> 4) <= (t >> 4) ? sm.x[t * (CT + 1) + s] : 0.f);
-    }
-    cp_async_wait<0>();
-    __syncthreads();
-    for (int i = tid; i < 16 * mtiles * (CK / 2); i += 128) {
-      const int t = i / (CK / 2), c = (i % (CK / 2)) * 2;
-      const float b = sm.beta[t], e = fast_exp2(sm.g[t]);
-      const uint32_t kw = *reinterpret_cast<const uint32_t*>(sm.k + t * LD + c);
-      *reinterpret_cast<uint32_t*>(sm.q + t * LD + c) = pack_bf16x2(bf2_lo(kw) * b * e, bf2_hi(kw) * b * e);
-      uint32_t* pv = reinterpret_cast<uint32_t*>(sm.v + t * LD + c);
-      *pv = pack_bf16x2(bf2_lo(*pv) * b, bf2_hi(*pv) * b);
-    }
-    __syncthreads();
-    // W = T K~, U = T V~ for rows [16 w, 16 w + 16); T is block lower-triangular: k-steps up to the diagonal block only
-    if (active) {
-#pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
-        const __nv_bfloat16* src = which ? sm.v : sm.q;
-        __nv_bfloat16* dst = which ? a.u_ws : a.w_ws;
-        float acc[16][4];
-#pragma unroll
-        for (int nt = 0; nt < 16; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
-#pragma unroll
-        for (int ks = 0; ks < CT / 16; ++ks) {
-          if (ks > warp) break;
-          uint32_t fa[4];
-          ldsm_x4(fa, frag_a(tb, LDS, 16 * warp, 16 * ks, lane));
-#pragma unroll
-          for (int np = 0; np < 8; ++np) {
-            uint32_t fb[4];
-            ldsm_x4_t(fb, frag_b_t(src, LD, 16 * ks, 16 * np, lane));
-            mma_bf16(acc[2 * np], fa, fb[0], fb[1]);
-            mma_bf16(acc[2 * np + 1], fa, fb[2], fb[3]);
-          }
-        }
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int t = 16 * warp + gq + 8 * h;
-          if (t < len) {
-            __nv_bfloat16* row = dst + (static_cast<int64_t>(p0 + t) * a.Hv + hv) * CK;
-#pragma unroll
-            for (int nt = 0; nt < 16; ++nt)
-              *reinterpret_cast<uint32_t*>(row + 8 * nt + 2 * tq) = pack_bf16x2(acc[nt][2 * h], acc[nt][2 * h + 1]);
-          }
-        }
-      }
-    }
-    __syncthreads();  // T, K~ and V~ are overwritten by the next value head
   }
 }
 
@@ -571,7 +599,7 @@ extern "C" int spinf_gdn_tree_prep(const void* q, const void* k, const void* v, 
   SPINF_CHECK_ARG(v_pitch >= static_cast<int64_t>(Hv) * CK && v_pitch % 8 == 0 && g_pitch >= Hv);
   if ((r = tree_attrs())) return r;
   a.chunk_p0 = chunk_p0, a.chunk_len = chunk_len;
-  gdn_tree_prep_kernel<<<dim3(static_cast<unsigned>(n_chunks), static_cast<unsigned>(Hk)), 128, sizeof(TreePrepSmem), static_cast<cudaStream_t>(stream)>>>(a);
+  gdn_tree_prep_kernel<<<dim3(static_cast<unsigned>(n_chunks), static_cast<unsigned>(Hv)), 128, sizeof(TreePrepSmem), static_cast<cudaStream_t>(stream)>>>(a);
   SPINF_CUDA_OK(cudaGetLastError());
   return 0;
 }
