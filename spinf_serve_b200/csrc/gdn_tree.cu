@@ -93,16 +93,17 @@ __device__ __forceinline__ void block16_mma(float (&acc)[2][4], const float* pa,
 //   r1  K (padded rows)                      -> K~ = bf16(k beta 2^G), in place
 //   r2  Q (padded rows) -> the inverse X in fp32 ([64][65]) -> T = bf16(X) as an MMA operand ([64][72])
 //   r3  A in fp32 ([64][65])                 -> V (64 rows of 256 bytes, 16-byte pieces XOR-swizzled by the row) -> V~ = bf16(v beta)
+static constexpr int LDA = CT + 2;  // row stride of the fp32 A and X: the two diagonal blocks a warp solves lie 16 banks apart
 struct TreePrepSmem {
   __nv_bfloat16 r1[CT * LD];
   __nv_bfloat16 r2[CT * LD];
-  float r3[CT * (CT + 1)];
+  float r3[CT * LDA];
   float m[4 * 16 * 17];       // a warp's inner sums of a merge round (one 16 x 16 block each)
   float g[CT], beta[CT];
   int64_t row[CT];
 };
 static_assert(sizeof(TreePrepSmem) <= 56 * 1024, "four preparation CTAs per SM");
-static_assert(CT * (CT + 1) * 4 <= CT * LD * 2 && CT * CK * 2 <= CT * (CT + 1) * 4, "the aliased tiles fit their regions");
+static_assert(CT * LDA * 4 <= CT * LD * 2 && CT * CK * 2 <= CT * LDA * 4, "the aliased tiles fit their regions");
 
 // element (row t, column c) of the swizzled V tile: 16-byte piece c / 8 of row t sits at piece (c / 8) ^ (t & 7)
 __device__ __forceinline__ int vsw(int t, int c) { return t * CK + ((((c >> 3) ^ (t & 7)) << 3) | (c & 7)); }
@@ -112,9 +113,9 @@ __global__ void __launch_bounds__(128, 4) gdn_tree_prep_kernel(const GdnTreeArgs
   TreePrepSmem& sm = *reinterpret_cast<TreePrepSmem*>(tprep_raw);
   __nv_bfloat16* const ktile = sm.r1;
   __nv_bfloat16* const qtile = sm.r2;
-  float* const xm = reinterpret_cast<float*>(sm.r2);               // the inverse, fp32 [64][65]
+  float* const xm = reinterpret_cast<float*>(sm.r2);               // the inverse, fp32 [64][66]
   __nv_bfloat16* const tb = sm.r2;                                 // T in bf16, [64][72]
-  float* const am = sm.r3;                                         // A, fp32 [64][65]
+  float* const am = sm.r3;                                         // A, fp32 [64][66]
   __nv_bfloat16* const vtile = reinterpret_cast<__nv_bfloat16*>(sm.r3);
   const int chunk = blockIdx.x, hv = blockIdx.y;
   const int hk = hv / (a.Hv / a.Hk);
@@ -197,8 +198,8 @@ __global__ void __launch_bounds__(128, 4) gdn_tree_prep_kernel(const GdnTreeArgs
           const int t = 16 * warp + gq + 8 * h, s0 = 8 * nt + 2 * tq;
           const float gt = sm.g[t], bt = sm.beta[t];
           const float d0 = fast_exp2(gt - sm.g[s0]), d1 = fast_exp2(gt - sm.g[s0 + 1]);
-          am[t * (CT + 1) + s0] = s0 < t ? kk[nt][2 * h] * d0 * bt : 0.f;
-          am[t * (CT + 1) + s0 + 1] = s0 + 1 < t ? kk[nt][2 * h + 1] * d1 * bt : 0.f;
+          am[t * LDA + s0] = s0 < t ? kk[nt][2 * h] * d0 * bt : 0.f;
+          am[t * LDA + s0 + 1] = s0 + 1 < t ? kk[nt][2 * h + 1] * d1 * bt : 0.f;
           if (t < len) {
             const float p0v = s0 <= t ? qk[nt][2 * h] * d0 : 0.f, p1v = s0 + 1 <= t ? qk[nt][2 * h + 1] * d1 : 0.f;
             *reinterpret_cast<uint32_t*>(a.p_ws + (static_cast<int64_t>(p0 + t) * a.Hv + hv) * CT + s0) = pack_bf16x2(p0v, p1v);
@@ -217,9 +218,9 @@ __global__ void __launch_bounds__(128, 4) gdn_tree_prep_kernel(const GdnTreeArgs
     for (int i = 0; i < 16; ++i) {
       float s = i == c ? 1.f : 0.f;
 #pragma unroll
-      for (int t = 0; t < i; ++t) s = fmaf(-am[(16 * b + i) * (CT + 1) + 16 * b + t], x[t], s);
+      for (int t = 0; t < i; ++t) s = fmaf(-am[(16 * b + i) * LDA + 16 * b + t], x[t], s);
       x[i] = s;
-      xm[(16 * b + i) * (CT + 1) + 16 * b + c] = s;
+      xm[(16 * b + i) * LDA + 16 * b + c] = s;
     }
   }
   __syncthreads();
@@ -230,7 +231,7 @@ __global__ void __launch_bounds__(128, 4) gdn_tree_prep_kernel(const GdnTreeArgs
     if (ib < mtiles) {
       float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
       for (int kb = jb; kb < ib; ++kb)
-        block16_mma(acc, am + (16 * ib) * (CT + 1) + 16 * kb, CT + 1, xm + (16 * kb) * (CT + 1) + 16 * jb, CT + 1, lane);
+        block16_mma(acc, am + (16 * ib) * LDA + 16 * kb, LDA, xm + (16 * kb) * LDA + 16 * jb, LDA, lane);
       float* mw = sm.m + warp * 16 * 17;
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
@@ -239,12 +240,12 @@ __global__ void __launch_bounds__(128, 4) gdn_tree_prep_kernel(const GdnTreeArgs
       }
       __syncwarp();
       float out[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-      block16_mma(out, xm + (16 * ib) * (CT + 1) + 16 * ib, CT + 1, mw, 17, lane);
-      float* dst = xm + (16 * ib) * (CT + 1) + 16 * jb;
+      block16_mma(out, xm + (16 * ib) * LDA + 16 * ib, LDA, mw, 17, lane);
+      float* dst = xm + (16 * ib) * LDA + 16 * jb;
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
-        dst[gq * (CT + 1) + 8 * nt + 2 * tq] = -out[nt][0], dst[gq * (CT + 1) + 8 * nt + 2 * tq + 1] = -out[nt][1];
-        dst[(gq + 8) * (CT + 1) + 8 * nt + 2 * tq] = -out[nt][2], dst[(gq + 8) * (CT + 1) + 8 * nt + 2 * tq + 1] = -out[nt][3];
+        dst[gq * LDA + 8 * nt + 2 * tq] = -out[nt][0], dst[gq * LDA + 8 * nt + 2 * tq + 1] = -out[nt][1];
+        dst[(gq + 8) * LDA + 8 * nt + 2 * tq] = -out[nt][2], dst[(gq + 8) * LDA + 8 * nt + 2 * tq + 1] = -out[nt][3];
       }
     }
     __syncthreads();
@@ -262,7 +263,7 @@ __global__ void __launch_bounds__(128, 4) gdn_tree_prep_kernel(const GdnTreeArgs
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
       const int i = tid + 128 * j, t = i >> 6, s = i & 63;
-      tx[j] = (s >> 4) <= (t >> 4) && t < 16 * mtiles ? xm[t * (CT + 1) + s] : 0.f;
+      tx[j] = (s >> 4) <= (t >> 4) && t < 16 * mtiles ? xm[t * LDA + s] : 0.f;
     }
     __syncthreads();
 #pragma unroll
