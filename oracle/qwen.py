@@ -89,8 +89,12 @@ def rope(x, cos, sin):
     return torch.cat([xr * cos[:, None] + rot * sin[:, None], xp], -1)
 
 
-def forward(cfg: QwenConfig, W, ids, art, end, pos, plan, n_layers=None, taps=None):
-    """packed forward -> final hidden states [T, hidden] bf16; plan: a TreePlan over the stream (gdn_plan.tree_plan on the CPU)"""
+def forward(cfg: QwenConfig, W, ids, art, end, pos, plan, n_layers=None, taps=None, caps=None, attend=None, recur=None):
+    """packed forward -> final hidden states [T, hidden] bf16; plan: a TreePlan over the stream (gdn_plan.tree_plan on the CPU).
+    caps: optional dict filled per layer with what an extraction capture keeps (recurrent layers: the in-projection rows y and
+    q, k, v, g, beta; attention layers: k, v). attend(layer, q, k, v) -> [T, H, D] and recur(layer, y) -> (o, z) stand in for the
+    tree attention and the recurrence over the plan in a decoding step (spinf_serve/models/qwen35/qwen_decode.py); art, end and
+    plan are unused then."""
     T = len(ids)
     lin = lambda x, w, extra=None: OL.int4_linear(x, *OL.gptq_unpack(*w), cfg.group, extra)  # noqa: E731
     x = W["embed"][torch.as_tensor(np.asarray(ids), dtype=torch.int64)]
@@ -98,14 +102,19 @@ def forward(cfg: QwenConfig, W, ids, art, end, pos, plan, n_layers=None, taps=No
     f = torch.as_tensor(np.asarray(pos), dtype=torch.float32)[:, None] * inv_freq[None]
     e = torch.cat([f, f], -1)
     cos, sin = e.cos().to(x.dtype), e.sin().to(x.dtype)
-    conv = plan.conv.numpy() if hasattr(plan.conv, "numpy") else np.asarray(plan.conv)
+    conv = None if plan is None else plan.conv.numpy() if hasattr(plan.conv, "numpy") else np.asarray(plan.conv)
     H, K, D = cfg.heads, cfg.kv_heads, cfg.head_dim
     for i, L in enumerate(W["layers"][: n_layers if n_layers is not None else cfg.layers]):
         h = rmsnorm(x, L["input_ln"], cfg.eps)
         if L["kind"] == "linear_attention":
             y = lin(h, L["in_proj"], L["in_extra"])
-            q, k, v, z, g, beta = OGD.prologue(y, conv, L["conv_w"], L["A_log"], L["dt_bias"], cfg.hk, cfg.dk, cfg.hv, cfg.dv)
-            o = OGD.gdn_tree(q, k, v, g, beta, plan)
+            if recur is not None:
+                o, z = recur(i, y)
+            else:
+                q, k, v, z, g, beta = OGD.prologue(y, conv, L["conv_w"], L["A_log"], L["dt_bias"], cfg.hk, cfg.dk, cfg.hv, cfg.dv)
+                o = OGD.gdn_tree(q, k, v, g, beta, plan)
+                if caps is not None:
+                    caps[i] = {"y": y, "q": q, "k": k, "v": v, "g": g, "beta": beta, "o": o}
             h = lin(OGD.epilogue(o, z, L["gdn_norm"], cfg.eps), L["out_proj"])
         else:
             y = lin(h, L["qkv_proj"])
@@ -116,7 +125,9 @@ def forward(cfg: QwenConfig, W, ids, art, end, pos, plan, n_layers=None, taps=No
             k = rmsnorm(y[:, nq : nq + nk].reshape(T, K, D), L["k_norm"], cfg.eps)
             v = y[:, nq + nk :].reshape(T, K, D)
             q, k = rope(q, cos, sin), rope(k, cos, sin)
-            o = OA.tree_attention(q, k, v, art, end, pos, D**-0.5, None).to(x.dtype)
+            if caps is not None:
+                caps[i] = {"k": k, "v": v}
+            o = attend(i, q, k, v) if attend is not None else OA.tree_attention(q, k, v, art, end, pos, D**-0.5, None).to(x.dtype)
             h = lin(o.reshape(T, -1) * torch.sigmoid(gate), L["o_proj"])
         x = x + h
         gu = lin(rmsnorm(x, L["post_ln"], cfg.eps), L["gate_up"])
