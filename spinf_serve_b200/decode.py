@@ -117,6 +117,7 @@ class Decoder:
         self.workspace = torch.empty(need, dtype=torch.uint8, device=device)
         self.step = 0
         self.graph, self.h_out = None, None
+        self.scaling = 1.0  # the Gemma-style layers norm q and k and attend with scaling 1
 
     def _attend(self, i, kind, q, k, v):
         """a layer's attention inside a step: the new tokens' K/V into the generated range at the current step (GroupKV.update),
@@ -129,7 +130,7 @@ class Decoder:
         window = cfg.window if kind == "sliding_attention" else None
         out = ops.x_attention(
             q.view(G, Q, cfg.heads, D), self.kp[i], self.vp[i], self.pos_p[i], self.kt[i], self.vt[i], self.pos_t, self.own_t, self.gk[i],
-            self.gv[i], self.qpos, self.step32, self.beam, 1.0, window, None, workspace=self.workspace,
+            self.gv[i], self.qpos, self.step32, self.beam, self.scaling, window, None, workspace=self.workspace,
         )
         return out.view(G * Q, cfg.heads, D)
 
@@ -147,7 +148,19 @@ class Decoder:
         self.qpos.copy_(self.base + self.step)
         self.step_t.fill_(self.step)
         self.step32.fill_(self.step)
+        self._prepare(self.step)
         self.step += 1
+        out = self._run()
+        self._finish()
+        return out
+
+    def _prepare(self, step: int) -> None:
+        """a family's own static buffers for this step (before the step runs, outside a captured graph)"""
+
+    def _finish(self) -> None:
+        """a family's bookkeeping after the step (outside a captured graph)"""
+
+    def _run(self):
         if self.graph is not None:
             self.graph.replay()
             return self.h_out
@@ -156,7 +169,7 @@ class Decoder:
         side = torch.cuda.Stream(self.device)
         side.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(side):
-            self._step_once()  # lazy initialisations must not happen inside the capture
+            self._step_once()  # lazy initialisations must not happen inside the capture; the step is idempotent
         torch.cuda.current_stream(self.device).wait_stream(side)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
@@ -171,6 +184,144 @@ class Decoder:
             for t in (self.gk[li], self.gv[li]):
                 flat = t.view(self.G * self.Q, *t.shape[2:])
                 flat.copy_(flat[parent])
+
+
+class HybridDecoder(Decoder):
+    """Decoder for the hybrid family (qwen_stack.QwenStack): the attention layers as above; a recurrent layer re-runs the gated
+    delta rule from the group's prefix state over the slot's own rows (its template's, then the tokens it generated): no per-slot
+    state is kept or copied when beams fan out, only the small row caches follow the beams; the 4-tap convolution reads a
+    per-slot ring of the three previous pre-convolution rows (spinf_serve/models/qwen35/qwen_decode.py:1-20,70-166). A group's
+    `extra` holds what QwenStack.capture delivered for it: {"state": {layer: S}, "tmpl": [per prompt {"tok": {layer: (q, k, v, g,
+    beta)}, "pre": {layer: [3, conv dim]}}]}."""
+
+    def __init__(self, stack, groups: list, device, beam: int = BEAM, graphs: bool = False):
+        extras = [g.extra for g in groups]
+        for g in groups:
+            g.extra = None  # the base class reads extra["pos0"] only
+        super().__init__(stack, groups, device, beam, graphs)
+        cfg = stack.cfg
+        self.scaling = cfg.head_dim**-0.5
+        G, Q, S = self.G, self.Q, self.S
+        n = self.n = G * Q
+        self.rec = [i for i in range(stack.n_layers) if stack.w.layers[i]["kind"] == "linear_attention"]
+        self.rec_pos = {li: x for x, li in enumerate(self.rec)}
+        n_g = len(self.rec)
+        hk, hv, dk, dv = cfg.hk, cfg.hv, cfg.dk, cfg.dv
+        cd = self.cd = 2 * hk * dk + hv * dv
+        width = cd + hv * dv + 2 * hv  # an in-projection row: q | k | v | z | b | a
+        bf = torch.bfloat16
+        self.h0 = torch.empty((n_g, G, hv, dk, dv), dtype=torch.float32, device=device)
+        for x, li in enumerate(self.rec):
+            for gi, e in enumerate(extras):
+                self.h0[x, gi].copy_(e["state"][li])
+        self.h0_idx = (torch.arange(n, dtype=torch.int64) // Q).to(device)
+        # row caches per recurrent layer: the templates' rows (prompt after prompt), then S generated rows per slot
+        t0, r = {}, 0
+        for gi, g in enumerate(groups):
+            for j, (_, _, T, _) in enumerate(g.prompts):
+                t0[(gi, j)] = r
+                r += T
+        self.gen0 = r
+        R = self.R = r + n * S
+        self.cq = torch.zeros((n_g, R, hk, dk), dtype=bf, device=device)
+        self.ck = torch.zeros((n_g, R, hk, dk), dtype=bf, device=device)
+        self.cv = torch.zeros((n_g, R, hv, dv), dtype=bf, device=device)
+        self.cg = torch.zeros((n_g, R, hv), dtype=torch.float32, device=device)
+        self.cb = torch.zeros((n_g, R, hv), dtype=bf, device=device)
+        # in-projection rows of a step with the conv rings behind them: rows 0 .. n - 1 the step's own, rows n + 3 s .. n + 3 s + 2
+        # slot s's three previous pre-convolution rows (taps 3 back .. 1 back); one prologue call reads both through its tap table
+        self.ybuf = torch.zeros((n_g, 4 * n, width), dtype=bf, device=device)
+        slot_T, slot_t0 = torch.zeros(n, dtype=torch.int64), torch.zeros(n, dtype=torch.int64)
+        for gi, (g, e) in enumerate(zip(groups, extras, strict=True)):
+            for j, (_, _, T, _) in enumerate(g.prompts):
+                a = t0[(gi, j)]
+                sl = slice(gi * Q + j * beam, gi * Q + (j + 1) * beam)
+                slot_T[sl], slot_t0[sl] = T, a
+                for x, li in enumerate(self.rec):
+                    q, k, v, gg, bb = e["tmpl"][j]["tok"][li]
+                    self.cq[x, a : a + T], self.ck[x, a : a + T], self.cv[x, a : a + T] = q, k, v
+                    self.cg[x, a : a + T], self.cb[x, a : a + T] = gg, bb
+                    ring = self.ybuf[x, n:].view(n, 3, width)
+                    ring[sl, :, :cd] = e["tmpl"][j]["pre"][li][None]
+        s_ar = torch.arange(n, dtype=torch.int64)
+        self.conv_idx = torch.stack([n + 3 * s_ar, n + 3 * s_ar + 1, n + 3 * s_ar + 2, s_ar], 1).contiguous().to(device)
+        # the recurrence's rows for every step, made once on the host: per slot its template rows, then its generated rows 0 .. step
+        lens = slot_T[None, :] + torch.arange(1, S + 1, dtype=torch.int64)[:, None]  # [S, n]
+        self.cu_all = torch.nn.functional.pad(lens.cumsum(1), (1, 0)).contiguous().to(device)  # [S, n + 1]
+        max_rows = int(lens[-1].sum())
+        idx_all = torch.zeros((S, max_rows), dtype=torch.int64)
+        for st in range(S):
+            parts = [torch.cat([slot_t0[s] + torch.arange(int(slot_T[s])), self.gen0 + s * S + torch.arange(st + 1)]) for s in range(n)]
+            row = torch.cat(parts)
+            idx_all[st, : row.numel()] = row
+        self.idx_all = idx_all.to(device)
+        self.gen_row0 = (self.gen0 + s_ar * S).to(device)
+        # static buffers of a step
+        self.idx_buf = self.idx_all[0].clone()
+        self.cu_buf = self.cu_all[0].clone()
+        self.cur_rows = self.gen_row0.clone()
+        self.o_buf = torch.zeros((R, hv, dv), dtype=bf, device=device)
+
+    def _prepare(self, step: int) -> None:
+        st = min(step, self.S - 1)
+        self.idx_buf.copy_(self.idx_all[st])
+        self.cu_buf.copy_(self.cu_all[st])
+        self.cur_rows.copy_(self.gen_row0 + st)
+
+    def _finish(self) -> None:
+        """the conv rings advance by the step's own pre-convolution rows"""
+        n, cd = self.n, self.cd
+        ring = self.ybuf[:, n:].view(len(self.rec), n, 3, -1)
+        ring[:, :, 0, :cd] = ring[:, :, 1, :cd].clone()
+        ring[:, :, 1, :cd] = ring[:, :, 2, :cd].clone()
+        ring[:, :, 2, :cd] = self.ybuf[:, :n, :cd]
+
+    def _attend_q(self, i, q, k, v):
+        G, Q = self.G, self.Q
+        cfg = self.stack.cfg
+        h, D = cfg.kv_heads, cfg.head_dim
+        self.gk[i].index_copy_(2, self.step_t, k.reshape(G, Q, 1, h, D))
+        self.gv[i].index_copy_(2, self.step_t, v.reshape(G, Q, 1, h, D))
+        out = ops.x_attention(
+            q.view(G, Q, cfg.heads, D), self.kp[i], self.vp[i], self.pos_p[i], self.kt[i], self.vt[i], self.pos_t, self.own_t, self.gk[i],
+            self.gv[i], self.qpos, self.step32, self.beam, self.scaling, None, None, workspace=self.workspace,
+        )
+        return out.view(G * Q, cfg.heads, D)
+
+    def _recur(self, i, y):
+        """a recurrent layer inside a step: the step's in-projection rows next to the rings, the fused steps before the recurrence
+        through the tap table, the new rows into the caches, the recurrence from the prefix state over every slot's rows; the
+        outputs of the step's own rows come back"""
+        from spinf_serve_b200 import gdn
+
+        cfg, L = self.stack.cfg, self.stack.w.layers[i]
+        x, n = self.rec_pos[i], self.n
+        yb = self.ybuf[x]
+        yb[:n].copy_(y)
+        q, k, v, z, g, beta = gdn.prologue(yb, self.conv_idx, L["conv_w"], L["A_log"], L["dt_bias"], cfg.hk, cfg.dk, cfg.hv, cfg.dv, n_tokens=n)
+        self.cq[x].index_copy_(0, self.cur_rows, q)
+        self.ck[x].index_copy_(0, self.cur_rows, k)
+        self.cv[x].index_copy_(0, self.cur_rows, v)
+        self.cg[x].index_copy_(0, self.cur_rows, g)
+        self.cb[x].index_copy_(0, self.cur_rows, beta)
+        gdn.recurrent(self.cq[x], self.ck[x], self.cv[x], self.cg[x], self.cb[x], cfg.dk**-0.5, self.cu_buf, n, h0=self.h0[x], h0_idx=self.h0_idx,
+                      idx=self.idx_buf, o=self.o_buf)
+        return self.o_buf.index_select(0, self.cur_rows), z
+
+    def _step_once(self):
+        inputs = {"ids": self.tok_buf.reshape(1, -1), "pos": self.qpos.reshape(1, -1)}
+        return self.stack.forward(None, None, inputs, None, attend=self._attend_q, recur=self._recur).reshape(self.G, self.Q, -1)
+
+    def reorder(self, parent) -> None:
+        """as Decoder.reorder, plus the generated rows of the recurrent caches and the conv rings (qwen_decode.Decoder._reorder)"""
+        super().reorder(parent)
+        n, S = self.n, self.S
+        for t in (self.cq, self.ck, self.cv, self.cg, self.cb):
+            for x in range(t.shape[0]):  # layer by layer: the gather's temporary is one layer's rows
+                gen = t[x, self.gen0 :].view(n, S, *t.shape[2:])
+                gen.copy_(gen[parent])
+        ring = self.ybuf[:, n:].view(len(self.rec), n, 3, -1)
+        ring.copy_(ring[:, parent])
 
 
 def search_text(dec: Decoder, lm_weight, stop_ids, banned_ids=(), topk: int | None = None, min_p: float = 0.002, softcap=None):

@@ -9,6 +9,7 @@ the stream layout, on library kernels only. Per layer (qwen.py:718-734):
         -> sigmoid gate -> int4 out-projection
 The plan of the recurrent layers (segments, levels, conv taps) is built on the host ahead of the GPU (gdn_plan.tree_plan)."""
 
+from contextlib import contextmanager
 from dataclasses import dataclass, field
 
 import torch
@@ -134,6 +135,7 @@ class QwenStack:
         self.compact, self.min_stream, self.align_jobs = compact, min_stream, align_jobs
         R = self.cfg.rotary
         self.inv_freq = (1.0 / (self.cfg.theta ** (torch.arange(0, R, 2, dtype=torch.float32) / R))).to(weights.embed.device)
+        self._cap = None  # capture() sets the ranges and the dicts the forward fills
 
     def compact_rows(self, b) -> int | None:
         """the rows the model runs on: the real tokens in whole blocks, at least the GEMM floor for aligned jobs, never more than the
@@ -147,6 +149,58 @@ class QwenStack:
         return min(b.length, max((R + BLOCK - 1) // BLOCK * BLOCK, floor))
 
     window = None  # every attention layer of the family is full attention
+
+    # ---- capture for the extraction decoder (Qwen35Stack.capture, spinf_serve/models/qwen35/qwen.py, and what qwen_decode.Decoder
+    # reads of it, qwen_decode.py:70-166): per attention layer the K/V of every owner's prefix and of every template branch; per
+    # recurrent layer the prefix's final state, the templates' q k v g beta rows and the pre-convolution rows of the last three
+    # tokens on the path to each template's end (the decoder's conv ring)
+    @contextmanager
+    def capture(self, sc, b, xo: list):
+        """around the forward of a batch whose owners `xo` have extraction branches -> {"kv": {key: {layer: (k, v)}}, "extra":
+        {"state": {key: {layer: S [Hv, K, V] fp32}}, "tok": {key: {layer: (q, k, v, g, beta)}}, "pre": {key: {layer: [3, conv
+        dim]}}}, "pos0": None}; keys ("p", id(owner)) for prefixes, ("t", prompt key) for templates"""
+        import numpy as np
+
+        real = b.art >= 0
+        to_row = (np.cumsum(real) - 1) if self.compact_rows(b) is not None else np.arange(b.length)
+        pre = [(int(to_row[o.start]), o.prefix_len, ("p", id(o))) for o in xo]
+        tmpl = [(int(to_row[bs]), bl, ("t", pr.key)) for o in xo for bs, bl, pr in o.xbranches]
+        cap = {"prefixes": pre, "templates": tmpl, "kv": {}, "state": {}, "tok": {}, "pre": {}}
+        self._cap = cap
+        try:
+            yield {"kv": cap["kv"], "extra": {"state": cap["state"], "tok": cap["tok"], "pre": cap["pre"]}, "pos0": None}
+        finally:
+            self._cap = None
+
+    def abandon(self, sc) -> None:
+        self._cap = None
+
+    def kv_bytes_per_token(self) -> dict:
+        return {i: 2 * self.cfg.kv_heads * self.cfg.head_dim * 2 for i in range(self.n_layers) if self.w.layers[i]["kind"] != "linear_attention"}
+
+    def _capture_recurrent(self, i, y, q, k, v, g, beta, plan):
+        cap, cfg = self._cap, self.cfg
+        cd = 2 * cfg.hk * cfg.dk + cfg.hv * cfg.dv
+        dev = y.device
+        if cap["prefixes"]:
+            # the prefixes' final states: the chunked recurrence once more over the prefix rows alone (only batches with
+            # extraction branches pay for it)
+            lens = [n for _, n, _ in cap["prefixes"]]
+            cu_cpu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int64)
+            idx = torch.cat([torch.arange(r0, r0 + n, dtype=torch.int64) for r0, n, _ in cap["prefixes"]]).to(dev)
+            ht = torch.empty((len(lens), cfg.hv, cfg.dk, cfg.dv), dtype=torch.float32, device=dev)
+            scratch = torch.empty((1, q.shape[0], cfg.hv, cfg.dv), dtype=torch.bfloat16, device=dev)
+            gdn.chunked(q, k, v, g, beta, cfg.dk**-0.5, cu_cpu.to(dev), cu_cpu, ht=ht, ht_idx=torch.arange(len(lens), dtype=torch.int64, device=dev),
+                        idx=idx, o=scratch)
+            for j, (_, _, key) in enumerate(cap["prefixes"]):
+                cap["state"].setdefault(key, {})[i] = ht[j]
+        n_rows = y.shape[0]
+        for r0, n, key in cap["templates"]:
+            sl = slice(r0, r0 + n)
+            cap["tok"].setdefault(key, {})[i] = (q[sl].clone(), k[sl].clone(), v[sl].clone(), g[sl].clone(), beta[sl].clone())
+            taps = plan.conv[r0 + n - 1, 1:4]  # the path's last three tokens, the template's end among them
+            ok = (taps >= 0) & (taps < n_rows)
+            cap["pre"].setdefault(key, {})[i] = y[taps.clamp(0, n_rows - 1), :cd] * ok[:, None].to(y.dtype)
 
     def plan(self, sc, b) -> None:
         """the host half of the recurrent layers' plan, ahead of the GPU (the packing thread; Qwen35Stack.plan, qwen.py:1056): the
@@ -178,15 +232,18 @@ class QwenStack:
             raise RuntimeError("compact rows: the batch was staged without its plan (call stack.plan(sc, b) before staging)")
         return {"ids": st["compact.ids"][None], "pos": st["compact.pos"][None], "plan": plan, "n": b.length, "to_row": st["compact.to_row"]}
 
-    def forward(self, sc, b, inputs: dict, masks: dict, rows=None, taps=None):
+    def forward(self, sc, b, inputs: dict, masks: dict, rows=None, taps=None, attend=None, recur=None):
         """packed forward (Stack.forward, base.py:62-64) -> final hidden states after the last norm, [1, stream length, hidden] bf16
         in the stream layout. Beyond the reference's signature: rows (stream positions) returns only those rows, [len(rows),
-        hidden]; taps: optional dict filled with the residual stream per layer, in the stream layout (tests)"""
+        hidden]; taps: optional dict filled with the residual stream per layer, in the stream layout (tests); attend(layer, q, k, v)
+        -> [n, H, D] and recur(layer, y) -> (o, z) stand in for the tree attention and the recurrence over the plan in a decoding
+        step (decode.HybridDecoder): masks and inputs["plan"] are unused then"""
         cfg, w = self.cfg, self.w
-        ids, pos, mask, plan = inputs["ids"].reshape(-1), inputs["pos"].reshape(-1), masks["full_attention"], inputs["plan"]
+        ids, pos, plan = inputs["ids"].reshape(-1), inputs["pos"].reshape(-1), inputs.get("plan")
+        mask = masks["full_attention"] if masks is not None else None
         n = ids.numel()          # rows the layers run on
-        T = inputs["n"]          # stream length (the attention's layout)
-        sidx = plan.sidx if plan.rows is not None else None
+        T = inputs.get("n", n)   # stream length (the attention's layout)
+        sidx = plan.sidx if plan is not None and plan.rows is not None else None
         R = sidx.numel() if sidx is not None else n
         H, K, D = cfg.heads, cfg.kv_heads, cfg.head_dim
         cos, sin = ops.rope_table(pos, self.inv_freq)
@@ -204,15 +261,25 @@ class QwenStack:
             L = w.layers[i]
             if L["kind"] == "linear_attention":
                 y = L["in_proj"](h)
-                q, k, v, z, g, beta = gdn.prologue(y, plan.conv, L["conv_w"], L["A_log"], L["dt_bias"], cfg.hk, cfg.dk, cfg.hv, cfg.dv)
-                o = gdn.gdn_tree(q, k, v, g, beta, plan)
+                if recur is not None:
+                    o, z = recur(i, y)
+                else:
+                    q, k, v, z, g, beta = gdn.prologue(y, plan.conv, L["conv_w"], L["A_log"], L["dt_bias"], cfg.hk, cfg.dk, cfg.hv, cfg.dv)
+                    o = gdn.gdn_tree(q, k, v, g, beta, plan)
+                    if self._cap is not None:
+                        self._capture_recurrent(i, y, q, k, v, g, beta, plan)
                 m = L["out_proj"](gdn.epilogue(o, z, L["gdn_norm"], cfg.eps))
             else:
                 y = L["qkv_proj"](h)
                 q = ops.qkv_norm_rope_gated(y, H, K, D, L["q_norm"], L["k_norm"], cos, sin, cfg.eps, plus1=True)
                 kk = y[:, 2 * H * D : (2 * H + K) * D].view(n, K, D)
                 vv = y[:, (2 * H + K) * D :].view(n, K, D)
-                if sidx is None:
+                if self._cap is not None:
+                    for r0, cnt, key in self._cap["prefixes"] + self._cap["templates"]:
+                        self._cap["kv"].setdefault(key, {})[i] = (kk[r0 : r0 + cnt].clone(), vv[r0 : r0 + cnt].clone())
+                if attend is not None:
+                    o = attend(i, q, kk, vv)
+                elif sidx is None:
                     o = attention.tree_attention(q, kk, vv, mask, D**-0.5)
                 else:  # the real rows scattered into the stream layout for the attention, its output gathered back (qwen.py:605-623)
                     o_s = attention.tree_attention(to_stream(q), to_stream(kk), to_stream(vv), mask, D**-0.5)
