@@ -362,7 +362,7 @@ int spinf_gdn_tree_scan_tc(const void* q, const void* k, void* o, int64_t n_rows
  *   qpos [G, Q] int32 the queries' positions; window > 0 also hides keys with qpos - pos >= window (sliding layers)
  * Rounding points as the reference: scores rounded to bf16 before scaling, soft cap (0: none) and mask; softmax in fp32 over the
  * three ranges together; probabilities rounded to bf16; each range's value product rounded to bf16, the three added in fp32. */
-int64_t spinf_x_attention_workspace_bytes(int64_t G, int64_t Q, int64_t H, int64_t Lp, int64_t Tt, int64_t S);
+int64_t spinf_x_attention_workspace_bytes(int64_t G, int64_t Q, int64_t H, int64_t D, int64_t Lp, int64_t Tt, int64_t S);
 int spinf_x_attention(const void* q, int64_t q_pitch, const void* kp, const void* vp, const int32_t* pos_p, int64_t Lp,
                       const void* kt, const void* vt, const int32_t* pos_t, const int32_t* own_t, int64_t Tt, const void* gk,
                       const void* gv, int64_t S, const int32_t* qpos, const int32_t* step, int64_t G, int64_t Q, int64_t H, int64_t h,

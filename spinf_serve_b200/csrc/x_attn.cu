@@ -6,15 +6,18 @@
 // The reference's rounding points are kept, so the product can be checked element by element: scores are bf16 products with fp32
 // accumulation rounded to bf16, then scaling / soft cap / mask / softmax in fp32 over the three ranges together, the
 // probabilities rounded to bf16, each range's value product rounded to bf16 and the three added in fp32. That forces the softmax
-// to be complete before any value product starts, hence three launches:
+// to be complete before any value product starts, hence separate launches:
 //   x_scores  (key tile of 64 | the generated range) x kv head x group : S = Q K^T on mma.sync, masked scores -> fp32 workspace
 //   x_softmax one row per CTA                                          : probabilities -> bf16 workspace
-//   x_values  64 output dims x kv head x group                         : P V per range on mma.sync, generated range on FMA
+//   x_values  (64 output dims x key-range part) x kv head x group      : P V per range on mma.sync, generated range on FMA -> fp32 parts
+//   x_combine                                                          : the parts rounded and added as the reference adds them
 // Each range is padded to a multiple of 64 columns in the workspace so every tile row starts 16-byte aligned. A decoding step is
 // bound by reading the prefix K / V once per layer; these kernels read it once per (kv head, 64-dim slice) from L2.
 #include "gdn_mma.cuh"
 #include "host_util.h"
 
+#include <algorithm>
+#include <climits>
 #include <atomic>
 
 namespace spinf {
@@ -37,6 +40,8 @@ struct XAttnArgs {
   int Lp64, Tt64, S64, pitch;  // padded range widths and the workspace row pitch (their sum)
   float* scores;
   __nv_bfloat16* probs;
+  float* part;   // [n_split + 2][G * H * Q][D] fp32: prefix partial sums per split, then the template's and the generated range's products
+  int n_split;
   __nv_bfloat16* out;
   int64_t out_pitch;
 };
@@ -84,7 +89,8 @@ __global__ void __launch_bounds__(128) x_scores_kernel(const XAttnArgs a) {
         if (lane + j * 32 < vec) qv[j] = *reinterpret_cast<const uint4*>(qr + (lane + j * 32) * 8);
       float* const dst = a.scores + x_ws_row(a, g, hk, r, q * r + rr) + a.Lp64 + a.Tt64;
       const __nv_bfloat16* const kbase = a.gk + (((static_cast<int64_t>(g) * a.Q + q) * a.S) * a.h + hk) * a.D;
-      for (int s0 = 0; s0 < a.S64; s0 += 4) {
+      for (int s = n_live + lane; s < a.S64; s += 32) dst[s] = X_NINF;  // tokens not written yet, and the padding columns
+      for (int s0 = 0; s0 < n_live; s0 += 4) {
         uint4 kv[4][2] = {};
 #pragma unroll
         for (int u = 0; u < 4; ++u)
@@ -108,7 +114,7 @@ __global__ void __launch_bounds__(128) x_scores_kernel(const XAttnArgs a) {
             }
           }
           for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-          if (lane == u) dst[s0 + u] = s0 + u < n_live ? x_finish_score(acc, a.scale, a.softcap) : X_NINF;
+          if (lane == u && s0 + u < n_live) dst[s0 + u] = x_finish_score(acc, a.scale, a.softcap);
         }
       }
     }
@@ -131,6 +137,15 @@ __global__ void __launch_bounds__(128) x_scores_kernel(const XAttnArgs a) {
   }
   cp_async_commit();
   const int gq = lane >> 2, tq = lane & 3;
+  // the tile's key positions and owners once per CTA (position INT_MIN: a key nobody sees)
+  __shared__ int32_t kp_s[XT], ko_s[XT];
+  if (tid < XT) {
+    const int key = k0 + tid;
+    const bool in = key < L;
+    const int kp = in ? kpos[key] : 0;
+    kp_s[tid] = in && (!prefix || kp >= 0) ? kp : INT_MIN;
+    ko_s[tid] = in && !prefix ? kown[key] : -1;
+  }
   for (int m0 = 0; m0 < R; m0 += XT) {
     __syncthreads();  // the previous pass has read qs
     for (int i = tid; i < XT * vec; i += 128) {
@@ -163,17 +178,16 @@ __global__ void __launch_bounds__(128) x_scores_kernel(const XAttnArgs a) {
         float* const dst = a.scores + x_ws_row(a, g, hk, r, m) + col0;
 #pragma unroll
         for (int n = 0; n < 8; ++n) {
+          float2 out;
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const int c = n * 8 + tq * 2 + e, key = k0 + c;
-            bool vis = key < L;
-            if (vis) {
-              const int kp = kpos[key];
-              vis = prefix ? kp >= 0 : kown[key] == mine;
-              if (a.window > 0) vis = vis && (qp - kp) < a.window;
-            }
-            dst[c] = vis ? x_finish_score(acc[n][half * 2 + e], a.scale, a.softcap) : X_NINF;
+            const int c = n * 8 + tq * 2 + e;
+            const int kp = kp_s[c];
+            bool vis = kp != INT_MIN && (prefix || ko_s[c] == mine);
+            if (a.window > 0) vis = vis && (qp - kp) < a.window;
+            (e ? out.y : out.x) = vis ? x_finish_score(acc[n][half * 2 + e], a.scale, a.softcap) : X_NINF;
           }
+          *reinterpret_cast<float2*>(dst + n * 8 + tq * 2) = out;
         }
       }
     }
@@ -219,23 +233,30 @@ __global__ void __launch_bounds__(128) x_softmax_kernel(const XAttnArgs a) {
   for (int i = tid + CACHE * 128; i < a.pitch; i += 128) p[i] = __float2bfloat16_rn(expf(s[i] - m) / sum);
 }
 
-// dynamic shared memory, two stages of: [XT][XT + 8] probabilities, [XT][XT + 8] values (keys x 64 dims of this CTA)
+// dynamic shared memory, two stages of: [XT][XT + 8] probabilities, [XT][XT + 8] values (keys x 64 dims of this CTA).
+// blockIdx.x = dims slice * (n_split + 1) + part: parts 0 .. n_split - 1 take a run of the prefix's key tiles each (fp32 partial sums,
+// added in split order by x_combine), part n_split takes the templates and the generated range.
 __global__ void __launch_bounds__(128) x_values_kernel(const XAttnArgs a) {
   extern __shared__ __align__(16) uint8_t xv_raw[];
   constexpr int ld = XT + 8;
   constexpr int STAGE = 2 * XT * ld;  // elements
   __nv_bfloat16* const sm = reinterpret_cast<__nv_bfloat16*>(xv_raw);
-  const int d0 = blockIdx.x * XT, hk = blockIdx.y, g = blockIdx.z;
+  const int parts = a.n_split + 1;
+  const int d0 = (blockIdx.x / parts) * XT, part = blockIdx.x % parts, hk = blockIdx.y, g = blockIdx.z;
   const int r = a.H / a.h, R = a.Q * r;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int gq = lane >> 2, tq = lane & 3;
   const int step = *a.step;
-  const int np = a.Lp64 / XT, n_tiles = np + a.Tt64 / XT;
+  const int np = a.Lp64 / XT;
+  const bool pre = part < a.n_split;
+  const int t_beg = pre ? static_cast<int>(static_cast<int64_t>(np) * part / a.n_split) : 0;
+  const int t_end = pre ? static_cast<int>(static_cast<int64_t>(np) * (part + 1) / a.n_split) : a.Tt64 / XT;
+  const int L = pre ? a.Lp : a.Tt, col0 = pre ? 0 : a.Lp64;
+  const __nv_bfloat16* const vbase = pre ? a.vp : a.vt;
+  const int64_t slab = static_cast<int64_t>(a.G) * a.H * a.Q * a.D;
   for (int m0 = 0; m0 < R; m0 += XT) {
     auto stage = [&](int tile, int buf) {
-      const bool pre = tile < np;
-      const int L = pre ? a.Lp : a.Tt, k0 = (pre ? tile : tile - np) * XT, col0 = pre ? 0 : a.Lp64;
-      const __nv_bfloat16* const vbase = pre ? a.vp : a.vt;
+      const int k0 = tile * XT;
       __nv_bfloat16* const ps = sm + buf * STAGE;
       __nv_bfloat16* const vs = ps + XT * ld;
       for (int i = tid; i < XT * 8; i += 128) {
@@ -247,17 +268,17 @@ __global__ void __launch_bounds__(128) x_values_kernel(const XAttnArgs a) {
         cp_async16(vs + t * ld + c * 8, okv ? p : vbase, okv ? 16 : 0);
       }
     };
-    float total[8][4] = {};
     float acc[8][4] = {};
     __syncthreads();  // the previous pass has read both stages
-    if (n_tiles > 0) stage(0, 0);
+    if (t_beg < t_end) stage(t_beg, 0);
     cp_async_commit();
-    for (int tile = 0; tile < n_tiles; ++tile) {
-      if (tile + 1 < n_tiles) stage(tile + 1, (tile + 1) & 1);
+    for (int tile = t_beg; tile < t_end; ++tile) {
+      const int buf = (tile - t_beg) & 1;
+      if (tile + 1 < t_end) stage(tile + 1, buf ^ 1);
       cp_async_commit();
       cp_async_wait<1>();
       __syncthreads();
-      const __nv_bfloat16* const ps = sm + (tile & 1) * STAGE;
+      const __nv_bfloat16* const ps = sm + buf * STAGE;
       const __nv_bfloat16* const vs = ps + XT * ld;
       if (m0 + warp * 16 < R) {
 #pragma unroll
@@ -273,26 +294,22 @@ __global__ void __launch_bounds__(128) x_values_kernel(const XAttnArgs a) {
           }
         }
       }
-      if (tile == np - 1 || tile == n_tiles - 1) {  // a range is complete: its product is rounded to bf16 on its own
-#pragma unroll
-        for (int n = 0; n < 8; ++n)
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            total[n][e] += x_round_bf16(acc[n][e]);
-            acc[n][e] = 0.f;
-          }
-      }
       __syncthreads();  // this stage is free for the tile after the next
     }
-    // the generated range: a row's own slot's tokens 0..step, on the FMA pipe for exactly the elements this thread holds
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       const int m = m0 + warp * 16 + gq + half * 8;
       if (m >= R) continue;
       const int q = m / r;
+      // the row of this (group, head, slot) in a slab of the partial buffer
+      float* const dst = a.part + ((static_cast<int64_t>(g) * a.H + hk * r + m % r) * a.Q + q) * a.D + d0 + tq * 2;
+#pragma unroll
+      for (int n = 0; n < 8; ++n) *reinterpret_cast<float2*>(dst + static_cast<int64_t>(part) * slab + n * 8) = make_float2(acc[n][half * 2], acc[n][half * 2 + 1]);
+      if (pre) continue;
+      // the generated range: the slot's own tokens 0..step, on the FMA pipe for exactly the elements this thread holds
       const __nv_bfloat16* const pr = a.probs + x_ws_row(a, g, hk, r, m) + a.Lp64 + a.Tt64;
       const __nv_bfloat16* const vr = a.gv + ((static_cast<int64_t>(g) * a.Q + q) * a.S * a.h + hk) * a.D + d0 + tq * 2;
-      float acc[8][2] = {};
+      float ag[8][2] = {};
       const int n_live = min(step + 1, a.S);
       for (int s = 0; s < n_live; ++s) {
         const float p = __bfloat162float(pr[s]);
@@ -300,21 +317,38 @@ __global__ void __launch_bounds__(128) x_values_kernel(const XAttnArgs a) {
 #pragma unroll
         for (int n = 0; n < 8; ++n) {
           const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(v + n * 8));
-          acc[n][0] = fmaf(p, f.x, acc[n][0]);
-          acc[n][1] = fmaf(p, f.y, acc[n][1]);
+          ag[n][0] = fmaf(p, f.x, ag[n][0]);
+          ag[n][1] = fmaf(p, f.y, ag[n][1]);
         }
       }
-      __nv_bfloat16* const dst = a.out + (static_cast<int64_t>(g) * a.Q + q) * a.out_pitch + static_cast<int64_t>(hk * r + m % r) * a.D + d0 + tq * 2;
 #pragma unroll
-      for (int n = 0; n < 8; ++n) {
-        const float x = total[n][half * 2] + x_round_bf16(acc[n][0]);
-        const float y = total[n][half * 2 + 1] + x_round_bf16(acc[n][1]);
-        *reinterpret_cast<__nv_bfloat162*>(dst + n * 8) = __floats2bfloat162_rn(x, y);
-      }
+      for (int n = 0; n < 8; ++n) *reinterpret_cast<float2*>(dst + static_cast<int64_t>(part + 1) * slab + n * 8) = make_float2(ag[n][0], ag[n][1]);
     }
   }
 }
 
+// out = bf16( (bf16(sum of the prefix's partial sums, in split order) + bf16(templates)) + bf16(generated) ), the reference's three
+// products rounded one by one and added in fp32 in its order
+__global__ void x_combine_kernel(const XAttnArgs a) {
+  const int64_t rows = static_cast<int64_t>(a.G) * a.H * a.Q, slab = rows * a.D;
+  const int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 2;
+  if (i >= slab) return;
+  float2 p = *reinterpret_cast<const float2*>(a.part + i);
+  for (int sp = 1; sp < a.n_split; ++sp) {
+    const float2 t = *reinterpret_cast<const float2*>(a.part + sp * slab + i);
+    p.x += t.x, p.y += t.y;
+  }
+  const float2 t = *reinterpret_cast<const float2*>(a.part + a.n_split * slab + i);
+  const float2 gn = *reinterpret_cast<const float2*>(a.part + (a.n_split + 1) * slab + i);
+  const float x = (x_round_bf16(p.x) + x_round_bf16(t.x)) + x_round_bf16(gn.x);
+  const float y = (x_round_bf16(p.y) + x_round_bf16(t.y)) + x_round_bf16(gn.y);
+  const int64_t row = i / a.D;  // (g * H + head) * Q + q
+  const int d = static_cast<int>(i % a.D);
+  const int q = static_cast<int>(row % a.Q), head = static_cast<int>((row / a.Q) % a.H), g = static_cast<int>(row / (static_cast<int64_t>(a.Q) * a.H));
+  *reinterpret_cast<__nv_bfloat162*>(a.out + (static_cast<int64_t>(g) * a.Q + q) * a.out_pitch + static_cast<int64_t>(head) * a.D + d) = __floats2bfloat162_rn(x, y);
+}
+
+static constexpr int X_MAX_SPLIT = 8;
 static int pad64(int64_t n) { return static_cast<int>((n + XT - 1) / XT * XT); }
 
 }  // namespace spinf
@@ -322,11 +356,16 @@ static int pad64(int64_t n) { return static_cast<int>((n + XT - 1) / XT * XT); }
 using namespace spinf;
 
 // bytes of the workspace spinf_x_attention needs: fp32 scores and bf16 probabilities, one row per (group, query head, slot), each
-// of the three key ranges padded to a multiple of 64 columns
-extern "C" int64_t spinf_x_attention_workspace_bytes(int64_t G, int64_t Q, int64_t H, int64_t Lp, int64_t Tt, int64_t S) {
-  if (G <= 0 || Q <= 0 || H <= 0 || Lp < 0 || Tt < 0 || S <= 0) return 0;
+// of the three key ranges padded to a multiple of 64 columns; then the fp32 partial products of the value kernel's parts
+static int x_splits(int64_t Lp) {
+  const int np = pad64(Lp) / XT;
+  return std::max(1, std::min(X_MAX_SPLIT, (np + 5) / 6));  // about six key tiles of the prefix per CTA
+}
+
+extern "C" int64_t spinf_x_attention_workspace_bytes(int64_t G, int64_t Q, int64_t H, int64_t D, int64_t Lp, int64_t Tt, int64_t S) {
+  if (G <= 0 || Q <= 0 || H <= 0 || D <= 0 || Lp < 0 || Tt < 0 || S <= 0) return 0;
   const int64_t pitch = pad64(Lp) + pad64(Tt) + pad64(S);
-  return G * H * Q * pitch * 6 + 256;
+  return G * H * Q * (pitch * 6 + (x_splits(Lp) + 2) * D * 4) + 256;
 }
 
 extern "C" int spinf_x_attention(const void* q, int64_t q_pitch, const void* kp, const void* vp, const int32_t* pos_p, int64_t Lp,
@@ -338,7 +377,7 @@ extern "C" int spinf_x_attention(const void* q, int64_t q_pitch, const void* kp,
   SPINF_CHECK_ARG(q && gk && gv && qpos && step && out && workspace && G > 0 && Q > 0 && H > 0 && h > 0 && H % h == 0 && S > 0);
   SPINF_CHECK_ARG(D >= 64 && D <= 512 && D % 64 == 0 && beam > 0 && window >= 0 && Lp >= 0 && Tt >= 0 && q_pitch % 8 == 0 && out_pitch % 2 == 0);
   SPINF_CHECK_ARG((Lp == 0 || (kp && vp && pos_p)) && (Tt == 0 || (kt && vt && pos_t && own_t)) && G < 65536 && h < 65536);
-  SPINF_CHECK_ARG(workspace_bytes >= spinf_x_attention_workspace_bytes(G, Q, H, Lp, Tt, S));
+  SPINF_CHECK_ARG(workspace_bytes >= spinf_x_attention_workspace_bytes(G, Q, H, D, Lp, Tt, S));
   XAttnArgs a;
   a.q = static_cast<const __nv_bfloat16*>(q);
   a.q_pitch = q_pitch;
@@ -362,6 +401,8 @@ extern "C" int spinf_x_attention(const void* q, int64_t q_pitch, const void* kp,
   ws += (256 - reinterpret_cast<uintptr_t>(ws) % 256) % 256;
   a.scores = reinterpret_cast<float*>(ws);
   a.probs = reinterpret_cast<__nv_bfloat16*>(ws + rows * a.pitch * 4);
+  a.part = reinterpret_cast<float*>(ws + rows * a.pitch * 6);
+  a.n_split = x_splits(Lp);
   a.out = static_cast<__nv_bfloat16*>(out);
   a.out_pitch = out_pitch;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -377,7 +418,9 @@ extern "C" int spinf_x_attention(const void* q, int64_t q_pitch, const void* kp,
   SPINF_CUDA_OK(cudaGetLastError());
   x_softmax_kernel<<<static_cast<unsigned>(rows), 128, 0, st>>>(a);
   SPINF_CUDA_OK(cudaGetLastError());
-  x_values_kernel<<<dim3(static_cast<unsigned>(D / XT), static_cast<unsigned>(h), static_cast<unsigned>(G)), 128, smem_v, st>>>(a);
+  x_values_kernel<<<dim3(static_cast<unsigned>(D / XT * (a.n_split + 1)), static_cast<unsigned>(h), static_cast<unsigned>(G)), 128, smem_v, st>>>(a);
+  SPINF_CUDA_OK(cudaGetLastError());
+  x_combine_kernel<<<static_cast<unsigned>((rows * D / 2 + 255) / 256), 256, 0, st>>>(a);
   SPINF_CUDA_OK(cudaGetLastError());
   return 0;
 }

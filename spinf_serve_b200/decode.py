@@ -113,7 +113,7 @@ class Decoder:
         self.tok_buf = torch.full((G, Q), PAD_TOKEN, dtype=torch.int64, device=device)
         self.step_t = torch.zeros(1, dtype=torch.int64, device=device)
         self.step32 = torch.zeros(1, dtype=torch.int32, device=device)
-        need = int(ops._lib.lib().spinf_x_attention_workspace_bytes(G, Q, cfg.heads, max(k.shape[1] for k in self.kp.values()), Tt, S))
+        need = int(ops._lib.lib().spinf_x_attention_workspace_bytes(G, Q, cfg.heads, D, max(k.shape[1] for k in self.kp.values()), Tt, S))
         self.workspace = torch.empty(need, dtype=torch.uint8, device=device)
         self.step = 0
         self.graph, self.h_out = None, None

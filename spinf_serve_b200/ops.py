@@ -275,7 +275,7 @@ def x_attention(q, kp, vp, pos_p, kt, vt, pos_t, own_t, gk, gv, qpos, step, beam
         raise SpinfError("x_attention: position / owner shapes do not agree")
     if out is None:
         out = torch.empty((G, Q, H, D), dtype=torch.bfloat16, device=q.device)
-    need = int(_lib.lib().spinf_x_attention_workspace_bytes(G, Q, H, Lp, Tt, S))
+    need = int(_lib.lib().spinf_x_attention_workspace_bytes(G, Q, H, D, Lp, Tt, S))
     if workspace is None:
         workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
     check(
@@ -286,7 +286,7 @@ def x_attention(q, kp, vp, pos_p, kt, vt, pos_t, own_t, gk, gv, qpos, step, beam
         ),
         "spinf_x_attention",
     )
-    COUNTS["launches"] += 3
+    COUNTS["launches"] += 4
     return out
 
 
