@@ -556,12 +556,9 @@ extern "C" int spinf_int8_rowwise_gemm(const void* x8, const float* xs, const vo
   return launch_gemm<KIND_S8, BN>(tmA, tmB, make_shape(M, N, K, BN), epi, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int spinf_fp8_rowwise_gemm(const void* x8, const float* xs, const void* w8, const float* ws, void* y_bf16, int64_t M,
-                                      int64_t N, int64_t K, void* stream) {
-  if (M == 0) return 0;  // nothing to do: the row pointers may be null
-  SPINF_CHECK_ARG(x8 && xs && w8 && ws && y_bf16 && M >= 0 && N > 0 && K > 0 && K % 16 == 0 && N % 16 == 0);
-  SPINF_CHECK_ARG(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31));
-  constexpr int BN = 256;
+template <int BN>
+static int fp8_rowwise_gemm_bn(const void* x8, const float* xs, const void* w8, const float* ws, void* y_bf16, int64_t M, int64_t N, int64_t K,
+                               void* stream) {
   CUtensorMap tmA, tmB;
   EpiStoreBf16<BN, true> epi;
   int r;
@@ -571,6 +568,17 @@ extern "C" int spinf_fp8_rowwise_gemm(const void* x8, const float* xs, const voi
   epi.rowscale = xs;
   epi.colscale_g = ws;
   return launch_gemm<KIND_F8, BN>(tmA, tmB, make_shape(M, N, K, BN), epi, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int spinf_fp8_rowwise_gemm(const void* x8, const float* xs, const void* w8, const float* ws, void* y_bf16, int64_t M,
+                                      int64_t N, int64_t K, void* stream) {
+  if (M == 0) return 0;  // nothing to do: the row pointers may be null
+  SPINF_CHECK_ARG(x8 && xs && w8 && ws && y_bf16 && M >= 0 && N > 0 && K > 0 && K % 16 == 0 && N % 16 == 0);
+  SPINF_CHECK_ARG(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31));
+  // a decoding step's few rows: one row tile, so the column tiles are all the parallelism there is; narrower tiles put the weight
+  // stream on twice as many SMs (the same sums in the same order: a tile's width changes no element)
+  if (M <= 128 && N / 256 < sm_count()) return fp8_rowwise_gemm_bn<128>(x8, xs, w8, ws, y_bf16, M, N, K, stream);
+  return fp8_rowwise_gemm_bn<256>(x8, xs, w8, ws, y_bf16, M, N, K, stream);
 }
 
 extern "C" int spinf_abs_max(const void* x_bf16, int64_t n, float* out, void* stream) {
