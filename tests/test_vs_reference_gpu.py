@@ -3,7 +3,7 @@
 The reference package is installed (unmodified) under baseline/_ref by the build container; where it is absent every test here
 skips. Each test runs one reference operator exactly as the reference's modules call it, the library's counterpart on the same
 tensors, compares the results and times both sides with CUDA events (20 repeats after warm-up). The numbers are collected in
-gpurun_out/vs_reference.json (a scratch file; the committed summary is made from it). A reference operator that does not run on
+vs_reference.json in the run's scratch output folder (the committed summary is made from it). A reference operator that does not run on
 this GPU with the installed torch / triton / fla is recorded there as "reference GPU path unavailable on this box" with the error,
 and its test skips: nothing here retries or works around a failing reference kernel.
 
