@@ -230,3 +230,46 @@ def test_down_projection_shape_rows_and_exact_product(dev):
     err = (y[rows].cpu().double() - ref.double()).abs()
     assert bool((err <= 2.0**-7 * ref.double().abs() + 2.0**-14 * ref.double().abs().max()).all())
     assert torch.equal(ops.fp8_rowwise_gemm(x8[:1000].contiguous(), xs[:1000].contiguous(), w8, ws), y[:1000])
+
+
+def test_decoding_step_at_the_12b_shapes(dev):
+    """the extraction decoder at full width and depth: 4 groups x 1 500-token prefixes, 5 prompts x 6 beams, 48 layers; the step
+    replayed from its CUDA graph equals the step launched eagerly bit for bit, its outputs are finite, and its time is printed"""
+    import types
+
+    from spinf_serve_b200 import decode as D
+    from spinf_serve_b200.gemma_stack import CONFIGS, GemmaConfig, GemmaStack, GemmaWeights
+
+    cfg = GemmaConfig(**CONFIGS["gemma12b"])
+    stack = GemmaStack(GemmaWeights.random(cfg, seed=0, device=dev))
+    G, J, P, T, beam = 4, 5, 1500, 12, 6
+    gen = torch.Generator(device=dev).manual_seed(1)
+
+    def kv(n):
+        return tuple(torch.randn((n, cfg.kv_heads, cfg.head_dim), generator=gen, device=dev).to(torch.bfloat16) for _ in range(2))
+
+    proto = []
+    for gi in range(G):
+        pre = {li: kv(min(P, cfg.window - 1) if cfg.layer_types[li] == "sliding_attention" else P) for li in range(cfg.layers)}
+        proto.append((pre, [(types.SimpleNamespace(key=(gi, j), max_tokens=16), {li: kv(T) for li in range(cfg.layers)}) for j in range(J)]))
+    times, outs = {}, {}
+    for graphs in (False, True):
+        groups = [D.Group(dict(pre), P, [(p, dict(t), T, None) for p, t in prompts]) for pre, prompts in proto]
+        dec = D.Decoder(stack, groups, dev, beam=beam, graphs=graphs)
+        tok = torch.randint(5, 1000, (dec.G, dec.Q), generator=torch.Generator().manual_seed(2)).to(dev)
+        for s in range(3):
+            out = dec.forward(tok, s)
+        outs[graphs] = out.clone()
+        torch.cuda.synchronize()
+        ms = []
+        for s in range(3, 11):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            dec.forward(tok, s)
+            e1.record()
+            e1.synchronize()
+            ms.append(e0.elapsed_time(e1))
+        times[graphs] = sorted(ms)[len(ms) // 2]
+        del dec
+    print(f"decoding step, {G * J * beam} rows, {cfg.layers} layers: {times[True]:.2f} ms from its graph, {times[False]:.2f} ms launched eagerly")
+    assert torch.equal(outs[False], outs[True]) and bool(torch.isfinite(outs[True].float()).all())
