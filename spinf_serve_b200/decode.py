@@ -34,29 +34,31 @@ class Group:
     extra_bytes: int = 0
 
 
+def _stored_prefix(g: Group, layer) -> int:
+    """tokens of the group's prefix a layer keeps (a sliding layer's capture is already cut to its window)"""
+    kv = g.prefix_kv.get(layer)
+    return g.P if kv is None else kv[0].shape[0]
+
+
+def _padded_bytes(per_tok_kv: dict, n_groups: int, prefix_of, template_tokens: int, slots: int, steps: int) -> int:
+    """K/V bytes of a decoder holding, per layer, n_groups x (prefix + templates once, `steps` generated tokens per slot)"""
+    return sum(per_tok * n_groups * (prefix_of(layer) + template_tokens + slots * steps) for layer, per_tok in per_tok_kv.items())
+
+
 def group_bytes(g: Group, per_tok_kv: dict, S: int, beam: int = BEAM) -> int:
-    """the decoder's memory for one group (decode.group_bytes, :392-402): prefix and templates once, generated K/V per slot"""
-    J = len(g.prompts)
-    T = sum(t for _, _, t, _ in g.prompts)
-    total = g.extra_bytes
-    for li, per_tok in per_tok_kv.items():
-        lp = g.prefix_kv[li][0].shape[0] if g.prefix_kv.get(li) is not None else g.P
-        total += per_tok * (lp + T + J * beam * S)
-    return total
+    """the decoder's memory for one group alone (the quantity decode.group_bytes estimates, spinf_serve/decode.py:392-402):
+    per_tok_kv maps each layer with K/V to the bytes one token takes there; S generated tokens per slot"""
+    templates = sum(p[2] for p in g.prompts)
+    return g.extra_bytes + _padded_bytes(per_tok_kv, 1, lambda layer: _stored_prefix(g, layer), templates, len(g.prompts) * beam, S)
 
 
 def chunk_bytes(groups: list, per_tok_kv: dict, extra: int = 0, beam: int = BEAM) -> int:
-    """the decoder's memory for groups decoded together (decode.chunk_bytes, :378-391): every group is padded to the chunk's
-    largest prefix, template total, prompt count and token limit, so a chunk costs more than the sum of its groups"""
-    G = len(groups)
-    J = max(len(g.prompts) for g in groups)
-    S = max(p.max_tokens for g in groups for p, *_ in g.prompts) + 1
-    Tt = max(sum(T for _, _, T, _ in g.prompts) for g in groups)
-    total = extra
-    for li, per_tok in per_tok_kv.items():
-        Lp = max((g.prefix_kv[li][0].shape[0] if g.prefix_kv.get(li) is not None else g.P) for g in groups)
-        total += per_tok * G * (Lp + Tt + J * beam * S)
-    return total
+    """the decoder's memory for groups decoded together (decode.chunk_bytes, :378-391): Decoder pads every group to the chunk's
+    longest prefix, largest template total, most prompts and largest token limit, so a chunk costs more than its groups' sum"""
+    slots = beam * max(len(g.prompts) for g in groups)
+    steps = 1 + max(p[0].max_tokens for g in groups for p in g.prompts)
+    templates = max(sum(p[2] for p in g.prompts) for g in groups)
+    return extra + _padded_bytes(per_tok_kv, len(groups), lambda layer: max(_stored_prefix(g, layer) for g in groups), templates, slots, steps)
 
 
 class Decoder:
