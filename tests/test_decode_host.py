@@ -57,3 +57,56 @@ def test_memory_estimates_grow_with_padding():
     Sa, Sb = 17, 65
     assert D.chunk_bytes([a, b], per) > D.group_bytes(a, per, Sa) + D.group_bytes(b, per, Sb)
     assert D.group_bytes(a, per, Sa) == 64 * (100 + 12 + 2 * D.BEAM * 17) + 64 * (15 + 12 + 2 * D.BEAM * 17)
+
+
+def _fake_hybrid(beam=2):
+    """a two-layer stand-in for the hybrid stack (layer 0 recurrent, layer 1 attention) and two groups with CPU tensors: enough
+    for decode.HybridDecoder's constructor, its per-step tables and its beam reorder, none of which launch a kernel"""
+    from spinf_serve_b200 import decode as D
+
+    cfg = types.SimpleNamespace(heads=2, kv_heads=1, head_dim=64, hk=1, hv=2, dk=128, dv=128)
+    stack = types.SimpleNamespace(cfg=cfg, n_layers=2, w=types.SimpleNamespace(layers=[{"kind": "linear_attention"}, {"kind": "full_attention"}]))
+    cd = 2 * cfg.hk * cfg.dk + cfg.hv * cfg.dv
+    g = torch.Generator().manual_seed(0)
+    bf = torch.bfloat16
+    groups = []
+    for gi, (P, Ts) in enumerate(((9, (3, 2)), (5, (4,)))):
+        grp = D.Group({1: (torch.randn((P, 1, 64), generator=g).to(bf), torch.randn((P, 1, 64), generator=g).to(bf))}, P)
+        grp.extra = {"state": {0: torch.full((cfg.hv, cfg.dk, cfg.dv), float(gi + 1))}, "tmpl": []}
+        for j, T in enumerate(Ts):
+            grp.prompts.append((types.SimpleNamespace(key=(gi, j), max_tokens=3), {1: (torch.randn((T, 1, 64), generator=g).to(bf), torch.randn((T, 1, 64), generator=g).to(bf))}, T, None))
+            tok = (torch.full((T, cfg.hk, cfg.dk), 10.0 * gi + j).to(bf), torch.zeros((T, cfg.hk, cfg.dk), dtype=bf), torch.zeros((T, cfg.hv, cfg.dv), dtype=bf),
+                   torch.zeros((T, cfg.hv)), torch.zeros((T, cfg.hv), dtype=bf))
+            grp.extra["tmpl"].append({"tok": {0: tok}, "pre": {0: torch.full((3, cd), 100.0 * gi + j).to(bf)}})
+        groups.append(grp)
+    return D.HybridDecoder(stack, groups, "cpu", beam=beam), cd
+
+
+def test_hybrid_decoder_tables_and_reorder():
+    beam = 2
+    dec, cd = _fake_hybrid(beam)
+    n, S = dec.n, dec.S
+    assert (dec.G, dec.Q, S, n) == (2, 4, 4, 8) and dec.gen0 == 9 and dec.R == 9 + n * S
+    slot_T, slot_t0 = [3, 3, 2, 2, 4, 4, 0, 0], [0, 0, 3, 3, 5, 5, 0, 0]  # group 1 has one prompt: its last two slots are padding
+    for st in range(S):
+        cu = dec.cu_all[st].tolist()
+        assert cu[0] == 0 and [cu[s + 1] - cu[s] for s in range(n)] == [t + st + 1 for t in slot_T]
+        for s in range(n):
+            rows = dec.idx_all[st, cu[s] : cu[s + 1]].tolist()
+            assert rows == list(range(slot_t0[s], slot_t0[s] + slot_T[s])) + [dec.gen0 + s * S + k for k in range(st + 1)]
+    assert dec.h0_idx.tolist() == [0, 0, 0, 0, 1, 1, 1, 1] and float(dec.h0[0, 1, 0, 0, 0]) == 2.0
+    assert dec.conv_idx[3].tolist() == [n + 9, n + 10, n + 11, 3]
+    ring = dec.ybuf[0, n:].view(n, 3, -1)
+    assert float(ring[2, 0, 0]) == 1.0 and float(ring[4, 2, cd - 1]) == 100.0 and float(ring[6].abs().max()) == 0.0
+    assert float(dec.cq[0, 3, 0, 0]) == 1.0 and float(dec.cq[0, 5, 0, 0]) == 10.0  # template rows: prompt (0, 1) at 3.., (1, 0) at 5..
+    # a step's tables, then the beams: slot 1 takes slot 0's generated rows and ring, slot 5 takes slot 4's
+    dec._prepare(2)
+    assert dec.cur_rows.tolist() == [dec.gen0 + s * S + 2 for s in range(n)] and torch.equal(dec.idx_buf, dec.idx_all[2])
+    dec.cq[0, dec.gen0 : dec.gen0 + S] = 7.0
+    ring[0] = 5.0
+    dec.gk[1][0, 0] = 3.0
+    parent = torch.arange(n)
+    parent[1] = 0
+    dec.reorder(parent)
+    assert float(dec.cq[0, dec.gen0 + S, 0, 0]) == 7.0 and float(dec.ybuf[0, n:].view(n, 3, -1)[1, 1, 0]) == 5.0 and float(dec.gk[1][0, 1, 0, 0, 0]) == 3.0
+    assert float(dec.cq[0, dec.gen0 + 2 * S, 0, 0]) == 0.0
