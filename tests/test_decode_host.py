@@ -110,3 +110,27 @@ def test_hybrid_decoder_tables_and_reorder():
     dec.reorder(parent)
     assert float(dec.cq[0, dec.gen0 + S, 0, 0]) == 7.0 and float(dec.ybuf[0, n:].view(n, 3, -1)[1, 1, 0]) == 5.0 and float(dec.gk[1][0, 1, 0, 0, 0]) == 3.0
     assert float(dec.cq[0, dec.gen0 + 2 * S, 0, 0]) == 0.0
+
+
+def test_decoder_pads_groups_as_the_reference_s_does():
+    """Decoder.__init__ on CPU tensors: padded prefixes carry position -1, a sliding layer's stored tail keeps its true positions,
+    templates carry their owner, every slot starts right after its own template (decode.py:123-177)"""
+    from spinf_serve_b200 import decode as D
+
+    cfg = types.SimpleNamespace(heads=2, kv_heads=1, head_dim=64, window=8)
+    stack = types.SimpleNamespace(cfg=cfg, n_layers=2)
+    kv = lambda n: (torch.ones((n, 1, 64), dtype=torch.bfloat16), torch.ones((n, 1, 64), dtype=torch.bfloat16))  # noqa: E731
+    groups = []
+    for gi, (P, Ts) in enumerate(((20, (3, 2)), (5, (4,)))):
+        g = D.Group({0: kv(min(P, cfg.window - 1)), 1: kv(P)}, P)  # layer 0 sliding: the last window - 1 tokens
+        for j, T in enumerate(Ts):
+            g.prompts.append((types.SimpleNamespace(key=(gi, j), max_tokens=5), {0: kv(T), 1: kv(T)}, T, None))
+        groups.append(g)
+    dec = D.Decoder(stack, groups, "cpu", beam=2)
+    assert (dec.G, dec.Q, dec.S, dec.Tt) == (2, 4, 6, 5)
+    assert dec.pos_p[0][0].tolist() == list(range(13, 20)) and dec.pos_p[0][1].tolist() == [0, 1, 2, 3, 4, -1, -1]
+    assert dec.pos_p[1][1].tolist() == list(range(5)) + [-1] * 15 and float(dec.kp[1][1, 5:].abs().max()) == 0.0
+    assert dec.pos_t[0].tolist() == [20, 21, 22, 20, 21] and dec.own_t[0].tolist() == [0, 0, 0, 1, 1]
+    assert dec.pos_t[1].tolist() == [5, 6, 7, 8, -1] and dec.own_t[1].tolist() == [0, 0, 0, 0, -1]
+    assert dec.base.tolist() == [[23, 23, 22, 22], [9, 9, 0, 0]]
+    assert dec.gk[0].shape == (2, 4, 6, 1, 64) and groups[0].prefix_kv[0] is None  # the captures were let go
