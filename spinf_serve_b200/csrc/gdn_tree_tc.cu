@@ -256,11 +256,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gdn_tree_scan_tc_kernel(const G
           }
         }
       }
-      if (u + 1 < u_end) {
-        queue_copies(sm.st[(i & 1) ^ 1], mn.tok, mn.row, mn.c0);
-      } else {
-        cp_async_commit();
-      }
       // this unit's U row straight from the workspace (threads 0..63), ahead of the waits
       uint4 urow[16];
       if (t < 64 && m_tok >= 0) {
@@ -302,9 +297,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gdn_tree_scan_tc_kernel(const G
         fence_proxy_async_smem();
         mbar_arrive(&sm.s_ready);
       }
-      cp_async_wait<1>();  // this unit's tiles (queued a unit ago) have landed; the next unit's stay in flight
+      cp_async_wait<0>();  // this unit's tiles (queued a unit ago) have landed
       fence_proxy_async_smem();
       mbar_arrive(&sm.ld_full[i & 1]);
+      // the next unit's tiles into the other stage, after the state has gone out: the copy instructions are off the chain
+      // state -> product -> v' -> update that sets a trunk's time, and still a whole unit ahead of their use
+      if (u + 1 < u_end) queue_copies(sm.st[(i & 1) ^ 1], mn.tok, mn.row, mn.c0);
 
       if (!mbar_wait(wc, &sm.d1_done, (n_d1++) & 1u, ST_TIMEOUT_TMEM)) break;
       tc_fence_after();
