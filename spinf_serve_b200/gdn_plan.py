@@ -43,7 +43,7 @@ class TreePlan:
 
 UNIT_WORDS = 12
 UF_UPDATE, UF_PARENT = 1, 2
-LIGHT_UNITS = 8  # units per CTA in a group of read-only children
+LIGHT_UNITS = 16  # units per CTA in a group of read-only children
 
 
 @dataclass
