@@ -358,14 +358,17 @@ int spinf_gdn_tree_scan_tc(const void* q, const void* k, void* o, int64_t n_rows
  *   kt, vt [G, Tt, h, D]  the templates, pos_t their positions, own_t [G, Tt] the owning prompt (-1: padding): slot s attends to
  *                         the tokens of prompt s / beam only
  *   gk, gv [G, Q, S, h, D] the tokens generated by each slot's own beam: tokens 0 .. *step are attended (step: int32 on the device,
- *                         so that a captured launch can be replayed at the next step)
+ *                         so that a captured launch can be replayed at the next step). k_new, v_new (both or neither): the step's
+ *                         own K / V rows (row g * Q + slot of kv_pitch elements, head j at j * D), written into gk / gv at token
+ *                         *step before they are attended: GroupKV.update (decode.py:60-65) inside the same launch
  *   qpos [G, Q] int32 the queries' positions; window > 0 also hides keys with qpos - pos >= window (sliding layers)
  * Rounding points as the reference: scores rounded to bf16 before scaling, soft cap (0: none) and mask; softmax in fp32 over the
  * three ranges together; probabilities rounded to bf16; each range's value product rounded to bf16, the three added in fp32. */
 int64_t spinf_x_attention_workspace_bytes(int64_t G, int64_t Q, int64_t H, int64_t D, int64_t Lp, int64_t Tt, int64_t S);
 int spinf_x_attention(const void* q, int64_t q_pitch, const void* kp, const void* vp, const int32_t* pos_p, int64_t Lp,
-                      const void* kt, const void* vt, const int32_t* pos_t, const int32_t* own_t, int64_t Tt, const void* gk,
-                      const void* gv, int64_t S, const int32_t* qpos, const int32_t* step, int64_t G, int64_t Q, int64_t H, int64_t h,
+                      const void* kt, const void* vt, const int32_t* pos_t, const int32_t* own_t, int64_t Tt, void* gk, void* gv,
+                      int64_t S, const void* k_new, const void* v_new, int64_t kv_pitch, const int32_t* qpos, const int32_t* step,
+                      int64_t G, int64_t Q, int64_t H, int64_t h,
                       int64_t D, int32_t beam, int32_t window, float scale, float softcap, void* out, int64_t out_pitch,
                       void* workspace, int64_t workspace_bytes, void* stream);
 

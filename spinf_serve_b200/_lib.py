@@ -66,7 +66,7 @@ SIGNATURES = {
     "spinf_x_attention_workspace_bytes": (_i64, [_i64, _i64, _i64, _i64, _i64, _i64, _i64]),
     "spinf_x_attention": (
         ctypes.c_int,
-        [_p, _i64, _p, _p, _p, _i64, _p, _p, _p, _p, _i64, _p, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _f32, _f32, _p, _i64, _p, _i64, _p],
+        [_p, _i64, _p, _p, _p, _i64, _p, _p, _p, _p, _i64, _p, _p, _i64, _p, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _f32, _f32, _p, _i64, _p, _i64, _p],
     ),
     "spinf_gdn_prologue": (ctypes.c_int, [_p, _i64, _i64, _i64, _p, _p, _p, _p, _i32, _i32, _i32, _i32, _p, _p, _p, _p, _p, _p]),
     "spinf_gdn_epilogue": (ctypes.c_int, [_p, _p, _i64, _p, _f32, _i64, _i32, _i32, _p, _p]),

@@ -32,7 +32,9 @@ struct XAttnArgs {
   const int32_t* pos_p;
   const __nv_bfloat16 *kt, *vt;
   const int32_t *pos_t, *own_t;
-  const __nv_bfloat16 *gk, *gv;
+  __nv_bfloat16 *gk, *gv;
+  const __nv_bfloat16 *k_new, *v_new;  // optional: this step's K / V rows (row g * Q + slot, head j at j * D), appended at token *step
+  int64_t kv_pitch;
   const int32_t* qpos;
   const int32_t* step;
   int G, Q, H, h, D, Lp, Tt, S, beam, window;
@@ -81,6 +83,16 @@ __global__ void __launch_bounds__(128) x_scores_kernel(const XAttnArgs a) {
     if (q >= a.Q) return;
     const int vec = a.D / 8;
     const int n_live = min(step + 1, a.S);
+    if (a.k_new && step < a.S) {
+      // the slot's new token into the generated range first (GroupKV.update, spinf_serve/decode.py:60-65): each lane copies the
+      // pieces it reads back below; the values are read by the value kernel, a launch later
+      const int64_t dst = (((static_cast<int64_t>(g) * a.Q + q) * a.S + step) * a.h + hk) * a.D;
+      const int64_t src = (static_cast<int64_t>(g) * a.Q + q) * a.kv_pitch + static_cast<int64_t>(hk) * a.D;
+      for (int c = lane; c < vec; c += 32) {
+        *reinterpret_cast<uint4*>(a.gk + dst + c * 8) = *reinterpret_cast<const uint4*>(a.k_new + src + c * 8);
+        *reinterpret_cast<uint4*>(a.gv + dst + c * 8) = *reinterpret_cast<const uint4*>(a.v_new + src + c * 8);
+      }
+    }
     for (int rr = 0; rr < r; ++rr) {
       uint4 qv[2] = {};
       const __nv_bfloat16* const qr = x_q_row(a, g, hk, r, q * r + rr);
@@ -369,8 +381,9 @@ extern "C" int64_t spinf_x_attention_workspace_bytes(int64_t G, int64_t Q, int64
 }
 
 extern "C" int spinf_x_attention(const void* q, int64_t q_pitch, const void* kp, const void* vp, const int32_t* pos_p, int64_t Lp,
-                                 const void* kt, const void* vt, const int32_t* pos_t, const int32_t* own_t, int64_t Tt, const void* gk,
-                                 const void* gv, int64_t S, const int32_t* qpos, const int32_t* step, int64_t G, int64_t Q, int64_t H,
+                                 const void* kt, const void* vt, const int32_t* pos_t, const int32_t* own_t, int64_t Tt, void* gk,
+                                 void* gv, int64_t S, const void* k_new, const void* v_new, int64_t kv_pitch, const int32_t* qpos,
+                                 const int32_t* step, int64_t G, int64_t Q, int64_t H,
                                  int64_t h, int64_t D, int32_t beam, int32_t window, float scale, float softcap, void* out,
                                  int64_t out_pitch, void* workspace, int64_t workspace_bytes, void* stream) {
   if (G == 0 || Q == 0) return 0;
@@ -378,6 +391,7 @@ extern "C" int spinf_x_attention(const void* q, int64_t q_pitch, const void* kp,
   SPINF_CHECK_ARG(D >= 64 && D <= 512 && D % 64 == 0 && beam > 0 && window >= 0 && Lp >= 0 && Tt >= 0 && q_pitch % 8 == 0 && out_pitch % 2 == 0);
   SPINF_CHECK_ARG((Lp == 0 || (kp && vp && pos_p)) && (Tt == 0 || (kt && vt && pos_t && own_t)) && G < 65536 && h < 65536);
   SPINF_CHECK_ARG(workspace_bytes >= spinf_x_attention_workspace_bytes(G, Q, H, D, Lp, Tt, S));
+  SPINF_CHECK_ARG((k_new == nullptr) == (v_new == nullptr) && (!k_new || (kv_pitch >= h * D && kv_pitch % 8 == 0)));
   XAttnArgs a;
   a.q = static_cast<const __nv_bfloat16*>(q);
   a.q_pitch = q_pitch;
@@ -388,8 +402,11 @@ extern "C" int spinf_x_attention(const void* q, int64_t q_pitch, const void* kp,
   a.vt = static_cast<const __nv_bfloat16*>(vt);
   a.pos_t = pos_t;
   a.own_t = own_t;
-  a.gk = static_cast<const __nv_bfloat16*>(gk);
-  a.gv = static_cast<const __nv_bfloat16*>(gv);
+  a.gk = static_cast<__nv_bfloat16*>(gk);
+  a.gv = static_cast<__nv_bfloat16*>(gv);
+  a.k_new = static_cast<const __nv_bfloat16*>(k_new);
+  a.v_new = static_cast<const __nv_bfloat16*>(v_new);
+  a.kv_pitch = kv_pitch;
   a.qpos = qpos;
   a.step = step;
   a.G = static_cast<int>(G), a.Q = static_cast<int>(Q), a.H = static_cast<int>(H), a.h = static_cast<int>(h), a.D = static_cast<int>(D);

@@ -122,17 +122,15 @@ class Decoder:
         self.scaling = 1.0  # the Gemma-style layers norm q and k and attend with scaling 1
 
     def _attend(self, i, kind, q, k, v):
-        """a layer's attention inside a step: the new tokens' K/V into the generated range at the current step (GroupKV.update),
-        then the three-range attention"""
+        """a layer's attention inside a step: the new tokens' K/V into the generated range at the current step (GroupKV.update,
+        done by the attention's first launch) and the three-range attention"""
         G, Q, S = self.G, self.Q, self.S
         cfg = self.stack.cfg
         h, D = cfg.kv_heads, cfg.head_dim
-        self.gk[i].index_copy_(2, self.step_t, k.reshape(G, Q, 1, h, D))
-        self.gv[i].index_copy_(2, self.step_t, v.reshape(G, Q, 1, h, D))
         window = cfg.window if kind == "sliding_attention" else None
         out = ops.x_attention(
             q.view(G, Q, cfg.heads, D), self.kp[i], self.vp[i], self.pos_p[i], self.kt[i], self.vt[i], self.pos_t, self.own_t, self.gk[i],
-            self.gv[i], self.qpos, self.step32, self.beam, self.scaling, window, None, workspace=self.workspace,
+            self.gv[i], self.qpos, self.step32, self.beam, self.scaling, window, None, workspace=self.workspace, k_new=k, v_new=v,
         )
         return out.view(G * Q, cfg.heads, D)
 
@@ -282,11 +280,9 @@ class HybridDecoder(Decoder):
         G, Q = self.G, self.Q
         cfg = self.stack.cfg
         h, D = cfg.kv_heads, cfg.head_dim
-        self.gk[i].index_copy_(2, self.step_t, k.reshape(G, Q, 1, h, D))
-        self.gv[i].index_copy_(2, self.step_t, v.reshape(G, Q, 1, h, D))
         out = ops.x_attention(
             q.view(G, Q, cfg.heads, D), self.kp[i], self.vp[i], self.pos_p[i], self.kt[i], self.vt[i], self.pos_t, self.own_t, self.gk[i],
-            self.gv[i], self.qpos, self.step32, self.beam, self.scaling, None, None, workspace=self.workspace,
+            self.gv[i], self.qpos, self.step32, self.beam, self.scaling, None, None, workspace=self.workspace, k_new=k, v_new=v,
         )
         return out.view(G * Q, cfg.heads, D)
 

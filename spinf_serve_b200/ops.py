@@ -255,11 +255,13 @@ def w4_small(x, q, scales, group, extra=None, workspace=None):
     return y
 
 
-def x_attention(q, kp, vp, pos_p, kt, vt, pos_t, own_t, gk, gv, qpos, step, beam, scaling, window=None, softcap=None, out=None, workspace=None):
+def x_attention(q, kp, vp, pos_p, kt, vt, pos_t, own_t, gk, gv, qpos, step, beam, scaling, window=None, softcap=None, out=None, workspace=None,
+                k_new=None, v_new=None):
     """the decoding step's attention (`_x_attention`, spinf_serve/decode.py:71-104) on token-major tensors: q [G, Q, H, D] (a view
     with unit stride over (H, D) and any row pitch); prefix kp / vp [G, Lp, h, D] + pos_p [G, Lp] int32 (-1: padding); templates
     kt / vt [G, Tt, h, D] + pos_t, own_t [G, Tt] int32; generated gk / gv [G, Q, S, h, D]; qpos [G, Q] int32; step: int32 device
-    scalar (tokens 0..step of the generated range are live) -> [G, Q, H, D] bf16"""
+    scalar (tokens 0..step of the generated range are live) -> [G, Q, H, D] bf16. k_new, v_new [G * Q, h, D] (views with contiguous
+    heads and one row pitch, e.g. of the fused q|k|v projection): written into gk / gv at token `step` inside the same launch"""
     G, Q, H, D = q.shape
     if q.dtype != torch.bfloat16 or not q.is_cuda or q.stride(3) != 1 or q.stride(2) != D or q.stride(0) != Q * q.stride(1):
         raise SpinfError("x_attention: q must be a CUDA bf16 [G, Q, H, D] view with contiguous heads and evenly pitched rows")
@@ -273,6 +275,14 @@ def x_attention(q, kp, vp, pos_p, kt, vt, pos_t, own_t, gk, gv, qpos, step, beam
         raise SpinfError("x_attention: key / value shapes do not agree")
     if pos_p.shape != (G, Lp) or pos_t.shape != (G, Tt) or own_t.shape != (G, Tt) or qpos.shape != (G, Q) or step.numel() != 1:
         raise SpinfError("x_attention: position / owner shapes do not agree")
+    kv_pitch = 0
+    if (k_new is None) != (v_new is None):
+        raise SpinfError("x_attention: k_new and v_new come together")
+    if k_new is not None:
+        for t in (k_new, v_new):
+            if t.dtype != torch.bfloat16 or not t.is_cuda or t.shape != (G * Q, h, D) or t.stride(2) != 1 or t.stride(1) != D or t.stride(0) != k_new.stride(0):
+                raise SpinfError("x_attention: k_new / v_new must be CUDA bf16 [G * Q, h, D] views with contiguous heads and one row pitch")
+        kv_pitch = k_new.stride(0)
     if out is None:
         out = torch.empty((G, Q, H, D), dtype=torch.bfloat16, device=q.device)
     need = int(_lib.lib().spinf_x_attention_workspace_bytes(G, Q, H, D, Lp, Tt, S))
@@ -281,7 +291,7 @@ def x_attention(q, kp, vp, pos_p, kt, vt, pos_t, own_t, gk, gv, qpos, step, beam
     check(
         _lib.lib().spinf_x_attention(
             ptr(q), q.stride(1), ptr(kp), ptr(vp), ptr(pos_p), Lp, ptr(kt), ptr(vt), ptr(pos_t), ptr(own_t), Tt, ptr(gk), ptr(gv), S,
-            ptr(qpos), ptr(step), G, Q, H, h, D, beam, int(window or 0), float(scaling), float(softcap or 0.0), ptr(out), out.stride(1),
+            ptr(k_new), ptr(v_new), kv_pitch, ptr(qpos), ptr(step), G, Q, H, h, D, beam, int(window or 0), float(scaling), float(softcap or 0.0), ptr(out), out.stride(1),
             ptr(workspace), workspace.numel(), stream_ptr(),
         ),
         "spinf_x_attention",
