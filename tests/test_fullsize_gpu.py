@@ -273,3 +273,58 @@ def test_decoding_step_at_the_12b_shapes(dev):
         del dec
     print(f"decoding step, {G * J * beam} rows, {cfg.layers} layers: {times[True]:.2f} ms from its graph, {times[False]:.2f} ms launched eagerly")
     assert torch.equal(outs[False], outs[True]) and bool(torch.isfinite(outs[True].float()).all())
+
+
+def test_hybrid_decoding_step_at_the_27b_shapes(dev):
+    """the hybrid family's extraction decoder at full width and depth (64 layers, 48 of them recurrent, int4 linears): 2 groups x
+    1 000-token prefixes, 3 prompts x 6 beams; graph replay equals eager bit for bit, outputs finite, time printed"""
+    import types
+
+    from spinf_serve_b200 import decode as D
+    from spinf_serve_b200.qwen_stack import QwenConfig, QwenStack, QwenWeights
+
+    cfg = QwenConfig()
+    stack = QwenStack(QwenWeights.random(cfg, seed=0, device=dev))
+    G, J, P, T, beam = 2, 3, 1000, 12, 6
+    gen = torch.Generator(device=dev).manual_seed(1)
+    rnd = lambda *s: torch.randn(s, generator=gen, device=dev).to(torch.bfloat16)  # noqa: E731
+    unit = lambda *s: torch.nn.functional.normalize(torch.randn(s, generator=gen, device=dev), dim=-1).to(torch.bfloat16)  # noqa: E731
+    att = [i for i in range(cfg.layers) if cfg.layer_types[i] == "full_attention"]
+    rec = [i for i in range(cfg.layers) if i not in att]
+    cd = 2 * cfg.hk * cfg.dk + cfg.hv * cfg.dv
+
+    def make_groups():
+        g2 = torch.Generator(device=dev).manual_seed(2)
+        groups = []
+        for gi in range(G):
+            grp = D.Group({li: (rnd(P, cfg.kv_heads, cfg.head_dim), rnd(P, cfg.kv_heads, cfg.head_dim)) for li in att}, P)
+            grp.extra = {"state": {li: torch.randn((cfg.hv, cfg.dk, cfg.dv), generator=g2, device=dev) * 0.05 for li in rec}, "tmpl": []}
+            for j in range(J):
+                grp.prompts.append((types.SimpleNamespace(key=(gi, j), max_tokens=8), {li: (rnd(T, cfg.kv_heads, cfg.head_dim), rnd(T, cfg.kv_heads, cfg.head_dim)) for li in att}, T, None))
+                tok = {li: (unit(T, cfg.hk, cfg.dk), unit(T, cfg.hk, cfg.dk), rnd(T, cfg.hv, cfg.dv), -torch.rand((T, cfg.hv), generator=g2, device=dev) * 0.1,
+                            torch.rand((T, cfg.hv), generator=g2, device=dev).to(torch.bfloat16)) for li in rec}
+                grp.extra["tmpl"].append({"tok": tok, "pre": {li: rnd(3, cd) for li in rec}})
+            groups.append(grp)
+        return groups
+
+    times, outs = {}, {}
+    for graphs in (False, True):
+        gen.manual_seed(1)
+        dec = D.HybridDecoder(stack, make_groups(), dev, beam=beam, graphs=graphs)
+        tok = torch.randint(5, 1000, (dec.G, dec.Q), generator=torch.Generator().manual_seed(2)).to(dev)
+        for s in range(3):
+            out = dec.forward(tok, s)
+        outs[graphs] = out.clone()
+        torch.cuda.synchronize()
+        ms = []
+        for s in range(3, 8):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            dec.forward(tok, s)
+            e1.record()
+            e1.synchronize()
+            ms.append(e0.elapsed_time(e1))
+        times[graphs] = sorted(ms)[len(ms) // 2]
+        del dec
+    print(f"hybrid decoding step, {G * J * beam} rows, {cfg.layers} layers: {times[True]:.2f} ms from its graph, {times[False]:.2f} ms launched eagerly")
+    assert torch.equal(outs[False], outs[True]) and bool(torch.isfinite(outs[True].float()).all())
