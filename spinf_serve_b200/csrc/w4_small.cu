@@ -27,6 +27,13 @@ __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1,
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void cp_async8(void* dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async4z(void* dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(src_bytes) : "memory");
+}
+
 // byte b (k even in the low nibble, k odd in the high) -> half2 ((lo - 8) * s, (hi - 8) * s), each product rounded to fp16
 __device__ __forceinline__ uint32_t w4_pair(uint32_t byte, __half2 s2) {
   const uint32_t v = (byte & 0xFu) | ((byte & 0xF0u) << 12) | 0x64006400u;  // fp16 1024 + nibble, twice
@@ -62,10 +69,19 @@ __global__ void __launch_bounds__(128) w4_small_kernel(const __half* __restrict_
       const bool ok = n0 + n < N;
       cp_async16(qb + n * WS_QLD + c * 16, ok ? q + static_cast<int64_t>(n0 + n) * (K / 2) + k0 / 2 + c * 16 : q, ok ? 16 : 0);
     }
+    // the tile's group scales ride the same asynchronous copies (a plain load here would put a global-memory latency in front of
+    // every tile's products): 2 gpt bytes per row, as one 16-, 8- or 4-byte piece
     __half* const sb = reinterpret_cast<__half*>(qb + WS_BN * WS_QLD);
-    for (int i = tid; i < WS_BN * gpt; i += 128) {
-      const int n = i / gpt, c = i % gpt;
-      sb[n * WS_MAXG + c] = n0 + n < N ? s[static_cast<int64_t>(n0 + n) * sld + k0 / group + c] : __float2half(0.f);
+    if (gpt >= 2) {
+      for (int n = tid; n < WS_BN; n += 128) {
+        const bool ok = n0 + n < N;
+        const __half* src = ok ? s + static_cast<int64_t>(n0 + n) * sld + k0 / group : s;
+        if (gpt == 8) cp_async16(sb + n * WS_MAXG, src, ok ? 16 : 0);
+        else if (gpt == 4) cp_async8(sb + n * WS_MAXG, src, ok ? 8 : 0);
+        else cp_async4z(sb + n * WS_MAXG, src, ok ? 4 : 0);
+      }
+    } else {
+      for (int n = tid; n < WS_BN; n += 128) sb[n * WS_MAXG] = n0 + n < N ? s[static_cast<int64_t>(n0 + n) * sld + k0 / group] : __float2half(0.f);
     }
   };
 
