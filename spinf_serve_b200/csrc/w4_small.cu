@@ -4,7 +4,7 @@
 // are the traffic. Arithmetic as the reference's kernel: the activations rounded to fp16, the weight (nibble - 8) * scale formed
 // and rounded in fp16, fp16 tensor-core products with fp32 accumulation, split-K partial sums in an fp32 buffer
 // [splits, M, N] added in split order, the sum rounded to bf16.
-//   grid (ceil(N / 64), splits), 128 threads: warp w owns 16 output channels of the block for all rows; a k-tile of 256 is staged in
+//   grid (ceil(N / 128), splits), 256 threads: warp w owns 16 output channels of the block for all rows; a k-tile of 256 is staged in
 //   shared memory by cp.async (two stages); a thread takes 8 consecutive k of its channel as one 32-bit word and of each of its
 //   rows as one 128-bit load: the tensor-core fragment slots are filled in that (permuted) k order on both operands.
 #include "common.cuh"
@@ -16,7 +16,7 @@
 
 namespace spinf {
 
-static constexpr int WS_BN = 64, WS_BK = 256;
+static constexpr int WS_BK = 256;  // k per staged tile; a CTA owns BN = 64 or 128 output channels, 16 per warp
 static constexpr int WS_XLD = WS_BK * 2 + 64;   // bytes per staged activation row: 144 words, rows alternate bank halves
 static constexpr int WS_QLD = WS_BK / 2 + 16;   // bytes per staged weight row: 36 words
 static constexpr int WS_MAXG = WS_BK / 32;      // group scales per row and k-tile at the smallest group (32)
@@ -42,11 +42,12 @@ __device__ __forceinline__ uint32_t w4_pair(uint32_t byte, __half2 s2) {
   return *reinterpret_cast<const uint32_t*>(&w);
 }
 
-template <int MT>  // row tiles of 16
-__global__ void __launch_bounds__(128) w4_small_kernel(const __half* __restrict__ x, const uint8_t* __restrict__ q, const __half* __restrict__ s,
+template <int MT, int WS_BN>  // row tiles of 16; output channels per CTA
+__global__ void __launch_bounds__(WS_BN * 2) w4_small_kernel(const __half* __restrict__ x, const uint8_t* __restrict__ q, const __half* __restrict__ s,
                                                         float* __restrict__ part, int M, int N, int K, int group, int k_per) {
   extern __shared__ __align__(16) uint8_t w4s_raw[];
   constexpr int BM = MT * 16;
+  constexpr int WS_TH = WS_BN * 2;
   constexpr int STAGE = BM * WS_XLD + WS_BN * WS_QLD + WS_BN * WS_MAXG * 2;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int gq = lane >> 2, tq = lane & 3;
@@ -58,13 +59,13 @@ __global__ void __launch_bounds__(128) w4_small_kernel(const __half* __restrict_
   auto stage = [&](int t, int buf) {
     uint8_t* const base = w4s_raw + buf * STAGE;
     const int k0 = k_lo + t * WS_BK;
-    for (int i = tid; i < BM * (WS_BK / 8); i += 128) {
+    for (int i = tid; i < BM * (WS_BK / 8); i += WS_TH) {
       const int m = i / (WS_BK / 8), c = i % (WS_BK / 8);
       const bool ok = m < M;
       cp_async16(base + m * WS_XLD + c * 16, ok ? x + static_cast<int64_t>(m) * K + k0 + c * 8 : x, ok ? 16 : 0);
     }
     uint8_t* const qb = base + BM * WS_XLD;
-    for (int i = tid; i < WS_BN * (WS_BK / 32); i += 128) {
+    for (int i = tid; i < WS_BN * (WS_BK / 32); i += WS_TH) {
       const int n = i / (WS_BK / 32), c = i % (WS_BK / 32);
       const bool ok = n0 + n < N;
       cp_async16(qb + n * WS_QLD + c * 16, ok ? q + static_cast<int64_t>(n0 + n) * (K / 2) + k0 / 2 + c * 16 : q, ok ? 16 : 0);
@@ -73,7 +74,7 @@ __global__ void __launch_bounds__(128) w4_small_kernel(const __half* __restrict_
     // every tile's products): 2 gpt bytes per row, as one 16-, 8- or 4-byte piece
     __half* const sb = reinterpret_cast<__half*>(qb + WS_BN * WS_QLD);
     if (gpt >= 2) {
-      for (int n = tid; n < WS_BN; n += 128) {
+      for (int n = tid; n < WS_BN; n += WS_TH) {
         const bool ok = n0 + n < N;
         const __half* src = ok ? s + static_cast<int64_t>(n0 + n) * sld + k0 / group : s;
         if (gpt == 8) cp_async16(sb + n * WS_MAXG, src, ok ? 16 : 0);
@@ -81,7 +82,7 @@ __global__ void __launch_bounds__(128) w4_small_kernel(const __half* __restrict_
         else cp_async4z(sb + n * WS_MAXG, src, ok ? 4 : 0);
       }
     } else {
-      for (int n = tid; n < WS_BN; n += 128) sb[n * WS_MAXG] = n0 + n < N ? s[static_cast<int64_t>(n0 + n) * sld + k0 / group] : __float2half(0.f);
+      for (int n = tid; n < WS_BN; n += WS_TH) sb[n * WS_MAXG] = n0 + n < N ? s[static_cast<int64_t>(n0 + n) * sld + k0 / group] : __float2half(0.f);
     }
   };
 
@@ -147,27 +148,35 @@ __global__ void w4_small_sum_kernel(const float* __restrict__ part, int splits, 
 
 static int w4_small_splits(int64_t N, int64_t K) {
   // the reference's rule (w4gemm.py:51-56): about 512 programs, a split count that divides the k-tiles
-  const int64_t n_blocks = (N + WS_BN - 1) / WS_BN;
+  const int64_t n_blocks = (N + 63) / 64;  // the reference's programs are 64 channels wide
   int64_t splits = std::max<int64_t>(1, std::min<int64_t>(K / WS_BK, 512 / n_blocks));
   while ((K / WS_BK) % splits) --splits;
   return static_cast<int>(splits);
 }
 
-template <int MT>
-static int w4_small_launch(const __half* xh, const uint8_t* q, const __half* s, float* part, int M, int N, int K, int group, int splits,
-                           cudaStream_t st) {
-  constexpr int smem = 2 * (MT * 16 * WS_XLD + WS_BN * WS_QLD + WS_BN * WS_MAXG * 2);
+template <int MT, int BN>
+static int w4_small_launch_bn(const __half* xh, const uint8_t* q, const __half* s, float* part, int M, int N, int K, int group, int splits,
+                              cudaStream_t st) {
+  constexpr int smem = 2 * (MT * 16 * WS_XLD + BN * WS_QLD + BN * WS_MAXG * 2);
   static std::atomic<bool> attr_set[64];
   int dev = 0;
   SPINF_CUDA_OK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64 || !attr_set[dev].load(std::memory_order_acquire)) {
-    SPINF_CUDA_OK(cudaFuncSetAttribute(w4_small_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    SPINF_CUDA_OK(cudaFuncSetAttribute(w4_small_kernel<MT, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     if (dev >= 0 && dev < 64) attr_set[dev].store(true, std::memory_order_release);
   }
-  w4_small_kernel<MT><<<dim3(static_cast<unsigned>((N + WS_BN - 1) / WS_BN), static_cast<unsigned>(splits)), 128, smem, st>>>(
+  w4_small_kernel<MT, BN><<<dim3(static_cast<unsigned>((N + BN - 1) / BN), static_cast<unsigned>(splits)), BN * 2, smem, st>>>(
       xh, q, s, part, M, N, K, group, K / splits);
   SPINF_CUDA_OK(cudaGetLastError());
   return 0;
+}
+
+template <int MT>
+static int w4_small_launch(const __half* xh, const uint8_t* q, const __half* s, float* part, int M, int N, int K, int group, int splits,
+                           cudaStream_t st) {
+  // 128 channels per CTA halve the re-reads of the activation tile; worth it while the grid still covers the SMs one and a half times
+  if (static_cast<int64_t>((N + 127) / 128) * splits * 2 >= 3 * sm_count()) return w4_small_launch_bn<MT, 128>(xh, q, s, part, M, N, K, group, splits, st);
+  return w4_small_launch_bn<MT, 64>(xh, q, s, part, M, N, K, group, splits, st);
 }
 
 }  // namespace spinf
