@@ -52,6 +52,7 @@ def test_x_attention_against_the_reference_s_outputs(dev, i):
     (2, 16, 8, 256, 6, 5, 700, 90, 17, 9, 512, None),   # 60 rows per kv head, sliding
     (1, 32, 16, 128, 6, 6, 300, 200, 9, 0, None, 30.0),  # 72 rows per kv head: two row passes
     (3, 4, 4, 64, 1, 3, 0, 10, 3, 2, None, None),       # no prefix at all
+    (2, 8, 2, 128, 2, 2, 90, 0, 4, 1, None, None),      # no templates: prefix and generated tokens only
 ])
 def test_x_attention_against_the_oracle(dev, G, H, h, Dh, beam, J, Lp, Tt, S, step, window, softcap):
     g = torch.Generator().manual_seed(G * 1000 + Lp)
@@ -65,7 +66,7 @@ def test_x_attention_against_the_oracle(dev, G, H, h, Dh, beam, J, Lp, Tt, S, st
         n = Lp - 13 * gi if Lp else 0
         Pn = n + 5
         pos_p[gi, :n] = torch.arange(Pn - n, Pn)
-        per = (Tt - gi) // J
+        per = max(Tt - gi, 0) // J
         for j in range(J):
             pos_t[gi, j * per : (j + 1) * per] = torch.arange(Pn, Pn + per)
             own_t[gi, j * per : (j + 1) * per] = j
