@@ -44,6 +44,7 @@ class EngineConfig:
     token_budget: int = 16384
     max_tokens: int = 65536
     prefetch: int = 6
+    pack_window: int = 96  # contents the packer holds back before it packs them first-fit-decreasing (the reference's Packer.push default)
     align_jobs: bool = True
     min_stream: int = 1024
     layers: int | None = None
@@ -404,7 +405,7 @@ class Scorer:
             for key, first, tree in items:
                 slots = out.setdefault(key, [])
                 slots.extend([None] * (first + len(tree.plans) - len(slots)))
-                yield from packer.push((key, first), tree)
+                yield from packer.push((key, first), tree, self.cfg.pack_window)
             yield from packer.flush()
 
         self._execute(batches, lambda lp, cols, b: read_grouped(lp, cols, b, out))
@@ -426,7 +427,7 @@ class Scorer:
                     raise ValueError(f"job {jid}: {e}") from None
                 for first, tree in runs:
                     results[jid].trees += 1
-                    yield from packer.push((jid, first), tree)
+                    yield from packer.push((jid, first), tree, self.cfg.pack_window)
             yield from packer.flush()
 
         self._execute(batches, lambda lp, cols, b: read_trees(lp, cols, b, results))
