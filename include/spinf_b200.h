@@ -145,6 +145,14 @@ int spinf_bf16_gemm_ld(const void* x, const void* w, void* y, int64_t M, int64_t
 int spinf_w4_gemm(const void* x, const void* qw, const void* scales, int32_t group, void* y, int64_t M, int64_t N, int64_t K,
                   int64_t y_pitch, void* stream);
 
+/* spinf_w4_gemm for a decoding step's few rows (M <= 256): the same kernel with the K dimension cut into slices when the column
+ * tiles alone do not occupy the GPU (out / down projections of 5 120 channels: 20 tiles for 74 CTA pairs); the slices' fp32 sums
+ * go through `workspace` and are added in slice order before the one rounding to bf16, so a result may differ from spinf_w4_gemm's
+ * in the last bf16 bit. Shapes that need no slices run spinf_w4_gemm itself. */
+int64_t spinf_w4_gemm_small_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int spinf_w4_gemm_small(const void* x, const void* qw, const void* scales, int32_t group, void* y, int64_t M, int64_t N, int64_t K,
+                        int64_t y_pitch, void* workspace, int64_t workspace_bytes, void* stream);
+
 /* Load-time re-ordering of the packed int4 weights for spinf_w4_gemm. q_in: uint8 [N, K/2] in the reference's engine layout (byte b
  * of a row = k 2b in the low nibble, k 2b+1 in the high nibble: the `q` buffer of Int4Linear, qwen.py:383-389). q_out (may be
  * q_in): per 32-bit word of 8 consecutive k, the even k in nibbles 0..3 and the odd k in nibbles 4..7, so that the kernel takes a

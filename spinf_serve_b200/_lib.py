@@ -61,6 +61,8 @@ SIGNATURES = {
     "spinf_gdn_tree_prep": (ctypes.c_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _p, _i64, _p, _p, _i64, _p, _i64, _p]),
     "spinf_gdn_tree_scan": (ctypes.c_int, [_p, _p, _p, _i64, _i64, _i32, _i32, _i32, _i32, _f32, _p, _i64, _p, _p, _p, _i64, _p, _p, _p, _i64, _p]),
     "spinf_gdn_tree_scan_tc": (ctypes.c_int, [_p, _p, _p, _i64, _i64, _i32, _i32, _i32, _i32, _f32, _i64, _p, _p, _p, _p, _i64, _p, _p, _p, _i64, _p]),
+    "spinf_w4_gemm_small_workspace_bytes": (_i64, [_i64, _i64, _i64]),
+    "spinf_w4_gemm_small": (ctypes.c_int, [_p, _p, _p, _i32, _p, _i64, _i64, _i64, _i64, _p, _i64, _p]),
     "spinf_w4_small_workspace_bytes": (_i64, [_i64, _i64, _i64]),
     "spinf_w4_small": (ctypes.c_int, [_p, _p, _p, _i32, _p, _i64, _i64, _i64, _i64, _p, _i64, _p]),
     "spinf_x_attention_workspace_bytes": (_i64, [_i64, _i64, _i64, _i64, _i64, _i64, _i64]),

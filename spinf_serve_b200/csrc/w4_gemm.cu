@@ -24,6 +24,7 @@
 // chunk is in registers (a staging buffer per chunk, so no chunk waits for an earlier chunk's store): about 5 % of a tile's main
 // loop at K = 5120, while loads and expansion run ahead through the ring.
 // K order per output element is ascending and the tile shape does not depend on M: rows are batch-invariant.
+#include <algorithm>
 #include <atomic>
 #include "gemm_tc.cuh"
 #include "host_util.h"
@@ -48,6 +49,11 @@ struct W4Args {
   const __half* scales;  // [N, K / G]
   int M, N, K, G;
   int tiles_m, tiles_n, group_m;  // tiles of 256 tokens x 256 output channels
+  // split-K (a decoding step's few rows, where the column tiles alone do not fill the GPU): a work unit is (tile, K slice of kb_per
+  // steps); the epilogue writes the slice's fp32 sums to part[slice][m][n] and a second kernel adds the slices in order. splits = 1,
+  // part = nullptr: the plain kernel.
+  int splits, kb_per;
+  float* part;
 };
 
 
@@ -105,8 +111,7 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const uint32_t tmem_base = *tmem_base_p;
   GemmShape shape;
   shape.M = a.M, shape.N = a.N, shape.K = a.K, shape.tiles_m = a.tiles_m, shape.tiles_n = a.tiles_n, shape.group_m = a.group_m;
-  const int num_tiles = a.tiles_m * a.tiles_n;
-  const int num_kb = a.K / 64;
+  const int num_tiles = a.tiles_m * a.tiles_n * a.splits;  // work units: tile-major, a tile's K slices next to one another
 
   if (warp == 0) {
     if (lane == 0) {
@@ -114,8 +119,9 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       bool ok = true;
       for (int tile = pair0; tile < num_tiles && ok; tile += pair_step) {
         int tm, tn;
-        tile_coords(shape, tile, tm, tn);
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        tile_coords(shape, tile / a.splits, tm, tn);
+        const int kb0 = (tile % a.splits) * a.kb_per;
+        for (int kb = kb0; kb < kb0 + a.kb_per; ++kb, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
           if (!mbar_wait(wc, &mma_done[s], ph ^ 1u, ST_TIMEOUT_EMPTY)) { ok = false; break; }
           if (!mbar_wait(wc, &raw_done[s], ph ^ 1u, ST_TIMEOUT_EMPTY)) { ok = false; break; }
@@ -140,7 +146,8 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (int tile = pair0; tile < num_tiles && ok; tile += pair_step, ++tcount) {
         if (!mbar_wait(wc, acc_empty, (tcount & 1u) ^ 1u, ST_TIMEOUT_TMEM)) { ok = false; break; }
         tc_fence_after();
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int kb0 = (tile % a.splits) * a.kb_per;
+        for (int kb = kb0; kb < kb0 + a.kb_per; ++kb, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
           if (!mbar_wait(wc, &full_a[s], ph, ST_TIMEOUT_FULL)) { ok = false; break; }
           if (!mbar_wait(wc, &b_full[s], ph, ST_TIMEOUT_OTHER)) { ok = false; break; }
@@ -148,7 +155,7 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const uint64_t xdesc = make_smem_desc_sw128(smem_u32(smem + s * L::STAGE_BYTES), 16, 1024);
           const uint32_t w_tmem = tmem_base + L::W_COL + s * 32;  // 16 bf16 of K = 8 packed columns per MMA
 #pragma unroll
-          for (int k = 0; k < 4; ++k) umma_f16_ts_pair(tmem_base + L::ACC_COL, w_tmem + 8 * k, xdesc + 2 * k, IDESC, (kb | k) != 0);
+          for (int k = 0; k < 4; ++k) umma_f16_ts_pair(tmem_base + L::ACC_COL, w_tmem + 8 * k, xdesc + 2 * k, IDESC, kb != kb0 || k != 0);
           umma_commit_pair_both(&mma_done[s]);  // one commit per step: every commit is a bubble in the tensor pipe
         }
         if (ok) umma_commit_pair_both(acc_full);
@@ -165,7 +172,8 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const uint32_t b_full_leader = map_to_cta(b_full, 0);
     for (int tile = pair0; tile < num_tiles && ok; tile += pair_step) {
       int tm, tn;
-      tile_coords(shape, tile, tm, tn);
+      tile_coords(shape, tile / a.splits, tm, tn);
+      const int kb0 = (tile % a.splits) * a.kb_per;
       const int n = tn * 256 + static_cast<int>(rank) * 128 + n_local;
       const bool n_ok = n < a.N;
       const __half* srow = a.scales + static_cast<int64_t>(n_ok ? n : 0) * groups;
@@ -178,7 +186,7 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const uint32_t lo = __float_as_uint(sc - __uint_as_float(hi << 16)) >> 16;
         s_hi2 = hi | (hi << 16), s_lo2 = lo | (lo << 16);
       };
-      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+      for (int kb = kb0; kb < kb0 + a.kb_per; ++kb, ++it) {
         if ((it & 1u) != static_cast<uint32_t>(grp)) continue;
         const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
         bool got = mbar_wait(wc, &full_w[s], ph, ST_TIMEOUT_FULL);
@@ -238,7 +246,8 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint32_t tcount = 0, nchunks = 0;
     for (int tile = pair0; tile < num_tiles; tile += pair_step, ++tcount) {
       int tm, tn;
-      tile_coords(shape, tile, tm, tn);
+      tile_coords(shape, tile / a.splits, tm, tn);
+      const int ks = tile % a.splits;
       const bool got = mbar_wait(wc, acc_full, tcount & 1u, ST_TIMEOUT_TMEM);
       if (!bar_red_and(1, 128, got)) break;
       tc_fence_after();
@@ -254,6 +263,20 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+        }
+        if (ACT < 0 && a.part != nullptr) {
+          // a K slice's sums, fp32, straight to part[slice][token][channel]: a warp's lanes are 32 neighbouring channels
+          const int n = tn * 256 + static_cast<int>(rank) * 128 + ch;
+          float* const dst = a.part + (static_cast<int64_t>(ks) * a.M + tm * 256 + c * 64) * a.N + n;
+          const int rows = a.M - (tm * 256 + c * 64);  // tokens of this chunk that exist
+          if (n < a.N) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              if (i < rows) dst[static_cast<int64_t>(i) * a.N] = __uint_as_float(v0[i]);
+              if (32 + i < rows) dst[static_cast<int64_t>(32 + i) * a.N] = __uint_as_float(v1[i]);
+            }
+          }
+          continue;
         }
         // transpose through the lane pair: the even lane keeps token 2 i of both channels, the odd lane token 2 i + 1
         uint32_t packed[32];
@@ -347,6 +370,24 @@ __global__ void __launch_bounds__(256) w4_repack_kernel(const uint32_t* __restri
   }
 }
 
+// y[m][n] = bf16(sum over the K slices, in slice order, of part[slice][m][n])
+__global__ void w4_splitk_sum_kernel(const float* __restrict__ part, int splits, int64_t MN, int N, __nv_bfloat16* __restrict__ y, int64_t y_pitch) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= MN) return;
+  float t = part[i];
+  for (int sp = 1; sp < splits; ++sp) t += part[sp * MN + i];
+  y[(i / N) * y_pitch + i % N] = __float2bfloat16_rn(t);
+}
+
+// K slices for a product of M <= 256 rows: as many as bring the work units (column tiles x slices) up to the number of CTA pairs,
+// a count that divides the K steps
+static int w4_splits(int64_t N, int64_t K) {
+  const int tiles_n = static_cast<int>((N + 255) / 256), pairs = sm_count() / 2, num_kb = static_cast<int>(K / 64);
+  int splits = std::max(1, std::min(num_kb, pairs / tiles_n));
+  while (num_kb % splits) --splits;
+  return splits;
+}
+
 }  // namespace spinf
 
 using namespace spinf;
@@ -366,7 +407,7 @@ extern "C" int spinf_w4_repack(const void* q_in, void* q_out, int64_t N, int64_t
 
 template <int ACT>
 static int launch_w4(const void* x, const void* qw, const void* scales, int32_t group, void* y, int64_t M, int64_t N, int64_t K,
-                     int64_t y_pitch, void* stream) {
+                     int64_t y_pitch, void* stream, int splits = 1, float* part = nullptr) {
   if (M == 0) return 0;  // nothing to do: the row pointers may be null
   const int64_t n_out = ACT < 0 ? N : N / 2;
   SPINF_CHECK_ARG(x && qw && scales && y && M >= 0 && N > 0 && K > 0 && group > 0);
@@ -386,6 +427,7 @@ static int launch_w4(const void* x, const void* qw, const void* scales, int32_t 
   a.M = static_cast<int>(M), a.N = static_cast<int>(N), a.K = static_cast<int>(K), a.G = group;
   a.tiles_m = static_cast<int>((M + 255) / 256);
   a.tiles_n = static_cast<int>((N + 255) / 256);
+  a.splits = splits, a.kb_per = static_cast<int>(K / 64) / splits, a.part = part;
   // groups of row tiles as tall as about 32 MB of bf16 activations allow (4..32 tiles of 256 rows): the packed weight streams past
   // once per group
   {
@@ -399,7 +441,7 @@ static int launch_w4(const void* x, const void* qw, const void* scales, int32_t 
     SPINF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, W4Smem::TOTAL));
     attr_set[dev].store(true, std::memory_order_release);
   }
-  const int tiles = a.tiles_m * a.tiles_n;
+  const int tiles = a.tiles_m * a.tiles_n * a.splits;
   const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
@@ -430,3 +472,29 @@ extern "C" int spinf_w4_gemm_glu(const void* x, const void* qw, const void* scal
                   : launch_w4<1>(x, qw, scales, group, y, M, N2, K, y_pitch, stream);
 }
 
+
+// bytes of workspace spinf_w4_gemm_small needs (0: the shape needs no split)
+extern "C" int64_t spinf_w4_gemm_small_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  if (M <= 0 || N <= 0 || K <= 0 || K % 64) return 0;
+  const int splits = w4_splits(N, K);
+  return splits > 1 ? static_cast<int64_t>(splits) * M * N * 4 + 256 : 0;
+}
+
+extern "C" int spinf_w4_gemm_small(const void* x, const void* qw, const void* scales, int32_t group, void* y, int64_t M, int64_t N, int64_t K,
+                                   int64_t y_pitch, void* workspace, int64_t workspace_bytes, void* stream) {
+  if (M == 0) return 0;
+  SPINF_CHECK_ARG(M > 0 && M <= 256 && N > 0 && K > 0 && K % 64 == 0);
+  const int splits = w4_splits(N, K);
+  if (splits == 1) return launch_w4<-1>(x, qw, scales, group, y, M, N, K, y_pitch, stream);
+  SPINF_CHECK_ARG(workspace && workspace_bytes >= spinf_w4_gemm_small_workspace_bytes(M, N, K));
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  ws += (256 - reinterpret_cast<uintptr_t>(ws) % 256) % 256;
+  float* const part = reinterpret_cast<float*>(ws);
+  const int r = launch_w4<-1>(x, qw, scales, group, y, M, N, K, y_pitch, stream, splits, part);
+  if (r) return r;
+  const int64_t MN = M * N;
+  w4_splitk_sum_kernel<<<static_cast<unsigned>((MN + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      part, splits, MN, static_cast<int>(N), static_cast<__nv_bfloat16*>(y), y_pitch);
+  SPINF_CUDA_OK(cudaGetLastError());
+  return 0;
+}

@@ -207,3 +207,12 @@ class Int4Linear(nn.Module):
             return y.reshape(*x.shape[:-1], y.shape[-1])
         y = ops.w4_gemm(x2 if x2.is_contiguous() else x2.contiguous(), self.q, self.s, self.group, self.extra)
         return y.reshape(*x.shape[:-1], y.shape[-1])
+
+    def few(self, x):
+        """forward for a decoding step's few rows (at most 256): narrow projections run the kernel with its K dimension cut into
+        slices so that every SM streams weights (the last bf16 bit may differ from forward's); gated projections as forward"""
+        if self.glu is not None:
+            return self.forward(x)
+        x2 = x.reshape(-1, x.shape[-1])
+        y = ops.w4_gemm_small(x2 if x2.is_contiguous() else x2.contiguous(), self.q, self.s, self.group, self.extra)
+        return y.reshape(*x.shape[:-1], y.shape[-1])

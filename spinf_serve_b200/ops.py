@@ -300,6 +300,33 @@ def x_attention(q, kp, vp, pos_p, kt, vt, pos_t, own_t, gk, gv, qpos, step, beam
     return out
 
 
+def w4_gemm_small(x, qw, scales, group, extra=None, workspace=None):
+    """w4_gemm for a decoding step's few rows (M <= 256): the K dimension is cut into slices where the column tiles alone do not
+    occupy the GPU, the slices' fp32 sums added in order before the rounding (may differ from w4_gemm in the last bf16 bit)"""
+    _need(x, torch.bfloat16, "x", 2)
+    _need(qw, torch.uint8, "qw", 2)
+    _need(scales, torch.float16, "scales", 2)
+    M, K = x.shape
+    N = qw.shape[0]
+    if qw.shape[1] * 2 != K or scales.shape != (N, K // group) or M > 256:
+        raise SpinfError("w4_gemm_small: shapes do not agree")
+    E = 0 if extra is None else extra.shape[0]
+    if extra is not None:
+        _need(extra, torch.bfloat16, "extra", 2)
+    y = torch.empty((M, N + E), dtype=torch.bfloat16, device=x.device)
+    need = int(_lib.lib().spinf_w4_gemm_small_workspace_bytes(M, N, K))
+    if need and (workspace is None or workspace.numel() < need):
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    check(_lib.lib().spinf_w4_gemm_small(ptr(x), ptr(qw), ptr(scales), group, ptr(y), M, N, K, N + E, ptr(workspace) if need else None,
+                                         workspace.numel() if need else 0, stream_ptr()), "spinf_w4_gemm_small")
+    COUNTS["launches"] += 2 if need else 1
+    if E:
+        tail = ctypes.c_void_p(y.data_ptr() + 2 * N)
+        check(_lib.lib().spinf_bf16_gemm_ld(ptr(x), ptr(extra), tail, M, E, K, N + E, stream_ptr()), "spinf_bf16_gemm_ld")
+        COUNTS["launches"] += 1
+    return y
+
+
 def glu_tile_order(F: int):
     """row permutation that puts a fused gate|up weight [2F, K] (gate rows first) into the tiled order of fp8_gemm_glu: per 128
     features, four blocks of 32 gate rows followed by the 32 up rows of the same features"""

@@ -257,10 +257,15 @@ class QwenStack:
                 return t
             return torch.zeros((T,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device).index_copy_(0, sidx, t[:R])
 
+        few = recur is not None or attend is not None  # a decoding step: the linears' few-row form
+
+        def lin(mod, t):
+            return mod.few(t) if few and t.shape[0] <= 256 else mod(t)
+
         for i in range(self.n_layers):
             L = w.layers[i]
             if L["kind"] == "linear_attention":
-                y = L["in_proj"](h)
+                y = lin(L["in_proj"], h)
                 if recur is not None:
                     o, z = recur(i, y)
                 else:
@@ -268,9 +273,9 @@ class QwenStack:
                     o = gdn.gdn_tree(q, k, v, g, beta, plan)
                     if self._cap is not None:
                         self._capture_recurrent(i, y, q, k, v, g, beta, plan)
-                m = L["out_proj"](gdn.epilogue(o, z, L["gdn_norm"], cfg.eps))
+                m = lin(L["out_proj"], gdn.epilogue(o, z, L["gdn_norm"], cfg.eps))
             else:
-                y = L["qkv_proj"](h)
+                y = lin(L["qkv_proj"], h)
                 q = ops.qkv_norm_rope_gated(y, H, K, D, L["q_norm"], L["k_norm"], cos, sin, cfg.eps, plus1=True)
                 kk = y[:, 2 * H * D : (2 * H + K) * D].view(n, K, D)
                 vv = y[:, (2 * H + K) * D :].view(n, K, D)
@@ -286,14 +291,14 @@ class QwenStack:
                     o = torch.zeros((n, H, D), dtype=o_s.dtype, device=o_s.device)
                     o[:R] = o_s.index_select(0, sidx)
                 ops.attn_gate(o, y, H, D)
-                m = L["o_proj"](o.view(n, H * D))
+                m = lin(L["o_proj"], o.view(n, H * D))
             r = ops.fused_norm(m, residual=x, w2=L["post_ln"], eps=cfg.eps, plus1=True, want_h=True, want_norm=True)
             x = r["h"]
             if w.fuse_glu:
-                act = L["gate_up"](r["norm"])
+                act = lin(L["gate_up"], r["norm"])
             else:
                 _, _, act = ops.glu_quant(L["gate_up"](r["norm"]), "silu", want_fp8=False, want_y=True)
-            d = L["down"](act)
+            d = lin(L["down"], act)
             last = i == self.n_layers - 1
             r = ops.fused_norm(d, residual=x, w2=None if last else w.layers[i + 1]["input_ln"], eps=cfg.eps, plus1=True, want_h=True,
                                want_norm=not last)

@@ -100,3 +100,33 @@ def test_w4_glu_epilogue_equals_the_separate_pass(dev, M, F, K, G, act):
     assert got.shape == (M, F) and torch.equal(got, want)
     with pytest.raises(RuntimeError):
         fused.fuse_glu(act)
+
+
+@pytest.mark.parametrize("M,N,K,G,E", [(36, 5120, 4096, 128, 0), (36, 5120, 17408, 128, 0), (120, 1024, 5120, 32, 64), (1, 256, 128, 128, 0),
+                                       (200, 6144, 2048, 64, 0), (36, 34816, 5120, 128, 0)])
+def test_w4_few_rows_with_k_slices(dev, M, N, K, G, E):
+    """Int4Linear.few (a decoding step): the kernel with K cut into slices for narrow projections, exact against the float64
+    product to bf16 rounding and within one bf16 step of forward on a few elements (wide ones run forward's kernel: equal)"""
+    from spinf_serve_b200 import ops
+    from spinf_serve_b200.linears import Int4Linear
+
+    qweight, scales = _gptq(N, K, G, 5)
+    g = torch.Generator().manual_seed(6)
+    x = torch.randn((M, K), generator=g).to(torch.bfloat16)
+    extra = (torch.randn((E, K), generator=g) * 0.05).to(torch.bfloat16) if E else None
+    lin = Int4Linear(qweight.to(dev), scales.to(dev))
+    if E:
+        lin.set_extra(extra.to(dev))
+    big, few = lin(x.to(dev)), lin.few(x.to(dev))
+    q, s = O.gptq_unpack(qweight, scales)
+    exact = O.int4_linear(x, q, s, G, extra, exact=True)
+    err = (few.cpu().double() - exact).abs()
+    assert bool((err <= exact.abs() * 2.0**-7 + exact.abs().max() * 2.0**-13).all())
+    d = (few.float() - big.float()).abs()
+    sliced = int(ops._lib.lib().spinf_w4_gemm_small_workspace_bytes(M, N, K)) > 0
+    print(f"w4 few {M}x{N}x{K}: K slices {'yes' if sliced else 'no'}, {(d > 0).float().mean().item():.4%} of elements differ from forward")
+    # sums that cancel to near zero move by more than one of their own bf16 steps: the bound is in steps of the row's scale
+    assert (d > 0).float().mean().item() < 0.01 and bool((d <= big.float().abs() * 2.0**-7 + big.float().abs().max() * 2.0**-12).all())
+    if not sliced:
+        assert torch.equal(few, big)
+    assert torch.equal(lin.few(x.to(dev)), few)  # run-to-run determinism
