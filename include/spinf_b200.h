@@ -63,6 +63,16 @@ int spinf_fp8_rowwise_quant(const void* x_bf16, int64_t M, int64_t K, void* x8, 
 int spinf_fp8_rowwise_gemm(const void* x8, const float* xs, const void* w8, const float* ws, void* y_bf16, int64_t M, int64_t N,
                            int64_t K, void* stream);
 
+/* The same linear for a decoding step's few rows (M <= 128; the linears of the extraction decoder's steps,
+ * spinf_serve/engine/decode.py:160-203, which the reference runs through the same torch._scaled_mm): the K dimension is cut into
+ * slices, a function of N and K only, so that every SM streams weights; fp32 partial sums go to `workspace` (16-byte aligned, at
+ * least spinf_fp8_rowwise_gemm_small_workspace_bytes), and a second launch adds them in slice order and applies the scales.
+ * Differs from spinf_fp8_rowwise_gemm in the order of the fp32 sum only; ws 16-byte aligned. M > 128, or a shape whose column
+ * tiles already cover the SMs (workspace bytes 0), runs spinf_fp8_rowwise_gemm. */
+int64_t spinf_fp8_rowwise_gemm_small_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int spinf_fp8_rowwise_gemm_small(const void* x8, const float* xs, const void* w8, const float* ws, void* y_bf16, int64_t M, int64_t N,
+                                 int64_t K, void* workspace, int64_t workspace_bytes, void* stream);
+
 /* ------------------------------------------------------------------------------------------------------------ fp8 per-tensor linears
  * The reference's Fp8Linear (dynamic) and Fp8StaticLinear (calibrated static activation scale, "fp8s"), both with one weight scale
  * per tensor (spinf_serve/quant/linears.py:66-119).

@@ -24,6 +24,8 @@ SIGNATURES = {
     "spinf_selftest_bounded_wait": (ctypes.c_int, [_i64, _p]),
     "spinf_fp8_rowwise_quant": (ctypes.c_int, [_p, _i64, _i64, _p, _p, _p]),
     "spinf_fp8_rowwise_gemm": (ctypes.c_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _p]),
+    "spinf_fp8_rowwise_gemm_small_workspace_bytes": (_i64, [_i64, _i64, _i64]),
+    "spinf_fp8_rowwise_gemm_small": (ctypes.c_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _p, _i64, _p]),
     "spinf_abs_max": (ctypes.c_int, [_p, _i64, _p, _p]),
     "spinf_fp8_tensor_quant": (ctypes.c_int, [_p, _i64, _p, _i32, _p, _p, _p, _p]),
     "spinf_fp8_tensor_gemm": (ctypes.c_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _p]),

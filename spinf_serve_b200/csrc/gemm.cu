@@ -493,7 +493,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
     SPINF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN>::TOTAL));
     attr_set[dev].store(true, std::memory_order_release);
   }
-  const int tiles = shape.tiles_m * shape.tiles_n;
+  const int tiles = shape.tiles_m * shape.tiles_n * (EpiSplitK<Epi>::value ? shape.splits : 1);
   const int grid = tiles < sm_count() ? tiles : sm_count();
   kern<<<grid, 192, GemmSmem<BN>::TOTAL, stream>>>(tmA, tmB, shape, epi, status);
   SPINF_CUDA_OK(cudaGetLastError());
@@ -514,7 +514,47 @@ static GemmShape make_shape(int64_t M, int64_t N, int64_t K, int BN, int elem_by
   const int64_t per_tile = 128 * K * elem_bytes;
   const int64_t g = (32ll << 20) / (per_tile > 0 ? per_tile : 1);
   s.group_m = static_cast<int>(g < 8 ? 8 : (g > 64 ? 64 : g));
+  s.splits = 1;
+  s.kb_per = 0;
   return s;
+}
+
+// K slices of the few-row fp8 linear: as many as put one (128-column tile, slice) unit on every SM, each at least 24 K blocks
+// (3 072 elements) long: below that the second launch costs what the slices save (measured inside a CUDA graph at 120 rows:
+// 3 840 x 15 360 38.7 -> 20.4 us in four slices, 3 840 x 4 096 13.8 -> 14.2 us). A function of N and K only.
+static int fp8_small_splits(int64_t N, int64_t K, int* kb_per_out) {
+  const int tiles_n = static_cast<int>((N + 127) / 128), num_kb = static_cast<int>((K + 127) / 128);
+  int s = sm_count() / tiles_n;
+  s = s > num_kb / 24 ? num_kb / 24 : s;
+  s = s > 16 ? 16 : s;
+  if (s < 2) {
+    *kb_per_out = num_kb;
+    return 1;
+  }
+  const int kb_per = (num_kb + s - 1) / s;
+  *kb_per_out = kb_per;
+  return (num_kb + kb_per - 1) / kb_per;
+}
+
+// y[m, n] = bf16((sum over slices, in slice order, of part[s][m][n]) * xs[m] * ws[n]), four columns per thread
+__global__ void __launch_bounds__(256) fp8_small_sum_kernel(const float* __restrict__ part, int splits, int M, int N,
+                                                            const float* __restrict__ xs, const float* __restrict__ ws,
+                                                            __nv_bfloat16* __restrict__ y) {
+  const int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+  const int64_t MN = static_cast<int64_t>(M) * N;
+  if (i >= MN) return;
+  float4 acc = *reinterpret_cast<const float4*>(part + i);
+  for (int k = 1; k < splits; ++k) {
+    const float4 p = *reinterpret_cast<const float4*>(part + k * MN + i);
+    acc.x += p.x, acc.y += p.y, acc.z += p.z, acc.w += p.w;
+  }
+  const int m = static_cast<int>(i / N), n = static_cast<int>(i % N);
+  const float rs = xs[m];
+  const float4 cs = *reinterpret_cast<const float4*>(ws + n);
+  uint2 out;
+  out.x = pack_bf16x2((acc.x * rs) * cs.x, (acc.y * rs) * cs.y);
+  out.y = pack_bf16x2((acc.z * rs) * cs.z, (acc.w * rs) * cs.w);
+  *reinterpret_cast<uint2*>(y + i) = out;
 }
 
 }  // namespace spinf
@@ -579,6 +619,45 @@ extern "C" int spinf_fp8_rowwise_gemm(const void* x8, const float* xs, const voi
   // stream on twice as many SMs (the same sums in the same order: a tile's width changes no element)
   if (M <= 128 && N / 256 < sm_count()) return fp8_rowwise_gemm_bn<128>(x8, xs, w8, ws, y_bf16, M, N, K, stream);
   return fp8_rowwise_gemm_bn<256>(x8, xs, w8, ws, y_bf16, M, N, K, stream);
+}
+
+// bytes of workspace spinf_fp8_rowwise_gemm_small needs (0: the shape runs unsplit)
+extern "C" int64_t spinf_fp8_rowwise_gemm_small_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  if (M <= 0 || M > 128 || N <= 0 || K <= 0) return 0;
+  int kb_per;
+  const int s = spinf::fp8_small_splits(N, K, &kb_per);
+  return s > 1 ? static_cast<int64_t>(s) * M * N * 4 : 0;
+}
+
+// spinf_fp8_rowwise_gemm for a decoding step's few rows (M <= 128): the K dimension is cut into slices so that every SM streams
+// weights; fp32 partial sums go to `workspace`, a second kernel adds them in slice order and applies the scales. Differs from
+// spinf_fp8_rowwise_gemm in the order of the fp32 sum only. More rows, or a shape that needs no split, run the plain kernel.
+extern "C" int spinf_fp8_rowwise_gemm_small(const void* x8, const float* xs, const void* w8, const float* ws, void* y_bf16, int64_t M,
+                                            int64_t N, int64_t K, void* workspace, int64_t workspace_bytes, void* stream) {
+  using namespace spinf;
+  if (M == 0) return 0;
+  const int64_t need = spinf_fp8_rowwise_gemm_small_workspace_bytes(M, N, K);
+  if (need == 0) return spinf_fp8_rowwise_gemm(x8, xs, w8, ws, y_bf16, M, N, K, stream);
+  SPINF_CHECK_ARG(x8 && xs && w8 && ws && y_bf16 && K % 16 == 0 && N % 16 == 0 && N < (1ll << 31) && K < (1ll << 31));
+  SPINF_CHECK_ARG(workspace && workspace_bytes >= need && reinterpret_cast<uintptr_t>(workspace) % 16 == 0);
+  SPINF_CHECK_ARG(reinterpret_cast<uintptr_t>(ws) % 16 == 0);
+  constexpr int BN = 128;
+  CUtensorMap tmA, tmB;
+  EpiPartial<BN> epi;
+  int r;
+  if ((r = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x8, M, K, K, 128, 128))) return r;
+  if ((r = make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w8, N, K, K, 128, BN))) return r;
+  epi.part = static_cast<float*>(workspace);
+  GemmShape shape = make_shape(M, N, K, BN);
+  shape.splits = fp8_small_splits(N, K, &shape.kb_per);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if ((r = launch_gemm<KIND_F8, BN>(tmA, tmB, shape, epi, st))) return r;
+  const int64_t quads = M * N / 4;
+  fp8_small_sum_kernel<<<static_cast<unsigned>((quads + 255) / 256), 256, 0, st>>>(epi.part, shape.splits, static_cast<int>(M),
+                                                                                   static_cast<int>(N), xs, ws,
+                                                                                   static_cast<__nv_bfloat16*>(y_bf16));
+  SPINF_CUDA_OK(cudaGetLastError());
+  return 0;
 }
 
 extern "C" int spinf_abs_max(const void* x_bf16, int64_t n, float* out, void* stream) {

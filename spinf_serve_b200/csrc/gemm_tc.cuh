@@ -11,7 +11,9 @@
 //            epilogue functor, so tile i's epilogue overlaps tile i+1's main loop
 //
 // Batch invariance: every output element is the sum over K in ascending order inside one CTA (no split-K, no stream-K), with a
-// tile shape that does not depend on M, so a row of C is bit-identical whatever other rows are in the call.
+// tile shape that does not depend on M, so a row of C is bit-identical whatever other rows are in the call. The one exception is
+// an epilogue that declares kSplitK (a decoding step's few rows): its work units are (tile, K slice) pairs that leave fp32
+// partial sums, added in slice order by a second kernel; the slicing depends on N and K only, so rows stay independent there too.
 #pragma once
 #include "common.cuh"
 
@@ -23,6 +25,19 @@ struct GemmShape {
   int M, N, K;
   int tiles_m, tiles_n;
   int group_m;  // rasterisation: tiles are walked in groups of `group_m` row-tiles, column-tile fastest inside a group
+  // K slices (only read by kernels whose epilogue declares kSplitK): a work unit is (tile, slice), slice = unit % splits covers
+  // the K blocks [slice * kb_per, min(num_kb, (slice + 1) * kb_per))
+  int splits, kb_per;
+};
+
+// an epilogue that declares `static constexpr bool kSplitK = true` receives K slices (its State has a member `ks`)
+template <class E, class = void>
+struct EpiSplitK {
+  static constexpr bool value = false;
+};
+template <class E>
+struct EpiSplitK<E, decltype(void(E::kSplitK))> {
+  static constexpr bool value = E::kSplitK;
 };
 
 template <int BN>
@@ -104,8 +119,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_p;
 
-  const int num_tiles = shape.tiles_m * shape.tiles_n;
+  constexpr bool SPLIT = EpiSplitK<Epi>::value;
+  const int splits = SPLIT ? shape.splits : 1;
+  const int num_tiles = shape.tiles_m * shape.tiles_n * splits;
   const int num_kb = (shape.K + KE - 1) / KE;
+  const int kb_per = SPLIT ? shape.kb_per : num_kb;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -113,8 +131,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int tm, tn;
-        tile_coords(shape, tile, tm, tn);
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        tile_coords(shape, SPLIT ? tile / splits : tile, tm, tn);
+        const int kb0 = SPLIT ? (tile % splits) * kb_per : 0, kb1 = min(num_kb, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
           if (!mbar_wait(wc, &empty[s], ph ^ 1u, ST_TIMEOUT_EMPTY)) { ok = false; break; }
           mbar_expect_tx(&full[s], L::STAGE_BYTES);
@@ -141,7 +160,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (!mbar_wait(wc, &acc_empty[ab], aph ^ 1u, ST_TIMEOUT_TMEM)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + ab * BN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int kb0 = SPLIT ? (tile % splits) * kb_per : 0, kb1 = min(num_kb, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
           if (!mbar_wait(wc, &full[s], ph, ST_TIMEOUT_FULL)) { ok = false; break; }
           tc_fence_after();
@@ -152,11 +172,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           for (int k = 0; k < 4; ++k) {
             // 32 bytes along K per step: +2 in the descriptor's 16-byte address units
             if (KIND == KIND_F8)
-              umma_f8_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, IDESC, (kb | k) != 0);
+              umma_f8_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, IDESC, ((kb - kb0) | k) != 0);
             else if (KIND == KIND_S8)
-              umma_i8_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, IDESC, (kb | k) != 0);
+              umma_i8_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, IDESC, ((kb - kb0) | k) != 0);
             else
-              umma_f16_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, IDESC, (kb | k) != 0);
+              umma_f16_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, IDESC, ((kb - kb0) | k) != 0);
           }
           umma_commit(&empty[s]);
         }
@@ -171,7 +191,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     typename Epi::State est{};
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
       int tm, tn;
-      tile_coords(shape, tile, tm, tn);
+      tile_coords(shape, SPLIT ? tile / splits : tile, tm, tn);
+      if constexpr (SPLIT) est.ks = tile % splits;
       const uint32_t ab = tcount & 1u, aph = (tcount >> 1) & 1u;
       __syncwarp();
       epi.begin_tile(est, shape, tm, tn, et, colscale);
@@ -285,6 +306,32 @@ struct EpiStoreBf16 {
   __device__ __forceinline__ void finish(State&, int et) const {
     if (et == 0) tma_store_wait_all<0>();
   }
+};
+
+// fp32 partial sums of one K slice: part[ks][m][n] (the epilogue of the few-row split; scales and rounding happen in the kernel
+// that adds the slices)
+template <int BN>
+struct EpiPartial {
+  static constexpr bool kReadsTmemInEnd = false;
+  static constexpr bool kSplitK = true;
+  float* part;  // [splits, M, N]
+  struct State {
+    int ks;
+  };
+  __device__ __forceinline__ void begin_tile(State&, const GemmShape&, int, int, int, float*) const {}
+  __device__ __forceinline__ void chunk(State& st, const GemmShape& s, int tm, int tn, int row, int, int c, const uint32_t (&v0)[32],
+                                        const uint32_t (&v1)[32], const float*, uint8_t*, uint32_t) const {
+    const int m = tm * 128 + row, n0 = tn * BN + c * 64;
+    if (m >= s.M) return;
+    float* dst = part + (static_cast<size_t>(st.ks) * s.M + m) * s.N + n0;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const uint32_t* v = j < 8 ? &v0[4 * j] : &v1[4 * (j - 8)];
+      if (n0 + 4 * j < s.N) *reinterpret_cast<uint4*>(dst + 4 * j) = make_uint4(v[0], v[1], v[2], v[3]);
+    }
+  }
+  __device__ __forceinline__ void end_tile(State&, const GemmShape&, int, int, int, int, uint32_t, const float*) const {}
+  __device__ __forceinline__ void finish(State&, int) const {}
 };
 
 }  // namespace spinf

@@ -288,6 +288,8 @@ class GemmaStack:
         n = ids.numel()
         row = w.scheme == "fp8row"
         fp8 = w.scheme in ("fp8row", "fp8", "fp8s")
+        # a decoding step's few rows: the narrow projections run with their K dimension cut into slices
+        row_gemm = ops.fp8_rowwise_gemm_small if attend is not None and n <= 128 else ops.fp8_rowwise_gemm
         tables = {k: ops.rope_table(pos, f) for k, f in self.inv_freq.items()}
         h = ops.embed_scale(ids, w.embed, self.embed_scale)
         if self.n_layers == 0:
@@ -322,7 +324,7 @@ class GemmaStack:
                 a = attention.tree_attention(q, k, v, masks[kind], 1.0, row_amax=amax)  # scaling = 1.0: q and k are normed
             if row:  # the tree attention kernel has already found the row maxima
                 a8, a_s = ops.fp8_quant_from_amax(a.view(n, H * D), amax) if amax is not None else ops.fp8_rowwise_quant(a.view(n, H * D))
-                o = ops.fp8_rowwise_gemm(a8, a_s, L["o_w"], L["o_s"])
+                o = row_gemm(a8, a_s, L["o_w"], L["o_s"])
             else:
                 o = self._linear(a.view(n, H * D), L, "o", ("o",))
             r = ops.fused_norm(o, w1=L["post_attn_ln"], residual=h, w2=L["pre_ffn_ln"], eps=cfg.eps, want_h=True, want_fp8=row,
@@ -330,7 +332,7 @@ class GemmaStack:
             h = r["h"]
             if row:
                 g8, g_s, _ = ops.fp8_gemm_glu(r["x8"], r["xs"], L["gu_w"], L["gu_s"], "gelu_tanh")
-                d = ops.fp8_rowwise_gemm(g8, g_s, L["down_w"], L["down_s"])
+                d = row_gemm(g8, g_s, L["down_w"], L["down_s"])
             else:
                 gu = self._linear(r["norm"], L, "gu", ("gate", "up"))
                 d = self._linear(ops.glu_quant(gu, "gelu_tanh", want_fp8=False, want_y=True)[2], L, "down", ("down",))

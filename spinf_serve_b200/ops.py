@@ -72,6 +72,34 @@ def fp8_rowwise_gemm(x8, xs, w8, ws, out=None):
     return y
 
 
+def fp8_rowwise_gemm_small(x8, xs, w8, ws, workspace=None):
+    """fp8_rowwise_gemm for a decoding step's few rows (M <= 128): the K dimension is cut into slices where the column tiles alone
+    do not occupy the GPU, the slices' fp32 sums added in order before the scales and the rounding (may differ from
+    fp8_rowwise_gemm in the last bf16 bit). workspace: optional uint8 tensor reused between calls."""
+    _need(x8, FP8, "x8", 2)
+    _need(w8, FP8, "w8", 2)
+    xs1, ws1 = xs.reshape(-1), ws.reshape(-1)
+    _need(xs1, torch.float32, "xs", 1)
+    _need(ws1, torch.float32, "ws", 1)
+    M, K = x8.shape
+    N = w8.shape[0]
+    if w8.shape[1] != K or xs1.numel() != M or ws1.numel() != N:
+        raise SpinfError("fp8_rowwise_gemm_small: shapes do not agree")
+    need = int(_lib.lib().spinf_fp8_rowwise_gemm_small_workspace_bytes(M, N, K))
+    if not need:
+        return fp8_rowwise_gemm(x8, xs, w8, ws)
+    if workspace is None or workspace.numel() < need:
+        workspace = torch.empty(need, dtype=torch.uint8, device=x8.device)
+    y = torch.empty((M, N), dtype=torch.bfloat16, device=x8.device)
+    check(
+        _lib.lib().spinf_fp8_rowwise_gemm_small(ptr(x8), ptr(xs1), ptr(w8), ptr(ws1), ptr(y), M, N, K, ptr(workspace), workspace.numel(),
+                                                stream_ptr()),
+        "spinf_fp8_rowwise_gemm_small",
+    )
+    COUNTS["launches"] += 2
+    return y
+
+
 def fp8_tensor_quant(x, scale=None, peak=None, want_amax=False):
     """per-tensor fp8 quantisation of x [..., K] bf16 -> (x8 [M, K] e4m3, s fp32 scalar on the device).
     scale = None: dynamic, s = max(max|x|, 1e-12) / 448 (quant_act, spinf_serve/quant/linears.py:22-26; two kernels, no host

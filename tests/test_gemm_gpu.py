@@ -55,6 +55,33 @@ def test_fp8_rowwise_gemm_vs_oracle(dev, M, N, K):
     assert mism < 0.05  # same value up to the last bf16 bit on almost every element
 
 
+# the 12B-class down and o projections at a decoding step's rows (the second too short to slice), a ragged last slice and
+# ragged column tile, one row
+@pytest.mark.parametrize("M,N,K", [(120, 3840, 15360), (120, 3840, 4096), (36, 1072, 15104), (128, 304, 208), (1, 2048, 12288)])
+def test_fp8_few_rows_with_k_slices(dev, M, N, K):
+    """the few-row entry point: same bound against the exact product as the plain kernel, rows independent of their neighbours,
+    run-to-run identical"""
+    from spinf_serve_b200 import ops
+
+    x = _rand((M, K), 12)
+    w = _rand((N, K), 13, 0.02)
+    w8, ws = O.quantize_weight_rowwise(w)
+    x8, xs = O.quant_act_row(x)
+    d8, ds, dw, dws = x8.to(dev), xs.to(dev), w8.to(dev), ws.to(dev)
+    y = ops.fp8_rowwise_gemm_small(d8, ds, dw, dws)
+    exact = O.scaled_mm_rowwise(x8, xs, w8, ws, exact=True)
+    err = (y.cpu().double() - exact).abs()
+    tol = exact.abs() * 2.0**-7 + exact.abs().max() * 2.0**-14
+    assert bool((err <= tol).all()), f"max err {err.max():.3e} at |ref| {exact.abs().max():.3e}"
+    plain = ops.fp8_rowwise_gemm(d8, ds, dw, dws)
+    mism = (y != plain).float().mean().item()
+    print(f"fp8 few rows {M}x{N}x{K}: differs from the unsliced kernel on {mism:.4%} of the elements")
+    assert mism < 0.05
+    assert torch.equal(ops.fp8_rowwise_gemm_small(d8, ds, dw, dws), y)
+    one = ops.fp8_rowwise_gemm_small(d8[:1].contiguous(), ds[:1].contiguous(), dw, dws)
+    assert torch.equal(one, y[:1])  # the slicing does not depend on M
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (3, 512, 128), (300, 3840, 4096), (1000, 1024, 5120)])
 def test_bf16_gemm_vs_oracle(dev, M, N, K):
     from spinf_serve_b200 import ops
