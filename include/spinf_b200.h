@@ -222,7 +222,7 @@ int spinf_option_logprobs_static(const void* h, const void* W, int64_t R, int64_
                                  int64_t n_cols, float softcap, float* out, int32_t* status, void* stream);
 
 /* ------------------------------------------------------------------------------------------------------------ tree-mask attention
- * Host function. Replaces packer.block_tables (spinf_serve/packer.py:426-491) for text-only streams: from the per-token arrays of
+ * Host function. Replaces packer.block_tables (spinf_serve/packer.py:426-491): from the per-token arrays of
  * a packed stream (art, end, pos: int32 [n], n a multiple of 128) builds, for each 128-row query block, the ascending list of
  * 128-column key blocks it must visit and a flag byte per entry: bit 0 = "full" in the reference's classification (every pair
  * attends; never set on the sliding table), bit 1 = the kernel may skip the mask evaluation (every pair attends, window included).
@@ -232,12 +232,28 @@ int spinf_option_logprobs_static(const void* h, const void* W, int64_t R, int64_
 int64_t spinf_tile_desc_build_host(const int32_t* art_host, const int32_t* end_host, const int32_t* pos_host, int64_t n,
                                    int32_t window, int32_t* counts_host, int32_t* blocks_host, uint8_t* flags_host);
 
+/* The same for streams with images (block_tables' `grp` argument, packer.py:455-467,479,485): grp_host [n] int32 = the image a
+ * placeholder token belongs to, -1 elsewhere (NULL: a text-only stream). A sliding-table tile is kept when its two blocks share an
+ * image even if the window would skip it, and a query block also visits the LATER key blocks of its images (partial tiles, listed
+ * after the diagonal, ascending). */
+int64_t spinf_tile_desc_build_host_img(const int32_t* art_host, const int32_t* end_host, const int32_t* pos_host, const int32_t* grp_host,
+                                       int64_t n, int32_t window, int32_t* counts_host, int32_t* blocks_host, uint8_t* flags_host);
+
 /* The mask rule of the packed stream (spinf_serve/scorer.py:173-177, the mask_mod the reference hands to create_block_mask) evaluated
  * once per stream and mask type instead of once per layer and head: for entry e of the packed tile lists, key half hf (0 / 1) and
  * row r of the entry's query block, bit c of bits[(e * 2 + hf) * 128 + r] = visible(128 qb + r, 128 j + 64 hf + c) as defined below.
  * art / end / pos, tile_offsets / tile_blocks on the device; bits: 2 * 128 * (number of entries) uint64 on the device. */
 int spinf_tile_mask_bits(const int32_t* art, const int32_t* end, const int32_t* pos, int64_t n, int32_t window,
                          const int32_t* tile_offsets, const int32_t* tile_blocks, uint64_t* bits, void* stream);
+
+/* The mask rules of streams with images (spinf_serve/scorer.py:178-198, the `full_img` / `sliding_img` mask_mods): visible(t, k) of
+ * spinf_tile_mask_bits, or grp[t] >= 0 && grp[k] == grp[t] (an image's placeholder tokens see each other both ways), with
+ * grp_in_window != 0 only when also pos[t] - pos[k] < window (the sliding layers of models whose global layers stay causal: those
+ * pass grp = NULL for their full-attention table). grp [n] int32 on the device, NULL = spinf_tile_mask_bits. The tile lists must
+ * come from spinf_tile_desc_build_host_img with the same grp. */
+int spinf_tile_mask_bits_img(const int32_t* art, const int32_t* end, const int32_t* pos, const int32_t* grp, int64_t n, int32_t window,
+                             int32_t grp_in_window, const int32_t* tile_offsets, const int32_t* tile_blocks, uint64_t* bits,
+                             void* stream);
 
 /* Replaces the "tree_flex" attention interface (spinf_serve/models/gemma4.py:99-121, mask rule spinf_serve/scorer.py:173-177) and
  * qwen.tree_attention (spinf_serve/models/qwen35/qwen.py:605-623):

@@ -105,7 +105,7 @@ def quantize(W, scheme="fp8row"):
 
 
 def forward(cfg: GemmaConfig, W, Q, ids, art, end, pos, n_layers=None, taps=None, scheme="fp8row", scales=None, amax=None, peaks=None,
-            attend=None):
+            attend=None, grp=None, bidir_all=True, media=()):
     """packed forward -> final hidden states [n, hidden] bf16 (after the model's last norm), the oracle of Gemma4Stack.forward
     (spinf_serve/models/gemma4.py:407-415). taps: optional dict filled with intermediate tensors for operator-level checks.
     scheme: fp8row (Fp8RowLinear), fp8 (Fp8Linear: dynamic per-tensor), fp8s (Fp8StaticLinear with scales[i][name]), w8a8 / w8a16
@@ -113,7 +113,9 @@ def forward(cfg: GemmaConfig, W, Q, ids, art, end, pos, n_layers=None, taps=None
     amax: optional list of per-layer dicts updated with the largest |input| of every linear (what the reference's calibration
     hooks record, quant/calibrate.py:117-124); peaks: the same for the static scheme's monitor (max|x| / (448 scale)).
     attend(layer, kind, q, k, v) -> [n, H, D]: another attention in place of the tree attention (a decoding step, where
-    transformers' layers call the "x_decode" interface instead: spinf_serve/decode.py:359-377); art / end are unused then."""
+    transformers' layers call the "x_decode" interface instead: spinf_serve/decode.py:359-377); art / end are unused then.
+    Streams with images: grp (Batch.grp) and bidir_all select the full_img / sliding_img mask rules (spinf_serve/scorer.py:178-198);
+    media = [(start, embeds [m, hidden])]: rows laid over the placeholders' embeddings, not scaled (gemma4.py:410-413)."""
     n = len(ids)
     H, K, D = cfg.heads, cfg.kv_heads, cfg.head_dim
     layer = [0]
@@ -135,6 +137,8 @@ def forward(cfg: GemmaConfig, W, Q, ids, art, end, pos, n_layers=None, taps=None
         return y
 
     h = W["embed"][torch.as_tensor(np.asarray(ids), dtype=torch.int64)] * torch.tensor(cfg.hidden**0.5).to(torch.bfloat16)
+    for start, e in media:
+        h[start : start + len(e)] = e.to(h.dtype)
     tables = {"sliding_attention": rope_tables(pos, D, cfg.theta_sliding), "full_attention": rope_tables(pos, D, cfg.theta_full)}
     for i in range(cfg.layers if n_layers is None else n_layers):
         L, q8 = W["layers"][i], Q[i]
@@ -150,7 +154,8 @@ def forward(cfg: GemmaConfig, W, Q, ids, art, end, pos, n_layers=None, taps=None
         if attend is not None:
             a = attend(i, kind, q, k, v)
         else:
-            a = OA.tree_attention(q, k, v, art, end, pos, 1.0, window).to(torch.bfloat16)  # the model passes scaling = 1.0
+            g = grp if (bidir_all or window) else None  # global layers stay causal when the images' blocks are sliding-only
+            a = OA.tree_attention(q, k, v, art, end, pos, 1.0, window, grp=g, grp_in_window=not bidir_all).to(torch.bfloat16)  # scaling = 1.0
         o = lin(a.reshape(n, H * D), "o", q8)
         h = h + rmsnorm(o, L["post_attn_ln"], cfg.eps)
         x = rmsnorm(h, L["pre_ffn_ln"], cfg.eps)

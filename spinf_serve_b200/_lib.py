@@ -43,6 +43,7 @@ SIGNATURES = {
     "spinf_option_logprobs": (ctypes.c_int, [_p, _p, _i64, _i64, _i64, _p, _i64, _f32, _p, _p, _i64, _p]),
     "spinf_option_logprobs_static": (ctypes.c_int, [_p, _p, _i64, _i64, _i64, _p, _i64, _f32, _p, _p, _p]),
     "spinf_tile_desc_build_host": (_i64, [_p, _p, _p, _i64, _i32, _p, _p, _p]),
+    "spinf_tile_desc_build_host_img": (_i64, [_p, _p, _p, _p, _i64, _i32, _p, _p, _p]),
     "spinf_fused_norm": (ctypes.c_int, [_p, _p, _p, _p, _p, _i64, _i64, _f32, _i32, _p, _p, _p, _p, _p]),
     "spinf_qkv_norm_rope": (ctypes.c_int, [_p, _i64, _i64, _i32, _i32, _i32, _p, _p, _p, _p, _i32, _f32, _i32, _i32, _p]),
     "spinf_qkv_norm_rope_gated": (ctypes.c_int, [_p, _i64, _i64, _i32, _i32, _i32, _p, _p, _p, _p, _i32, _f32, _i32, _p, _p]),
@@ -79,6 +80,7 @@ SIGNATURES = {
         [_p, _p, _p, _p, _i64, _i32, _i32, _i32, _i64, _i64, _i64, _p, _p, _p, _i32, _f32, _p, _p, _p, _p, _p, _p],
     ),
     "spinf_tile_mask_bits": (ctypes.c_int, [_p, _p, _p, _i64, _i32, _p, _p, _p, _p]),
+    "spinf_tile_mask_bits_img": (ctypes.c_int, [_p, _p, _p, _p, _i64, _i32, _i32, _p, _p, _p, _p]),
 }
 
 ERRORS = {

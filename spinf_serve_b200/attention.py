@@ -42,6 +42,8 @@ class HostTiles:
     window: int
     full: "packer.TileDesc"
     sliding: "packer.TileDesc | None"
+    grp: "np.ndarray | None" = None  # streams with images: the image of every placeholder token, -1 elsewhere
+    bidir_all: bool = True           # images' bidirectional blocks on every layer, past the window; False: sliding layers only, within it
 
     @property
     def n(self) -> int:
@@ -50,6 +52,8 @@ class HostTiles:
     def arrays(self) -> dict:
         """name -> array, everything the device half needs (one staging copy carries them all)"""
         out = {"art": self.art, "end": self.end, "pos32": self.pos}
+        if self.grp is not None:
+            out["grp"] = self.grp
         for name, td in (("full", self.full), ("sliding", self.sliding)):
             if td is not None:
                 out[name + ".offsets"] = td.offsets
@@ -58,18 +62,24 @@ class HostTiles:
         return out
 
 
-def host_tiles(art, end, pos, window, always_window=True) -> HostTiles:
+def host_tiles(art, end, pos, window, always_window=True, grp=None, bidir_all=True) -> HostTiles:
     """the tile lists of one packed stream as Scorer._block_masks takes them from block_tables (spinf_serve/scorer.py:207-238,
     packer.py:426-491): the sliding table is used when a position reaches the window or always_window is set (aligned jobs),
-    else sliding layers share the full table. Host work only (the library's C++ descriptor builder)."""
+    else sliding layers share the full table. grp: Batch.grp of a stream with images (None: text only); bidir_all: which layers
+    give an image's placeholders their two-way block (the reference's model._vision_bidir_all, scorer.py:178-198). Host work only
+    (the library's C++ descriptor builder)."""
     art = np.ascontiguousarray(art, np.int32)
     end = np.ascontiguousarray(end, np.int32)
     pos = np.ascontiguousarray(pos, np.int32)
+    grp = None if grp is None else np.ascontiguousarray(grp, np.int32)
     n = len(art)
     if n % packer.BLOCK:
         raise SpinfError(f"stream length {n} is not a multiple of {packer.BLOCK}")
+    if grp is not None and len(grp) != n:
+        raise SpinfError("grp does not cover the stream")
     binding = window is not None and (always_window or (n > 0 and int(pos.max()) >= window))
-    return HostTiles(art, end, pos, int(window or 0), packer.tile_desc(art, end, pos, None), packer.tile_desc(art, end, pos, window) if binding else None)
+    return HostTiles(art, end, pos, int(window or 0), packer.tile_desc(art, end, pos, None, grp),
+                     packer.tile_desc(art, end, pos, window, grp) if binding else None, grp, bool(bidir_all))
 
 
 def device_masks(ht: HostTiles, st: dict, device) -> dict:
@@ -77,27 +87,35 @@ def device_masks(ht: HostTiles, st: dict, device) -> dict:
     stream). Evaluates the mask rule once per layer type (spinf_tile_mask_bits): every layer of the type and every head reads
     those words. -> {"full_attention": TileMask, "sliding_attention": TileMask}"""
     n = ht.n
+    grp = st["grp"] if ht.grp is not None else None
 
-    def one(name, td, w):
+    def one(name, td, w, g, in_window):
         d_off, d_blocks, d_flags = st[name + ".offsets"], st[name + ".blocks"], st[name + ".flags"]
         bits = torch.empty((d_blocks.numel(), 2, packer.BLOCK), dtype=torch.int64, device=device)
         if n:
             check(
-                _lib.lib().spinf_tile_mask_bits(ptr(st["art"]), ptr(st["end"]), ptr(st["pos32"]), n, int(w), ptr(d_off), ptr(d_blocks), ptr(bits),
-                                                stream_ptr()),
-                "spinf_tile_mask_bits",
+                _lib.lib().spinf_tile_mask_bits_img(ptr(st["art"]), ptr(st["end"]), ptr(st["pos32"]), ptr(g), n, int(w), int(in_window),
+                                                    ptr(d_off), ptr(d_blocks), ptr(bits), stream_ptr()),
+                "spinf_tile_mask_bits_img",
             )
             ops.COUNTS["launches"] += 1
         return TileMask(st["art"], st["end"], st["pos32"], d_off, d_blocks, d_flags, bits, int(w), n, td.visited, td.skipped_fraction)
 
-    full = one("full", ht.full, 0)
-    return {"full_attention": full, "sliding_attention": one("sliding", ht.sliding, ht.window) if ht.sliding is not None else full}
+    # images: every layer, past the window (bidir_all), or the sliding layers only and within the window (scorer.py:186-198)
+    full = one("full", ht.full, 0, grp if ht.bidir_all else None, 0)
+    if ht.sliding is not None:
+        sliding = one("sliding", ht.sliding, ht.window, grp, 0 if ht.bidir_all else 1)
+    elif grp is not None and not ht.bidir_all:  # no position reaches the window: the full table with the sliding layers' rule
+        sliding = one("full", ht.full, ht.window, grp, 1)
+    else:
+        sliding = full
+    return {"full_attention": full, "sliding_attention": sliding}
 
 
-def stream_masks(art, end, pos, window, device, always_window=True):
+def stream_masks(art, end, pos, window, device, always_window=True, grp=None, bidir_all=True):
     """host_tiles + device_masks in one call, each array going up through pinned memory on the current stream (one-off streams:
     tests, calibration; the scorer stages a forward's arrays in one copy instead)"""
-    ht = host_tiles(art, end, pos, window, always_window)
+    ht = host_tiles(art, end, pos, window, always_window, grp, bidir_all)
     st = {k: torch.from_numpy(a).pin_memory().to(device, non_blocking=True) for k, a in ht.arrays().items()}
     return device_masks(ht, st, device)
 

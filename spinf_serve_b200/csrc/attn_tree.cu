@@ -557,16 +557,19 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 // Visibility words of a packed stream: for list entry e (query block qb against key block j), key half hf and row r of the query
 // block, bit c of bits[(e * 2 + hf) * 128 + r] says whether query t = 128 qb + r sees key k = 128 j + 64 hf + c:
 //   (k <= t && art[t] >= 0 && art[k] == art[t] && t < end[k] && (window <= 0 || pos[t] - pos[k] < window)) || t == k
+//   || (grp && grp[t] >= 0 && grp[k] == grp[t] && (!grp_in_window || window <= 0 || pos[t] - pos[k] < window))
+// (the last line: an image's placeholder tokens see each other both ways, spinf_serve/scorer.py:178-198).
 // One CTA per query block, thread = (row, half). Runs once per stream and mask type; every layer and head reads the result.
 __global__ void __launch_bounds__(256) tile_mask_bits_kernel(const int32_t* __restrict__ art, const int32_t* __restrict__ end,
-                                                             const int32_t* __restrict__ pos, int nb, int window,
-                                                             const int32_t* __restrict__ tile_offsets,
+                                                             const int32_t* __restrict__ pos, const int32_t* __restrict__ grp, int nb,
+                                                             int window, int grp_in_window, const int32_t* __restrict__ tile_offsets,
                                                              const int32_t* __restrict__ tile_blocks, uint64_t* __restrict__ bits) {
-  __shared__ int k_art[128], k_end[128], k_pos[128];
+  __shared__ int k_art[128], k_end[128], k_pos[128], k_grp[128];
   const int qb = blockIdx.x;
   const int r = threadIdx.x & 127, hf = threadIdx.x >> 7;
   const int t = qb * 128 + r;
   const int art_q = art[t], pos_q = pos[t];
+  const int grp_q = grp ? grp[t] : -1;
   const int e0 = tile_offsets[qb], e1 = tile_offsets[qb + 1];
   for (int e = e0; e < e1; ++e) {
     const int j = tile_blocks[e];
@@ -576,6 +579,7 @@ __global__ void __launch_bounds__(256) tile_mask_bits_kernel(const int32_t* __re
       k_art[threadIdx.x] = art[j * 128 + threadIdx.x];
       k_end[threadIdx.x] = end[j * 128 + threadIdx.x];
       k_pos[threadIdx.x] = pos[j * 128 + threadIdx.x];
+      k_grp[threadIdx.x] = grp ? grp[j * 128 + threadIdx.x] : -1;
     }
     __syncthreads();
     uint64_t word = 0;
@@ -585,7 +589,8 @@ __global__ void __launch_bounds__(256) tile_mask_bits_kernel(const int32_t* __re
         const int k = j * 128 + kk;
         const bool tree = k <= t && art_q >= 0 && k_art[kk] == art_q && t < k_end[kk];
         const bool win = window <= 0 || pos_q - k_pos[kk] < window;
-        if ((tree && win) || k == t) word |= 1ull << c;
+        const bool img = grp_q >= 0 && k_grp[kk] == grp_q && (!grp_in_window || win);
+        if ((tree && win) || k == t || img) word |= 1ull << c;
       }
     }
     bits[(static_cast<int64_t>(e) * 2 + hf) * 128 + r] = word;
@@ -640,14 +645,21 @@ static int launch_attn(const void* q, const void* k, const void* v, int64_t n, i
 
 using namespace spinf;
 
-extern "C" int spinf_tile_mask_bits(const int32_t* art, const int32_t* end, const int32_t* pos, int64_t n, int32_t window,
-                                    const int32_t* tile_offsets, const int32_t* tile_blocks, uint64_t* bits, void* stream) {
+extern "C" int spinf_tile_mask_bits_img(const int32_t* art, const int32_t* end, const int32_t* pos, const int32_t* grp, int64_t n,
+                                        int32_t window, int32_t grp_in_window, const int32_t* tile_offsets, const int32_t* tile_blocks,
+                                        uint64_t* bits, void* stream) {
   if (n == 0) return 0;  // nothing to do: the row pointers may be null
   SPINF_CHECK_ARG(art && end && pos && tile_offsets && tile_blocks && bits && n >= 0 && n % SPINF_BLOCK == 0 && n < (1ll << 30));
   const int nb = static_cast<int>(n / SPINF_BLOCK);
-  tile_mask_bits_kernel<<<nb, 256, 0, static_cast<cudaStream_t>(stream)>>>(art, end, pos, nb, window, tile_offsets, tile_blocks, bits);
+  tile_mask_bits_kernel<<<nb, 256, 0, static_cast<cudaStream_t>(stream)>>>(art, end, pos, grp, nb, window, grp_in_window, tile_offsets,
+                                                                           tile_blocks, bits);
   SPINF_CUDA_OK(cudaGetLastError());
   return 0;
+}
+
+extern "C" int spinf_tile_mask_bits(const int32_t* art, const int32_t* end, const int32_t* pos, int64_t n, int32_t window,
+                                    const int32_t* tile_offsets, const int32_t* tile_blocks, uint64_t* bits, void* stream) {
+  return spinf_tile_mask_bits_img(art, end, pos, nullptr, n, window, 0, tile_offsets, tile_blocks, bits, stream);
 }
 
 extern "C" int spinf_tree_attn_fwd(const void* q, const void* k, const void* v, void* out, int64_t n, int32_t H, int32_t Hkv,

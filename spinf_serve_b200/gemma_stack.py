@@ -175,8 +175,12 @@ class GemmaStack:
 
     family = "gemma"
     hybrid = False
+    bidirectional_images = True  # an image's placeholder tokens attend to each other both ways (Stack.bidirectional_images, base.py:28)
 
-    def __init__(self, weights: GemmaWeights, n_layers: int | None = None):
+    def __init__(self, weights: GemmaWeights, n_layers: int | None = None, vision_bidir_all: bool = True):
+        """vision_bidir_all (the reference's model._vision_bidir_all, gemma4.py:259): images' two-way blocks on every layer and
+        past the window (the "unified" checkpoints); False: on the sliding layers only, within the window (global layers causal)"""
+        self.vision_bidir_all = vision_bidir_all
         self.w = weights
         self.cfg = weights.cfg
         self.n_layers = self.cfg.layers if n_layers is None else n_layers  # the reference's EngineConfig.layers debug knob
@@ -234,7 +238,10 @@ class GemmaStack:
         """what forward reads of the staged arrays (Stack.stage, base.py:53-60, returns {"ids": [1, n], "pos": [1, n]}). `st` maps
         array names to device tensors: the scorer has laid the batch's arrays out in one pinned block and queued its single
         upload, so there is nothing left to copy here."""
-        return {"ids": st["ids"][None], "pos": st["pos32"][None]}
+        out = {"ids": st["ids"][None], "pos": st["pos32"][None]}
+        if b.media:
+            out["media"] = list(b.media)
+        return out
 
     # ---- per-tensor schemes (fp8: the activation scale from the forward's own maximum; fp8s: a calibrated fixed scale). The
     # GEMMs are the row-wise kernels with every row given the tensor's one scale, so their fused epilogues stay; the reference
@@ -292,6 +299,9 @@ class GemmaStack:
         row_gemm = ops.fp8_rowwise_gemm_small if attend is not None and n <= 128 else ops.fp8_rowwise_gemm
         tables = {k: ops.rope_table(pos, f) for k, f in self.inv_freq.items()}
         h = ops.embed_scale(ids, w.embed, self.embed_scale)
+        for start, obj in inputs.get("media", ()):  # the media rows over their placeholders, not scaled (gemma4.py:410-413)
+            if obj.embeds is not None:
+                h[start : start + obj.n_tokens] = obj.embeds.to(device=h.device, dtype=h.dtype)
         if self.n_layers == 0:
             out = ops.fused_norm(h, w2=w.norm, rows=rows, eps=cfg.eps, want_norm=True)["norm"]
             return out if rows is not None else out[None]

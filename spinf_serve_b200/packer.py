@@ -10,8 +10,11 @@ Reference behaviour mirrored here, by symbol:
     build_tree            packer.py:38-64        ReadPlan.build        packer.py:81-104
     trie_branches         packer.py:141-185      build_grouped_tree    packer.py:188-198
     split_grouped_trees   packer.py:201-215      split_trees           packer.py:218-233
-    Packer                packer.py:275-423      block_tables          packer.py:426-491 (text-only streams)
-Media (images / audio in the prefix) is outside this path: a tree that carries media is refused.
+    Packer                packer.py:275-423      block_tables          packer.py:426-491
+Media in the shared prefix (GroupedTree.media, packer.py:114-117,367-374): the packer records where each item's placeholders lie
+(Batch.media) and which image every placeholder belongs to (Batch.grp: an image's placeholders attend to each other both ways).
+Decoding images / audio and the towers that embed them are outside this path: Image / Audio below carry the placeholder count and,
+for the stacks, the rows of input embeddings the caller computed.
 """
 
 import ctypes
@@ -115,6 +118,27 @@ class ReadPlan:
             toks.extend(t[1:])
             opts.extend([o] * (len(t) - 1))
         return cls(list(first_row), np.array(rows, np.int64), np.array(toks, np.int64), np.array(opts, np.int64), len(option_ids), n_rows)
+
+
+@dataclass(eq=False)
+class Image:
+    """what the packed stream needs of an image in the shared prefix (the counterpart of media.Image, spinf_serve/media.py:41-50):
+    the number of placeholder tokens and their input embeddings [n_tokens, hidden] bf16 (None: the ids' own embeddings stay)"""
+
+    n_tokens: int
+    embeds: object = None
+
+
+@dataclass(eq=False)
+class Audio:
+    """the counterpart of media.Audio (spinf_serve/media.py:52-59): placeholders that attend causally, as text"""
+
+    n_tokens: int
+    embeds: object = None
+
+
+def _is_image(obj) -> bool:
+    return isinstance(obj, Image) or type(obj).__name__ == "Image"
 
 
 @dataclass
@@ -322,14 +346,21 @@ class Packer:
         end = np.full(n, -1, np.int32)
         prev = np.full(n, -1, np.int64)
         sel_parts, owners = [], []
+        media, grp = [], None
         n_sel = real = 0
         cursor = 0
         for slot, (jid, t) in enumerate(items):
-            if getattr(t, "media", None):
-                raise ValueError("media in the prefix is outside the packed scoring path of this build")
             grouped = isinstance(t, GroupedTree)
             s0 = cursor
             P = len(t.prefix)
+            for off, obj in getattr(t, "media", None) or ():
+                if off + obj.n_tokens > P:
+                    raise ValueError("media must lie in the shared prefix")
+                media.append((s0 + off, obj))
+                if _is_image(obj):
+                    if grp is None:
+                        grp = np.full(n, -1, np.int32)
+                    grp[s0 + off : s0 + off + obj.n_tokens] = len(media)
             nb = len(t.branches)
             lens = np.fromiter((len(b) for b in t.branches), np.int64, nb)
             parents = np.asarray(getattr(t, "parents", None) or [-1] * nb, np.int64)
@@ -402,7 +433,7 @@ class Packer:
             n_sel += len(rows)
             cursor = _round_up(job_end) if self.align else job_end
         sel = np.concatenate(sel_parts) if sel_parts else np.zeros(0, np.int64)
-        return Batch(ids, pos, seg, art, sel.astype(np.int64), owners, real, [], None, end, prev)
+        return Batch(ids, pos, seg, art, sel.astype(np.int64), owners, real, media, grp, end, prev)
 
 
 # ------------------------------------------------------------------------------------------------ tile descriptors
@@ -426,34 +457,38 @@ class TileDesc:
         return 1.0 - self.visited / causal if causal else 0.0
 
 
-def _pad_to_block(art, end, pos):
+def _pad_to_block(art, end, pos, grp=None):
     n = len(art)
     m = _round_up(n)
     if m == n:
-        return art, end, pos
+        return art, end, pos, grp
     fill = np.full(m - n, -1, np.int32)
-    return np.concatenate([art, fill]), np.concatenate([end, fill]), np.concatenate([pos, np.zeros(m - n, pos.dtype)])
+    return (np.concatenate([art, fill]), np.concatenate([end, fill]), np.concatenate([pos, np.zeros(m - n, pos.dtype)]),
+            None if grp is None else np.concatenate([grp, fill]))
 
 
-def tile_desc(art, end, pos, window: int | None = None) -> TileDesc:
+def tile_desc(art, end, pos, window: int | None = None, grp=None) -> TileDesc:
     """the tile descriptor of one layer type: window None / <= 0 = full attention, else the sliding variant (no "full" tiles, key
-    blocks wholly outside the window skipped). Built by the library's host function (spinf_tile_desc_build_host)."""
+    blocks wholly outside the window skipped). grp: the image of every placeholder token (Batch.grp) or None: blocks that share an
+    image are kept past the window, and a query block also visits the later key blocks of its images. Built by the library's host
+    function (spinf_tile_desc_build_host_img)."""
     from spinf_serve_b200 import _lib
 
-    art, end, pos = _pad_to_block(np.asarray(art), np.asarray(end), np.asarray(pos))
+    art, end, pos, grp = _pad_to_block(np.asarray(art), np.asarray(end), np.asarray(pos), None if grp is None else np.asarray(grp))
     art = np.ascontiguousarray(art, np.int32)
     end = np.ascontiguousarray(end, np.int32)
     pos = np.ascontiguousarray(pos, np.int32)
+    grp = None if grp is None else np.ascontiguousarray(grp, np.int32)
     nb = len(art) // BLOCK
     counts = np.zeros(nb, np.int32)
     blocks = np.zeros(max(nb * nb, 1), np.int32)
     flags = np.zeros(max(nb * nb, 1), np.uint8)
-    total = _lib.lib().spinf_tile_desc_build_host(
-        _lib.ptr(art), _lib.ptr(end), _lib.ptr(pos), len(art), ctypes.c_int32(window if window else 0), _lib.ptr(counts),
-        _lib.ptr(blocks), _lib.ptr(flags),
+    total = _lib.lib().spinf_tile_desc_build_host_img(
+        _lib.ptr(art), _lib.ptr(end), _lib.ptr(pos), None if grp is None else _lib.ptr(grp), len(art),
+        ctypes.c_int32(window if window else 0), _lib.ptr(counts), _lib.ptr(blocks), _lib.ptr(flags),
     )
     if total < 0:
-        _lib.check(int(total), "spinf_tile_desc_build_host")
+        _lib.check(int(total), "spinf_tile_desc_build_host_img")
     offsets = np.zeros(nb + 1, np.int32)
     np.cumsum(counts, out=offsets[1:])
     if nb:
@@ -484,10 +519,8 @@ def _tables(td: TileDesc):
 
 def block_tables(art, end, pos, window: int | None, grp=None, always_window: bool = False):
     """the reference's block-table interface (packer.py:426-491): -> (tables of the full-attention layers, tables of the sliding
-    layers or None when no position reaches the window and always_window is off). Text-only streams (grp must be None)."""
-    if grp is not None:
-        raise ValueError("image groups are outside the packed scoring path of this build")
+    layers or None when no position reaches the window and always_window is off). grp: Batch.grp of a stream with images."""
     pos = np.asarray(pos)
     binding = window is not None and (always_window or (len(pos) > 0 and int(pos.max()) >= window))
-    full = _tables(tile_desc(art, end, pos, None))
-    return full, (_tables(tile_desc(art, end, pos, window)) if binding else None)
+    full = _tables(tile_desc(art, end, pos, None, grp))
+    return full, (_tables(tile_desc(art, end, pos, window, grp)) if binding else None)

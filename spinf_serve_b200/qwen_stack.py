@@ -125,6 +125,7 @@ class QwenWeights:
 class QwenStack:
     family = "qwen"
     hybrid = True
+    bidirectional_images = False  # image tokens attend causally, as text (qwen.py:1014)
 
     def __init__(self, weights: QwenWeights, n_layers: int | None = None, compact: bool = True, min_stream: int = 0, align_jobs: bool = True):
         """compact (QwenOptions.compact, qwen.py:86, default on): the model runs on the stream's real tokens only, in stream order,
@@ -161,6 +162,8 @@ class QwenStack:
         dim]}}}, "pos0": None}; keys ("p", id(owner)) for prefixes, ("t", prompt key) for templates"""
         import numpy as np
 
+        if b.media:
+            raise ValueError("media in a hybrid-family stream needs the (t, h, w) rotary positions of its images, which are outside this path")
         real = b.art >= 0
         to_row = (np.cumsum(real) - 1) if self.compact_rows(b) is not None else np.arange(b.length)
         pre = [(int(to_row[o.start]), o.prefix_len, ("p", id(o))) for o in xo]

@@ -233,7 +233,9 @@ class _Flight:
 def stage_arrays(stack, sc, b: Batch, cols) -> tuple:
     """host work of one forward: the stack's plan, the tile lists, -> (HostTiles, {name: array}) ready for a StagingBlock"""
     stack.plan(sc, b)
-    tiles = attention.host_tiles(b.art, b.end, b.pos, getattr(stack, "window", None), always_window=sc.cfg.align_jobs)
+    grp = b.grp if getattr(stack, "bidirectional_images", True) else None  # else image tokens attend causally, as text
+    tiles = attention.host_tiles(b.art, b.end, b.pos, getattr(stack, "window", None), always_window=sc.cfg.align_jobs, grp=grp,
+                                 bidir_all=getattr(stack, "vision_bidir_all", True))
     arrays = {"ids": b.ids, "sel": np.asarray(b.sel, np.int64), "cols": np.asarray(cols, np.int32)}
     arrays.update(tiles.arrays())
     arrays.update(getattr(b, "staged", None) or {})
