@@ -33,6 +33,7 @@ import numpy as np
 import torch
 
 from spinf_serve_b200 import _lib, attention, ops
+from spinf_serve_b200.extraction import Extractor
 from spinf_serve_b200.packer import Batch, Packer, split_trees
 
 
@@ -50,6 +51,11 @@ class EngineConfig:
     layers: int | None = None
     fp8s_monitor_every: int = 0
     readback_lag: int = 1
+    # extraction branches read on the scoring pass (spinf_serve/config.py:35-49)
+    decode_budget_gib: float = 4.0    # captures held between forwards before they are decoded
+    decoder_budget_gib: float = 4.0   # one decoder's working set
+    capture_budget_gib: float = 2.0   # what one stream's forward may capture (the packer's cost budget)
+    x_cuda_graphs: bool = False       # decoding steps replayed from a CUDA graph
 
 
 @dataclass
@@ -239,6 +245,9 @@ def stage_arrays(stack, sc, b: Batch, cols) -> tuple:
     arrays = {"ids": b.ids, "sel": np.asarray(b.sel, np.int64), "cols": np.asarray(cols, np.int32)}
     arrays.update(tiles.arrays())
     arrays.update(getattr(b, "staged", None) or {})
+    xo = Extractor.owners(b)
+    if xo:  # the templates' last tokens: their final hidden states start the decoding
+        arrays["xends"] = np.asarray(Extractor.ends(xo), np.int64)
     return tiles, arrays
 
 
@@ -263,9 +272,13 @@ def forward_one(stack, b: Batch, device, rows=None, taps=None, cfg: EngineConfig
 
 
 class Scorer:
-    def __init__(self, stack, cfg: EngineConfig | None = None, device="cuda:0"):
+    extractor = None  # extraction.Extractor when the scorer was given stop_ids
+
+    def __init__(self, stack, cfg: EngineConfig | None = None, device="cuda:0", stop_ids=None, banned_ids=(), beam: int | None = None):
         """stack: a built family stack (gemma_stack.GemmaStack, qwen_stack.QwenStack): plan(sc, b), stage(sc, b, st),
-        forward(sc, b, inputs, masks, rows=...), .w.lm_weight, .window"""
+        forward(sc, b, inputs, masks, rows=...), .w.lm_weight, .window. stop_ids: the token ids that end a generated answer
+        (with them the scorer also decodes the extraction branches of the trees it reads: extraction.Extractor, answers in
+        x_found); banned_ids: ids an answer never contains; beam: sequences kept per extraction prompt"""
         self.cfg = cfg or EngineConfig()
         self.device = torch.device(device)
         if self.device.type != "cuda":
@@ -282,11 +295,20 @@ class Scorer:
         self._blocks = [StagingBlock(self.device) for _ in range(max(self.cfg.prefetch, 1) + 1)]
         self._results = []     # pinned result buffers not in flight
         self._workspace = None
+        self.extractor = None
+        if stop_ids:
+            self.extractor = Extractor(stack, self.device, tuple(stop_ids), tuple(banned_ids), softcap=self.softcap, graphs=self.cfg.x_cuda_graphs,
+                                       hold_budget=self.cfg.decode_budget_gib * 2**30, chunk_budget=self.cfg.decoder_budget_gib * 2**30,
+                                       **({"beam": beam} if beam else {}))
 
     # ------------------------------------------------------------------ one forward
     def _launch(self, t: _Ticket, flow: _Flow | None) -> _Flight:
         b, cols = t.batch, t.cols
-        if not len(b.sel) or not cols:
+        xo = Extractor.owners(b)
+        if xo and self.extractor is None:
+            raise RuntimeError("a tree carries extraction branches but the scorer was built without stop_ids")
+        reads = bool(len(b.sel)) and bool(cols)
+        if not reads and not xo:
             if flow is not None:
                 flow.give_block(t.block)
             return _Flight(b, cols, None, None)
@@ -303,7 +325,18 @@ class Scorer:
             flow.give_block(t.block)  # reusable by the packing thread once the copy's event has completed
         masks = attention.device_masks(t.tiles, st, self.device)
         inputs = self.stack.stage(self, b, st)
-        rows = self.stack.forward(self, b, inputs, masks, rows=st["sel"])
+        if xo:  # the forward keeps what decoding needs; the answers are generated between forwards (extraction.Extractor)
+            n_sel = st["sel"].numel()
+            with self.stack.capture(self, b, xo) as cap:
+                rows = self.stack.forward(self, b, inputs, masks, rows=torch.cat([st["sel"], st["xends"]]))
+            self.extractor.collect(xo, cap, rows[n_sel:].clone())
+            rows = rows[:n_sel]
+            if not reads:
+                e1.record()
+                self.stats._spans.append((e0, e1))
+                return _Flight(b, cols, None, None)
+        else:
+            rows = self.stack.forward(self, b, inputs, masks, rows=st["sel"])
         W = self.stack.w.lm_weight
         need = _lib.lib().spinf_option_logprobs_workspace_bytes(rows.shape[0], W.shape[0], len(cols))
         if self._workspace is None or self._workspace.numel() < need:
@@ -372,11 +405,16 @@ class Scorer:
                 self.stats.forwards += 1
                 self._harvest(flights, sink, self.cfg.readback_lag)
             self._harvest(flights, sink, 0)
+            if self.extractor is not None:
+                self.extractor.flush()
             self._settle(check=True)
         except BaseException:
             flow.cancel()
             self._settle(check=False)  # nothing of the failed call stays in flight over the staging blocks
             self.stats._spans = []
+            if self.extractor is not None:  # nor do its captures (spinf_serve/scorer.py:493-507)
+                self.extractor.drop()
+                self.stack.abandon(self)
             raise
         finally:
             worker.join()
@@ -394,7 +432,15 @@ class Scorer:
 
     # ------------------------------------------------------------------ public
     def _packer(self):
-        return Packer(self.cfg.token_budget, self.cfg.max_tokens, self.cfg.align_jobs, self.min_stream)
+        if self.extractor is None:
+            return Packer(self.cfg.token_budget, self.cfg.max_tokens, self.cfg.align_jobs, self.min_stream)
+        return Packer(self.cfg.token_budget, self.cfg.max_tokens, self.cfg.align_jobs, self.min_stream, cost=self.extractor.tree_bytes,
+                      cost_budget=int(self.cfg.capture_budget_gib * 2**30))
+
+    @property
+    def x_found(self) -> dict:
+        """answers of the extraction branches read so far: {prompt key: [(token ids, log-prob)] best first} (Scorer.x_found)"""
+        return self.extractor.found if self.extractor is not None else {}
 
     def score_grouped(self, items) -> dict:
         """items: an iterable of (key, first prompt index, GroupedTree); several items may share a key (a job split over the
