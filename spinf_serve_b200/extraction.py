@@ -22,6 +22,26 @@ GIB = float(2**30)
 
 
 @dataclass
+class ExtractPrompt:
+    """one extraction read (extract.ExtractPrompt, spinf_serve/extract.py:58-69): the tokens after the job's prefix up to the slot
+    (may be empty: the slot starts right after the prefix) and how many tokens an answer may have; `kind` is "text" here"""
+
+    key: object
+    ids: list
+    max_tokens: int
+    kind: str = "text"
+
+
+@dataclass
+class ExtractJob:
+    """one content's extraction reads (extract.ExtractJob, :71-78): the prefix, read once, and the prompts that decode from it"""
+
+    prefix: list
+    prompts: list
+    media: list = field(default_factory=list)
+
+
+@dataclass
 class Extractor:
     stack: object
     device: object

@@ -167,7 +167,8 @@ class QwenStack:
         real = b.art >= 0
         to_row = (np.cumsum(real) - 1) if self.compact_rows(b) is not None else np.arange(b.length)
         pre = [(int(to_row[o.start]), o.prefix_len, ("p", id(o))) for o in xo]
-        tmpl = [(int(to_row[bs]), bl, ("t", pr.key)) for o in xo for bs, bl, pr in o.xbranches]
+        # (first row, length, key, row of the template's last token: the prefix's last token for a slot without template tokens)
+        tmpl = [(int(to_row[bs]) if bl else 0, bl, ("t", pr.key), int(to_row[bs + bl - 1])) for o in xo for bs, bl, pr in o.xbranches]
         cap = {"prefixes": pre, "templates": tmpl, "kv": {}, "state": {}, "tok": {}, "pre": {}}
         self._cap = cap
         try:
@@ -198,10 +199,10 @@ class QwenStack:
             for j, (_, _, key) in enumerate(cap["prefixes"]):
                 cap["state"].setdefault(key, {})[i] = ht[j]
         n_rows = y.shape[0]
-        for r0, n, key in cap["templates"]:
+        for r0, n, key, r_end in cap["templates"]:
             sl = slice(r0, r0 + n)
             cap["tok"].setdefault(key, {})[i] = (q[sl].clone(), k[sl].clone(), v[sl].clone(), g[sl].clone(), beta[sl].clone())
-            taps = plan.conv[r0 + n - 1, 1:4]  # the path's last three tokens, the template's end among them
+            taps = plan.conv[r_end, 1:4]  # the path's last three tokens, the template's end among them
             ok = (taps >= 0) & (taps < n_rows)
             cap["pre"].setdefault(key, {})[i] = y[taps.clamp(0, n_rows - 1), :cd] * ok[:, None].to(y.dtype)
 
@@ -283,7 +284,7 @@ class QwenStack:
                 kk = y[:, 2 * H * D : (2 * H + K) * D].view(n, K, D)
                 vv = y[:, (2 * H + K) * D :].view(n, K, D)
                 if self._cap is not None:
-                    for r0, cnt, key in self._cap["prefixes"] + self._cap["templates"]:
+                    for r0, cnt, key in self._cap["prefixes"] + [t[:3] for t in self._cap["templates"]]:
                         self._cap["kv"].setdefault(key, {})[i] = (kk[r0 : r0 + cnt].clone(), vv[r0 : r0 + cnt].clone())
                 if attend is not None:
                     o = attend(i, q, kk, vv)

@@ -459,6 +459,30 @@ class Scorer:
         self._execute(batches, lambda lp, cols, b: read_grouped(lp, cols, b, out))
         return out
 
+    def extract(self, jobs) -> dict:
+        """extraction jobs (extraction.ExtractJob) -> {prompt key: [(token ids, log-prob)] best first}: each job's prefix read once
+        through the packed path with its prompts as extraction branches (a prompt without template tokens: a zero-length branch at
+        the prefix's end), all decoded together; the form the reference uses for its hybrid models (Scorer._extract_hybrid,
+        spinf_serve/scorer.py:748-766), here for both families"""
+        from spinf_serve_b200.packer import GroupedTree
+
+        if self.extractor is None:
+            raise RuntimeError("extract needs a scorer built with stop_ids")
+        items = []
+        for n, job in enumerate(jobs):
+            branches, xb = [], []
+            for pr in job.prompts:
+                if pr.kind != "text":
+                    raise ValueError(f"prompt {pr.key}: only text slots are searched here")
+                if pr.ids:
+                    xb.append((len(branches), pr))
+                    branches.append(list(pr.ids))
+                else:
+                    xb.append((-1, pr))
+            items.append((("x", n), 0, GroupedTree(list(job.prefix), branches, [], [], media=list(job.media), xbranches=xb, parents=[-1] * len(branches))))
+        self.score_grouped(items)
+        return {pr.key: self.extractor.found.pop(pr.key) for job in jobs for pr in job.prompts}
+
     def score_trees(self, jobs) -> dict:
         """jobs: (job id, prompt token ids, option token ids per prompt), the reference's Scorer.score after tokenisation ->
         {job id: JobResult}"""

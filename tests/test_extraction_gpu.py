@@ -127,6 +127,37 @@ def test_scoring_and_extraction_in_one_call_hybrid(dev):
     _check_family(stack, _mixed_trees(9, ((70, 3, (5, 9)), (130, 2, (7,))), 2048), dev, hybrid=True)
 
 
+@pytest.mark.parametrize("family", ["gemma", "hybrid"])
+def test_extract_jobs_with_and_without_template_tokens(dev, family):
+    """Scorer.extract: a prompt whose slot starts right after the prefix decodes like the same prompt with the prefix's last
+    token moved into its template"""
+    from spinf_serve_b200.extraction import ExtractJob, ExtractPrompt
+
+    if family == "gemma":
+        from oracle import gemma as OG
+        from spinf_serve_b200.gemma_stack import GemmaConfig, GemmaStack, GemmaWeights
+        from tests.test_decode_gpu import _cfg
+
+        W = OG.init_weights(OG.GemmaConfig(**_cfg()), seed=4)
+        stack, vocab = GemmaStack(GemmaWeights.from_quantized(GemmaConfig(**_cfg()), W, OG.quantize(W, "bf16"), dev, "bf16")), 4096
+    else:
+        from oracle import qwen as OQ
+        from spinf_serve_b200.qwen_stack import QwenConfig, QwenStack, QwenWeights
+        from tests.test_qwen_gpu import SMALL
+
+        stack, vocab = QwenStack(QwenWeights(QwenConfig(**SMALL), OQ.init_weights(OQ.QwenConfig(**SMALL), seed=3), dev)), 2048
+    rng = np.random.default_rng(12)
+    prefix = rng.integers(5, vocab, 90).tolist()
+    tmpl = rng.integers(5, vocab, 6).tolist()
+    sc = _scorer(stack, dev)
+    a = sc.extract([ExtractJob(prefix, [ExtractPrompt("bare", [], 3), ExtractPrompt("tmpl", tmpl, 3)])])
+    b = sc.extract([ExtractJob(prefix[:-1], [ExtractPrompt("moved", prefix[-1:], 3)])])
+    assert set(a) == {"bare", "tmpl"} and a["bare"] and a["tmpl"] and sc.x_found == {}
+    (t0, lp0), (t1, lp1) = a["bare"][0], b["moved"][0]
+    print(f"{family}: bare slot {t0} ({lp0:.3f}); the same sequence with the last prefix token as its template {t1} ({lp1:.3f})")
+    assert t0 == t1 and abs(lp0 - lp1) < 0.05
+
+
 def test_extraction_branches_need_stop_ids(dev):
     from oracle import gemma as OG
     from spinf_serve_b200.gemma_stack import GemmaConfig, GemmaStack, GemmaWeights
