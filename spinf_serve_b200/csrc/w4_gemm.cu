@@ -31,19 +31,25 @@
 
 namespace spinf {
 
+template <int TOK>
 struct W4Smem {
-  static constexpr int STAGES = 6;            // stage s: activation half tile + raw weight tile in shared memory, expansion in TMEM
+  // stage s: activation half tile + raw weight tile in shared memory, expansion in TMEM. The narrow tile (TOK = 64) moves 8 KB per
+  // stage instead of 20: twice the stages keep as many weight bytes in flight per SM as the wide tile's ring (a few-row call is a
+  // weight stream bound by the bytes in flight, not by the tensor pipe)
+  static constexpr int STAGES = TOK == 256 ? 6 : 12;
   static constexpr int EPI_BUFS = 4;          // one staging buffer per 64-token chunk of a tile: no chunk waits for an earlier store
-  static constexpr int X_BYTES = 128 * 128;   // this CTA's activations: 128 tokens x 64 bf16
+  static constexpr int X_BYTES = TOK / 2 * 128;  // this CTA's activations: TOK / 2 tokens x 64 bf16
   static constexpr int RAW_BYTES = 128 * 32;  // this CTA's raw weights: 128 rows x 64 nibbles
   static constexpr int STAGE_BYTES = X_BYTES + RAW_BYTES;
   static constexpr int EPI_OFF = STAGES * STAGE_BYTES;
   static constexpr int EPI_BYTES = 64 * 256;  // one staging buffer: 64 tokens x 128 output channels (two swizzled 64 x 64 boxes)
   static constexpr int BAR_OFF = EPI_OFF + EPI_BUFS * EPI_BYTES;
-  static constexpr int TOTAL = BAR_OFF + 512 + 1024;
-  static constexpr uint32_t ACC_COL = 0, W_COL = 256;  // tensor-memory columns: accumulator, weight slots (32 columns each)
+  static constexpr int TOTAL = BAR_OFF + 1024 + 1024;  // barriers: (5 STAGES + 2) x 8 B, then the tensor-memory base and the abort flag
+  static constexpr uint32_t ACC_COL = 0, W_COL = TOK;  // tensor-memory columns: accumulator (TOK), weight slots (32 columns each)
+  static_assert(W_COL + STAGES * 32 <= 512, "accumulator and weight slots fit tensor memory");
+  static_assert((5 * STAGES + 2) * 8 + 8 <= 1024, "barriers fit their area");
 };
-static_assert(W4Smem::STAGE_BYTES % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
+static_assert(W4Smem<256>::STAGE_BYTES % 1024 == 0 && W4Smem<64>::STAGE_BYTES % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
 
 struct W4Args {
   const __half* scales;  // [N, K / G]
@@ -61,13 +67,18 @@ struct W4Args {
 // time (row 2c = gate channel c, row 2c + 1 = up channel c), so a lane pair of the epilogue holds a channel's gate and up values
 // and writes y[m, c] = bf16(bf16(act(bf16 gate)) * bf16 up): the arithmetic of the linear followed by the gated-activation pass,
 // without the [M, 2F] intermediate.
-template <int ACT>
+// TOK: tokens per tile = the MMA's N: 256, or 64 for calls of at most 64 rows (a decoding step), where a 256-wide product would
+// spend four times the tensor-pipe time on rows that do not exist; each CTA then loads 32 token rows per stage and the epilogue
+// has one 64-token chunk. An output element's sum over K is the same sequence of products either way.
+template <int ACT, int TOK>
 __global__ void __launch_bounds__(448, 1)
 w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmC,
                const W4Args a, int* __restrict__ status) {
-  using L = W4Smem;
+  using L = W4Smem<TOK>;
   constexpr int STAGES = L::STAGES;
-  constexpr uint32_t IDESC = make_idesc(FMT_BF16, FMT_BF16, 256, 256, 0, 0);  // M = weight rows, N = tokens (K-major in shared memory)
+  constexpr uint32_t IDESC = make_idesc(FMT_BF16, FMT_BF16, 256, TOK, 0, 0);  // M = weight rows, N = tokens (K-major in shared memory)
+  constexpr int HALF = TOK / 2;            // token rows of a tile this CTA loads
+  constexpr int CHUNKS = TOK / 64;         // 64-token chunks of the epilogue
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* full_a = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);  // leader's: both halves of the activation tile landed
@@ -127,7 +138,7 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if (!mbar_wait(wc, &raw_done[s], ph ^ 1u, ST_TIMEOUT_EMPTY)) { ok = false; break; }
           uint8_t* sa = smem + s * L::STAGE_BYTES;
           if (rank == 0) mbar_expect_tx(&full_a[s], 2 * L::X_BYTES);  // the leader's barrier counts both CTAs' activation bytes
-          tma_load_2d_pair(sa, &tmA, kb * 64, tm * 256 + static_cast<int>(rank) * 128, map_to_cta(&full_a[s], 0));
+          tma_load_2d_pair(sa, &tmA, kb * 64, tm * TOK + static_cast<int>(rank) * HALF, map_to_cta(&full_a[s], 0));
           mbar_expect_tx(&full_w[s], L::RAW_BYTES);
           tma_load_2d(sa + L::X_BYTES, &tmW, kb * 32, tn * 256 + static_cast<int>(rank) * 128, &full_w[s]);
         }
@@ -252,14 +263,14 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (!bar_red_and(1, 128, got)) break;
       tc_fence_after();
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c, ++nchunks) {  // 64-token chunks
+      for (int c = 0; c < CHUNKS; ++c, ++nchunks) {  // 64-token chunks
         uint32_t v0[32], v1[32];
         __syncwarp();
         const uint32_t taddr = tmem_base + L::ACC_COL + c * 64 + (static_cast<uint32_t>(q * 32) << 16);
         tmem_ld_x32(taddr, v0);
         tmem_ld_x32(taddr + 32, v1);
         tmem_wait_ld();
-        if (c == 3) {  // the accumulator is in registers: one arrival per warp on the leader's barrier
+        if (c == CHUNKS - 1) {  // the accumulator is in registers: one arrival per warp on the leader's barrier
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
@@ -267,8 +278,8 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (ACT < 0 && a.part != nullptr) {
           // a K slice's sums, fp32, straight to part[slice][token][channel]: a warp's lanes are 32 neighbouring channels
           const int n = tn * 256 + static_cast<int>(rank) * 128 + ch;
-          float* const dst = a.part + (static_cast<int64_t>(ks) * a.M + tm * 256 + c * 64) * a.N + n;
-          const int rows = a.M - (tm * 256 + c * 64);  // tokens of this chunk that exist
+          float* const dst = a.part + (static_cast<int64_t>(ks) * a.M + tm * TOK + c * 64) * a.N + n;
+          const int rows = a.M - (tm * TOK + c * 64);  // tokens of this chunk that exist
           if (n < a.N) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
@@ -328,7 +339,7 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         fence_proxy_async_smem();
         named_bar_sync(1, 128);
         if (et == 0) {
-          const int m0 = tm * 256 + c * 64;
+          const int m0 = tm * TOK + c * 64;
           if (ACT < 0) {
             const int n0 = tn * 256 + static_cast<int>(rank) * 128;
             if (m0 < a.M && n0 < a.N) tma_store_2d(&tmC, buf, n0, m0);  // boxes that lie wholly outside the output are skipped,
@@ -419,13 +430,14 @@ static int launch_w4(const void* x, const void* qw, const void* scales, int32_t 
   if (!status) return SPINF_ERR_CUDA;
   CUtensorMap tmA, tmW, tmC;
   int r;
-  if ((r = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, M, K, K * 2, 64, 128))) return r;
+  const int TOK = M <= 64 ? 64 : 256;  // tokens per tile (the kernel's TOK)
+  if ((r = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, M, K, K * 2, 64, TOK / 2))) return r;
   if ((r = make_tmap_2d_plain(&tmW, qw, N, K / 2, K / 2, 32, 128))) return r;
   if ((r = make_tmap_2d(&tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y, M, n_out, y_pitch * 2, 64, 64))) return r;
   W4Args a;
   a.scales = static_cast<const __half*>(scales);
   a.M = static_cast<int>(M), a.N = static_cast<int>(N), a.K = static_cast<int>(K), a.G = group;
-  a.tiles_m = static_cast<int>((M + 255) / 256);
+  a.tiles_m = static_cast<int>((M + TOK - 1) / TOK);
   a.tiles_n = static_cast<int>((N + 255) / 256);
   a.splits = splits, a.kb_per = static_cast<int>(K / 64) / splits, a.part = part;
   // groups of row tiles as tall as about 32 MB of bf16 activations allow (4..32 tiles of 256 rows): the packed weight streams past
@@ -435,10 +447,11 @@ static int launch_w4(const void* x, const void* qw, const void* scales, int32_t 
     const int64_t g = (32ll << 20) / per_tile;
     a.group_m = static_cast<int>(g < 4 ? 4 : (g > 32 ? 32 : g));
   }
-  auto kern = w4_gemm_kernel<ACT>;
+  auto kern = TOK == 64 ? w4_gemm_kernel<ACT, 64> : w4_gemm_kernel<ACT, 256>;
   static std::atomic<bool> attr_set[64];  // zero-initialised; setting the attribute twice from two threads is harmless
   if (!attr_set[dev].load(std::memory_order_acquire)) {
-    SPINF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, W4Smem::TOTAL));
+    SPINF_CUDA_OK(cudaFuncSetAttribute(w4_gemm_kernel<ACT, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, W4Smem<256>::TOTAL));
+    SPINF_CUDA_OK(cudaFuncSetAttribute(w4_gemm_kernel<ACT, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, W4Smem<256>::TOTAL));
     attr_set[dev].store(true, std::memory_order_release);
   }
   const int tiles = a.tiles_m * a.tiles_n * a.splits;
@@ -446,7 +459,7 @@ static int launch_w4(const void* x, const void* qw, const void* scales, int32_t 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
   cfg.blockDim = dim3(448);
-  cfg.dynamicSmemBytes = W4Smem::TOTAL;
+  cfg.dynamicSmemBytes = W4Smem<256>::TOTAL;
   cfg.stream = static_cast<cudaStream_t>(stream);
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
