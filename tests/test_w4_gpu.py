@@ -63,7 +63,7 @@ def test_w4_rows_do_not_depend_on_M(dev):
     q, s = ops.w4_repack(q.to(dev)), s.to(dev)
     x = torch.randn((1000, 1024), generator=torch.Generator().manual_seed(4)).to(torch.bfloat16).to(dev)
     full = ops.w4_gemm(x, q, s, 128)
-    for M in (1, 255, 256, 257):
+    for M in (1, 36, 64, 65, 255, 256, 257):  # up to 64 rows run on the 64-token tile, more on the 256-token one
         assert torch.equal(ops.w4_gemm(x[:M].contiguous(), q, s, 128), full[:M])
 
 
@@ -84,7 +84,8 @@ def test_w4_expansion_is_the_reference_dequantisation_bit_for_bit(dev, G):
     assert torch.equal(y.view(torch.int16), want.contiguous().view(torch.int16))
 
 
-@pytest.mark.parametrize("M,F,K,G,act", [(300, 384, 512, 128, "silu"), (77, 104, 192, 64, "silu"), (513, 1024, 1024, 32, "gelu_tanh"), (1, 64, 128, 128, "silu")])
+@pytest.mark.parametrize("M,F,K,G,act", [(300, 384, 512, 128, "silu"), (77, 104, 192, 64, "silu"), (513, 1024, 1024, 32, "gelu_tanh"), (1, 64, 128, 128, "silu"),
+                                             (36, 640, 1024, 128, "silu"), (64, 104, 192, 64, "gelu_tanh")])
 def test_w4_glu_epilogue_equals_the_separate_pass(dev, M, F, K, G, act):
     """the fused gate|up projection with the gated activation in its epilogue gives the bits of the plain projection followed by
     the gated-activation pass (ragged M, F not a multiple of the tile, both activations)"""
