@@ -33,13 +33,11 @@ def _reference_on_path():
     sys.path.insert(0, REF)
     yield
     sys.path.remove(REF)
-    out = os.path.join(ROOT, "gpurun_out")
-    try:
+    out = os.environ.get("SPINF_VS_REFERENCE_OUT")  # a folder: the timings and parity figures of this run as vs_reference.json
+    if out:
         os.makedirs(out, exist_ok=True)
         with open(os.path.join(out, "vs_reference.json"), "w") as f:
             json.dump(RESULTS, f, indent=1)
-    except OSError:
-        pass
 
 
 def timed(fn, repeats=20, warm=3):
