@@ -145,6 +145,15 @@ int spinf_bf16_gemm(const void* x, const void* w, void* y, int64_t M, int64_t N,
  * Int4Linear appends its un-quantised "extra" output channels to the int4 ones (spinf_serve/models/qwen35/qwen.py:421-426). */
 int spinf_bf16_gemm_ld(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, int64_t y_pitch, void* stream);
 
+/* spinf_bf16_gemm_ld for a decoding step's few rows (M <= 128) and few output channels (the un-quantised b | a rows beside an
+ * Int4Linear, spinf_serve/models/qwen35/qwen.py:421-426,456-457, at a decoding step's rows): K in slices on separate CTAs, fp32
+ * partial sums in `workspace` (16-byte aligned, at least spinf_bf16_gemm_small_workspace_bytes), added in slice order by a second
+ * launch. Differs from spinf_bf16_gemm_ld in the order of the fp32 sum only; y 8-byte aligned, y_pitch a multiple of 4. A shape
+ * that needs no slices (workspace bytes 0) runs spinf_bf16_gemm_ld. */
+int64_t spinf_bf16_gemm_small_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int spinf_bf16_gemm_small(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, int64_t y_pitch, void* workspace,
+                          int64_t workspace_bytes, void* stream);
+
 /* ------------------------------------------------------------------------------------------------------------ int4 weight-only linear
  * Replaces Int4Linear.forward in bf16 mode (spinf_serve/models/qwen35/qwen.py:455-458) with its per-call dequantisation dq_bf16
  * (qwen.py:326-330):  y[m,n] = bf16( sum_k x[m,k] * w[n,k] ),  w[n,k] = bf16( (nibble(n,k) - 8) * float(scales[n, k / group]) ).

@@ -35,6 +35,8 @@ SIGNATURES = {
     "spinf_fp8_rowwise_gemm_qkv": (ctypes.c_int, [_p, _p, _p, _p, _p, _i64, _i32, _i32, _i32, _i64, _p, _p, _p, _p, _f32, _i32, _i32, _p]),
     "spinf_fp8_quant_from_amax": (ctypes.c_int, [_p, _p, _i64, _i64, _p, _p, _p]),
     "spinf_bf16_gemm_ld": (ctypes.c_int, [_p, _p, _p, _i64, _i64, _i64, _i64, _p]),
+    "spinf_bf16_gemm_small_workspace_bytes": (_i64, [_i64, _i64, _i64]),
+    "spinf_bf16_gemm_small": (ctypes.c_int, [_p, _p, _p, _i64, _i64, _i64, _i64, _p, _i64, _p]),
     "spinf_w4_repack": (ctypes.c_int, [_p, _p, _i64, _i64, _p]),
     "spinf_w4_gemm_glu": (ctypes.c_int, [_p, _p, _p, _i32, _i32, _p, _i64, _i64, _i64, _i64, _p]),
     "spinf_w4_gemm": (ctypes.c_int, [_p, _p, _p, _i32, _p, _i64, _i64, _i64, _i64, _p]),

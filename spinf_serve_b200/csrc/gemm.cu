@@ -723,6 +723,78 @@ extern "C" int spinf_bf16_gemm_ld(const void* x, const void* w, void* y, int64_t
   return launch_gemm<KIND_BF16, BN>(tmA, tmB, make_shape(M, N, K, BN, 2), epi, static_cast<cudaStream_t>(stream));
 }
 
+namespace spinf {
+// K slices of the few-row bf16 product (a handful of un-quantised output channels beside a quantised linear: one or two column
+// tiles whose serial K loop, not their bytes, is the cost): slices of at least 8 K blocks (512 elements), at most 16
+static int bf16_small_splits(int64_t N, int64_t K, int* kb_per_out) {
+  const int tiles_n = static_cast<int>((N + 127) / 128), num_kb = static_cast<int>((K + 63) / 64);
+  int s = sm_count() / tiles_n;
+  s = s > num_kb / 8 ? num_kb / 8 : s;
+  s = s > 16 ? 16 : s;
+  if (s < 2) {
+    *kb_per_out = num_kb;
+    return 1;
+  }
+  const int kb_per = (num_kb + s - 1) / s;
+  *kb_per_out = kb_per;
+  return (num_kb + kb_per - 1) / kb_per;
+}
+
+// y[m, n] = bf16(sum over slices, in slice order, of part[s][m][n]); y rows y_pitch elements apart
+__global__ void __launch_bounds__(256) bf16_small_sum_kernel(const float* __restrict__ part, int splits, int M, int N,
+                                                             __nv_bfloat16* __restrict__ y, int64_t y_pitch) {
+  const int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+  const int64_t MN = static_cast<int64_t>(M) * N;
+  if (i >= MN) return;
+  float4 acc = *reinterpret_cast<const float4*>(part + i);
+  for (int k = 1; k < splits; ++k) {
+    const float4 p = *reinterpret_cast<const float4*>(part + k * MN + i);
+    acc.x += p.x, acc.y += p.y, acc.z += p.z, acc.w += p.w;
+  }
+  uint2 out;
+  out.x = pack_bf16x2(acc.x, acc.y);
+  out.y = pack_bf16x2(acc.z, acc.w);
+  *reinterpret_cast<uint2*>(y + (i / N) * y_pitch + i % N) = out;
+}
+}  // namespace spinf
+
+extern "C" int64_t spinf_bf16_gemm_small_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  if (M <= 0 || M > 128 || N <= 0 || K <= 0 || N % 4) return 0;
+  int kb_per;
+  const int s = spinf::bf16_small_splits(N, K, &kb_per);
+  return s > 1 ? static_cast<int64_t>(s) * M * N * 4 : 0;
+}
+
+// spinf_bf16_gemm_ld for a decoding step's few rows (M <= 128) and few output channels: the K dimension in slices on separate
+// CTAs, fp32 partial sums in `workspace` (16-byte aligned), added in slice order by a second launch. Differs from spinf_bf16_gemm_ld
+// in the order of the fp32 sum only. A shape that needs no slices (workspace bytes 0) runs spinf_bf16_gemm_ld.
+extern "C" int spinf_bf16_gemm_small(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, int64_t y_pitch, void* workspace,
+                                     int64_t workspace_bytes, void* stream) {
+  using namespace spinf;
+  if (M == 0) return 0;
+  const int64_t need = spinf_bf16_gemm_small_workspace_bytes(M, N, K);
+  if (need == 0) return spinf_bf16_gemm_ld(x, w, y, M, N, K, y_pitch, stream);
+  SPINF_CHECK_ARG(x && w && y && K % 8 == 0 && N % 8 == 0 && y_pitch >= N && y_pitch % 4 == 0 && N < (1ll << 31) && K < (1ll << 31));
+  SPINF_CHECK_ARG(workspace && workspace_bytes >= need && reinterpret_cast<uintptr_t>(workspace) % 16 == 0);
+  SPINF_CHECK_ARG(reinterpret_cast<uintptr_t>(y) % 8 == 0);
+  constexpr int BN = 128;
+  CUtensorMap tmA, tmB;
+  EpiPartial<BN> epi;
+  int r;
+  if ((r = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, M, K, K * 2, 64, 128))) return r;
+  if ((r = make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, N, K, K * 2, 64, BN))) return r;
+  epi.part = static_cast<float*>(workspace);
+  GemmShape shape = make_shape(M, N, K, BN, 2);
+  shape.splits = bf16_small_splits(N, K, &shape.kb_per);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if ((r = launch_gemm<KIND_BF16, BN>(tmA, tmB, shape, epi, st))) return r;
+  const int64_t quads = M * N / 4;
+  bf16_small_sum_kernel<<<static_cast<unsigned>((quads + 255) / 256), 256, 0, st>>>(epi.part, shape.splits, static_cast<int>(M),
+                                                                                    static_cast<int>(N), static_cast<__nv_bfloat16*>(y), y_pitch);
+  SPINF_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
 extern "C" int spinf_bf16_gemm(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, void* stream) {
   return spinf_bf16_gemm_ld(x, w, y, M, N, K, N, stream);
 }

@@ -350,8 +350,11 @@ def w4_gemm_small(x, qw, scales, group, extra=None, workspace=None):
     COUNTS["launches"] += 2 if need else 1
     if E:
         tail = ctypes.c_void_p(y.data_ptr() + 2 * N)
-        check(_lib.lib().spinf_bf16_gemm_ld(ptr(x), ptr(extra), tail, M, E, K, N + E, stream_ptr()), "spinf_bf16_gemm_ld")
-        COUNTS["launches"] += 1
+        need_e = int(_lib.lib().spinf_bf16_gemm_small_workspace_bytes(M, E, K))  # the extra rows' product in K slices too
+        ws_e = torch.empty(max(need_e, 16), dtype=torch.uint8, device=x.device)
+        check(_lib.lib().spinf_bf16_gemm_small(ptr(x), ptr(extra), tail, M, E, K, N + E, ptr(ws_e), ws_e.numel(), stream_ptr()),
+              "spinf_bf16_gemm_small")
+        COUNTS["launches"] += 2 if need_e else 1
     return y
 
 

@@ -104,7 +104,7 @@ def test_w4_glu_epilogue_equals_the_separate_pass(dev, M, F, K, G, act):
 
 
 @pytest.mark.parametrize("M,N,K,G,E", [(36, 5120, 4096, 128, 0), (36, 5120, 17408, 128, 0), (120, 1024, 5120, 32, 64), (1, 256, 128, 128, 0),
-                                       (200, 6144, 2048, 64, 0), (36, 34816, 5120, 128, 0)])
+                                       (200, 6144, 2048, 64, 0), (36, 34816, 5120, 128, 0), (36, 2048, 5120, 128, 96)])
 def test_w4_few_rows_with_k_slices(dev, M, N, K, G, E):
     """Int4Linear.few (a decoding step): the kernel with K cut into slices for narrow projections, exact against the float64
     product to bf16 rounding and within one bf16 step of forward on a few elements (wide ones run forward's kernel: equal)"""
