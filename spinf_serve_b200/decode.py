@@ -188,7 +188,7 @@ class Decoder:
 
 class HybridDecoder(Decoder):
     """Decoder for the hybrid family (qwen_stack.QwenStack): the attention layers as above; a recurrent layer re-runs the gated
-    delta rule from the group's prefix state over the slot's own rows (its template's, then the tokens it generated): no per-slot
+    delta rule from the group's prefix state over the slot's own rows (its template's, once per prompt for all its beams, then the tokens it generated): no per-slot
     state is kept or copied when beams fan out, only the small row caches follow the beams; the 4-tap convolution reads a
     per-slot ring of the three previous pre-convolution rows (spinf_serve/models/qwen35/qwen_decode.py:1-20,70-166). A group's
     `extra` holds what QwenStack.capture delivered for it: {"state": {layer: S}, "tmpl": [per prompt {"tok": {layer: (q, k, v, g,
@@ -231,12 +231,10 @@ class HybridDecoder(Decoder):
         # in-projection rows of a step with the conv rings behind them: rows 0 .. n - 1 the step's own, rows n + 3 s .. n + 3 s + 2
         # slot s's three previous pre-convolution rows (taps 3 back .. 1 back); one prologue call reads both through its tap table
         self.ybuf = torch.zeros((n_g, 4 * n, width), dtype=bf, device=device)
-        slot_T, slot_t0 = torch.zeros(n, dtype=torch.int64), torch.zeros(n, dtype=torch.int64)
         for gi, (g, e) in enumerate(zip(groups, extras, strict=True)):
             for j, (_, _, T, _) in enumerate(g.prompts):
                 a = t0[(gi, j)]
                 sl = slice(gi * Q + j * beam, gi * Q + (j + 1) * beam)
-                slot_T[sl], slot_t0[sl] = T, a
                 for x, li in enumerate(self.rec):
                     q, k, v, gg, bb = e["tmpl"][j]["tok"][li]
                     self.cq[x, a : a + T], self.ck[x, a : a + T], self.cv[x, a : a + T] = q, k, v
@@ -245,15 +243,27 @@ class HybridDecoder(Decoder):
                     ring[sl, :, :cd] = e["tmpl"][j]["pre"][li][None]
         s_ar = torch.arange(n, dtype=torch.int64)
         self.conv_idx = torch.stack([n + 3 * s_ar, n + 3 * s_ar + 1, n + 3 * s_ar + 2, s_ar], 1).contiguous().to(device)
-        # the recurrence's rows for every step, made once on the host: per slot its template rows, then its generated rows 0 .. step
-        lens = slot_T[None, :] + torch.arange(1, S + 1, dtype=torch.int64)[:, None]  # [S, n]
-        self.cu_all = torch.nn.functional.pad(lens.cumsum(1), (1, 0)).contiguous().to(device)  # [S, n + 1]
-        max_rows = int(lens[-1].sum())
-        idx_all = torch.zeros((S, max_rows), dtype=torch.int64)
+        # The recurrence of a step runs as two calls. First every prompt's template rows from its group's prefix state (the beams of
+        # a prompt share them: once per prompt, not once per slot), leaving the state at the template's end in `ht` (one buffer for
+        # all layers: the second call of the same layer consumes it); a prompt slot without a prompt has no rows and passes the
+        # prefix state on. Then every slot's generated rows 0 .. step from its prompt's entry of `ht`. The state goes through memory
+        # in fp32 unchanged, so a slot sees the same sequence of updates as one call over template + generated rows would give it.
+        J = Q // beam
+        t_len = torch.zeros(G * J, dtype=torch.int64)
+        for gi, g in enumerate(groups):
+            for j, (_, _, T, _) in enumerate(g.prompts):
+                t_len[gi * J + j] = T
+        self.t_cu = torch.nn.functional.pad(t_len.cumsum(0), (1, 0)).contiguous().to(device)  # rows 0 .. gen0 - 1, prompt after prompt
+        self.t_h0_idx = (torch.arange(G * J, dtype=torch.int64) // J).to(device)
+        self.t_ht_idx = torch.arange(G * J, dtype=torch.int64, device=device)
+        self.ht = torch.empty((G * J, hv, dk, dv), dtype=torch.float32, device=device)
+        self.slot_prompt = (s_ar // beam).to(device)
+        # the generated rows of every step, made once on the host: slot s, step st -> rows gen0 + s S + (0 .. st)
+        steps = torch.arange(1, S + 1, dtype=torch.int64)
+        self.cu_all = (steps[:, None] * torch.arange(n + 1, dtype=torch.int64)[None, :]).contiguous().to(device)  # [S, n + 1]
+        idx_all = torch.zeros((S, n * S), dtype=torch.int64)
         for st in range(S):
-            parts = [torch.cat([slot_t0[s] + torch.arange(int(slot_T[s])), self.gen0 + s * S + torch.arange(st + 1)]) for s in range(n)]
-            row = torch.cat(parts)
-            idx_all[st, : row.numel()] = row
+            idx_all[st, : n * (st + 1)] = (self.gen0 + s_ar[:, None] * S + torch.arange(st + 1)[None, :]).reshape(-1)
         self.idx_all = idx_all.to(device)
         self.gen_row0 = (self.gen0 + s_ar * S).to(device)
         # static buffers of a step
@@ -302,8 +312,13 @@ class HybridDecoder(Decoder):
         self.cv[x].index_copy_(0, self.cur_rows, v)
         self.cg[x].index_copy_(0, self.cur_rows, g)
         self.cb[x].index_copy_(0, self.cur_rows, beta)
-        gdn.recurrent(self.cq[x], self.ck[x], self.cv[x], self.cg[x], self.cb[x], cfg.dk**-0.5, self.cu_buf, n, h0=self.h0[x], h0_idx=self.h0_idx,
-                      idx=self.idx_buf, o=self.o_buf)
+        rows = (self.cq[x], self.ck[x], self.cv[x], self.cg[x], self.cb[x])
+        if self.gen0:
+            gdn.recurrent(*rows, cfg.dk**-0.5, self.t_cu, self.t_cu.numel() - 1, h0=self.h0[x], h0_idx=self.t_h0_idx, ht=self.ht,
+                          ht_idx=self.t_ht_idx, o=self.o_buf)
+            gdn.recurrent(*rows, cfg.dk**-0.5, self.cu_buf, n, h0=self.ht, h0_idx=self.slot_prompt, idx=self.idx_buf, o=self.o_buf)
+        else:  # no prompt has template tokens: the slots start from their groups' prefix states
+            gdn.recurrent(*rows, cfg.dk**-0.5, self.cu_buf, n, h0=self.h0[x], h0_idx=self.h0_idx, idx=self.idx_buf, o=self.o_buf)
         return self.o_buf.index_select(0, self.cur_rows), z
 
     def _step_once(self):

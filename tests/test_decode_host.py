@@ -87,13 +87,16 @@ def test_hybrid_decoder_tables_and_reorder():
     dec, cd = _fake_hybrid(beam)
     n, S = dec.n, dec.S
     assert (dec.G, dec.Q, S, n) == (2, 4, 4, 8) and dec.gen0 == 9 and dec.R == 9 + n * S
-    slot_T, slot_t0 = [3, 3, 2, 2, 4, 4, 0, 0], [0, 0, 3, 3, 5, 5, 0, 0]  # group 1 has one prompt: its last two slots are padding
+    # the templates' call: one segment per prompt slot (group 1 has one prompt: its second slot has no rows and passes the
+    # prefix state on), from the group's prefix state into the prompt's entry of `ht`
+    assert dec.t_cu.tolist() == [0, 3, 5, 9, 9] and dec.t_h0_idx.tolist() == [0, 0, 1, 1] and dec.t_ht_idx.tolist() == [0, 1, 2, 3]
+    assert dec.ht.shape[0] == 4 and dec.slot_prompt.tolist() == [0, 0, 1, 1, 2, 2, 3, 3]
+    # the slots' call: every slot's generated rows 0 .. step, from its prompt's entry
     for st in range(S):
         cu = dec.cu_all[st].tolist()
-        assert cu[0] == 0 and [cu[s + 1] - cu[s] for s in range(n)] == [t + st + 1 for t in slot_T]
+        assert cu == [s * (st + 1) for s in range(n + 1)]
         for s in range(n):
-            rows = dec.idx_all[st, cu[s] : cu[s + 1]].tolist()
-            assert rows == list(range(slot_t0[s], slot_t0[s] + slot_T[s])) + [dec.gen0 + s * S + k for k in range(st + 1)]
+            assert dec.idx_all[st, cu[s] : cu[s + 1]].tolist() == [dec.gen0 + s * S + k for k in range(st + 1)]
     assert dec.h0_idx.tolist() == [0, 0, 0, 0, 1, 1, 1, 1] and float(dec.h0[0, 1, 0, 0, 0]) == 2.0
     assert dec.conv_idx[3].tolist() == [n + 9, n + 10, n + 11, 3]
     ring = dec.ybuf[0, n:].view(n, 3, -1)
