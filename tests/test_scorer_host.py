@@ -151,6 +151,41 @@ def test_a_failure_in_the_gpu_loop_cancels_the_packing_thread(error):
     check(good.score_grouped(items), truth)
 
 
+def test_a_failed_call_keeps_none_of_its_extraction_captures():
+    """a forward fails after earlier forwards of the call left captures with the extractor: the error reaches the caller, the held
+    captures are dropped and the stack is told to close its capture; a call that succeeds decodes what it held at its end"""
+    calls = []
+
+    class FakeExtractor:
+        found = {}
+
+        def __init__(self):
+            self.held = ["captures of the first forward"]
+
+        def flush(self):
+            calls.append(("flush", list(self.held)))
+            self.held = []
+
+        def drop(self):
+            calls.append(("drop", list(self.held)))
+            self.held = []
+
+        tree_bytes = staticmethod(lambda tree: 0)
+
+    items, truth = jobs(60)
+    sc = make_scorer(n_blocks=2, fail_at=2, error=RuntimeError("launch failed"))
+    sc.extractor = FakeExtractor()
+    sc.stack.abandon = lambda s: calls.append(("abandon", s is sc))
+    with pytest.raises(RuntimeError, match="launch failed"):
+        sc.score_grouped(items)
+    assert calls == [("drop", ["captures of the first forward"]), ("abandon", True)] and sc.extractor.held == []
+    calls.clear()
+    good = make_scorer(n_blocks=2)
+    good.extractor = FakeExtractor()
+    check(good.score_grouped(items), truth)
+    assert calls == [("flush", ["captures of the first forward"])] and good.x_found == {}
+
+
 def test_results_are_handed_over_in_launch_order_and_at_most_lag_stay_back():
     class Later(Done):
         def __init__(self):
