@@ -70,7 +70,9 @@ struct W4Args {
 // TOK: tokens per tile = the MMA's N: 256, or 64 for calls of at most 64 rows (a decoding step), where a 256-wide product would
 // spend four times the tensor-pipe time on rows that do not exist; each CTA then loads 32 token rows per stage and the epilogue
 // has one 64-token chunk. An output element's sum over K is the same sequence of products either way.
-template <int ACT, int TOK>
+// COARSE: the scale group is a multiple of the 64-wide K step (one scale per step, known at compile time so that the expansion loop
+// has no branch in it).
+template <int ACT, int TOK, bool COARSE>
 __global__ void __launch_bounds__(448, 1)
 w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmC,
                const W4Args a, int* __restrict__ status) {
@@ -179,7 +181,7 @@ w4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint32_t it = 0;
     bool ok = true;
     const int groups = a.K / a.G;
-    const bool coarse = a.G % 64 == 0;
+    constexpr bool coarse = COARSE;
     const uint32_t b_full_leader = map_to_cta(b_full, 0);
     for (int tile = pair0; tile < num_tiles && ok; tile += pair_step) {
       int tm, tn;
@@ -447,11 +449,15 @@ static int launch_w4(const void* x, const void* qw, const void* scales, int32_t 
     const int64_t g = (32ll << 20) / per_tile;
     a.group_m = static_cast<int>(g < 4 ? 4 : (g > 32 ? 32 : g));
   }
-  auto kern = TOK == 64 ? w4_gemm_kernel<ACT, 64> : w4_gemm_kernel<ACT, 256>;
+  const bool coarse = group % 64 == 0;
+  auto kern = TOK == 64 ? (coarse ? w4_gemm_kernel<ACT, 64, true> : w4_gemm_kernel<ACT, 64, false>)
+                        : (coarse ? w4_gemm_kernel<ACT, 256, true> : w4_gemm_kernel<ACT, 256, false>);
   static std::atomic<bool> attr_set[64];  // zero-initialised; setting the attribute twice from two threads is harmless
   if (!attr_set[dev].load(std::memory_order_acquire)) {
-    SPINF_CUDA_OK(cudaFuncSetAttribute(w4_gemm_kernel<ACT, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, W4Smem<256>::TOTAL));
-    SPINF_CUDA_OK(cudaFuncSetAttribute(w4_gemm_kernel<ACT, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, W4Smem<256>::TOTAL));
+    SPINF_CUDA_OK(cudaFuncSetAttribute(w4_gemm_kernel<ACT, 64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, W4Smem<256>::TOTAL));
+    SPINF_CUDA_OK(cudaFuncSetAttribute(w4_gemm_kernel<ACT, 64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, W4Smem<256>::TOTAL));
+    SPINF_CUDA_OK(cudaFuncSetAttribute(w4_gemm_kernel<ACT, 256, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, W4Smem<256>::TOTAL));
+    SPINF_CUDA_OK(cudaFuncSetAttribute(w4_gemm_kernel<ACT, 256, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, W4Smem<256>::TOTAL));
     attr_set[dev].store(true, std::memory_order_release);
   }
   const int tiles = a.tiles_m * a.tiles_n * a.splits;
